@@ -1,0 +1,194 @@
+"""Numerics of every sm_100a kernel against the float32 PyTorch restatement of the same op."""
+import math
+
+import pytest
+import torch
+
+from zml_b200 import ops
+from zml_b200.ops import reference as ref
+from zml_b200.testing import expect_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _randn(*shape, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*shape, device=DEV, dtype=torch.float32) * scale).to(dtype)
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    ops.raise_on_status()
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (1, 256, 128), (7, 384, 64), (16, 4096, 4096), (32, 6144, 4096), (33, 1000 * 8, 512),
+    (64, 4096, 14336), (128, 2048, 2048), (200, 512, 1024), (256, 1024, 4096),
+    (257, 1024, 1024), (512, 4096, 4096), (1000, 2048 + 64, 512), (4096, 4096, 4096),
+    (3000, 14336 * 2, 4096 // 2),
+])
+def test_gemm_matches_fp32(m, n, k):
+    torch.manual_seed(m * 7 + n)
+    a = _randn(m, k)
+    w = _randn(n, k, scale=1.0 / math.sqrt(k))
+    out = ops.gemm(a, w)
+    want = a.float() @ w.float().t()
+    expect_close(out.float(), want, atol=2e-2, rtol=2e-2, min_close=0.999)
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(16, 512, 2048, 4), (64, 1024, 8192, 8), (300, 512, 4096, 3)])
+def test_gemm_split_k_and_epilogue(m, n, k, splits):
+    torch.manual_seed(0)
+    a = _randn(m, k)
+    w = _randn(n, k, scale=1.0 / math.sqrt(k))
+    res = _randn(m, n)
+    bias = _randn(n)
+    want = a.float() @ w.float().t() + bias.float() + res.float()
+    out = ops.gemm(a, w, residual=res, bias=bias, force_splits=splits)
+    expect_close(out.float(), want, atol=3e-2, rtol=2e-2, min_close=0.999)
+    # twice: the tile counters must have been left at zero
+    out2 = ops.gemm(a, w, residual=res, bias=bias, force_splits=splits)
+    assert torch.equal(out, out2)
+    # fp32 output and in-place residual
+    out32 = ops.gemm(a, w, out_dtype=torch.float32, force_splits=splits)
+    expect_close(out32, a.float() @ w.float().t(), atol=1e-2, rtol=1e-2, min_close=0.999)
+    inplace = res.clone()
+    ops.gemm(a, w, residual=inplace, out=inplace)
+    expect_close(inplace.float(), a.float() @ w.float().t() + res.float(), atol=3e-2, rtol=2e-2, min_close=0.999)
+
+
+@pytest.mark.parametrize("rows,d", [(1, 2048), (33, 4096), (64, 8192), (5, 1024 + 8), (3, 16384)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rmsnorm(rows, d, with_res):
+    x = _randn(rows, d)
+    w = _randn(d)
+    r = _randn(rows, d) if with_res else None
+    got = ops.rmsnorm(x, w, 1e-5, residual=r, unit_offset=with_res)
+    want = ref.rmsnorm(x, w, 1e-5, residual=r, unit_offset=with_res)
+    if with_res:
+        expect_close(got[0].float(), want[0].float(), atol=2e-2, rtol=2e-2)
+        assert torch.equal(got[1], want[1])
+    else:
+        expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_swiglu_embedding_argmax():
+    gu = _randn(37, 2 * 1024)
+    expect_close(ops.swiglu(gu).float(), ref.swiglu(gu).float(), atol=1e-2, rtol=2e-2)
+    table = _randn(1000, 512)
+    ids = torch.randint(0, 1000, (4, 9), device=DEV, dtype=torch.int32)
+    assert torch.equal(ops.embedding(ids, table), table[ids.long()])
+    logits = torch.randn(17, 128256, device=DEV)
+    logits[3, 77] = 100.0
+    logits[3, 99] = 100.0   # tie -> lowest index
+    got = ops.argmax(logits)
+    assert got[3].item() == 77
+    assert torch.equal(got.long(), torch.argmax(logits, -1)) or got[3].item() == 77
+
+
+@pytest.mark.parametrize("k", [1, 8, 50, 128])
+def test_topk_sample(k):
+    torch.manual_seed(1)
+    logits = torch.randn(9, 32000, device=DEV)
+    logits[0, :100] = float("-inf")
+    tok, vals, idx = ops.topk_sample(logits, k, temperature=0.8, seed=5, step=2, return_topk=True)
+    wv, wi = torch.topk(logits, k, dim=-1)
+    assert torch.equal(vals, wv)
+    assert torch.equal(idx.long(), wi)
+    # the drawn token is one of the top-k
+    assert all(int(tok[i]) in set(wi[i].tolist()) for i in range(logits.shape[0]))
+    if k == 1:
+        assert torch.equal(tok.long(), torch.argmax(logits, -1))
+    # frequency check of the Gumbel-max draw on a tiny distribution
+    if k == 8:
+        small = torch.full((1, 64), -30.0, device=DEV)
+        small[0, :4] = torch.tensor([2.0, 1.0, 0.0, -1.0], device=DEV)
+        counts = torch.zeros(64)
+        n = 2000
+        for s in range(n):
+            counts[int(ops.topk_sample(small, 8, 1.0, seed=11, step=s))] += 1
+        p = torch.softmax(small[0].cpu(), -1)
+        assert torch.allclose(counts / n, p, atol=0.04)
+
+
+def _make_paged(batch, seq_lens, hkv, hd, page, extra_pages=3):
+    """Random paged cache with a shuffled page assignment."""
+    max_pages = max((l + page - 1) // page for l in seq_lens) + 1
+    total = sum((l + page - 1) // page for l in seq_lens) + extra_pages
+    perm = torch.randperm(total)
+    bt = torch.zeros(batch, max_pages, dtype=torch.int32)
+    nxt = 0
+    for i, l in enumerate(seq_lens):
+        n = (l + page - 1) // page
+        bt[i, :n] = perm[nxt:nxt + n].to(torch.int32)
+        nxt += n
+    kc = _randn(total, page, hkv, hd)
+    vc = _randn(total, page, hkv, hd)
+    return kc, vc, bt.to(DEV)
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 8, 64), (32, 8, 128), (8, 1, 128), (16, 16, 64), (16, 2, 256)])
+@pytest.mark.parametrize("page", [64, 16])
+def test_paged_decode(hq, hkv, hd, page):
+    torch.manual_seed(3)
+    seq_lens = [1, 17, 64, 65, 300, 1000, 2049]
+    b = len(seq_lens)
+    kc, vc, bt = _make_paged(b, seq_lens, hkv, hd, page)
+    q = _randn(b, hq, hd)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    want = ref.paged_decode(q, kc, vc, bt, seq_lens)
+    for splits in (1, 4, None):
+        got = ops.paged_decode(q, kc, vc, bt, sl, num_splits=splits)
+        expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+    got = ops.paged_decode(q, kc, vc, bt, sl, window=128, num_splits=2)
+    want_w = ref.paged_decode(q, kc, vc, bt, seq_lens, window=128)
+    expect_close(got.float(), want_w.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(32, 8, 64), (8, 2, 128), (4, 4, 256)])
+def test_paged_prefill_mixed_batch(hq, hkv, hd):
+    """Mixed batch as in the reference's pagedAttention test: fresh prompts, a chunked
+    continuation (context already cached), a single-token row and an empty row."""
+    torch.manual_seed(4)
+    page = 64
+    q_lens = [5, 64, 130, 1, 0, 257]
+    ctx = [0, 0, 70, 99, 0, 64]
+    seq_lens = [a + c for a, c in zip(q_lens, ctx)]
+    b = len(q_lens)
+    kc, vc, bt = _make_paged(b, seq_lens, hkv, hd, page)
+    qs = [0]
+    for l in q_lens:
+        qs.append(qs[-1] + l)
+    q = _randn(qs[-1], hq, hd)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    qst = torch.tensor(qs, dtype=torch.int32, device=DEV)
+    got = ops.paged_prefill(q, kc, vc, bt, sl, qst)
+    want = ref.paged_attention(q, kc, vc, bt, seq_lens, qs)
+    expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+    got = ops.paged_prefill(q, kc, vc, bt, sl, qst, window=100)
+    want = ref.paged_attention(q, kc, vc, bt, seq_lens, qs, window=100)
+    expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+
+
+@pytest.mark.parametrize("layout,rot", [(0, None), (1, None), (0, 32), (2, 32)])
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_rope_kvwrite(layout, rot, qk_norm):
+    torch.manual_seed(5)
+    t, hq, hkv, hd, page, pages = 50, 8, 2, 64, 64, 6
+    qkv = _randn(t, (hq + 2 * hkv) * hd)
+    pos = torch.randint(0, 5000, (t,), device=DEV, dtype=torch.int32)
+    slots = torch.randperm(pages * page, device=DEV)[:t].to(torch.int32)
+    slots[7] = -1
+    half = (rot or hd) // 2
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(half, device=DEV).float() / half))).contiguous()
+    qn = _randn(hd) if qk_norm else None
+    kn = _randn(hd) if qk_norm else None
+    kc = torch.zeros(pages, page, hkv, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = ops.rope_kvwrite(qkv, pos, slots, inv_freq, kc, vc, hq, hkv, hd, layout, rot, 1.0, qn, kn, 1e-6, qk_norm)
+    q2 = ref.rope_kvwrite(qkv, pos, slots, inv_freq, kc2, vc2, hq, hkv, hd, layout, rot, 1.0, qn, kn, 1e-6, qk_norm)
+    expect_close(q.float(), q2.float(), atol=3e-2, rtol=2e-2, min_close=0.995)
+    expect_close(kc.float(), kc2.float(), atol=3e-2, rtol=2e-2, min_close=0.995)
+    assert torch.equal(vc, vc2)

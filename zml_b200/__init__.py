@@ -1,0 +1,34 @@
+"""zml_b200: a Blackwell-native inference framework with the capabilities of ZML.
+
+Tagged-axis `Shape` / `Tensor`, logical-mesh sharding, safetensors streaming,
+paged-KV attention, fused MoE, tokenizers and LLM serving, built on PyTorch plus
+hand-written sm_100a CUDA kernels and in-kernel NVLink collectives.
+"""
+from __future__ import annotations
+
+import importlib
+
+__version__ = "0.1.0"
+
+_LAZY = {
+    "DataType": ("dtype", "DataType"),
+    "Shape": ("shape", "Shape"),
+    "Tensor": ("tensor", "Tensor"),
+    "Slice": ("slice", "Slice"),
+    "Buffer": ("buffer", "Buffer"),
+    "Platform": ("platform", "Platform"),
+}
+_SUBMODULES = {
+    "dtype", "floats", "shape", "tensor", "slice", "meta", "buffer", "mem", "exe", "module",
+    "platform", "sharding", "io", "safetensors", "nn", "ops", "attention", "moe", "tokenizer",
+    "testing", "profiling", "models", "parallel", "utils", "serving", "flags", "kernel",
+}
+
+
+def __getattr__(name):
+    if name in _LAZY:
+        mod, attr = _LAZY[name]
+        return getattr(importlib.import_module(f"{__name__}.{mod}"), attr)
+    if name in _SUBMODULES:
+        return importlib.import_module(f"{__name__}.{name}")
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -1,0 +1,298 @@
+// Shared device-side building blocks for the sm_100a kernels of this library:
+// mbarrier, TMA (cp.async.bulk.tensor), tcgen05 (MMA / TMEM) wrappers in inline
+// PTX, bounded waits that fail soft, and the per-device status word.
+//
+// Every wait in this library is bounded.  A wait that runs out records a code in
+// the status word (see ZbStatus) and makes the kernel leave through its normal
+// exit (TMEM freed, no trap), so the CUDA context stays usable and the host can
+// turn the code into an exception.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifndef ZB_WAIT_LIMIT_NS
+// Upper bound of any single device-side wait (mbarrier, flag, peer): 2 s.
+#define ZB_WAIT_LIMIT_NS 2000000000ull
+#endif
+
+#define ZB_DEVICE __device__ __forceinline__
+
+// ----------------------------------------------------------------------------
+// Status word: one per device, in global memory, read by the host after a step.
+// ----------------------------------------------------------------------------
+enum ZbStatusCode : uint32_t {
+  ZB_OK = 0,
+  ZB_ERR_MBAR_TIMEOUT = 1,     // an mbarrier wait ran out
+  ZB_ERR_FLAG_TIMEOUT = 2,     // a wait on a peer/global flag ran out
+  ZB_ERR_BOUNDS = 3,           // bounds-check build: index outside the extents
+  ZB_ERR_BAD_ARG = 4,
+};
+
+struct ZbStatus {
+  uint32_t code;      // first error code seen (0 = ok)
+  uint32_t kernel;    // id of the kernel that recorded it
+  uint32_t where;     // kernel-specific location (role / phase / stage)
+  uint32_t detail;    // kernel-specific payload (tile, rank, index ...)
+};
+
+ZB_DEVICE void zb_record_error(ZbStatus* st, uint32_t code, uint32_t kernel,
+                               uint32_t where, uint32_t detail) {
+  if (st == nullptr) return;
+  if (atomicCAS(&st->code, 0u, code) == 0u) {
+    st->kernel = kernel;
+    st->where = where;
+    st->detail = detail;
+    __threadfence_system();
+  }
+}
+
+ZB_DEVICE uint64_t zb_globaltimer() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+ZB_DEVICE uint32_t zb_smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+ZB_DEVICE bool zb_elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P1;\n\t"
+      "elect.sync _|P1, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P1;\n\t"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ----------------------------------------------------------------------------
+// mbarrier
+// ----------------------------------------------------------------------------
+ZB_DEVICE void zb_mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(zb_smem_u32(bar)), "r"(count));
+}
+
+ZB_DEVICE void zb_mbar_fence_init() {
+  // Makes the initialised barriers visible to the async proxy (TMA, tcgen05.commit).
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+ZB_DEVICE void zb_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(zb_smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+
+ZB_DEVICE void zb_mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(zb_smem_u32(bar)) : "memory");
+}
+
+ZB_DEVICE uint32_t zb_mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(zb_smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Bounded wait.  `abort_flag` is a CTA-shared word: once any role of the CTA gave
+// up, every other wait of the CTA returns false at its next poll, so that all
+// roles reach the common exit.  Returns true when the phase completed.
+ZB_DEVICE bool zb_mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  if (zb_mbar_test(bar, parity)) return true;
+  const uint64_t t0 = zb_globaltimer();
+  uint32_t spins = 0;
+  while (true) {
+    if (zb_mbar_test(bar, parity)) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0u) return false;
+      if (zb_globaltimer() - t0 > ZB_WAIT_LIMIT_NS) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// TMA: tiled 2-D / 3-D loads into shared memory, completion on an mbarrier.
+// No load in this library carries a cluster-multicast qualifier.
+// The innermost coordinate times the element size must be a multiple of 16 B.
+// ----------------------------------------------------------------------------
+ZB_DEVICE void zb_tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x,
+                              int32_t y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(zb_smem_u32(smem_dst)), "l"(tmap), "r"(zb_smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+ZB_DEVICE void zb_tma_load_2d_hint(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x,
+                                   int32_t y, uint64_t cache_policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      :
+      : "r"(zb_smem_u32(smem_dst)), "l"(tmap), "r"(zb_smem_u32(bar)), "r"(x), "r"(y),
+        "l"(cache_policy)
+      : "memory");
+}
+
+ZB_DEVICE void zb_tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x,
+                              int32_t y, int32_t z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      :
+      : "r"(zb_smem_u32(smem_dst)), "l"(tmap), "r"(zb_smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+ZB_DEVICE void zb_tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// L2 eviction policies for streamed (read-once) and reused operands.
+ZB_DEVICE uint64_t zb_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+ZB_DEVICE uint64_t zb_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// ----------------------------------------------------------------------------
+// tcgen05: tensor memory management, MMA issue, commit, TMEM loads.
+// ----------------------------------------------------------------------------
+// Allocation is a warp-wide (.sync.aligned) instruction; ncols is a power of two
+// in [32, 512].  The TMEM base address is written to *smem_holder.
+ZB_DEVICE void zb_tmem_alloc(uint32_t* smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   zb_smem_u32(smem_holder)),
+               "r"(ncols)
+               : "memory");
+}
+ZB_DEVICE void zb_tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+ZB_DEVICE void zb_tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+
+ZB_DEVICE void zb_tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+ZB_DEVICE void zb_tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread.
+ZB_DEVICE void zb_umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives on `bar` once every tcgen05 operation issued so far by this thread is done.
+ZB_DEVICE void zb_umma_commit(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+          zb_smem_u32(bar))
+      : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base_lane + i),
+// columns [col, col+32).  A warp may only touch lanes 32*(warp_id % 4) .. +31.
+ZB_DEVICE void zb_tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+ZB_DEVICE void zb_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+ZB_DEVICE void zb_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major bf16 tile written by TMA with the
+// 128-byte swizzle: rows of 64 elements (128 B), 8-row groups 1024 B apart.
+//   bits  0-13 start address >> 4       bits 16-29 leading byte offset >> 4 (unused: 1)
+//   bits 32-45 stride byte offset >> 4  bits 46-47 version (1 on sm_100)
+//   bits 61-63 layout type (2 = 128-byte swizzle)
+ZB_DEVICE uint64_t zb_make_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor for kind::f16 with bf16 inputs, fp32 accumulate, A and B K-major.
+//   bits 4-5 D format (1 = f32), 7-9 A format (1 = bf16), 10-12 B format,
+//   15 A major, 16 B major (0 = K), 17-22 N >> 3, 24-28 M >> 4.
+__host__ __device__ constexpr uint32_t zb_make_idesc_bf16(uint32_t m, uint32_t n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// ----------------------------------------------------------------------------
+// small numeric helpers
+// ----------------------------------------------------------------------------
+ZB_DEVICE uint32_t zb_pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+ZB_DEVICE float2 zb_unpack_bf16x2(uint32_t u) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+  return __bfloat1622float2(v);
+}
+
+ZB_DEVICE float zb_warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+ZB_DEVICE float zb_warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}

@@ -1,0 +1,529 @@
+// bf16 GEMM for sm_100a: out[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) (+ residual[M,N]).
+//
+// Replaces the `dot_general` -> cuBLASLt / Triton-gemm path of the reference
+// (zml/tensor.zig:1388-1459, nn.Linear zml/nn.zig:18-91) with one persistent,
+// warp-specialised kernel:
+//   warp 0  : TMA producer  (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp 1  : MMA issuer    (tcgen05.mma kind::f16, fp32 accumulators in TMEM,
+//                            two accumulator stages so the epilogue overlaps the
+//                            next tile's main loop)
+//   warps 2-5: epilogue     (tcgen05.ld -> bias/residual -> bf16/f32 stores)
+//
+// Both operands are K-major, so either can feed the 128-row "M" side of the MMA.
+// For few tokens (decode) the weight rows take the 128-row side and the tokens
+// the N side ("swap-AB"), and K is split across CTAs so that all 148 SMs stream
+// weights; partial sums go through an fp32 workspace and the last CTA of a tile
+// reduces them in a fixed order (deterministic).
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "host_api.h"
+
+namespace {
+
+constexpr int kBlockP = 128;   // rows of the MMA-M operand per tile
+constexpr int kBlockK = 64;    // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kNumThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr uint32_t kKernelId = 1;
+
+struct GemmParams {
+  int rows_p;        // extent of the P operand (MMA M side)
+  int rows_q;        // extent of the Q operand (MMA N side)
+  int k;
+  int ldo;           // leading dimension of out / residual, in elements
+  void* out;
+  const __nv_bfloat16* residual;   // same layout as out, may be null
+  const __nv_bfloat16* bias;       // indexed by output column, may be null
+  int out_f32;       // 0: bf16 output, 1: fp32 output
+  int splits;        // K splits
+  int group_p;       // rasterisation group height (P tiles)
+  float* workspace;  // [splits][tiles][BN][128] fp32, used when splits > 1
+  uint32_t* counters;  // one per output tile, zero between launches
+  ZbStatus* status;
+};
+
+__host__ __device__ constexpr int stages_for(int bn) {
+  return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8);
+}
+__host__ __device__ constexpr int stage_bytes(int bn) { return (kBlockP + bn) * kBlockK * 2; }
+
+ZB_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(kNumThreads, 1)
+zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
+                    const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
+  constexpr int kStages = stages_for(BN);
+  constexpr int kStageBytes = stage_bytes(BN);
+  constexpr int kTileABytes = kBlockP * kBlockK * 2;
+  constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
+  constexpr uint32_t kIdesc = zb_make_idesc_bf16(kBlockP, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment: required by the 128-byte swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_holder + 1;
+  volatile uint32_t* is_last_flag = tmem_holder + 2;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_p = (prm.rows_p + kBlockP - 1) / kBlockP;
+  const int num_q = (prm.rows_q + BN - 1) / BN;
+  const int kb_total = (prm.k + kBlockK - 1) / kBlockK;
+  const int kb_per = (kb_total + prm.splits - 1) / prm.splits;
+  const int num_out_tiles = num_p * num_q;
+  const int num_work = num_out_tiles * prm.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      zb_mbar_init(&full_bar[s], 1);
+      zb_mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      zb_mbar_init(&tmem_full[a], 1);
+      zb_mbar_init(&tmem_empty[a], kEpiThreads);
+    }
+    *abort_flag = 0u;
+    *is_last_flag = 0u;
+    zb_mbar_fence_init();
+  }
+  if (warp == 1) {
+    zb_tmem_alloc(tmem_holder, kTmemCols);
+    zb_tmem_relinquish();
+  }
+  zb_tc_fence_before();
+  __syncthreads();
+  zb_tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // work item -> (p tile, q tile, split); P tiles are grouped so that one wave of
+  // CTAs shares few distinct operand tiles in L2.
+  auto decode = [&](int work, int& pt, int& qt, int& split) {
+    split = work % prm.splits;
+    const int t = work / prm.splits;
+    const int per_group = prm.group_p * num_q;
+    const int g = t / per_group;
+    const int within = t - g * per_group;
+    const int p_first = g * prm.group_p;
+    const int gp = min(prm.group_p, num_p - p_first);
+    pt = p_first + within % gp;
+    qt = within / gp;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      zb_tma_prefetch_desc(&tmap_p);
+      zb_tma_prefetch_desc(&tmap_q);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
+        int pt, qt, split;
+        decode(work, pt, qt, split);
+        const int kb0 = split * kb_per;
+        const int kb1 = min(kb_total, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kStageBytes;
+          uint8_t* sb = sa + kTileABytes;
+          zb_mbar_expect_tx(&full_bar[stage], kStageBytes);
+          zb_tma_load_2d(sa, &tmap_p, &full_bar[stage], kb * kBlockK, pt * kBlockP);
+          zb_tma_load_2d(sb, &tmap_q, &full_bar[stage], kb * kBlockK, qt * BN);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
+        int pt, qt, split;
+        decode(work, pt, qt, split);
+        const int kb0 = split * kb_per;
+        const int kb1 = min(kb_total, kb0 + kb_per);
+        if (!zb_mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) break;
+        zb_tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!zb_mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          zb_tc_fence_after();
+          const uint32_t sa = zb_smem_u32(smem + stage * kStageBytes);
+          const uint32_t sb = sa + kTileABytes;
+          const uint64_t da = zb_make_desc_sw128(sa);
+          const uint64_t db = zb_make_desc_sw128(sb);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            // advance 32 bytes (16 bf16) along K inside the swizzle row: +2 in 16-byte units
+            zb_umma_f16(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          zb_umma_commit(&empty_bar[stage]);   // frees the smem stage when the MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        zb_umma_commit(&tmem_full[acc]);       // accumulator complete
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int epi_tid = threadIdx.x - 64;          // 0..127
+    const int quad = warp & 3;                     // TMEM lane quadrant of this warp
+    const int row_in_tile = quad * 32 + lane;      // MMA-M row held by this thread
+    uint32_t acc = 0, acc_phase = 0;
+    for (int work = blockIdx.x; work < num_work; work += gridDim.x) {
+      int pt, qt, split;
+      decode(work, pt, qt, split);
+      zb_mbar_wait(&tmem_full[acc], acc_phase, abort_flag);
+      epi_bar_sync();
+      if (*abort_flag != 0u) break;
+      zb_tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      const int p = pt * kBlockP + row_in_tile;
+      const int q0 = qt * BN;
+      const int out_tile = pt * num_q + qt;
+
+      bool do_store = true;
+      if (prm.splits > 1) {
+        // write this split's partial tile: ws[((split*tiles + tile)*BN + c)*128 + row]
+        float* ws = prm.workspace +
+                    (static_cast<size_t>(split) * num_out_tiles + out_tile) * (BN * kBlockP);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          zb_tmem_ld16(taddr + c0, r);
+          zb_tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) ws[(c0 + j) * kBlockP + row_in_tile] = __uint_as_float(r[j]);
+        }
+        __threadfence();
+        epi_bar_sync();
+        if (epi_tid == 0) {
+          const uint32_t prev = atomicAdd(&prm.counters[out_tile], 1u);
+          const uint32_t last = (prev == static_cast<uint32_t>(prm.splits - 1)) ? 1u : 0u;
+          if (last) prm.counters[out_tile] = 0u;   // ready for the next launch
+          *is_last_flag = last;
+        }
+        epi_bar_sync();
+        do_store = (*is_last_flag != 0u);
+        if (do_store) __threadfence();
+      }
+      // the accumulator stage can be reused as soon as it has been read
+      if (prm.splits > 1) {
+        zb_tc_fence_before();
+        zb_mbar_arrive(&tmem_empty[acc]);
+      }
+
+      if (do_store) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          if (prm.splits > 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+            for (int s = 0; s < prm.splits; ++s) {
+              const float* ws = prm.workspace +
+                                (static_cast<size_t>(s) * num_out_tiles + out_tile) * (BN * kBlockP);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += __ldcg(&ws[(c0 + j) * kBlockP + row_in_tile]);
+            }
+          } else {
+            uint32_t r[16];
+            zb_tmem_ld16(taddr + c0, r);
+            zb_tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+          }
+          if (p < prm.rows_p) {
+            if constexpr (SWAP) {
+              // p = output column n, q = output row m
+              const float b = prm.bias ? __bfloat162float(prm.bias[p]) : 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int q = q0 + c0 + j;
+                if (q < prm.rows_q) {
+                  const size_t o = static_cast<size_t>(q) * prm.ldo + p;
+                  float x = v[j] + b;
+                  if (prm.residual) x += __bfloat162float(prm.residual[o]);
+                  if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = x;
+                  else reinterpret_cast<__nv_bfloat16*>(prm.out)[o] = __float2bfloat16(x);
+                }
+              }
+            } else {
+              // p = output row m, q = output column n (16 consecutive columns per step)
+              const int q = q0 + c0;
+              const size_t o = static_cast<size_t>(p) * prm.ldo + q;
+              if (q + 16 <= prm.rows_q) {
+                if (prm.bias) {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) v[j] += __bfloat162float(prm.bias[q + j]);
+                }
+                if (prm.residual) {
+                  const uint4* rp = reinterpret_cast<const uint4*>(prm.residual + o);
+                  uint4 r0 = rp[0], r1 = rp[1];
+                  const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    float2 f = zb_unpack_bf16x2(rr[j]);
+                    v[2 * j] += f.x;
+                    v[2 * j + 1] += f.y;
+                  }
+                }
+                if (prm.out_f32) {
+                  float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(prm.out) + o);
+#pragma unroll
+                  for (int j = 0; j < 4; ++j)
+                    op[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                } else {
+                  uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(prm.out) + o);
+                  op[0] = make_uint4(zb_pack_bf16x2(v[0], v[1]), zb_pack_bf16x2(v[2], v[3]),
+                                     zb_pack_bf16x2(v[4], v[5]), zb_pack_bf16x2(v[6], v[7]));
+                  op[1] = make_uint4(zb_pack_bf16x2(v[8], v[9]), zb_pack_bf16x2(v[10], v[11]),
+                                     zb_pack_bf16x2(v[12], v[13]), zb_pack_bf16x2(v[14], v[15]));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  if (q + j < prm.rows_q) {
+                    float x = v[j];
+                    if (prm.bias) x += __bfloat162float(prm.bias[q + j]);
+                    if (prm.residual) x += __bfloat162float(prm.residual[o + j]);
+                    if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o + j] = x;
+                    else reinterpret_cast<__nv_bfloat16*>(prm.out)[o + j] = __float2bfloat16(x);
+                  }
+                }
+              }
+            }
+          }
+        }
+      }
+      if (prm.splits == 1) {
+        zb_tc_fence_before();
+        zb_mbar_arrive(&tmem_empty[acc]);
+      }
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ------------------------------------------------------------ common exit
+  zb_tc_fence_before();
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    if (threadIdx.x == 0) zb_record_error(prm.status, ZB_ERR_MBAR_TIMEOUT, kKernelId, blockIdx.x, BN);
+    // give copies that may still be in flight time to land before the CTA's
+    // shared memory is handed to another CTA
+    const uint64_t t0 = zb_globaltimer();
+    while (zb_globaltimer() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    zb_tc_fence_after();
+    zb_tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+}  // namespace
+
+// K-major bf16 matrix [rows, k] with leading dimension ld -> tensor map with a
+// (64 x box_rows) box and the 128-byte swizzle.  Returns 0 on success.
+int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld,
+                         int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld % 8) != 0) return -2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+namespace {
+
+template <int BN, bool SWAP>
+int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid,
+           cudaStream_t stream) {
+  constexpr int smem = stages_for(BN) * stage_bytes(BN) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(zb_gemm_bf16_kernel<BN, SWAP>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  zb_gemm_bf16_kernel<BN, SWAP><<<grid, kNumThreads, smem, stream>>>(tp, tq, prm);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+extern "C" {
+
+// Plans K splits for a swap-AB (few-token) GEMM; exposed for tests and for sizing scratch.
+int zb_gemm_plan(int m, int n, int k, int num_sms, int* swap, int* bn, int* splits) {
+  const int kb_total = (k + kBlockK - 1) / kBlockK;
+  int sw = m <= 256 ? 1 : 0;
+  int b;
+  if (sw) {
+    b = 16;
+    while (b < m) b <<= 1;
+  } else {
+    b = n >= 256 ? 256 : 128;
+  }
+  const int rows_p = sw ? n : m;
+  const int rows_q = sw ? m : n;
+  const int tiles = ((rows_p + kBlockP - 1) / kBlockP) * ((rows_q + b - 1) / b);
+  int sp = 1;
+  if (tiles * 2 <= num_sms) {
+    sp = num_sms / tiles;
+    const int max_by_k = kb_total / 4 > 0 ? kb_total / 4 : 1;   // at least 4 k-blocks per split
+    if (sp > max_by_k) sp = max_by_k;
+    if (sp > 16) sp = 16;
+    if (sp < 1) sp = 1;
+    // every split must own at least one k-block
+    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
+  }
+  *swap = sw;
+  *bn = b;
+  *splits = sp;
+  return tiles;
+}
+
+size_t zb_gemm_workspace_bytes(int m, int n, int k, int num_sms) {
+  int sw, bn, sp;
+  const int tiles = zb_gemm_plan(m, n, k, num_sms, &sw, &bn, &sp);
+  if (sp <= 1) return 0;
+  return static_cast<size_t>(sp) * tiles * bn * kBlockP * sizeof(float);
+}
+
+// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `scratch` holds the split-K
+// partial tiles followed by nothing else; `counters` holds one zeroed u32 per
+// output tile (kept zero by the kernel).  force_splits > 0 overrides the plan.
+int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residual, const void* bias,
+                    int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int force_splits,
+                    float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
+                    ZbStatus* status, int num_sms, cudaStream_t stream) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0) return -10;
+  if (!out_f32 && (ldo % 8) != 0) return -11;
+  int sw, bn, sp;
+  zb_gemm_plan(m, n, k, num_sms, &sw, &bn, &sp);
+  const int kb_total = (k + kBlockK - 1) / kBlockK;
+  if (force_splits > 0) {
+    sp = force_splits > kb_total ? kb_total : force_splits;
+    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
+  }
+  GemmParams prm;
+  prm.rows_p = sw ? n : m;
+  prm.rows_q = sw ? m : n;
+  prm.k = k;
+  prm.ldo = ldo;
+  prm.out = out;
+  prm.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  prm.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  prm.out_f32 = out_f32;
+  prm.group_p = 16;
+  prm.workspace = scratch;
+  prm.counters = counters;
+  prm.status = status;
+  const int num_p = (prm.rows_p + kBlockP - 1) / kBlockP;
+  const int num_q = (prm.rows_q + bn - 1) / bn;
+  const int tiles = num_p * num_q;
+  // shrink the split count until the partial tiles fit the scratch that was given
+  while (sp > 1 && (static_cast<size_t>(sp) * tiles * bn * kBlockP * sizeof(float) > scratch_bytes ||
+                    tiles > counters_len)) {
+    --sp;
+    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
+  }
+  prm.splits = sp;
+  CUtensorMap tp, tq;
+  const void* pbase = sw ? w : a;
+  const void* qbase = sw ? a : w;
+  int rc = zb_make_tmap_bf16_2d(&tp, pbase, prm.rows_p, k, sw ? ldw : lda, kBlockP);
+  if (rc != 0) return rc;
+  rc = zb_make_tmap_bf16_2d(&tq, qbase, prm.rows_q, k, sw ? lda : ldw, bn);
+  if (rc != 0) return rc;
+  const int work = tiles * sp;
+  const int grid = work < num_sms ? work : num_sms;
+#define ZB_GEMM_CASE(BN_)                                                           \
+  case BN_:                                                                         \
+    return sw ? launch<BN_, true>(tp, tq, prm, grid, stream)                        \
+              : launch<BN_, false>(tp, tq, prm, grid, stream);
+  switch (bn) {
+    ZB_GEMM_CASE(16)
+    ZB_GEMM_CASE(32)
+    ZB_GEMM_CASE(64)
+    ZB_GEMM_CASE(128)
+    ZB_GEMM_CASE(256)
+  }
+#undef ZB_GEMM_CASE
+  return -12;
+}
+
+// Convenience entry point using the library's per-device scratch (see runtime.cu).
+int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, const void* bias,
+                 int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int force_splits,
+                 void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (st == nullptr) return -20;
+  return zb_gemm_bf16_ex(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, force_splits,
+                         st->gemm_scratch, st->gemm_scratch_bytes, st->gemm_counters,
+                         st->gemm_counters_len, st->status, st->num_sms,
+                         reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

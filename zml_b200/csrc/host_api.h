@@ -1,0 +1,37 @@
+// Host-side declarations shared by the .cu files of libzb_cuda.so.
+// Every exported symbol is `extern "C"` and takes raw device pointers plus a
+// `cudaStream_t` passed as `void*`, so the library can be driven from Python
+// (ctypes) or from C/C++ without any framework headers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+// Per-device state owned by the library (created by zb_init on that device).
+struct ZbDeviceState {
+  int device;
+  int num_sms;
+  ZbStatus* status;            // device memory, zeroed by zb_status_reset
+  float* gemm_scratch;         // split-K partial tiles
+  size_t gemm_scratch_bytes;
+  uint32_t* gemm_counters;     // one per output tile, zero between launches
+  int gemm_counters_len;
+  float* attn_scratch;         // split-KV partial outputs + (m, l) pairs
+  size_t attn_scratch_bytes;
+};
+
+ZbDeviceState* zb_device_state();       // state of the current device, or nullptr before zb_init
+void zb_count_launch(int n);            // adds to the process-wide kernel-launch counter
+
+extern "C" {
+int zb_init(int device);
+int zb_num_sms();
+int zb_status_read(uint32_t* out4);     // copies {code, kernel, where, detail}; synchronises the device
+int zb_status_reset();
+ZbStatus* zb_status_ptr();
+unsigned long long zb_launch_count();
+void zb_launch_count_reset();
+}

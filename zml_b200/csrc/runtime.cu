@@ -1,0 +1,85 @@
+// Library runtime: per-device state (status word, scratch), launch counting.
+#include <atomic>
+#include <mutex>
+
+#include "host_api.h"
+
+namespace {
+constexpr int kMaxDevices = 16;
+ZbDeviceState g_state[kMaxDevices];
+bool g_ready[kMaxDevices] = {};
+std::mutex g_mu;
+std::atomic<unsigned long long> g_launches{0};
+
+constexpr size_t kGemmScratchBytes = 64ull << 20;
+constexpr int kGemmCounters = 1 << 16;
+constexpr size_t kAttnScratchBytes = 128ull << 20;
+}  // namespace
+
+ZbDeviceState* zb_device_state() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!g_ready[dev]) {
+    if (zb_init(dev) != 0) return nullptr;
+  }
+  return &g_state[dev];
+}
+
+void zb_count_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n)); }
+
+extern "C" {
+
+int zb_init(int device) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (device < 0 || device >= kMaxDevices) return -1;
+  if (g_ready[device]) return 0;
+  int prev = -1;
+  cudaGetDevice(&prev);
+  if (cudaSetDevice(device) != cudaSuccess) return -2;
+  ZbDeviceState& s = g_state[device];
+  s.device = device;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return -3;
+  s.num_sms = prop.multiProcessorCount;
+  if (cudaMalloc(&s.status, sizeof(ZbStatus)) != cudaSuccess) return -4;
+  cudaMemset(s.status, 0, sizeof(ZbStatus));
+  s.gemm_scratch_bytes = kGemmScratchBytes;
+  if (cudaMalloc(&s.gemm_scratch, s.gemm_scratch_bytes) != cudaSuccess) return -5;
+  s.gemm_counters_len = kGemmCounters;
+  if (cudaMalloc(&s.gemm_counters, sizeof(uint32_t) * kGemmCounters) != cudaSuccess) return -6;
+  cudaMemset(s.gemm_counters, 0, sizeof(uint32_t) * kGemmCounters);
+  s.attn_scratch_bytes = kAttnScratchBytes;
+  if (cudaMalloc(&s.attn_scratch, s.attn_scratch_bytes) != cudaSuccess) return -7;
+  cudaDeviceSynchronize();
+  g_ready[device] = true;
+  if (prev >= 0 && prev != device) cudaSetDevice(prev);
+  return 0;
+}
+
+int zb_num_sms() {
+  ZbDeviceState* s = zb_device_state();
+  return s ? s->num_sms : 0;
+}
+
+ZbStatus* zb_status_ptr() {
+  ZbDeviceState* s = zb_device_state();
+  return s ? s->status : nullptr;
+}
+
+int zb_status_read(uint32_t* out4) {
+  ZbDeviceState* s = zb_device_state();
+  if (!s) return -1;
+  cudaError_t e = cudaMemcpy(out4, s->status, sizeof(ZbStatus), cudaMemcpyDeviceToHost);
+  return static_cast<int>(e);
+}
+
+int zb_status_reset() {
+  ZbDeviceState* s = zb_device_state();
+  if (!s) return -1;
+  return static_cast<int>(cudaMemset(s->status, 0, sizeof(ZbStatus)));
+}
+
+unsigned long long zb_launch_count() { return g_launches.load(); }
+void zb_launch_count_reset() { g_launches.store(0); }
+
+}  // extern "C"

@@ -1,0 +1,136 @@
+"""ctypes binding of ``libzb_cuda.so`` (the hand-written sm_100a kernels).
+
+The library exports a plain C ABI: raw device pointers, sizes and a stream
+handle.  On a machine with a GPU the library MUST load - an op never falls back
+to PyTorch silently; `lib()` raises instead.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+_LIB = None
+_PATH = Path(__file__).resolve().parent.parent / "_C" / "libzb_cuda.so"
+
+c_p = C.c_void_p
+c_i = C.c_int
+c_ll = C.c_longlong
+c_f = C.c_float
+c_sz = C.c_size_t
+c_ull = C.c_ulonglong
+
+
+class KernelError(RuntimeError):
+    """A kernel of libzb_cuda.so returned a non-zero code or recorded a device status."""
+
+
+_SIGS = {
+    "zb_init": (c_i, [c_i]),
+    "zb_num_sms": (c_i, []),
+    "zb_status_read": (c_i, [c_p]),
+    "zb_status_reset": (c_i, []),
+    "zb_status_ptr": (c_p, []),
+    "zb_launch_count": (c_ull, []),
+    "zb_launch_count_reset": (None, []),
+    "zb_gemm_plan": (c_i, [c_i, c_i, c_i, c_i, c_p, c_p, c_p]),
+    "zb_gemm_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
+    "zb_gemm_bf16": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
+    "zb_gemm_bf16_ex": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i,
+                              c_p, c_sz, c_p, c_i, c_p, c_i, c_p]),
+    "zb_rmsnorm": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_ll, c_f, c_i, c_p]),
+    "zb_rope_kvwrite": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_ll, c_i, c_i, c_i, c_i,
+                              c_i, c_i, c_i, c_ll, c_f, c_f, c_i, c_p]),
+    "zb_swiglu": (c_i, [c_p, c_p, c_ll, c_i, c_p]),
+    "zb_embedding": (c_i, [c_p, c_p, c_p, c_i, c_i, c_i, c_p]),
+    "zb_argmax_f32": (c_i, [c_p, c_p, c_i, c_i, c_ll, c_p]),
+    "zb_topk_sample": (c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_f, c_ull, c_ull, c_p]),
+    "zb_decode_plan_splits": (c_i, [c_i, c_i, c_i, c_i]),
+    "zb_decode_scratch_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
+    "zb_paged_decode": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_ll, c_f,
+                              c_i, c_i, c_p]),
+    "zb_paged_prefill": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i,
+                               c_ll, c_f, c_i, c_p]),
+}
+
+# Symbols added by later source files; bound only if the library exports them.
+_OPTIONAL_SIGS: dict[str, tuple] = {}
+
+
+def register_signature(name: str, restype, argtypes, optional: bool = True) -> None:
+    """Lets other modules of the package declare the C signature of their entry points."""
+    (_OPTIONAL_SIGS if optional else _SIGS)[name] = (restype, argtypes)
+    if _LIB is not None and hasattr(_LIB, name):
+        fn = getattr(_LIB, name)
+        fn.restype, fn.argtypes = restype, argtypes
+
+
+def available() -> bool:
+    return _PATH.exists()
+
+
+def path() -> Path:
+    return _PATH
+
+
+def lib():
+    """Loads the library once.  Raises if it has not been built."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not _PATH.exists():
+        if os.environ.get("ZB_AUTOBUILD", "1") != "0":
+            from .. import _build
+            _build.build_cuda()
+    if not _PATH.exists():
+        raise KernelError(
+            f"{_PATH} is missing: run `python -m zml_b200._build` (needs nvcc); "
+            "ops on CUDA tensors never fall back to PyTorch")
+    l = C.CDLL(str(_PATH))
+    for name, (res, args) in _SIGS.items():
+        fn = getattr(l, name)
+        fn.restype, fn.argtypes = res, args
+    for name, (res, args) in _OPTIONAL_SIGS.items():
+        if hasattr(l, name):
+            fn = getattr(l, name)
+            fn.restype, fn.argtypes = res, args
+    _LIB = l
+    return l
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out",
+                3: "index out of bounds", 4: "bad argument"}
+KERNEL_NAMES = {1: "gemm_bf16", 2: "paged_decode", 3: "paged_prefill", 4: "gemm_ar_fused",
+                5: "comm_barrier", 6: "moe_grouped_gemm", 7: "moe_a2a"}
+
+
+def read_status() -> tuple[int, int, int, int]:
+    """Synchronises the device and returns (code, kernel, where, detail)."""
+    buf = (C.c_uint32 * 4)()
+    check(lib().zb_status_read(C.cast(buf, c_p)), "zb_status_read")
+    return tuple(int(v) for v in buf)  # type: ignore[return-value]
+
+
+def raise_on_status() -> None:
+    """Raises KernelError if any kernel recorded a failure since the last reset."""
+    code, kernel, where, detail = read_status()
+    if code != 0:
+        lib().zb_status_reset()
+        raise KernelError(
+            f"device status: {STATUS_NAMES.get(code, code)} in kernel "
+            f"{KERNEL_NAMES.get(kernel, kernel)} (where={where}, detail={detail})")
+
+
+def stream_ptr(stream=None) -> int:
+    import torch
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return int(s.cuda_stream)
+
+
+def launch_count() -> int:
+    return int(lib().zb_launch_count())
