@@ -1,0 +1,81 @@
+"""End-to-end generation on CPU: the paged engine must reproduce, token for token, a plain
+dense-attention recomputation of the same weights."""
+import math
+
+import torch
+
+from zml_b200.models.common import SamplingStrategy
+from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
+from zml_b200.nn import rotary as rope_mod
+from zml_b200.ops import reference as ref
+from zml_b200.serving import Engine
+
+
+def dense_logits(model: LlamaModel, ids: list[int]) -> torch.Tensor:
+    """Straightforward full-sequence forward (no cache, no paging) -> logits of the last token."""
+    c = model.config
+    x = model.embed[torch.tensor(ids)]
+    t = len(ids)
+    pos = torch.arange(t)
+    for lw in model.layers:
+        n1 = ref.rmsnorm(x, lw.input_norm, c.rms_norm_eps)
+        qkv = ref.gemm(n1, lw.qkv, bias=lw.qkv_bias)
+        q, k, v = qkv.split([model.hq * c.hd, model.hkv * c.hd, model.hkv * c.hd], -1)
+        q = q.reshape(t, model.hq, c.hd); k = k.reshape(t, model.hkv, c.hd); v = v.reshape(t, model.hkv, c.hd)
+        q = ref.rope_rotate(q, pos, model.inv_freq, model.rope_layout, model.rot_dim, model.attn_factor)
+        k = ref.rope_rotate(k, pos, model.inv_freq, model.rope_layout, model.rot_dim, model.attn_factor)
+        g = model.hq // model.hkv
+        kk = k.float().repeat_interleave(g, 1); vv = v.float().repeat_interleave(g, 1)
+        s = torch.einsum("qhd,khd->hqk", q.float(), kk) / math.sqrt(c.hd)
+        s = s.masked_fill(~torch.tril(torch.ones(t, t, dtype=torch.bool)), float("-inf"))
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv).to(x.dtype).reshape(t, -1)
+        x = ref.gemm(a, lw.o, residual=x)
+        n2 = ref.rmsnorm(x, lw.post_norm, c.rms_norm_eps)
+        x = ref.gemm(ref.swiglu(ref.gemm(n2, lw.gate_up)), lw.down, residual=x)
+    n = ref.rmsnorm(x[-1:], model.final_norm, c.rms_norm_eps)
+    return ref.gemm(n, model.lm_head, out_dtype=torch.float32)[0]
+
+
+def test_engine_matches_dense_recompute():
+    torch.manual_seed(0)
+    cfg = LlamaConfig.from_hf(PRESETS["tiny-llama-test"])
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=1, std=0.08)
+    eng = Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=256, max_prefill_tokens=48)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,)).tolist() for n in (5, 37, 70)]
+    outs, stats = eng.generate(prompts, max_new_tokens=6)
+    assert stats.output_tokens == 18 and len(stats.ttft_ms) == 3
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for tok in o:
+            want = int(torch.argmax(dense_logits(model, seq)))
+            assert tok == want
+            seq.append(tok)
+    # every page went back to the pool
+    assert eng.pool.num_free == 63
+
+
+def test_engine_eos_and_sampling():
+    torch.manual_seed(0)
+    cfg = LlamaConfig.from_hf(PRESETS["tiny-llama-test"])
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=2, std=0.08)
+    eng = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=128)
+    p = [[1, 2, 3, 4]]
+    greedy, _ = eng.generate(p, 8)
+    eos = greedy[0][2]
+    cut, _ = eng.generate(p, 8, eos_ids=[eos], sync_interval=2)
+    assert cut[0] == greedy[0][:greedy[0].index(eos) + 1]
+    sampled, _ = eng.generate(p, 8, SamplingStrategy(topk=5, temperature=1.0))
+    assert len(sampled[0]) == 8
+
+
+def test_llama3_inv_freq_matches_hf_formula():
+    """Llama-3 scaled frequencies (the reference checks the same against HF values, zml/nn.zig:882-985)."""
+    cfg = LlamaConfig.from_hf(PRESETS["llama-3.1-8b"])
+    f = rope_mod.inv_freq(cfg.hd, cfg.rope_opts()).double()
+    base = 1.0 / (500000.0 ** (torch.arange(0, 128, 2).double() / 128))
+    wavelen = 2 * math.pi / base
+    low, high = 8192 / 1.0, 8192 / 4.0
+    smooth = (8192 / wavelen - 1.0) / (4.0 - 1.0)
+    want = torch.where(wavelen < high, base, torch.where(wavelen > low, base / 8.0,
+                       (1 - smooth) * base / 8.0 + smooth * base))
+    assert torch.allclose(f, want, rtol=1e-5, atol=0)

@@ -428,6 +428,34 @@ __global__ void __launch_bounds__(1024) zb_topk_sample_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------- decode bookkeeping
+// After sampling: feed the sampled token back as the next input, advance position and
+// length, compute the KV slot of the new position from the block table, and append the
+// token to the on-device history so that the host can read tokens in batches.
+__global__ void zb_decode_advance_kernel(const int32_t* __restrict__ sampled, int32_t* __restrict__ ids,
+                                         int32_t* __restrict__ positions, int32_t* __restrict__ seq_lens,
+                                         int32_t* __restrict__ slot_mapping,
+                                         const int32_t* __restrict__ block_table, int32_t* __restrict__ history,
+                                         int32_t* __restrict__ step_counter, int batch, int max_pages,
+                                         int page_size, int history_stride, int history_rows) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  const int step = *step_counter;
+  if (b < batch) {
+    const int tok = sampled[b];
+    ids[b] = tok;
+    const int pos = positions[b] + 1;
+    positions[b] = pos;
+    seq_lens[b] = pos + 1;
+    const int pg = pos / page_size;
+    slot_mapping[b] = pg < max_pages ? block_table[static_cast<size_t>(b) * max_pages + pg] * page_size + pos % page_size : -1;
+    if (step < history_rows) history[static_cast<size_t>(step) * history_stride + b] = tok;
+  }
+}
+
+// Runs after the kernel above on the same stream, so every block has read the old value.
+__global__ void zb_counter_inc_kernel(int32_t* c) { *c += 1; }
+
 }  // namespace
 
 extern "C" {
@@ -530,6 +558,22 @@ int zb_topk_sample(const float* logits, int32_t* out_token, float* topk_vals, in
   zb_topk_sample_kernel<<<rows, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       logits, out_token, topk_vals, topk_idx, vocab, stride, k, temperature, seed, step);
   zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Feeds sampled tokens back for the next decode step (see the kernel's comment).
+int zb_decode_advance(const int32_t* sampled, int32_t* ids, int32_t* positions, int32_t* seq_lens,
+                      int32_t* slot_mapping, const int32_t* block_table, int32_t* history,
+                      int32_t* step_counter, int batch, int max_pages, int page_size,
+                      int history_stride, int history_rows, void* stream) {
+  if (batch <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  zb_decode_advance_kernel<<<(batch + 127) / 128, 128, 0, s>>>(sampled, ids, positions, seq_lens,
+                                                             slot_mapping, block_table, history,
+                                                             step_counter, batch, max_pages, page_size,
+                                                             history_stride, history_rows);
+  zb_counter_inc_kernel<<<1, 1, 0, s>>>(step_counter);
+  zb_count_launch(2);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -34,4 +34,5 @@ int zb_status_reset();
 ZbStatus* zb_status_ptr();
 unsigned long long zb_launch_count();
 void zb_launch_count_reset();
+void zb_launch_count_add(unsigned long long n);  // e.g. nodes of a replayed CUDA graph
 }

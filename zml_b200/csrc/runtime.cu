@@ -81,5 +81,6 @@ int zb_status_reset() {
 
 unsigned long long zb_launch_count() { return g_launches.load(); }
 void zb_launch_count_reset() { g_launches.store(0); }
+void zb_launch_count_add(unsigned long long n) { g_launches.fetch_add(n); }
 
 }  // extern "C"

@@ -1,0 +1,65 @@
+"""Name -> model construction for the CLIs and the benchmark.
+
+`model_type` dispatch mirrors examples/llm/models.zig:189-194 of the reference.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..parallel.comm import Comm
+from . import common
+from .llama import PRESETS as LLAMA_PRESETS, LlamaConfig, LlamaModel
+
+
+def preset_names() -> list[str]:
+    names = list(LLAMA_PRESETS)
+    try:
+        from .qwen3_moe import PRESETS as MOE_PRESETS
+        names += list(MOE_PRESETS)
+    except ImportError:
+        pass
+    return names
+
+
+def build_model(name: str, comm: Optional[Comm] = None, device="cuda", seed: int = 0,
+                baseline: bool = False, fused: bool = True, dtype=torch.bfloat16):
+    """Random-init model of a named architecture on `device` (this rank's shard)."""
+    comm = comm or Comm.single(torch.device(device))
+    if name in LLAMA_PRESETS:
+        cfg = LlamaConfig.from_hf(LLAMA_PRESETS[name])
+        model = LlamaModel(cfg, comm, device=device, dtype=dtype).init_random(seed)
+    else:
+        from .qwen3_moe import PRESETS as MOE_PRESETS, Qwen3MoeConfig, Qwen3MoeModel
+        if name not in MOE_PRESETS:
+            raise KeyError(f"unknown model {name!r}; known: {preset_names()}")
+        cfg = Qwen3MoeConfig.from_hf(MOE_PRESETS[name])
+        model = Qwen3MoeModel(cfg, comm, device=device, dtype=dtype).init_random(seed)
+    if baseline:
+        from ..ops import baseline as _baseline
+        _baseline.enable(True)
+    elif fused and comm.world > 1 and torch.device(device).type == "cuda":
+        from ..parallel import symm
+        comm.fused = symm.SymmetricContext.create(comm, model.config.hidden_size)
+    return model
+
+
+def model_class_for(config: dict):
+    """Implementation for a HF config.json (by `model_type`)."""
+    kind = common.detect_model_type(config)
+    if kind in ("llama", "qwen3"):
+        return LlamaConfig, LlamaModel
+    if kind == "qwen3_moe":
+        from .qwen3_moe import Qwen3MoeConfig, Qwen3MoeModel
+        return Qwen3MoeConfig, Qwen3MoeModel
+    if kind == "qwen3_5":
+        from .qwen3_5 import Qwen35Config, Qwen35Model
+        return Qwen35Config, Qwen35Model
+    if kind == "qwen3_5_moe":
+        from .qwen3_5_moe import Qwen35MoeConfig, Qwen35MoeModel
+        return Qwen35MoeConfig, Qwen35MoeModel
+    if kind == "lfm2":
+        from .lfm2 import Lfm2Config, Lfm2Model
+        return Lfm2Config, Lfm2Model
+    raise ValueError(kind)

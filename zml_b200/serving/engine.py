@@ -1,0 +1,373 @@
+"""LLM serving engine: paged KV cache, chunked varlen prefill, CUDA-graph decode.
+
+This is the B200-first counterpart of the reference's session / inference layer
+(examples/llm/models/llama/{inference,session}.zig): where the reference runs a
+batch-1 dense-cache prefill executable followed by one PJRT execution per layer
+per token with a 4-byte device->host read each step, this engine
+
+* keeps K/V in 64-token pages shared by all sequences (block tables),
+* prefills many prompts per launch as one flattened varlen batch, in chunks
+  bounded by a token budget,
+* captures one whole decode step (all layers, sampling, feeding the token back,
+  advancing positions / slots on the device) in a CUDA graph per batch bucket, so
+  that a decode step costs one graph launch and no host synchronisation,
+* reads generated tokens back in blocks from an on-device history.
+
+One Engine instance lives in each tensor-parallel rank; all ranks execute the same
+schedule (SPMD), so no control traffic is needed.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional, Sequence as Seq
+
+import torch
+
+from .. import ops
+from ..models.common import SamplingStrategy
+from ..models.llama import AttnMeta
+from ..ops import _lib
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PagePool:
+    """Free list of KV pages.  Page 0 is reserved as the write target of padding rows."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self.free = list(range(num_pages - 1, 0, -1))
+
+    def alloc(self, n: int) -> list[int]:
+        if n > len(self.free):
+            raise OutOfPages(f"need {n} KV pages, {len(self.free)} free")
+        out = self.free[-n:][::-1] if n else []
+        del self.free[len(self.free) - n:]
+        return out
+
+    def release(self, pages: list[int]) -> None:
+        self.free.extend(reversed(pages))
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+
+@dataclass
+class Request:
+    prompt: list[int]
+    max_new_tokens: int
+    rid: int = 0
+    pages: list[int] = field(default_factory=list)
+    output: list[int] = field(default_factory=list)
+    computed: int = 0            # prompt tokens whose KV is in the cache
+    finished: bool = False
+    ttft_ms: Optional[float] = None
+
+    @property
+    def total_len(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+
+@dataclass
+class GenerationStats:
+    prefill_ms: float = 0.0
+    decode_ms: float = 0.0
+    total_ms: float = 0.0
+    ttft_ms: list = field(default_factory=list)
+    prompt_tokens: int = 0
+    output_tokens: int = 0
+    decode_steps: int = 0
+    h2d_bytes: int = 0
+    d2h_bytes: int = 0
+    launches: int = 0
+
+    def ttft_p50(self) -> float:
+        if not self.ttft_ms:
+            return 0.0
+        s = sorted(self.ttft_ms)
+        return s[len(s) // 2]
+
+
+def _bucket(n: int) -> int:
+    b = 1
+    while b < n:
+        b <<= 1
+    return b
+
+
+class Engine:
+    def __init__(self, model, num_pages: int, page_size: int = 64, max_batch: int = 64,
+                 max_seq_len: int = 4096, max_prefill_tokens: int = 8192, use_graphs: Optional[bool] = None,
+                 history_steps: int = 1024):
+        self.model = model
+        self.device = model.device
+        self.page_size = page_size
+        self.max_batch = max_batch
+        self.max_seq_len = max_seq_len
+        self.max_pages = (max_seq_len + page_size - 1) // page_size
+        self.max_prefill_tokens = max_prefill_tokens
+        self.pool = PagePool(num_pages)
+        self.kv_cache = torch.zeros(model.kv_cache_shape(num_pages, page_size), dtype=model.dtype,
+                                    device=self.device)
+        self.on_gpu = self.device.type == "cuda"
+        self.use_graphs = self.on_gpu if use_graphs is None else (use_graphs and self.on_gpu)
+        self.history_steps = history_steps
+        self._graphs: dict = {}
+        self._next_rid = 0
+        self.seed = 0
+        i32 = dict(dtype=torch.int32, device=self.device)
+        mb = max_batch
+        # static decode buffers (graph inputs / outputs)
+        self.d_ids = torch.zeros(mb, **i32)
+        self.d_pos = torch.zeros(mb, **i32)
+        self.d_seq = torch.zeros(mb, **i32)
+        self.d_slot = torch.full((mb,), -1, **i32)
+        self.d_bt = torch.zeros((mb, self.max_pages), **i32)
+        self.d_hist = torch.zeros((history_steps, mb), **i32)
+        self.d_step = torch.zeros(1, **i32)
+
+    # ------------------------------------------------------------------ helpers
+    def _pin(self, t: torch.Tensor) -> torch.Tensor:
+        return t.pin_memory() if self.on_gpu else t
+
+    def _to_dev(self, host: torch.Tensor, stats: Optional[GenerationStats] = None) -> torch.Tensor:
+        if stats is not None:
+            stats.h2d_bytes += host.numel() * host.element_size()
+        return host.to(self.device, non_blocking=True) if self.on_gpu else host
+
+    def new_request(self, prompt: Seq[int], max_new_tokens: int) -> Request:
+        r = Request(list(prompt), max_new_tokens, self._next_rid)
+        self._next_rid += 1
+        need = (len(r.prompt) + max_new_tokens + self.page_size - 1) // self.page_size
+        if need > self.max_pages:
+            raise ValueError(f"request needs {need} pages, engine allows {self.max_pages} per sequence")
+        r.pages = self.pool.alloc(need)
+        return r
+
+    def release(self, r: Request) -> None:
+        self.pool.release(r.pages)
+        r.pages = []
+
+    # ------------------------------------------------------------------ prefill
+    def _prefill_chunks(self, reqs: list[Request]):
+        """Packs (request, start, end) prompt ranges into chunks of at most max_prefill_tokens."""
+        chunks, cur, used = [], [], 0
+        for r in reqs:
+            pos = r.computed
+            n = len(r.prompt)
+            while pos < n:
+                take = min(n - pos, self.max_prefill_tokens - used)
+                cur.append((r, pos, pos + take))
+                used += take
+                pos += take
+                if used == self.max_prefill_tokens:
+                    chunks.append(cur)
+                    cur, used = [], 0
+        if cur:
+            chunks.append(cur)
+        return chunks
+
+    def _run_prefill_chunk(self, chunk, strategy, stats: Optional[GenerationStats]):
+        """Runs one flattened varlen prefill.  Returns (finishing requests, their first tokens)."""
+        ps = self.page_size
+        ids, pos, slots, qs, sl, rows, done = [], [], [], [0], [], [], []
+        bt = torch.zeros((len(chunk), self.max_pages), dtype=torch.int32)
+        for i, (r, a, b) in enumerate(chunk):
+            ids.extend(r.prompt[a:b])
+            pos.extend(range(a, b))
+            pg = r.pages
+            slots.extend(pg[p // ps] * ps + p % ps for p in range(a, b))
+            qs.append(qs[-1] + (b - a))
+            sl.append(b)
+            bt[i, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+            if b == len(r.prompt):
+                rows.append(qs[-1] - 1)
+                done.append(r)
+        t = len(ids)
+        host = self._pin(torch.tensor([ids, pos, slots], dtype=torch.int32))
+        meta_h = self._pin(torch.tensor(qs + sl + rows, dtype=torch.int32))
+        bt_h = self._pin(bt)
+        dev = self._to_dev(host, stats)
+        meta_d = self._to_dev(meta_h, stats)
+        bt_d = self._to_dev(bt_h, stats)
+        nb = len(chunk)
+        meta = AttnMeta(True, dev[1], dev[2], bt_d, meta_d[nb + 1:2 * nb + 1], meta_d[:nb + 1],
+                        total_q_blocks=sum((b - a + 63) // 64 for _, a, b in chunk),
+                        logits_rows=meta_d[2 * nb + 1:] if rows else None)
+        if rows:
+            toks = self.model.forward(dev[0], meta, self.kv_cache, strategy, self.seed, 0)
+        else:
+            self.model.hidden_states(dev[0], meta, self.kv_cache)
+            toks = None
+        for r, a, b in chunk:
+            r.computed = b
+        return done, toks, t
+
+    # ------------------------------------------------------------------ decode
+    def _decode_body(self, b: int, strategy, num_splits, max_seq_len):
+        meta = AttnMeta(False, self.d_pos[:b], self.d_slot[:b], self.d_bt[:b], self.d_seq[:b],
+                        num_splits=num_splits, max_seq_len=max_seq_len)
+        toks = self.model.forward(self.d_ids[:b], meta, self.kv_cache, strategy, self.seed, 0)
+        if self.on_gpu:
+            rc = _lib.lib().zb_decode_advance(
+                toks.data_ptr(), self.d_ids.data_ptr(), self.d_pos.data_ptr(), self.d_seq.data_ptr(),
+                self.d_slot.data_ptr(), self.d_bt.data_ptr(), self.d_hist.data_ptr(),
+                self.d_step.data_ptr(), b, self.max_pages, self.page_size, self.d_hist.shape[1],
+                self.d_hist.shape[0], _lib.stream_ptr())
+            _lib.check(rc, "zb_decode_advance")
+        else:
+            step = int(self.d_step[0])
+            self.d_ids[:b] = toks
+            self.d_pos[:b] += 1
+            self.d_seq[:b] = self.d_pos[:b] + 1
+            pg = torch.div(self.d_pos[:b], self.page_size, rounding_mode="floor").long()
+            page = self.d_bt[:b].gather(1, pg.clamp_max(self.max_pages - 1)[:, None])[:, 0]
+            self.d_slot[:b] = page * self.page_size + self.d_pos[:b] % self.page_size
+            if step < self.d_hist.shape[0]:
+                self.d_hist[step, :b] = toks
+            self.d_step += 1
+
+    def _decode_step(self, b: int, strategy, num_splits, max_seq_len, stats):
+        if not self.use_graphs:
+            self._decode_body(b, strategy, num_splits, max_seq_len)
+            return
+        key = (b, strategy.topk, float(strategy.temperature), num_splits)
+        g = self._graphs.get(key)
+        if g is None:
+            # warm up on a side stream (lazy kernel attributes, allocator), then capture
+            saved = [t.clone() for t in (self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist)]
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_body(b, strategy, num_splits, max_seq_len)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = _lib.launch_count()
+            with torch.cuda.graph(graph):
+                self._decode_body(b, strategy, num_splits, max_seq_len)
+            nodes = _lib.launch_count() - before
+            # the warm-up and capture passes must not count as decode steps: restore the state
+            # (the warm-up really ran; the capture pass did not execute anything)
+            for dst, src in zip((self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist), saved):
+                dst.copy_(src)
+            # the warm-up wrote one KV row per sequence at the slot of the next position; the
+            # real step writes the same slot with the real values, so nothing needs undoing
+            g = (graph, nodes)
+            self._graphs[key] = g
+        g[0].replay()
+        _lib.lib().zb_launch_count_add(g[1])
+
+    # ------------------------------------------------------------------ public API
+    def generate(self, prompts: Seq[Seq[int]], max_new_tokens: int,
+                 strategy: Optional[SamplingStrategy] = None, eos_ids: Seq[int] = (),
+                 sync_interval: int = 64, seed: int = 0) -> tuple[list[list[int]], GenerationStats]:
+        """Generates up to max_new_tokens per prompt.  Token ids go host -> device from pinned
+        memory, generated ids come back device -> host in blocks of `sync_interval` steps.
+        Returns (outputs, stats); stats times are device times (CUDA events)."""
+        strategy = strategy or SamplingStrategy()
+        self.seed = seed
+        stats = GenerationStats()
+        if len(prompts) > self.max_batch:
+            raise ValueError(f"{len(prompts)} prompts exceed max_batch={self.max_batch}")
+        launches0 = _lib.launch_count() if self.on_gpu else 0
+        reqs = [self.new_request(p, max_new_tokens) for p in prompts]
+        stats.prompt_tokens = sum(len(p) for p in prompts)
+        ev = (lambda: torch.cuda.Event(enable_timing=True)) if self.on_gpu else None
+        t_host0 = time.perf_counter()
+        if self.on_gpu:
+            e_start = ev(); e_start.record()
+        first_tok: dict[int, torch.Tensor] = {}
+        ttft_events = []
+        # ---------------- prefill
+        for chunk in self._prefill_chunks(reqs):
+            done, toks, _ = self._run_prefill_chunk(chunk, strategy, stats)
+            if self.on_gpu:
+                e = ev(); e.record()
+            else:
+                e = time.perf_counter()
+            for i, r in enumerate(done):
+                first_tok[r.rid] = toks[i:i + 1]
+                ttft_events.append((r, e))
+        if self.on_gpu:
+            e_prefill = ev(); e_prefill.record()
+        t_host1 = time.perf_counter()
+        # ---------------- decode set-up: device state of every running sequence
+        b = len(reqs)
+        bb = _bucket(b) if self.use_graphs else b
+        bb = min(bb, self.max_batch)
+        ps = self.page_size
+        pos = [len(r.prompt) for r in reqs]                # position of the first generated token
+        st = torch.zeros((4, bb), dtype=torch.int32)
+        st[3, :] = -1
+        bt = torch.zeros((bb, self.max_pages), dtype=torch.int32)
+        for i, r in enumerate(reqs):
+            st[1, i] = pos[i]
+            st[2, i] = pos[i] + 1
+            st[3, i] = r.pages[pos[i] // ps] * ps + pos[i] % ps
+            bt[i, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+        st_d = self._to_dev(self._pin(st), stats)
+        self.d_bt[:bb].copy_(self._to_dev(self._pin(bt), stats))
+        self.d_pos[:bb].copy_(st_d[1]); self.d_seq[:bb].copy_(st_d[2]); self.d_slot[:bb].copy_(st_d[3])
+        self.d_ids[:bb].zero_()
+        self.d_ids[:b].copy_(torch.cat([first_tok[r.rid] for r in reqs]))
+        self.d_step.zero_()
+        max_total = max(pos) + max_new_tokens
+        num_splits = ops.decode_plan_splits(bb, self.model.hkv, max_total) if self.on_gpu else 1
+        # ---------------- decode loop
+        outputs = [[] for _ in reqs]
+        first_host = self.d_ids[:b].cpu() if max_new_tokens > 0 else None
+        if first_host is not None:
+            stats.d2h_bytes += b * 4
+            for i in range(b):
+                outputs[i].append(int(first_host[i]))
+        eos = set(int(e) for e in eos_ids)
+        alive = [not (eos and outputs[i] and outputs[i][-1] in eos) for i in range(b)]
+        steps_total = max_new_tokens - 1
+        done_steps = 0
+        while done_steps < steps_total and any(alive):
+            n = min(sync_interval, steps_total - done_steps, self.history_steps)
+            self.d_step.zero_()
+            for _ in range(n):
+                self._decode_step(bb, strategy, num_splits, max_total, stats)
+            hist = self.d_hist[:n, :b].cpu()              # device -> host read (synchronises)
+            stats.d2h_bytes += n * b * 4
+            for i in range(b):
+                if not alive[i]:
+                    continue
+                for s in range(n):
+                    tok = int(hist[s, i])
+                    outputs[i].append(tok)
+                    if tok in eos:
+                        alive[i] = False
+                        break
+            done_steps += n
+            stats.decode_steps += n
+        if self.on_gpu:
+            e_end = ev(); e_end.record()
+            torch.cuda.synchronize()
+            stats.prefill_ms = e_start.elapsed_time(e_prefill)
+            stats.decode_ms = e_prefill.elapsed_time(e_end)
+            stats.total_ms = e_start.elapsed_time(e_end)
+            stats.ttft_ms = [e_start.elapsed_time(e) for _, e in ttft_events]
+            stats.launches = _lib.launch_count() - launches0
+        else:
+            t_end = time.perf_counter()
+            stats.prefill_ms = (t_host1 - t_host0) * 1e3
+            stats.total_ms = (t_end - t_host0) * 1e3
+            stats.decode_ms = stats.total_ms - stats.prefill_ms
+            stats.ttft_ms = [(e - t_host0) * 1e3 for _, e in ttft_events]
+        for (r, _), t in zip(ttft_events, stats.ttft_ms):
+            r.ttft_ms = t
+        stats.output_tokens = sum(len(o) for o in outputs)
+        for r, o in zip(reqs, outputs):
+            r.output = o
+            r.finished = True
+            self.release(r)
+        if self.on_gpu:
+            ops.raise_on_status()
+        return outputs, stats
