@@ -1,0 +1,156 @@
+// Communication runtime: symmetric heap over CUDA IPC, peer pointer tables, a
+// device-side barrier with bounded waits, and a stand-alone in-kernel all-reduce.
+//
+// One process drives one GPU.  Every rank allocates the same-sized heap with
+// cudaMalloc, exports it with cudaIpcGetMemHandle, and opens the handles of its
+// peers, which gives plain device pointers into the peers' HBM; loads and stores
+// through them travel over NVLink 5 / NVSwitch.  The host-side exchange of the
+// 64-byte handles goes through torch.distributed (see parallel/symm.py).
+//
+// This replaces what NCCL (through XLA) does for the reference
+// (zml/ops.zig:24-173; platforms/cuda/cuda.bzl:229-238): the collectives of the hot
+// path are issued by the compute kernels themselves (see fused_ar.h), and this
+// file provides the memory they talk through.
+#include <cstring>
+
+#include "host_api.h"
+
+namespace {
+
+constexpr uint32_t kKernelBarrier = 5;
+
+// Barrier over all ranks: rank r writes `epoch` into slot [r] of every peer's flag
+// array, then waits until its own array holds `epoch` in every slot.
+__global__ void zb_barrier_kernel(ZbArContext ctx, size_t flag_off, ZbStatus* status,
+                                  uint32_t* epoch_ptr) {
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) abort_flag = 0u;
+  __syncthreads();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ptr);
+  const int r = threadIdx.x;
+  if (r < ctx.world) {
+    uint32_t* peer = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(ctx.heap[r]) + flag_off);
+    __threadfence_system();
+    zb_st_release_sys(peer + ctx.rank, epoch);
+    const uint32_t* mine =
+        reinterpret_cast<const uint32_t*>(reinterpret_cast<char*>(ctx.heap[ctx.rank]) + flag_off);
+    if (!zb_wait_flag(mine + r, epoch, &abort_flag))
+      zb_record_error(status, ZB_ERR_FLAG_TIMEOUT, kKernelBarrier, static_cast<uint32_t>(r), epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(epoch_ptr) = epoch + 1u;
+}
+
+// One-shot all-reduce (sum) of a bf16 buffer that lives at the same offset of every
+// rank's heap: every rank reads all peers' copies and writes the sum to `out` locally.
+// Used for small messages and as the in-kernel counterpart of the NCCL baseline in tests.
+__global__ void zb_allreduce_oneshot_kernel(ZbArContext ctx, size_t in_off, __nv_bfloat16* out,
+                                            size_t n_vec) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < ctx.world; ++r) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<char*>(ctx.heap[r]) + in_off);
+      const uint4 v = __ldcg(src + i);
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = zb_unpack_bf16x2(u[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    reinterpret_cast<uint4*>(out)[i] =
+        make_uint4(zb_pack_bf16x2(acc[0], acc[1]), zb_pack_bf16x2(acc[2], acc[3]),
+                   zb_pack_bf16x2(acc[4], acc[5]), zb_pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int zb_symm_alloc(size_t bytes, void** ptr) {
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  return static_cast<int>(cudaDeviceSynchronize());
+}
+
+int zb_symm_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
+
+int zb_symm_ipc_handle(void* ptr, unsigned char* out64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, ptr);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  std::memcpy(out64, &h, 64);
+  return 0;
+}
+
+int zb_symm_ipc_open(const unsigned char* in64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, in64, 64);
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int zb_symm_ipc_close(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }
+
+// heap[r] for r != rank are the opened peer pointers; heap[rank] is the local allocation.
+ZbArContext* zb_ar_ctx_create(int rank, int world, void* const* heap, size_t recv_off,
+                              size_t recv_bytes, size_t push_flag_off, size_t done_flag_off,
+                              int max_tiles) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world) return nullptr;
+  ZbArContext* c = new ZbArContext();
+  c->rank = rank;
+  c->world = world;
+  for (int r = 0; r < 8; ++r) c->heap[r] = r < world ? heap[r] : nullptr;
+  c->recv_off = recv_off;
+  c->recv_bytes = recv_bytes;
+  c->push_flag_off = push_flag_off;
+  c->done_flag_off = done_flag_off;
+  c->max_tiles = max_tiles;
+  uint32_t* ctr = nullptr;
+  if (cudaMalloc(&ctr, 4 * sizeof(uint32_t)) != cudaSuccess) {
+    delete c;
+    return nullptr;
+  }
+  const uint32_t init[4] = {1u, 0u, 1u, 0u};   // {gemm epoch, exit ticket, barrier epoch, unused}
+  cudaMemcpy(ctr, init, sizeof(init), cudaMemcpyHostToDevice);
+  c->epoch = ctr;
+  c->exit_ticket = ctr + 1;
+  return c;
+}
+
+void zb_ar_ctx_destroy(ZbArContext* c) {
+  if (c == nullptr) return;
+  cudaFree(c->epoch);
+  delete c;
+}
+
+// Device-side barrier across the group on `stream`; flag_off addresses 8 u32 slots in the heap.
+int zb_comm_barrier(const ZbArContext* c, size_t flag_off, void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (!st || !c) return -20;
+  zb_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(*c, flag_off, st->status,
+                                                                         c->epoch + 2);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Sum of the bf16 buffers at `in_off` of every heap -> local `out`.  The caller brackets it
+// with zb_comm_barrier (inputs written before, inputs reusable after).
+int zb_allreduce_oneshot(const ZbArContext* c, size_t in_off, void* out, size_t n_elems, void* stream) {
+  if (!c) return -20;
+  if (n_elems % 8 != 0 || in_off % 16 != 0) return -10;
+  const size_t n_vec = n_elems / 8;
+  size_t blocks = (n_vec + 255) / 256;
+  if (blocks > 296) blocks = 296;
+  zb_allreduce_oneshot_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      *c, in_off, reinterpret_cast<__nv_bfloat16*>(out), n_vec);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -296,3 +296,32 @@ ZB_DEVICE float zb_warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+
+// ----------------------------------------------------------------------------
+// cross-GPU flags (peer memory over NVLink): release stores, bounded acquire waits
+// ----------------------------------------------------------------------------
+ZB_DEVICE void zb_st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+ZB_DEVICE uint32_t zb_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Waits until *p has reached `epoch` (flags only grow).  Gives up after ZB_WAIT_LIMIT_NS
+// or as soon as another role of the CTA gave up; returns false and raises `abort_flag`.
+ZB_DEVICE bool zb_wait_flag(const uint32_t* p, uint32_t epoch, volatile uint32_t* abort_flag) {
+  if (static_cast<int32_t>(zb_ld_acquire_sys(p) - epoch) >= 0) return true;
+  const uint64_t t0 = zb_globaltimer();
+  uint32_t spins = 0;
+  while (true) {
+    if (static_cast<int32_t>(zb_ld_acquire_sys(p) - epoch) >= 0) return true;
+    if ((++spins & 0x3f) == 0) {
+      if (*abort_flag != 0u) return false;
+      if (zb_globaltimer() - t0 > ZB_WAIT_LIMIT_NS) {
+        *abort_flag = 1u;
+        return false;
+      }
+    }
+  }
+}

@@ -22,6 +22,8 @@
 #include "common.cuh"
 #include "host_api.h"
 
+#include "fused_ar.h"
+
 namespace {
 
 constexpr int kBlockP = 128;   // rows of the MMA-M operand per tile
@@ -30,6 +32,7 @@ constexpr int kUmmaK = 16;
 constexpr int kNumThreads = 192;
 constexpr int kEpiThreads = 128;
 constexpr uint32_t kKernelId = 1;
+constexpr uint32_t kKernelIdFused = 4;
 
 struct GemmParams {
   int rows_p;        // extent of the P operand (MMA M side)
@@ -45,6 +48,7 @@ struct GemmParams {
   float* workspace;  // [splits][tiles][BN][128] fp32, used when splits > 1
   uint32_t* counters;  // one per output tile, zero between launches
   ZbStatus* status;
+  ZbFusedAr ar;        // used by the fused GEMM + all-reduce variant only
 };
 
 __host__ __device__ constexpr int stages_for(int bn) {
@@ -54,7 +58,7 @@ __host__ __device__ constexpr int stage_bytes(int bn) { return (kBlockP + bn) * 
 
 ZB_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, bool FUSED>
 __global__ void __launch_bounds__(kNumThreads, 1)
 zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                     const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
@@ -75,6 +79,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_flag = tmem_holder + 1;
   volatile uint32_t* is_last_flag = tmem_holder + 2;
+  volatile uint32_t* abort_where = tmem_holder + 3;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -97,6 +102,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     }
     *abort_flag = 0u;
     *is_last_flag = 0u;
+    *abort_where = 0u;
     zb_mbar_fence_init();
   }
   if (warp == 1) {
@@ -198,6 +204,8 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     const int quad = warp & 3;                     // TMEM lane quadrant of this warp
     const int row_in_tile = quad * 32 + lane;      // MMA-M row held by this thread
     uint32_t acc = 0, acc_phase = 0;
+    uint32_t epoch = 0;
+    if constexpr (FUSED) epoch = *reinterpret_cast<volatile uint32_t*>(prm.ar.epoch);
     for (int work = blockIdx.x; work < num_work; work += gridDim.x) {
       int pt, qt, split;
       decode(work, pt, qt, split);
@@ -241,95 +249,211 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         zb_mbar_arrive(&tmem_empty[acc]);
       }
 
-      if (do_store) {
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          float v[16];
-          if (prm.splits > 1) {
+      // chunk of 16 accumulator columns of this thread's row (summed over splits if any)
+      auto load_chunk = [&](int c0, float (&v)[16]) {
+        if (prm.splits > 1) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = 0.f;
-            for (int s = 0; s < prm.splits; ++s) {
-              const float* ws = prm.workspace +
-                                (static_cast<size_t>(s) * num_out_tiles + out_tile) * (BN * kBlockP);
+          for (int j = 0; j < 16; ++j) v[j] = 0.f;
+          for (int s = 0; s < prm.splits; ++s) {
+            const float* ws = prm.workspace +
+                              (static_cast<size_t>(s) * num_out_tiles + out_tile) * (BN * kBlockP);
 #pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] += __ldcg(&ws[(c0 + j) * kBlockP + row_in_tile]);
+            for (int j = 0; j < 16; ++j) v[j] += __ldcg(&ws[(c0 + j) * kBlockP + row_in_tile]);
+          }
+        } else {
+          uint32_t r[16];
+          zb_tmem_ld16(taddr + c0, r);
+          zb_tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+        }
+      };
+      // bias / residual (read from this rank's memory) then store into `outp`
+      auto finish_chunk = [&](int c0, float (&v)[16]) {
+        if constexpr (SWAP) {
+          const float b = prm.bias ? __bfloat162float(prm.bias[p]) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int q = q0 + c0 + j;
+            v[j] += b;
+            if (prm.residual && q < prm.rows_q)
+              v[j] += __bfloat162float(prm.residual[static_cast<size_t>(q) * prm.ldo + p]);
+          }
+        } else {
+          const int q = q0 + c0;
+          const size_t o = static_cast<size_t>(p) * prm.ldo + q;
+          if (q + 16 <= prm.rows_q) {
+            if (prm.bias) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] += __bfloat162float(prm.bias[q + j]);
+            }
+            if (prm.residual) {
+              const uint4* rp = reinterpret_cast<const uint4*>(prm.residual + o);
+              uint4 r0 = rp[0], r1 = rp[1];
+              const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float2 f = zb_unpack_bf16x2(rr[j]);
+                v[2 * j] += f.x;
+                v[2 * j + 1] += f.y;
+              }
             }
           } else {
-            uint32_t r[16];
-            zb_tmem_ld16(taddr + c0, r);
-            zb_tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
-          }
-          if (p < prm.rows_p) {
-            if constexpr (SWAP) {
-              // p = output column n, q = output row m
-              const float b = prm.bias ? __bfloat162float(prm.bias[p]) : 0.f;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int q = q0 + c0 + j;
-                if (q < prm.rows_q) {
-                  const size_t o = static_cast<size_t>(q) * prm.ldo + p;
-                  float x = v[j] + b;
-                  if (prm.residual) x += __bfloat162float(prm.residual[o]);
-                  if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = x;
-                  else reinterpret_cast<__nv_bfloat16*>(prm.out)[o] = __float2bfloat16(x);
-                }
-              }
-            } else {
-              // p = output row m, q = output column n (16 consecutive columns per step)
-              const int q = q0 + c0;
-              const size_t o = static_cast<size_t>(p) * prm.ldo + q;
-              if (q + 16 <= prm.rows_q) {
-                if (prm.bias) {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) v[j] += __bfloat162float(prm.bias[q + j]);
-                }
-                if (prm.residual) {
-                  const uint4* rp = reinterpret_cast<const uint4*>(prm.residual + o);
-                  uint4 r0 = rp[0], r1 = rp[1];
-                  const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    float2 f = zb_unpack_bf16x2(rr[j]);
-                    v[2 * j] += f.x;
-                    v[2 * j + 1] += f.y;
-                  }
-                }
-                if (prm.out_f32) {
-                  float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(prm.out) + o);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j)
-                    op[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                } else {
-                  uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(prm.out) + o);
-                  op[0] = make_uint4(zb_pack_bf16x2(v[0], v[1]), zb_pack_bf16x2(v[2], v[3]),
-                                     zb_pack_bf16x2(v[4], v[5]), zb_pack_bf16x2(v[6], v[7]));
-                  op[1] = make_uint4(zb_pack_bf16x2(v[8], v[9]), zb_pack_bf16x2(v[10], v[11]),
-                                     zb_pack_bf16x2(v[12], v[13]), zb_pack_bf16x2(v[14], v[15]));
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  if (q + j < prm.rows_q) {
-                    float x = v[j];
-                    if (prm.bias) x += __bfloat162float(prm.bias[q + j]);
-                    if (prm.residual) x += __bfloat162float(prm.residual[o + j]);
-                    if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o + j] = x;
-                    else reinterpret_cast<__nv_bfloat16*>(prm.out)[o + j] = __float2bfloat16(x);
-                  }
-                }
+            for (int j = 0; j < 16; ++j) {
+              if (q + j < prm.rows_q) {
+                if (prm.bias) v[j] += __bfloat162float(prm.bias[q + j]);
+                if (prm.residual) v[j] += __bfloat162float(prm.residual[o + j]);
               }
             }
           }
         }
+      };
+      auto store_chunk = [&](int c0, const float (&v)[16], void* outp) {
+        if constexpr (SWAP) {
+          // p = output column n, q = output row m
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int q = q0 + c0 + j;
+            if (q < prm.rows_q) {
+              const size_t o = static_cast<size_t>(q) * prm.ldo + p;
+              if (prm.out_f32) reinterpret_cast<float*>(outp)[o] = v[j];
+              else reinterpret_cast<__nv_bfloat16*>(outp)[o] = __float2bfloat16(v[j]);
+            }
+          }
+        } else {
+          // p = output row m, q = output column n (16 consecutive columns per step)
+          const int q = q0 + c0;
+          const size_t o = static_cast<size_t>(p) * prm.ldo + q;
+          if (q + 16 <= prm.rows_q) {
+            if (prm.out_f32) {
+              float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(outp) + o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                op[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            } else {
+              uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(outp) + o);
+              op[0] = make_uint4(zb_pack_bf16x2(v[0], v[1]), zb_pack_bf16x2(v[2], v[3]),
+                                 zb_pack_bf16x2(v[4], v[5]), zb_pack_bf16x2(v[6], v[7]));
+              op[1] = make_uint4(zb_pack_bf16x2(v[8], v[9]), zb_pack_bf16x2(v[10], v[11]),
+                                 zb_pack_bf16x2(v[12], v[13]), zb_pack_bf16x2(v[14], v[15]));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (q + j < prm.rows_q) {
+                if (prm.out_f32) reinterpret_cast<float*>(outp)[o + j] = v[j];
+                else reinterpret_cast<__nv_bfloat16*>(outp)[o + j] = __float2bfloat16(v[j]);
+              }
+            }
+          }
+        }
+      };
+
+      if constexpr (!FUSED) {
+        if (do_store) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            load_chunk(c0, v);
+            if (p < prm.rows_p) {
+              finish_chunk(c0, v);
+              store_chunk(c0, v, prm.out);
+            }
+          }
+        }
+      } else {
+        if (do_store) {
+          const ZbFusedAr& ar = prm.ar;
+          const int owner = out_tile % ar.world;
+          const int slot = out_tile / ar.world;
+          // 1. partial tile -> owner's staging slot [src = rank][slot][row][BN]
+          __nv_bfloat16* dst = ar.recv_peer[owner] +
+                               ((static_cast<size_t>(ar.rank) * ar.slots_per_src + slot) * kBlockP + row_in_tile) * BN;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            load_chunk(c0, v);
+            uint4* d4 = reinterpret_cast<uint4*>(dst + c0);
+            d4[0] = make_uint4(zb_pack_bf16x2(v[0], v[1]), zb_pack_bf16x2(v[2], v[3]),
+                               zb_pack_bf16x2(v[4], v[5]), zb_pack_bf16x2(v[6], v[7]));
+            d4[1] = make_uint4(zb_pack_bf16x2(v[8], v[9]), zb_pack_bf16x2(v[10], v[11]),
+                               zb_pack_bf16x2(v[12], v[13]), zb_pack_bf16x2(v[14], v[15]));
+          }
+          if (prm.splits == 1) {
+            zb_tc_fence_before();
+            zb_mbar_arrive(&tmem_empty[acc]);
+          }
+          __threadfence_system();
+          epi_bar_sync();
+          if (epi_tid == 0)
+            zb_st_release_sys(ar.push_flag_peer[owner] + static_cast<size_t>(slot) * ar.world + ar.rank, epoch);
+          if (owner == ar.rank) {
+            // 2. reduce the partials of all ranks and broadcast the result
+            if (epi_tid < ar.world) {
+              const uint32_t* f = ar.push_flag_peer[ar.rank] + static_cast<size_t>(slot) * ar.world + epi_tid;
+              if (!zb_wait_flag(f, epoch, abort_flag)) *abort_where = 100u + epi_tid;
+            }
+            epi_bar_sync();
+            if (*abort_flag != 0u) break;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = 0.f;
+              for (int src = 0; src < ar.world; ++src) {
+                const uint4* s4 = reinterpret_cast<const uint4*>(
+                    ar.recv_peer[ar.rank] +
+                    ((static_cast<size_t>(src) * ar.slots_per_src + slot) * kBlockP + row_in_tile) * BN + c0);
+                const uint4 x0 = __ldcg(s4), x1 = __ldcg(s4 + 1);
+                const uint32_t xx[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float2 f2 = zb_unpack_bf16x2(xx[j]);
+                  v[2 * j] += f2.x;
+                  v[2 * j + 1] += f2.y;
+                }
+              }
+              if (p < prm.rows_p) {
+                finish_chunk(c0, v);
+                for (int d = 0; d < ar.world; ++d) store_chunk(c0, v, ar.out_peer[d]);
+              }
+            }
+            __threadfence_system();
+            epi_bar_sync();
+            if (epi_tid < ar.world) zb_st_release_sys(ar.done_flag_peer[epi_tid] + out_tile, epoch);
+          }
+        } else if (prm.splits == 1) {
+          zb_tc_fence_before();
+          zb_mbar_arrive(&tmem_empty[acc]);
+        }
       }
-      if (prm.splits == 1) {
+      if (!FUSED && prm.splits == 1) {
         zb_tc_fence_before();
         zb_mbar_arrive(&tmem_empty[acc]);
       }
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if constexpr (FUSED) {
+      // 3. the all-reduced output is complete on this rank once every tile is marked done
+      if (*abort_flag == 0u) {
+        for (int t = blockIdx.x * kEpiThreads + epi_tid; t < num_out_tiles; t += gridDim.x * kEpiThreads) {
+          if (!zb_wait_flag(prm.ar.done_flag_peer[prm.ar.rank] + t, epoch, abort_flag)) {
+            *abort_where = 200u;
+            break;
+          }
+        }
+      }
+      epi_bar_sync();
+      if (epi_tid == 0) {
+        __threadfence();
+        const uint32_t ticket = atomicAdd(prm.ar.exit_ticket, 1u);
+        if (ticket == gridDim.x - 1) {
+          *prm.ar.exit_ticket = 0u;
+          *reinterpret_cast<volatile uint32_t*>(prm.ar.epoch) = epoch + 1u;
+        }
+      }
     }
   }
 
@@ -337,7 +461,9 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   zb_tc_fence_before();
   __syncthreads();
   if (*abort_flag != 0u) {
-    if (threadIdx.x == 0) zb_record_error(prm.status, ZB_ERR_MBAR_TIMEOUT, kKernelId, blockIdx.x, BN);
+    if (threadIdx.x == 0)
+      zb_record_error(prm.status, *abort_where >= 100u ? ZB_ERR_FLAG_TIMEOUT : ZB_ERR_MBAR_TIMEOUT,
+                      FUSED ? kKernelIdFused : kKernelId, *abort_where, blockIdx.x);
     // give copies that may still be in flight time to land before the CTA's
     // shared memory is handed to another CTA
     const uint64_t t0 = zb_globaltimer();
@@ -393,18 +519,18 @@ int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, in
 
 namespace {
 
-template <int BN, bool SWAP>
+template <int BN, bool SWAP, bool FUSED = false>
 int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid,
            cudaStream_t stream) {
   constexpr int smem = stages_for(BN) * stage_bytes(BN) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(zb_gemm_bf16_kernel<BN, SWAP>,
+    cudaError_t e = cudaFuncSetAttribute(zb_gemm_bf16_kernel<BN, SWAP, FUSED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  zb_gemm_bf16_kernel<BN, SWAP><<<grid, kNumThreads, smem, stream>>>(tp, tq, prm);
+  zb_gemm_bf16_kernel<BN, SWAP, FUSED><<<grid, kNumThreads, smem, stream>>>(tp, tq, prm);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -524,6 +650,85 @@ int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, 
                          st->gemm_scratch, st->gemm_scratch_bytes, st->gemm_counters,
                          st->gemm_counters_len, st->status, st->num_sms,
                          reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Row-parallel GEMM fused with the tensor-parallel all-reduce (and bias / residual):
+//   out_r = sum over ranks r' of a_r'[M,K_r'] * w_r'[N,K_r']^T (+ bias) (+ residual), on every rank.
+// `out_off` is the byte offset of the output inside every rank's symmetric heap.  All ranks
+// must call this with the same shapes, in the same order.  See fused_ar.h for the protocol.
+int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_t out_off,
+                     const void* residual, const void* bias, int m, int n, int k, int lda, int ldw,
+                     int ldo, int force_splits, void* stream) {
+  if (ctx == nullptr || ctx->world < 1 || ctx->world > kZbMaxRanks) return -50;
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (ldo % 8) != 0 || (out_off % 16) != 0) return -10;
+  ZbDeviceState* st = zb_device_state();
+  if (st == nullptr) return -20;
+  int sw, bn, sp;
+  zb_gemm_plan(m, n, k, st->num_sms, &sw, &bn, &sp);
+  const int kb_total = (k + kBlockK - 1) / kBlockK;
+  if (force_splits > 0) {
+    sp = force_splits > kb_total ? kb_total : force_splits;
+    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
+  }
+  GemmParams prm;
+  prm.rows_p = sw ? n : m;
+  prm.rows_q = sw ? m : n;
+  prm.k = k;
+  prm.ldo = ldo;
+  prm.out = nullptr;
+  prm.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  prm.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  prm.out_f32 = 0;
+  prm.group_p = 16;
+  prm.workspace = st->gemm_scratch;
+  prm.counters = st->gemm_counters;
+  prm.status = st->status;
+  const int num_p = (prm.rows_p + kBlockP - 1) / kBlockP;
+  const int num_q = (prm.rows_q + bn - 1) / bn;
+  const int tiles = num_p * num_q;
+  while (sp > 1 && (static_cast<size_t>(sp) * tiles * bn * kBlockP * sizeof(float) > st->gemm_scratch_bytes ||
+                    tiles > st->gemm_counters_len)) {
+    --sp;
+    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
+  }
+  prm.splits = sp;
+  ZbFusedAr& ar = prm.ar;
+  ar.rank = ctx->rank;
+  ar.world = ctx->world;
+  ar.slots_per_src = (tiles + ctx->world - 1) / ctx->world;
+  const size_t need = static_cast<size_t>(ctx->world) * ar.slots_per_src * kBlockP * bn * 2;
+  if (need > ctx->recv_bytes || tiles > ctx->max_tiles) return -51;
+  for (int r = 0; r < ctx->world; ++r) {
+    char* base = reinterpret_cast<char*>(ctx->heap[r]);
+    ar.recv_peer[r] = reinterpret_cast<__nv_bfloat16*>(base + ctx->recv_off);
+    ar.out_peer[r] = reinterpret_cast<__nv_bfloat16*>(base + out_off);
+    ar.push_flag_peer[r] = reinterpret_cast<uint32_t*>(base + ctx->push_flag_off);
+    ar.done_flag_peer[r] = reinterpret_cast<uint32_t*>(base + ctx->done_flag_off);
+  }
+  ar.epoch = ctx->epoch;
+  ar.exit_ticket = ctx->exit_ticket;
+  CUtensorMap tp, tq;
+  int rc = zb_make_tmap_bf16_2d(&tp, sw ? w : a, prm.rows_p, k, sw ? ldw : lda, kBlockP);
+  if (rc != 0) return rc;
+  rc = zb_make_tmap_bf16_2d(&tq, sw ? a : w, prm.rows_q, k, sw ? lda : ldw, bn);
+  if (rc != 0) return rc;
+  const int work = tiles * sp;
+  const int grid = work < st->num_sms ? work : st->num_sms;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define ZB_GEMM_CASE(BN_)                                                     \
+  case BN_:                                                                   \
+    return sw ? launch<BN_, true, true>(tp, tq, prm, grid, s)                 \
+              : launch<BN_, false, true>(tp, tq, prm, grid, s);
+  switch (bn) {
+    ZB_GEMM_CASE(16)
+    ZB_GEMM_CASE(32)
+    ZB_GEMM_CASE(64)
+    ZB_GEMM_CASE(128)
+    ZB_GEMM_CASE(256)
+  }
+#undef ZB_GEMM_CASE
+  return -12;
 }
 
 }  // extern "C"

@@ -23,6 +23,20 @@ struct ZbDeviceState {
   size_t attn_scratch_bytes;
 };
 
+// Peer-memory description of one tensor-parallel group, built by zb_ar_ctx_create (comm.cu).
+struct ZbArContext {
+  int rank;
+  int world;
+  void* heap[8];          // base of every rank's symmetric heap (peer pointers; [rank] is local)
+  size_t recv_off;        // staging area for partial tiles
+  size_t recv_bytes;
+  size_t push_flag_off;   // u32 flags [max_tiles / world + 1][world]
+  size_t done_flag_off;   // u32 flags [max_tiles]
+  int max_tiles;
+  uint32_t* epoch;        // local device counter, starts at 1
+  uint32_t* exit_ticket;  // local device counter
+};
+
 ZbDeviceState* zb_device_state();       // state of the current device, or nullptr before zb_init
 void zb_count_launch(int n);            // adds to the process-wide kernel-launch counter
 

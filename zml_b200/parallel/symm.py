@@ -1,0 +1,179 @@
+"""Symmetric memory for in-kernel collectives and the fused row-parallel GEMM + all-reduce.
+
+Every rank allocates an identical heap; CUDA IPC handles are exchanged through the
+process group, after which each rank holds a device pointer to every peer's heap.
+The heap holds, at the same offsets on every rank,
+
+    [push flags | done flags | barrier flags | staging for partial tiles | act 0 | act 1]
+
+`gemm_allreduce` computes ``sum_r a_r @ w_r^T + residual`` on every rank with ONE
+kernel (libzb_cuda.so: zb_gemm_ar_fused): the GEMM epilogue pushes partial tiles to
+the tile's owner over NVLink, the owner reduces and broadcasts, and the kernel ends
+when the full result is present locally.  Its output alternates between the two
+activation buffers, so the residual stream of a tensor-parallel model lives in
+symmetric memory.
+
+The reference obtains the same result from an XLA-inserted NCCL all-reduce after
+the GEMM (examples/llm/models/llama/model.zig:421-442,613-617).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..ops import _lib
+from .comm import Comm
+
+_lib.register_signature("zb_symm_alloc", C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)], optional=False)
+_lib.register_signature("zb_symm_free", C.c_int, [C.c_void_p], optional=False)
+_lib.register_signature("zb_symm_ipc_handle", C.c_int, [C.c_void_p, C.c_char_p], optional=False)
+_lib.register_signature("zb_symm_ipc_open", C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)], optional=False)
+_lib.register_signature("zb_symm_ipc_close", C.c_int, [C.c_void_p], optional=False)
+_lib.register_signature("zb_ar_ctx_create", C.c_void_p,
+                        [C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_size_t, C.c_size_t, C.c_size_t,
+                         C.c_size_t, C.c_int], optional=False)
+_lib.register_signature("zb_ar_ctx_destroy", None, [C.c_void_p], optional=False)
+_lib.register_signature("zb_comm_barrier", C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p], optional=False)
+_lib.register_signature("zb_allreduce_oneshot", C.c_int,
+                        [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p], optional=False)
+_lib.register_signature("zb_gemm_ar_fused", C.c_int,
+                        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
+                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p], optional=False)
+
+
+class _DevMem:
+    """Exposes a raw device range to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int, owner=None):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 2}
+        self._owner = owner
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
+
+
+class SymmetricContext:
+    MAX_TILES = 8192
+
+    def __init__(self):
+        self.comm: Optional[Comm] = None
+        self.ctx = None
+        self.local_ptr = 0
+        self.peer_ptrs: list[int] = []
+        self.heap_bytes = 0
+        self.act = []
+        self.act_off = []
+        self._next = 0
+        self.staging = None
+        self.staging_off = 0
+
+    @staticmethod
+    def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0) -> "SymmetricContext":
+        """Collective: every rank of `comm` must call it with the same arguments."""
+        l = _lib.lib()
+        self = SymmetricContext()
+        self.comm = comm
+        w = comm.world
+        push_bytes = _align((self.MAX_TILES // w + 2) * w * 4)
+        done_bytes = _align(self.MAX_TILES * 4)
+        bar_bytes = 256
+        # staging: `world` sources x padded tile grid; both tile shapes stay below this bound
+        m_pad = (max_tokens + 255) // 256 * 256
+        n_pad = (hidden + 255) // 256 * 256 + 256 * w
+        recv_bytes = _align(max(m_pad, 256) * n_pad * 2 + w * 128 * 256 * 2)
+        act_bytes = _align(max_tokens * hidden * 2)
+        stg_bytes = _align(staging_elems * 2)
+        self.push_off = 0
+        self.done_off = push_bytes
+        self.bar_off = self.done_off + done_bytes
+        self.recv_off = self.bar_off + bar_bytes
+        self.recv_bytes = recv_bytes
+        self.act_off = [self.recv_off + recv_bytes, self.recv_off + recv_bytes + act_bytes]
+        self.staging_off = self.act_off[1] + act_bytes
+        self.heap_bytes = self.staging_off + stg_bytes
+        self.hidden, self.max_tokens = hidden, max_tokens
+        p = C.c_void_p()
+        _lib.check(l.zb_symm_alloc(self.heap_bytes, C.byref(p)), "zb_symm_alloc")
+        self.local_ptr = p.value
+        h = C.create_string_buffer(64)
+        _lib.check(l.zb_symm_ipc_handle(self.local_ptr, h), "zb_symm_ipc_handle")
+        handles = comm.all_gather_object(bytes(h.raw))
+        self.peer_ptrs = []
+        for r, hb in enumerate(handles):
+            if r == comm.rank:
+                self.peer_ptrs.append(self.local_ptr)
+            else:
+                q = C.c_void_p()
+                _lib.check(l.zb_symm_ipc_open(hb, C.byref(q)), f"zb_symm_ipc_open(rank {r})")
+                self.peer_ptrs.append(q.value)
+        arr = (C.c_void_p * 8)(*(self.peer_ptrs + [None] * (8 - w)))
+        self.ctx = l.zb_ar_ctx_create(comm.rank, w, arr, self.recv_off, recv_bytes, self.push_off,
+                                      self.done_off, self.MAX_TILES)
+        if not self.ctx:
+            raise _lib.KernelError("zb_ar_ctx_create failed")
+        dev = comm.device
+        self._holder = _DevMem(self.local_ptr, self.heap_bytes, self)
+        heap = torch.as_tensor(self._holder, device=dev)
+        self.heap = heap
+        self.act = [heap[o:o + act_bytes].view(torch.bfloat16) for o in self.act_off]
+        if stg_bytes:
+            self.staging = heap[self.staging_off:self.staging_off + stg_bytes].view(torch.bfloat16)
+        comm.barrier()
+        return self
+
+    # ------------------------------------------------------------------ ops
+    def gemm_allreduce(self, a, w, residual=None, bias=None, force_splits: int = 0):
+        """All ranks: returns sum_r(a_r @ w_r^T) + bias + residual, bf16 [M, N], N == hidden."""
+        m, k = a.shape
+        n = w.shape[0]
+        if n != self.hidden or m > self.max_tokens:
+            raise ValueError(f"fused all-reduce output [{m},{n}] exceeds the context [{self.max_tokens},{self.hidden}]")
+        idx = self._next
+        # never write the buffer the residual lives in
+        if residual is not None and residual.data_ptr() == self.act[idx].data_ptr():
+            idx ^= 1
+        self._next = idx ^ 1
+        out = self.act[idx][: m * n].view(m, n)
+        rc = _lib.lib().zb_gemm_ar_fused(
+            self.ctx, a.data_ptr(), w.data_ptr(), self.act_off[idx],
+            residual.data_ptr() if residual is not None else None,
+            bias.data_ptr() if bias is not None else None, m, n, k, a.stride(0), w.stride(0), n,
+            force_splits, _lib.stream_ptr())
+        _lib.check(rc, "zb_gemm_ar_fused")
+        return out
+
+    def barrier(self):
+        """Device-side barrier across the group on the current stream."""
+        _lib.check(_lib.lib().zb_comm_barrier(self.ctx, self.bar_off, _lib.stream_ptr()), "zb_comm_barrier")
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """In-kernel one-shot all-reduce through the staging area (small bf16 tensors)."""
+        n = t.numel()
+        assert self.staging is not None and n <= self.staging.numel() and n % 8 == 0
+        self.staging[:n].copy_(t.reshape(-1))
+        self.barrier()
+        out = torch.empty_like(t)
+        _lib.check(_lib.lib().zb_allreduce_oneshot(self.ctx, self.staging_off, out.data_ptr(), n,
+                                                   _lib.stream_ptr()), "zb_allreduce_oneshot")
+        self.barrier()
+        return out
+
+    def close(self):
+        l = _lib.lib()
+        torch.cuda.synchronize()
+        if self.comm is not None:
+            self.comm.barrier()
+        for r, p in enumerate(self.peer_ptrs):
+            if self.comm is not None and r != self.comm.rank:
+                l.zb_symm_ipc_close(p)
+        if self.ctx:
+            l.zb_ar_ctx_destroy(self.ctx)
+            self.ctx = None
+        self.act, self.heap, self.staging = [], None, None
+        if self.local_ptr:
+            l.zb_symm_free(self.local_ptr)
+            self.local_ptr = 0
