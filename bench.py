@@ -210,7 +210,7 @@ def main() -> None:
                     "ms_per_step": wall_ms / steps},
             "gpu_launches": int(launches),
         }))
-    comm.close()
+    comm.finish(0)
 
 
 if __name__ == "__main__":

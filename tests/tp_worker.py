@@ -76,8 +76,8 @@ def main():
     ctx.close()
     comm.barrier()
     if comm.rank == 0:
-        print("TP_OK")
-    comm.close()
+        print("TP_OK", flush=True)
+    comm.finish(0)
 
 
 if __name__ == "__main__":

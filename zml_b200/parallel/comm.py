@@ -122,5 +122,21 @@ class Comm:
         return float(t.item())
 
     def close(self) -> None:
+        """Leaves the group.  The NCCL communicator is not destroyed explicitly: with collectives
+        captured in CUDA graphs the teardown can wait forever on the graph's pending work, so the
+        process group is left to process exit (see `finish`)."""
         if self.world > 1 and dist.is_initialized():
-            dist.destroy_process_group()
+            if self.device is not None and self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self.barrier()
+
+    def finish(self, code: int = 0) -> None:
+        """Barrier, flush, and end the process without running NCCL / CUDA destructors.  Every
+        rank calls it as its last statement."""
+        import os
+        import sys
+        self.close()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        if self.world > 1:
+            os._exit(code)
