@@ -12,8 +12,10 @@
 // The decode kernel is bandwidth bound (it streams the KV cache once): each warp
 // runs its own cp.async pipeline over 16-key blocks, the G query heads that share
 // one KV head are packed into the 16 rows of one m16n8k16 tile, and the KV range
-// of a sequence is split across CTAs so that all SMs stream.  Partial results
-// (unnormalised O, running max m, running sum l) are merged by a second kernel.
+// of a sequence is cut into fixed-size chunks, one CTA each, so that all SMs stream
+// whatever the mix of sequence lengths.  Partial results (unnormalised O, running
+// max m, running sum l) go to scratch and the last chunk of a (sequence, kv head)
+// to finish merges them in chunk order, in the same launch.
 #include "common.cuh"
 #include "host_api.h"
 
@@ -74,7 +76,9 @@ struct AttnParams {
   int num_kv_heads;
   int page_size;
   int max_pages;
-  int num_splits;
+  int num_splits;               // decode: upper bound of KV chunks per sequence (grid.y)
+  int chunk_blocks;             // decode: 16-key blocks per chunk
+  uint32_t* counters;           // decode: one per (sequence, kv head), zero between launches
   int window;                   // sliding window (keys), <= 0: none
   float scale_log2;             // softmax scale * log2(e)
   float softcap;                // reserved (0 = off)
@@ -183,7 +187,11 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
   const int group = p.num_q_heads / p.num_kv_heads;
   const int len = p.seq_lens[seq];
   const int nblk = (len + 15) >> 4;
-  const int per = (nblk + p.num_splits - 1) / p.num_splits;
+  // the sequence is cut into chunks of `chunk_blocks` 16-key blocks; CTAs beyond the
+  // last chunk of a short sequence have nothing to do
+  const int per = p.chunk_blocks;
+  const int my_splits = max(1, (nblk + per - 1) / per);
+  if (split >= my_splits) return;
   const int blk0 = split * per;
   const int blk1 = min(nblk, blk0 + per);
   const int first_visible = p.window > 0 ? max(0, len - p.window) : 0;
@@ -302,7 +310,7 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
       ll += f * sm_ml[(w * 16 + r) * 2 + 1];
     }
     const int head = kvh * group + r;
-    if (p.num_splits == 1) {
+    if (my_splits == 1) {
       const float inv = ll > 0.f ? 1.f / ll : 0.f;
       p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(acc * inv);
     } else {
@@ -314,24 +322,34 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
       }
     }
   }
-}
-
-template <int HD>
-__global__ void zb_decode_merge_kernel(const AttnParams p) {
-  const int sh = blockIdx.x;   // seq * num_q_heads + head
-  const int c = threadIdx.x;
-  if (c >= HD) return;
-  const size_t base = static_cast<size_t>(sh) * p.num_splits;
-  float mm = -INFINITY;
-  for (int s = 0; s < p.num_splits; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
-  const float muse = (mm == -INFINITY) ? 0.f : mm;
-  float acc = 0.f, ll = 0.f;
-  for (int s = 0; s < p.num_splits; ++s) {
-    const float f = exp2f(p.part_ml[(base + s) * 2] - muse);
-    acc += f * p.part_o[(base + s) * HD + c];
-    ll += f * p.part_ml[(base + s) * 2 + 1];
+  if (my_splits == 1) return;
+  // the last chunk to finish merges all chunks of this (sequence, kv head)
+  __shared__ uint32_t s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&p.counters[blockIdx.x], 1u);
+    s_last = (prev == static_cast<uint32_t>(my_splits - 1)) ? 1u : 0u;
+    if (s_last) p.counters[blockIdx.x] = 0u;
   }
-  p.out[static_cast<size_t>(sh) * HD + c] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+  __syncthreads();
+  if (s_last == 0u) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+    const int r = idx / HD, c = idx % HD;
+    const int head = kvh * group + r;
+    const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + head) * p.num_splits;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < my_splits; ++sp) mm = fmaxf(mm, __ldcg(&p.part_ml[(base + sp) * 2]));
+    const float muse = (mm == -INFINITY) ? 0.f : mm;
+    float acc = 0.f, ll = 0.f;
+    for (int sp = 0; sp < my_splits; ++sp) {
+      const float f = exp2f(__ldcg(&p.part_ml[(base + sp) * 2]) - muse);
+      acc += f * __ldcg(&p.part_o[(base + sp) * HD + c]);
+      ll += f * __ldcg(&p.part_ml[(base + sp) * 2 + 1]);
+    }
+    p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+  }
 }
 
 // --------------------------------------------------------------------- prefill
@@ -476,10 +494,6 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
   dim3 grid(p.batch * p.num_kv_heads, p.num_splits);
   zb_paged_decode_kernel<HD><<<grid, 128, smem, stream>>>(p);
   zb_count_launch(1);
-  if (p.num_splits > 1) {
-    zb_decode_merge_kernel<HD><<<p.batch * p.num_q_heads, HD, 0, stream>>>(p);
-    zb_count_launch(1);
-  }
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -509,30 +523,49 @@ size_t zb_decode_scratch_bytes(int batch, int num_q_heads, int head_dim, int num
   return static_cast<size_t>(batch) * num_q_heads * num_splits * (head_dim + 2) * sizeof(float);
 }
 
-// Picks the number of KV splits so that batch * kv_heads * splits covers the SMs
-// about twice, without making a split shorter than 256 keys.
-int zb_decode_plan_splits(int batch, int num_kv_heads, int max_seq_len, int num_sms) {
+// Plans the split of the KV range: returns the chunk length in 16-key blocks such that the
+// CTAs (batch * kv_heads * chunks) cover the SMs a few times over; *max_chunks receives the
+// chunk count of the longest possible sequence (the grid's second dimension).
+int zb_decode_plan_chunks(int batch, int num_kv_heads, int max_seq_len, int num_sms, int* max_chunks) {
   const int base = batch * num_kv_heads;
-  if (base <= 0) return 1;
-  int want = (2 * num_sms + base - 1) / base;
-  int by_len = (max_seq_len + 255) / 256;
-  if (want > by_len) want = by_len;
-  if (want > 32) want = 32;
-  return want < 1 ? 1 : want;
+  // 512-key chunks amortise a CTA's fixed cost (Q fragments, cross-warp merge, partial
+  // write); go down to 256 only when that leaves fewer CTAs than two per SM
+  int chunk_keys = 512;
+  if (static_cast<long long>(base) * ((max_seq_len / 2 + chunk_keys - 1) / chunk_keys) < 2ll * num_sms)
+    chunk_keys = 256;
+  int mc = (max_seq_len + chunk_keys - 1) / chunk_keys;
+  while (mc > 64) {      // bound the scratch and the merge loop
+    chunk_keys <<= 1;
+    mc = (max_seq_len + chunk_keys - 1) / chunk_keys;
+  }
+  if (max_chunks) *max_chunks = mc < 1 ? 1 : mc;
+  return chunk_keys / 16;
+}
+
+// kept for callers that think in splits: number of chunks the plan uses for max_seq_len
+int zb_decode_plan_splits(int batch, int num_kv_heads, int max_seq_len, int num_sms) {
+  int mc = 1;
+  zb_decode_plan_chunks(batch, num_kv_heads, max_seq_len, num_sms, &mc);
+  return mc;
 }
 
 int zb_paged_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
                        const int32_t* block_table, const int32_t* seq_lens, int batch,
                        int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
                        long long q_stride, float scale, int window, int num_splits, float* scratch,
-                       size_t scratch_bytes, ZbStatus* status, cudaStream_t stream) {
+                       size_t scratch_bytes, uint32_t* counters, int counters_len, ZbStatus* status,
+                       cudaStream_t stream) {
   if (batch <= 0) return 0;
   if (num_q_heads % num_kv_heads != 0 || num_q_heads / num_kv_heads > 16) return -30;
   if (page_size % 16 != 0) return -31;
   if (num_splits < 1) num_splits = 1;
+  if (batch * num_kv_heads > counters_len) return -33;
   while (num_splits > 1 &&
          zb_decode_scratch_bytes(batch, num_q_heads, head_dim, num_splits) > scratch_bytes)
     --num_splits;
+  // chunk length that lets `num_splits` chunks cover the longest sequence the block table allows
+  const int max_blocks = (max_pages * page_size + 15) / 16;
+  const int chunk_blocks = (max_blocks + num_splits - 1) / num_splits;
   AttnParams p = {};
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache);
@@ -551,6 +584,8 @@ int zb_paged_decode_ex(const void* q, const void* k_cache, const void* v_cache, 
   p.page_size = page_size;
   p.max_pages = max_pages;
   p.num_splits = num_splits;
+  p.chunk_blocks = chunk_blocks < 1 ? 1 : chunk_blocks;
+  p.counters = counters;
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
@@ -570,8 +605,8 @@ int zb_paged_decode(const void* q, const void* k_cache, const void* v_cache, voi
   if (!st) return -20;
   return zb_paged_decode_ex(q, k_cache, v_cache, out, block_table, seq_lens, batch, num_q_heads,
                             num_kv_heads, head_dim, page_size, max_pages, q_stride, scale, window,
-                            num_splits, st->attn_scratch, st->attn_scratch_bytes, st->status,
-                            reinterpret_cast<cudaStream_t>(stream));
+                            num_splits, st->attn_scratch, st->attn_scratch_bytes, st->attn_counters,
+                            st->attn_counters_len, st->status, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // total_q_blocks >= sum over sequences of ceil(q_len / 64); a safe bound is

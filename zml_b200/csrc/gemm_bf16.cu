@@ -11,9 +11,14 @@
 //
 // Both operands are K-major, so either can feed the 128-row "M" side of the MMA.
 // For few tokens (decode) the weight rows take the 128-row side and the tokens
-// the N side ("swap-AB"), and K is split across CTAs so that all 148 SMs stream
-// weights; partial sums go through an fp32 workspace and the last CTA of a tile
-// reduces them in a fixed order (deterministic).
+// the N side ("swap-AB").
+//
+// Work is distributed stream-K style: the (output tile, k-block) space is cut into
+// one contiguous, equally sized range per CTA, so every SM streams the same number
+// of operand bytes whatever the tile count (no wave quantisation).  A CTA whose
+// range covers only part of a tile's K extent writes an fp32 partial tile to scratch
+// (at most two per CTA); the last CTA to arrive for a tile sums the pieces in CTA
+// order (deterministic) and runs the epilogue.
 #include <cuda.h>
 
 #include <mutex>
@@ -43,9 +48,10 @@ struct GemmParams {
   const __nv_bfloat16* residual;   // same layout as out, may be null
   const __nv_bfloat16* bias;       // indexed by output column, may be null
   int out_f32;       // 0: bf16 output, 1: fp32 output
-  int splits;        // K splits
+  int units_per_cta; // k-blocks per CTA (stream-K range length)
+  int rr_tiles;      // > 0: whole tiles dealt round-robin, this many per CTA (large problems)
   int group_p;       // rasterisation group height (P tiles)
-  float* workspace;  // [splits][tiles][BN][128] fp32, used when splits > 1
+  float* workspace;  // [grid][2][BN][128] fp32 partial tiles
   uint32_t* counters;  // one per output tile, zero between launches
   ZbStatus* status;
   ZbFusedAr ar;        // used by the fused GEMM + all-reduce variant only
@@ -87,9 +93,14 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   const int num_p = (prm.rows_p + kBlockP - 1) / kBlockP;
   const int num_q = (prm.rows_q + BN - 1) / BN;
   const int kb_total = (prm.k + kBlockK - 1) / kBlockK;
-  const int kb_per = (kb_total + prm.splits - 1) / prm.splits;
   const int num_out_tiles = num_p * num_q;
-  const int num_work = num_out_tiles * prm.splits;
+  // Large problems: whole tiles are dealt round-robin (CTAs running at the same time work on
+  // neighbouring tiles and share operands in L2); a CTA's "virtual" tiles are then contiguous
+  // and map to actual tile (v % rr_tiles) * grid + cta.  Small problems: stream-K ranges.
+  const long long total_units =
+      static_cast<long long>(prm.rr_tiles > 0 ? static_cast<int>(gridDim.x) * prm.rr_tiles : num_out_tiles) * kb_total;
+  const long long u_begin = min(total_units, static_cast<long long>(blockIdx.x) * prm.units_per_cta);
+  const long long u_end = min(total_units, u_begin + prm.units_per_cta);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -114,11 +125,9 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   zb_tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  // work item -> (p tile, q tile, split); P tiles are grouped so that one wave of
-  // CTAs shares few distinct operand tiles in L2.
-  auto decode = [&](int work, int& pt, int& qt, int& split) {
-    split = work % prm.splits;
-    const int t = work / prm.splits;
+  // output tile -> (p tile, q tile); P tiles are grouped so that CTAs working at the
+  // same time share few distinct operand tiles in L2.
+  auto decode = [&](int t, int& pt, int& qt) {
     const int per_group = prm.group_p * num_q;
     const int g = t / per_group;
     const int within = t - g * per_group;
@@ -135,11 +144,17 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       zb_tma_prefetch_desc(&tmap_q);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
-        int pt, qt, split;
-        decode(work, pt, qt, split);
-        const int kb0 = split * kb_per;
-        const int kb1 = min(kb_total, kb0 + kb_per);
+      for (long long u = u_begin; ok && u < u_end;) {
+        const int v = static_cast<int>(u / kb_total);
+        const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
+        const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
+        const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles : v;
+        if (t >= num_out_tiles) {
+          u += kb1 - kb0;
+          continue;
+        }
+        int pt, qt;
+        decode(t, pt, qt);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
             ok = false;
@@ -155,6 +170,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             phase ^= 1u;
           }
         }
+        u += kb1 - kb0;
       }
     }
   } else if (warp == 1) {
@@ -163,11 +179,12 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int work = blockIdx.x; ok && work < num_work; work += gridDim.x) {
-        int pt, qt, split;
-        decode(work, pt, qt, split);
-        const int kb0 = split * kb_per;
-        const int kb1 = min(kb_total, kb0 + kb_per);
+      for (long long u = u_begin; ok && u < u_end;) {
+        const int v = static_cast<int>(u / kb_total);
+        const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
+        const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
+        u += kb1 - kb0;
+        if (prm.rr_tiles > 0 && (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles >= num_out_tiles) continue;
         if (!zb_mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) break;
         zb_tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -206,9 +223,21 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     uint32_t acc = 0, acc_phase = 0;
     uint32_t epoch = 0;
     if constexpr (FUSED) epoch = *reinterpret_cast<volatile uint32_t*>(prm.ar.epoch);
-    for (int work = blockIdx.x; work < num_work; work += gridDim.x) {
-      int pt, qt, split;
-      decode(work, pt, qt, split);
+    for (long long u = u_begin; u < u_end;) {
+      const int v = static_cast<int>(u / kb_total);
+      const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
+      const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
+      const bool partial = !(kb0 == 0 && kb1 == kb_total);
+      const int my_slot = (u == u_begin) ? 0 : 1;
+      u += kb1 - kb0;
+      const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles : v;
+      if (t >= num_out_tiles) continue;
+      int pt, qt;
+      decode(t, pt, qt);
+      // CTAs that hold a piece of this tile: [first_cta, last_cta]
+      const long long t_begin = static_cast<long long>(t) * kb_total;
+      const int first_cta = static_cast<int>(t_begin / prm.units_per_cta);
+      const int last_cta = static_cast<int>((t_begin + kb_total - 1) / prm.units_per_cta);
       zb_mbar_wait(&tmem_full[acc], acc_phase, abort_flag);
       epi_bar_sync();
       if (*abort_flag != 0u) break;
@@ -219,10 +248,9 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const int out_tile = pt * num_q + qt;
 
       bool do_store = true;
-      if (prm.splits > 1) {
-        // write this split's partial tile: ws[((split*tiles + tile)*BN + c)*128 + row]
-        float* ws = prm.workspace +
-                    (static_cast<size_t>(split) * num_out_tiles + out_tile) * (BN * kBlockP);
+      if (partial) {
+        // write this CTA's piece: ws[((cta*2 + slot)*BN + c)*128 + row]
+        float* ws = prm.workspace + (static_cast<size_t>(blockIdx.x) * 2 + my_slot) * (BN * kBlockP);
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16];
@@ -235,7 +263,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         epi_bar_sync();
         if (epi_tid == 0) {
           const uint32_t prev = atomicAdd(&prm.counters[out_tile], 1u);
-          const uint32_t last = (prev == static_cast<uint32_t>(prm.splits - 1)) ? 1u : 0u;
+          const uint32_t last = (prev == static_cast<uint32_t>(last_cta - first_cta)) ? 1u : 0u;
           if (last) prm.counters[out_tile] = 0u;   // ready for the next launch
           *is_last_flag = last;
         }
@@ -244,19 +272,20 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         if (do_store) __threadfence();
       }
       // the accumulator stage can be reused as soon as it has been read
-      if (prm.splits > 1) {
+      if (partial) {
         zb_tc_fence_before();
         zb_mbar_arrive(&tmem_empty[acc]);
       }
 
-      // chunk of 16 accumulator columns of this thread's row (summed over splits if any)
+      // chunk of 16 accumulator columns of this thread's row (summed over the pieces if any)
       auto load_chunk = [&](int c0, float (&v)[16]) {
-        if (prm.splits > 1) {
+        if (partial) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int s = 0; s < prm.splits; ++s) {
-            const float* ws = prm.workspace +
-                              (static_cast<size_t>(s) * num_out_tiles + out_tile) * (BN * kBlockP);
+          for (int c = first_cta; c <= last_cta; ++c) {
+            const long long c_begin = static_cast<long long>(c) * prm.units_per_cta;
+            const int slot = (max(t_begin, c_begin) == c_begin) ? 0 : 1;
+            const float* ws = prm.workspace + (static_cast<size_t>(c) * 2 + slot) * (BN * kBlockP);
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] += __ldcg(&ws[(c0 + j) * kBlockP + row_in_tile]);
           }
@@ -380,7 +409,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             d4[1] = make_uint4(zb_pack_bf16x2(v[8], v[9]), zb_pack_bf16x2(v[10], v[11]),
                                zb_pack_bf16x2(v[12], v[13]), zb_pack_bf16x2(v[14], v[15]));
           }
-          if (prm.splits == 1) {
+          if (!partial) {
             zb_tc_fence_before();
             zb_mbar_arrive(&tmem_empty[acc]);
           }
@@ -423,12 +452,9 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             epi_bar_sync();
             if (epi_tid < ar.world) zb_st_release_sys(ar.done_flag_peer[epi_tid] + out_tile, epoch);
           }
-        } else if (prm.splits == 1) {
-          zb_tc_fence_before();
-          zb_mbar_arrive(&tmem_empty[acc]);
         }
       }
-      if (!FUSED && prm.splits == 1) {
+      if (!FUSED && !partial) {
         zb_tc_fence_before();
         zb_mbar_arrive(&tmem_empty[acc]);
       }
@@ -539,10 +565,13 @@ int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, 
 
 extern "C" {
 
-// Plans K splits for a swap-AB (few-token) GEMM; exposed for tests and for sizing scratch.
-int zb_gemm_plan(int m, int n, int k, int num_sms, int* swap, int* bn, int* splits) {
+// Tile shape and grid for a problem: swap-AB for few tokens, and a stream-K grid in
+// which every CTA owns at least `min_units` k-blocks.  `split_hint` > 0 asks for about
+// that many CTAs per output tile (used by tests).  Returns the number of output tiles.
+int zb_gemm_plan(int m, int n, int k, int num_sms, int split_hint, int* swap, int* bn, int* grid,
+                 int* units_per_cta, int* rr_tiles) {
   const int kb_total = (k + kBlockK - 1) / kBlockK;
-  int sw = m <= 256 ? 1 : 0;
+  const int sw = m <= 256 ? 1 : 0;
   int b;
   if (sw) {
     b = 16;
@@ -553,46 +582,54 @@ int zb_gemm_plan(int m, int n, int k, int num_sms, int* swap, int* bn, int* spli
   const int rows_p = sw ? n : m;
   const int rows_q = sw ? m : n;
   const int tiles = ((rows_p + kBlockP - 1) / kBlockP) * ((rows_q + b - 1) / b);
-  int sp = 1;
-  if (tiles * 2 <= num_sms) {
-    sp = num_sms / tiles;
-    const int max_by_k = kb_total / 4 > 0 ? kb_total / 4 : 1;   // at least 4 k-blocks per split
-    if (sp > max_by_k) sp = max_by_k;
-    if (sp > 16) sp = 16;
-    if (sp < 1) sp = 1;
-    // every split must own at least one k-block
-    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
-  }
   *swap = sw;
   *bn = b;
-  *splits = sp;
+  if (tiles >= 4 * num_sms && split_hint <= 0) {
+    // many tiles: whole tiles, round-robin; wave quantisation is below 1/4 of a wave in 4+
+    const int per = (tiles + num_sms - 1) / num_sms;
+    *grid = num_sms;
+    *rr_tiles = per;
+    *units_per_cta = per * kb_total;
+    return tiles;
+  }
+  *rr_tiles = 0;
+  const long long total = static_cast<long long>(tiles) * kb_total;
+  const int min_units = 4;
+  long long g = total / min_units;
+  if (g < 1) g = 1;
+  if (g > num_sms) g = num_sms;
+  if (split_hint > 0) {
+    g = static_cast<long long>(tiles) * split_hint;
+    if (g > num_sms) g = num_sms;
+    if (g > total) g = total;
+  }
+  int upc = static_cast<int>((total + g - 1) / g);
+  g = (total + upc - 1) / upc;            // drop CTAs that would get nothing
+  *grid = static_cast<int>(g);
+  *units_per_cta = upc;
   return tiles;
 }
 
 size_t zb_gemm_workspace_bytes(int m, int n, int k, int num_sms) {
-  int sw, bn, sp;
-  const int tiles = zb_gemm_plan(m, n, k, num_sms, &sw, &bn, &sp);
-  if (sp <= 1) return 0;
-  return static_cast<size_t>(sp) * tiles * bn * kBlockP * sizeof(float);
+  int sw, bn, grid, upc, rr;
+  zb_gemm_plan(m, n, k, num_sms, 0, &sw, &bn, &grid, &upc, &rr);
+  return static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float);
 }
 
-// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `scratch` holds the split-K
-// partial tiles followed by nothing else; `counters` holds one zeroed u32 per
-// output tile (kept zero by the kernel).  force_splits > 0 overrides the plan.
+// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `scratch` receives the partial
+// tiles of CTAs whose k-range does not cover a whole tile (2 per CTA); `counters`
+// holds one zeroed u32 per output tile (kept zero by the kernel).
 int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residual, const void* bias,
-                    int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int force_splits,
+                    int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
                     float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
                     ZbStatus* status, int num_sms, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0) return -10;
   if (!out_f32 && (ldo % 8) != 0) return -11;
-  int sw, bn, sp;
-  zb_gemm_plan(m, n, k, num_sms, &sw, &bn, &sp);
-  const int kb_total = (k + kBlockK - 1) / kBlockK;
-  if (force_splits > 0) {
-    sp = force_splits > kb_total ? kb_total : force_splits;
-    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
-  }
+  int sw, bn, grid, upc, rr;
+  const int tiles = zb_gemm_plan(m, n, k, num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
+  if (static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > scratch_bytes) return -13;
+  if (tiles > counters_len) return -14;
   GemmParams prm;
   prm.rows_p = sw ? n : m;
   prm.rows_q = sw ? m : n;
@@ -603,28 +640,16 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   prm.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   prm.out_f32 = out_f32;
   prm.group_p = 16;
+  prm.units_per_cta = upc;
+  prm.rr_tiles = rr;
   prm.workspace = scratch;
   prm.counters = counters;
   prm.status = status;
-  const int num_p = (prm.rows_p + kBlockP - 1) / kBlockP;
-  const int num_q = (prm.rows_q + bn - 1) / bn;
-  const int tiles = num_p * num_q;
-  // shrink the split count until the partial tiles fit the scratch that was given
-  while (sp > 1 && (static_cast<size_t>(sp) * tiles * bn * kBlockP * sizeof(float) > scratch_bytes ||
-                    tiles > counters_len)) {
-    --sp;
-    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
-  }
-  prm.splits = sp;
   CUtensorMap tp, tq;
-  const void* pbase = sw ? w : a;
-  const void* qbase = sw ? a : w;
-  int rc = zb_make_tmap_bf16_2d(&tp, pbase, prm.rows_p, k, sw ? ldw : lda, kBlockP);
+  int rc = zb_make_tmap_bf16_2d(&tp, sw ? w : a, prm.rows_p, k, sw ? ldw : lda, kBlockP);
   if (rc != 0) return rc;
-  rc = zb_make_tmap_bf16_2d(&tq, qbase, prm.rows_q, k, sw ? lda : ldw, bn);
+  rc = zb_make_tmap_bf16_2d(&tq, sw ? a : w, prm.rows_q, k, sw ? lda : ldw, bn);
   if (rc != 0) return rc;
-  const int work = tiles * sp;
-  const int grid = work < num_sms ? work : num_sms;
 #define ZB_GEMM_CASE(BN_)                                                           \
   case BN_:                                                                         \
     return sw ? launch<BN_, true>(tp, tq, prm, grid, stream)                        \
@@ -642,11 +667,11 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
 
 // Convenience entry point using the library's per-device scratch (see runtime.cu).
 int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, const void* bias,
-                 int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int force_splits,
+                 int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
                  void* stream) {
   ZbDeviceState* st = zb_device_state();
   if (st == nullptr) return -20;
-  return zb_gemm_bf16_ex(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, force_splits,
+  return zb_gemm_bf16_ex(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, split_hint,
                          st->gemm_scratch, st->gemm_scratch_bytes, st->gemm_counters,
                          st->gemm_counters_len, st->status, st->num_sms,
                          reinterpret_cast<cudaStream_t>(stream));
@@ -658,19 +683,16 @@ int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, 
 // must call this with the same shapes, in the same order.  See fused_ar.h for the protocol.
 int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_t out_off,
                      const void* residual, const void* bias, int m, int n, int k, int lda, int ldw,
-                     int ldo, int force_splits, void* stream) {
+                     int ldo, int split_hint, void* stream) {
   if (ctx == nullptr || ctx->world < 1 || ctx->world > kZbMaxRanks) return -50;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (ldo % 8) != 0 || (out_off % 16) != 0) return -10;
   ZbDeviceState* st = zb_device_state();
   if (st == nullptr) return -20;
-  int sw, bn, sp;
-  zb_gemm_plan(m, n, k, st->num_sms, &sw, &bn, &sp);
-  const int kb_total = (k + kBlockK - 1) / kBlockK;
-  if (force_splits > 0) {
-    sp = force_splits > kb_total ? kb_total : force_splits;
-    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
-  }
+  int sw, bn, grid, upc, rr;
+  const int tiles = zb_gemm_plan(m, n, k, st->num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
+  if (static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > st->gemm_scratch_bytes) return -13;
+  if (tiles > st->gemm_counters_len) return -14;
   GemmParams prm;
   prm.rows_p = sw ? n : m;
   prm.rows_q = sw ? m : n;
@@ -681,18 +703,11 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   prm.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   prm.out_f32 = 0;
   prm.group_p = 16;
+  prm.units_per_cta = upc;
+  prm.rr_tiles = rr;
   prm.workspace = st->gemm_scratch;
   prm.counters = st->gemm_counters;
   prm.status = st->status;
-  const int num_p = (prm.rows_p + kBlockP - 1) / kBlockP;
-  const int num_q = (prm.rows_q + bn - 1) / bn;
-  const int tiles = num_p * num_q;
-  while (sp > 1 && (static_cast<size_t>(sp) * tiles * bn * kBlockP * sizeof(float) > st->gemm_scratch_bytes ||
-                    tiles > st->gemm_counters_len)) {
-    --sp;
-    while (sp > 1 && ((kb_total + sp - 1) / sp) * (sp - 1) >= kb_total) --sp;
-  }
-  prm.splits = sp;
   ZbFusedAr& ar = prm.ar;
   ar.rank = ctx->rank;
   ar.world = ctx->world;
@@ -713,8 +728,6 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   if (rc != 0) return rc;
   rc = zb_make_tmap_bf16_2d(&tq, sw ? a : w, prm.rows_q, k, sw ? lda : ldw, bn);
   if (rc != 0) return rc;
-  const int work = tiles * sp;
-  const int grid = work < st->num_sms ? work : st->num_sms;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define ZB_GEMM_CASE(BN_)                                                     \
   case BN_:                                                                   \

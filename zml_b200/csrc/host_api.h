@@ -21,6 +21,8 @@ struct ZbDeviceState {
   int gemm_counters_len;
   float* attn_scratch;         // split-KV partial outputs + (m, l) pairs
   size_t attn_scratch_bytes;
+  uint32_t* attn_counters;     // one per (sequence, kv head), zero between launches
+  int attn_counters_len;
 };
 
 // Peer-memory description of one tensor-parallel group, built by zb_ar_ctx_create (comm.cu).

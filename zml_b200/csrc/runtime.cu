@@ -50,6 +50,9 @@ int zb_init(int device) {
   cudaMemset(s.gemm_counters, 0, sizeof(uint32_t) * kGemmCounters);
   s.attn_scratch_bytes = kAttnScratchBytes;
   if (cudaMalloc(&s.attn_scratch, s.attn_scratch_bytes) != cudaSuccess) return -7;
+  s.attn_counters_len = 1 << 16;
+  if (cudaMalloc(&s.attn_counters, sizeof(uint32_t) * s.attn_counters_len) != cudaSuccess) return -8;
+  cudaMemset(s.attn_counters, 0, sizeof(uint32_t) * s.attn_counters_len);
   cudaDeviceSynchronize();
   g_ready[device] = true;
   if (prev >= 0 && prev != device) cudaSetDevice(prev);

@@ -35,7 +35,7 @@ _SIGS = {
     "zb_launch_count_reset": (None, []),
     "zb_launch_count_add": (None, [c_ull]),
     "zb_decode_advance": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p]),
-    "zb_gemm_plan": (c_i, [c_i, c_i, c_i, c_i, c_p, c_p, c_p]),
+    "zb_gemm_plan": (c_i, [c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
     "zb_gemm_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "zb_gemm_bf16": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
     "zb_gemm_bf16_ex": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i,

@@ -1,0 +1,98 @@
+"""Slice: a host n-d array view = shape + bytes + byte strides (zml/slice.zig).
+
+Host-side counterpart of a Buffer: what weights look like right after they were read
+from disk and what results look like after they were copied back.  Backed by numpy.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import numpy as np
+
+from .dtype import DataType
+from .shape import Shape
+
+
+class Slice:
+    def __init__(self, shape: Shape, data: Optional[np.ndarray] = None, byte_strides: Optional[Sequence[int]] = None,
+                 offset_bytes: int = 0, mutable: bool = True):
+        self.shape = shape
+        if data is None:
+            data = np.zeros(shape.byte_size(), dtype=np.uint8)
+        self.bytes = np.ascontiguousarray(data).view(np.uint8).reshape(-1) if not (
+            isinstance(data, np.ndarray) and data.dtype == np.uint8 and data.ndim == 1) else data
+        self.byte_strides = tuple(byte_strides) if byte_strides is not None else shape.compute_byte_strides()
+        self.offset_bytes = offset_bytes
+        self.mutable = mutable
+
+    # ------------------------------------------------------------------ constructors
+    @staticmethod
+    def alloc(shape: Shape) -> "Slice":
+        return Slice(shape)
+
+    @staticmethod
+    def init(shape: Shape, data) -> "Slice":
+        arr = np.asarray(data)
+        if arr.dtype != np.uint8 or arr.ndim != 1:
+            arr = np.ascontiguousarray(arr.astype(shape.dtype.to_numpy(), copy=False))
+        s = Slice(shape, arr)
+        if s.bytes.nbytes < shape.byte_size():
+            raise ValueError(f"{s.bytes.nbytes} bytes given, {shape} needs {shape.byte_size()}")
+        return s
+
+    @staticmethod
+    def from_numpy(arr: np.ndarray, tags=None) -> "Slice":
+        dt = DataType.from_numpy(arr.dtype)
+        return Slice(Shape(tuple(arr.shape), dt, tags), np.ascontiguousarray(arr))
+
+    def free(self) -> None:
+        self.bytes = np.zeros(0, dtype=np.uint8)
+
+    # ------------------------------------------------------------------ views
+    def dtype(self) -> DataType:
+        return self.shape.dtype
+
+    def const_data(self) -> np.ndarray:
+        return self.bytes[self.offset_bytes:]
+
+    def is_contiguous(self) -> bool:
+        return self.byte_strides == self.shape.compute_byte_strides()
+
+    def items(self) -> np.ndarray:
+        """Typed n-d numpy view (no copy); sub-byte and exotic 8-bit floats come back as raw bytes."""
+        npdt = np.dtype(self.shape.dtype.to_numpy())
+        return np.lib.stride_tricks.as_strided(
+            self.bytes[self.offset_bytes:].view(npdt) if self.offset_bytes % npdt.itemsize == 0
+            else np.frombuffer(self.bytes.tobytes()[self.offset_bytes:], dtype=npdt),
+            shape=self.shape.dims, strides=self.byte_strides, writeable=self.mutable)
+
+    def sub_slice(self, axis, start: int, size: int) -> "Slice":
+        a = self.shape.axis(axis)
+        if start < 0 or start + size > self.shape.dims[a]:
+            raise IndexError(f"sub_slice [{start}, {start + size}) outside axis {axis} of {self.shape}")
+        return Slice(self.shape.set_dim(a, size), self.bytes, self.byte_strides,
+                     self.offset_bytes + start * self.byte_strides[a], self.mutable)
+
+    subSlice = sub_slice
+
+    def squeeze(self, axis) -> "Slice":
+        a = self.shape.axis(axis)
+        if self.shape.dims[a] != 1:
+            raise ValueError("squeeze needs an axis of size 1")
+        return Slice(self.shape.remove(a), self.bytes, self.byte_strides[:a] + self.byte_strides[a + 1:],
+                     self.offset_bytes, self.mutable)
+
+    def copy(self) -> "Slice":
+        return Slice.from_numpy(np.ascontiguousarray(self.items()), self.shape.tags)
+
+    def to_torch(self):
+        import torch
+        arr = np.ascontiguousarray(self.items())
+        t = torch.from_numpy(arr)
+        if self.shape.dtype is DataType.bf16:
+            t = t.view(torch.bfloat16)
+        return t
+
+    def __repr__(self) -> str:
+        body = np.array2string(self.items(), threshold=32, edgeitems=3, precision=4) if self.shape.count() else "[]"
+        return f"Slice({self.shape})\n{body}"
