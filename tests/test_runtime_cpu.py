@@ -1,0 +1,161 @@
+"""Platform / Buffer / compile / Exe / safetensors / TensorStore / Loader / tracer on CPU,
+with 4 virtual devices and mock 2x2 meshes like the reference's test platform."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from zml_b200 import meta, safetensors
+from zml_b200.buffer import Buffer
+from zml_b200.io import Loader, TensorStore
+from zml_b200.platform import CreateOptions, Platform, Target
+from zml_b200.profiling import Profiler, tracer
+from zml_b200.shape import Shape
+from zml_b200.sharding import TORUS, LogicalMesh, PhysicalMesh, Strategy
+from zml_b200.tensor import Tensor
+
+
+def cpu_platform(mesh=None):
+    return Platform.init(Target.cpu, CreateOptions(physical_mesh=mesh))
+
+
+def test_buffer_roundtrip_under_shardings():
+    """Replicated / 1-D / 2-D / folded shardings, like the reference's writer tests (zml/io.zig:1503-1631)."""
+    mesh = PhysicalMesh.grid((2, 2), TORUS)
+    p = cpu_platform(mesh)
+    s1 = p.register_sharding_with_strategy("m1", LogicalMesh({"model": "high_bandwidth"}), Strategy.parse_bindings({"model": "link_x"}))
+    s2 = p.register_sharding_with_strategy("m2", LogicalMesh({"a": "high_bandwidth", "b": "low_bandwidth"}),
+                                           Strategy.parse_bindings({"a": "link_x", "b": "link_y"}))
+    s3 = p.register_sharding_with_strategy("fold", LogicalMesh({"f": "high_bandwidth"}), Strategy.parse_bindings({"f": ("link_x", "link_y")}))
+    host = torch.arange(8 * 12, dtype=torch.float32).reshape(8, 12)
+    cases = [(Shape({"r": 8, "c": 12}, "f32"), None),
+             (Shape({"r": 8, "c": 12}, "f32").with_partitioning({"r": "model"}), s1),
+             (Shape({"r": 8, "c": 12}, "f32").with_partitioning({"r": "a", "c": "b"}), s2),
+             (Shape({"r": 8, "c": 12}, "f32").with_partitioning({"c": "f"}), s3)]
+    for shape, sh in cases:
+        b = Buffer.from_tensor(p, host, shape, sh)
+        assert len(b.shards) == 4
+        assert torch.equal(b.to_tensor(), host)
+        assert b.to_slice().items().tolist() == host.tolist()
+    b = Buffer.from_tensor(p, host, cases[2][0], s2)
+    assert tuple(b.local(3).shape) == (4, 6) and torch.equal(b.local(3), host[4:, 6:])
+    assert Buffer.scalar(p, 7, "i32").get_value() == 7
+    assert Buffer.uninitialized(p, cases[1][0], s1).local().shape == (4, 12)
+
+
+def test_compile_call_runner_and_result_shapes():
+    p = cpu_platform()
+
+    def forward(w: Tensor, x: Tensor) -> Tensor:
+        return x.dot(w, "d").relu()
+
+    w = Tensor.init({"dout": 3, "d": 4}, "f32")
+    x = Tensor.init({"b": 2, "d": 4}, "f32")
+    exe = p.compile(forward, (w, x))
+    assert exe.result_shapes.tags == ("b", "dout")
+    wb = Buffer.from_tensor(p, torch.ones(3, 4), w.shape())
+    xb = Buffer.from_tensor(p, torch.arange(8.0).reshape(2, 4) - 3, x.shape())
+    out = exe.call(wb, xb)
+    assert out.to_tensor().tolist() == [[0, 0, 0], [10, 10, 10]]
+    runner = exe.runner(wb)
+    assert runner.call(xb).to_tensor().tolist() == [[0, 0, 0], [10, 10, 10]]
+    with pytest.raises(ValueError):
+        exe.call(wb)
+    args = exe.args().bake(wb).set(xb)
+    assert args.flat[1] is xb
+    with pytest.raises(ValueError):
+        exe.args().set(xb, wb)
+
+
+def test_safetensors_roundtrip_index_and_metadata(tmp_path):
+    torch.manual_seed(0)
+    tensors = {"model.layers.0.w": torch.randn(6, 8).bfloat16(), "model.layers.1.w": torch.randn(6, 8).bfloat16(),
+               "model.embed": torch.arange(20, dtype=torch.int32).reshape(4, 5), "flag": torch.tensor([True, False])}
+    single = tmp_path / "one"
+    safetensors.save_sharded(tensors, str(single), metadata={"format": "pt"})
+    reg = safetensors.TensorRegistry.from_path(str(single))
+    assert set(reg.keys()) == set(tensors) and reg.metadata["format"] == "pt"
+    multi = tmp_path / "many"
+    files = safetensors.save_sharded(tensors, str(multi), max_shard_bytes=100)
+    assert len(files) > 1 and os.path.exists(multi / safetensors.INDEX_NAME)
+    reg = safetensors.TensorRegistry.from_repo(str(multi))
+    assert reg.metadata["total_size"] == sum(t.numel() * t.element_size() for t in tensors.values())
+    for k, t in tensors.items():
+        info = reg.get(k)
+        got = safetensors.bytes_to_torch(reg.reader(k).read_all(), info.shape.dims, info.shape.dtype)
+        assert torch.equal(got.view(t.dtype) if t.dtype != torch.bool else got.bool(), t)
+    # range read of rows 2..4 of a matrix
+    info = reg.get("model.layers.0.w")
+    buf = np.empty(2 * 8 * 2, dtype=np.uint8)
+    reg.reader("model.layers.0.w").read_into(buf, [(2 * 16, 32)])
+    assert torch.equal(torch.from_numpy(buf).view(torch.bfloat16).reshape(2, 8), tensors["model.layers.0.w"][2:4])
+    assert safetensors.flatten_metadata({"a": {"b": 1, "c": [1, 2]}, "d": [{"e": 1}, 2], "z": []}) == \
+        {"a.b": 1, "a.c": [1, 2], "d.0.e": 1, "d.1": 2}
+    with pytest.raises(safetensors.SafetensorsError):
+        bad = tmp_path / "bad.safetensors"
+        bad.write_bytes(b"\xff" * 16)
+        safetensors.TensorRegistry.from_path(str(bad))
+    assert safetensors.resolve_model_entrypoint(str(multi)).endswith("index.json")
+
+
+def test_tensorstore_views_and_sharded_loader(tmp_path):
+    torch.manual_seed(1)
+    w0, w1 = torch.randn(8, 12).bfloat16(), torch.randn(8, 12).bfloat16()
+    safetensors.save_sharded({"model.layers.0.mlp.w": w0, "model.layers.1.mlp.w": w1, "model.norm": torch.ones(12).bfloat16()},
+                             str(tmp_path))
+    store = TensorStore.from_path(str(tmp_path))
+    view = store.view().with_prefix("model")
+    assert view.has_key("norm") and not view.has_key("nope") and view.count() == 3
+    assert view.with_prefix("layers").with_layer(1).get_shape("mlp.w").dims == (8, 12)
+    assert view.maybe_create_tensor("nope") is None
+    mesh = PhysicalMesh.grid((2, 2), TORUS)
+    p = cpu_platform(mesh)
+    sh = p.register_sharding_with_strategy("model", LogicalMesh({"model": "high_bandwidth"}),
+                                           Strategy.parse_bindings({"model": ("link_x", "link_y")}))
+
+    class Layer:
+        def __init__(self, v):
+            self.w = v.create_tensor("mlp.w", ("dout", "d"), {"dout": "model"})
+            self.cols = v.create_tensor("mlp.w", ("d", "dout"), {"dout": "model"})      # column sharded
+            self.name = "not a tensor"
+
+    class Model:
+        def __init__(self, v):
+            self.layers = [Layer(v.with_prefix("layers").with_layer(i)) for i in range(2)]
+            self.norm = v.create_tensor("norm", ("d",))
+
+    model = Model(view)
+    loader = Loader(p, parallelism=4)
+    bufs = loader.load(model, store, [sh])
+    assert not hasattr(bufs.layers[0], "name")
+    assert torch.equal(bufs.layers[0].w.to_tensor(), w0) and torch.equal(bufs.layers[1].cols.to_tensor(), w1)
+    assert tuple(bufs.layers[0].w.local(2).shape) == (2, 12) and tuple(bufs.layers[0].cols.local(2).shape) == (8, 3)
+    assert torch.equal(bufs.layers[0].cols.local(1), w0[:, 3:6])
+    assert torch.equal(bufs.norm.to_tensor(), torch.ones(12).bfloat16()) and len(bufs.norm.shards) == 4
+    assert loader.bytes_loaded == (2 * 2 * 8 * 12 + 12 * 4) * 2
+    assert torch.equal(store.load_tensor("model.layers.0.mlp.w", rows=(2, 5), cols=(4, 10)), w0[2:5, 4:10])
+    loader.close()
+
+
+def test_tracer_and_profiler_write_trace_events(tmp_path):
+    tracer.start()
+    with tracer.span("zml.exe.call", wait=True, arg_count=2):
+        with tracer.span("inner"):
+            pass
+    tracer.instant("marker")
+    tracer.stop()
+    out = tmp_path / "t.json"
+    tracer.write_json(str(out))
+    ev = json.load(open(out))["traceEvents"]
+    names = [e["name"] for e in ev]
+    assert "zml.exe.call" in names and "inner" in names
+    call = next(e for e in ev if e["name"] == "zml.exe.call")
+    assert call["args"] == {"wait": "True", "arg_count": "2"} and call["dur"] >= 0
+    assert tracer.encode("a", k=1) == "a#k=1#"
+    prof = Profiler(logdir=str(tmp_path), device=False)
+    with prof:
+        with tracer.span("step"):
+            pass
+    assert os.path.exists(prof.host_trace)

@@ -1,0 +1,188 @@
+"""Exe: an executable produced by `module.compile` (zml/exe.zig).
+
+`Exe.call(*buffers)` runs the program; `Exe.args()` / `Exe.results()` give the argument
+and result holders of the reference API (`set`, `bake`, `get`); `Exe.runner(prefix)` is
+`FnExe(fn).Runner(baked)`: it pre-binds a prefix of the inputs (typically the weights)
+so that later calls pass only the remaining ones.
+"""
+from __future__ import annotations
+
+from typing import Any, Callable, Optional, Sequence
+
+import torch
+
+from . import meta
+from .buffer import Buffer
+from .profiling import tracer
+from .shape import Shape
+from .tensor import Tensor
+
+
+def _is_buffer(x) -> bool:
+    return isinstance(x, Buffer)
+
+
+class Arguments:
+    """Flat list of input buffers in declaration order."""
+
+    def __init__(self, exe: "Exe"):
+        self.exe = exe
+        self.flat: list[Optional[Buffer]] = [None] * len(exe.arg_shapes)
+        self.baked = 0
+
+    def set(self, *trees) -> "Arguments":
+        bufs = meta.collect(trees, _is_buffer)
+        if len(bufs) != len(self.flat) - self.baked:
+            raise ValueError(f"expected {len(self.flat) - self.baked} buffers, got {len(bufs)}")
+        for i, b in enumerate(bufs):
+            self._check(self.baked + i, b)
+            self.flat[self.baked + i] = b
+        return self
+
+    def set_partial(self, offset: int, *trees) -> "Arguments":
+        for i, b in enumerate(meta.collect(trees, _is_buffer)):
+            self._check(offset + i, b)
+            self.flat[offset + i] = b
+        return self
+
+    def bake(self, *trees) -> "Arguments":
+        """Binds the first inputs for good; later `set` calls fill the rest."""
+        bufs = meta.collect(trees, _is_buffer)
+        for i, b in enumerate(bufs):
+            self._check(i, b)
+            self.flat[i] = b
+        self.baked = len(bufs)
+        return self
+
+    def _check(self, i: int, b: Buffer) -> None:
+        want = self.exe.arg_shapes[i]
+        if b.shape().dims != want.dims or b.shape().dtype is not want.dtype:
+            raise ValueError(f"argument {i}: expected {want}, got {b.shape()}")
+
+
+class Results:
+    def __init__(self, exe: "Exe"):
+        self.exe = exe
+        self.tree = None
+
+    def get(self):
+        return self.tree
+
+    def fill(self, tree) -> None:
+        self.tree = tree
+
+
+class Exe:
+    def __init__(self, fn: Callable, arg_tree: tuple, arg_shapes: list[Shape], result_shapes, platform, name: str,
+                 cuda_graph: bool):
+        self.fn = fn
+        self.arg_tree = arg_tree
+        self.arg_shapes = arg_shapes
+        self.result_shapes = result_shapes
+        self.platform = platform
+        self.name = name
+        self.use_graph = cuda_graph and platform.target.value == "cuda"
+        self._graph = None
+        self._static_in: Optional[list[torch.Tensor]] = None
+        self._static_out = None
+        self.calls = 0
+
+    def args(self) -> Arguments:
+        return Arguments(self)
+
+    def results(self) -> Results:
+        return Results(self)
+
+    # ------------------------------------------------------------------ execution
+    def _device(self) -> torch.device:
+        return self.platform.local_devices()[0].torch_device
+
+    def _to_tensors(self, flat: Sequence[Buffer]) -> list[torch.Tensor]:
+        dev = self._device()
+        out = []
+        for b in flat:
+            if len(b.shards) == 1 and b.sharding.sharded_shape(b.shape()).dims == b.shape().dims:
+                out.append(b.local().to(dev))
+            else:
+                out.append(b.to_tensor().to(dev))
+        return out
+
+    def _run_fn(self, tensors: list[torch.Tensor]):
+        it = iter(tensors)
+        wrapped = meta.map_tree(lambda t: Tensor(next(it), t.shape()), self.arg_tree, lambda x: isinstance(x, Tensor))
+        return self.fn(*wrapped)
+
+    def _wrap_results(self, out):
+        def to_buf(t: Tensor) -> Buffer:
+            return Buffer.from_tensor(self.platform, t.data, t.shape(), self.platform.pick_sharding(t.shape()))
+        return meta.map_tree(to_buf, out, lambda x: isinstance(x, Tensor))
+
+    def call(self, *trees, wait: bool = False):
+        """Runs the program on the given buffers (any tree matching the declared arguments)."""
+        flat = meta.collect(trees, _is_buffer)
+        return self._call_flat(flat, wait)
+
+    def call_opts(self, *trees, wait: bool = True):
+        return self.call(*trees, wait=wait)
+
+    def _call_flat(self, flat: Sequence[Buffer], wait: bool):
+        if len(flat) != len(self.arg_shapes):
+            raise ValueError(f"{self.name}: expected {len(self.arg_shapes)} buffers, got {len(flat)}")
+        with tracer.span(f"zml.exe.call#wait={wait},arg_count={len(flat)}#"):
+            tensors = self._to_tensors(flat)
+            self.calls += 1
+            if self.use_graph and self.calls >= 2:
+                out = self._replay(tensors)
+            else:
+                out = self._run_fn(tensors)
+            res = self._wrap_results(out)
+            if wait and self.platform.target.value == "cuda":
+                torch.cuda.synchronize()
+            return res
+
+    def _replay(self, tensors: list[torch.Tensor]):
+        """Second and later calls on CUDA: capture once into a graph, then copy inputs into
+        the static buffers and replay."""
+        if self._graph is None:
+            self._static_in = [t.clone() for t in tensors]
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._run_fn(self._static_in)
+            torch.cuda.current_stream().wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(g):
+                    self._static_out = self._run_fn(self._static_in)
+                self._graph = g
+            except Exception:
+                # programs that synchronise or allocate outside torch cannot be captured
+                self.use_graph = False
+                torch.cuda.synchronize()
+                return self._run_fn(tensors)
+        for dst, src in zip(self._static_in, tensors):
+            dst.copy_(src)
+        self._graph.replay()
+        return meta.map_tree(lambda t: Tensor(t.data.clone(), t.shape()), self._static_out, lambda x: isinstance(x, Tensor))
+
+    def runner(self, *baked_trees) -> "Runner":
+        return Runner(self, meta.collect(baked_trees, _is_buffer))
+
+    def __repr__(self) -> str:
+        return f"Exe({self.name}, {len(self.arg_shapes)} args)"
+
+
+class Runner:
+    """An Exe with its first inputs (weights) bound once."""
+
+    def __init__(self, exe: Exe, baked: list[Buffer]):
+        self.exe = exe
+        self.baked = baked
+        for i, b in enumerate(baked):
+            want = exe.arg_shapes[i]
+            if b.shape().dims != want.dims:
+                raise ValueError(f"baked argument {i}: expected {want}, got {b.shape()}")
+
+    def call(self, *trees, wait: bool = False):
+        rest = meta.collect(trees, _is_buffer)
+        return self.exe._call_flat(self.baked + rest, wait)

@@ -10,7 +10,22 @@ import dataclasses
 from typing import Any, Callable, Iterator
 
 
+_ATOM_MODULES = ("zml_b200.tensor", "zml_b200.shape", "zml_b200.buffer", "zml_b200.dtype", "zml_b200.sharding",
+                 "torch", "numpy", "concurrent.futures")
+
+
+def _is_atom(obj) -> bool:
+    """Values that are never descended into (framework value types, arrays, scalars, enums)."""
+    import enum
+    if obj is None or isinstance(obj, (str, bytes, int, float, bool, complex, enum.Enum, type)) or callable(obj):
+        return True
+    mod = type(obj).__module__ or ""
+    return any(mod == m or mod.startswith(m + ".") for m in _ATOM_MODULES)
+
+
 def _children(obj) -> Iterator[tuple[Any, Any]]:
+    if _is_atom(obj):
+        return
     if isinstance(obj, dict):
         yield from obj.items()
     elif isinstance(obj, (list, tuple)):

@@ -1,0 +1,185 @@
+"""Platform: the devices of this machine, their mesh, and the registered shardings.
+
+Role of zml/platform.zig.  The reference loads a PJRT plugin per target and tries
+tpu, neuron, rocm, cuda, oneapi, metal, cpu in turn; this framework has exactly two
+targets: `cuda` (B200, sm_100a) and `cpu` (N virtual devices in one process - how the
+multi-device logic is tested without GPUs, like the reference's 4-device CPU test
+platform, zml/platform.zig:708-725).  A power-of-two device count is required
+(zml/platform.zig:37-50).
+"""
+from __future__ import annotations
+
+import enum
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from .shape import Shape
+from .sharding import LogicalMesh, Partitioning, PhysicalMesh, Sharding, Strategy
+
+
+class Target(enum.Enum):
+    cpu = "cpu"
+    cuda = "cuda"
+
+
+class MemoryKind(enum.Enum):
+    """zml/platform.zig:63-115."""
+    default = "default"
+    host_unpinned = "host_unpinned"
+    host_pinned = "host_pinned"
+    device = "device"
+
+
+@dataclass
+class CpuOptions:
+    device_count: int = 4
+
+
+@dataclass
+class CudaOptions:
+    allocator: str = "async"            # bfc | async | platform: torch's caching allocator is always used
+    memory_fraction: float = 0.90
+    preallocate: bool = False
+    collective_memory_size_mb: int = 0  # size of the symmetric heap for in-kernel collectives (0: on demand)
+    gpu_async_dispatch: bool = True
+
+
+@dataclass
+class CreateOptions:
+    cpu: CpuOptions = field(default_factory=CpuOptions)
+    cuda: CudaOptions = field(default_factory=CudaOptions)
+    physical_mesh: Optional[PhysicalMesh] = None     # custom mesh (tests build 2x2 / 2x2x2 tori)
+
+
+@dataclass
+class DeviceInfo:
+    id: int
+    mesh_device: object                 # sharding.Device
+    torch_device: torch.device
+    description: str = ""
+
+    def memory_stats(self) -> dict:
+        if self.torch_device.type != "cuda":
+            return {}
+        free, total = torch.cuda.mem_get_info(self.torch_device)
+        return {"bytes_in_use": total - free, "bytes_limit": total,
+                "peak_bytes_in_use": torch.cuda.max_memory_allocated(self.torch_device)}
+
+
+class Platform:
+    def __init__(self, target: Target, options: Optional[CreateOptions] = None, comm=None):
+        self.target = target
+        self.options = options or CreateOptions()
+        self.comm = comm
+        if target is Target.cuda:
+            if not torch.cuda.is_available():
+                raise RuntimeError("cuda target requested but no CUDA device is visible")
+            world = comm.world if comm is not None and comm.world > 1 else None
+            n = world or torch.cuda.device_count()
+        else:
+            n = self.options.cpu.device_count
+        if n & (n - 1):
+            raise ValueError(f"device count must be a power of two, got {n}")
+        self.physical_mesh = self.options.physical_mesh or PhysicalMesh.auto(target.value, n)
+        if self.physical_mesh.num_devices() != n:
+            raise ValueError("custom physical mesh does not match the device count")
+        self.devices: list[DeviceInfo] = []
+        for rank, md in enumerate(self.physical_mesh.devices):
+            if target is Target.cuda:
+                idx = (comm.device.index if comm is not None and comm.world > 1 else rank)
+                td = torch.device("cuda", idx)
+                desc = torch.cuda.get_device_name(idx) if (comm is None or comm.world == 1 or rank == comm.rank) else "remote"
+            else:
+                td, desc = torch.device("cpu"), "virtual cpu device"
+            self.devices.append(DeviceInfo(md.id, md, td, desc))
+        self._shardings: dict[str, Sharding] = {}
+        self._replicated = Sharding.replicated(self.physical_mesh)
+        self._shardings["replicated"] = self._replicated
+
+    # ------------------------------------------------------------------ construction
+    @staticmethod
+    def auto(options: Optional[CreateOptions] = None, comm=None) -> "Platform":
+        """cuda when a GPU is visible, else cpu (the reference tries its targets in order)."""
+        want = os.environ.get("ZB_TARGET")
+        if want:
+            return Platform(Target(want), options, comm)
+        return Platform(Target.cuda if torch.cuda.is_available() else Target.cpu, options, comm)
+
+    @staticmethod
+    def init(target, options: Optional[CreateOptions] = None, comm=None) -> "Platform":
+        return Platform(Target(target) if not isinstance(target, Target) else target, options, comm)
+
+    # ------------------------------------------------------------------ devices
+    def local_devices(self) -> list[DeviceInfo]:
+        if self.comm is not None and self.comm.world > 1:
+            return [self.devices[self.comm.rank]]
+        return list(self.devices)
+
+    def num_devices(self) -> int:
+        return len(self.devices)
+
+    def compute_capability(self) -> Optional[str]:
+        if self.target is not Target.cuda:
+            return None
+        major, minor = torch.cuda.get_device_capability(self.local_devices()[0].torch_device)
+        return f"{major}.{minor}"
+
+    # ------------------------------------------------------------------ shardings
+    def replicated_sharding(self) -> Sharding:
+        return self._replicated
+
+    def register_sharding(self, name: str, logical: LogicalMesh) -> Sharding:
+        return self.register_sharding_with_strategy(name, logical, Strategy.suggest(logical, self.physical_mesh))
+
+    def register_sharding_with_strategy(self, name: str, logical: LogicalMesh, strategy: Strategy) -> Sharding:
+        s = Sharding(name, self.physical_mesh, logical, strategy)
+        self._shardings[name] = s
+        return s
+
+    def sharding(self, name: str) -> Sharding:
+        return self._shardings[name]
+
+    def shardings(self) -> list[Sharding]:
+        return [s for n, s in self._shardings.items() if n != "replicated"]
+
+    def partitioning(self) -> Partitioning:
+        return Partitioning(self.shardings() or [self._replicated])
+
+    def pick_sharding(self, shape: Shape) -> Sharding:
+        if shape.has_at_least_one_partitioned_axis():
+            for s in self.shardings():
+                if s.covers(shape):
+                    return s
+        return self._replicated
+
+    # ------------------------------------------------------------------ compile / profile
+    def compile(self, fn, args=(), **opts):
+        from . import module
+        return module.compile(fn, args, self, **opts)
+
+    compile_fn = compile
+
+    def compile_model(self, model, method: str = "forward", args=(), **opts):
+        from . import module
+        return module.compile(getattr(model, method), args, self, **opts)
+
+    def profiler(self, **opts):
+        from .profiling import Profiler
+        return Profiler(**opts)
+
+    # ------------------------------------------------------------------ printing
+    def fmt_verbose(self) -> str:
+        lines = [f"Platform(target={self.target.value}, devices={len(self.devices)})", f"  mesh: {self.physical_mesh}"]
+        for d in self.local_devices():
+            st = d.memory_stats()
+            mem = f" mem {st['bytes_in_use'] / 2 ** 30:.1f}/{st['bytes_limit'] / 2 ** 30:.1f} GiB" if st else ""
+            lines.append(f"  device {d.id} coords={d.mesh_device.coords} {d.torch_device} {d.description}{mem}")
+        for name, s in self._shardings.items():
+            lines.append(f"  sharding {name}: {s.strategy.bindings}")
+        return "\n".join(lines)
+
+    def __repr__(self) -> str:
+        return f"Platform({self.target.value}, {len(self.devices)} devices)"
