@@ -79,3 +79,32 @@ def test_llama3_inv_freq_matches_hf_formula():
     want = torch.where(wavelen < high, base, torch.where(wavelen > low, base / 8.0,
                        (1 - smooth) * base / 8.0 + smooth * base))
     assert torch.allclose(f, want, rtol=1e-5, atol=0)
+
+
+def test_moe_model_generates_and_matches_dense_expert_math():
+    from zml_b200 import moe
+    from zml_b200.models.qwen3_moe import PRESETS as MOE_PRESETS, Qwen3MoeConfig, Qwen3MoeModel
+    torch.manual_seed(0)
+    cfg = Qwen3MoeConfig.from_hf(MOE_PRESETS["tiny-moe-test"])
+    model = Qwen3MoeModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=4, std=0.08)
+    eng = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=128)
+    outs, st = eng.generate([[3, 4, 5, 6, 7], list(range(20, 60))], 5)
+    assert [len(o) for o in outs] == [5, 5]
+    # the layer's MoE equals the per-expert dense computation
+    lw = model.layers[0]
+    x = torch.randn(9, cfg.hidden_size) * 0.5
+    y = model.mlp(lw, torch.zeros_like(x), x)
+    logits = ref.gemm(x, lw.extra["router"], out_dtype=torch.float32)
+    ids, w = moe.router_topk(logits, cfg.num_experts_per_tok)
+    g, u = moe.ops.deinterleave_gate_up(lw.extra["gate_up"])
+    want = moe.reference_fused_experts(x, ids, w, g, u, lw.extra["down"])
+    assert torch.allclose(y, want, atol=1e-4, rtol=1e-4)
+    # HF-named state dict round trip through safetensors and the store-based loader
+    import tempfile
+    from zml_b200 import safetensors
+    from zml_b200.io import TensorStore
+    with tempfile.TemporaryDirectory() as d:
+        safetensors.save_sharded(model.state_dict_hf(), d)
+        m2 = Qwen3MoeModel(cfg, device="cpu", dtype=torch.float32).load(TensorStore.from_path(d))
+        outs2, _ = Engine(m2, num_pages=32, page_size=16, max_batch=2, max_seq_len=128).generate([[3, 4, 5, 6, 7], list(range(20, 60))], 5)
+        assert outs2 == outs

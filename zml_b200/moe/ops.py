@@ -1,0 +1,207 @@
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Optional
+
+import torch
+
+from ..ops import _lib
+
+_lib.register_signature("zb_moe_router_topk", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                                         C.c_longlong, C.c_int, C.c_void_p], optional=False)
+_lib.register_signature("zb_moe_align", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                   C.c_int, C.c_void_p], optional=False)
+_lib.register_signature("zb_moe_gather", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                    C.c_int, C.c_int, C.c_void_p], optional=False)
+_lib.register_signature("zb_moe_finalize", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                      C.c_int, C.c_void_p], optional=False)
+_lib.register_signature("zb_moe_grouped_gemm", C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p],
+                        optional=False)
+
+
+class Backend(enum.Enum):
+    """b200: the tcgen05 grouped-GEMM path; reference: per-expert torch matmuls (CPU / oracle)."""
+    b200 = "b200"
+    reference = "reference"
+
+    @staticmethod
+    def auto(x: torch.Tensor) -> "Backend":
+        return Backend.b200 if x.is_cuda else Backend.reference
+
+
+# ---------------------------------------------------------------------- router
+def router_topk(logits: torch.Tensor, k: int, renormalize: bool = True):
+    """float32 logits [T, E] -> (ids int32 [T, k], weights float32 [T, k]): top-k experts and the
+    softmax over the selected logits (`renormalize`) or the softmax over all experts."""
+    if not logits.is_cuda:
+        lf = logits.float()
+        v, i = torch.topk(lf, k, dim=-1)
+        w = torch.softmax(v, -1) if renormalize else torch.softmax(lf, -1).gather(1, i)
+        return i.to(torch.int32), w
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    t, e = logits.shape
+    ids = torch.empty((t, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((t, k), dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.lib().zb_moe_router_topk(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), t, e, k,
+                                             logits.stride(0), int(renormalize), _lib.stream_ptr()), "zb_moe_router_topk")
+    return ids, w
+
+
+# ---------------------------------------------------------------------- permutation
+def moe_align(ids: torch.Tensor, e0: int, e_local: int):
+    """Groups the (token, expert) pairs of the local experts [e0, e0 + e_local) by expert.
+    Returns (meta, sorted_pair, pair_pos): meta[:e_local + 1] are the row offsets of each
+    expert in the permuted order, sorted_pair[pos] is the pair index t * k + j at row `pos`,
+    pair_pos[pair] is the row of a pair (-1: expert not local)."""
+    pairs = ids.numel()
+    dev = ids.device
+    if not ids.is_cuda:
+        flat = ids.reshape(-1).long() - e0
+        local = (flat >= 0) & (flat < e_local)
+        order = torch.argsort(torch.where(local, flat, torch.full_like(flat, e_local)), stable=True)
+        n = int(local.sum())
+        sorted_pair = order[:n].to(torch.int32)
+        counts = torch.bincount(flat[local], minlength=e_local)
+        meta = torch.zeros(2 * e_local + 2, dtype=torch.int32)
+        meta[1:e_local + 1] = torch.cumsum(counts, 0).to(torch.int32)
+        pair_pos = torch.full((pairs,), -1, dtype=torch.int32)
+        pair_pos[sorted_pair.long()] = torch.arange(n, dtype=torch.int32)
+        full = torch.zeros(pairs, dtype=torch.int32)
+        full[:n] = sorted_pair
+        return meta, full, pair_pos
+    meta = torch.empty(2 * e_local + 2, dtype=torch.int32, device=dev)
+    sorted_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
+    pair_pos = torch.empty(pairs, dtype=torch.int32, device=dev)
+    _lib.check(_lib.lib().zb_moe_align(ids.data_ptr(), meta.data_ptr(), sorted_pair.data_ptr(), pair_pos.data_ptr(),
+                                       pairs, e0, e_local, _lib.stream_ptr()), "zb_moe_align")
+    return meta, sorted_pair, pair_pos
+
+
+def gather(x: torch.Tensor, sorted_pair: torch.Tensor, meta: torch.Tensor, e_local: int, k: int, cap: int):
+    """xs[pos] = x[sorted_pair[pos] // k] for the rows in use; xs has `cap` rows."""
+    d = x.shape[1]
+    if not x.is_cuda:
+        n = int(meta[e_local])
+        xs = torch.zeros((cap, d), dtype=x.dtype)
+        xs[:n] = x[(sorted_pair[:n].long() // k)]
+        return xs
+    xs = torch.empty((cap, d), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().zb_moe_gather(x.data_ptr(), sorted_pair.data_ptr(), meta.data_ptr(), xs.data_ptr(), e_local,
+                                        k, d, cap, _lib.stream_ptr()), "zb_moe_gather")
+    return xs
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[E, F, D] x 2 -> [E, 2F, D] with rows laid out [64 gate | 64 up] per 128-row block, the
+    layout the grouped GEMM's SwiGLU epilogue expects (F must be a multiple of 64)."""
+    e, f, d = gate.shape
+    assert f % 64 == 0 and up.shape == gate.shape
+    g = gate.reshape(e, f // 64, 64, d)
+    u = up.reshape(e, f // 64, 64, d)
+    return torch.cat([g, u], 2).reshape(e, 2 * f, d).contiguous()
+
+
+def deinterleave_gate_up(w: torch.Tensor):
+    e, f2, d = w.shape
+    b = w.reshape(e, f2 // 128, 2, 64, d)
+    return b[:, :, 0].reshape(e, f2 // 2, d), b[:, :, 1].reshape(e, f2 // 2, d)
+
+
+def grouped_gemm(xs: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8):
+    """Per local expert e: out[rows_e] = xs[rows_e] @ w[e]^T; `swiglu`: w is the interleaved
+    gate/up weight [E, 2F, K] and out is silu(gate) * up, [cap, F]."""
+    e_local, n, k = w.shape
+    cap = xs.shape[0]
+    n_out = n // 2 if swiglu else n
+    if not xs.is_cuda:
+        out = torch.zeros((cap, n_out), dtype=xs.dtype)
+        gate_up = deinterleave_gate_up(w) if swiglu else None
+        for e in range(e_local):
+            a, b = int(meta[e]), int(meta[e + 1])
+            if b <= a:
+                continue
+            x = xs[a:b].float()
+            if swiglu:
+                g, u = gate_up
+                out[a:b] = (torch.nn.functional.silu(x @ g[e].float().t()) * (x @ u[e].float().t())).to(xs.dtype)
+            else:
+                out[a:b] = (x @ w[e].float().t()).to(xs.dtype)
+        return out
+    assert xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and xs.is_contiguous() and w.is_contiguous()
+    out = torch.empty((cap, n_out), dtype=xs.dtype, device=xs.device)
+    _lib.check(_lib.lib().zb_moe_grouped_gemm(xs.data_ptr(), w.data_ptr(), out.data_ptr(), meta.data_ptr(), e_local, n, k,
+                                              cap, n_out, int(swiglu), int(avg_tokens), _lib.stream_ptr()),
+               "zb_moe_grouped_gemm")
+    return out
+
+
+def finalize(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tokens: int, k: int):
+    """y[t] = sum_j weights[t, j] * o[pair_pos[t * k + j]] over the pairs that are local."""
+    d = o.shape[1]
+    if not o.is_cuda:
+        pos = pair_pos.reshape(tokens, k).long()
+        valid = pos >= 0
+        rows = o[pos.clamp_min(0)].float() * (weights.float() * valid)[..., None]
+        return rows.sum(1).to(o.dtype)
+    y = torch.empty((tokens, d), dtype=o.dtype, device=o.device)
+    _lib.check(_lib.lib().zb_moe_finalize(o.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(), y.data_ptr(), tokens, k, d,
+                                          _lib.stream_ptr()), "zb_moe_finalize")
+    return y
+
+
+# ---------------------------------------------------------------------- fused experts
+def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w_gate_up_il: torch.Tensor,
+                  w_down: torch.Tensor, e0: int = 0, num_experts_total: Optional[int] = None) -> torch.Tensor:
+    """Mixture output of the LOCAL experts for all tokens: permute -> grouped GEMM (+SwiGLU) ->
+    grouped GEMM -> un-permute x routing weight.  x [T, D] bf16; w_gate_up_il [E_local, 2F, D]
+    (interleaved, see `interleave_gate_up`); w_down [E_local, D, F]."""
+    t, d = x.shape
+    k = topk_ids.shape[1]
+    e_local = w_gate_up_il.shape[0]
+    total_e = num_experts_total or e_local
+    cap = t * k
+    avg = max(1, (t * k) // max(total_e, 1))
+    meta, sorted_pair, pair_pos = moe_align(topk_ids, e0, e_local)
+    xs = gather(x, sorted_pair, meta, e_local, k, cap)
+    h = grouped_gemm(xs, w_gate_up_il, meta, swiglu=True, avg_tokens=avg)
+    o = grouped_gemm(h, w_down, meta, swiglu=False, avg_tokens=avg)
+    return finalize(o, pair_pos, topk_w, t, k)
+
+
+def reference_fused_experts(x, topk_ids, topk_w, gate, up, down, e0: int = 0):
+    """Oracle: for every token, sum over its experts that are local (dense per-expert matmuls in f32)."""
+    t, d = x.shape
+    y = torch.zeros((t, d), dtype=torch.float32, device=x.device)
+    xf = x.float()
+    for e in range(gate.shape[0]):
+        sel = (topk_ids == (e + e0))
+        tok = sel.any(1).nonzero()[:, 0]
+        if tok.numel() == 0:
+            continue
+        w = (topk_w.float() * sel).sum(1)[tok]
+        h = torch.nn.functional.silu(xf[tok] @ gate[e].float().t()) * (xf[tok] @ up[e].float().t())
+        h = h.to(x.dtype).float()
+        y[tok] += w[:, None] * (h @ down[e].float().t()).to(x.dtype).float()
+    return y.to(x.dtype)
+
+
+def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor, comm=None, num_experts_total: Optional[int] = None, residual=None):
+    """Routed mixture with expert parallelism.  `w_gate_up` / `w_down` hold this rank's experts
+    (rank r owns experts [r * E_local, (r + 1) * E_local)); partial outputs are summed across
+    ranks (in-kernel over peer memory when `comm.fused` is set, NCCL otherwise) and `residual`
+    is added once."""
+    e_local = w_gate_up.shape[0]
+    world = comm.world if comm is not None else 1
+    rank = comm.rank if comm is not None else 0
+    y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, num_experts_total or e_local * world)
+    if world > 1:
+        if getattr(comm, "fused", None) is not None and y.is_cuda and comm.fused.staging is not None:
+            y = comm.fused.all_reduce(y)
+        else:
+            y = comm.all_reduce_(y)
+    if residual is not None:
+        y = y + residual
+    return y
