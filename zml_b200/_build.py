@@ -78,6 +78,9 @@ def build_cuda(force: bool = False, verbose: bool = False, extra_flags: list[str
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
         objs = list(ex.map(compile_one, srcs))
     _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-lpthread", "-ldl"])
+    # every symbol must resolve at load time (works without a GPU or a driver)
+    import ctypes
+    ctypes.CDLL(str(target), mode=getattr(os, "RTLD_NOW", 2))
     return target
 
 

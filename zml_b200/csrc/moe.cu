@@ -13,7 +13,7 @@
 #include "common.cuh"
 #include "host_api.h"
 
-extern "C" int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld, int box_rows);
+int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld, int box_rows);
 
 namespace {
 
@@ -572,7 +572,7 @@ int zb_moe_grouped_gemm(const void* xs, const void* w, void* out, const int32_t*
     while (bn < avg_tokens * 2 && bn < 64) bn <<= 1;
     if (n % kBlockP != 0) return -64;
   } else {
-    bn = 256;
+    bn = (n % 256 == 0) ? 256 : 128;
     if (n % bn != 0) return -64;
   }
   GroupedParams prm;
@@ -600,8 +600,10 @@ int zb_moe_grouped_gemm(const void* xs, const void* w, void* out, const int32_t*
       case 32: ZB_G(32, true)
       case 64: ZB_G(64, true)
     }
-  } else {
+  } else if (bn == 256) {
     ZB_G(256, false)
+  } else {
+    ZB_G(128, false)
   }
 #undef ZB_G
   return -65;
