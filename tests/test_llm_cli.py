@@ -1,0 +1,53 @@
+"""The llm CLI end to end on CPU: synthetic repo (config.json, safetensors, tokenizer.json)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from zml_b200 import safetensors
+from zml_b200.models import hub
+from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
+from zml_b200.serving import Engine
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+tokenizers = pytest.importorskip("tokenizers")
+
+
+def make_repo(path):
+    from tokenizers import Tokenizer as HfTok, decoders, models, pre_tokenizers, trainers
+    cfg = dict(PRESETS["tiny-llama-test"], model_type="llama", vocab_size=512)
+    model = LlamaModel(LlamaConfig.from_hf(cfg), device="cpu", dtype=torch.float32).init_random(seed=9, std=0.08)
+    safetensors.save_sharded({k: v.contiguous() for k, v in model.state_dict_hf().items()}, path, max_shard_bytes=1 << 20)
+    json.dump(cfg, open(os.path.join(path, "config.json"), "w"))
+    t = HfTok(models.BPE())
+    t.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    t.decoder = decoders.ByteLevel()
+    t.train_from_iterator(["hello world the quick brown fox"] * 10,
+                          trainers.BpeTrainer(vocab_size=300, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                              special_tokens=["<|begin_of_text|>", "<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"]))
+    t.save(os.path.join(path, "tokenizer.json"))
+    return model
+
+
+def test_load_model_from_repo_reproduces_weights(tmp_path):
+    ref_model = make_repo(str(tmp_path))
+    model, tok = hub.load_model(str(tmp_path), device="cpu", dtype=torch.float32)
+    assert tok is not None and torch.equal(model.layers[1].qkv, ref_model.layers[1].qkv)
+    assert torch.equal(model.layers[0].gate_up, ref_model.layers[0].gate_up)
+    a, _ = Engine(model, 32, 16, 2, 128).generate([[1, 2, 3]], 4)
+    b, _ = Engine(ref_model, 32, 16, 2, 128).generate([[1, 2, 3]], 4)
+    assert a == b
+    ids = hub.tokenize_prompt(tok, "hello", "llama3", 0)
+    assert ids[:2] == [0, tok.token_id("<|start_header_id|>")] and ids.count(tok.token_id("<|eot_id|>")) == 1
+
+
+def test_cli_prompt_mode(tmp_path):
+    make_repo(str(tmp_path))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "llm", "main.py"), f"--model={tmp_path}",
+                        "--prompt=hello world", "--seqlen=128", "--max-new-tokens=5", "--cpu"],
+                       capture_output=True, text=True, timeout=180)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "tok/s" in r.stdout and "Loaded weights" in r.stderr

@@ -1,0 +1,73 @@
+"""Open a model repository (config.json + safetensors + tokenizer) and build the matching
+model, as `LoadedModel.load` does in the reference (examples/llm/models.zig:27-95)."""
+from __future__ import annotations
+
+import logging
+import os
+import time
+from typing import Optional
+
+import torch
+
+from ..io import TensorStore
+from ..parallel.comm import Comm
+from ..tokenizer import Tokenizer
+from . import common
+from .registry import model_class_for
+
+log = logging.getLogger("zml_b200.llm")
+
+
+def open_repo(path: str):
+    """(config dict, TensorStore, repo dir) for a checkpoint path (directory, .safetensors or index)."""
+    from .. import safetensors
+    repo = safetensors.resolve_model_repo(path)
+    cfg = common.read_config_json(repo)
+    entry = path if os.path.isfile(path) else safetensors.resolve_model_entrypoint(repo)
+    return cfg, TensorStore.from_path(entry), repo
+
+
+def load_model(path: str, comm: Optional[Comm] = None, device="cpu", dtype=torch.bfloat16, fused: bool = True):
+    """Returns (model, tokenizer or None).  Weights are streamed shard-by-shard for this rank."""
+    cfg, store, repo = open_repo(path)
+    config_cls, model_cls = model_class_for(cfg)
+    config = config_cls.from_hf(cfg.get("text_config", cfg) if "hidden_size" not in cfg else cfg)
+    comm = comm or Comm.single(torch.device(device))
+    t0 = time.perf_counter()
+    model = model_cls(config, comm, device=device, dtype=dtype).load(store)
+    dt = time.perf_counter() - t0
+    nbytes = model.weight_bytes()
+    log.info("Loaded weights [%.2f GiB, %.2fs, %.2f GiB/s]", nbytes / 2 ** 30, dt, nbytes / 2 ** 30 / max(dt, 1e-9))
+    if fused and comm.world > 1 and torch.device(device).type == "cuda":
+        from ..parallel import symm
+        comm.fused = symm.SymmetricContext.create(comm, config.hidden_size, staging_elems=8192 * config.hidden_size)
+    tok = None
+    for name in ("tokenizer.json", "tokenizer.model"):
+        p = os.path.join(repo, name)
+        if os.path.exists(p):
+            tok = Tokenizer.from_file(p)
+            break
+    return model, tok
+
+
+def chat_template(model_type: str) -> str:
+    return "chatml" if model_type.startswith(("qwen", "lfm")) else "llama3"
+
+
+def tokenize_prompt(tok: Tokenizer, prompt: str, template: str, bos: Optional[int], first_turn: bool = True) -> list[int]:
+    """Chat-template tokenisation built from special tokens, as the reference's sessions do
+    (llama: examples/llm/models/llama/session.zig:100-146; ChatML for the Qwen / LFM families)."""
+    if template == "llama3":
+        sh, eh, eot = tok.token_id("<|start_header_id|>"), tok.token_id("<|end_header_id|>"), tok.token_id("<|eot_id|>")
+        if None in (sh, eh, eot):
+            return ([bos] if first_turn and bos is not None else []) + tok.encode(prompt)
+        nl = tok.encode("\n")
+        out = [bos, sh] if first_turn and bos is not None else ([sh] if first_turn else [eot] + nl + [sh])
+        out += tok.encode("user") + [eh] + nl + tok.encode(prompt) + [eot] + nl + [sh] + tok.encode("assistant") + [eh] + nl
+        return out
+    ims, ime = tok.token_id("<|im_start|>"), tok.token_id("<|im_end|>")
+    if None in (ims, ime):
+        return tok.encode(prompt)
+    nl = tok.encode("\n")
+    pre = [] if first_turn else [ime] + nl
+    return pre + [ims] + tok.encode("user") + nl + tok.encode(prompt) + [ime] + nl + [ims] + tok.encode("assistant") + nl

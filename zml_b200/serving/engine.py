@@ -371,3 +371,75 @@ class Engine:
         if self.on_gpu:
             ops.raise_on_status()
         return outputs, stats
+
+
+class Session:
+    """One multi-turn conversation on an Engine (examples/llm/models/llama/session.zig of the
+    reference: `runPrefill` / `runDecode` over a KV cache that persists across turns).
+    The KV pages for `max_tokens` are reserved when the session is created."""
+
+    def __init__(self, engine: Engine, max_tokens: int, strategy: Optional[SamplingStrategy] = None,
+                 eos_ids: Seq[int] = (), seed: int = 0):
+        self.engine = engine
+        self.max_tokens = min(max_tokens, engine.max_pages * engine.page_size)
+        self.strategy = strategy or SamplingStrategy()
+        self.eos = set(int(e) for e in eos_ids)
+        self.tokens: list[int] = []
+        self.req = Request([], 0, -1)
+        self.req.pages = engine.pool.alloc((self.max_tokens + engine.page_size - 1) // engine.page_size)
+        self._next: Optional[int] = None
+        engine.seed = seed
+
+    def close(self) -> None:
+        self.engine.release(self.req)
+
+    def remaining(self) -> int:
+        return self.max_tokens - len(self.tokens)
+
+    def run_prefill(self, new_tokens: Seq[int]) -> int:
+        """Appends `new_tokens` to the conversation, computes their KV, returns the next token."""
+        if len(self.tokens) + len(new_tokens) >= self.max_tokens:
+            raise ValueError("PromptTooLong: not enough tokens remaining; use a higher seqlen")
+        eng = self.engine
+        self.tokens.extend(int(t) for t in new_tokens)
+        self.req.prompt = self.tokens
+        tok = None
+        for chunk in eng._prefill_chunks([self.req]):
+            _, toks, _ = eng._run_prefill_chunk(chunk, self.strategy, None)
+            if toks is not None:
+                tok = int(toks[0])
+        self._next = tok
+        return tok
+
+    def run_decode(self, on_token=None, max_new_tokens: Optional[int] = None) -> list[int]:
+        """Generates until EOS or the token budget; `on_token(id)` is called per token.
+        One device -> host read per token, like the reference's decode loop."""
+        eng = self.engine
+        out: list[int] = []
+        if self._next is None:
+            return out
+        budget = self.remaining() - 1 if max_new_tokens is None else min(max_new_tokens, self.remaining() - 1)
+        tok = self._next
+        ps = eng.page_size
+        pos = len(self.tokens)
+        i32 = dict(dtype=torch.int32, device=eng.device)
+        eng.d_ids[:1] = torch.tensor([tok], **i32)
+        eng.d_pos[:1] = torch.tensor([pos], **i32)
+        eng.d_seq[:1] = torch.tensor([pos + 1], **i32)
+        eng.d_slot[:1] = torch.tensor([self.req.pages[pos // ps] * ps + pos % ps], **i32)
+        eng.d_bt[:1].zero_()
+        eng.d_bt[0, :len(self.req.pages)] = torch.tensor(self.req.pages, **i32)
+        splits = ops.decode_plan_splits(1, eng.model.hkv, self.max_tokens) if eng.on_gpu else 1
+        while True:
+            out.append(tok)
+            self.tokens.append(tok)
+            if on_token is not None:
+                on_token(tok)
+            if tok in self.eos or len(out) >= budget:
+                break
+            eng.d_step.zero_()
+            eng._decode_step(1, self.strategy, splits, self.max_tokens, None)
+            tok = int(eng.d_ids[0])
+        self._next = None
+        self.req.computed = len(self.tokens) - 1
+        return out
