@@ -1,0 +1,220 @@
+"""Virtual file system: open files by URI scheme (vfs/*.zig of the reference).
+
+Schemes: plain paths and `file://`; `http(s)://` with ranged reads; `hf://org/repo[@rev]/path`
+(Hugging Face hub, token from HF_TOKEN); `s3://bucket/key` and `gs://bucket/key` through
+their public HTTPS endpoints (anonymous or pre-signed access).  Remote files are read with
+parallel HTTP range requests (vfs/parallel_read.zig:55-211).  Every backend exposes the same
+small interface: `stat`, `read_range`, `list`, `open` (a seekable file object).
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import io
+import os
+import urllib.error
+import urllib.parse
+import urllib.request
+from dataclasses import dataclass
+from typing import Optional
+
+
+@dataclass
+class Stat:
+    size: int
+    kind: str = "file"          # file | directory
+
+
+class Backend:
+    def stat(self, path: str) -> Stat:
+        raise NotImplementedError
+
+    def read_range(self, path: str, offset: int, length: int) -> bytes:
+        raise NotImplementedError
+
+    def list(self, path: str) -> list[str]:
+        raise NotImplementedError("listing is not supported by this backend")
+
+    def realpath(self, path: str) -> str:
+        return path
+
+
+class FileBackend(Backend):
+    def stat(self, path):
+        st = os.stat(path)
+        return Stat(st.st_size, "directory" if os.path.isdir(path) else "file")
+
+    def read_range(self, path, offset, length):
+        with open(path, "rb") as f:
+            f.seek(offset)
+            return f.read(length)
+
+    def list(self, path):
+        return sorted(os.listdir(path))
+
+    def realpath(self, path):
+        return os.path.realpath(path)
+
+
+class HttpBackend(Backend):
+    def __init__(self, headers: Optional[dict] = None, timeout: float = 60.0):
+        self.headers = headers or {}
+        self.timeout = timeout
+
+    def url(self, path: str) -> str:
+        return path
+
+    def _req(self, path: str, method: str = "GET", extra: Optional[dict] = None):
+        h = dict(self.headers)
+        h.update(extra or {})
+        return urllib.request.urlopen(urllib.request.Request(self.url(path), method=method, headers=h), timeout=self.timeout)
+
+    def stat(self, path):
+        try:
+            with self._req(path, "HEAD") as r:
+                n = r.headers.get("Content-Length")
+                if n is not None:
+                    return Stat(int(n))
+        except urllib.error.HTTPError:
+            pass
+        with self._req(path, "GET", {"Range": "bytes=0-0"}) as r:
+            cr = r.headers.get("Content-Range", "")
+            return Stat(int(cr.rsplit("/", 1)[1]) if "/" in cr else int(r.headers.get("Content-Length", 0)))
+
+    def read_range(self, path, offset, length):
+        if length <= 0:
+            return b""
+        with self._req(path, "GET", {"Range": f"bytes={offset}-{offset + length - 1}"}) as r:
+            data = r.read()
+        if len(data) > length:            # server ignored the range
+            data = data[offset:offset + length]
+        return data
+
+
+class HfBackend(HttpBackend):
+    """hf://org/repo[@revision]/path/in/repo"""
+
+    def __init__(self, endpoint: str = "https://huggingface.co"):
+        tok = os.environ.get("HF_TOKEN")
+        super().__init__({"Authorization": f"Bearer {tok}"} if tok else {})
+        self.endpoint = endpoint.rstrip("/")
+
+    @staticmethod
+    def split(path: str) -> tuple[str, str, str]:
+        rest = path[len("hf://"):]
+        parts = rest.split("/")
+        if len(parts) < 2:
+            raise ValueError(f"hf uri needs org/repo: {path}")
+        repo, rev = parts[1], "main"
+        if "@" in repo:
+            repo, rev = repo.split("@", 1)
+        return f"{parts[0]}/{repo}", rev, "/".join(parts[2:])
+
+    def url(self, path):
+        repo, rev, file = self.split(path)
+        return f"{self.endpoint}/{repo}/resolve/{rev}/{file}"
+
+
+class BucketBackend(HttpBackend):
+    def __init__(self, template: str):
+        super().__init__()
+        self.template = template
+
+    def url(self, path):
+        u = urllib.parse.urlparse(path)
+        return self.template.format(bucket=u.netloc, key=u.path.lstrip("/"))
+
+
+class Vfs:
+    """Scheme multiplexer (vfs/vfs.zig:49-90)."""
+
+    def __init__(self):
+        self.backends: dict[str, Backend] = {}
+        self.register("file", FileBackend())
+
+    def register(self, scheme: str, backend: Backend) -> None:
+        self.backends[scheme] = backend
+
+    @staticmethod
+    def default() -> "Vfs":
+        v = Vfs()
+        v.register("http", HttpBackend())
+        v.register("https", HttpBackend())
+        v.register("hf", HfBackend())
+        v.register("s3", BucketBackend("https://{bucket}.s3.amazonaws.com/{key}"))
+        v.register("gs", BucketBackend("https://storage.googleapis.com/{bucket}/{key}"))
+        return v
+
+    def resolve(self, uri: str) -> tuple[Backend, str]:
+        if "://" not in uri:
+            return self.backends["file"], uri
+        scheme = uri.split("://", 1)[0]
+        if scheme not in self.backends:
+            raise ValueError(f"no backend registered for scheme {scheme!r}")
+        return self.backends[scheme], (uri[len("file://"):] if scheme == "file" else uri)
+
+    def stat(self, uri: str) -> Stat:
+        b, p = self.resolve(uri)
+        return b.stat(p)
+
+    def list(self, uri: str) -> list[str]:
+        b, p = self.resolve(uri)
+        return b.list(p)
+
+    def realpath(self, uri: str) -> str:
+        b, p = self.resolve(uri)
+        return b.realpath(p)
+
+    def read_range(self, uri: str, offset: int, length: int) -> bytes:
+        b, p = self.resolve(uri)
+        return b.read_range(p, offset, length)
+
+    def read(self, uri: str, chunk: int = 8 << 20, parallelism: int = 8) -> bytes:
+        """Whole file; remote files are fetched as parallel range requests."""
+        b, p = self.resolve(uri)
+        size = b.stat(p).size
+        if isinstance(b, FileBackend) or size <= chunk:
+            return b.read_range(p, 0, size)
+        offs = list(range(0, size, chunk))
+        with cf.ThreadPoolExecutor(max_workers=parallelism) as ex:
+            parts = list(ex.map(lambda o: b.read_range(p, o, min(chunk, size - o)), offs))
+        return b"".join(parts)
+
+    def open(self, uri: str) -> "VfsFile":
+        return VfsFile(self, uri)
+
+    def copy(self, src: str, dst: str) -> int:
+        data = self.read(src)
+        b, p = self.resolve(dst)
+        if not isinstance(b, FileBackend):
+            raise ValueError("copy destination must be a local path")
+        with open(p, "wb") as f:
+            f.write(data)
+        return len(data)
+
+
+class VfsFile(io.RawIOBase):
+    """Seekable read-only file over any backend."""
+
+    def __init__(self, vfs: Vfs, uri: str):
+        self.vfs, self.uri = vfs, uri
+        self.size = vfs.stat(uri).size
+        self.pos = 0
+
+    def readable(self):
+        return True
+
+    def seekable(self):
+        return True
+
+    def seek(self, off, whence=0):
+        self.pos = off if whence == 0 else (self.pos + off if whence == 1 else self.size + off)
+        return self.pos
+
+    def tell(self):
+        return self.pos
+
+    def read(self, n=-1):
+        n = self.size - self.pos if n is None or n < 0 else min(n, self.size - self.pos)
+        data = self.vfs.read_range(self.uri, self.pos, n) if n > 0 else b""
+        self.pos += len(data)
+        return data
