@@ -1,0 +1,46 @@
+"""zb-smi against the fake NVML: formats, HTTP endpoints, and that no setter is ever called."""
+import json
+import os
+import subprocess
+import sys
+import urllib.request
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "bin", "zb_smi"))
+
+import metrics  # noqa: E402
+import outputs  # noqa: E402
+
+
+def test_snapshot_and_formats():
+    fake = metrics.FakeNvml(devices=2)
+    be = metrics.NvmlBackend(fake)
+    snap = metrics.snapshot(be, metrics.HostPoller())
+    assert len(snap["gpus"]) == 2 and snap["gpus"][1]["util_percent"] == 91
+    g = snap["gpus"][0]
+    assert g["fan_percent"] is None and g["power_w"] == 950.0 and g["throttle_reasons"] == ["sw_power_cap"]
+    assert g["processes"][0]["pid"] == os.getpid() and snap["host"]["driver_version"] == "580.159"
+    prom = outputs.to_prometheus(snap)
+    assert 'zml_device_power_watts{device="0",name="NVIDIA B200"} 950.0' in prom and "zml_host_memory_total_bytes" in prom
+    assert "zml_device_fan_percent" not in prom
+    assert outputs.to_csv(snap).count("\n") == 1 and outputs.csv_header().startswith("timestamp,index")
+    assert json.loads(outputs.to_json(snap))["gpus"][0]["name"] == "NVIDIA B200"
+    assert "NVIDIA B200" in outputs.to_table(snap)
+    srv = outputs.serve(lambda: snap, "127.0.0.1", 0)
+    try:
+        port = srv.server_address[1]
+        assert b"zml_device_utilization_percent" in urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics").read()
+        assert json.loads(urllib.request.urlopen(f"http://127.0.0.1:{port}/json").read())["gpus"]
+    finally:
+        srv.shutdown()
+    be.close()
+    assert fake.calls == ["init", "shutdown"]
+
+
+def test_cli_fake_one_shot():
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "zb_smi", "main.py"), "--fake", "--json"],
+                       capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and json.loads(r.stdout.strip())["gpus"][0]["clock_sm_max_mhz"] == 1965
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "zb_smi", "main.py"), "--fake", "--csv", "--interval=0.1", "--count=2"],
+                       capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and len(r.stdout.strip().splitlines()) == 5
