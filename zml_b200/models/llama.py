@@ -295,7 +295,7 @@ class LlamaModel:
         comm = self.comm
         if comm.world == 1:
             return ops.gemm(a, w, residual=residual, out=residual if residual.is_cuda else None)
-        if comm.fused is not None and a.is_cuda:
+        if comm.fused is not None and a.is_cuda and a.shape[0] <= comm.fused.fused_max_tokens:
             return comm.fused.gemm_allreduce(a, w, residual)
         part = ops.gemm(a, w, residual=residual if comm.rank == 0 else None)
         return comm.all_reduce_(part)

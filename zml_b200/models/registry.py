@@ -41,7 +41,7 @@ def build_model(name: str, comm: Optional[Comm] = None, device="cuda", seed: int
         _baseline.enable(True)
     elif fused and comm.world > 1 and torch.device(device).type == "cuda":
         from ..parallel import symm
-        comm.fused = symm.SymmetricContext.create(comm, model.config.hidden_size)
+        comm.fused = symm.SymmetricContext.create(comm, model.config.hidden_size, staging_elems=512 * model.config.hidden_size)
     return model
 
 

@@ -32,10 +32,15 @@ class Backend(enum.Enum):
 
 
 # ---------------------------------------------------------------------- router
+def _baseline_on() -> bool:
+    from ..ops import baseline as _baseline
+    return _baseline.enabled()
+
+
 def router_topk(logits: torch.Tensor, k: int, renormalize: bool = True):
     """float32 logits [T, E] -> (ids int32 [T, k], weights float32 [T, k]): top-k experts and the
     softmax over the selected logits (`renormalize`) or the softmax over all experts."""
-    if not logits.is_cuda:
+    if not logits.is_cuda or _baseline_on():
         lf = logits.float()
         v, i = torch.topk(lf, k, dim=-1)
         w = torch.softmax(v, -1) if renormalize else torch.softmax(lf, -1).gather(1, i)
@@ -187,6 +192,33 @@ def reference_fused_experts(x, topk_ids, topk_w, gate, up, down, e0: int = 0):
     return y.to(x.dtype)
 
 
+def library_experts(x, topk_ids, topk_w, w_gate_up_il, w_down, e0: int = 0):
+    """Comparison path built from library pieces only: torch sort / gather for the permutation,
+    the library grouped GEMM (`torch._grouped_mm`) for both expert GEMMs, unfused SwiGLU, and an
+    index_add for the weighted combine.  No host synchronisation, so it can be graph-captured."""
+    t, d = x.shape
+    k = topk_ids.shape[1]
+    e_local = w_gate_up_il.shape[0]
+    flat = topk_ids.reshape(-1).long() - e0
+    local = (flat >= 0) & (flat < e_local)
+    key = torch.where(local, flat, torch.full_like(flat, e_local))        # foreign pairs sort last
+    order = torch.argsort(key, stable=True)
+    counts = torch.bincount(key, minlength=e_local + 1)[:e_local]
+    offs = torch.cumsum(counts, 0).to(torch.int32)
+    tok = torch.div(order, k, rounding_mode="floor")
+    xs = x[tok]                                                            # [T*k, D]; rows past offs[-1] unused
+    h = torch._grouped_mm(xs, w_gate_up_il.transpose(-2, -1), offs=offs)
+    f2 = h.shape[1]
+    h = h.reshape(-1, f2 // 128, 2, 64)
+    h = (torch.nn.functional.silu(h[:, :, 0].float()) * h[:, :, 1].float()).to(x.dtype).reshape(-1, f2 // 2)
+    o = torch._grouped_mm(h, w_down.transpose(-2, -1), offs=offs)
+    w = (topk_w.reshape(-1).float() * local.float())[order]
+    valid = (torch.arange(t * k, device=x.device) < offs[-1]).float()
+    y = torch.zeros((t, d), dtype=torch.float32, device=x.device)
+    y.index_add_(0, tok, torch.nan_to_num(o.float()) * (w * valid)[:, None])
+    return y.to(x.dtype)
+
+
 def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, comm=None, num_experts_total: Optional[int] = None, residual=None):
     """Routed mixture with expert parallelism.  `w_gate_up` / `w_down` hold this rank's experts
@@ -196,9 +228,16 @@ def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Ten
     e_local = w_gate_up.shape[0]
     world = comm.world if comm is not None else 1
     rank = comm.rank if comm is not None else 0
+    from ..ops import baseline as _baseline
+    if _baseline.enabled():
+        y = library_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local)
+        if world > 1:
+            y = comm.all_reduce_(y)
+        return y + residual if residual is not None else y
     y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, num_experts_total or e_local * world)
     if world > 1:
-        if getattr(comm, "fused", None) is not None and y.is_cuda and comm.fused.staging is not None:
+        if (getattr(comm, "fused", None) is not None and y.is_cuda and comm.fused.staging is not None
+                and y.numel() <= comm.fused.staging.numel()):
             y = comm.fused.all_reduce(y)
         else:
             y = comm.all_reduce_(y)

@@ -70,6 +70,9 @@ class SymmetricContext:
         self._next = 0
         self.staging = None
         self.staging_off = 0
+        # the fused GEMM + all-reduce is used up to this many tokens; above it the partial tiles
+        # are large enough that the GEMM followed by a bandwidth-optimal NCCL all-reduce wins
+        self.fused_max_tokens = 512
 
     @staticmethod
     def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0) -> "SymmetricContext":

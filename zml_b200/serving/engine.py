@@ -212,7 +212,8 @@ class Engine:
         meta = AttnMeta(False, self.d_pos[:b], self.d_slot[:b], self.d_bt[:b], self.d_seq[:b],
                         num_splits=num_splits, max_seq_len=max_seq_len)
         toks = self.model.forward(self.d_ids[:b], meta, self.kv_cache, strategy, self.seed, 0)
-        if self.on_gpu:
+        from ..ops import baseline as _baseline
+        if self.on_gpu and not _baseline.enabled():
             rc = _lib.lib().zb_decode_advance(
                 toks.data_ptr(), self.d_ids.data_ptr(), self.d_pos.data_ptr(), self.d_seq.data_ptr(),
                 self.d_slot.data_ptr(), self.d_bt.data_ptr(), self.d_hist.data_ptr(),
@@ -220,15 +221,15 @@ class Engine:
                 self.d_hist.shape[0], _lib.stream_ptr())
             _lib.check(rc, "zb_decode_advance")
         else:
-            step = int(self.d_step[0])
             self.d_ids[:b] = toks
             self.d_pos[:b] += 1
             self.d_seq[:b] = self.d_pos[:b] + 1
             pg = torch.div(self.d_pos[:b], self.page_size, rounding_mode="floor").long()
             page = self.d_bt[:b].gather(1, pg.clamp_max(self.max_pages - 1)[:, None])[:, 0]
             self.d_slot[:b] = page * self.page_size + self.d_pos[:b] % self.page_size
-            if step < self.d_hist.shape[0]:
-                self.d_hist[step, :b] = toks
+            # graph-capturable history write: row index comes from the device-side step counter
+            row = self.d_step.long().clamp_max(self.d_hist.shape[0] - 1)
+            self.d_hist[:, :b].index_copy_(0, row, toks[None, :].to(self.d_hist.dtype))
             self.d_step += 1
 
     def _decode_step(self, b: int, strategy, num_splits, max_seq_len, stats):
