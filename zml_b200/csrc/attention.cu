@@ -176,6 +176,8 @@ constexpr int kDecStages = 3;
 
 template <int HD>
 __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kChunks = HD / 8;
   constexpr int kBlkBytes = 16 * HD * 2;              // one 16-key block of K (or V)
@@ -355,6 +357,8 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
 // --------------------------------------------------------------------- prefill
 template <int HD>
 __global__ void __launch_bounds__(128) zb_paged_prefill_kernel(const AttnParams p) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   extern __shared__ __align__(128) uint8_t smem[];
   constexpr int kChunks = HD / 8;
   constexpr int kTileBytes = 64 * HD * 2;
@@ -492,7 +496,7 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(p.batch * p.num_kv_heads, p.num_splits);
-  zb_paged_decode_kernel<HD><<<grid, 128, smem, stream>>>(p);
+  zb_launch(zb_paged_decode_kernel<HD>, dim3(grid), dim3(128), smem, stream, p);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -508,7 +512,7 @@ int launch_prefill(const AttnParams& p, int num_q_blocks, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(num_q_blocks, p.num_q_heads);
-  zb_paged_prefill_kernel<HD><<<grid, 128, smem, stream>>>(p);
+  zb_launch(zb_paged_prefill_kernel<HD>, dim3(grid), dim3(128), smem, stream, p);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

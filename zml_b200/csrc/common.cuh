@@ -140,6 +140,12 @@ ZB_DEVICE void zb_tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, i
       : "memory");
 }
 
+// Brings a tile into L2 only (no shared-memory destination, no barrier).
+ZB_DEVICE void zb_tma_prefetch_l2_2d(const void* tmap, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y)
+               : "memory");
+}
+
 ZB_DEVICE void zb_tma_load_2d_hint(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x,
                                    int32_t y, uint64_t cache_policy) {
   asm volatile(
@@ -160,6 +166,14 @@ ZB_DEVICE void zb_tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, i
       : "r"(zb_smem_u32(smem_dst)), "l"(tmap), "r"(zb_smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+
+// Programmatic dependent launch.  `zb_pdl_wait` blocks until every grid this one depends on has
+// finished and its writes are visible; nothing produced or still read by a preceding kernel may
+// be touched before it.  `zb_pdl_launch` lets the next kernel in the stream begin its own
+// prologue while this one is still running.  Both are no-ops for a kernel launched without the
+// programmatic-serialisation attribute.
+ZB_DEVICE void zb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+ZB_DEVICE void zb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 ZB_DEVICE void zb_tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(256) zb_rmsnorm_kernel(
     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
     __nv_bfloat16* __restrict__ residual_out, int rows, int d, long long x_stride,
     long long out_stride, float eps, int unit_offset) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int row = blockIdx.x;
   if (row >= rows) return;
   const int nvec = d >> 3;
@@ -120,6 +122,8 @@ struct RopeParams {
 };
 
 __global__ void __launch_bounds__(128) zb_rope_kvwrite_kernel(const RopeParams p) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int heads = p.hq + 2 * p.hkv;
@@ -194,6 +198,8 @@ __global__ void __launch_bounds__(128) zb_rope_kvwrite_kernel(const RopeParams p
 __global__ void __launch_bounds__(256) zb_swiglu_kernel(const __nv_bfloat16* __restrict__ gu,
                                                         __nv_bfloat16* __restrict__ out,
                                                         long long total_vec, int f_vec) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   for (long long idx = blockIdx.x * 256ll + threadIdx.x; idx < total_vec;
        idx += static_cast<long long>(gridDim.x) * 256) {
     const long long t = idx / f_vec;
@@ -220,6 +226,8 @@ __global__ void __launch_bounds__(128) zb_embedding_kernel(const int32_t* __rest
                                                            const __nv_bfloat16* __restrict__ table,
                                                            __nv_bfloat16* __restrict__ out, int tokens,
                                                            int d, int vocab) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int t = blockIdx.x;
   if (t >= tokens) return;
   int id = ids[t];
@@ -234,6 +242,8 @@ __global__ void __launch_bounds__(128) zb_embedding_kernel(const int32_t* __rest
 __global__ void __launch_bounds__(1024) zb_argmax_f32_kernel(const float* __restrict__ logits,
                                                              int32_t* __restrict__ out, int vocab,
                                                              long long stride) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const float* row = logits + static_cast<size_t>(blockIdx.x) * stride;
   float best = -INFINITY;
   int bi = 0x7fffffff;
@@ -302,6 +312,8 @@ __global__ void __launch_bounds__(1024) zb_topk_sample_kernel(
     const float* __restrict__ logits, int32_t* __restrict__ out_token, float* __restrict__ topk_vals,
     int32_t* __restrict__ topk_idx, int vocab, long long stride, int k, float temperature,
     uint64_t seed, uint64_t step) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const float* row = logits + static_cast<size_t>(blockIdx.x) * stride;
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_remaining;
@@ -439,6 +451,8 @@ __global__ void zb_decode_advance_kernel(const int32_t* __restrict__ sampled, in
                                          const int32_t* __restrict__ block_table, int32_t* __restrict__ history,
                                          int32_t* __restrict__ step_counter, int batch, int max_pages,
                                          int page_size, int history_stride, int history_rows) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   const int step = *step_counter;
   if (b < batch) {
@@ -454,7 +468,11 @@ __global__ void zb_decode_advance_kernel(const int32_t* __restrict__ sampled, in
 }
 
 // Runs after the kernel above on the same stream, so every block has read the old value.
-__global__ void zb_counter_inc_kernel(int32_t* c) { *c += 1; }
+__global__ void zb_counter_inc_kernel(int32_t* c) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  *c += 1;
+}
 
 }  // namespace
 
@@ -472,10 +490,10 @@ int zb_rmsnorm(const void* x, const void* residual, const void* w, void* out, vo
   auto W = reinterpret_cast<const __nv_bfloat16*>(w);
   auto O = reinterpret_cast<__nv_bfloat16*>(out);
   auto RO = reinterpret_cast<__nv_bfloat16*>(residual_out);
-  if (nvec <= 256) zb_rmsnorm_kernel<1><<<rows, 256, 0, s>>>(X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
-  else if (nvec <= 512) zb_rmsnorm_kernel<2><<<rows, 256, 0, s>>>(X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
-  else if (nvec <= 1024) zb_rmsnorm_kernel<4><<<rows, 256, 0, s>>>(X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
-  else if (nvec <= 2048) zb_rmsnorm_kernel<8><<<rows, 256, 0, s>>>(X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
+  if (nvec <= 256) zb_launch(zb_rmsnorm_kernel<1>, dim3(rows), dim3(256), 0, s, X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
+  else if (nvec <= 512) zb_launch(zb_rmsnorm_kernel<2>, dim3(rows), dim3(256), 0, s, X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
+  else if (nvec <= 1024) zb_launch(zb_rmsnorm_kernel<4>, dim3(rows), dim3(256), 0, s, X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
+  else if (nvec <= 2048) zb_launch(zb_rmsnorm_kernel<8>, dim3(rows), dim3(256), 0, s, X, R, W, O, RO, rows, d, x_stride, out_stride, eps, unit_offset);
   else return -41;
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
@@ -513,7 +531,7 @@ int zb_rope_kvwrite(const void* qkv, void* q_out, void* k_cache, void* v_cache,
   p.num_slots = num_slots;
   const long long warps = static_cast<long long>(tokens) * (hq + 2 * hkv);
   const int blocks = static_cast<int>((warps + 3) / 4);
-  zb_rope_kvwrite_kernel<<<blocks, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  zb_launch(zb_rope_kvwrite_kernel, dim3(blocks), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), p);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -524,7 +542,7 @@ int zb_swiglu(const void* gate_up, void* out, long long tokens, int f, void* str
   const long long total_vec = tokens * (f / 8);
   long long blocks = (total_vec + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  zb_swiglu_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  zb_launch(zb_swiglu_kernel, dim3(static_cast<int>(blocks)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 
       reinterpret_cast<const __nv_bfloat16*>(gate_up), reinterpret_cast<__nv_bfloat16*>(out), total_vec,
       f / 8);
   zb_count_launch(1);
@@ -535,7 +553,7 @@ int zb_embedding(const int32_t* ids, const void* table, void* out, int tokens, i
                  void* stream) {
   if (tokens <= 0) return 0;
   if (d % 8 != 0) return -44;
-  zb_embedding_kernel<<<tokens, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  zb_launch(zb_embedding_kernel, dim3(tokens), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), 
       ids, reinterpret_cast<const __nv_bfloat16*>(table), reinterpret_cast<__nv_bfloat16*>(out), tokens, d,
       vocab);
   zb_count_launch(1);
@@ -545,7 +563,7 @@ int zb_embedding(const int32_t* ids, const void* table, void* out, int tokens, i
 int zb_argmax_f32(const float* logits, int32_t* out, int rows, int vocab, long long stride,
                   void* stream) {
   if (rows <= 0) return 0;
-  zb_argmax_f32_kernel<<<rows, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(logits, out, vocab, stride);
+  zb_launch(zb_argmax_f32_kernel, dim3(rows), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), logits, out, vocab, stride);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -555,7 +573,7 @@ int zb_topk_sample(const float* logits, int32_t* out_token, float* topk_vals, in
                    unsigned long long seed, unsigned long long step, void* stream) {
   if (rows <= 0) return 0;
   if (k < 1 || k > kMaxTopK) return -45;
-  zb_topk_sample_kernel<<<rows, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  zb_launch(zb_topk_sample_kernel, dim3(rows), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), 
       logits, out_token, topk_vals, topk_idx, vocab, stride, k, temperature, seed, step);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
@@ -568,11 +586,11 @@ int zb_decode_advance(const int32_t* sampled, int32_t* ids, int32_t* positions, 
                       int history_stride, int history_rows, void* stream) {
   if (batch <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  zb_decode_advance_kernel<<<(batch + 127) / 128, 128, 0, s>>>(sampled, ids, positions, seq_lens,
+  zb_launch(zb_decode_advance_kernel, dim3((batch + 127) / 128), dim3(128), 0, s, sampled, ids, positions, seq_lens,
                                                              slot_mapping, block_table, history,
                                                              step_counter, batch, max_pages, page_size,
                                                              history_stride, history_rows);
-  zb_counter_inc_kernel<<<1, 1, 0, s>>>(step_counter);
+  zb_launch(zb_counter_inc_kernel, dim3(1), dim3(1), 0, s, step_counter);
   zb_count_launch(2);
   return static_cast<int>(cudaGetLastError());
 }

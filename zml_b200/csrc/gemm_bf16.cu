@@ -51,6 +51,8 @@ struct GemmParams {
   int units_per_cta; // k-blocks per CTA (stream-K range length)
   int rr_tiles;      // > 0: whole tiles dealt round-robin, this many per CTA (large problems)
   int group_p;       // rasterisation group height (P tiles)
+  int flags;         // bit 0: the weight operand is not written by the preceding kernel
+  int l2_prefetch;   // weight tiles per CTA to pull into L2 ahead of the shared-memory ring
   float* workspace;  // [grid][2][BN][128] fp32 partial tiles
   uint32_t* counters;  // one per output tile, zero between launches
   ZbStatus* status;
@@ -102,6 +104,19 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   const long long u_begin = min(total_units, static_cast<long long>(blockIdx.x) * prm.units_per_cta);
   const long long u_end = min(total_units, u_begin + prm.units_per_cta);
 
+  // output tile -> (p tile, q tile); P tiles are grouped so that CTAs working at the
+  // same time share few distinct operand tiles in L2.
+  auto decode = [&](int t, int& pt, int& qt) {
+    const int per_group = prm.group_p * num_q;
+    const int g = t / per_group;
+    const int within = t - g * per_group;
+    const int p_first = g * prm.group_p;
+    const int gp = min(prm.group_p, num_p - p_first);
+    pt = p_first + within % gp;
+    qt = within / gp;
+  };
+
+  int early = 0;     // producer thread: stages whose weight tile was requested ahead of the dependency wait
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       zb_mbar_init(&full_bar[s], 1);
@@ -115,6 +130,40 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     *is_last_flag = 0u;
     *abort_where = 0u;
     zb_mbar_fence_init();
+    zb_tma_prefetch_desc(&tmap_p);
+    zb_tma_prefetch_desc(&tmap_q);
+    if ((prm.flags & 1) != 0) {
+      // The weight operand (P when swapped, Q otherwise) is a parameter, so its first tiles are
+      // requested right away - before this CTA's tensor memory is allocated and before the
+      // preceding kernel of the stream has finished: a ring of tiles into shared memory, then
+      // `l2_prefetch` further tiles into L2.  The activation tiles follow after the dependency wait.
+      uint32_t stage = 0;
+      int issued = 0;
+      const int limit = kStages + prm.l2_prefetch;
+      for (long long u = u_begin; issued < limit && u < u_end;) {
+        const int v = static_cast<int>(u / kb_total);
+        const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
+        const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
+        const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles : v;
+        u += kb1 - kb0;
+        if (t >= num_out_tiles) continue;
+        int pt, qt;
+        decode(t, pt, qt);
+        for (int kb = kb0; kb < kb1 && issued < limit; ++kb, ++issued) {
+          const void* wmap = SWAP ? static_cast<const void*>(&tmap_p) : static_cast<const void*>(&tmap_q);
+          const int wy = SWAP ? pt * kBlockP : qt * BN;
+          if (issued < kStages) {
+            uint8_t* dst = smem + stage * kStageBytes + (SWAP ? 0 : kTileABytes);
+            zb_mbar_expect_tx(&full_bar[stage], kStageBytes);
+            zb_tma_load_2d(dst, wmap, &full_bar[stage], kb * kBlockK, wy);
+            ++stage;
+            ++early;
+          } else {
+            zb_tma_prefetch_l2_2d(wmap, kb * kBlockK, wy);
+          }
+        }
+      }
+    }
   }
   if (warp == 1) {
     zb_tmem_alloc(tmem_holder, kTmemCols);
@@ -124,25 +173,22 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   __syncthreads();
   zb_tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
-
-  // output tile -> (p tile, q tile); P tiles are grouped so that CTAs working at the
-  // same time share few distinct operand tiles in L2.
-  auto decode = [&](int t, int& pt, int& qt) {
-    const int per_group = prm.group_p * num_q;
-    const int g = t / per_group;
-    const int within = t - g * per_group;
-    const int p_first = g * prm.group_p;
-    const int gp = min(prm.group_p, num_p - p_first);
-    pt = p_first + within % gp;
-    qt = within / gp;
-  };
+  // Everything above touches only parameters and this CTA's shared and tensor memory.  The next
+  // kernel may start now that this CTA holds its tensor memory (a dependent CTA sharing the SM
+  // that allocated first would block this one for good).  The producer thread waits for the
+  // preceding kernel before its first activation load; the epilogue warps, which read the
+  // residual and write the output, wait here.
+  zb_pdl_launch();
+  if (warp >= 2) zb_pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       zb_tma_prefetch_desc(&tmap_p);
       zb_tma_prefetch_desc(&tmap_q);
+      zb_pdl_wait();
       uint32_t stage = 0, phase = 0;
+      int issued = 0;
       bool ok = true;
       for (long long u = u_begin; ok && u < u_end;) {
         const int v = static_cast<int>(u / kb_total);
@@ -155,16 +201,22 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
         int pt, qt;
         decode(t, pt, qt);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
-            ok = false;
-            break;
-          }
+        for (int kb = kb0; kb < kb1; ++kb, ++issued) {
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kTileABytes;
-          zb_mbar_expect_tx(&full_bar[stage], kStageBytes);
-          zb_tma_load_2d(sa, &tmap_p, &full_bar[stage], kb * kBlockK, pt * kBlockP);
-          zb_tma_load_2d(sb, &tmap_q, &full_bar[stage], kb * kBlockK, qt * BN);
+          if (issued < early) {
+            // the weight tile of this stage is already in flight: add the activation tile
+            if constexpr (SWAP) zb_tma_load_2d(sb, &tmap_q, &full_bar[stage], kb * kBlockK, qt * BN);
+            else zb_tma_load_2d(sa, &tmap_p, &full_bar[stage], kb * kBlockK, pt * kBlockP);
+          } else {
+            if (!zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+              ok = false;
+              break;
+            }
+            zb_mbar_expect_tx(&full_bar[stage], kStageBytes);
+            zb_tma_load_2d(sa, &tmap_p, &full_bar[stage], kb * kBlockK, pt * kBlockP);
+            zb_tma_load_2d(sb, &tmap_q, &full_bar[stage], kb * kBlockK, qt * BN);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -556,9 +608,20 @@ int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  zb_gemm_bf16_kernel<BN, SWAP, FUSED><<<grid, kNumThreads, smem, stream>>>(tp, tq, prm);
+  const cudaError_t le = zb_launch(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, dim3(grid), dim3(kNumThreads), smem, stream, tp, tq, prm);
   zb_count_launch(1);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
+}
+
+// Weight tiles per CTA to pull into L2 ahead of the shared-memory ring while the preceding
+// kernel drains: only for the weight-streaming (few tokens) regime, and at most ~40 MB in all,
+// a third of the L2.
+int l2_prefetch_tiles(int swap, int bn, int grid, int rr_tiles) {
+  if (!swap || rr_tiles > 0 || grid <= 0) return 0;
+  const long long tile_bytes = static_cast<long long>(kBlockP) * kBlockK * 2;
+  (void)bn;
+  const long long per_cta = (40ll << 20) / grid / tile_bytes;
+  return static_cast<int>(per_cta > 64 ? 64 : per_cta);
 }
 
 }  // namespace
@@ -616,7 +679,10 @@ size_t zb_gemm_workspace_bytes(int m, int n, int k, int num_sms) {
   return static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float);
 }
 
-// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `scratch` receives the partial
+// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `out_f32` is a bit set: bit 0 selects an
+// fp32 output, bit 1 states that `w` is a parameter (not written by the kernel that precedes
+// this one on the stream), which lets the kernel request weight tiles while that kernel is
+// still finishing.  `scratch` receives the partial
 // tiles of CTAs whose k-range does not cover a whole tile (2 per CTA); `counters`
 // holds one zeroed u32 per output tile (kept zero by the kernel).
 int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residual, const void* bias,
@@ -625,6 +691,8 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
                     ZbStatus* status, int num_sms, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0) return -10;
+  const int static_w = (out_f32 >> 1) & 1;
+  out_f32 &= 1;
   if (!out_f32 && (ldo % 8) != 0) return -11;
   int sw, bn, grid, upc, rr;
   const int tiles = zb_gemm_plan(m, n, k, num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
@@ -639,6 +707,8 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   prm.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   prm.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   prm.out_f32 = out_f32;
+  prm.flags = static_w;
+  prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
   prm.group_p = 16;
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;
@@ -702,6 +772,8 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   prm.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   prm.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   prm.out_f32 = 0;
+  prm.flags = 1;     // `w` is a model parameter in every use of the fused kernel
+  prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
   prm.group_p = 16;
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;

@@ -42,7 +42,29 @@ struct ZbArContext {
 ZbDeviceState* zb_device_state();       // state of the current device, or nullptr before zb_init
 void zb_count_launch(int n);            // adds to the process-wide kernel-launch counter
 
+bool zb_pdl_enabled();                  // programmatic dependent launch on (default) or off
+
+// Launches `kernel` so that it may start while the preceding kernel of the stream is still
+// running (programmatic stream serialisation).  Only for kernels that execute `zb_pdl_wait()`
+// before their first access to memory another kernel writes or reads.
+template <typename... KArgs, typename... Args>
+inline cudaError_t zb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = zb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 extern "C" {
+void zb_set_pdl(int on);
 int zb_init(int device);
 int zb_num_sms();
 int zb_status_read(uint32_t* out4);     // copies {code, kernel, where, detail}; synchronises the device

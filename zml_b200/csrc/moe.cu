@@ -26,6 +26,8 @@ template <int MAX_PER_LANE>
 __global__ void __launch_bounds__(128) zb_moe_router_topk_kernel(const float* __restrict__ logits, int32_t* __restrict__ ids,
                                                                  float* __restrict__ weights, int tokens, int experts,
                                                                  int k, long long stride, int renormalize) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= tokens) return;
@@ -91,6 +93,8 @@ __global__ void __launch_bounds__(128) zb_moe_router_topk_kernel(const float* __
 //                      [E+1, 2E]   cursors (scratch)
 __global__ void zb_moe_count_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ meta, int pairs, int e0,
                                     int e_local) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   int32_t* counts = meta + e_local + 1;      // cursors double as counts in this pass
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += gridDim.x * blockDim.x) {
     const int e = ids[i] - e0;
@@ -99,6 +103,8 @@ __global__ void zb_moe_count_kernel(const int32_t* __restrict__ ids, int32_t* __
 }
 
 __global__ void zb_moe_offsets_kernel(int32_t* __restrict__ meta, int e_local) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   // single thread block; E is small (<= 1024)
   __shared__ int32_t s[1025];
   int32_t* counts = meta + e_local + 1;
@@ -119,6 +125,8 @@ __global__ void zb_moe_offsets_kernel(int32_t* __restrict__ meta, int e_local) {
 __global__ void zb_moe_scatter_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ meta,
                                       int32_t* __restrict__ sorted_pair, int32_t* __restrict__ pair_pos, int pairs,
                                       int e0, int e_local) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   int32_t* cursors = meta + e_local + 1;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < pairs; i += gridDim.x * blockDim.x) {
     const int e = ids[i] - e0;
@@ -137,6 +145,8 @@ __global__ void __launch_bounds__(128) zb_moe_gather_kernel(const __nv_bfloat16*
                                                             const int32_t* __restrict__ sorted_pair,
                                                             const int32_t* __restrict__ meta, __nv_bfloat16* __restrict__ xs,
                                                             int e_local, int k, int d, int cap) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int total = min(meta[e_local], cap);
   for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
     const int t = sorted_pair[pos] / k;
@@ -151,6 +161,8 @@ __global__ void __launch_bounds__(128) zb_moe_finalize_kernel(const __nv_bfloat1
                                                               const int32_t* __restrict__ pair_pos,
                                                               const float* __restrict__ weights,
                                                               __nv_bfloat16* __restrict__ y, int tokens, int k, int d) {
+  zb_pdl_launch();
+  zb_pdl_wait();
   const int t = blockIdx.x;
   if (t >= tokens) return;
   for (int i = threadIdx.x; i < d / 8; i += 128) {
@@ -250,6 +262,11 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
   __syncthreads();
   zb_tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // The next kernel may start only now that this CTA holds its tensor memory: a dependent CTA
+  // that shared the SM and allocated first would block this one for good.  The tile walk reads
+  // the expert offsets written by the preceding kernels, so every thread waits for them.
+  zb_pdl_launch();
+  zb_pdl_wait();
 
   // tiles of expert e: weight tiles x token tiles
   const int w_tiles = SWAP ? prm.n / kBlockP : prm.n / BN;
@@ -492,7 +509,7 @@ int launch_grouped(const CUtensorMap& tx, const CUtensorMap& tw, const GroupedPa
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU><<<grid, kThreads, smem, s>>>(tx, tw, prm);
+  zb_launch(zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(kThreads), smem, s, tx, tw, prm);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -507,9 +524,9 @@ int zb_moe_router_topk(const float* logits, int32_t* ids, float* weights, int to
   if (k < 1 || k > 32 || experts < k || experts > 512) return -60;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int blocks = (tokens + 3) / 4;
-  if (experts <= 128) zb_moe_router_topk_kernel<4><<<blocks, 128, 0, s>>>(logits, ids, weights, tokens, experts, k, stride, renormalize);
-  else if (experts <= 256) zb_moe_router_topk_kernel<8><<<blocks, 128, 0, s>>>(logits, ids, weights, tokens, experts, k, stride, renormalize);
-  else zb_moe_router_topk_kernel<16><<<blocks, 128, 0, s>>>(logits, ids, weights, tokens, experts, k, stride, renormalize);
+  if (experts <= 128) zb_launch(zb_moe_router_topk_kernel<4>, dim3(blocks), dim3(128), 0, s, logits, ids, weights, tokens, experts, k, stride, renormalize);
+  else if (experts <= 256) zb_launch(zb_moe_router_topk_kernel<8>, dim3(blocks), dim3(128), 0, s, logits, ids, weights, tokens, experts, k, stride, renormalize);
+  else zb_launch(zb_moe_router_topk_kernel<16>, dim3(blocks), dim3(128), 0, s, logits, ids, weights, tokens, experts, k, stride, renormalize);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -527,9 +544,9 @@ int zb_moe_align(const int32_t* ids, int32_t* meta, int32_t* sorted_pair, int32_
   if (pairs > 0) {
     int blocks = (pairs + 255) / 256;
     if (blocks > 592) blocks = 592;
-    zb_moe_count_kernel<<<blocks, 256, 0, s>>>(ids, meta, pairs, e0, e_local);
-    zb_moe_offsets_kernel<<<1, 256, 0, s>>>(meta, e_local);
-    zb_moe_scatter_kernel<<<blocks, 256, 0, s>>>(ids, meta, sorted_pair, pair_pos, pairs, e0, e_local);
+    zb_launch(zb_moe_count_kernel, dim3(blocks), dim3(256), 0, s, ids, meta, pairs, e0, e_local);
+    zb_launch(zb_moe_offsets_kernel, dim3(1), dim3(256), 0, s, meta, e_local);
+    zb_launch(zb_moe_scatter_kernel, dim3(blocks), dim3(256), 0, s, ids, meta, sorted_pair, pair_pos, pairs, e0, e_local);
     zb_count_launch(3);
   }
   return static_cast<int>(cudaGetLastError());
@@ -540,7 +557,7 @@ int zb_moe_gather(const void* x, const int32_t* sorted_pair, const int32_t* meta
   if (cap <= 0) return 0;
   if (d % 8 != 0) return -62;
   int blocks = cap < 2368 ? cap : 2368;
-  zb_moe_gather_kernel<<<blocks, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  zb_launch(zb_moe_gather_kernel, dim3(blocks), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), 
       reinterpret_cast<const __nv_bfloat16*>(x), sorted_pair, meta, reinterpret_cast<__nv_bfloat16*>(xs), e_local, k, d, cap);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
@@ -550,7 +567,7 @@ int zb_moe_finalize(const void* o, const int32_t* pair_pos, const float* weights
                     void* stream) {
   if (tokens <= 0) return 0;
   if (d % 8 != 0) return -62;
-  zb_moe_finalize_kernel<<<tokens, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  zb_launch(zb_moe_finalize_kernel, dim3(tokens), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), 
       reinterpret_cast<const __nv_bfloat16*>(o), pair_pos, weights, reinterpret_cast<__nv_bfloat16*>(y), tokens, k, d);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());

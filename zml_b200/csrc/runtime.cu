@@ -1,5 +1,6 @@
 // Library runtime: per-device state (status word, scratch), launch counting.
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "host_api.h"
@@ -24,6 +25,18 @@ ZbDeviceState* zb_device_state() {
   }
   return &g_state[dev];
 }
+
+static std::atomic<int> g_pdl{-1};
+bool zb_pdl_enabled() {
+  int v = g_pdl.load();
+  if (v < 0) {
+    const char* e = getenv("ZB_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    g_pdl.store(v);
+  }
+  return v != 0;
+}
+extern "C" void zb_set_pdl(int on) { g_pdl.store(on ? 1 : 0); }
 
 void zb_count_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n)); }
 

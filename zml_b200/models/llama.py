@@ -130,6 +130,7 @@ class AttnMeta:
     num_splits: Optional[int] = None
     max_seq_len: Optional[int] = None
     logits_rows: Optional[torch.Tensor] = None    # rows of the hidden state that need logits
+    state_slots: Optional[torch.Tensor] = None    # {b} slot of every sequence in a model's recurrent-state pool
 
 
 class LayerWeights:
@@ -294,20 +295,20 @@ class LlamaModel:
         """Row-parallel linear + all-reduce + residual add: the o_proj / down_proj pattern."""
         comm = self.comm
         if comm.world == 1:
-            return ops.gemm(a, w, residual=residual, out=residual if residual.is_cuda else None)
+            return ops.gemm(a, w, residual=residual, out=residual if residual.is_cuda else None, static_w=True)
         if comm.fused is not None and a.is_cuda and a.shape[0] <= comm.fused.fused_max_tokens:
             return comm.fused.gemm_allreduce(a, w, residual)
-        part = ops.gemm(a, w, residual=residual if comm.rank == 0 else None)
+        part = ops.gemm(a, w, residual=residual if comm.rank == 0 else None, static_w=True)
         return comm.all_reduce_(part)
 
     def mlp(self, lw: LayerWeights, x, n2):
-        gu = ops.gemm(n2, lw.gate_up)
+        gu = ops.gemm(n2, lw.gate_up, static_w=True)
         act = ops.swiglu(gu)
         return self.row_parallel(act, lw.down, x)
 
     def attention(self, lw: LayerWeights, n1, meta: AttnMeta, kc, vc):
         c = self.config
-        qkv = ops.gemm(n1, lw.qkv, bias=lw.qkv_bias)
+        qkv = ops.gemm(n1, lw.qkv, bias=lw.qkv_bias, static_w=True)
         q = ops.rope_kvwrite(qkv, meta.positions, meta.slot_mapping, self.inv_freq, kc, vc, self.hq,
                              self.hkv, c.hd, self.rope_layout, self.rot_dim, self.attn_factor,
                              lw.q_norm, lw.k_norm, c.rms_norm_eps, False)
@@ -339,7 +340,7 @@ class LlamaModel:
         if rows is not None:
             x = x.index_select(0, rows.long() if rows.dtype != torch.int64 else rows)
         n = ops.rmsnorm(x, self.final_norm, self.config.rms_norm_eps)
-        return ops.gemm(n, self.lm_head, out_dtype=torch.float32)
+        return ops.gemm(n, self.lm_head, out_dtype=torch.float32, static_w=True)
 
     def sample(self, logits, strategy: common.SamplingStrategy, seed: int = 0, step: int = 0):
         """Token ids int32 [B] from vocab-parallel logits."""

@@ -32,6 +32,8 @@ class Qwen3MoeConfig(LlamaConfig):
     def from_hf(obj: dict) -> "Qwen3MoeConfig":
         names = set(Qwen3MoeConfig.__dataclass_fields__)
         kw = {k: v for k, v in obj.items() if k in names and v is not None}
+        if "num_experts" not in kw and obj.get("num_local_experts") is not None:
+            kw["num_experts"] = obj["num_local_experts"]      # transformers >= 5 serialises it under this name
         kw.setdefault("qk_norm", True)
         kw.setdefault("intermediate_size", kw.get("moe_intermediate_size", 768))
         kw.setdefault("num_key_value_heads", kw.get("num_attention_heads"))
@@ -125,13 +127,21 @@ class Qwen3MoeModel(LlamaModel):
                 lw.q_norm = get(p + "self_attn.q_norm.weight")
                 lw.k_norm = get(p + "self_attn.k_norm.weight")
             lw.o = get(p + "self_attn.o_proj.weight", cols=(q0, q1))
-            gates, ups, downs = [], [], []
-            for e in range(self.e0, self.e0 + self.e_local):
-                gates.append(get(p + f"mlp.experts.{e}.gate_proj.weight"))
-                ups.append(get(p + f"mlp.experts.{e}.up_proj.weight"))
-                downs.append(get(p + f"mlp.experts.{e}.down_proj.weight"))
+            if store.has_key(prefix + p + "mlp.experts.gate_up_proj"):
+                # fused layout: gate_up_proj [E, 2F, d] with [gate | up] rows, down_proj [E, d, F]
+                gu = get(p + "mlp.experts.gate_up_proj", rows=(self.e0, self.e0 + self.e_local))
+                f = gu.shape[1] // 2
+                gate_s, up_s = gu[:, :f], gu[:, f:]
+                down_s = get(p + "mlp.experts.down_proj", rows=(self.e0, self.e0 + self.e_local))
+            else:
+                gates, ups, downs = [], [], []
+                for e in range(self.e0, self.e0 + self.e_local):
+                    gates.append(get(p + f"mlp.experts.{e}.gate_proj.weight"))
+                    ups.append(get(p + f"mlp.experts.{e}.up_proj.weight"))
+                    downs.append(get(p + f"mlp.experts.{e}.down_proj.weight"))
+                gate_s, up_s, down_s = torch.stack(gates), torch.stack(ups), torch.stack(downs)
             lw.extra = {"router": get(p + "mlp.gate.weight"),
-                        "gate_up": moe.interleave_gate_up(torch.stack(gates), torch.stack(ups)), "down": torch.stack(downs)}
+                        "gate_up": moe.interleave_gate_up(gate_s, up_s), "down": down_s.contiguous()}
             self.layers.append(lw)
         return self
 
@@ -171,6 +181,6 @@ class Qwen3MoeModel(LlamaModel):
     # ------------------------------------------------------------------ forward
     def mlp(self, lw: LayerWeights, x, n2):
         c = self.config
-        logits = ops.gemm(n2, lw.extra["router"], out_dtype=torch.float32)
+        logits = ops.gemm(n2, lw.extra["router"], out_dtype=torch.float32, static_w=True)
         ids, w = moe.router_topk(logits, c.num_experts_per_tok, c.norm_topk_prob)
         return moe.forward_moe(n2, ids, w, lw.extra["gate_up"], lw.extra["down"], self.comm, c.num_experts, residual=x)

@@ -13,29 +13,31 @@ from . import common
 from .llama import PRESETS as LLAMA_PRESETS, LlamaConfig, LlamaModel
 
 
+def _families():
+    """(presets, config class, model class) of every model family, imported lazily."""
+    from .lfm2 import PRESETS as P_LFM2, Lfm2Config, Lfm2Model
+    from .qwen3_5 import PRESETS as P_Q35, Qwen35Config, Qwen35Model
+    from .qwen3_5_moe import PRESETS as P_Q35M, Qwen35MoeConfig, Qwen35MoeModel
+    from .qwen3_moe import PRESETS as P_MOE, Qwen3MoeConfig, Qwen3MoeModel
+    return [(LLAMA_PRESETS, LlamaConfig, LlamaModel), (P_MOE, Qwen3MoeConfig, Qwen3MoeModel),
+            (P_Q35, Qwen35Config, Qwen35Model), (P_Q35M, Qwen35MoeConfig, Qwen35MoeModel),
+            (P_LFM2, Lfm2Config, Lfm2Model)]
+
+
 def preset_names() -> list[str]:
-    names = list(LLAMA_PRESETS)
-    try:
-        from .qwen3_moe import PRESETS as MOE_PRESETS
-        names += list(MOE_PRESETS)
-    except ImportError:
-        pass
-    return names
+    return [n for presets, _, _ in _families() for n in presets]
 
 
 def build_model(name: str, comm: Optional[Comm] = None, device="cuda", seed: int = 0,
                 baseline: bool = False, fused: bool = True, dtype=torch.bfloat16):
     """Random-init model of a named architecture on `device` (this rank's shard)."""
     comm = comm or Comm.single(torch.device(device))
-    if name in LLAMA_PRESETS:
-        cfg = LlamaConfig.from_hf(LLAMA_PRESETS[name])
-        model = LlamaModel(cfg, comm, device=device, dtype=dtype).init_random(seed)
+    for presets, cfg_cls, model_cls in _families():
+        if name in presets:
+            model = model_cls(cfg_cls.from_hf(presets[name]), comm, device=device, dtype=dtype).init_random(seed)
+            break
     else:
-        from .qwen3_moe import PRESETS as MOE_PRESETS, Qwen3MoeConfig, Qwen3MoeModel
-        if name not in MOE_PRESETS:
-            raise KeyError(f"unknown model {name!r}; known: {preset_names()}")
-        cfg = Qwen3MoeConfig.from_hf(MOE_PRESETS[name])
-        model = Qwen3MoeModel(cfg, comm, device=device, dtype=dtype).init_random(seed)
+        raise KeyError(f"unknown model {name!r}; known: {preset_names()}")
     if baseline:
         from ..ops import baseline as _baseline
         _baseline.enable(True)

@@ -203,7 +203,7 @@ def library_experts(x, topk_ids, topk_w, w_gate_up_il, w_down, e0: int = 0):
     local = (flat >= 0) & (flat < e_local)
     key = torch.where(local, flat, torch.full_like(flat, e_local))        # foreign pairs sort last
     order = torch.argsort(key, stable=True)
-    counts = torch.bincount(key, minlength=e_local + 1)[:e_local]
+    counts = (key[:, None] == torch.arange(e_local, device=x.device)[None, :]).sum(0)
     offs = torch.cumsum(counts, 0).to(torch.int32)
     tok = torch.div(order, k, rounding_mode="floor")
     xs = x[tok]                                                            # [T*k, D]; rows past offs[-1] unused
@@ -220,21 +220,27 @@ def library_experts(x, topk_ids, topk_w, w_gate_up_il, w_down, e0: int = 0):
 
 
 def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, w_gate_up: torch.Tensor,
-                w_down: torch.Tensor, comm=None, num_experts_total: Optional[int] = None, residual=None):
+                w_down: torch.Tensor, comm=None, num_experts_total: Optional[int] = None, residual=None,
+                extra_partial=None):
     """Routed mixture with expert parallelism.  `w_gate_up` / `w_down` hold this rank's experts
     (rank r owns experts [r * E_local, (r + 1) * E_local)); partial outputs are summed across
     ranks (in-kernel over peer memory when `comm.fused` is set, NCCL otherwise) and `residual`
-    is added once."""
+    is added once.  `extra_partial` is another per-rank partial sum (a tensor-parallel shared
+    expert) that rides on the same all-reduce."""
     e_local = w_gate_up.shape[0]
     world = comm.world if comm is not None else 1
     rank = comm.rank if comm is not None else 0
     from ..ops import baseline as _baseline
     if _baseline.enabled():
         y = library_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local)
+        if extra_partial is not None:
+            y = y + extra_partial
         if world > 1:
             y = comm.all_reduce_(y)
         return y + residual if residual is not None else y
     y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, num_experts_total or e_local * world)
+    if extra_partial is not None:
+        y = y + extra_partial
     if world > 1:
         if (getattr(comm, "fused", None) is not None and y.is_cuda and comm.fused.staging is not None
                 and y.numel() <= comm.fused.staging.numel()):

@@ -36,12 +36,14 @@ def _need_bf16(*ts):
 
 
 # ------------------------------------------------------------------ GEMM
-def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits: int = 0):
+def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits: int = 0, static_w: bool = False):
     """out[M,N] = a[M,K] @ w[N,K]^T (+ bias[N]) (+ residual[M,N]).
 
     `w` is stored [N, K] (the safetensors layout of every HF linear weight), so both
     operands are K-major and no transpose is ever materialised.  `out` may alias
-    `residual` (in-place residual stream update).
+    `residual` (in-place residual stream update).  `static_w=True` declares `w` a parameter that
+    no kernel still in flight on the stream writes; the kernel then fetches its first weight
+    tiles while the preceding kernel drains.
     """
     if not _cuda(a):
         r = reference.gemm(a, w, residual, bias, out_dtype)
@@ -62,17 +64,18 @@ def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits:
         assert residual.stride(0) == out.stride(0) and residual.stride(1) == 1
     rc = _lib.lib().zb_gemm_bf16(
         _ptr(a), _ptr(w), _ptr(out), _ptr(residual), _ptr(bias), m, n, k, a.stride(0), w.stride(0),
-        out.stride(0), 1 if out.dtype == torch.float32 else 0, force_splits, _lib.stream_ptr())
+        out.stride(0), (1 if out.dtype == torch.float32 else 0) | (2 if static_w else 0), force_splits,
+        _lib.stream_ptr())
     _lib.check(rc, "zb_gemm_bf16")
     return out
 
 
-def linear(x, w, bias=None, residual=None, out=None, out_dtype=None):
+def linear(x, w, bias=None, residual=None, out=None, out_dtype=None, static_w: bool = True):
     """`gemm` over the flattened leading dims of x[..., K]."""
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
     r2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
-    o = gemm(x2, w, r2, bias, out=out, out_dtype=out_dtype)
+    o = gemm(x2, w, r2, bias, out=out, out_dtype=out_dtype, static_w=static_w)
     return o.reshape(*lead, w.shape[0])
 
 

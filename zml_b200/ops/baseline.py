@@ -18,7 +18,7 @@ from . import reference
 _saved: dict = {}
 
 
-def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits: int = 0):
+def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits: int = 0, static_w: bool = False):
     y = torch.matmul(a, w.t())
     if bias is not None:
         y = y + bias
@@ -32,7 +32,7 @@ def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits:
     return y
 
 
-def linear(x, w, bias=None, residual=None, out=None, out_dtype=None):
+def linear(x, w, bias=None, residual=None, out=None, out_dtype=None, static_w: bool = True):
     lead = x.shape[:-1]
     r2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
     return gemm(x.reshape(-1, x.shape[-1]), w, r2, bias, out, out_dtype).reshape(*lead, w.shape[0])

@@ -66,6 +66,7 @@ class Request:
     computed: int = 0            # prompt tokens whose KV is in the cache
     finished: bool = False
     ttft_ms: Optional[float] = None
+    slot: int = -1               # row in the model's recurrent-state pool (hybrid models)
 
     @property
     def total_len(self) -> int:
@@ -129,6 +130,16 @@ class Engine:
         self.d_bt = torch.zeros((mb, self.max_pages), **i32)
         self.d_hist = torch.zeros((history_steps, mb), **i32)
         self.d_step = torch.zeros(1, **i32)
+        # recurrent-state slots (models with per-sequence state besides KV pages); the last slot is a
+        # scratch row for padding rows of a batch bucket and for graph warm-up passes
+        self.num_slots = 2 * mb
+        self.scratch_slot = self.num_slots
+        self.slot_free = list(range(self.num_slots - 1, -1, -1))
+        self.d_sslot = torch.full((mb,), self.scratch_slot, **i32)
+        self.d_qs = torch.arange(mb + 1, **i32)
+        self.stateful = hasattr(model, "alloc_state")
+        if self.stateful:
+            model.alloc_state(self.num_slots + 1)
 
     # ------------------------------------------------------------------ helpers
     def _pin(self, t: torch.Tensor) -> torch.Tensor:
@@ -146,11 +157,19 @@ class Engine:
         if need > self.max_pages:
             raise ValueError(f"request needs {need} pages, engine allows {self.max_pages} per sequence")
         r.pages = self.pool.alloc(need)
+        if self.stateful:
+            if not self.slot_free:
+                self.pool.release(r.pages)
+                raise OutOfPages("no free recurrent-state slot")
+            r.slot = self.slot_free.pop()
         return r
 
     def release(self, r: Request) -> None:
         self.pool.release(r.pages)
         r.pages = []
+        if r.slot >= 0:
+            self.slot_free.append(r.slot)
+            r.slot = -1
 
     # ------------------------------------------------------------------ prefill
     def _prefill_chunks(self, reqs: list[Request]):
@@ -189,7 +208,8 @@ class Engine:
                 done.append(r)
         t = len(ids)
         host = self._pin(torch.tensor([ids, pos, slots], dtype=torch.int32))
-        meta_h = self._pin(torch.tensor(qs + sl + rows, dtype=torch.int32))
+        sslots = [max(r.slot, 0) if self.stateful else 0 for r, _, _ in chunk]
+        meta_h = self._pin(torch.tensor(qs + sl + sslots + rows, dtype=torch.int32))
         bt_h = self._pin(bt)
         dev = self._to_dev(host, stats)
         meta_d = self._to_dev(meta_h, stats)
@@ -197,7 +217,8 @@ class Engine:
         nb = len(chunk)
         meta = AttnMeta(True, dev[1], dev[2], bt_d, meta_d[nb + 1:2 * nb + 1], meta_d[:nb + 1],
                         total_q_blocks=sum((b - a + 63) // 64 for _, a, b in chunk),
-                        logits_rows=meta_d[2 * nb + 1:] if rows else None)
+                        logits_rows=meta_d[3 * nb + 1:] if rows else None,
+                        state_slots=meta_d[2 * nb + 1:3 * nb + 1] if self.stateful else None)
         if rows:
             toks = self.model.forward(dev[0], meta, self.kv_cache, strategy, self.seed, 0)
         else:
@@ -210,7 +231,9 @@ class Engine:
     # ------------------------------------------------------------------ decode
     def _decode_body(self, b: int, strategy, num_splits, max_seq_len):
         meta = AttnMeta(False, self.d_pos[:b], self.d_slot[:b], self.d_bt[:b], self.d_seq[:b],
-                        num_splits=num_splits, max_seq_len=max_seq_len)
+                        num_splits=num_splits, max_seq_len=max_seq_len,
+                        q_start=self.d_qs[:b + 1] if self.stateful else None,
+                        state_slots=self.d_sslot[:b] if self.stateful else None)
         toks = self.model.forward(self.d_ids[:b], meta, self.kv_cache, strategy, self.seed, 0)
         from ..ops import baseline as _baseline
         if self.on_gpu and not _baseline.enabled():
@@ -240,7 +263,9 @@ class Engine:
         g = self._graphs.get(key)
         if g is None:
             # warm up on a side stream (lazy kernel attributes, allocator), then capture
-            saved = [t.clone() for t in (self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist)]
+            saved = [t.clone() for t in (self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist,
+                                         self.d_sslot)]
+            self.d_sslot.fill_(self.scratch_slot)    # the warm-up pass must not advance any real recurrent state
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
@@ -254,7 +279,8 @@ class Engine:
             nodes = _lib.launch_count() - before
             # the warm-up and capture passes must not count as decode steps: restore the state
             # (the warm-up really ran; the capture pass did not execute anything)
-            for dst, src in zip((self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist), saved):
+            for dst, src in zip((self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist,
+                                 self.d_sslot), saved):
                 dst.copy_(src)
             # the warm-up wrote one KV row per sequence at the slot of the next position; the
             # real step writes the same slot with the real values, so nothing needs undoing
@@ -316,6 +342,10 @@ class Engine:
         self.d_pos[:bb].copy_(st_d[1]); self.d_seq[:bb].copy_(st_d[2]); self.d_slot[:bb].copy_(st_d[3])
         self.d_ids[:bb].zero_()
         self.d_ids[:b].copy_(torch.cat([first_tok[r.rid] for r in reqs]))
+        if self.stateful:
+            ss = torch.full((bb,), self.scratch_slot, dtype=torch.int32)
+            ss[:b] = torch.tensor([r.slot for r in reqs], dtype=torch.int32)
+            self.d_sslot[:bb].copy_(self._to_dev(self._pin(ss), stats))
         self.d_step.zero_()
         max_total = max(pos) + max_new_tokens
         num_splits = ops.decode_plan_splits(bb, self.model.hkv, max_total) if self.on_gpu else 1
@@ -388,6 +418,8 @@ class Session:
         self.tokens: list[int] = []
         self.req = Request([], 0, -1)
         self.req.pages = engine.pool.alloc((self.max_tokens + engine.page_size - 1) // engine.page_size)
+        if engine.stateful:
+            self.req.slot = engine.slot_free.pop()
         self._next: Optional[int] = None
         engine.seed = seed
 
@@ -430,6 +462,8 @@ class Session:
         eng.d_slot[:1] = torch.tensor([self.req.pages[pos // ps] * ps + pos % ps], **i32)
         eng.d_bt[:1].zero_()
         eng.d_bt[0, :len(self.req.pages)] = torch.tensor(self.req.pages, **i32)
+        if eng.stateful:
+            eng.d_sslot[:1] = torch.tensor([self.req.slot], **i32)
         splits = ops.decode_plan_splits(1, eng.model.hkv, self.max_tokens) if eng.on_gpu else 1
         while True:
             out.append(tok)
