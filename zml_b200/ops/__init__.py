@@ -269,3 +269,9 @@ def paged_prefill(q, k_cache, v_cache, block_table, seq_lens, q_start, scale: fl
         float(scale if scale is not None else 1.0 / math.sqrt(hd)), int(window), _lib.stream_ptr())
     _lib.check(rc, "zb_paged_prefill")
     return out
+
+
+# structured ops (collectives, reductions, control flow, custom calls) live in ops.structured
+from .structured import (CustomCallOptions, ReduceWindowOpts, all_reduce, custom_call, gather, if2, if_,  # noqa: E402,F401
+                         manual_computation, partition_id, print_, reduce, reduce_window, register_custom_call,
+                         scatter, sort, while_)

@@ -57,9 +57,11 @@ class Comm:
         return Comm(rank, world, dist.group.WORLD, device)
 
     # ----------------------------------------------------------------- collectives
-    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+    def all_reduce_(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
         if self.world > 1:
-            dist.all_reduce(t, group=self.group)
+            ops = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN,
+                   "prod": dist.ReduceOp.PRODUCT}
+            dist.all_reduce(t, op=ops[op], group=self.group)
         return t
 
     def all_reduce_max_(self, t: torch.Tensor) -> torch.Tensor:
@@ -71,11 +73,14 @@ class Comm:
         if self.world == 1:
             return t
         t = t.contiguous()
-        out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+        if t.dim() == 0:
+            t = t[None]
+        # the flat [world * n, ...] form is the one every back-end accepts (gloo rejects [world, n, ...])
+        out = torch.empty((self.world * t.shape[0],) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
         dist.all_gather_into_tensor(out, t, group=self.group)
         if dim == 0:
-            return out.reshape(self.world * t.shape[0], *t.shape[1:])
-        return torch.cat(list(out.unbind(0)), dim=dim)
+            return out
+        return torch.cat(list(out.reshape(self.world, *t.shape).unbind(0)), dim=dim)
 
     def reduce_scatter(self, t: torch.Tensor) -> torch.Tensor:
         """Sums over ranks and leaves rank r with rows [r*n/P, (r+1)*n/P)."""
