@@ -1,0 +1,147 @@
+"""Failure detection without faulting a GPU: the flag protocol's state machine on CPU threads
+with host-injected faults, heartbeats over a store, a process group whose peer left (gloo),
+and - on a GPU - a bounded wait on a flag that nothing sets."""
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from zml_b200.parallel import health
+from zml_b200.parallel import protocol_sim as sim
+
+
+def _partials(world, tiles, elems, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.standard_normal((tiles, elems)).astype(np.float32) for _ in range(world)]
+
+
+@pytest.mark.parametrize("world,tiles", [(2, 5), (4, 8), (8, 3)])
+def test_protocol_all_ranks_agree_over_several_epochs(world, tiles):
+    heap = sim.SharedHeap(world, tiles, 16)
+    for epoch in (1, 2, 3):
+        parts = _partials(world, tiles, 16, epoch)
+        res = sim.run_step(heap, epoch, parts, limit_s=2.0)
+        assert all(v is None for v in res.values())
+        want = sum(parts)
+        for r in range(world):
+            np.testing.assert_allclose(heap.out[r], want, rtol=1e-6)
+
+
+def test_protocol_dead_rank_is_reported_not_deadlocked():
+    heap = sim.SharedHeap(4, 8, 4)
+    t0 = time.monotonic()
+    res = sim.run_step(heap, 1, _partials(4, 8, 4), limit_s=0.2, faults=sim.Faults(dead_ranks={2}))
+    assert time.monotonic() - t0 < 5.0
+    assert set(res) == {0, 1, 3}
+    for r, to in res.items():
+        assert isinstance(to, sim.Timeout) and to.epoch == 1
+        # owners miss rank 2's partial; a rank that owns nothing pending waits on a tile rank 2 owns
+        assert (to.phase == sim.PHASE_PUSH_WAIT and to.awaited == 2) or (to.phase == sim.PHASE_DONE_WAIT)
+
+
+def test_protocol_lost_flag_writes_name_phase_and_rank():
+    heap = sim.SharedHeap(2, 4, 4)
+    res = sim.run_step(heap, 1, _partials(2, 4, 4), limit_s=0.2, faults=sim.Faults(drop_push={(1, 2)}))
+    assert res[0] == sim.Timeout(0, sim.PHASE_PUSH_WAIT, 2, 1, 1)          # owner of tile 2 misses rank 1
+    assert res[1].phase == sim.PHASE_DONE_WAIT and res[1].tile == 2
+    heap = sim.SharedHeap(2, 4, 4)
+    res = sim.run_step(heap, 1, _partials(2, 4, 4), limit_s=0.2, faults=sim.Faults(drop_done={(1, 0, 3)}))
+    assert res[1] is None and res[0] == sim.Timeout(0, sim.PHASE_DONE_WAIT, 3, 1, 1)
+
+
+def test_protocol_slow_rank_within_limit_is_fine_and_stale_epoch_does_not_satisfy():
+    heap = sim.SharedHeap(2, 3, 4)
+    assert all(v is None for v in sim.run_step(heap, 1, _partials(2, 3, 4), limit_s=2.0,
+                                               faults=sim.Faults(delay_s={1: 0.1})).values())
+    # flags left at epoch 1 must not satisfy the waits of epoch 2 when a rank is missing
+    res = sim.run_step(heap, 2, _partials(2, 3, 4), limit_s=0.15, faults=sim.Faults(dead_ranks={1}))
+    assert isinstance(res[0], sim.Timeout) and res[0].epoch == 2
+
+
+def test_heartbeat_detects_silent_and_departed_ranks():
+    store = torch.distributed.HashStore()
+    hb = [health.Heartbeat(store, r, 3, timeout_s=5.0) for r in range(3)]
+    hb[0].check(now=100.0)
+    hb[1].beat(); hb[2].beat()
+    hb[0].check(now=104.0)
+    hb[1].beat()
+    with pytest.raises(health.RankFailure) as e:
+        hb[0].check(now=110.0)                                   # rank 2 silent since t=104
+    assert e.value.ranks == [2]
+    hb[2].leave()
+    with pytest.raises(health.RankFailure) as e:
+        hb[0].check(now=111.0)
+    assert e.value.ranks == [2] and "left" in e.value.reason
+
+
+_WORKER = r"""
+import os, sys, time, datetime, torch
+import torch.distributed as dist
+sys.path.insert(0, os.environ["ZB_ROOT"])
+from zml_b200.parallel import health
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 1, world, rank == 0, timeout=datetime.timedelta(seconds=30))
+dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world,
+                        timeout=datetime.timedelta(seconds=5))
+hb = health.Heartbeat(store, rank, world, timeout_s=2.0)
+x = torch.ones(4)
+dist.all_reduce(x)                         # step 1: everybody is here
+assert x[0].item() == world
+hb.beat()
+if rank == world - 1:
+    hb.leave()                             # leaves between steps, nothing in flight
+    print("LEFT", rank, flush=True)
+    os._exit(0)
+deadline = time.time() + 20
+while True:                                # the others learn of it on the host, before the next collective
+    try:
+        hb.check()
+    except health.RankFailure as e:
+        print("DETECTED", rank, e.ranks, flush=True)
+        break
+    assert time.time() < deadline
+    time.sleep(0.05)
+store.set(f"seen/{rank}", b"1")
+if rank == 0:                              # rank 0 hosts the store: it goes last
+    store.wait([f"seen/{r}" for r in range(world - 1)], datetime.timedelta(seconds=20))
+    time.sleep(0.2)
+os._exit(0)
+"""
+
+
+def test_rank_leaving_between_steps_is_seen_before_the_next_collective(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text(_WORKER)
+    env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3",
+                        "--master-addr", "127.0.0.1", "--master-port", "29641", str(script)],
+                       capture_output=True, text=True, env=env, timeout=180)
+    assert r.stdout.count("DETECTED") == 2 and "LEFT 2" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "[2]" in r.stdout
+
+
+@pytest.mark.gpu
+def test_bounded_wait_times_out_cleanly_on_the_gpu():
+    from zml_b200 import ops
+    from zml_b200.ops import _lib
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    reached = torch.full((1,), 7, dtype=torch.int32, device="cuda")
+    l = _lib.lib()
+    t0 = time.time()
+    _lib.check(l.zb_wait_probe(flag.data_ptr(), 1, 50_000_000, 3, reached.data_ptr(), _lib.stream_ptr()), "probe")
+    with pytest.raises(ops.CollectiveTimeout) as e:
+        ops.raise_on_status()
+    assert time.time() - t0 < 2.0
+    assert e.value.kernel == "wait_probe" and e.value.phase == 3 and e.value.detail == 1
+    assert int(reached.item()) == 0
+    # the context is still usable and a satisfied wait returns at once
+    flag.fill_(5)
+    _lib.check(l.zb_wait_probe(flag.data_ptr(), 5, 50_000_000, 4, reached.data_ptr(), _lib.stream_ptr()), "probe")
+    ops.raise_on_status()
+    assert int(reached.item()) == 1
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
+    assert l.zb_wait_probe(flag.data_ptr(), 9, 6_000_000_000, 0, None, _lib.stream_ptr()) == -21

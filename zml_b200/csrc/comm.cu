@@ -68,7 +68,34 @@ __global__ void zb_allreduce_oneshot_kernel(ZbArContext ctx, size_t in_off, __nv
 
 }  // namespace
 
+// A wait with a caller-chosen limit on a flag the caller owns: the building block of every
+// in-kernel collective, exposed so that the timeout path (status word, clean return, context
+// still usable) can be exercised without a peer.
+constexpr uint32_t kKernelWaitProbe = 8;
+__global__ void zb_wait_probe_kernel(const uint32_t* flag, uint32_t expected, unsigned long long limit_ns,
+                                     ZbStatus* status, uint32_t phase, uint32_t* reached) {
+  __shared__ uint32_t abort_flag;
+  abort_flag = 0u;
+  const bool ok = zb_wait_flag_limit(flag, expected, &abort_flag, limit_ns);
+  if (!ok) zb_record_error(status, ZB_ERR_FLAG_TIMEOUT, kKernelWaitProbe, phase, expected);
+  if (reached != nullptr) *reached = ok ? 1u : 0u;
+}
+
 extern "C" {
+
+// Launches one thread that waits until *flag >= expected or `limit_ns` passed.  On a timeout the
+// device status records {flag timeout, wait_probe, phase, expected} and *reached is 0.
+int zb_wait_probe(const void* flag, unsigned expected, unsigned long long limit_ns, unsigned phase,
+                  void* reached, void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (st == nullptr) return -20;
+  if (limit_ns > 5000000000ull) return -21;      // a probe never waits longer than 5 s
+  zb_wait_probe_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint32_t*>(flag), expected, limit_ns, st->status, phase,
+      reinterpret_cast<uint32_t*>(reached));
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
 
 int zb_symm_alloc(size_t bytes, void** ptr) {
   cudaError_t e = cudaMalloc(ptr, bytes);

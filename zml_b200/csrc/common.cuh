@@ -322,9 +322,10 @@ ZB_DEVICE uint32_t zb_ld_acquire_sys(const uint32_t* p) {
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// Waits until *p has reached `epoch` (flags only grow).  Gives up after ZB_WAIT_LIMIT_NS
-// or as soon as another role of the CTA gave up; returns false and raises `abort_flag`.
-ZB_DEVICE bool zb_wait_flag(const uint32_t* p, uint32_t epoch, volatile uint32_t* abort_flag) {
+// Waits until *p has reached `epoch` (flags only grow).  Gives up after `limit_ns` or as soon
+// as another role of the CTA gave up; returns false and raises `abort_flag`.
+ZB_DEVICE bool zb_wait_flag_limit(const uint32_t* p, uint32_t epoch, volatile uint32_t* abort_flag,
+                                  unsigned long long limit_ns) {
   if (static_cast<int32_t>(zb_ld_acquire_sys(p) - epoch) >= 0) return true;
   const uint64_t t0 = zb_globaltimer();
   uint32_t spins = 0;
@@ -332,10 +333,14 @@ ZB_DEVICE bool zb_wait_flag(const uint32_t* p, uint32_t epoch, volatile uint32_t
     if (static_cast<int32_t>(zb_ld_acquire_sys(p) - epoch) >= 0) return true;
     if ((++spins & 0x3f) == 0) {
       if (*abort_flag != 0u) return false;
-      if (zb_globaltimer() - t0 > ZB_WAIT_LIMIT_NS) {
+      if (zb_globaltimer() - t0 > limit_ns) {
         *abort_flag = 1u;
         return false;
       }
     }
   }
+}
+
+ZB_DEVICE bool zb_wait_flag(const uint32_t* p, uint32_t epoch, volatile uint32_t* abort_flag) {
+  return zb_wait_flag_limit(p, epoch, abort_flag, ZB_WAIT_LIMIT_NS);
 }

@@ -12,7 +12,7 @@ import math
 import torch
 
 from . import _lib, reference
-from ._lib import KernelError, launch_count, raise_on_status  # noqa: F401
+from ._lib import CollectiveTimeout, KernelError, launch_count, raise_on_status  # noqa: F401
 
 __all__ = [
     "gemm", "linear", "rmsnorm", "rope_kvwrite", "swiglu", "embedding", "argmax", "topk_sample",

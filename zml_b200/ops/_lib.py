@@ -25,6 +25,15 @@ class KernelError(RuntimeError):
     """A kernel of libzb_cuda.so returned a non-zero code or recorded a device status."""
 
 
+class CollectiveTimeout(KernelError):
+    """A bounded device-side wait (on an mbarrier, a flag or a peer) ran out.  The kernel returned
+    cleanly and the CUDA context is still usable; `kernel`, `phase` and `detail` say where it gave up."""
+
+    def __init__(self, msg: str, kernel: str = "", phase: int = 0, detail: int = 0, rank: int = 0):
+        super().__init__(msg)
+        self.kernel, self.phase, self.detail, self.rank = kernel, phase, detail, rank
+
+
 _SIGS = {
     "zb_init": (c_i, [c_i]),
     "zb_num_sms": (c_i, []),
@@ -34,6 +43,7 @@ _SIGS = {
     "zb_launch_count": (c_ull, []),
     "zb_launch_count_reset": (None, []),
     "zb_launch_count_add": (None, [c_ull]),
+    "zb_wait_probe": (c_i, [c_p, C.c_uint, c_ull, C.c_uint, c_p, c_p]),
     "zb_decode_advance": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p]),
     "zb_gemm_plan": (c_i, [c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
     "zb_gemm_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
@@ -108,7 +118,7 @@ def check(rc: int, what: str) -> None:
 STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out",
                 3: "index out of bounds", 4: "bad argument"}
 KERNEL_NAMES = {1: "gemm_bf16", 2: "paged_decode", 3: "paged_prefill", 4: "gemm_ar_fused",
-                5: "comm_barrier", 6: "moe_grouped_gemm", 7: "moe_a2a"}
+                5: "comm_barrier", 6: "moe_grouped_gemm", 7: "moe_a2a", 8: "wait_probe"}
 
 
 def read_status() -> tuple[int, int, int, int]:
@@ -123,9 +133,13 @@ def raise_on_status() -> None:
     code, kernel, where, detail = read_status()
     if code != 0:
         lib().zb_status_reset()
-        raise KernelError(
-            f"device status: {STATUS_NAMES.get(code, code)} in kernel "
-            f"{KERNEL_NAMES.get(kernel, kernel)} (where={where}, detail={detail})")
+        msg = (f"device status: {STATUS_NAMES.get(code, code)} in kernel "
+               f"{KERNEL_NAMES.get(kernel, kernel)} (where={where}, detail={detail})")
+        if code in (1, 2):
+            import os
+            raise CollectiveTimeout(msg, str(KERNEL_NAMES.get(kernel, kernel)), where, detail,
+                                    int(os.environ.get("RANK", "0")))
+        raise KernelError(msg)
 
 
 def stream_ptr(stream=None) -> int:

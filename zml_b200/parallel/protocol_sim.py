@@ -1,0 +1,112 @@
+"""Host simulation of the peer-memory protocol of the fused GEMM + all-reduce kernel, rank per
+thread, with the same state machine as the device code (csrc/fused_ar.h):
+
+  per tile t (owner = t % world):
+    1. every rank stores its partial tile into the owner's receive slot [src][t // world],
+       then sets push_flag[owner][(t // world) * world + src] = epoch;
+    2. the owner waits for its `world` push flags, sums the partials in rank order, writes the
+       result into every rank's output and sets done_flag[dst][t] = epoch on every rank;
+    3. every rank waits for done_flag[t] == epoch for all t before it leaves the step.
+  Flags are never reset: `epoch` counts launches.  Every wait is bounded; a wait that runs out
+  records (phase, tile, awaited rank) and the rank returns instead of hanging.
+
+It exists to test the protocol logic and its failure behaviour without a GPU: ranks can be
+dropped, delayed, or have single flag writes suppressed, and the survivors must report a
+`Timeout` naming the phase and the missing rank rather than deadlock.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import numpy as np
+
+PHASE_PUSH_WAIT = 1      # owner waiting for a partial tile
+PHASE_DONE_WAIT = 2      # rank waiting for a finished tile
+
+
+@dataclass
+class Timeout:
+    rank: int
+    phase: int
+    tile: int
+    awaited: int          # rank whose flag did not arrive (push wait) or the tile's owner (done wait)
+    epoch: int
+
+
+class SharedHeap:
+    """What the symmetric heaps hold, for all ranks."""
+
+    def __init__(self, world: int, tiles: int, tile_elems: int):
+        self.world, self.tiles = world, tiles
+        slots = (tiles + world - 1) // world
+        self.recv = np.zeros((world, world, slots, tile_elems), dtype=np.float32)     # [owner][src][slot]
+        self.push = np.zeros((world, slots * world), dtype=np.int64)                   # [owner][slot * world + src]
+        self.done = np.zeros((world, tiles), dtype=np.int64)                           # [rank][tile]
+        self.out = np.zeros((world, tiles, tile_elems), dtype=np.float32)
+
+
+@dataclass
+class Faults:
+    """Host-side fault injection."""
+    dead_ranks: set = field(default_factory=set)                 # never run the step
+    drop_push: set = field(default_factory=set)                  # {(src, tile)}: partial stored, flag write lost
+    drop_done: set = field(default_factory=set)                  # {(owner, dst, tile)}
+    delay_s: dict = field(default_factory=dict)                  # rank -> seconds before it starts
+
+
+def _wait(read: Callable[[], int], epoch: int, limit_s: float) -> bool:
+    t0 = time.monotonic()
+    while read() < epoch:
+        if time.monotonic() - t0 > limit_s:
+            return False
+        time.sleep(0.0002)
+    return True
+
+
+def run_rank(heap: SharedHeap, rank: int, epoch: int, partial: np.ndarray, limit_s: float, faults: Faults) -> Optional[Timeout]:
+    """One launch of the kernel on `rank`; partial is [tiles, tile_elems]."""
+    w = heap.world
+    if rank in faults.delay_s:
+        time.sleep(faults.delay_s[rank])
+    # 1. push every partial tile to its owner
+    for t in range(heap.tiles):
+        owner, slot = t % w, t // w
+        heap.recv[owner, rank, slot] = partial[t]
+        if (rank, t) not in faults.drop_push:
+            heap.push[owner, slot * w + rank] = epoch
+    # 2. reduce the tiles this rank owns
+    for t in range(rank, heap.tiles, w):
+        slot = t // w
+        for src in range(w):
+            if not _wait(lambda s=src: heap.push[rank, slot * w + s], epoch, limit_s):
+                return Timeout(rank, PHASE_PUSH_WAIT, t, src, epoch)
+        acc = np.zeros_like(partial[t])
+        for src in range(w):
+            acc = acc + heap.recv[rank, src, slot]
+        for dst in range(w):
+            heap.out[dst, t] = acc
+            if (rank, dst, t) not in faults.drop_done:
+                heap.done[dst, t] = epoch
+    # 3. leave only when every tile is complete locally
+    for t in range(heap.tiles):
+        if not _wait(lambda tt=t: heap.done[rank, tt], epoch, limit_s):
+            return Timeout(rank, PHASE_DONE_WAIT, t, t % w, epoch)
+    return None
+
+
+def run_step(heap: SharedHeap, epoch: int, partials: list, limit_s: float = 0.3, faults: Optional[Faults] = None) -> dict:
+    """Runs one launch on every live rank concurrently; returns {rank: Timeout or None}."""
+    faults = faults or Faults()
+    results: dict = {}
+
+    def body(r):
+        results[r] = run_rank(heap, r, epoch, partials[r], limit_s, faults)
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(heap.world) if r not in faults.dead_ranks]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    return results
