@@ -102,11 +102,33 @@ def test_hybrid_model_graph_decode_equals_eager_and_chunking(name):
     assert same >= 0.9 * 60          # chunked prefill differs only by bf16 round-off in rare ties
 
 
-@pytest.mark.parametrize("name", ["tiny-qwen35-test", "tiny-lfm2-test"])
+def _to_cpu(obj):
+    """Deep copy of a weight container (tensors, dicts, slotted objects) onto the CPU."""
+    if torch.is_tensor(obj):
+        return obj.cpu()
+    if isinstance(obj, dict):
+        return {k: _to_cpu(v) for k, v in obj.items()}
+    if hasattr(obj, "__slots__"):
+        c = type(obj)()
+        for s in obj.__slots__:
+            setattr(c, s, _to_cpu(getattr(obj, s)))
+        return c
+    return obj
+
+
+def _cpu_twin(gpu, name):
+    """CPU model with the GPU model's weights (the CUDA and CPU generators draw different streams)."""
+    cpu = registry.build_model(name, device="cpu", seed=2)
+    cpu.embed, cpu.final_norm, cpu.lm_head = gpu.embed.cpu(), gpu.final_norm.cpu(), gpu.lm_head.cpu()
+    cpu.layers = [_to_cpu(lw) for lw in gpu.layers]
+    return cpu
+
+
+@pytest.mark.parametrize("name", ["tiny-qwen35-test", "tiny-qwen35-moe-test", "tiny-lfm2-test"])
 def test_hybrid_prefill_logits_match_cpu(name):
     from zml_b200.models.llama import AttnMeta
     gpu = registry.build_model(name, device=DEV, seed=2)
-    cpu = registry.build_model(name, device="cpu", seed=2)
+    cpu = _cpu_twin(gpu, name)
     lens, page = [50, 7], 64
     ids = torch.randint(3, 1000, (sum(lens),), dtype=torch.int32)
     pos = torch.cat([torch.arange(n) for n in lens]).int()

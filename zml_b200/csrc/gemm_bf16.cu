@@ -616,17 +616,22 @@ int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, 
 // Weight tiles per CTA to pull into L2 ahead of the shared-memory ring while the preceding
 // kernel drains: only for the weight-streaming (few tokens) regime, and at most ~40 MB in all,
 // a third of the L2.
+int g_l2_prefetch_mb = 40;
 int l2_prefetch_tiles(int swap, int bn, int grid, int rr_tiles) {
-  if (!swap || rr_tiles > 0 || grid <= 0) return 0;
+  if (!swap || rr_tiles > 0 || grid <= 0 || g_l2_prefetch_mb <= 0) return 0;
   const long long tile_bytes = static_cast<long long>(kBlockP) * kBlockK * 2;
   (void)bn;
-  const long long per_cta = (40ll << 20) / grid / tile_bytes;
+  const long long per_cta = (static_cast<long long>(g_l2_prefetch_mb) << 20) / grid / tile_bytes;
   return static_cast<int>(per_cta > 64 ? 64 : per_cta);
 }
 
 }  // namespace
 
 extern "C" {
+
+// Megabytes of weight tiles (over the whole grid) that a weight-streaming GEMM pulls into L2
+// ahead of its shared-memory ring; 0 turns the prefetch off.
+void zb_set_l2_prefetch_mb(int mb) { g_l2_prefetch_mb = mb < 0 ? 0 : (mb > 96 ? 96 : mb); }
 
 // Tile shape and grid for a problem: swap-AB for few tokens, and a stream-K grid in
 // which every CTA owns at least `min_units` k-blocks.  `split_hint` > 0 asks for about
