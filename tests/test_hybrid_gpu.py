@@ -144,3 +144,46 @@ def test_hybrid_prefill_logits_match_cpu(name):
         x = m.hidden_states(ids.to(dev), meta, kv)
         outs.append(m.logits(x).float().cpu())
     expect_close(outs[0], outs[1], atol=6e-2, rtol=6e-2, min_close=0.99)
+
+
+def test_quant_kernels_match_torch_formulation():
+    from zml_b200.nn import quant as Q
+    from zml_b200.ops import quant as opsq
+    torch.manual_seed(0)
+    x = (torch.randn(37, 256, device=DEV) * 3).bfloat16()
+    x[0, :16] = 0                                              # an all-zero block takes the minimum scale
+    codes, scales = opsq.nvfp4_quantize(x)
+    rc, rs = Q.quantize_nvfp4(x.cpu())
+    assert torch.equal(scales.cpu().view(torch.uint8), rs.view(torch.uint8))
+    assert torch.equal(codes.cpu(), Q.pack_e2m1(rc))
+    gs = torch.tensor(0.37)
+    codes_g, scales_g = opsq.nvfp4_quantize(x, gs.to(DEV))
+    rc_g, rs_g = Q.quantize_nvfp4(x.cpu(), gs)
+    assert (codes_g.cpu() != Q.pack_e2m1(rc_g)).float().mean().item() < 0.01
+    back = opsq.nvfp4_dequantize(codes, scales)
+    want = Q.dequantize_nvfp4(rc, rs, None, torch.bfloat16)
+    assert torch.equal(back.cpu(), want)
+    err = (back.float() - x.float()).abs().mean() / x.float().abs().mean()
+    assert err.item() < 0.12
+    q8, s8 = opsq.fp8_group_quant(x, 128)
+    rq, rsc = Q.per_token_group_quant_fp8(x.cpu(), 128)
+    torch.testing.assert_close(s8.cpu(), rsc, rtol=1e-6, atol=0)
+    assert (q8.cpu().view(torch.uint8) != rq.view(torch.uint8)).float().mean().item() < 0.002
+
+
+def test_nvfp4_linear_runs_on_the_bf16_gemm():
+    from zml_b200.nn import layers, quant as Q
+    from zml_b200.shape import Shape
+    from zml_b200.tensor import Tensor
+    torch.manual_seed(1)
+    w = torch.randn(256, 128) * 0.1
+    packed, scales, gs = Q.quantize_weight_nvfp4(w)
+    x = torch.randn(9, 128).bfloat16()
+    def make(dev):
+        lin = layers.Linear(Tensor(packed.to(dev), Shape({"dout": 256, "d": 64}, "u8")), None, "d",
+                            layers.Quant(Q.QuantScheme.nvfp4, Tensor(scales.to(dev), Shape({"dout": 256, "d": 8}, "f8e4m3fn")),
+                                         layers.TensorScale(Tensor(gs.reshape(1).to(dev), Shape((1,), "f32")))))
+        return lin(Tensor(x.to(dev), Shape({"b": 9, "d": 128}, "bf16"))).to_torch().float().cpu()
+    expect_close(make(DEV), make("cpu"), atol=3e-2, rtol=3e-2, min_close=0.995)
+    exact = x.float() @ w.t()
+    assert ((make("cpu") - exact).norm() / exact.norm()).item() < 0.2          # 4-bit weights: ~10 % error

@@ -490,8 +490,7 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
   constexpr int smem = pipe > merge ? pipe : merge;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(zb_paged_decode_kernel<HD>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = zb_config_smem(zb_paged_decode_kernel<HD>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
@@ -506,8 +505,7 @@ int launch_prefill(const AttnParams& p, int num_q_blocks, cudaStream_t stream) {
   constexpr int smem = 5 * 64 * HD * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(zb_paged_prefill_kernel<HD>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = zb_config_smem(zb_paged_prefill_kernel<HD>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }

@@ -53,13 +53,18 @@ struct GemmParams {
   int group_p;       // rasterisation group height (P tiles)
   int flags;         // bit 0: the weight operand is not written by the preceding kernel
   int l2_prefetch;   // weight tiles per CTA to pull into L2 ahead of the shared-memory ring
+  unsigned long long* timeline;   // optional [grid][8] globaltimer stamps of this launch's phases (profiling)
   float* workspace;  // [grid][2][BN][128] fp32 partial tiles
   uint32_t* counters;  // one per output tile, zero between launches
   ZbStatus* status;
   ZbFusedAr ar;        // used by the fused GEMM + all-reduce variant only
 };
 
-__host__ __device__ constexpr int stages_for(int bn) {
+// Pipeline depth: as many stages as fit beside the barriers in one CTA's shared memory.  (Sizing the
+// weight-streaming configurations for two CTAs per SM, so that the next GEMM of the stream could
+// run under this one's tail, measured slower: 127 vs 121 us per decoder layer on the 8B shapes.)
+__host__ __device__ constexpr int stages_for(int bn, bool swap) {
+  (void)swap;
   return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8);
 }
 __host__ __device__ constexpr int stage_bytes(int bn) { return (kBlockP + bn) * kBlockK * 2; }
@@ -70,7 +75,7 @@ template <int BN, bool SWAP, bool FUSED>
 __global__ void __launch_bounds__(kNumThreads, 1)
 zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                     const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
-  constexpr int kStages = stages_for(BN);
+  constexpr int kStages = stages_for(BN, SWAP);
   constexpr int kStageBytes = stage_bytes(BN);
   constexpr int kTileABytes = kBlockP * kBlockK * 2;
   constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
@@ -116,8 +121,10 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     qt = within / gp;
   };
 
+  unsigned long long* tl = prm.timeline != nullptr ? prm.timeline + static_cast<size_t>(blockIdx.x) * 8 : nullptr;
   int early = 0;     // producer thread: stages whose weight tile was requested ahead of the dependency wait
   if (threadIdx.x == 0) {
+    if (tl) tl[0] = zb_globaltimer();
     for (int s = 0; s < kStages; ++s) {
       zb_mbar_init(&full_bar[s], 1);
       zb_mbar_init(&empty_bar[s], 1);
@@ -179,6 +186,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // preceding kernel before its first activation load; the epilogue warps, which read the
   // residual and write the output, wait here.
   zb_pdl_launch();
+  if (tl && threadIdx.x == 0) tl[1] = zb_globaltimer();
   if (warp >= 2) zb_pdl_wait();
 
   if (warp == 0) {
@@ -187,6 +195,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       zb_tma_prefetch_desc(&tmap_p);
       zb_tma_prefetch_desc(&tmap_q);
       zb_pdl_wait();
+      if (tl) tl[2] = zb_globaltimer();
       uint32_t stage = 0, phase = 0;
       int issued = 0;
       bool ok = true;
@@ -245,6 +254,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             ok = false;
             break;
           }
+          if (tl && tl[3] == 0ull) tl[3] = zb_globaltimer();
           zb_tc_fence_after();
           const uint32_t sa = zb_smem_u32(smem + stage * kStageBytes);
           const uint32_t sb = sa + kTileABytes;
@@ -263,6 +273,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
         if (!ok) break;
         zb_umma_commit(&tmem_full[acc]);       // accumulator complete
+        if (tl) tl[4] = zb_globaltimer();
         acc ^= 1u;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -291,6 +302,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const int first_cta = static_cast<int>(t_begin / prm.units_per_cta);
       const int last_cta = static_cast<int>((t_begin + kb_total - 1) / prm.units_per_cta);
       zb_mbar_wait(&tmem_full[acc], acc_phase, abort_flag);
+      if (tl && epi_tid == 0 && tl[5] == 0ull) tl[5] = zb_globaltimer();
       epi_bar_sync();
       if (*abort_flag != 0u) break;
       zb_tc_fence_after();
@@ -513,6 +525,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (tl && epi_tid == 0) tl[6] = zb_globaltimer();
     if constexpr (FUSED) {
       // 3. the all-reduced output is complete on this rank once every tile is marked done
       if (*abort_flag == 0u) {
@@ -553,6 +566,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     zb_tc_fence_after();
     zb_tmem_dealloc(tmem_base, kTmemCols);
   }
+  if (tl && threadIdx.x == 64) tl[7] = zb_globaltimer();
 }
 
 // ------------------------------------------------------------------ host side
@@ -600,11 +614,10 @@ namespace {
 template <int BN, bool SWAP, bool FUSED = false>
 int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid,
            cudaStream_t stream) {
-  constexpr int smem = stages_for(BN) * stage_bytes(BN) + 1024 + 256;
+  constexpr int smem = stages_for(BN, SWAP) * stage_bytes(BN) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(zb_gemm_bf16_kernel<BN, SWAP, FUSED>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = zb_config_smem(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
@@ -617,6 +630,7 @@ int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, 
 // kernel drains: only for the weight-streaming (few tokens) regime, and at most ~40 MB in all,
 // a third of the L2.
 int g_l2_prefetch_mb = 40;
+unsigned long long* g_timeline = nullptr;
 int l2_prefetch_tiles(int swap, int bn, int grid, int rr_tiles) {
   if (!swap || rr_tiles > 0 || grid <= 0 || g_l2_prefetch_mb <= 0) return 0;
   const long long tile_bytes = static_cast<long long>(kBlockP) * kBlockK * 2;
@@ -628,6 +642,12 @@ int l2_prefetch_tiles(int swap, int bn, int grid, int rr_tiles) {
 }  // namespace
 
 extern "C" {
+
+// Profiling aid: when set, every CTA of the following GEMM launches writes globaltimer stamps to
+// buf[cta][8] = {entry, prologue done, producer past the dependency wait, first tile landed,
+// last accumulator committed, first accumulator seen by the epilogue, epilogue done, exit}.
+// `buf` must hold 8 * (number of SMs) zeroed u64 and be re-zeroed between launches; null turns it off.
+void zb_gemm_set_timeline(unsigned long long* buf) { g_timeline = buf; }
 
 // Megabytes of weight tiles (over the whole grid) that a weight-streaming GEMM pulls into L2
 // ahead of its shared-memory ring; 0 turns the prefetch off.
@@ -714,6 +734,7 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   prm.out_f32 = out_f32;
   prm.flags = static_w;
   prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
+  prm.timeline = g_timeline;
   prm.group_p = 16;
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;
@@ -779,6 +800,7 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   prm.out_f32 = 0;
   prm.flags = 1;     // `w` is a model parameter in every use of the fused kernel
   prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
+  prm.timeline = g_timeline;
   prm.group_p = 16;
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;

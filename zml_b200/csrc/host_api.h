@@ -63,6 +63,16 @@ inline cudaError_t zb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Opts a kernel into `smem` bytes of dynamic shared memory and asks for the largest shared-memory
+// carve-out, so that as many CTAs as the byte count allows are resident per SM (the default
+// carve-out is only as large as one CTA needs).
+template <typename K>
+inline cudaError_t zb_config_smem(K kernel, int smem) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 extern "C" {
 void zb_set_pdl(int on);
 int zb_init(int device);

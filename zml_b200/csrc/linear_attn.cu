@@ -236,8 +236,7 @@ int launch_gdn(const GdnParams& p, int num_seqs, cudaStream_t s) {
   const size_t smem = (2 * kGdnChunk * DK + 2 * kGdnChunk * p.dv + 2 * kGdnChunk) * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(zb_gated_delta_scan_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (2 * kGdnChunk * DK + 2 * kGdnChunk * 256 + 2 * kGdnChunk) * 4);
+    cudaError_t e = zb_config_smem(zb_gated_delta_scan_kernel<DK>, (2 * kGdnChunk * DK + 2 * kGdnChunk * 256 + 2 * kGdnChunk) * 4);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }

@@ -504,8 +504,7 @@ int launch_grouped(const CUtensorMap& tx, const CUtensorMap& tw, const GroupedPa
   constexpr int smem = g_stages(BN) * g_stage_bytes(BN) + ((SWAP && SWIGLU) ? BN * 64 * 4 : 0) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = zb_config_smem(zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }

@@ -63,7 +63,14 @@ class Linear:
         x2 = xm.reshape(-1, xm.shape[-1])
         wgs = q.weight_scale.as_multiplier() if q.weight_scale else None
         igs = q.input_scale.as_multiplier() if q.input_scale else None
-        if q.scheme is Q.QuantScheme.nvfp4:
+        if q.scheme is Q.QuantScheme.nvfp4 and w.is_cuda and self.weight.dtype() is DataType.u8:
+            # B200: de-quantise the packed weight once (cached) and run the bf16 tcgen05 GEMM
+            from .. import ops
+            from ..ops import quant as opsq
+            if getattr(self, "_dequant", None) is None:
+                self._dequant = opsq.nvfp4_dequantize(w.contiguous(), q.scales.data.contiguous())
+            acc = ops.gemm(x2.contiguous(), self._dequant, out_dtype=torch.float32)
+        elif q.scheme is Q.QuantScheme.nvfp4:
             codes = Q.unpack_e2m1(w) if self.weight.dtype() is DataType.u8 else w
             acc = Q.scaled_dot(x2, codes, None, q.scales.data)
         elif q.scheme is Q.QuantScheme.fp8_block128:
