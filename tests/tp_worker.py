@@ -73,6 +73,27 @@ def main():
     allo = comm.all_gather_object(outs["fused"])
     assert all(o == allo[0] for o in allo)
     ops.raise_on_status()
+
+    # every model family under 2-way parallelism (TP attention / MLP, EP experts, sharded linear-attention
+    # heads and conv channels) against the same global weights on one rank
+    from zml_b200.models import registry
+    single = Comm.single(dev)
+    for name in ("tiny-moe-test", "tiny-qwen35-test", "tiny-qwen35-moe-test", "tiny-lfm2-test"):
+        prompts2 = [torch.randint(3, 1000, (n,), generator=torch.Generator().manual_seed(11)).tolist() for n in (21, 70)]
+        got = {}
+        for label, c, fused in (("tp_nccl", comm, False), ("tp_fused", comm, True), ("single", single, False)):
+            model = registry.build_model(name, c, device=dev, seed=3, fused=fused)
+            eng = Engine(model, num_pages=32, page_size=64, max_batch=4, max_seq_len=512)
+            got[label], _ = eng.generate(prompts2, 10)
+            if fused and c.fused is not None:
+                c.fused.close()
+                c.fused = None
+        for label in ("tp_nccl", "tp_fused"):
+            same = sum(a == b for x, y in zip(got[label], got["single"]) for a, b in zip(x[:4], y[:4]))
+            assert same >= 6, (name, label, got)
+        allo = comm.all_gather_object(got["tp_fused"])
+        assert all(o == allo[0] for o in allo), name
+        ops.raise_on_status()
     ctx.close()
     comm.barrier()
     if comm.rank == 0:

@@ -337,18 +337,40 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
   __syncthreads();
   if (s_last == 0u) return;
   __threadfence();
+  // Phase 1: (max, sum) of every (row, chunk) -> shared memory, one round trip to L2.
+  // Phase 2: every thread combines its output elements with the chunk loads of an element
+  // batched eight at a time, so that the merge costs a few round trips, not one per chunk.
+  float* s_m = reinterpret_cast<float*>(smem);          // [group][my_splits]
+  float* s_l = s_m + 16 * 64;                           // [group][my_splits] (at most 16 rows x 64 chunks)
+  const int nsp = min(my_splits, 64);
+  for (int i = threadIdx.x; i < group * nsp; i += blockDim.x) {
+    const int r = i / nsp, sp = i - r * nsp;
+    const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + kvh * group + r) * p.num_splits;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&p.part_ml[(base + sp) * 2]));
+    s_m[r * 64 + sp] = ml.x;
+    s_l[r * 64 + sp] = ml.y;
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
     const int r = idx / HD, c = idx % HD;
     const int head = kvh * group + r;
     const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + head) * p.num_splits;
     float mm = -INFINITY;
-    for (int sp = 0; sp < my_splits; ++sp) mm = fmaxf(mm, __ldcg(&p.part_ml[(base + sp) * 2]));
+    for (int sp = 0; sp < nsp; ++sp) mm = fmaxf(mm, s_m[r * 64 + sp]);
     const float muse = (mm == -INFINITY) ? 0.f : mm;
     float acc = 0.f, ll = 0.f;
-    for (int sp = 0; sp < my_splits; ++sp) {
-      const float f = exp2f(__ldcg(&p.part_ml[(base + sp) * 2]) - muse);
-      acc += f * __ldcg(&p.part_o[(base + sp) * HD + c]);
-      ll += f * __ldcg(&p.part_ml[(base + sp) * 2 + 1]);
+    for (int sp0 = 0; sp0 < nsp; sp0 += 8) {
+      float pv[8];
+#pragma unroll
+      for (int b = 0; b < 8; ++b) pv[b] = __ldcg(&p.part_o[(base + min(sp0 + b, nsp - 1)) * HD + c]);
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        if (sp0 + b < nsp) {
+          const float f = exp2f(s_m[r * 64 + sp0 + b] - muse);
+          acc += f * pv[b];
+          ll += f * s_l[r * 64 + sp0 + b];
+        }
+      }
     }
     p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
   }
@@ -561,6 +583,7 @@ int zb_paged_decode_ex(const void* q, const void* k_cache, const void* v_cache, 
   if (num_q_heads % num_kv_heads != 0 || num_q_heads / num_kv_heads > 16) return -30;
   if (page_size % 16 != 0) return -31;
   if (num_splits < 1) num_splits = 1;
+  if (num_splits > 64) num_splits = 64;      // the in-kernel merge keeps per-chunk statistics for 64 chunks
   if (batch * num_kv_heads > counters_len) return -33;
   while (num_splits > 1 &&
          zb_decode_scratch_bytes(batch, num_q_heads, head_dim, num_splits) > scratch_bytes)

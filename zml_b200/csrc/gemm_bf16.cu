@@ -64,6 +64,9 @@ struct GemmParams {
 // weight-streaming configurations for two CTAs per SM, so that the next GEMM of the stream could
 // run under this one's tail, measured slower: 127 vs 121 us per decoder layer on the 8B shapes.)
 __host__ __device__ constexpr int stages_for(int bn, bool swap) {
+#ifdef ZB_GEMM_TWO_CTA
+  if (swap) return bn <= 16 ? 6 : (bn <= 32 ? 5 : (bn <= 64 ? 4 : (bn <= 128 ? 3 : 4)));
+#endif
   (void)swap;
   return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8);
 }
@@ -71,8 +74,14 @@ __host__ __device__ constexpr int stage_bytes(int bn) { return (kBlockP + bn) * 
 
 ZB_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+#ifdef ZB_GEMM_TWO_CTA
+#define ZB_GEMM_MIN_CTAS(SWAP, BN) (((SWAP) && (BN) <= 128) ? 2 : 1)
+#else
+#define ZB_GEMM_MIN_CTAS(SWAP, BN) 1
+#endif
+
 template <int BN, bool SWAP, bool FUSED>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kNumThreads, ZB_GEMM_MIN_CTAS(SWAP, BN))
 zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                     const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
   constexpr int kStages = stages_for(BN, SWAP);
@@ -346,12 +355,26 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         if (partial) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] = 0.f;
-          for (int c = first_cta; c <= last_cta; ++c) {
-            const long long c_begin = static_cast<long long>(c) * prm.units_per_cta;
-            const int slot = (max(t_begin, c_begin) == c_begin) ? 0 : 1;
-            const float* ws = prm.workspace + (static_cast<size_t>(c) * 2 + slot) * (BN * kBlockP);
+          // four pieces per round trip to L2: the loads of a batch are all in flight before the
+          // first add (summation order stays ascending in c, so the result does not depend on it)
+          for (int c = first_cta; c <= last_cta; c += 4) {
+            float t4[4][16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] += __ldcg(&ws[(c0 + j) * kBlockP + row_in_tile]);
+            for (int b = 0; b < 4; ++b) {
+              const int cc = min(c + b, last_cta);
+              const long long c_begin = static_cast<long long>(cc) * prm.units_per_cta;
+              const int slot = (max(t_begin, c_begin) == c_begin) ? 0 : 1;
+              const float* ws = prm.workspace + (static_cast<size_t>(cc) * 2 + slot) * (BN * kBlockP);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) t4[b][j] = __ldcg(&ws[(c0 + j) * kBlockP + row_in_tile]);
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              if (c + b <= last_cta) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += t4[b][j];
+              }
+            }
           }
         } else {
           uint32_t r[16];
@@ -443,7 +466,96 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
       };
 
-      if constexpr (!FUSED) {
+      if constexpr (!FUSED && SWAP && BN <= 64) {
+        if (partial && do_store) {
+          // Fix-up of a split tile, few tokens: the pieces are summed straight from the workspace by
+          // all 128 epilogue threads with 16-byte loads - thread (lane, g) owns rows 4*lane..4*lane+3
+          // and columns g, g+4, ... - several pieces per round trip to L2 (this serial tail is what a
+          // weight-streaming GEMM of a few tens of megabytes spends most of its time on otherwise).
+          constexpr int kCols = BN / 4;                        // columns per thread
+          constexpr int kBatch = BN <= 16 ? 6 : (BN <= 32 ? 3 : 1);
+          const int r4 = (epi_tid & 31) * 4;
+          const int cg = epi_tid >> 5;
+          float4 accv[kCols];
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) accv[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int c = first_cta; c <= last_cta; c += kBatch) {
+            float4 tv[kBatch][kCols];
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+              const int cc = min(c + b, last_cta);
+              const long long c_begin = static_cast<long long>(cc) * prm.units_per_cta;
+              const int slot = (max(t_begin, c_begin) == c_begin) ? 0 : 1;
+              const float4* w4 = reinterpret_cast<const float4*>(
+                  prm.workspace + (static_cast<size_t>(cc) * 2 + slot) * (BN * kBlockP));
+#pragma unroll
+              for (int i = 0; i < kCols; ++i) tv[b][i] = __ldcg(&w4[(cg + 4 * i) * (kBlockP / 4) + (epi_tid & 31)]);
+            }
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+              if (c + b <= last_cta) {
+#pragma unroll
+                for (int i = 0; i < kCols; ++i) {
+                  accv[i].x += tv[b][i].x;
+                  accv[i].y += tv[b][i].y;
+                  accv[i].z += tv[b][i].z;
+                  accv[i].w += tv[b][i].w;
+                }
+              }
+            }
+          }
+          const int pb = pt * kBlockP + r4;                     // first of this thread's 4 output columns
+          float bz[4] = {0.f, 0.f, 0.f, 0.f};
+          if (prm.bias) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) bz[e] = (pb + e) < prm.rows_p ? __bfloat162float(prm.bias[pb + e]) : 0.f;
+          }
+          const bool vec = (pb + 3) < prm.rows_p && (prm.ldo % 4) == 0;
+#pragma unroll
+          for (int i = 0; i < kCols; ++i) {
+            const int q = q0 + cg + 4 * i;
+            if (q >= prm.rows_q) continue;
+            float v4[4] = {accv[i].x + bz[0], accv[i].y + bz[1], accv[i].z + bz[2], accv[i].w + bz[3]};
+            const size_t o = static_cast<size_t>(q) * prm.ldo + pb;
+            if (vec) {
+              if (prm.residual) {
+                const uint2 rr = *reinterpret_cast<const uint2*>(prm.residual + o);
+                const float2 f0 = zb_unpack_bf16x2(rr.x), f1 = zb_unpack_bf16x2(rr.y);
+                v4[0] += f0.x;
+                v4[1] += f0.y;
+                v4[2] += f1.x;
+                v4[3] += f1.y;
+              }
+              if (prm.out_f32) {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(prm.out) + o) = make_float4(v4[0], v4[1], v4[2], v4[3]);
+              } else {
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(prm.out) + o) =
+                    make_uint2(zb_pack_bf16x2(v4[0], v4[1]), zb_pack_bf16x2(v4[2], v4[3]));
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                if (pb + e < prm.rows_p) {
+                  float x = v4[e];
+                  if (prm.residual) x += __bfloat162float(prm.residual[o + e]);
+                  if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o + e] = x;
+                  else reinterpret_cast<__nv_bfloat16*>(prm.out)[o + e] = __float2bfloat16(x);
+                }
+              }
+            }
+          }
+        } else if (do_store) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            load_chunk(c0, v);
+            if (p < prm.rows_p) {
+              finish_chunk(c0, v);
+              store_chunk(c0, v, prm.out);
+            }
+          }
+        }
+      } else if constexpr (!FUSED) {
         if (do_store) {
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -631,6 +743,14 @@ int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, 
 // a third of the L2.
 int g_l2_prefetch_mb = 40;
 unsigned long long* g_timeline = nullptr;
+int g_timeline_slots = 0;
+int g_timeline_next = 0;
+unsigned long long* next_timeline(int grid) {
+  if (g_timeline == nullptr || g_timeline_slots <= 0 || grid > 160) return nullptr;
+  unsigned long long* p = g_timeline + static_cast<size_t>(g_timeline_next % g_timeline_slots) * 160 * 8;
+  ++g_timeline_next;
+  return p;
+}
 int l2_prefetch_tiles(int swap, int bn, int grid, int rr_tiles) {
   if (!swap || rr_tiles > 0 || grid <= 0 || g_l2_prefetch_mb <= 0) return 0;
   const long long tile_bytes = static_cast<long long>(kBlockP) * kBlockK * 2;
@@ -646,8 +766,13 @@ extern "C" {
 // Profiling aid: when set, every CTA of the following GEMM launches writes globaltimer stamps to
 // buf[cta][8] = {entry, prologue done, producer past the dependency wait, first tile landed,
 // last accumulator committed, first accumulator seen by the epilogue, epilogue done, exit}.
-// `buf` must hold 8 * (number of SMs) zeroed u64 and be re-zeroed between launches; null turns it off.
-void zb_gemm_set_timeline(unsigned long long* buf) { g_timeline = buf; }
+// `buf` holds `slots` records of 160 * 8 zeroed u64; consecutive launches take consecutive records
+// (wrapping around).  Null turns it off.
+void zb_gemm_set_timeline(unsigned long long* buf, int slots) {
+  g_timeline = buf;
+  g_timeline_slots = slots;
+  g_timeline_next = 0;
+}
 
 // Megabytes of weight tiles (over the whole grid) that a weight-streaming GEMM pulls into L2
 // ahead of its shared-memory ring; 0 turns the prefetch off.
@@ -734,7 +859,7 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   prm.out_f32 = out_f32;
   prm.flags = static_w;
   prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
-  prm.timeline = g_timeline;
+  prm.timeline = next_timeline(grid);
   prm.group_p = 16;
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;
@@ -800,7 +925,7 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   prm.out_f32 = 0;
   prm.flags = 1;     // `w` is a model parameter in every use of the fused kernel
   prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
-  prm.timeline = g_timeline;
+  prm.timeline = next_timeline(grid);
   prm.group_p = 16;
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;
