@@ -167,6 +167,26 @@ ZB_DEVICE void zb_tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, i
       : "memory");
 }
 
+// Thread-block clusters: rank, cluster-wide barrier (every thread of every CTA of the cluster
+// takes part), and loads from a peer CTA's shared memory (distributed shared memory).
+ZB_DEVICE uint32_t zb_cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+ZB_DEVICE void zb_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+ZB_DEVICE void zb_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+ZB_DEVICE uint32_t zb_mapa(uint32_t smem_addr, uint32_t cta_rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+  return r;
+}
+ZB_DEVICE float zb_ld_dsmem_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
 // Programmatic dependent launch.  `zb_pdl_wait` blocks until every grid this one depends on has
 // finished and its writes are visible; nothing produced or still read by a preceding kernel may
 // be touched before it.  `zb_pdl_launch` lets the next kernel in the stream begin its own

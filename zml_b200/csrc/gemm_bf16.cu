@@ -24,6 +24,8 @@
 #include <mutex>
 #include <unordered_map>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "host_api.h"
 
@@ -53,6 +55,7 @@ struct GemmParams {
   int group_p;       // rasterisation group height (P tiles)
   int flags;         // bit 0: the weight operand is not written by the preceding kernel
   int l2_prefetch;   // weight tiles per CTA to pull into L2 ahead of the shared-memory ring
+  int cluster;       // > 1: the CTAs of a cluster split one tile along K and reduce it through shared memory
   unsigned long long* timeline;   // optional [grid][8] globaltimer stamps of this launch's phases (profiling)
   float* workspace;  // [grid][2][BN][128] fp32 partial tiles
   uint32_t* counters;  // one per output tile, zero between launches
@@ -115,8 +118,15 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // and map to actual tile (v % rr_tiles) * grid + cta.  Small problems: stream-K ranges.
   const long long total_units =
       static_cast<long long>(prm.rr_tiles > 0 ? static_cast<int>(gridDim.x) * prm.rr_tiles : num_out_tiles) * kb_total;
-  const long long u_begin = min(total_units, static_cast<long long>(blockIdx.x) * prm.units_per_cta);
-  const long long u_end = min(total_units, u_begin + prm.units_per_cta);
+  long long u_begin = min(total_units, static_cast<long long>(blockIdx.x) * prm.units_per_cta);
+  long long u_end = min(total_units, u_begin + prm.units_per_cta);
+  if (prm.cluster > 1) {
+    // cluster split-K: CTA (tile, rank) takes k-blocks [rank * upc, (rank + 1) * upc) of its tile
+    const long long tile = blockIdx.x / prm.cluster;
+    const int rank = static_cast<int>(blockIdx.x % prm.cluster);
+    u_begin = tile * kb_total + min(kb_total, rank * prm.units_per_cta);
+    u_end = tile * kb_total + min(kb_total, (rank + 1) * prm.units_per_cta);
+  }
 
   // output tile -> (p tile, q tile); P tiles are grouped so that CTAs working at the
   // same time share few distinct operand tiles in L2.
@@ -130,7 +140,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     qt = within / gp;
   };
 
-  unsigned long long* tl = prm.timeline != nullptr ? prm.timeline + static_cast<size_t>(blockIdx.x) * 8 : nullptr;
+  unsigned long long* tl = prm.timeline != nullptr ? prm.timeline + static_cast<size_t>(blockIdx.x) * 12 : nullptr;
   int early = 0;     // producer thread: stages whose weight tile was requested ahead of the dependency wait
   if (threadIdx.x == 0) {
     if (tl) tl[0] = zb_globaltimer();
@@ -243,6 +253,14 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         u += kb1 - kb0;
       }
     }
+    if (prm.cluster > 1) {
+      // the cluster barriers of the epilogue count every thread of every CTA
+      __syncwarp();
+      zb_cluster_arrive();
+      zb_cluster_wait();
+      zb_cluster_arrive();
+      zb_cluster_wait();
+    }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
@@ -287,12 +305,21 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         if (acc == 0) acc_phase ^= 1u;
       }
     }
+    if (prm.cluster > 1) {
+      // the cluster barriers of the epilogue count every thread of every CTA
+      __syncwarp();
+      zb_cluster_arrive();
+      zb_cluster_wait();
+      zb_cluster_arrive();
+      zb_cluster_wait();
+    }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int epi_tid = threadIdx.x - 64;          // 0..127
     const int quad = warp & 3;                     // TMEM lane quadrant of this warp
     const int row_in_tile = quad * 32 + lane;      // MMA-M row held by this thread
     uint32_t acc = 0, acc_phase = 0;
+    bool did_cluster_sync = false;
     uint32_t epoch = 0;
     if constexpr (FUSED) epoch = *reinterpret_cast<volatile uint32_t*>(prm.ar.epoch);
     for (long long u = u_begin; u < u_end;) {
@@ -319,6 +346,171 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const int p = pt * kBlockP + row_in_tile;
       const int q0 = qt * BN;
       const int out_tile = pt * num_q + qt;
+
+      if constexpr (SWAP && BN <= 64) {
+        if (prm.cluster > 1) {
+          // Cluster split-K: every CTA of the cluster holds a partial of the same tile.  Partials go
+          // to the CTA's own shared memory (the operand ring is idle: this CTA has no other tile),
+          // and after a cluster barrier every CTA sums a band of rows over all peers through
+          // distributed shared memory - no trip through L2, no last-arriver tail.
+          float* part = reinterpret_cast<float*>(smem);          // [BN][128]
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint32_t r[16];
+            zb_tmem_ld16(taddr + c0, r);
+            zb_tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) part[(c0 + j) * kBlockP + row_in_tile] = __uint_as_float(r[j]);
+          }
+          zb_tc_fence_before();
+          zb_mbar_arrive(&tmem_empty[acc]);
+          zb_cluster_arrive();
+          zb_cluster_wait();
+          did_cluster_sync = true;
+          const int S = prm.cluster;
+          const int rank = static_cast<int>(zb_cluster_ctarank());
+          const int rb0 = rank * kBlockP / S, rb1 = (rank + 1) * kBlockP / S;
+          const int nrows = rb1 - rb0;
+          const int total = BN * nrows;
+          const uint32_t part_u32 = zb_smem_u32(part);
+          uint32_t peer_base[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) peer_base[c] = zb_mapa(part_u32, static_cast<uint32_t>(c < S ? c : 0));
+          // all loads of a batch (peer partials, residual, bias) are issued before its first store:
+          // `out` may alias `residual`, so the compiler would otherwise serialise them
+          auto reduce_batch = [&](auto kb_tag, auto kc_tag, int e0) {
+            constexpr int KB = decltype(kb_tag)::value, KC = decltype(kc_tag)::value;
+            float tv[KB][KC], rsd[KB], bs[KB];
+            int off[KB];
+#pragma unroll
+            for (int i = 0; i < KB; ++i) {
+              const int e = min(e0 + i * kEpiThreads, total - 1);
+              const int col = e / nrows, row = rb0 + (e - col * nrows);
+              off[i] = col * kBlockP + row;
+#pragma unroll
+              for (int c = 0; c < KC; ++c) tv[i][c] = c < S ? zb_ld_dsmem_f32(peer_base[c] + off[i] * 4) : 0.f;
+              const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
+              rsd[i] = prm.residual ? __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]) : 0.f;
+              bs[i] = prm.bias ? __bfloat162float(prm.bias[pp]) : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < KB; ++i) {
+              const int e = e0 + i * kEpiThreads;
+              if (e >= total) continue;
+              float v = 0.f;
+#pragma unroll
+              for (int c = 0; c < KC; ++c) v += tv[i][c];            // ascending rank: deterministic
+              const int col = off[i] / kBlockP, row = off[i] - col * kBlockP;
+              const int pp = pt * kBlockP + row, qq = q0 + col;
+              if (pp < prm.rows_p && qq < prm.rows_q) {
+                const size_t o = static_cast<size_t>(qq) * prm.ldo + pp;
+                v += bs[i] + rsd[i];
+                if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
+                else reinterpret_cast<__nv_bfloat16*>(prm.out)[o] = __float2bfloat16(v);
+              }
+            }
+          };
+          if constexpr (!FUSED) {
+            if (S <= 4) {
+              for (int e0 = epi_tid; e0 < total; e0 += 8 * kEpiThreads)
+                reduce_batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{}, e0);
+            } else {
+              for (int e0 = epi_tid; e0 < total; e0 += 4 * kEpiThreads)
+                reduce_batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{}, e0);
+            }
+            // nobody may leave (and release its shared memory) while a peer still reads it
+            zb_cluster_arrive();
+            zb_cluster_wait();
+          } else {
+            // Tensor-parallel variant: the band this CTA reduced over the cluster is this rank's
+            // partial; it goes to every rank in one hop, and the band is finished from the copies
+            // of all ranks (fused_ar.h, one_shot).  Up to 16 elements per thread.
+            const ZbFusedAr& ar = prm.ar;
+            constexpr int kE = 16;
+            float val[kE];
+            int offs[kE];
+#pragma unroll
+            for (int b4 = 0; b4 < kE; b4 += 4) {
+              float tv[4][8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int e = min(epi_tid + (b4 + i) * kEpiThreads, total - 1);
+                const int col = e / nrows, row = rb0 + (e - col * nrows);
+                offs[b4 + i] = col * kBlockP + row;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) tv[i][c] = c < S ? zb_ld_dsmem_f32(peer_base[c] + offs[b4 + i] * 4) : 0.f;
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float v = 0.f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v += tv[i][c];
+                val[b4 + i] = v;
+              }
+            }
+            if (tl && epi_tid == 0) tl[8] = zb_globaltimer();
+            zb_cluster_arrive();                 // peers' shared memory is no longer needed; waited for below
+            const size_t tile_elems = static_cast<size_t>(kBlockP) * BN;
+            const size_t half = static_cast<size_t>(ar.world) * num_out_tiles * tile_elems;
+            const size_t base_off = (epoch & 1u) * half + static_cast<size_t>(out_tile) * tile_elems;
+            const size_t src_stride = static_cast<size_t>(num_out_tiles) * tile_elems;
+            for (int d = 0; d < ar.world; ++d) {
+              __nv_bfloat16* dst = ar.recv_peer[d] + base_off + static_cast<size_t>(ar.rank) * src_stride;
+#pragma unroll
+              for (int i = 0; i < kE; ++i)
+                if (epi_tid + i * kEpiThreads < total) dst[offs[i]] = __float2bfloat16(val[i]);
+            }
+            __threadfence_system();
+            if (tl && epi_tid == 0) tl[9] = zb_globaltimer();
+            epi_bar_sync();
+            const size_t fidx = (static_cast<size_t>(out_tile) * S + rank) * ar.world;
+            if (epi_tid < ar.world) zb_st_release_sys(ar.push_flag_peer[epi_tid] + fidx + ar.rank, epoch);
+            if (epi_tid < ar.world) {
+              if (!zb_wait_flag(ar.push_flag_peer[ar.rank] + fidx + epi_tid, epoch, abort_flag)) *abort_where = 100u + epi_tid;
+            }
+            epi_bar_sync();
+            if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
+            if (*abort_flag == 0u) {
+              const __nv_bfloat16* mine = ar.recv_peer[ar.rank] + base_off;
+#pragma unroll
+              for (int b4 = 0; b4 < kE; b4 += 4) {
+                __nv_bfloat16 xv[4][kZbMaxRanks];
+                float rsd[4], bs[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int o_t = offs[b4 + i];
+#pragma unroll
+                  for (int src = 0; src < kZbMaxRanks; ++src)
+                    xv[i][src] = mine[static_cast<size_t>(src < ar.world ? src : 0) * src_stride + o_t];
+                  const int col = o_t / kBlockP, row = o_t - col * kBlockP;
+                  const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
+                  rsd[i] = prm.residual ? __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]) : 0.f;
+                  bs[i] = prm.bias ? __bfloat162float(prm.bias[pp]) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  if (epi_tid + (b4 + i) * kEpiThreads >= total) continue;
+                  float v = 0.f;
+#pragma unroll
+                  for (int src = 0; src < kZbMaxRanks; ++src)
+                    if (src < ar.world) v += __bfloat162float(xv[i][src]);
+                  const int o_t = offs[b4 + i];
+                  const int col = o_t / kBlockP, row = o_t - col * kBlockP;
+                  const int pp = pt * kBlockP + row, qq = q0 + col;
+                  if (pp < prm.rows_p && qq < prm.rows_q)
+                    ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = __float2bfloat16(v + bs[i] + rsd[i]);
+                }
+              }
+            }
+            if (tl && epi_tid == 0) tl[11] = zb_globaltimer();
+            zb_cluster_wait();
+            if (*abort_flag != 0u) break;
+          }
+          acc ^= 1u;
+          if (acc == 0) acc_phase ^= 1u;
+          continue;
+        }
+      }
 
       bool do_store = true;
       if (partial) {
@@ -511,6 +703,16 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             for (int e = 0; e < 4; ++e) bz[e] = (pb + e) < prm.rows_p ? __bfloat162float(prm.bias[pb + e]) : 0.f;
           }
           const bool vec = (pb + 3) < prm.rows_p && (prm.ldo % 4) == 0;
+          // residual loads first, all of them: `out` may alias `residual`, which would otherwise
+          // order every load behind the previous column's store
+          uint2 rres[kCols];
+          if (vec && prm.residual) {
+#pragma unroll
+            for (int i = 0; i < kCols; ++i) {
+              const int q = min(q0 + cg + 4 * i, prm.rows_q - 1);
+              rres[i] = *reinterpret_cast<const uint2*>(prm.residual + static_cast<size_t>(q) * prm.ldo + pb);
+            }
+          }
 #pragma unroll
           for (int i = 0; i < kCols; ++i) {
             const int q = q0 + cg + 4 * i;
@@ -519,7 +721,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             const size_t o = static_cast<size_t>(q) * prm.ldo + pb;
             if (vec) {
               if (prm.residual) {
-                const uint2 rr = *reinterpret_cast<const uint2*>(prm.residual + o);
+                const uint2 rr = rres[i];
                 const float2 f0 = zb_unpack_bf16x2(rr.x), f1 = zb_unpack_bf16x2(rr.y);
                 v4[0] += f0.x;
                 v4[1] += f0.y;
@@ -564,6 +766,77 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             if (p < prm.rows_p) {
               finish_chunk(c0, v);
               store_chunk(c0, v, prm.out);
+            }
+          }
+        }
+      } else if (SWAP && BN <= 64 && prm.ar.one_shot != 0) {
+        if (do_store) {
+          // single-hop all-reduce of a tile (few tokens)
+          const ZbFusedAr& ar = prm.ar;
+          const size_t tile_elems = static_cast<size_t>(kBlockP) * BN;
+          const size_t half = static_cast<size_t>(ar.world) * num_out_tiles * tile_elems;
+          const size_t my_off = (epoch & 1u) * half + (static_cast<size_t>(ar.rank) * num_out_tiles + out_tile) * tile_elems +
+                                static_cast<size_t>(row_in_tile) * BN;
+          // 1. this rank's partial -> every rank's staging slot [parity][src = rank][tile][row][BN]
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            load_chunk(c0, v);
+            const uint4 lo = make_uint4(zb_pack_bf16x2(v[0], v[1]), zb_pack_bf16x2(v[2], v[3]),
+                                        zb_pack_bf16x2(v[4], v[5]), zb_pack_bf16x2(v[6], v[7]));
+            const uint4 hi = make_uint4(zb_pack_bf16x2(v[8], v[9]), zb_pack_bf16x2(v[10], v[11]),
+                                        zb_pack_bf16x2(v[12], v[13]), zb_pack_bf16x2(v[14], v[15]));
+            for (int d = 0; d < ar.world; ++d) {
+              uint4* d4 = reinterpret_cast<uint4*>(ar.recv_peer[d] + my_off + c0);
+              d4[0] = lo;
+              d4[1] = hi;
+            }
+          }
+          if (!partial) {
+            zb_tc_fence_before();
+            zb_mbar_arrive(&tmem_empty[acc]);
+          }
+          __threadfence_system();
+          epi_bar_sync();
+          const size_t fidx = static_cast<size_t>(out_tile) * ar.world;
+          if (epi_tid < ar.world) zb_st_release_sys(ar.push_flag_peer[epi_tid] + fidx + ar.rank, epoch);
+          // 2. wait for the copies of all ranks, sum in rank order, finish, store locally
+          if (epi_tid < ar.world) {
+            if (!zb_wait_flag(ar.push_flag_peer[ar.rank] + fidx + epi_tid, epoch, abort_flag)) *abort_where = 100u + epi_tid;
+          }
+          epi_bar_sync();
+          if (*abort_flag != 0u) break;
+          const __nv_bfloat16* mine = ar.recv_peer[ar.rank] + (epoch & 1u) * half +
+                                      static_cast<size_t>(out_tile) * tile_elems + static_cast<size_t>(row_in_tile) * BN;
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 16) {
+            uint4 x[kZbMaxRanks][2];
+#pragma unroll
+            for (int src = 0; src < kZbMaxRanks; ++src) {
+              const int ss = src < ar.world ? src : 0;
+              const uint4* s4 = reinterpret_cast<const uint4*>(mine + static_cast<size_t>(ss) * num_out_tiles * tile_elems + c0);
+              x[src][0] = __ldcg(s4);
+              x[src][1] = __ldcg(s4 + 1);
+            }
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.f;
+#pragma unroll
+            for (int src = 0; src < kZbMaxRanks; ++src) {
+              if (src < ar.world) {
+                const uint32_t xx[8] = {x[src][0].x, x[src][0].y, x[src][0].z, x[src][0].w,
+                                        x[src][1].x, x[src][1].y, x[src][1].z, x[src][1].w};
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float2 f2 = zb_unpack_bf16x2(xx[j]);
+                  v[2 * j] += f2.x;
+                  v[2 * j + 1] += f2.y;
+                }
+              }
+            }
+            if (p < prm.rows_p) {
+              finish_chunk(c0, v);
+              store_chunk(c0, v, ar.out_peer[ar.rank]);
             }
           }
         }
@@ -637,10 +910,18 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (prm.cluster > 1 && !did_cluster_sync) {
+      // gave up before the exchange (a bounded wait ran out): still meet the peers at both barriers
+      __syncwarp();
+      zb_cluster_arrive();
+      zb_cluster_wait();
+      zb_cluster_arrive();
+      zb_cluster_wait();
+    }
     if (tl && epi_tid == 0) tl[6] = zb_globaltimer();
     if constexpr (FUSED) {
       // 3. the all-reduced output is complete on this rank once every tile is marked done
-      if (*abort_flag == 0u) {
+      if (*abort_flag == 0u && !(SWAP && BN <= 64 && prm.ar.one_shot != 0)) {
         for (int t = blockIdx.x * kEpiThreads + epi_tid; t < num_out_tiles; t += gridDim.x * kEpiThreads) {
           if (!zb_wait_flag(prm.ar.done_flag_peer[prm.ar.rank] + t, epoch, abort_flag)) {
             *abort_where = 200u;
@@ -733,9 +1014,68 @@ int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const cudaError_t le = zb_launch(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, dim3(grid), dim3(kNumThreads), smem, stream, tp, tq, prm);
+  const cudaError_t le = zb_launch_cluster(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, dim3(grid), dim3(kNumThreads), smem, stream,
+                                           prm.cluster, tp, tq, prm);
   zb_count_launch(1);
   return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
+}
+
+// CTAs of the swap-AB kernel that can be resident at once when launched in clusters of `s`.
+template <int BN>
+int max_cluster_ctas(int s) {
+  static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (s < 2 || s > 8) return 0;
+  if (cache[s] != 0) return cache[s] < 0 ? 0 : cache[s];
+  constexpr int smem = stages_for(BN, true) * stage_bytes(BN) + 1024 + 256;
+  if (zb_config_smem(zb_gemm_bf16_kernel<BN, true, false>, smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    cache[s] = -1;
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(s) * 64);
+  cfg.blockDim = dim3(kNumThreads);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(s);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, zb_gemm_bf16_kernel<BN, true, false>, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  cache[s] = n > 0 ? n * s : -1;
+  return n * s;
+}
+
+int g_cluster_splitk = 1;
+
+// Cluster split-K plan for a weight-streaming GEMM with fewer tiles than SMs: every tile is cut
+// along K over the CTAs of one cluster, which reduce it through distributed shared memory.
+// Returns the cluster size (1: keep the stream-K plan) and updates grid / units per CTA.
+int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* upc) {
+  if (!g_cluster_splitk || bn > 64 || tiles >= num_sms) return 1;
+  int best = 1, best_ctas = 0;
+  const int sizes[5] = {8, 6, 4, 3, 2};
+  for (int i = 0; i < 5; ++i) {
+    const int s = sizes[i];
+    if ((kb_total + s - 1) / s < 2) continue;
+    const int cap = bn <= 16 ? max_cluster_ctas<16>(s) : (bn <= 32 ? max_cluster_ctas<32>(s) : max_cluster_ctas<64>(s));
+    const int ctas = tiles * s;
+    if (ctas > cap || ctas > num_sms) continue;
+    if (ctas > best_ctas) {
+      best = s;
+      best_ctas = ctas;
+    }
+  }
+  if (best == 1 || best_ctas * 10 < num_sms * 6) return 1;     // too few SMs busy: stream-K does better
+  *grid = best_ctas;
+  *upc = (kb_total + best - 1) / best;
+  return best;
 }
 
 // Weight tiles per CTA to pull into L2 ahead of the shared-memory ring while the preceding
@@ -747,7 +1087,7 @@ int g_timeline_slots = 0;
 int g_timeline_next = 0;
 unsigned long long* next_timeline(int grid) {
   if (g_timeline == nullptr || g_timeline_slots <= 0 || grid > 160) return nullptr;
-  unsigned long long* p = g_timeline + static_cast<size_t>(g_timeline_next % g_timeline_slots) * 160 * 8;
+  unsigned long long* p = g_timeline + static_cast<size_t>(g_timeline_next % g_timeline_slots) * 160 * 12;
   ++g_timeline_next;
   return p;
 }
@@ -764,15 +1104,19 @@ int l2_prefetch_tiles(int swap, int bn, int grid, int rr_tiles) {
 extern "C" {
 
 // Profiling aid: when set, every CTA of the following GEMM launches writes globaltimer stamps to
-// buf[cta][8] = {entry, prologue done, producer past the dependency wait, first tile landed,
-// last accumulator committed, first accumulator seen by the epilogue, epilogue done, exit}.
-// `buf` holds `slots` records of 160 * 8 zeroed u64; consecutive launches take consecutive records
+// buf[cta][12] = {entry, prologue done, producer past the dependency wait, first tile landed,
+// last accumulator committed, first accumulator seen by the epilogue, epilogue done, exit,
+// cluster reduction done, partial pushed and fenced, peers' flags seen, tile stored}.
+// `buf` holds `slots` records of 160 * 12 zeroed u64; consecutive launches take consecutive records
 // (wrapping around).  Null turns it off.
 void zb_gemm_set_timeline(unsigned long long* buf, int slots) {
   g_timeline = buf;
   g_timeline_slots = slots;
   g_timeline_next = 0;
 }
+
+// Cluster split-K (see plan_cluster) on / off.
+void zb_set_cluster_splitk(int on) { g_cluster_splitk = on ? 1 : 0; }
 
 // Megabytes of weight tiles (over the whole grid) that a weight-streaming GEMM pulls into L2
 // ahead of its shared-memory ring; 0 turns the prefetch off.
@@ -846,9 +1190,12 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   if (!out_f32 && (ldo % 8) != 0) return -11;
   int sw, bn, grid, upc, rr;
   const int tiles = zb_gemm_plan(m, n, k, num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
+  int cluster = 1;
+  if (sw && rr == 0 && split_hint <= 0) cluster = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, num_sms, &grid, &upc);
   if (static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > scratch_bytes) return -13;
   if (tiles > counters_len) return -14;
   GemmParams prm;
+  prm.cluster = cluster;
   prm.rows_p = sw ? n : m;
   prm.rows_q = sw ? m : n;
   prm.k = k;
@@ -914,7 +1261,22 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   const int tiles = zb_gemm_plan(m, n, k, st->num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
   if (static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > st->gemm_scratch_bytes) return -13;
   if (tiles > st->gemm_counters_len) return -14;
+  int cluster = 1;
+  const bool one_shot_fits = sw && bn <= 64 && static_cast<long long>(tiles) * ctx->world <= ctx->max_tiles &&
+                             2 * static_cast<size_t>(ctx->world) * tiles * kBlockP * bn * 2 <= ctx->recv_bytes;
+  if (one_shot_fits && rr == 0 && split_hint <= 0) {
+    int cg = grid, cu = upc;
+    const int cs = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &cg, &cu);
+    // the tensor-parallel epilogue keeps at most 16 elements per thread
+    if (cs > 1 && bn * ((kBlockP + cs - 1) / cs) <= 16 * kEpiThreads &&
+        static_cast<long long>(tiles) * cs * ctx->world <= ctx->max_tiles) {
+      cluster = cs;
+      grid = cg;
+      upc = cu;
+    }
+  }
   GemmParams prm;
+  prm.cluster = cluster;
   prm.rows_p = sw ? n : m;
   prm.rows_q = sw ? m : n;
   prm.k = k;
@@ -936,7 +1298,14 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   ar.rank = ctx->rank;
   ar.world = ctx->world;
   ar.slots_per_src = (tiles + ctx->world - 1) / ctx->world;
-  const size_t need = static_cast<size_t>(ctx->world) * ar.slots_per_src * kBlockP * bn * 2;
+  ar.one_shot = (sw && bn <= 64) ? 1 : 0;
+  size_t need = static_cast<size_t>(ctx->world) * ar.slots_per_src * kBlockP * bn * 2;
+  if (ar.one_shot) {
+    need = 2 * static_cast<size_t>(ctx->world) * tiles * kBlockP * bn * 2;          // two halves, every source, every tile
+    if (static_cast<long long>(tiles) * ctx->world > ctx->max_tiles) ar.one_shot = 0;
+    if (need > ctx->recv_bytes) ar.one_shot = 0;
+    if (!ar.one_shot) need = static_cast<size_t>(ctx->world) * ar.slots_per_src * kBlockP * bn * 2;
+  }
   if (need > ctx->recv_bytes || tiles > ctx->max_tiles) return -51;
   for (int r = 0; r < ctx->world; ++r) {
     char* base = reinterpret_cast<char*>(ctx->heap[r]);
