@@ -7,6 +7,7 @@
     python examples/benchmark/kernels.py --op=moe --tokens=128 --experts=128 --topk=8 --n=768 --k=2048
     python examples/benchmark/kernels.py --op=gated_delta_scan --batch=32 --seqlen=1024
     python examples/benchmark/kernels.py --op=decode_layers --model=llama-3.1-8b --batch=32 --seqlen=1344
+    python examples/benchmark/kernels.py --op=gemm_chain_timeline --model=llama-3.1-8b --batch=32
 
 Every op works on inputs larger than the L2 (or rotates through several copies of its operands
 so that each launch reads cold data); `--iters` timed launches follow `--warmup` untimed ones.
@@ -229,7 +230,65 @@ def bench_decode_layers(a: Args) -> None:
     report(a, ms, wbytes + kvb, 2.0 * B * wbytes / 2, dict(row, model=a.model, batch=B, seqlen=L, weight_bytes_per_layer=wbytes, kv_bytes_per_layer=kvb))
 
 
-OPS = {"gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
+def bench_gemm_chain_timeline(a: Args) -> None:
+    """Phase stamps (globaltimer, microseconds since the first CTA's entry) of the four GEMMs of a
+    decoder layer launched back to back in a CUDA graph: do consecutive kernels overlap, and where
+    does each one spend its time?  Uses the library's GEMM timeline hook."""
+    import ctypes
+    from zml_b200.models.llama import PRESETS, LlamaConfig
+    from zml_b200.ops import _lib
+    lib = _lib.lib()
+    lib.zb_gemm_set_timeline.argtypes = [ctypes.c_void_p, ctypes.c_int]
+    c = LlamaConfig.from_hf(PRESETS[a.model])
+    h, f, qkv_n = c.hidden_size, c.intermediate_size, (c.num_attention_heads + 2 * c.num_key_value_heads) * c.hd
+    sets = [[torch.randn(n, k, device="cuda").bfloat16() * 0.02 for (n, k) in ((qkv_n, h), (h, c.num_attention_heads * c.hd), (2 * f, h), (h, f))]
+            for _ in range(3)]
+    x = torch.randn(a.batch, h, device="cuda").bfloat16()
+
+    def chain(ws):
+        xx = x
+        qkv = ops.gemm(xx, ws[0], static_w=True)
+        xx = ops.gemm(qkv[:, :c.num_attention_heads * c.hd], ws[1], residual=xx, static_w=True)
+        gu = ops.gemm(xx, ws[2], static_w=True)
+        return ops.gemm(gu[:, :f], ws[3], residual=xx, static_w=True)
+    for ws in sets:
+        chain(ws)
+    torch.cuda.synchronize()
+    slots, stride = 8, 160 * 12
+    tl = torch.zeros(slots * stride, dtype=torch.int64, device="cuda")
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        chain(sets[0])
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    lib.zb_gemm_set_timeline(tl.data_ptr(), slots)
+    with torch.cuda.graph(g):
+        chain(sets[1])
+        chain(sets[2])
+    lib.zb_gemm_set_timeline(None, 0)
+    for _ in range(2):
+        tl.zero_()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+    t = tl.view(slots, 160, 12).cpu()
+    base = t[0, :, 0][t[0, :, 0] > 0].min()
+    names = ["qkv", "o_proj", "gate_up", "down"] * 2
+    rows = []
+    for k in range(slots):
+        r = t[k]
+        live = r[:, 0] > 0
+        rel = (r[live] - base).double() / 1000.0
+        med = lambda i: round(float(rel[:, i][r[live][:, i] > 0].median()), 2)
+        rows.append({"gemm": names[k], "ctas": int(live.sum()), "entry_min": round(float(rel[:, 0].min()), 2),
+                     "entry_max": round(float(rel[:, 0].max()), 2), "dep_wait_done": med(2), "first_tile": med(3),
+                     "last_commit": med(4), "epilogue_done": med(6), "exit_max": round(float(rel[:, 7].max()), 2)})
+    print(json.dumps({"op": a.op, "model": a.model, "batch": a.batch, "unit": "us since first entry", "launches": rows}))
+
+
+OPS = {"gemm_chain_timeline": bench_gemm_chain_timeline, "gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
        "moe": bench_moe, "gated_delta_scan": bench_gated_delta_scan, "decode_layers": bench_decode_layers}
 
 

@@ -187,6 +187,18 @@ ZB_DEVICE float zb_ld_dsmem_f32(uint32_t cluster_addr) {
   return v;
 }
 
+// 8-byte "data + tag" slots for latency-bound exchanges over NVLink: an aligned 8-byte store
+// arrives whole, so a receiver that sees the expected tag also has the data - no fence, no
+// separate flag.
+ZB_DEVICE void zb_st_ll(uint2* p, uint32_t data, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(data), "r"(tag) : "memory");
+}
+ZB_DEVICE uint2 zb_ld_ll(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 // Programmatic dependent launch.  `zb_pdl_wait` blocks until every grid this one depends on has
 // finished and its writes are visible; nothing produced or still read by a preceding kernel may
 // be touched before it.  `zb_pdl_launch` lets the next kernel in the stream begin its own

@@ -431,6 +431,14 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             int offs[kE];
 #pragma unroll
             for (int b4 = 0; b4 < kE; b4 += 4) {
+              if (epi_tid + b4 * kEpiThreads >= total) {              // nothing left for this thread
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  val[b4 + i] = 0.f;
+                  offs[b4 + i] = 0;
+                }
+                continue;
+              }
               float tv[4][8];
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -450,55 +458,89 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             }
             if (tl && epi_tid == 0) tl[8] = zb_globaltimer();
             zb_cluster_arrive();                 // peers' shared memory is no longer needed; waited for below
-            const size_t tile_elems = static_cast<size_t>(kBlockP) * BN;
-            const size_t half = static_cast<size_t>(ar.world) * num_out_tiles * tile_elems;
-            const size_t base_off = (epoch & 1u) * half + static_cast<size_t>(out_tile) * tile_elems;
-            const size_t src_stride = static_cast<size_t>(num_out_tiles) * tile_elems;
-            for (int d = 0; d < ar.world; ++d) {
-              __nv_bfloat16* dst = ar.recv_peer[d] + base_off + static_cast<size_t>(ar.rank) * src_stride;
+            // Exchange in 8-byte {two bf16 values, epoch} slots, indexed by thread on both sides (the
+            // peer's thread with this index holds the same elements): no fence, no flags.
+            const int n_el = (total - epi_tid + kEpiThreads - 1) / kEpiThreads;      // this thread's elements
+            const int n_pair = (min(n_el, kE) + 1) / 2;
+            const size_t per_band = static_cast<size_t>(kE / 2) * kEpiThreads;       // uint2 slots per (src, tile, band)
+            const size_t band_idx = static_cast<size_t>(out_tile) * S + rank;
+            const size_t src_stride = static_cast<size_t>(num_out_tiles) * S * per_band;
+            const size_t half = static_cast<size_t>(ar.world) * src_stride;
+            const size_t my_slot = (epoch & 1u) * half + band_idx * per_band + epi_tid;
+            uint32_t mine_w[kE / 2];
 #pragma unroll
-              for (int i = 0; i < kE; ++i)
-                if (epi_tid + i * kEpiThreads < total) dst[offs[i]] = __float2bfloat16(val[i]);
+            for (int j = 0; j < kE / 2; ++j) mine_w[j] = zb_pack_bf16x2(val[2 * j], (2 * j + 1) < n_el ? val[2 * j + 1] : 0.f);
+            for (int d = 0; d < ar.world; ++d) {
+              if (d == ar.rank) continue;
+              uint2* dst = reinterpret_cast<uint2*>(ar.recv_peer[d]) + my_slot + static_cast<size_t>(ar.rank) * src_stride;
+#pragma unroll
+              for (int j = 0; j < kE / 2; ++j)
+                if (j < n_pair) zb_st_ll(dst + static_cast<size_t>(j) * kEpiThreads, mine_w[j], epoch);
             }
-            __threadfence_system();
             if (tl && epi_tid == 0) tl[9] = zb_globaltimer();
-            epi_bar_sync();
-            const size_t fidx = (static_cast<size_t>(out_tile) * S + rank) * ar.world;
-            if (epi_tid < ar.world) zb_st_release_sys(ar.push_flag_peer[epi_tid] + fidx + ar.rank, epoch);
-            if (epi_tid < ar.world) {
-              if (!zb_wait_flag(ar.push_flag_peer[ar.rank] + fidx + epi_tid, epoch, abort_flag)) *abort_where = 100u + epi_tid;
+            // bias / residual loads go out while the peers' slots are in flight
+            float add[kE];
+#pragma unroll
+            for (int i = 0; i < kE; ++i) {
+              add[i] = 0.f;
+              if (i < n_el) {
+                const int o_t = offs[i];
+                const int col = o_t / kBlockP, row = o_t - col * kBlockP;
+                const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
+                if (prm.residual) add[i] = __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]);
+                if (prm.bias) add[i] += __bfloat162float(prm.bias[pp]);
+              }
             }
-            epi_bar_sync();
+            float sum[kE];
+#pragma unroll
+            for (int i = 0; i < kE; ++i) sum[i] = 0.f;
+            const uint2* slots = reinterpret_cast<const uint2*>(ar.recv_peer[ar.rank]) + my_slot;
+            const uint64_t t_wait0 = zb_globaltimer();
+            for (int src = 0; src < ar.world; ++src) {              // ascending rank: the same bits everywhere
+              uint32_t w[kE / 2];
+              if (src == ar.rank) {
+#pragma unroll
+                for (int j = 0; j < kE / 2; ++j) w[j] = mine_w[j];
+              } else {
+                const uint2* sp = slots + static_cast<size_t>(src) * src_stride;
+                bool ready = false;
+                uint32_t spins = 0;
+                while (!ready) {
+                  ready = true;
+#pragma unroll
+                  for (int j = 0; j < kE / 2; ++j) {
+                    if (j < n_pair) {
+                      const uint2 x = zb_ld_ll(sp + static_cast<size_t>(j) * kEpiThreads);
+                      w[j] = x.x;
+                      ready = ready && (x.y == epoch);
+                    }
+                  }
+                  if (!ready && (++spins & 0x3f) == 0) {
+                    if (*abort_flag != 0u || zb_globaltimer() - t_wait0 > ZB_WAIT_LIMIT_NS) {
+                      *abort_flag = 1u;
+                      *abort_where = 100u + src;
+                      break;
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < kE / 2; ++j) {
+                const float2 f2 = zb_unpack_bf16x2(w[j]);
+                sum[2 * j] += f2.x;
+                sum[2 * j + 1] += f2.y;
+              }
+            }
             if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
             if (*abort_flag == 0u) {
-              const __nv_bfloat16* mine = ar.recv_peer[ar.rank] + base_off;
 #pragma unroll
-              for (int b4 = 0; b4 < kE; b4 += 4) {
-                __nv_bfloat16 xv[4][kZbMaxRanks];
-                float rsd[4], bs[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int o_t = offs[b4 + i];
-#pragma unroll
-                  for (int src = 0; src < kZbMaxRanks; ++src)
-                    xv[i][src] = mine[static_cast<size_t>(src < ar.world ? src : 0) * src_stride + o_t];
-                  const int col = o_t / kBlockP, row = o_t - col * kBlockP;
-                  const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
-                  rsd[i] = prm.residual ? __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]) : 0.f;
-                  bs[i] = prm.bias ? __bfloat162float(prm.bias[pp]) : 0.f;
-                }
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  if (epi_tid + (b4 + i) * kEpiThreads >= total) continue;
-                  float v = 0.f;
-#pragma unroll
-                  for (int src = 0; src < kZbMaxRanks; ++src)
-                    if (src < ar.world) v += __bfloat162float(xv[i][src]);
-                  const int o_t = offs[b4 + i];
+              for (int i = 0; i < kE; ++i) {
+                if (i < n_el) {
+                  const int o_t = offs[i];
                   const int col = o_t / kBlockP, row = o_t - col * kBlockP;
                   const int pp = pt * kBlockP + row, qq = q0 + col;
                   if (pp < prm.rows_p && qq < prm.rows_q)
-                    ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = __float2bfloat16(v + bs[i] + rsd[i]);
+                    ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = __float2bfloat16(sum[i] + add[i]);
                 }
               }
             }
@@ -1269,7 +1311,7 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
     const int cs = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &cg, &cu);
     // the tensor-parallel epilogue keeps at most 16 elements per thread
     if (cs > 1 && bn * ((kBlockP + cs - 1) / cs) <= 16 * kEpiThreads &&
-        static_cast<long long>(tiles) * cs * ctx->world <= ctx->max_tiles) {
+        2 * static_cast<size_t>(ctx->world) * tiles * cs * 8 * kEpiThreads * sizeof(uint2) <= ctx->recv_bytes) {
       cluster = cs;
       grid = cg;
       upc = cu;
