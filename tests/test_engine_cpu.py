@@ -108,3 +108,19 @@ def test_moe_model_generates_and_matches_dense_expert_math():
         m2 = Qwen3MoeModel(cfg, device="cpu", dtype=torch.float32).load(TensorStore.from_path(d))
         outs2, _ = Engine(m2, num_pages=32, page_size=16, max_batch=2, max_seq_len=128).generate([[3, 4, 5, 6, 7], list(range(20, 60))], 5)
         assert outs2 == outs
+
+
+def test_moe_nvfp4_expert_weights_are_representable():
+    """`expert_dtype="nvfp4"` holds expert weights at values an NVFP4 checkpoint can store."""
+    from zml_b200 import moe
+    from zml_b200.models.qwen3_moe import PRESETS as MOE_PRESETS, Qwen3MoeConfig, Qwen3MoeModel
+    w = torch.randn(2, 32, 64).bfloat16() * 0.02
+    r = moe.nvfp4_roundtrip(w)
+    assert ((r.float() - w.float()).norm() / w.float().norm()).item() < 0.15
+    again = moe.nvfp4_roundtrip(r)
+    assert ((again.float() - r.float()).norm() / r.float().norm()).item() < 0.02      # (nearly) a fixed point
+    cfg = Qwen3MoeConfig.from_hf(dict(MOE_PRESETS["tiny-moe-test"], expert_dtype="nvfp4"))
+    m = Qwen3MoeModel(cfg, device="cpu").init_random(0)
+    eng = Engine(m, num_pages=16, page_size=16, max_batch=2, max_seq_len=64)
+    out, _ = eng.generate([[5, 6, 7, 8]], 4)
+    assert len(out[0]) == 4

@@ -423,127 +423,144 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
             zb_cluster_wait();
           } else {
             // Tensor-parallel variant: the band this CTA reduced over the cluster is this rank's
-            // partial; it goes to every rank in one hop, and the band is finished from the copies
-            // of all ranks (fused_ar.h, one_shot).  Up to 16 elements per thread.
+            // partial; it goes to every rank in one hop, in 8-byte {two bf16 values, epoch} slots
+            // indexed by thread on both sides (the peer's thread with this index holds the same
+            // elements) - no fence, no flags - and the band is finished from the copies of all ranks
+            // (fused_ar.h, one_shot).  A thread holds up to 32 elements, handled as two halves of 16.
             const ZbFusedAr& ar = prm.ar;
-            constexpr int kE = 16;
-            float val[kE];
-            int offs[kE];
+            constexpr int kE = 16, kHalves = 2;
+            const int n_el = (total - epi_tid + kEpiThreads - 1) / kEpiThreads;      // this thread's elements
+            const size_t per_band = static_cast<size_t>(kHalves) * (kE / 2) * kEpiThreads;   // uint2 slots per (src, tile, band)
+            const size_t band_idx = static_cast<size_t>(out_tile) * S + rank;
+            const size_t src_stride = static_cast<size_t>(num_out_tiles) * S * per_band;
+            const size_t half_sz = static_cast<size_t>(ar.world) * src_stride;
+            const size_t my_slot = (epoch & 1u) * half_sz + band_idx * per_band + epi_tid;
+            auto elem_off = [&](int i) {                  // element i of this thread -> offset in a [BN][128] tile
+              const int e = min(epi_tid + i * kEpiThreads, total - 1);
+              const int col = e / nrows;
+              return col * kBlockP + rb0 + (e - col * nrows);
+            };
+            uint32_t mine_w[kHalves][kE / 2];
 #pragma unroll
-            for (int b4 = 0; b4 < kE; b4 += 4) {
-              if (epi_tid + b4 * kEpiThreads >= total) {              // nothing left for this thread
+            for (int hf = 0; hf < kHalves; ++hf) {
+              const int i0 = hf * kE;
+              if (i0 >= n_el) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  val[b4 + i] = 0.f;
-                  offs[b4 + i] = 0;
-                }
+                for (int j = 0; j < kE / 2; ++j) mine_w[hf][j] = 0u;
                 continue;
               }
-              float tv[4][8];
+              float val[kE];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int e = min(epi_tid + (b4 + i) * kEpiThreads, total - 1);
-                const int col = e / nrows, row = rb0 + (e - col * nrows);
-                offs[b4 + i] = col * kBlockP + row;
+              for (int b4 = 0; b4 < kE; b4 += 4) {
+                if (i0 + b4 >= n_el) {
 #pragma unroll
-                for (int c = 0; c < 8; ++c) tv[i][c] = c < S ? zb_ld_dsmem_f32(peer_base[c] + offs[b4 + i] * 4) : 0.f;
+                  for (int i = 0; i < 4; ++i) val[b4 + i] = 0.f;
+                  continue;
+                }
+                float tv[4][8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int o_t = elem_off(i0 + b4 + i);
+#pragma unroll
+                  for (int c = 0; c < 8; ++c) tv[i][c] = c < S ? zb_ld_dsmem_f32(peer_base[c] + o_t * 4) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  float v = 0.f;
+#pragma unroll
+                  for (int c = 0; c < 8; ++c) v += tv[i][c];
+                  val[b4 + i] = (i0 + b4 + i) < n_el ? v : 0.f;
+                }
               }
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                float v = 0.f;
+              for (int j = 0; j < kE / 2; ++j) mine_w[hf][j] = zb_pack_bf16x2(val[2 * j], val[2 * j + 1]);
+              const int n_pair = (min(n_el - i0, kE) + 1) / 2;
+              for (int d = 0; d < ar.world; ++d) {
+                if (d == ar.rank) continue;
+                uint2* dst = reinterpret_cast<uint2*>(ar.recv_peer[d]) + my_slot + static_cast<size_t>(ar.rank) * src_stride +
+                             static_cast<size_t>(hf) * (kE / 2) * kEpiThreads;
 #pragma unroll
-                for (int c = 0; c < 8; ++c) v += tv[i][c];
-                val[b4 + i] = v;
+                for (int j = 0; j < kE / 2; ++j)
+                  if (j < n_pair) zb_st_ll(dst + static_cast<size_t>(j) * kEpiThreads, mine_w[hf][j], epoch);
               }
             }
             if (tl && epi_tid == 0) tl[8] = zb_globaltimer();
             zb_cluster_arrive();                 // peers' shared memory is no longer needed; waited for below
-            // Exchange in 8-byte {two bf16 values, epoch} slots, indexed by thread on both sides (the
-            // peer's thread with this index holds the same elements): no fence, no flags.
-            const int n_el = (total - epi_tid + kEpiThreads - 1) / kEpiThreads;      // this thread's elements
-            const int n_pair = (min(n_el, kE) + 1) / 2;
-            const size_t per_band = static_cast<size_t>(kE / 2) * kEpiThreads;       // uint2 slots per (src, tile, band)
-            const size_t band_idx = static_cast<size_t>(out_tile) * S + rank;
-            const size_t src_stride = static_cast<size_t>(num_out_tiles) * S * per_band;
-            const size_t half = static_cast<size_t>(ar.world) * src_stride;
-            const size_t my_slot = (epoch & 1u) * half + band_idx * per_band + epi_tid;
-            uint32_t mine_w[kE / 2];
-#pragma unroll
-            for (int j = 0; j < kE / 2; ++j) mine_w[j] = zb_pack_bf16x2(val[2 * j], (2 * j + 1) < n_el ? val[2 * j + 1] : 0.f);
-            for (int d = 0; d < ar.world; ++d) {
-              if (d == ar.rank) continue;
-              uint2* dst = reinterpret_cast<uint2*>(ar.recv_peer[d]) + my_slot + static_cast<size_t>(ar.rank) * src_stride;
-#pragma unroll
-              for (int j = 0; j < kE / 2; ++j)
-                if (j < n_pair) zb_st_ll(dst + static_cast<size_t>(j) * kEpiThreads, mine_w[j], epoch);
-            }
             if (tl && epi_tid == 0) tl[9] = zb_globaltimer();
-            // bias / residual loads go out while the peers' slots are in flight
-            float add[kE];
-#pragma unroll
-            for (int i = 0; i < kE; ++i) {
-              add[i] = 0.f;
-              if (i < n_el) {
-                const int o_t = offs[i];
-                const int col = o_t / kBlockP, row = o_t - col * kBlockP;
-                const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
-                if (prm.residual) add[i] = __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]);
-                if (prm.bias) add[i] += __bfloat162float(prm.bias[pp]);
-              }
-            }
-            float sum[kE];
-#pragma unroll
-            for (int i = 0; i < kE; ++i) sum[i] = 0.f;
             const uint2* slots = reinterpret_cast<const uint2*>(ar.recv_peer[ar.rank]) + my_slot;
             const uint64_t t_wait0 = zb_globaltimer();
-            for (int src = 0; src < ar.world; ++src) {              // ascending rank: the same bits everywhere
-              uint32_t w[kE / 2];
-              if (src == ar.rank) {
 #pragma unroll
-                for (int j = 0; j < kE / 2; ++j) w[j] = mine_w[j];
-              } else {
-                const uint2* sp = slots + static_cast<size_t>(src) * src_stride;
-                bool ready = false;
-                uint32_t spins = 0;
-                while (!ready) {
-                  ready = true;
+            for (int hf = 0; hf < kHalves; ++hf) {
+              const int i0 = hf * kE;
+              if (i0 >= n_el || *abort_flag != 0u) continue;
+              const int n_here = min(n_el - i0, kE);
+              const int n_pair = (n_here + 1) / 2;
+              // bias / residual loads go out while the peers' slots are in flight
+              float add[kE];
 #pragma unroll
-                  for (int j = 0; j < kE / 2; ++j) {
-                    if (j < n_pair) {
-                      const uint2 x = zb_ld_ll(sp + static_cast<size_t>(j) * kEpiThreads);
-                      w[j] = x.x;
-                      ready = ready && (x.y == epoch);
+              for (int i = 0; i < kE; ++i) {
+                add[i] = 0.f;
+                if (i < n_here) {
+                  const int o_t = elem_off(i0 + i);
+                  const int col = o_t / kBlockP, row = o_t - col * kBlockP;
+                  const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
+                  if (prm.residual) add[i] = __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]);
+                  if (prm.bias) add[i] += __bfloat162float(prm.bias[pp]);
+                }
+              }
+              float sum[kE];
+#pragma unroll
+              for (int i = 0; i < kE; ++i) sum[i] = 0.f;
+              for (int src = 0; src < ar.world; ++src) {              // ascending rank: the same bits everywhere
+                uint32_t w[kE / 2];
+                if (src == ar.rank) {
+#pragma unroll
+                  for (int j = 0; j < kE / 2; ++j) w[j] = mine_w[hf][j];
+                } else {
+                  const uint2* sp = slots + static_cast<size_t>(src) * src_stride + static_cast<size_t>(hf) * (kE / 2) * kEpiThreads;
+                  bool ready = false;
+                  uint32_t spins = 0;
+                  while (!ready) {
+                    ready = true;
+#pragma unroll
+                    for (int j = 0; j < kE / 2; ++j) {
+                      w[j] = 0u;
+                      if (j < n_pair) {
+                        const uint2 x = zb_ld_ll(sp + static_cast<size_t>(j) * kEpiThreads);
+                        w[j] = x.x;
+                        ready = ready && (x.y == epoch);
+                      }
                     }
-                  }
-                  if (!ready && (++spins & 0x3f) == 0) {
-                    if (*abort_flag != 0u || zb_globaltimer() - t_wait0 > ZB_WAIT_LIMIT_NS) {
-                      *abort_flag = 1u;
-                      *abort_where = 100u + src;
-                      break;
+                    if (!ready && (++spins & 0x3f) == 0) {
+                      if (*abort_flag != 0u || zb_globaltimer() - t_wait0 > ZB_WAIT_LIMIT_NS) {
+                        *abort_flag = 1u;
+                        *abort_where = 100u + src;
+                        break;
+                      }
                     }
                   }
                 }
-              }
 #pragma unroll
-              for (int j = 0; j < kE / 2; ++j) {
-                const float2 f2 = zb_unpack_bf16x2(w[j]);
-                sum[2 * j] += f2.x;
-                sum[2 * j + 1] += f2.y;
+                for (int j = 0; j < kE / 2; ++j) {
+                  const float2 f2 = zb_unpack_bf16x2(w[j]);
+                  sum[2 * j] += f2.x;
+                  sum[2 * j + 1] += f2.y;
+                }
+              }
+              if (*abort_flag == 0u) {
+#pragma unroll
+                for (int i = 0; i < kE; ++i) {
+                  if (i < n_here) {
+                    const int o_t = elem_off(i0 + i);
+                    const int col = o_t / kBlockP, row = o_t - col * kBlockP;
+                    const int pp = pt * kBlockP + row, qq = q0 + col;
+                    if (pp < prm.rows_p && qq < prm.rows_q)
+                      ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = __float2bfloat16(sum[i] + add[i]);
+                  }
+                }
               }
             }
             if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
-            if (*abort_flag == 0u) {
-#pragma unroll
-              for (int i = 0; i < kE; ++i) {
-                if (i < n_el) {
-                  const int o_t = offs[i];
-                  const int col = o_t / kBlockP, row = o_t - col * kBlockP;
-                  const int pp = pt * kBlockP + row, qq = q0 + col;
-                  if (pp < prm.rows_p && qq < prm.rows_q)
-                    ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = __float2bfloat16(sum[i] + add[i]);
-                }
-              }
-            }
             if (tl && epi_tid == 0) tl[11] = zb_globaltimer();
             zb_cluster_wait();
             if (*abort_flag != 0u) break;
@@ -1114,7 +1131,7 @@ int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* u
       best_ctas = ctas;
     }
   }
-  if (best == 1 || best_ctas * 10 < num_sms * 6) return 1;     // too few SMs busy: stream-K does better
+  if (best == 1 || best_ctas * 2 < num_sms) return 1;     // under half of the SMs busy: stream-K does better
   *grid = best_ctas;
   *upc = (kb_total + best - 1) / best;
   return best;
@@ -1309,9 +1326,9 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   if (one_shot_fits && rr == 0 && split_hint <= 0) {
     int cg = grid, cu = upc;
     const int cs = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &cg, &cu);
-    // the tensor-parallel epilogue keeps at most 16 elements per thread
-    if (cs > 1 && bn * ((kBlockP + cs - 1) / cs) <= 16 * kEpiThreads &&
-        2 * static_cast<size_t>(ctx->world) * tiles * cs * 8 * kEpiThreads * sizeof(uint2) <= ctx->recv_bytes) {
+    // the tensor-parallel epilogue keeps at most 32 elements per thread (two halves of 16)
+    if (cs > 1 && bn * ((kBlockP + cs - 1) / cs) <= 32 * kEpiThreads &&
+        2 * static_cast<size_t>(ctx->world) * tiles * cs * 16 * kEpiThreads * sizeof(uint2) <= ctx->recv_bytes) {
       cluster = cs;
       grid = cg;
       upc = cu;

@@ -101,6 +101,8 @@ class Qwen3MoeModel(LlamaModel):
             gate = rw((c.num_experts, f, d), b + 4, rows=erng)
             up = rw((c.num_experts, f, d), b + 5, rows=erng)
             down = rw((c.num_experts, d, f), b + 6, rows=erng)
+            if c.expert_dtype == "nvfp4":
+                gate, up, down = moe.nvfp4_roundtrip(gate), moe.nvfp4_roundtrip(up), moe.nvfp4_roundtrip(down)
             lw.extra = {"router": rw((c.num_experts, d), b + 7), "gate_up": moe.interleave_gate_up(gate, up), "down": down}
             del gate, up
             self.layers.append(lw)

@@ -11,4 +11,5 @@ and SwiGLU are one grouped tcgen05 GEMM, and the cross-rank sum is done from ins
 kernel over NVLink peer memory when symmetric memory is set up.
 """
 from .ops import (Backend, deinterleave_gate_up, finalize, forward_moe, fused_experts, gather, grouped_gemm, interleave_gate_up,  # noqa: F401
+                  nvfp4_roundtrip,
                   moe_align, reference_fused_experts, router_topk)

@@ -98,6 +98,19 @@ def gather(x: torch.Tensor, sorted_pair: torch.Tensor, meta: torch.Tensor, e_loc
     return xs
 
 
+def nvfp4_roundtrip(w: torch.Tensor) -> torch.Tensor:
+    """Quantises expert weights [..., N, K] to NVFP4 (e2m1 values, one f8e4m3fn scale per 16, one
+    fp32 scale per matrix) and returns them de-quantised to the input dtype: the values an NVFP4
+    checkpoint holds, in the layout the bf16 grouped GEMM consumes."""
+    from ..nn import quant as Q
+    out = torch.empty_like(w)
+    flat_in, flat_out = w.reshape(-1, w.shape[-2], w.shape[-1]), out.reshape(-1, w.shape[-2], w.shape[-1])
+    for e in range(flat_in.shape[0]):                      # one matrix at a time bounds the fp32 temporaries
+        packed, scales, gs = Q.quantize_weight_nvfp4(flat_in[e])
+        flat_out[e] = Q.dequantize_nvfp4(Q.unpack_e2m1(packed), scales, gs, w.dtype)
+    return out
+
+
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """[E, F, D] x 2 -> [E, 2F, D] with rows laid out [64 gate | 64 up] per 128-row block, the
     layout the grouped GEMM's SwiGLU epilogue expects (F must be a multiple of 64)."""
