@@ -257,6 +257,13 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
   for (int blk = blk0 + warp; blk < blk1; blk += 4) {
     cp_async_wait<kDecStages - 2>();
     __syncwarp();
+    // refill the stage consumed in the previous iteration BEFORE computing on this one, so that
+    // the loads of two blocks are in flight while the tensor cores work (the kernel is bound by
+    // memory latency: 8 warps per SM, each waiting on its own copies)
+    int fill = stage + kDecStages - 1;
+    if (fill >= kDecStages) fill -= kDecStages;
+    issue(nxt, fill);
+    nxt += 4;
     const uint32_t ks = wbase + stage * 2 * kBlkBytes;
     const int tok0 = blk << 4;
     attn_block16<HD>(qf, ks, ks + kBlkBytes, 0, o, m, l, p.scale_log2,
@@ -265,11 +272,6 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
                        return kidx < len && kidx >= first_visible;
                      });
     __syncwarp();
-    // refill the stage consumed in the previous iteration
-    int fill = stage + kDecStages - 1;
-    if (fill >= kDecStages) fill -= kDecStages;
-    issue(nxt, fill);
-    nxt += 4;
     if (++stage == kDecStages) stage = 0;
   }
   cp_async_wait<0>();
