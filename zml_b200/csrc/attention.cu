@@ -16,8 +16,12 @@
 // whatever the mix of sequence lengths.  Partial results (unnormalised O, running
 // max m, running sum l) go to scratch and the last chunk of a (sequence, kv head)
 // to finish merges them in chunk order, in the same launch.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "host_api.h"
+
+int zb_make_tmap_kv_cache(CUtensorMap* out, const void* base, long long slots, int kv_heads, int head_dim, int box_rows);
 
 namespace {
 
@@ -60,6 +64,18 @@ ZB_DEVICE uint32_t tile_off(int row, int chunk) {
   return static_cast<uint32_t>(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
+// Same for a tile written by a tensor-map copy with the 128-byte swizzle: HD / 64 sub-tiles of
+// [64 rows][64 columns], each row 128 bytes, 16-byte chunks XOR-ed with the row inside its sub-tile.
+template <int HD>
+ZB_DEVICE uint32_t tile_off_tma(int row, int chunk) {
+  return static_cast<uint32_t>((chunk >> 3) * (64 * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+template <int HD, int LAYOUT>
+ZB_DEVICE uint32_t tile_off_l(int row, int chunk) {
+  if constexpr (LAYOUT == 0) return tile_off<HD>(row, chunk);
+  else return tile_off_tma<HD>(row, chunk);
+}
+
 struct AttnParams {
   const __nv_bfloat16* q;       // [tokens, num_q_heads, HD] with token stride q_stride
   const __nv_bfloat16* k_cache; // [pages, page_size, num_kv_heads, HD]
@@ -90,7 +106,7 @@ struct AttnParams {
 //   k_base : shared address of the 16 K rows of this block (tile-relative row0)
 //   row0   : first row of the block inside its swizzled tile
 //   mask0/mask1 : per-row predicate producers are inlined by the callers via `visible`
-template <int HD, typename Visible>
+template <int HD, int LAYOUT = 0, typename Visible>
 ZB_DEVICE void attn_block16(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile,
                             int row0, float (&o)[HD / 8][4], float (&m)[2], float (&l)[2],
                             float scale_log2, Visible visible) {
@@ -102,7 +118,7 @@ ZB_DEVICE void attn_block16(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, u
   for (int kk = 0; kk < HD / 16; ++kk) {
     uint32_t b[4];
     const int krow = row0 + (mi >> 1) * 8 + r8;
-    ldmatrix_x4(b, k_tile + tile_off<HD>(krow, 2 * kk + (mi & 1)));
+    ldmatrix_x4(b, k_tile + tile_off_l<HD, LAYOUT>(krow, 2 * kk + (mi & 1)));
     mma_bf16(s[0], qf[kk], b[0], b[1]);
     mma_bf16(s[1], qf[kk], b[2], b[3]);
   }
@@ -160,7 +176,7 @@ ZB_DEVICE void attn_block16(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, u
   for (int c = 0; c < HD / 8; c += 2) {
     uint32_t b[4];
     const int vrow = row0 + (mi & 1) * 8 + r8;
-    ldmatrix_x4_trans(b, v_tile + tile_off<HD>(vrow, c + (mi >> 1)));
+    ldmatrix_x4_trans(b, v_tile + tile_off_l<HD, LAYOUT>(vrow, c + (mi >> 1)));
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       o[c][j] *= corr[j >> 1];
@@ -168,6 +184,115 @@ ZB_DEVICE void attn_block16(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, u
     }
     mma_bf16(o[c], pa, b[0], b[1]);
     mma_bf16(o[c + 1], pa, b[2], b[3]);
+  }
+}
+
+// Tail shared by the decode kernels: merges the four consumer warps of the CTA through shared
+// memory, writes the chunk's partial (or the final output when the sequence has one chunk), and
+// lets the last chunk of a (sequence, kv head) to finish merge all of them.  Every thread of the
+// CTA calls it (warps beyond the fourth only take part in the barriers and the element loops).
+template <int HD>
+ZB_DEVICE void decode_tail(const AttnParams& p, uint8_t* smem, const float (&o)[HD / 8][4], const float (&m)[2],
+                           const float (&l)[2], int seq, int kvh, int split, int my_splits, int group) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // merge the four warps through shared memory (pipeline buffers are free now)
+  float* sm_o = reinterpret_cast<float*>(smem);                 // [4][16][HD]
+  float* sm_ml = sm_o + 4 * 16 * HD;                            // [4][16][2]
+  if (warp < 4) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+      const int c = nt * 8 + 2 * t;
+      float* r0 = sm_o + (warp * 16 + g) * HD + c;
+      float* r1 = sm_o + (warp * 16 + g + 8) * HD + c;
+      r0[0] = o[nt][0];
+      r0[1] = o[nt][1];
+      r1[0] = o[nt][2];
+      r1[1] = o[nt][3];
+    }
+    if (t == 0) {
+      sm_ml[(warp * 16 + g) * 2 + 0] = m[0];
+      sm_ml[(warp * 16 + g) * 2 + 1] = l[0];
+      sm_ml[(warp * 16 + g + 8) * 2 + 0] = m[1];
+      sm_ml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+    const int r = idx / HD, c = idx % HD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + r) * 2]);
+    const float muse = (mm == -INFINITY) ? 0.f : mm;
+    float acc = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(sm_ml[(w * 16 + r) * 2] - muse);
+      acc += f * sm_o[(w * 16 + r) * HD + c];
+      ll += f * sm_ml[(w * 16 + r) * 2 + 1];
+    }
+    const int head = kvh * group + r;
+    if (my_splits == 1) {
+      const float inv = ll > 0.f ? 1.f / ll : 0.f;
+      p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(acc * inv);
+    } else {
+      const size_t pi = (static_cast<size_t>(seq) * p.num_q_heads + head) * p.num_splits + split;
+      p.part_o[pi * HD + c] = acc;
+      if (c == 0) {
+        p.part_ml[pi * 2] = mm;
+        p.part_ml[pi * 2 + 1] = ll;
+      }
+    }
+  }
+  if (my_splits == 1) return;
+  // the last chunk to finish merges all chunks of this (sequence, kv head)
+  __shared__ uint32_t s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(&p.counters[blockIdx.x], 1u);
+    s_last = (prev == static_cast<uint32_t>(my_splits - 1)) ? 1u : 0u;
+    if (s_last) p.counters[blockIdx.x] = 0u;
+  }
+  __syncthreads();
+  if (s_last == 0u) return;
+  __threadfence();
+  // Phase 1: (max, sum) of every (row, chunk) -> shared memory, one round trip to L2.
+  // Phase 2: every thread combines its output elements with the chunk loads of an element
+  // batched eight at a time, so that the merge costs a few round trips, not one per chunk.
+  float* s_m = reinterpret_cast<float*>(smem);          // [group][my_splits]
+  float* s_l = s_m + 16 * 64;                           // [group][my_splits] (at most 16 rows x 64 chunks)
+  const int nsp = min(my_splits, 64);
+  for (int i = threadIdx.x; i < group * nsp; i += blockDim.x) {
+    const int r = i / nsp, sp = i - r * nsp;
+    const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + kvh * group + r) * p.num_splits;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&p.part_ml[(base + sp) * 2]));
+    s_m[r * 64 + sp] = ml.x;
+    s_l[r * 64 + sp] = ml.y;
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+    const int r = idx / HD, c = idx % HD;
+    const int head = kvh * group + r;
+    const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + head) * p.num_splits;
+    float mm = -INFINITY;
+    for (int sp = 0; sp < nsp; ++sp) mm = fmaxf(mm, s_m[r * 64 + sp]);
+    const float muse = (mm == -INFINITY) ? 0.f : mm;
+    float acc = 0.f, ll = 0.f;
+    for (int sp0 = 0; sp0 < nsp; sp0 += 8) {
+      float pv[8];
+#pragma unroll
+      for (int b = 0; b < 8; ++b) pv[b] = __ldcg(&p.part_o[(base + min(sp0 + b, nsp - 1)) * HD + c]);
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        if (sp0 + b < nsp) {
+          const float f = exp2f(s_m[r * 64 + sp0 + b] - muse);
+          acc += f * pv[b];
+          ll += f * s_l[r * 64 + sp0 + b];
+        }
+      }
+    }
+    p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
   }
 }
 
@@ -276,106 +401,136 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
   }
   cp_async_wait<0>();
   __syncthreads();
+  decode_tail<HD>(p, smem, o, m, l, seq, kvh, split, my_splits, group);
+}
 
-  // merge the four warps through shared memory (pipeline buffers are free now)
-  float* sm_o = reinterpret_cast<float*>(smem);                 // [4][16][HD]
-  float* sm_ml = sm_o + 4 * 16 * HD;                            // [4][16][2]
-  {
-    const int g = lane >> 2, t = lane & 3;
-#pragma unroll
-    for (int nt = 0; nt < HD / 8; ++nt) {
-      const int c = nt * 8 + 2 * t;
-      float* r0 = sm_o + (warp * 16 + g) * HD + c;
-      float* r1 = sm_o + (warp * 16 + g + 8) * HD + c;
-      r0[0] = o[nt][0];
-      r0[1] = o[nt][1];
-      r1[0] = o[nt][2];
-      r1[1] = o[nt][3];
-    }
-    if (t == 0) {
-      sm_ml[(warp * 16 + g) * 2 + 0] = m[0];
-      sm_ml[(warp * 16 + g) * 2 + 1] = l[0];
-      sm_ml[(warp * 16 + g + 8) * 2 + 0] = m[1];
-      sm_ml[(warp * 16 + g + 8) * 2 + 1] = l[1];
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
-    const int r = idx / HD, c = idx % HD;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sm_ml[(w * 16 + r) * 2]);
-    const float muse = (mm == -INFINITY) ? 0.f : mm;
-    float acc = 0.f, ll = 0.f;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float f = exp2f(sm_ml[(w * 16 + r) * 2] - muse);
-      acc += f * sm_o[(w * 16 + r) * HD + c];
-      ll += f * sm_ml[(w * 16 + r) * 2 + 1];
-    }
-    const int head = kvh * group + r;
-    if (my_splits == 1) {
-      const float inv = ll > 0.f ? 1.f / ll : 0.f;
-      p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(acc * inv);
-    } else {
-      const size_t pi = (static_cast<size_t>(seq) * p.num_q_heads + head) * p.num_splits + split;
-      p.part_o[pi * HD + c] = acc;
-      if (c == 0) {
-        p.part_ml[pi * 2] = mm;
-        p.part_ml[pi * 2 + 1] = ll;
-      }
-    }
-  }
-  if (my_splits == 1) return;
-  // the last chunk to finish merges all chunks of this (sequence, kv head)
-  __shared__ uint32_t s_last;
-  __threadfence();
-  __syncthreads();
+// ------------------------------------------------------- decode, tensor-map fed
+// Same math as zb_paged_decode_kernel with the K/V pages brought in by a producer warp through
+// tensor-map copies (one 64-key page of one head per copy, 128-byte swizzle) into a ring of
+// stages; the four consumer warps each own 16 of the 64 keys of a tile and never wait on their
+// own copies.  Needs 64-token pages and KV chunks that are multiples of 64 keys.
+template <int HD>
+constexpr int dec_tma_stages() { return HD >= 256 ? 2 : 3; }
+
+template <int HD>
+__global__ void __launch_bounds__(160) zb_paged_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_k,
+                                                                  const __grid_constant__ CUtensorMap tmap_v,
+                                                                  const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  constexpr int kStages = dec_tma_stages<HD>();
+  constexpr int kTileBytes = 64 * HD * 2;                 // one page of K (or V) of one head
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * 2 * kTileBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty_bar + kStages);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
-    const uint32_t prev = atomicAdd(&p.counters[blockIdx.x], 1u);
-    s_last = (prev == static_cast<uint32_t>(my_splits - 1)) ? 1u : 0u;
-    if (s_last) p.counters[blockIdx.x] = 0u;
+    for (int s = 0; s < kStages; ++s) {
+      zb_mbar_init(&full_bar[s], 1);
+      zb_mbar_init(&empty_bar[s], 4);
+    }
+    *abort_flag = 0u;
+    zb_mbar_fence_init();
+    zb_tma_prefetch_desc(&tmap_k);
+    zb_tma_prefetch_desc(&tmap_v);
   }
   __syncthreads();
-  if (s_last == 0u) return;
-  __threadfence();
-  // Phase 1: (max, sum) of every (row, chunk) -> shared memory, one round trip to L2.
-  // Phase 2: every thread combines its output elements with the chunk loads of an element
-  // batched eight at a time, so that the merge costs a few round trips, not one per chunk.
-  float* s_m = reinterpret_cast<float*>(smem);          // [group][my_splits]
-  float* s_l = s_m + 16 * 64;                           // [group][my_splits] (at most 16 rows x 64 chunks)
-  const int nsp = min(my_splits, 64);
-  for (int i = threadIdx.x; i < group * nsp; i += blockDim.x) {
-    const int r = i / nsp, sp = i - r * nsp;
-    const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + kvh * group + r) * p.num_splits;
-    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&p.part_ml[(base + sp) * 2]));
-    s_m[r * 64 + sp] = ml.x;
-    s_l[r * 64 + sp] = ml.y;
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
-    const int r = idx / HD, c = idx % HD;
-    const int head = kvh * group + r;
-    const size_t base = (static_cast<size_t>(seq) * p.num_q_heads + head) * p.num_splits;
-    float mm = -INFINITY;
-    for (int sp = 0; sp < nsp; ++sp) mm = fmaxf(mm, s_m[r * 64 + sp]);
-    const float muse = (mm == -INFINITY) ? 0.f : mm;
-    float acc = 0.f, ll = 0.f;
-    for (int sp0 = 0; sp0 < nsp; sp0 += 8) {
-      float pv[8];
+  zb_pdl_launch();
+  zb_pdl_wait();
+  const int seq = blockIdx.x / p.num_kv_heads;
+  const int kvh = blockIdx.x % p.num_kv_heads;
+  const int split = blockIdx.y;
+  const int group = p.num_q_heads / p.num_kv_heads;
+  const int len = p.seq_lens[seq];
+  const int nblk = (len + 15) >> 4;
+  const int per = p.chunk_blocks;                          // a multiple of 4 (64 keys)
+  const int my_splits = max(1, (nblk + per - 1) / per);
+  if (split >= my_splits) return;
+  const int blk0 = split * per;
+  const int blk1 = min(nblk, blk0 + per);
+  const int tile0 = blk0 >> 2, tile1 = (blk1 + 3) >> 2;
+  const int first_visible = p.window > 0 ? max(0, len - p.window) : 0;
+  const int32_t* bt = p.block_table + static_cast<size_t>(seq) * p.max_pages;
+
+  float o[HD / 8][4];
 #pragma unroll
-      for (int b = 0; b < 8; ++b) pv[b] = __ldcg(&p.part_o[(base + min(sp0 + b, nsp - 1)) * HD + c]);
-#pragma unroll
-      for (int b = 0; b < 8; ++b) {
-        if (sp0 + b < nsp) {
-          const float f = exp2f(s_m[r * 64 + sp0 + b] - muse);
-          acc += f * pv[b];
-          ll += f * s_l[r * 64 + sp0 + b];
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  if (warp == 4) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      for (int t = tile0; t < tile1; ++t) {
+        if (!zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
+        const int page = bt[t];
+        uint8_t* ks = smem + stage * 2 * kTileBytes;
+        zb_mbar_expect_tx(&full_bar[stage], 2 * kTileBytes);
+        zb_tma_load_4d(ks, &tmap_k, &full_bar[stage], 0, page * 64, 0, kvh);
+        zb_tma_load_4d(ks + kTileBytes, &tmap_v, &full_bar[stage], 0, page * 64, 0, kvh);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
-    p.out[(static_cast<size_t>(seq) * p.num_q_heads + head) * HD + c] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+  } else {
+    // Q fragments: row r < group is query head kvh*group + r of this sequence's token
+    uint32_t qf[HD / 16][4];
+    {
+      const int g = lane >> 2, t = lane & 3;
+      const __nv_bfloat16* qrow0 = p.q + static_cast<size_t>(seq) * p.q_stride + static_cast<size_t>(kvh * group + g) * HD;
+      const __nv_bfloat16* qrow1 = qrow0 + static_cast<size_t>(8) * HD;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        const int c = kk * 16 + 2 * t;
+        qf[kk][0] = g < group ? *reinterpret_cast<const uint32_t*>(qrow0 + c) : 0u;
+        qf[kk][1] = (g + 8) < group ? *reinterpret_cast<const uint32_t*>(qrow1 + c) : 0u;
+        qf[kk][2] = g < group ? *reinterpret_cast<const uint32_t*>(qrow0 + c + 8) : 0u;
+        qf[kk][3] = (g + 8) < group ? *reinterpret_cast<const uint32_t*>(qrow1 + c + 8) : 0u;
+      }
+    }
+    uint32_t stage = 0, phase = 0;
+    for (int t = tile0; t < tile1; ++t) {
+      if (!zb_mbar_wait(&full_bar[stage], phase, abort_flag)) break;
+      const int tok0 = t * 64 + warp * 16;                 // this warp's 16 keys of the tile
+      if (tok0 < len && (tok0 >> 4) >= blk0 && (tok0 >> 4) < blk1) {
+        const uint32_t ks = zb_smem_u32(smem + stage * 2 * kTileBytes);
+        const uint32_t vs = ks + kTileBytes;
+        if (tok0 + 16 > len) {
+          // rows past the end of the sequence hold whatever the page held before: their
+          // probabilities are zero, but 0 x NaN would still poison the sum - clear those V rows
+          for (int idx = lane; idx < 16 * (HD / 8); idx += 32) {
+            const int row = warp * 16 + idx / (HD / 8), chunk = idx % (HD / 8);
+            if (t * 64 + row >= len)
+              *reinterpret_cast<uint4*>(smem + stage * 2 * kTileBytes + kTileBytes + tile_off_tma<HD>(row, chunk)) =
+                  make_uint4(0u, 0u, 0u, 0u);
+          }
+          __syncwarp();
+        }
+        attn_block16<HD, 1>(qf, ks, vs, warp * 16, o, m, l, p.scale_log2, [&](int /*half*/, int col) {
+          const int kidx = tok0 + col;
+          return kidx < len && kidx >= first_visible;
+        });
+      }
+      __syncwarp();
+      if (lane == 0) zb_mbar_arrive(&empty_bar[stage]);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
   }
+  __syncthreads();
+  if (*abort_flag != 0u) {
+    if (threadIdx.x == 0) zb_record_error(p.status, ZB_ERR_MBAR_TIMEOUT, 2u, 1u, blockIdx.x);
+    // copies that may still be in flight must land before the shared memory is reused
+    const uint64_t t0 = zb_globaltimer();
+    while (zb_globaltimer() - t0 < 200000ull) {
+    }
+    __syncthreads();
+    return;
+  }
+  decode_tail<HD>(p, smem, o, m, l, seq, kvh, split, my_splits, group);
 }
 
 // --------------------------------------------------------------------- prefill
@@ -524,6 +679,29 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
   return static_cast<int>(cudaGetLastError());
 }
 
+int g_decode_tma = 1;
+
+template <int HD>
+int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
+  constexpr int smem = dec_tma_stages<HD>() * 2 * 64 * HD * 2 + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = zb_config_smem(zb_paged_decode_tma_kernel<HD>, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  CUtensorMap tk, tv;
+  const long long slots = 1ll << 30;      // bound only: pages are addressed through the block table
+  int rc = zb_make_tmap_kv_cache(&tk, p.k_cache, slots, p.num_kv_heads, HD, 64);
+  if (rc != 0) return rc;
+  rc = zb_make_tmap_kv_cache(&tv, p.v_cache, slots, p.num_kv_heads, HD, 64);
+  if (rc != 0) return rc;
+  dim3 grid(p.batch * p.num_kv_heads, p.num_splits);
+  zb_launch(zb_paged_decode_tma_kernel<HD>, dim3(grid), dim3(160), smem, stream, tk, tv, p);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
 template <int HD>
 int launch_prefill(const AttnParams& p, int num_q_blocks, cudaStream_t stream) {
   constexpr int smem = 5 * 64 * HD * 2;
@@ -575,6 +753,9 @@ int zb_decode_plan_splits(int batch, int num_kv_heads, int max_seq_len, int num_
   return mc;
 }
 
+// Tensor-map fed decode kernel on (default) / off.
+void zb_set_decode_tma(int on) { g_decode_tma = on ? 1 : 0; }
+
 int zb_paged_decode_ex(const void* q, const void* k_cache, const void* v_cache, void* out,
                        const int32_t* block_table, const int32_t* seq_lens, int batch,
                        int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
@@ -592,7 +773,8 @@ int zb_paged_decode_ex(const void* q, const void* k_cache, const void* v_cache, 
     --num_splits;
   // chunk length that lets `num_splits` chunks cover the longest sequence the block table allows
   const int max_blocks = (max_pages * page_size + 15) / 16;
-  const int chunk_blocks = (max_blocks + num_splits - 1) / num_splits;
+  int chunk_blocks = (max_blocks + num_splits - 1) / num_splits;
+  if (page_size == 64) chunk_blocks = (chunk_blocks + 3) / 4 * 4;      // whole pages per chunk (tensor-map fed kernel)
   AttnParams p = {};
   p.q = reinterpret_cast<const __nv_bfloat16*>(q);
   p.k_cache = reinterpret_cast<const __nv_bfloat16*>(k_cache);
@@ -616,10 +798,13 @@ int zb_paged_decode_ex(const void* q, const void* k_cache, const void* v_cache, 
   p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  // 64-token pages and chunks of whole pages: the tensor-map fed kernel; otherwise per-warp cp.async
+  const bool tma = g_decode_tma != 0 && page_size == 64 && (p.chunk_blocks % 4) == 0 &&
+                   (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0;
   switch (head_dim) {
-    case 64: return launch_decode<64>(p, stream);
-    case 128: return launch_decode<128>(p, stream);
-    case 256: return launch_decode<256>(p, stream);
+    case 64: return tma ? launch_decode_tma<64>(p, stream) : launch_decode<64>(p, stream);
+    case 128: return tma ? launch_decode_tma<128>(p, stream) : launch_decode<128>(p, stream);
+    case 256: return tma ? launch_decode_tma<256>(p, stream) : launch_decode<256>(p, stream);
   }
   return -32;
 }

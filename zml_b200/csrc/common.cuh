@@ -167,6 +167,16 @@ ZB_DEVICE void zb_tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, i
       : "memory");
 }
 
+ZB_DEVICE void zb_tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x, int32_t y,
+                              int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(zb_smem_u32(smem_dst)), "l"(tmap), "r"(zb_smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
 // Thread-block clusters: rank, cluster-wide barrier (every thread of every CTA of the cluster
 // takes part), and loads from a peer CTA's shared memory (distributed shared memory).
 ZB_DEVICE uint32_t zb_cluster_ctarank() {

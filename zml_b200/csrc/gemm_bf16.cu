@@ -1061,6 +1061,27 @@ int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, in
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// Paged K or V cache [slots, kv_heads, head_dim] bf16 -> 4-D tensor map (64 columns, slots, head_dim / 64
+// column groups, kv heads) with box (64, box_rows, head_dim / 64, 1) and the 128-byte swizzle: one copy
+// brings `box_rows` consecutive slots of one head into shared memory as head_dim / 64 tiles of
+// [box_rows][64], each with 128-byte rows.  Returns 0 on success.
+int zb_make_tmap_kv_cache(CUtensorMap* out, const void* base, long long slots, int kv_heads, int head_dim,
+                          int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || head_dim % 64 != 0 || box_rows < 1 || box_rows > 256) return -2;
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(kv_heads) * head_dim * 2;
+  cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(slots), static_cast<cuuint64_t>(head_dim / 64),
+                        static_cast<cuuint64_t>(kv_heads)};
+  cuuint64_t strides[3] = {row_bytes, 128, static_cast<cuuint64_t>(head_dim) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(head_dim / 64), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 namespace {
 
 template <int BN, bool SWAP, bool FUSED = false>
