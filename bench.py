@@ -34,6 +34,7 @@ WORKLOADS = {
     "llama-3.1-8b": dict(batch=32, prompt=(128, 2048), new_tokens=512),
     "llama-3.1-70b": dict(batch=64, prompt=(2048, 2048), new_tokens=256),
     "qwen3-30b-a3b": dict(batch=128, prompt=(1024, 1024), new_tokens=256),
+    "qwen3-30b-a3b-nvfp4": dict(batch=128, prompt=(1024, 1024), new_tokens=256),
     "qwen3.5-9b": dict(batch=32, prompt=(128, 2048), new_tokens=512),
     "qwen3.5-35b-a3b": dict(batch=64, prompt=(1024, 1024), new_tokens=256),
     "lfm2-1.2b": dict(batch=32, prompt=(128, 2048), new_tokens=512),

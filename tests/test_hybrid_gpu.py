@@ -187,3 +187,25 @@ def test_nvfp4_linear_runs_on_the_bf16_gemm():
     expect_close(make(DEV), make("cpu"), atol=3e-2, rtol=3e-2, min_close=0.995)
     exact = x.float() @ w.t()
     assert ((make("cpu") - exact).norm() / exact.norm()).item() < 0.2          # 4-bit weights: ~10 % error
+
+
+@pytest.mark.parametrize("tokens,e_local,k_top,d,f", [(24, 8, 2, 256, 128), (128, 16, 4, 512, 256), (7, 4, 1, 128, 128)])
+def test_moe_grouped_gemm_nvfp4_weights(tokens, e_local, k_top, d, f):
+    """NVFP4 expert weights de-quantised inside the grouped GEMM == the bf16 kernels on the de-quantised weights."""
+    from zml_b200 import moe
+    torch.manual_seed(tokens)
+    gate = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
+    up = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
+    down = (torch.randn(e_local, d, f, device=DEV) * 0.05).bfloat16()
+    gu_q = moe.Nvfp4Experts.quantize(moe.interleave_gate_up(gate, up))
+    dn_q = moe.Nvfp4Experts.quantize(down)
+    gu_bf, dn_bf = gu_q.dequantize(), dn_q.dequantize()
+    x = torch.randn(tokens, d, device=DEV).bfloat16()
+    logits = torch.randn(tokens, e_local, device=DEV)
+    ids, w = moe.router_topk(logits, k_top, True)
+    want = moe.fused_experts(x, ids, w, gu_bf, dn_bf, 0, e_local)
+    got = moe.fused_experts(x, ids, w, gu_bf, dn_bf, 0, e_local, w4=(gu_q, dn_q))
+    expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+    g, u = moe.deinterleave_gate_up(gu_bf)
+    ref = moe.reference_fused_experts(x.cpu(), ids.cpu(), w.cpu(), g.cpu(), u.cpu(), dn_bf.cpu(), 0)
+    expect_close(got.float().cpu(), ref.float(), atol=3e-2, rtol=3e-2, min_close=0.99)

@@ -1061,6 +1061,22 @@ int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, in
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// Byte matrix [rows, row_bytes] -> tensor map with a (box_bytes x box_rows) box, no swizzle (packed
+// sub-byte data such as NVFP4 codes).  row_bytes and box_bytes multiples of 16.
+int zb_make_tmap_u8_2d(CUtensorMap* out, const void* base, long long rows, long long row_bytes, int box_bytes, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes % 16) != 0 || (box_bytes % 16) != 0 || box_rows > 256) return -2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 // Paged K or V cache [slots, kv_heads, head_dim] bf16 -> 4-D tensor map (64 columns, slots, head_dim / 64
 // column groups, kv heads) with box (64, box_rows, head_dim / 64, 1) and the 128-byte swizzle: one copy
 // brings `box_rows` consecutive slots of one head into shared memory as head_dim / 64 tiles of

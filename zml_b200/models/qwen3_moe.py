@@ -53,12 +53,16 @@ PRESETS = {
                           num_experts_per_tok=8, vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6,
                           tie_word_embeddings=False, max_position_embeddings=40960, norm_topk_prob=True,
                           bos_token_id=151643, eos_token_id=[151645, 151643], model_type="qwen3_moe"),
+    "qwen3-30b-a3b-nvfp4": None,     # filled below: same shape, NVFP4 expert weights
     "tiny-moe-test": dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
                           head_dim=64, intermediate_size=128, moe_intermediate_size=128, num_experts=8,
                           num_experts_per_tok=2, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=10000.0,
                           tie_word_embeddings=True, max_position_embeddings=4096, norm_topk_prob=True,
                           bos_token_id=1, eos_token_id=2, model_type="qwen3_moe"),
 }
+
+
+PRESETS["qwen3-30b-a3b-nvfp4"] = dict(PRESETS["qwen3-30b-a3b"], expert_dtype="nvfp4")
 
 
 class Qwen3MoeModel(LlamaModel):
@@ -101,12 +105,22 @@ class Qwen3MoeModel(LlamaModel):
             gate = rw((c.num_experts, f, d), b + 4, rows=erng)
             up = rw((c.num_experts, f, d), b + 5, rows=erng)
             down = rw((c.num_experts, d, f), b + 6, rows=erng)
-            if c.expert_dtype == "nvfp4":
-                gate, up, down = moe.nvfp4_roundtrip(gate), moe.nvfp4_roundtrip(up), moe.nvfp4_roundtrip(down)
             lw.extra = {"router": rw((c.num_experts, d), b + 7), "gate_up": moe.interleave_gate_up(gate, up), "down": down}
             del gate, up
+            if c.expert_dtype == "nvfp4":
+                self._to_nvfp4(lw)
             self.layers.append(lw)
         return self
+
+    def _to_nvfp4(self, lw: LayerWeights) -> None:
+        """Expert weights become NVFP4 (quantised in the interleaved gate|up layout the kernels use).  The
+        packed form feeds the decode-regime kernel; its de-quantised bf16 twin feeds the compute-bound
+        prefill kernel, so both see the same values."""
+        gu = moe.Nvfp4Experts.quantize(lw.extra["gate_up"])
+        dn = moe.Nvfp4Experts.quantize(lw.extra["down"])
+        lw.extra["gate_up"] = gu.dequantize(self.dtype)
+        lw.extra["down"] = dn.dequantize(self.dtype)
+        lw.extra["w4"] = (gu, dn)
 
     def load(self, store, prefix: str = "") -> "Qwen3MoeModel":
         c, hd = self.config, self.config.hd
@@ -177,7 +191,8 @@ class Qwen3MoeModel(LlamaModel):
     def weight_bytes(self) -> int:
         n = super().weight_bytes()
         for lw in self.layers:
-            n += sum(t.numel() * t.element_size() for t in lw.extra.values())
+            n += sum(t.numel() * t.element_size() for t in lw.extra.values() if isinstance(t, torch.Tensor))
+            n += sum(q.nbytes() for q in lw.extra.get("w4", ()))
         return n
 
     # ------------------------------------------------------------------ forward
@@ -185,4 +200,5 @@ class Qwen3MoeModel(LlamaModel):
         c = self.config
         logits = ops.gemm(n2, lw.extra["router"], out_dtype=torch.float32, static_w=True)
         ids, w = moe.router_topk(logits, c.num_experts_per_tok, c.norm_topk_prob)
-        return moe.forward_moe(n2, ids, w, lw.extra["gate_up"], lw.extra["down"], self.comm, c.num_experts, residual=x)
+        return moe.forward_moe(n2, ids, w, lw.extra["gate_up"], lw.extra["down"], self.comm, c.num_experts, residual=x,
+                               w4=lw.extra.get("w4"))

@@ -155,6 +155,53 @@ def grouped_gemm(xs: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, swiglu: 
     return out
 
 
+class Nvfp4Experts:
+    """Expert weights [E, N, K] in NVFP4: packed e2m1 codes [E * N, K / 2] (low nibble first), one
+    f8e4m3fn scale per 16 values [E * N, K / 16], one float32 scale per expert matrix [E]."""
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, gscale: torch.Tensor, e: int, n: int, k: int):
+        self.codes, self.scales, self.gscale = codes, scales, gscale
+        self.e, self.n, self.k = e, n, k
+
+    @staticmethod
+    def quantize(w: torch.Tensor) -> "Nvfp4Experts":
+        from ..nn import quant as Q
+        e, n, k = w.shape
+        codes = torch.empty((e * n, k // 2), dtype=torch.uint8, device=w.device)
+        scales = torch.empty((e * n, k // 16), dtype=torch.float8_e4m3fn, device=w.device)
+        gs = torch.empty(e, dtype=torch.float32, device=w.device)
+        for i in range(e):
+            c, s, g = Q.quantize_weight_nvfp4(w[i])
+            codes[i * n:(i + 1) * n], scales[i * n:(i + 1) * n], gs[i] = c, s, g
+        return Nvfp4Experts(codes, scales, gs, e, n, k)
+
+    def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
+        from ..nn import quant as Q
+        out = torch.empty((self.e, self.n, self.k), dtype=dtype, device=self.codes.device)
+        for i in range(self.e):
+            sl = slice(i * self.n, (i + 1) * self.n)
+            out[i] = Q.dequantize_nvfp4(Q.unpack_e2m1(self.codes[sl]), self.scales[sl], self.gscale[i], dtype)
+        return out
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel() + self.gscale.numel() * 4
+
+
+def grouped_gemm_w4(xs: torch.Tensor, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8):
+    """`grouped_gemm` with NVFP4 expert weights de-quantised inside the kernel (few tokens per
+    expert; libzb_cuda.so: zb_moe_grouped_gemm_w4).  CPU tensors: de-quantise, then the float path."""
+    if not xs.is_cuda:
+        return grouped_gemm(xs, w.dequantize(xs.dtype), meta, swiglu, avg_tokens)
+    cap = xs.shape[0]
+    n_out = w.n // 2 if swiglu else w.n
+    assert xs.dtype == torch.bfloat16 and xs.is_contiguous() and xs.shape[1] == w.k
+    out = torch.empty((cap, n_out), dtype=xs.dtype, device=xs.device)
+    _lib.check(_lib.lib().zb_moe_grouped_gemm_w4(xs.data_ptr(), w.codes.data_ptr(), w.scales.data_ptr(), w.gscale.data_ptr(),
+                                                 out.data_ptr(), meta.data_ptr(), w.e, w.n, w.k, cap, n_out, int(swiglu),
+                                                 int(avg_tokens), _lib.stream_ptr()), "zb_moe_grouped_gemm_w4")
+    return out
+
+
 def finalize(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tokens: int, k: int):
     """y[t] = sum_j weights[t, j] * o[pair_pos[t * k + j]] over the pairs that are local."""
     d = o.shape[1]
@@ -170,8 +217,12 @@ def finalize(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tok
 
 
 # ---------------------------------------------------------------------- fused experts
+W4_MAX_AVG_TOKENS = 32      # NVFP4 kernel: tiles of at most 64 tokens per expert
+
+
 def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w_gate_up_il: torch.Tensor,
-                  w_down: torch.Tensor, e0: int = 0, num_experts_total: Optional[int] = None) -> torch.Tensor:
+                  w_down: torch.Tensor, e0: int = 0, num_experts_total: Optional[int] = None,
+                  w4: Optional[tuple] = None) -> torch.Tensor:
     """Mixture output of the LOCAL experts for all tokens: permute -> grouped GEMM (+SwiGLU) ->
     grouped GEMM -> un-permute x routing weight.  x [T, D] bf16; w_gate_up_il [E_local, 2F, D]
     (interleaved, see `interleave_gate_up`); w_down [E_local, D, F]."""
@@ -183,8 +234,13 @@ def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor,
     avg = max(1, (t * k) // max(total_e, 1))
     meta, sorted_pair, pair_pos = moe_align(topk_ids, e0, e_local)
     xs = gather(x, sorted_pair, meta, e_local, k, cap)
-    h = grouped_gemm(xs, w_gate_up_il, meta, swiglu=True, avg_tokens=avg)
-    o = grouped_gemm(h, w_down, meta, swiglu=False, avg_tokens=avg)
+    if w4 is not None and avg <= W4_MAX_AVG_TOKENS:
+        # few tokens per expert: the step is bound by reading expert weights - read them as NVFP4
+        h = grouped_gemm_w4(xs, w4[0], meta, swiglu=True, avg_tokens=avg)
+        o = grouped_gemm_w4(h, w4[1], meta, swiglu=False, avg_tokens=avg)
+    else:
+        h = grouped_gemm(xs, w_gate_up_il, meta, swiglu=True, avg_tokens=avg)
+        o = grouped_gemm(h, w_down, meta, swiglu=False, avg_tokens=avg)
     return finalize(o, pair_pos, topk_w, t, k)
 
 
@@ -234,7 +290,7 @@ def library_experts(x, topk_ids, topk_w, w_gate_up_il, w_down, e0: int = 0):
 
 def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, w_gate_up: torch.Tensor,
                 w_down: torch.Tensor, comm=None, num_experts_total: Optional[int] = None, residual=None,
-                extra_partial=None):
+                extra_partial=None, w4: Optional[tuple] = None):
     """Routed mixture with expert parallelism.  `w_gate_up` / `w_down` hold this rank's experts
     (rank r owns experts [r * E_local, (r + 1) * E_local)); partial outputs are summed across
     ranks (in-kernel over peer memory when `comm.fused` is set, NCCL otherwise) and `residual`
@@ -251,7 +307,7 @@ def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Ten
         if world > 1:
             y = comm.all_reduce_(y)
         return y + residual if residual is not None else y
-    y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, num_experts_total or e_local * world)
+    y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, num_experts_total or e_local * world, w4)
     if extra_partial is not None:
         y = y + extra_partial
     if world > 1:
