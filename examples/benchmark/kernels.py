@@ -48,6 +48,7 @@ class Args:
     model: str = "llama-3.1-8b"
     iters: int = 20
     warmup: int = 3
+    w4: int = 0              # moe: 1 = NVFP4 expert weights de-quantised inside the grouped GEMM
     copies: int = 0          # operand copies to rotate through (0: enough to exceed the L2)
     help = __doc__
 
@@ -145,15 +146,22 @@ def bench_moe(a: Args) -> None:
     for _ in range(c):
         g = torch.randn(e, f, d, device="cuda").bfloat16() * 0.02
         u = torch.randn(e, f, d, device="cuda").bfloat16() * 0.02
-        sets.append((moe.interleave_gate_up(g, u), torch.randn(e, d, f, device="cuda").bfloat16() * 0.02))
+        gu, dn = moe.interleave_gate_up(g, u), torch.randn(e, d, f, device="cuda").bfloat16() * 0.02
         del g, u
+        if a.w4:
+            q = (moe.Nvfp4Experts.quantize(gu), moe.Nvfp4Experts.quantize(dn))
+            sets.append((q[0].dequantize(), q[1].dequantize(), q))
+        else:
+            sets.append((gu, dn, None))
+        del gu, dn
     x = torch.randn(a.tokens, d, device="cuda").bfloat16()
     logits = torch.randn(a.tokens, e, device="cuda")
     ids, w = moe.router_topk(logits, k, True)
-    fns = [(lambda gu=gu, dn=dn: moe.fused_experts(x, ids, w, gu, dn, 0, e)) for gu, dn in sets]
+    fns = [(lambda gu=gu, dn=dn, q=q: moe.fused_experts(x, ids, w, gu, dn, 0, e, q)) for gu, dn, q in sets]
     ms = timed(fns, a.iters, a.warmup)
     active = min(e, a.tokens * k)
-    report(a, ms, active * 3 * d * f * 2, 6.0 * a.tokens * k * d * f, {"tokens": a.tokens, "experts": e, "topk": k, "copies": c})
+    wbytes = active * 3 * d * f * (0.5 + 1.0 / 16 if a.w4 else 2)
+    report(a, ms, wbytes, 6.0 * a.tokens * k * d * f, {"tokens": a.tokens, "experts": e, "topk": k, "copies": c, "w4": a.w4})
 
 
 def bench_gated_delta_scan(a: Args) -> None:

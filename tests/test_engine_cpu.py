@@ -124,3 +124,19 @@ def test_moe_nvfp4_expert_weights_are_representable():
     eng = Engine(m, num_pages=16, page_size=16, max_batch=2, max_seq_len=64)
     out, _ = eng.generate([[5, 6, 7, 8]], 4)
     assert len(out[0]) == 4
+
+
+def test_nvfp4_experts_container_and_cpu_path():
+    from zml_b200 import moe
+    torch.manual_seed(0)
+    w = torch.randn(3, 128, 64).bfloat16() * 0.05
+    q = moe.Nvfp4Experts.quantize(w)
+    assert q.codes.shape == (3 * 128, 32) and q.scales.shape == (3 * 128, 4) and q.gscale.shape == (3,)
+    assert q.nbytes() == 3 * 128 * 32 + 3 * 128 * 4 + 12
+    d = q.dequantize()
+    assert ((d.float() - w.float()).norm() / w.float().norm()).item() < 0.15
+    xs = torch.randn(10, 64).bfloat16()
+    meta = torch.tensor([0, 4, 4, 10], dtype=torch.int32)
+    got = moe.grouped_gemm_w4(xs, q, meta)
+    want = moe.grouped_gemm(xs, d, meta)
+    assert torch.equal(got, want)

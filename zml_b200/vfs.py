@@ -11,6 +11,7 @@ from __future__ import annotations
 import concurrent.futures as cf
 import io
 import os
+import sys
 import urllib.error
 import urllib.parse
 import urllib.request
@@ -90,11 +91,29 @@ class HttpBackend(Backend):
         return data
 
 
+def hf_token_path() -> str:
+    home = os.environ.get("HF_HOME", os.path.join(os.path.expanduser("~"), ".cache", "huggingface"))
+    return os.path.join(home, "token")
+
+
+def hf_token() -> Optional[str]:
+    """HF_TOKEN from the environment, else the token stored by `python -m zml_b200.vfs auth login`
+    (the reference's `bazel run //tools/hf -- auth login`)."""
+    tok = os.environ.get("HF_TOKEN")
+    if tok:
+        return tok.strip()
+    try:
+        with open(hf_token_path(), "r") as f:
+            return f.read().strip() or None
+    except OSError:
+        return None
+
+
 class HfBackend(HttpBackend):
     """hf://org/repo[@revision]/path/in/repo"""
 
     def __init__(self, endpoint: str = "https://huggingface.co"):
-        tok = os.environ.get("HF_TOKEN")
+        tok = hf_token()
         super().__init__({"Authorization": f"Bearer {tok}"} if tok else {})
         self.endpoint = endpoint.rstrip("/")
 
@@ -218,3 +237,33 @@ class VfsFile(io.RawIOBase):
         data = self.vfs.read_range(self.uri, self.pos, n) if n > 0 else b""
         self.pos += len(data)
         return data
+
+
+def _auth_main(argv) -> int:
+    """`python -m zml_b200.vfs auth login [--token=...]` / `auth logout` / `auth whoami`."""
+    import getpass
+    if len(argv) < 2 or argv[0] != "auth" or argv[1] not in ("login", "logout", "whoami"):
+        print(_auth_main.__doc__, file=sys.stderr)
+        return 1
+    path = hf_token_path()
+    if argv[1] == "logout":
+        if os.path.exists(path):
+            os.remove(path)
+        print("logged out")
+        return 0
+    if argv[1] == "whoami":
+        tok = hf_token()
+        print("token: " + (tok[:6] + "..." if tok else "none"))
+        return 0
+    tok = next((a.split("=", 1)[1] for a in argv[2:] if a.startswith("--token=")), None) or getpass.getpass("HF token: ")
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    with open(path, "w") as f:
+        f.write(tok.strip())
+    os.chmod(path, 0o600)
+    print(f"token stored in {path}")
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(_auth_main(sys.argv[1:]))
