@@ -48,6 +48,7 @@ class Args:
     model: str = "llama-3.1-8b"
     iters: int = 20
     warmup: int = 3
+    splits: int = 0          # decode_attention: KV chunks per sequence (0: the planner's choice)
     w4: int = 0              # moe: 1 = NVFP4 expert weights de-quantised inside the grouped GEMM
     copies: int = 0          # operand copies to rotate through (0: enough to exceed the L2)
     help = __doc__
@@ -119,7 +120,7 @@ def bench_decode_attention(a: Args) -> None:
     caches, bt = _kv(a, c)
     q = torch.randn(a.batch, a.hq, a.hd, device="cuda").bfloat16()
     sl = torch.full((a.batch,), a.seqlen, dtype=torch.int32, device="cuda")
-    splits = ops.decode_plan_splits(a.batch, a.hkv, a.seqlen)
+    splits = a.splits or ops.decode_plan_splits(a.batch, a.hkv, a.seqlen)
     fns = [(lambda kc=kc, vc=vc: ops.paged_decode(q, kc, vc, bt, sl, num_splits=splits, max_seq_len=a.seqlen)) for kc, vc in caches]
     ms = timed(fns, a.iters, a.warmup)
     report(a, ms, kvb, 4.0 * a.batch * a.hq * a.seqlen * a.hd, {"batch": a.batch, "seqlen": a.seqlen, "splits": splits, "copies": c})

@@ -128,15 +128,71 @@ def test_moe_nvfp4_expert_weights_are_representable():
 
 def test_nvfp4_experts_container_and_cpu_path():
     from zml_b200 import moe
+    from zml_b200.nn import quant as Q
     torch.manual_seed(0)
+    # K = 64: not a shape the kernel streams -> plain codes and scales, de-quantising fallback
     w = torch.randn(3, 128, 64).bfloat16() * 0.05
     q = moe.Nvfp4Experts.quantize(w)
-    assert q.codes.shape == (3 * 128, 32) and q.scales.shape == (3 * 128, 4) and q.gscale.shape == (3,)
+    assert not q.kernel_ready and q.blocks is None
+    assert q.codes.shape == (3 * 128, 32) and q.scales.shape == (3 * 128, 4) and q.gscale.shape == (3, 1)
     assert q.nbytes() == 3 * 128 * 32 + 3 * 128 * 4 + 12
     d = q.dequantize()
     assert ((d.float() - w.float()).norm() / w.float().norm()).item() < 0.15
     xs = torch.randn(10, 64).bfloat16()
     meta = torch.tensor([0, 4, 4, 10], dtype=torch.int32)
-    got = moe.grouped_gemm_w4(xs, q, meta)
-    want = moe.grouped_gemm(xs, d, meta)
-    assert torch.equal(got, want)
+    assert torch.equal(moe.grouped_gemm_w4(xs, q, meta), moe.grouped_gemm(xs, d, meta))
+    # N a multiple of 128 and K of 256: tile-major 18 KB blocks, a bijection of the checkpoint arrays
+    w2 = torch.randn(2, 256, 512).bfloat16() * 0.05
+    q2 = moe.Nvfp4Experts.quantize(w2)
+    assert q2.kernel_ready and q2.blocks.shape == (2, 2, 2, moe.ops.W4_BLOCK_BYTES) and q2.codes is None
+    c, s_, g = Q.quantize_weight_nvfp4(w2)
+    codes, scales = q2.checkpoint_arrays()
+    assert torch.equal(codes, c.reshape(512, 256)) and torch.equal(scales.view(torch.uint8), s_.reshape(512, 32).view(torch.uint8))
+    want = Q.dequantize_nvfp4(Q.unpack_e2m1(c), s_, None) * g.reshape(2, 1, 1)
+    assert torch.allclose(q2.dequantize(torch.float32), want.float(), rtol=1e-6, atol=1e-9)
+    assert torch.equal(moe.ops.nvfp4_codes_from_kernel_order(moe.ops.nvfp4_codes_to_kernel_order(c[0])), c[0])
+    # block layout: chunk ch of row r of block (e, tile, kchunk) sits at [ch][r][16 bytes], scales after the codes
+    blk = q2.blocks[1, 1, 0]
+    krow = moe.ops.nvfp4_codes_to_kernel_order(c[1])[128 + 5]            # row 5 of tile 1, kernel nibble order
+    assert torch.equal(blk[(3 * 128 + 5) * 16:(3 * 128 + 5) * 16 + 16], krow[3 * 16:4 * 16])
+    assert torch.equal(blk[128 * 128 + 5 * 16:128 * 128 + 5 * 16 + 16], s_[1, 128 + 5, :16].view(torch.uint8))
+
+
+def test_moe_loads_nvfp4_expert_checkpoints(tmp_path):
+    """Per-expert packed weights + block scales + matrix scale (both spellings) load into the NVFP4 container
+    and its bf16 twin; gate and up keep their own matrix scales."""
+    from zml_b200 import moe, safetensors
+    from zml_b200.io import TensorStore
+    from zml_b200.nn import quant as Q
+    from zml_b200.models.qwen3_moe import PRESETS as MOE_PRESETS, Qwen3MoeConfig, Qwen3MoeModel
+    cfg = Qwen3MoeConfig.from_hf(dict(MOE_PRESETS["tiny-moe-test"]))
+    model = Qwen3MoeModel(cfg, device="cpu", dtype=torch.float32).init_random(1)
+    sd = model.state_dict_hf()
+    for spelling in ("modelopt", "compressed-tensors"):
+        out, want = {}, {}
+        for name, t in sd.items():
+            if ".mlp.experts." not in name:
+                out[name] = t
+                continue
+            base = name[:-len("weight")]
+            codes, scales, g = Q.quantize_weight_nvfp4(t * (3.0 if "up_proj" in name else 1.0))
+            want[name] = Q.dequantize_nvfp4(Q.unpack_e2m1(codes), scales, g)
+            if spelling == "modelopt":
+                out[base + "weight"], out[base + "weight_scale"], out[base + "weight_scale_2"] = codes, scales, g.reshape(())
+            else:
+                out[base + "weight_packed"], out[base + "weight_scale"] = codes, scales
+                out[base + "weight_global_scale"] = (1.0 / g).reshape(1)
+        d = tmp_path / spelling
+        d.mkdir()
+        safetensors.save_sharded(out, str(d))
+        m2 = Qwen3MoeModel(cfg, device="cpu", dtype=torch.float32).load(TensorStore.from_path(str(d)))
+        lw = m2.layers[0]
+        gu, dn = lw.extra["w4"]
+        assert gu.gscale.shape == (cfg.num_experts, 2) and dn.gscale.shape == (cfg.num_experts, 1)
+        g_, u_ = moe.ops.deinterleave_gate_up(lw.extra["gate_up"])
+        for e in (0, cfg.num_experts - 1):
+            assert torch.allclose(g_[e], want[f"model.layers.0.mlp.experts.{e}.gate_proj.weight"], rtol=1e-6, atol=1e-8)
+            assert torch.allclose(u_[e], want[f"model.layers.0.mlp.experts.{e}.up_proj.weight"], rtol=1e-6, atol=1e-8)
+            assert torch.allclose(lw.extra["down"][e], want[f"model.layers.0.mlp.experts.{e}.down_proj.weight"], rtol=1e-6, atol=1e-8)
+        outs, _ = Engine(m2, num_pages=32, page_size=16, max_batch=2, max_seq_len=128).generate([[3, 4, 5, 6, 7]], 4)
+        assert len(outs[0]) == 4

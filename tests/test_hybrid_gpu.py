@@ -189,15 +189,23 @@ def test_nvfp4_linear_runs_on_the_bf16_gemm():
     assert ((make("cpu") - exact).norm() / exact.norm()).item() < 0.2          # 4-bit weights: ~10 % error
 
 
-@pytest.mark.parametrize("tokens,e_local,k_top,d,f", [(24, 8, 2, 256, 128), (128, 16, 4, 512, 256), (7, 4, 1, 128, 128)])
+@pytest.mark.parametrize("tokens,e_local,k_top,d,f", [(24, 8, 2, 256, 256), (128, 16, 4, 512, 768), (7, 4, 1, 256, 512), (300, 8, 2, 512, 256),
+                                                     (9, 4, 2, 128, 128)])
 def test_moe_grouped_gemm_nvfp4_weights(tokens, e_local, k_top, d, f):
-    """NVFP4 expert weights de-quantised inside the grouped GEMM == the bf16 kernels on the de-quantised weights."""
+    """NVFP4 expert weights de-quantised inside the grouped GEMM == the bf16 kernels on the de-quantised weights
+    (the last case has K = 128, which the NVFP4 kernel does not take: the bf16 kernels run)."""
     from zml_b200 import moe
     torch.manual_seed(tokens)
     gate = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
     up = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
     down = (torch.randn(e_local, d, f, device=DEV) * 0.05).bfloat16()
-    gu_q = moe.Nvfp4Experts.quantize(moe.interleave_gate_up(gate, up))
+    if tokens % 2 == 0:
+        gu_q = moe.Nvfp4Experts.quantize(moe.interleave_gate_up(gate, up))
+    else:
+        # gate and up quantised separately, as a checkpoint stores them: two matrix scales per expert
+        from zml_b200.nn import quant as Q
+        gu_q = moe.Nvfp4Experts.from_checkpoint_gate_up(Q.quantize_weight_nvfp4(gate), Q.quantize_weight_nvfp4(up * 4.0))
+        assert gu_q.gscale.shape == (e_local, 2)
     dn_q = moe.Nvfp4Experts.quantize(down)
     gu_bf, dn_bf = gu_q.dequantize(), dn_q.dequantize()
     x = torch.randn(tokens, d, device=DEV).bfloat16()

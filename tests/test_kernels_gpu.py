@@ -231,9 +231,29 @@ def test_moe_fused_experts_vs_dense_reference(t, e_total, e_local, e0, k, d, f):
     expect_close(cpu.float(), want.float().cpu(), atol=3e-2, rtol=3e-2, min_close=0.995)
 
 
-def test_moe_align_is_a_permutation():
+def test_moe_combine_adds_extra_and_residual():
+    """One-launch combine == finalize + shared-expert partial + residual."""
     from zml_b200 import moe
-    ids = torch.randint(0, 64, (333, 6), device=DEV, dtype=torch.int32)
+    torch.manual_seed(3)
+    t, k, d, e = 37, 4, 512, 16
+    ids, w = moe.router_topk(torch.randn(t, e, device=DEV), k)
+    meta, sorted_pair, pair_pos = moe.moe_align(ids, 4, 8)            # half of the experts are "remote"
+    o = _randn(t * k, d)
+    extra, res = _randn(t, d), _randn(t, d)
+    want = moe.finalize(o, pair_pos, w, t, k).float() + extra.float() + res.float()
+    got = moe.combine(o, pair_pos, w, t, k, extra, res)
+    expect_close(got.float(), want, atol=3e-2, rtol=2e-2)
+    only = moe.combine(o, pair_pos, w, t, k)
+    assert torch.equal(only, moe.finalize(o, pair_pos, w, t, k))
+    cpu = moe.combine(o.cpu(), pair_pos.cpu(), w.cpu(), t, k, extra.cpu(), res.cpu())
+    expect_close(cpu.float(), want.cpu(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("tokens", [1, 333, 1365, 3000])       # up to 8192 pairs: one launch; above: count / prefix / scatter
+def test_moe_align_is_a_permutation(tokens):
+    from zml_b200 import moe
+    torch.manual_seed(tokens)
+    ids = torch.randint(0, 64, (tokens, 6), device=DEV, dtype=torch.int32)
     meta, sorted_pair, pair_pos = moe.moe_align(ids, 16, 24)
     flat = ids.reshape(-1).cpu()
     local = (flat >= 16) & (flat < 40)

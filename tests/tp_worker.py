@@ -52,6 +52,28 @@ def main():
         assert all(torch.equal(gathered[0], gathered[r]) for r in range(comm.world)), (m, k)
     ops.raise_on_status()
 
+    # mixture-of-experts combine with the expert-parallel all-reduce inside vs finalize + NCCL all-reduce
+    from zml_b200 import moe
+    cctx = SymmetricContext.create(comm, 512, max_tokens=64, combine_tokens=64)
+    for it, (t, k) in enumerate([(5, 2), (64, 4), (33, 8), (64, 4)]):
+        g = torch.Generator(device="cpu").manual_seed(100 + it)
+        ids, w = moe.router_topk(torch.randn(t, 16, generator=g).to(dev), k)
+        e_local = 16 // comm.world
+        meta, sorted_pair, pair_pos = moe.moe_align(ids, comm.rank * e_local, e_local)
+        o = (torch.randn(t * k, 512, device=dev) * 0.5).bfloat16()
+        extra = (torch.randn(t, 512, device=dev) * 0.5).bfloat16()
+        res = torch.randn(t, 512, generator=g).to(dev).bfloat16()
+        part = moe.finalize(o, pair_pos, w, t, k).float() + extra.float()
+        want = part.bfloat16().float()
+        dist.all_reduce(want)
+        want = want + res.float()
+        got = cctx.moe_combine(o, pair_pos, w, t, k, extra, res)
+        expect_close(got.float(), want, atol=6e-2, rtol=3e-2, min_close=0.995)
+        gathered = comm.all_gather(got[None].contiguous())
+        assert all(torch.equal(gathered[0], gathered[r]) for r in range(comm.world)), ("combine", t, k)
+    ops.raise_on_status()
+    cctx.close()
+
     # tensor-parallel model: fused kernels vs NCCL collectives on the same weights
     cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], hidden_size=512, num_attention_heads=8,
                                    num_key_value_heads=2, intermediate_size=1024))

@@ -727,23 +727,35 @@ size_t zb_decode_scratch_bytes(int batch, int num_q_heads, int head_dim, int num
   return static_cast<size_t>(batch) * num_q_heads * num_splits * (head_dim + 2) * sizeof(float);
 }
 
-// Plans the split of the KV range: returns the chunk length in 16-key blocks such that the
-// CTAs (batch * kv_heads * chunks) cover the SMs a few times over; *max_chunks receives the
-// chunk count of the longest possible sequence (the grid's second dimension).
+// Plans the split of the KV range: returns the chunk length in 16-key blocks that minimises the
+// modelled time; *max_chunks receives the chunk count of the longest possible sequence (the grid's
+// second dimension).
 int zb_decode_plan_chunks(int batch, int num_kv_heads, int max_seq_len, int num_sms, int* max_chunks) {
-  const int base = batch * num_kv_heads;
-  // 512-key chunks amortise a CTA's fixed cost (Q fragments, cross-warp merge, partial
-  // write); go down to 256 only when that leaves fewer CTAs than two per SM
-  int chunk_keys = 512;
-  if (static_cast<long long>(base) * ((max_seq_len / 2 + chunk_keys - 1) / chunk_keys) < 2ll * num_sms)
-    chunk_keys = 256;
-  int mc = (max_seq_len + chunk_keys - 1) / chunk_keys;
-  while (mc > 64) {      // bound the scratch and the merge loop
-    chunk_keys <<= 1;
-    mc = (max_seq_len + chunk_keys - 1) / chunk_keys;
+  // Cost model fitted to measurements on B200 (batch 32 x 8 KV heads x 1 344 keys and 128 x 4 x 1 152, 1 to 7
+  // chunks): an SM streams K and V at about 45 GB/s whatever the number of resident CTAs (0.0114 us per key of
+  // 128-dim bf16 K + V), a CTA of a split sequence pays about 2.5 us more (partial write, fence, ticket) and
+  // the merge about 3 us once.  Splitting therefore only pays when there are too few (sequence, KV head)
+  // pairs to occupy the SMs.
+  const long long base = static_cast<long long>(batch) * num_kv_heads;
+  const double us_per_key = 0.0114, cta_fixed_us = 2.5, merge_us = 3.0;
+  int best_mc = 1, best_keys = (max_seq_len + 63) / 64 * 64;
+  double best_t = 1e30;
+  for (int mc = 1; mc <= 64; ++mc) {
+    int keys = (max_seq_len + mc - 1) / mc;
+    keys = (keys + 63) / 64 * 64;                       // whole 64-key pages per chunk
+    if (mc > 1 && keys < 128) break;
+    const int real_mc = (max_seq_len + keys - 1) / keys;
+    if (real_mc < mc) continue;                         // same plan as a smaller mc
+    const long long per_sm = (base * real_mc + num_sms - 1) / num_sms;
+    const double t = per_sm * (keys * us_per_key + (real_mc > 1 ? cta_fixed_us : 0.0)) + (real_mc > 1 ? merge_us : 0.0);
+    if (t < best_t - 1e-9) {
+      best_t = t;
+      best_mc = real_mc;
+      best_keys = keys;
+    }
   }
-  if (max_chunks) *max_chunks = mc < 1 ? 1 : mc;
-  return chunk_keys / 16;
+  if (max_chunks) *max_chunks = best_mc;
+  return best_keys / 16;
 }
 
 // kept for callers that think in splits: number of chunks the plan uses for max_seq_len

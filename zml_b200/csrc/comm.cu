@@ -139,11 +139,12 @@ ZbArContext* zb_ar_ctx_create(int rank, int world, void* const* heap, size_t rec
   c->done_flag_off = done_flag_off;
   c->max_tiles = max_tiles;
   uint32_t* ctr = nullptr;
-  if (cudaMalloc(&ctr, 4 * sizeof(uint32_t)) != cudaSuccess) {
+  if (cudaMalloc(&ctr, 8 * sizeof(uint32_t)) != cudaSuccess) {
     delete c;
     return nullptr;
   }
-  const uint32_t init[4] = {1u, 0u, 1u, 0u};   // {gemm epoch, exit ticket, barrier epoch, unused}
+  // {gemm epoch, exit ticket, barrier epoch, unused, combine epoch, combine exit ticket, unused, unused}
+  const uint32_t init[8] = {1u, 0u, 1u, 0u, 1u, 0u, 0u, 0u};
   cudaMemcpy(ctr, init, sizeof(init), cudaMemcpyHostToDevice);
   c->epoch = ctr;
   c->exit_ticket = ctr + 1;

@@ -130,6 +130,16 @@ ZB_DEVICE bool zb_mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* a
 // No load in this library carries a cluster-multicast qualifier.
 // The innermost coordinate times the element size must be a multiple of 16 B.
 // ----------------------------------------------------------------------------
+// Untiled bulk copy global -> shared of `bytes` contiguous bytes (both addresses 16-byte aligned,
+// size a multiple of 16), completion counted on an mbarrier.
+ZB_DEVICE void zb_bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      :
+      : "r"(zb_smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(zb_smem_u32(bar))
+      : "memory");
+}
+
 ZB_DEVICE void zb_tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x,
                               int32_t y) {
   asm volatile(
@@ -273,6 +283,21 @@ ZB_DEVICE void zb_umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, ui
       : "memory");
 }
 
+// The same MMA with the A operand in tensor memory: lane = row of A (0..127), each 32-bit column holds two
+// consecutive K elements (lower K in the low half), so one K = 16 step reads 8 columns from `tmem_a`.
+ZB_DEVICE void zb_umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // Arrives on `bar` once every tcgen05 operation issued so far by this thread is done.
 ZB_DEVICE void zb_umma_commit(uint64_t* bar) {
   asm volatile(
@@ -307,6 +332,19 @@ ZB_DEVICE void zb_tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 ZB_DEVICE void zb_tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Registers -> tensor memory: lane i of the warp writes 16 consecutive 32-bit columns of TMEM lane
+// (32 * (warp % 4) + i) starting at column `taddr`.
+ZB_DEVICE void zb_tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 "
+      "[%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+ZB_DEVICE void zb_tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor of a K-major bf16 tile written by TMA with the
 // 128-byte swizzle: rows of 64 elements (128 B), 8-row groups 1024 B apart.

@@ -1063,18 +1063,25 @@ int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, in
 
 // Byte matrix [rows, row_bytes] -> tensor map with a (box_bytes x box_rows) box, no swizzle (packed
 // sub-byte data such as NVFP4 codes).  row_bytes and box_bytes multiples of 16.
-int zb_make_tmap_u8_2d(CUtensorMap* out, const void* base, long long rows, long long row_bytes, int box_bytes, int box_rows) {
+// `swizzle128`: rows of the box are 128 bytes and land with the 128-byte swizzle (16-byte chunk j of row r at j ^ (r % 8)).
+int zb_make_tmap_u8_2d_ex(CUtensorMap* out, const void* base, long long rows, long long row_bytes, int box_bytes, int box_rows,
+                          int swizzle128) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -1;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_bytes % 16) != 0 || (box_bytes % 16) != 0 || box_rows > 256) return -2;
+  if (swizzle128 && box_bytes != 128) return -2;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_bytes), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+int zb_make_tmap_u8_2d(CUtensorMap* out, const void* base, long long rows, long long row_bytes, int box_bytes, int box_rows) {
+  return zb_make_tmap_u8_2d_ex(out, base, rows, row_bytes, box_bytes, box_rows, 0);
 }
 
 // Paged K or V cache [slots, kv_heads, head_dim] bf16 -> 4-D tensor map (64 columns, slots, head_dim / 64

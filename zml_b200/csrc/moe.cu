@@ -140,6 +140,79 @@ __global__ void zb_moe_scatter_kernel(const int32_t* __restrict__ ids, int32_t* 
   }
 }
 
+// Count, prefix and scatter in one launch for the pair counts of a decode step (one CTA; every
+// thread keeps its pairs' expert and rank within the expert in registers between the phases).
+constexpr int kAlignSmallThreads = 1024;
+constexpr int kAlignSmallPerThread = 8;
+__global__ void __launch_bounds__(kAlignSmallThreads)
+zb_moe_align_small_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ meta, int32_t* __restrict__ sorted_pair,
+                          int32_t* __restrict__ pair_pos, int pairs, int e0, int e_local) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  __shared__ int32_t hist[1024];
+  __shared__ int32_t warp_sum[32];
+  const int tid = threadIdx.x;
+  hist[tid] = 0;
+  __syncthreads();
+  int ex[kAlignSmallPerThread], rank[kAlignSmallPerThread];
+#pragma unroll
+  for (int j = 0; j < kAlignSmallPerThread; ++j) {
+    const int i = tid + j * kAlignSmallThreads;
+    ex[j] = -1;
+    rank[j] = 0;
+    if (i < pairs) {
+      const int e = ids[i] - e0;
+      if (e >= 0 && e < e_local) {
+        ex[j] = e;
+        rank[j] = atomicAdd(&hist[e], 1);
+      }
+    }
+  }
+  __syncthreads();
+  // exclusive prefix of hist over 1024 entries: warp scan, scan of the warp totals, add
+  const int c = hist[tid];
+  int incl = c;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if ((tid & 31) >= o) incl += v;
+  }
+  if ((tid & 31) == 31) warp_sum[tid >> 5] = incl;
+  __syncthreads();
+  if (tid < 32) {
+    const int w = warp_sum[tid];
+    int wi = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, wi, o);
+      if (tid >= o) wi += v;
+    }
+    warp_sum[tid] = wi - w;
+  }
+  __syncthreads();
+  const int excl = incl - c + warp_sum[tid >> 5];
+  hist[tid] = excl;
+  if (tid < e_local) {
+    meta[tid] = excl;
+    meta[e_local + 1 + tid] = excl + c;        // cursors as the multi-kernel path leaves them
+  }
+  if (tid == e_local - 1) meta[e_local] = excl + c;
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kAlignSmallPerThread; ++j) {
+    const int i = tid + j * kAlignSmallThreads;
+    if (i < pairs) {
+      if (ex[j] >= 0) {
+        const int pos = hist[ex[j]] + rank[j];
+        sorted_pair[pos] = i;
+        pair_pos[i] = pos;
+      } else {
+        pair_pos[i] = -1;
+      }
+    }
+  }
+}
+
 // xs[pos, :] = x[sorted_pair[pos] / k, :]
 __global__ void __launch_bounds__(128) zb_moe_gather_kernel(const __nv_bfloat16* __restrict__ x,
                                                             const int32_t* __restrict__ sorted_pair,
@@ -183,6 +256,137 @@ __global__ void __launch_bounds__(128) zb_moe_finalize_kernel(const __nv_bfloat1
     reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * d)[i] =
         make_uint4(zb_pack_bf16x2(acc[0], acc[1]), zb_pack_bf16x2(acc[2], acc[3]), zb_pack_bf16x2(acc[4], acc[5]),
                    zb_pack_bf16x2(acc[6], acc[7]));
+  }
+}
+
+// ------------------------------------------------------------------ combine (+ all-reduce over peer memory)
+// y[t, :] = residual[t, :] + sum over ranks r of ( extra_r[t, :] + sum_j weights[t, j] * o_r[pair_pos_r[t*k + j], :] )
+//
+// One kernel for the un-permute, the routing-weight sum, the expert-parallel all-reduce and the residual
+// add.  Every rank rounds its partial row to bf16 and stores it into every peer's slot area as 8-byte
+// {two bf16, epoch} words (a word arrives whole, so the tag that says "this is launch `epoch`" needs no
+// fence and no flag); then it reads the slots the peers wrote here, waiting on the tags, and sums the
+// world's partials in rank order, so all ranks produce the same bits.  Slot areas alternate by epoch
+// parity: a rank can start launch n + 1 only after it has read everything of launch n, and it cannot
+// finish n + 1 without the peers' n + 1 words, so a peer still reading launch n is never overwritten
+// by launch n + 2.  WORLD == 1 is the single-GPU combine (no slots).
+//
+// Slot area of one parity half: [src rank][token][d / 8 vectors][4 words].
+// The reference sums expert-parallel partials with an XLA all-reduce after its MoE custom call
+// (zml/moe/moe.zig, zml/nn.zig); here the reduction rides in the combine kernel.
+constexpr uint32_t kKernelCombine = 10;
+
+struct CombineAr {
+  uint2* slots[8];          // slot area in every rank's heap ([rank] is local)
+  size_t half_words;        // 8-byte words of one parity half
+  uint32_t* epoch;
+  uint32_t* ticket;
+  int rank;
+  int world;
+};
+
+template <bool AR>
+__global__ void __launch_bounds__(128)
+zb_moe_combine_kernel(const __nv_bfloat16* __restrict__ o, const int32_t* __restrict__ pair_pos,
+                      const float* __restrict__ weights, const __nv_bfloat16* __restrict__ extra,
+                      const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ y, int tokens, int k, int d,
+                      const CombineAr ar, ZbStatus* status) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  const int t = blockIdx.x;
+  const int nvec = d / 8;
+  uint32_t epoch = 0;
+  if constexpr (AR) epoch = *reinterpret_cast<volatile uint32_t*>(ar.epoch);
+  bool timed_out = false;
+  for (int i = threadIdx.x; i < nvec; i += 128) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const int pos = pair_pos[static_cast<size_t>(t) * k + j];
+      if (pos < 0) continue;
+      const float w = weights[static_cast<size_t>(t) * k + j];
+      const uint4 v = reinterpret_cast<const uint4*>(o + static_cast<size_t>(pos) * d)[i];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = zb_unpack_bf16x2(u[q]);
+        acc[2 * q] += w * f.x;
+        acc[2 * q + 1] += w * f.y;
+      }
+    }
+    if (extra != nullptr) {
+      const uint4 v = reinterpret_cast<const uint4*>(extra + static_cast<size_t>(t) * d)[i];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = zb_unpack_bf16x2(u[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    uint4 rv = make_uint4(0u, 0u, 0u, 0u);
+    if (residual != nullptr) rv = reinterpret_cast<const uint4*>(residual + static_cast<size_t>(t) * d)[i];   // before any store: y may alias it
+    if constexpr (AR) {
+      const uint32_t mine[4] = {zb_pack_bf16x2(acc[0], acc[1]), zb_pack_bf16x2(acc[2], acc[3]), zb_pack_bf16x2(acc[4], acc[5]),
+                                zb_pack_bf16x2(acc[6], acc[7])};
+      const size_t word0 = (epoch & 1u) * ar.half_words + ((static_cast<size_t>(ar.rank) * tokens + t) * nvec + i) * 4;
+      for (int r = 0; r < ar.world; ++r) {
+        if (r == ar.rank) continue;
+        uint2* dst = ar.slots[r] + word0;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) zb_st_ll(dst + q, mine[q], epoch);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+      const uint64_t t0 = zb_globaltimer();
+      for (int r = 0; r < ar.world; ++r) {
+        uint32_t got[4] = {mine[0], mine[1], mine[2], mine[3]};
+        if (r != ar.rank) {
+          const uint2* src = ar.slots[ar.rank] + (epoch & 1u) * ar.half_words + ((static_cast<size_t>(r) * tokens + t) * nvec + i) * 4;
+          uint32_t spins = 0;
+          while (true) {
+            bool ready = true;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint2 x = zb_ld_ll(src + q);
+              got[q] = x.x;
+              ready = ready && (x.y == epoch);
+            }
+            if (ready || timed_out) break;
+            if ((++spins & 0x3f) == 0 && zb_globaltimer() - t0 > ZB_WAIT_LIMIT_NS) timed_out = true;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = zb_unpack_bf16x2(got[q]);
+          acc[2 * q] += f.x;
+          acc[2 * q + 1] += f.y;
+        }
+      }
+    }
+    if (residual != nullptr) {
+      const uint32_t u[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = zb_unpack_bf16x2(u[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * d)[i] =
+        make_uint4(zb_pack_bf16x2(acc[0], acc[1]), zb_pack_bf16x2(acc[2], acc[3]), zb_pack_bf16x2(acc[4], acc[5]),
+                   zb_pack_bf16x2(acc[6], acc[7]));
+  }
+  if constexpr (AR) {
+    if (timed_out) zb_record_error(status, ZB_ERR_FLAG_TIMEOUT, kKernelCombine, blockIdx.x, ar.rank);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t ticket = atomicAdd(ar.ticket, 1u);
+      if (ticket == gridDim.x - 1) {
+        *ar.ticket = 0u;
+        *reinterpret_cast<volatile uint32_t*>(ar.epoch) = epoch + 1u;
+      }
+    }
   }
 }
 
@@ -538,6 +742,12 @@ int zb_moe_align(const int32_t* ids, int32_t* meta, int32_t* sorted_pair, int32_
                  int e_local, void* stream) {
   if (e_local < 1 || e_local > 1024) return -61;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (pairs > 0 && pairs <= kAlignSmallThreads * kAlignSmallPerThread) {
+    zb_launch(zb_moe_align_small_kernel, dim3(1), dim3(kAlignSmallThreads), 0, s, ids, meta, sorted_pair, pair_pos, pairs, e0,
+              e_local);
+    zb_count_launch(1);
+    return static_cast<int>(cudaGetLastError());
+  }
   cudaError_t e = cudaMemsetAsync(meta, 0, sizeof(int32_t) * (2 * e_local + 2), s);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (pairs > 0) {
@@ -568,6 +778,41 @@ int zb_moe_finalize(const void* o, const int32_t* pair_pos, const float* weights
   if (d % 8 != 0) return -62;
   zb_launch(zb_moe_finalize_kernel, dim3(tokens), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), 
       reinterpret_cast<const __nv_bfloat16*>(o), pair_pos, weights, reinterpret_cast<__nv_bfloat16*>(y), tokens, k, d);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// y = residual + all-reduce over the group of (extra + un-permuted, routing-weighted expert outputs); see the kernel.
+// `ctx` null: one rank.  `slot_off` / `slot_bytes`: the slot area inside every rank's symmetric heap
+// (2 parity halves x world x tokens x d x 4 bytes at least).  extra / residual may be null; y may alias residual.
+int zb_moe_combine(const void* o, const int32_t* pair_pos, const float* weights, const void* extra, const void* residual,
+                   void* y, int tokens, int k, int d, const ZbArContext* ctx, size_t slot_off, size_t slot_bytes,
+                   void* stream) {
+  if (tokens <= 0) return 0;
+  if (d % 8 != 0) return -62;
+  ZbDeviceState* st = zb_device_state();
+  if (!st) return -20;
+  CombineAr ar = {};
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const auto* o_ = reinterpret_cast<const __nv_bfloat16*>(o);
+  const auto* ex_ = reinterpret_cast<const __nv_bfloat16*>(extra);
+  const auto* rs_ = reinterpret_cast<const __nv_bfloat16*>(residual);
+  auto* y_ = reinterpret_cast<__nv_bfloat16*>(y);
+  if (ctx == nullptr || ctx->world == 1) {
+    zb_launch(zb_moe_combine_kernel<false>, dim3(tokens), dim3(128), 0, s, o_, pair_pos, weights, ex_, rs_, y_, tokens, k, d, ar,
+              st->status);
+  } else {
+    const size_t half_words = static_cast<size_t>(ctx->world) * tokens * (d / 8) * 4;
+    if (slot_off % 16 != 0 || 2 * half_words * sizeof(uint2) > slot_bytes) return -68;
+    for (int r = 0; r < ctx->world; ++r) ar.slots[r] = reinterpret_cast<uint2*>(reinterpret_cast<char*>(ctx->heap[r]) + slot_off);
+    ar.half_words = half_words;
+    ar.epoch = ctx->epoch + 4;
+    ar.ticket = ctx->epoch + 5;
+    ar.rank = ctx->rank;
+    ar.world = ctx->world;
+    zb_launch(zb_moe_combine_kernel<true>, dim3(tokens), dim3(128), 0, s, o_, pair_pos, weights, ex_, rs_, y_, tokens, k, d, ar,
+              st->status);
+  }
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -5,10 +5,36 @@
 //
 // for the few-tokens-per-expert (decode) regime, where the expert weights are what the step
 // reads from HBM: 4.5 bits per weight instead of 16.  Same warp-specialised structure as the bf16
-// grouped kernel (moe.cu) with one more stage: a producer thread brings packed code tiles
-// (128 weight rows x 32 bytes) and activation tiles in with TMA, four de-quantising warps turn a
-// code tile into the bf16, 128-byte-swizzled operand tile that tcgen05.mma reads, one thread
-// issues the MMAs into TMEM, four warps run the epilogue.
+// grouped kernel (moe.cu) with one more stage: a producer thread brings a block of packed codes
+// and block scales (one bulk copy) and the activation tiles (TMA) of four k-blocks per stage, eight
+// de-quantising warps turn the codes into bf16 and write them with tcgen05.st straight into tensor
+// memory, where tcgen05.mma reads its A operand (a de-quantised tile never passes through shared
+// memory: at 4.5 bits per weight the shared-memory traffic of a bf16 staging tile would be four
+// times the HBM traffic), one thread issues the MMAs, four warps run the epilogue.
+//
+// The weights arrive in a tile-major layout made at load time (Nvfp4Experts, moe/ops.py): for every
+// expert, 128-row tile and 256-wide K chunk one contiguous 18 KB block
+//     [8 chunks of 16 bytes][128 rows] codes (chunk c of row r = bytes 16c .. 16c+15 of the row's 128)
+//     [128 rows][16] f8e4m3 block scales
+// which is exactly the shared-memory image the de-quantising threads read without bank conflicts, so
+// the weights of a load stage are ONE untiled bulk copy of sequential memory.
+//
+// Measured on B200, 128 experts x [1536, 2048], 8 tokens per expert: 110 us against 131 us for the bf16
+// kernel.  With the MMAs or the bit placement switched off the time drops to 82-86 us, with both off to
+// 47 us (4.8 TB/s of packed weights): the three stages do not overlap as the ring depths would allow,
+// and the tensor pipe spends about 55 cycles on each 128 x 16 x 16 MMA however A is supplied.
+//
+// De-quantisation is integer bit placement plus one packed bf16 multiply per two weights (no
+// conversion instructions, which issue at a fraction of the ALU rate):
+//   * the codes arrive re-ordered (Nvfp4Experts, moe/ops.py): in each 32-bit word of 8 weights,
+//     nibble i holds weight 2i and nibble i + 4 holds weight 2i + 1, so one shift and one mask put
+//     the exponent / mantissa bits of a PAIR at bits 8..6 of both halves of a bf16x2, and a second
+//     shift and mask put the two signs at bits 15 and 31;
+//   * those bits read as bf16 are the e2m1 value x 2^-126 (the code's sub-normal 0.5 included);
+//   * the f8e4m3 block scale shifted left by 4 reads as bf16 scale x 2^-120; two multiplies by
+//     powers of two turn it into scale x 2^117;
+//   * value bits x scale = e2m1 x scale x 2^-9, exact in bf16 (2 + 4 significant bits);
+//   * the epilogue multiplies the fp32 accumulator by (matrix scale x 2^9).
 //
 // The reference reaches this through the FlashInfer CUTLASS NVFP4 runner
 // (zml/moe/cutlass_flashinfer.zig:275-330) or XLA's scaled-dot composite (zml/nn.zig:294-398).
@@ -20,7 +46,6 @@
 #include "host_api.h"
 
 int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld, int box_rows);
-int zb_make_tmap_u8_2d(CUtensorMap* out, const void* base, long long rows, long long row_bytes, int box_bytes, int box_rows);
 
 namespace {
 
@@ -28,8 +53,11 @@ constexpr uint32_t kKernelGroupedW4 = 9;
 constexpr int kBlockP = 128;
 constexpr int kBlockK = 64;
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 320;        // producer, MMA, 4 epilogue warps, 4 de-quantising warps
-constexpr int kRawBytes = kBlockP * kBlockK / 2;      // packed codes of one weight tile
+constexpr int kDqGroups = 2;          // groups of 4 de-quantising warps; group g takes k-block g of every stage
+constexpr int kThreads = 192 + kDqGroups * 128;   // producer, MMA, 4 epilogue warps, the de-quantising warps
+constexpr int kSub = 4;              // k-blocks per load stage: 128 bytes of codes and 16 bytes of scales per weight row
+constexpr int kCodeBytes = kBlockP * kSub * kBlockK / 2;      // 16 KB of packed codes per load stage
+constexpr int kScaleBytes = kBlockP * kSub * kBlockK / 16;    // 2 KB of block scales per load stage
 
 struct W4Params {
   const int32_t* offsets;   // [e_local + 1]
@@ -39,69 +67,88 @@ struct W4Params {
   int ldo;
   __nv_bfloat16* out;
   int cap;
-  const uint8_t* scales;    // [e_local * n, k / 16] f8e4m3fn
-  const float* gscale;      // [e_local] per-matrix scale
+  const uint8_t* blocks;    // [e_local, n / 128, k / 256] blocks of 18 KB (codes, then scales)
+  const float* gscale;      // [e_local, gs_per] per-matrix scale (gs_per = 2: gate rows, up rows)
+  int gs_per;
   ZbStatus* status;
 };
 
-__host__ __device__ constexpr int w4_stages(int bn) { return bn >= 64 ? 5 : 6; }
-__host__ __device__ constexpr int w4_stage_bytes(int bn) { return (kBlockP + bn) * kBlockK * 2 + kRawBytes; }
-
-ZB_DEVICE void w4_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-ZB_DEVICE void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
-ZB_DEVICE float fp8_e4m3_to_float(uint32_t b) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(b & 0xffu), __NV_E4M3);
-  return __half2float(*reinterpret_cast<const __half*>(&h));
+// Two rings.  The LOAD ring is what hides the latency of HBM: a stage holds everything the copy engine
+// brings for 4 k-blocks of one tile (codes, block scales, the activation tiles), and the ring is as deep
+// as shared memory allows, because at 4.5 bits per weight a k-block is only 4.6 KB of HBM traffic and tens
+// of KB must be in flight per SM to reach the memory bandwidth.  The OPERAND ring holds de-quantised bf16
+// weight tiles (32 columns of tensor memory each) between the de-quantising warps and the MMA thread.
+__host__ __device__ constexpr int w4_load_stage_bytes(int bn) { return kCodeBytes + kScaleBytes + kSub * bn * kBlockK * 2; }
+__host__ __device__ constexpr int w4_load_stages(int bn) { return bn >= 64 ? 4 : (bn >= 32 ? 6 : 8); }
+constexpr int kAStages = 3;                  // operand stages; one holds the 4 k-blocks of a load stage
+constexpr int kACols = kBlockK / 2;          // 32-bit tensor-memory columns of one k-block of the operand (two bf16 per column)
+constexpr int kAStageCols = kSub * kACols;   // 128
+constexpr uint32_t kTmemACol = 128;          // accumulators in columns [0, 2 BN), operand stages in [128, 512)
+constexpr uint32_t kTmemCols = 512;          // one CTA per SM: the whole tensor memory
+__host__ __device__ constexpr int w4_smem_bytes(int bn, bool swiglu) {
+  return w4_load_stages(bn) * w4_load_stage_bytes(bn) + (swiglu ? bn * 64 * 4 : 0) + 1024 + 512;   // alignment slack + barriers
 }
 
-// 8 codes (one u32) x scale -> 8 bf16 (one 16-byte chunk)
-ZB_DEVICE uint4 dequant8(uint32_t codes, float s) {
-  uint32_t o[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __half2_raw hr = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>((codes >> (8 * i)) & 0xffu), __NV_E2M1);
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
-    o[i] = zb_pack_bf16x2(f.x * s, f.y * s);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
+ZB_DEVICE void w4_epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+ZB_DEVICE uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// byte j of s4 (an f8e4m3 block scale) -> bf16x2 with scale x 2^117 in both halves
+ZB_DEVICE uint32_t scale_pair(uint32_t s4, int j) {
+  const uint32_t b = (s4 >> (8 * j)) & 0x7fu;
+  const uint32_t bits = (b << 4) | (b << 20);                  // bf16 bits: scale x 2^-120
+  return mul_bf16x2(mul_bf16x2(bits, 0x7B807B80u), 0x7A007A00u);   // x 2^120, x 2^117
+}
+
+// 8 re-ordered codes (one u32) x scale pair -> 8 bf16 in K order (one 16-byte chunk)
+ZB_DEVICE uint4 dequant8(uint32_t c, uint32_t m2) {
+  constexpr uint32_t kMag = 0x01C001C0u, kSgn = 0x80008000u;
+  const uint32_t x0 = ((c << 6) & kMag) | ((c << 12) & kSgn);
+  const uint32_t x1 = ((c << 2) & kMag) | ((c << 8) & kSgn);
+  const uint32_t x2 = ((c >> 2) & kMag) | ((c << 4) & kSgn);
+  const uint32_t x3 = ((c >> 6) & kMag) | (c & kSgn);
+  return make_uint4(mul_bf16x2(x0, m2), mul_bf16x2(x1, m2), mul_bf16x2(x2, m2), mul_bf16x2(x3, m2));
 }
 
 template <int BN, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
-zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                              const W4Params prm) {
-  constexpr int kStages = w4_stages(BN);
-  constexpr int kStageBytes = w4_stage_bytes(BN);
-  constexpr int kTileABytes = kBlockP * kBlockK * 2;
+zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Params prm) {
+  constexpr int kLoadStages = w4_load_stages(BN);
+  constexpr int kLoadBytes = w4_load_stage_bytes(BN);
   constexpr int kTileBBytes = BN * kBlockK * 2;
-  constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);
+  static_assert(2 * BN <= static_cast<int>(kTmemACol), "accumulators below the operand tiles");
   constexpr uint32_t kIdesc = zb_make_idesc_bf16(kBlockP, BN);
   constexpr int kXchBytes = SWIGLU ? BN * 64 * 4 : 0;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  // stage s: [A bf16 tile 16 KB | B tile | raw codes 4 KB]; the raw tiles come after all operand tiles
-  uint8_t* raw_base = smem + kStages * (kTileABytes + kTileBBytes);
-  float* xch = reinterpret_cast<float*>(raw_base + kStages * kRawBytes);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xch) + kXchBytes);
-  uint64_t* empty_bar = full_bar + kStages;
-  uint64_t* raw_full = empty_bar + kStages;
-  uint64_t* raw_empty = raw_full + kStages;
-  uint64_t* tmem_full = raw_empty + kStages;
+  // load stage: [codes 16 KB | scales 2 KB | 4 activation tiles]; the activation tiles start on 1 KB
+  uint8_t* load_base = smem;
+  float* xch = reinterpret_cast<float*>(smem + kLoadStages * kLoadBytes);
+  uint64_t* load_full = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xch) + kXchBytes);
+  uint64_t* load_empty = load_full + kLoadStages;
+  uint64_t* a_full = load_empty + kLoadStages;
+  uint64_t* a_empty = a_full + kAStages;
+  uint64_t* tmem_full = a_empty + kAStages;
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_flag = tmem_holder + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb_total = prm.k / kBlockK;
+  const int lb_total = prm.k / (kBlockK * kSub);          // load stages per tile
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      zb_mbar_init(&full_bar[s], 1 + 4);     // producer (activation tile, with bytes) + one lane per de-quantising warp
-      zb_mbar_init(&empty_bar[s], 1);        // MMA commit
-      zb_mbar_init(&raw_full[s], 1);         // producer (code tile, with bytes)
-      zb_mbar_init(&raw_empty[s], 4);        // one lane per de-quantising warp
+    for (int s = 0; s < kLoadStages; ++s) {
+      zb_mbar_init(&load_full[s], 1);        // producer, with the bytes of the three copies
+      zb_mbar_init(&load_empty[s], 4 * kDqGroups + 1);   // one lane per de-quantising warp + the MMA commit (activation tiles)
+    }
+    for (int s = 0; s < kAStages; ++s) {
+      zb_mbar_init(&a_full[s], 4 * kDqGroups);   // one lane per de-quantising warp (each wrote its k-blocks of its 32 rows)
+      zb_mbar_init(&a_empty[s], 1);          // MMA commit
     }
     for (int a = 0; a < 2; ++a) {
       zb_mbar_init(&tmem_full[a], 1);
@@ -140,34 +187,36 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     }
     return false;
   };
-  auto a_tile = [&](uint32_t stage) { return smem + stage * (kTileABytes + kTileBBytes); };
+  auto codes_of = [&](uint32_t ls) { return load_base + ls * kLoadBytes; };
+  auto scales_of = [&](uint32_t ls) { return load_base + ls * kLoadBytes + kCodeBytes; };
+  auto btile_of = [&](uint32_t ls, int sub) { return load_base + ls * kLoadBytes + kCodeBytes + kScaleBytes + sub * kTileBBytes; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       zb_tma_prefetch_desc(&tmap_x);
-      zb_tma_prefetch_desc(&tmap_w);
-      uint32_t stage = 0, phase = 0;
+      uint32_t ls = 0, lphase = 0;
       Cursor c{0, 0};
       bool ok = true;
       for (int g = blockIdx.x; ok; g += gridDim.x) {
         int wt, tt;
         if (!locate(c, g, wt, tt)) break;
         const int tok0 = prm.offsets[c.e] + tt * BN;
-        const int wrow0 = c.e * prm.n + wt * kBlockP;
-        for (int kb = 0; kb < kb_total; ++kb) {
-          if (!zb_mbar_wait(&raw_empty[stage], phase ^ 1u, abort_flag) ||
-              !zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+        const uint8_t* wblock = prm.blocks + (static_cast<size_t>(c.e) * w_tiles + wt) * lb_total * (kCodeBytes + kScaleBytes);
+        for (int lb = 0; lb < lb_total; ++lb) {
+          if (!zb_mbar_wait(&load_empty[ls], lphase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
-          zb_mbar_expect_tx(&raw_full[stage], kRawBytes);
-          zb_tma_load_2d(raw_base + stage * kRawBytes, &tmap_w, &raw_full[stage], kb * (kBlockK / 2), wrow0);
-          zb_mbar_expect_tx(&full_bar[stage], kTileBBytes);
-          zb_tma_load_2d(a_tile(stage) + kTileABytes, &tmap_x, &full_bar[stage], kb * kBlockK, tok0);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+          zb_mbar_expect_tx(&load_full[ls], kCodeBytes + kScaleBytes + kSub * kTileBBytes);
+          zb_bulk_load(codes_of(ls), wblock + static_cast<size_t>(lb) * (kCodeBytes + kScaleBytes), kCodeBytes + kScaleBytes,
+                       &load_full[ls]);
+#pragma unroll
+          for (int sub = 0; sub < kSub; ++sub)
+            zb_tma_load_2d(btile_of(ls, sub), &tmap_x, &load_full[ls], (lb * kSub + sub) * kBlockK, tok0);
+          if (++ls == kLoadStages) {
+            ls = 0;
+            lphase ^= 1u;
           }
         }
       }
@@ -175,7 +224,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      uint32_t ls = 0, lphase = 0, as = 0, aphase = 0, acc = 0, acc_phase = 0;
       Cursor c{0, 0};
       bool ok = true;
       for (int g = blockIdx.x; ok; g += gridDim.x) {
@@ -184,22 +233,36 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         if (!zb_mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) break;
         zb_tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < kb_total; ++kb) {
-          if (!zb_mbar_wait(&full_bar[stage], phase, abort_flag)) {
+        for (int lb = 0; lb < lb_total && ok; ++lb) {
+          if (!zb_mbar_wait(&load_full[ls], lphase, abort_flag)) {      // the activation tiles of 4 k-blocks
+            ok = false;
+            break;
+          }
+          if (!zb_mbar_wait(&a_full[as], aphase, abort_flag)) {          // the de-quantised weights of the same 4 k-blocks
             ok = false;
             break;
           }
           zb_tc_fence_after();
-          const uint32_t sa = zb_smem_u32(a_tile(stage));
-          const uint64_t da = zb_make_desc_sw128(sa);
-          const uint64_t db = zb_make_desc_sw128(sa + kTileABytes);
+          {
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k)
-            zb_umma_f16(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
-          zb_umma_commit(&empty_bar[stage]);
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1u;
+            for (int sub = 0; sub < kSub; ++sub) {
+              const uint32_t ta = tmem_base + kTmemACol + as * kAStageCols + sub * kACols;
+              const uint64_t db = zb_make_desc_sw128(zb_smem_u32(btile_of(ls, sub)));
+#pragma unroll
+              for (int k = 0; k < kBlockK / kUmmaK; ++k)
+                zb_umma_f16_ts(tmem_d, ta + 8 * k, db + 2 * k, kIdesc, (lb > 0 || sub > 0 || k > 0) ? 1u : 0u);
+            }
+          }
+          zb_umma_commit(&a_empty[as]);
+          if (++as == kAStages) {
+            as = 0;
+            aphase ^= 1u;
+          }
+          if (!ok) break;
+          zb_umma_commit(&load_empty[ls]);
+          if (++ls == kLoadStages) {
+            ls = 0;
+            lphase ^= 1u;
           }
         }
         if (!ok) break;
@@ -210,43 +273,60 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     }
   } else if (warp >= 6) {
     // ------------------------------------------------------------------ de-quantisers: thread = weight row
-    const int r = threadIdx.x - 192;                        // 0..127
-    uint32_t stage = 0, phase = 0;
+    // every group of four warps de-quantises its share of the four k-blocks of a stage (four groups measured
+    // slower than two: 119 vs 110 us on 128 experts x 1536 x 2048)
+    const int group = (warp - 6) >> 2;
+    const int r = (warp & 3) * 32 + lane;                  // a warp reaches the 32 tensor-memory lanes of its quarter
+    const uint32_t ta_row = tmem_base + kTmemACol + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    uint32_t ls = 0, lphase = 0, as = 0, aphase = 0;
     Cursor c{0, 0};
     bool ok = true;
     for (int g = blockIdx.x; ok; g += gridDim.x) {
       int wt, tt;
       if (!locate(c, g, wt, tt)) break;
-      const int wrow = c.e * prm.n + wt * kBlockP + r;
-      const float gs = prm.gscale != nullptr ? prm.gscale[c.e] : 1.f;
-      const uint32_t* srow = reinterpret_cast<const uint32_t*>(prm.scales + static_cast<size_t>(wrow) * (prm.k / 16));
-      uint32_t s_next = __ldg(srow);                        // the 4 block scales of k-block 0
-      for (int kb = 0; kb < kb_total; ++kb) {
-        const uint32_t s4 = s_next;
-        if (kb + 1 < kb_total) s_next = __ldg(srow + kb + 1);
-        if (!zb_mbar_wait(&raw_full[stage], phase, abort_flag) || !zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+      for (int lb = 0; lb < lb_total && ok; ++lb) {
+        if (!zb_mbar_wait(&load_full[ls], lphase, abort_flag)) {
           ok = false;
           break;
         }
-        const uint4* raw = reinterpret_cast<const uint4*>(raw_base + stage * kRawBytes + r * 32);
-        const uint4 c0 = raw[0], c1 = raw[1];
-        const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        // operand tile: 8-row atoms of 1 KB, 128-byte rows, 16-byte chunk j at (j ^ (row % 8))
-        uint8_t* arow = a_tile(stage) + (r >> 3) * 1024 + (r & 7) * 128;
+        const uint4* crow = reinterpret_cast<const uint4*>(codes_of(ls)) + r;      // chunk c of this row at crow[c * 128]
+        const uint4 sc = *reinterpret_cast<const uint4*>(scales_of(ls) + r * 16);
+        const uint32_t s4s[kSub] = {sc.x, sc.y, sc.z, sc.w};
+        if (!zb_mbar_wait(&a_empty[as], aphase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        zb_tc_fence_after();
+        {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float s = fp8_e4m3_to_float(s4 >> (8 * (j >> 1))) * gs;
-          *reinterpret_cast<uint4*>(arow + ((j ^ (r & 7)) << 4)) = dequant8(cw[j], s);
+          for (int sub = 0; sub < kSub; ++sub) {
+            if ((sub % kDqGroups) != group) continue;
+            const uint4 c0 = crow[(2 * sub) * kBlockP];
+            const uint4 c1 = crow[(2 * sub + 1) * kBlockP];
+            const uint32_t cw[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            uint32_t v[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint4 d = dequant8(cw[j], scale_pair(s4s[sub], j >> 1));
+              v[4 * j] = d.x, v[4 * j + 1] = d.y, v[4 * j + 2] = d.z, v[4 * j + 3] = d.w;
+            }
+            zb_tmem_st16(ta_row + as * kAStageCols + sub * kACols, v);
+            zb_tmem_st16(ta_row + as * kAStageCols + sub * kACols + 16, v + 16);
+          }
         }
-        fence_proxy_async();                                 // generic-proxy writes -> visible to the tensor core's reads
+        zb_tmem_st_wait();
+        zb_tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          zb_mbar_arrive(&full_bar[stage]);
-          zb_mbar_arrive(&raw_empty[stage]);
+        if (lane == 0) zb_mbar_arrive(&a_full[as]);
+        if (++as == kAStages) {
+          as = 0;
+          aphase ^= 1u;
         }
-        if (++stage == kStages) {
-          stage = 0;
-          phase ^= 1u;
+        __syncwarp();
+        if (lane == 0) zb_mbar_arrive(&load_empty[ls]);      // this warp has read its codes and scales of the stage
+        if (++ls == kLoadStages) {
+          ls = 0;
+          lphase ^= 1u;
         }
       }
     }
@@ -267,6 +347,9 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       const int off_e = prm.offsets[c.e];
       const int end_e = min(prm.offsets[c.e + 1], prm.cap);
       const int tok0 = off_e + tt * BN;
+      // matrix scale x 2^9; with two scales per expert the up rows (64..127 of the tile) take the second
+      const float oscale = (prm.gscale != nullptr ? prm.gscale[c.e * prm.gs_per + ((SWIGLU && row_in_tile >= 64) ? prm.gs_per - 1 : 0)]
+                                                  : 1.f) * 512.f;
       if constexpr (!SWIGLU) {
         const int feat = wt * kBlockP + row_in_tile;
 #pragma unroll 1
@@ -277,7 +360,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
-            if (tok < end_e) prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(__uint_as_float(rr[j]));
+            if (tok < end_e) prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(__uint_as_float(rr[j]) * oscale);
           }
         }
       } else {
@@ -291,7 +374,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           zb_tmem_ld_wait();
           if (is_up) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) xch[(c0 + j) * 64 + (row_in_tile - 64)] = __uint_as_float(rr[j]);
+            for (int j = 0; j < 16; ++j) xch[(c0 + j) * 64 + (row_in_tile - 64)] = __uint_as_float(rr[j]) * oscale;
           }
           w4_epi_bar();
           if (!is_up) {
@@ -299,7 +382,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
             for (int j = 0; j < 16; ++j) {
               const int tok = tok0 + c0 + j;
               if (tok < end_e) {
-                const float gt = __uint_as_float(rr[j]);
+                const float gt = __uint_as_float(rr[j]) * oscale;
                 const float up = xch[(c0 + j) * 64 + row_in_tile];
                 prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(gt / (1.f + __expf(-gt)) * up);
               }
@@ -331,15 +414,16 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
 }
 
 template <int BN, bool SWIGLU>
-int launch_w4(const CUtensorMap& tx, const CUtensorMap& tw, const W4Params& prm, int grid, cudaStream_t s) {
-  constexpr int smem = w4_stages(BN) * w4_stage_bytes(BN) + (SWIGLU ? BN * 64 * 4 : 0) + 1024 + 256;
+int launch_w4(const CUtensorMap& tx, const W4Params& prm, int grid, cudaStream_t s) {
+  constexpr int smem = w4_smem_bytes(BN, SWIGLU);
+  static_assert(smem <= 232448, "shared memory of one CTA");
   static bool configured = false;
   if (!configured) {
     cudaError_t e = zb_config_smem(zb_moe_grouped_gemm_w4_kernel<BN, SWIGLU>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  zb_launch(zb_moe_grouped_gemm_w4_kernel<BN, SWIGLU>, dim3(grid), dim3(kThreads), smem, s, tx, tw, prm);
+  zb_launch(zb_moe_grouped_gemm_w4_kernel<BN, SWIGLU>, dim3(grid), dim3(kThreads), smem, s, tx, prm);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -348,16 +432,18 @@ int launch_w4(const CUtensorMap& tx, const CUtensorMap& tw, const W4Params& prm,
 
 extern "C" {
 
-// xs [cap, k] bf16 rows grouped by expert (offsets [e_local + 1]); codes [e_local * n, k / 2] packed e2m1
-// (low nibble first); scales [e_local * n, k / 16] f8e4m3fn; gscale [e_local] fp32 or null.
+// xs [cap, k] bf16 rows grouped by expert (offsets [e_local + 1]); blocks [e_local, n / 128, k / 256, 18432]
+// bytes: the tile-major packed e2m1 codes and f8e4m3fn block scales (see the head of this file); gscale
+// [e_local, gs_per] fp32 or null (gs_per = 2 with `swiglu`: one scale for the gate rows, one for the up rows).
 // out [cap, ldo] bf16; with `swiglu` the weight rows are interleaved [64 gate | 64 up] per 128 and the
-// output has n / 2 features.  k a multiple of 64, n a multiple of 128.  Few tokens per expert only
+// output has n / 2 features.  k a multiple of 256, n a multiple of 128.  Few tokens per expert only
 // (tiles of 16 / 32 / 64 tokens).
-int zb_moe_grouped_gemm_w4(const void* xs, const void* codes, const void* scales, const float* gscale, void* out,
-                           const int32_t* offsets, int e_local, int n, int k, int cap, int ldo, int swiglu,
+int zb_moe_grouped_gemm_w4(const void* xs, const void* blocks, const float* gscale, int gs_per,
+                           void* out, const int32_t* offsets, int e_local, int n, int k, int cap, int ldo, int swiglu,
                            int avg_tokens, void* stream) {
   if (cap <= 0 || e_local <= 0) return 0;
-  if (k % 64 != 0 || n % kBlockP != 0 || ldo % 8 != 0) return -66;
+  if (k % (kBlockK * kSub) != 0 || n % kBlockP != 0 || ldo % 8 != 0) return -66;
+  if (gs_per != 1 && !(gs_per == 2 && swiglu)) return -67;
   ZbDeviceState* st = zb_device_state();
   if (!st) return -20;
   int bn = 16;
@@ -370,17 +456,17 @@ int zb_moe_grouped_gemm_w4(const void* xs, const void* codes, const void* scales
   prm.ldo = ldo;
   prm.out = reinterpret_cast<__nv_bfloat16*>(out);
   prm.cap = cap;
-  prm.scales = reinterpret_cast<const uint8_t*>(scales);
   prm.gscale = gscale;
+  prm.gs_per = gs_per;
   prm.status = st->status;
-  CUtensorMap tx, tw;
+  if ((reinterpret_cast<uintptr_t>(blocks) & 15) != 0) return -66;
+  prm.blocks = reinterpret_cast<const uint8_t*>(blocks);
+  CUtensorMap tx;
   int rc = zb_make_tmap_bf16_2d(&tx, xs, cap, k, k, bn);
-  if (rc != 0) return rc;
-  rc = zb_make_tmap_u8_2d(&tw, codes, static_cast<long long>(e_local) * n, k / 2, kBlockK / 2, kBlockP);
   if (rc != 0) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = st->num_sms;
-#define ZB_W4(BN_) return swiglu ? launch_w4<BN_, true>(tx, tw, prm, grid, s) : launch_w4<BN_, false>(tx, tw, prm, grid, s);
+#define ZB_W4(BN_) return swiglu ? launch_w4<BN_, true>(tx, prm, grid, s) : launch_w4<BN_, false>(tx, prm, grid, s);
   switch (bn) {
     case 16: ZB_W4(16)
     case 32: ZB_W4(32)

@@ -143,6 +143,11 @@ class Qwen3MoeModel(LlamaModel):
                 lw.q_norm = get(p + "self_attn.q_norm.weight")
                 lw.k_norm = get(p + "self_attn.k_norm.weight")
             lw.o = get(p + "self_attn.o_proj.weight", cols=(q0, q1))
+            if self._has_nvfp4_experts(store, prefix + p):
+                lw.extra = {"router": get(p + "mlp.gate.weight")}
+                self._load_nvfp4_experts(store, prefix + p, lw)
+                self.layers.append(lw)
+                continue
             if store.has_key(prefix + p + "mlp.experts.gate_up_proj"):
                 # fused layout: gate_up_proj [E, 2F, d] with [gate | up] rows, down_proj [E, d, F]
                 gu = get(p + "mlp.experts.gate_up_proj", rows=(self.e0, self.e0 + self.e_local))
@@ -160,6 +165,39 @@ class Qwen3MoeModel(LlamaModel):
                         "gate_up": moe.interleave_gate_up(gate_s, up_s), "down": down_s.contiguous()}
             self.layers.append(lw)
         return self
+
+    # NVFP4 expert checkpoints: per expert and projection a packed u8 weight [N, K / 2], f8e4m3fn block scales
+    # [N, K / 16] and one float32 matrix scale, in either of the two common spellings:
+    #   weight + weight_scale + weight_scale_2          (w = code x weight_scale x weight_scale_2)
+    #   weight_packed + weight_scale + weight_global_scale   (w = code x weight_scale / weight_global_scale)
+    def _has_nvfp4_experts(self, store, layer_prefix: str) -> bool:
+        base = layer_prefix + f"mlp.experts.{self.e0}.gate_proj."
+        return store.has_key(base + "weight_scale") and (store.has_key(base + "weight_scale_2") or
+                                                         store.has_key(base + "weight_global_scale"))
+
+    def _load_nvfp4_experts(self, store, layer_prefix: str, lw: LayerWeights) -> None:
+        dev = self.device
+
+        def proj(name: str):
+            codes, scales, gs = [], [], []
+            for e in range(self.e0, self.e0 + self.e_local):
+                base = layer_prefix + f"mlp.experts.{e}.{name}."
+                packed = base + ("weight_packed" if store.has_key(base + "weight_packed") else "weight")
+                codes.append(store.load_tensor(packed, device=dev).view(torch.uint8))
+                scales.append(store.load_tensor(base + "weight_scale", device=dev).view(torch.float8_e4m3fn))
+                if store.has_key(base + "weight_scale_2"):
+                    gs.append(store.load_tensor(base + "weight_scale_2", device=dev).float().reshape(()))
+                else:
+                    gs.append(1.0 / store.load_tensor(base + "weight_global_scale", device=dev).float().reshape(()))
+            return torch.stack(codes), torch.stack(scales), torch.stack(gs)
+
+        gu = moe.Nvfp4Experts.from_checkpoint_gate_up(proj("gate_proj"), proj("up_proj"))
+        dc, ds, dg = proj("down_proj")
+        e, n, kb = dc.shape
+        dn = moe.Nvfp4Experts.from_checkpoint(dc, ds, dg, e, n, kb * 2)
+        lw.extra["gate_up"] = gu.dequantize(self.dtype)
+        lw.extra["down"] = dn.dequantize(self.dtype)
+        lw.extra["w4"] = (gu, dn)
 
     def state_dict_hf(self) -> dict:
         from ..moe.ops import deinterleave_gate_up

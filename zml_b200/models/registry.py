@@ -43,7 +43,9 @@ def build_model(name: str, comm: Optional[Comm] = None, device="cuda", seed: int
         _baseline.enable(True)
     elif fused and comm.world > 1 and torch.device(device).type == "cuda":
         from ..parallel import symm
-        comm.fused = symm.SymmetricContext.create(comm, model.config.hidden_size, staging_elems=512 * model.config.hidden_size)
+        is_moe = getattr(model.config, "num_experts", 0) > 0
+        comm.fused = symm.SymmetricContext.create(comm, model.config.hidden_size, staging_elems=512 * model.config.hidden_size,
+                                                  combine_tokens=256 if is_moe else 0)
     return model
 
 

@@ -155,49 +155,138 @@ def grouped_gemm(xs: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, swiglu: 
     return out
 
 
+_KERNEL_NIBBLE_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)     # nibble position p of a 32-bit word holds weight _KERNEL_NIBBLE_ORDER[p]
+
+
+def nvfp4_codes_to_kernel_order(codes: torch.Tensor) -> torch.Tensor:
+    """Packed e2m1 codes [R, K / 2] (two per byte, low nibble first) -> the same codes with the 8
+    nibbles of every 4 bytes re-ordered to (w0 w2 w4 w6 w1 w3 w5 w7), the order the grouped GEMM
+    de-quantises with one shift and one mask per weight pair (csrc/moe_w4.cu)."""
+    r, kb = codes.shape
+    assert kb % 4 == 0
+    b = codes.reshape(r, kb // 4, 4)
+    nib = torch.stack([b & 0xF, b >> 4], dim=-1).reshape(r, kb // 4, 8)        # weight order
+    nib = nib[..., list(_KERNEL_NIBBLE_ORDER)].reshape(r, kb // 4, 4, 2)
+    return (nib[..., 0] | (nib[..., 1] << 4)).reshape(r, kb).contiguous()
+
+
+def nvfp4_codes_from_kernel_order(codes: torch.Tensor) -> torch.Tensor:
+    r, kb = codes.shape
+    b = codes.reshape(r, kb // 4, 4)
+    nib = torch.stack([b & 0xF, b >> 4], dim=-1).reshape(r, kb // 4, 8)        # kernel order
+    inv = [0] * 8
+    for pos, w in enumerate(_KERNEL_NIBBLE_ORDER):
+        inv[w] = pos
+    nib = nib[..., inv].reshape(r, kb // 4, 4, 2)
+    return (nib[..., 0] | (nib[..., 1] << 4)).reshape(r, kb).contiguous()
+
+
+W4_K_MULTIPLE = 256         # NVFP4 kernel: one load stage is 4 k-blocks of 64 (16 bytes of block scales per weight row)
+W4_BLOCK_BYTES = 128 * 128 + 128 * 16      # one (128 rows x 256 K) block: 16 KB of codes + 2 KB of block scales
+
+
+def nvfp4_pack_blocks(codes: torch.Tensor, scales: torch.Tensor, e: int, n: int, k: int) -> torch.Tensor:
+    """Checkpoint-order codes [E * N, K / 2] and f8e4m3fn scales [E * N, K / 16] -> the tile-major
+    layout the grouped GEMM streams (csrc/moe_w4.cu): uint8 [E, N / 128, K / 256, 18432], each block
+    [8 chunks][128 rows][16 bytes] of nibble-re-ordered codes, then [128 rows][16] scales."""
+    assert n % 128 == 0 and k % 256 == 0
+    c = nvfp4_codes_to_kernel_order(codes.reshape(e * n, k // 2)).reshape(e, n // 128, 128, k // 256, 8, 16)
+    c = c.permute(0, 1, 3, 4, 2, 5).reshape(e, n // 128, k // 256, 128 * 128)
+    sc = scales.reshape(e * n, k // 16).view(torch.uint8).reshape(e, n // 128, 128, k // 256, 16)
+    sc = sc.permute(0, 1, 3, 2, 4).reshape(e, n // 128, k // 256, 128 * 16)
+    return torch.cat([c, sc], -1).contiguous()
+
+
+def nvfp4_unpack_blocks(blocks: torch.Tensor, e: int, n: int, k: int):
+    """Inverse of `nvfp4_pack_blocks`: (codes [E * N, K / 2] in checkpoint order, scales [E * N, K / 16])."""
+    c = blocks[..., :128 * 128].reshape(e, n // 128, k // 256, 8, 128, 16).permute(0, 1, 4, 2, 3, 5).reshape(e * n, k // 2)
+    sc = blocks[..., 128 * 128:].reshape(e, n // 128, k // 256, 128, 16).permute(0, 1, 3, 2, 4).reshape(e * n, k // 16)
+    return nvfp4_codes_from_kernel_order(c.contiguous()), sc.contiguous().view(torch.float8_e4m3fn)
+
+
 class Nvfp4Experts:
-    """Expert weights [E, N, K] in NVFP4: packed e2m1 codes [E * N, K / 2] (low nibble first), one
-    f8e4m3fn scale per 16 values [E * N, K / 16], one float32 scale per expert matrix [E]."""
+    """Expert weights [E, N, K] in NVFP4: e2m1 codes, one f8e4m3fn scale per 16 values along K, and
+    float32 matrix scales [E, P]: P = 1, or P = 2 for an interleaved gate|up matrix whose gate and up
+    halves were quantised separately (rows 0-63 of every 128 take scale 0, rows 64-127 scale 1).
+    Held as `blocks` (`nvfp4_pack_blocks`, what the kernel streams) when N is a multiple of 128 and K
+    of 256; otherwise as checkpoint-order `codes` [E * N, K / 2] and `scales` [E * N, K / 16], which
+    only the de-quantising fallback reads."""
 
     def __init__(self, codes: torch.Tensor, scales: torch.Tensor, gscale: torch.Tensor, e: int, n: int, k: int):
-        self.codes, self.scales, self.gscale = codes, scales, gscale
         self.e, self.n, self.k = e, n, k
+        self.gscale = gscale.reshape(e, -1).float().contiguous()
+        assert self.gscale.shape[1] in (1, 2)
+        codes = codes.reshape(e * n, k // 2)
+        scales = scales.reshape(e * n, k // 16)
+        self.kernel_ready = n % 128 == 0 and k % W4_K_MULTIPLE == 0
+        if self.kernel_ready:
+            self.blocks, self.codes, self.scales = nvfp4_pack_blocks(codes, scales, e, n, k), None, None
+        else:
+            self.blocks, self.codes, self.scales = None, codes.contiguous(), scales.contiguous()
+
+    # kept for callers that name where the data comes from
+    from_checkpoint = classmethod(lambda cls, codes, scales, gscale, e, n, k: cls(codes, scales, gscale, e, n, k))
+
+    @staticmethod
+    def from_checkpoint_gate_up(gate, up) -> "Nvfp4Experts":
+        """gate, up: (codes [E, F, K / 2], scales [E, F, K / 16], gscale [E]) of separately quantised
+        projections -> one interleaved gate|up matrix [E, 2F, K] with two matrix scales per expert."""
+        (gc, gs, gg), (uc, us, ug) = gate, up
+        e, f, kb = gc.shape
+        codes = interleave_gate_up(gc, uc)
+        scales = interleave_gate_up(gs.view(torch.uint8), us.view(torch.uint8)).view(torch.float8_e4m3fn)
+        gscale = torch.stack([gg.reshape(e).float(), ug.reshape(e).float()], 1)
+        return Nvfp4Experts(codes, scales, gscale, e, 2 * f, kb * 2)
 
     @staticmethod
     def quantize(w: torch.Tensor) -> "Nvfp4Experts":
         from ..nn import quant as Q
         e, n, k = w.shape
-        codes = torch.empty((e * n, k // 2), dtype=torch.uint8, device=w.device)
-        scales = torch.empty((e * n, k // 16), dtype=torch.float8_e4m3fn, device=w.device)
-        gs = torch.empty(e, dtype=torch.float32, device=w.device)
-        for i in range(e):
-            c, s, g = Q.quantize_weight_nvfp4(w[i])
-            codes[i * n:(i + 1) * n], scales[i * n:(i + 1) * n], gs[i] = c, s, g
+        codes, scales, gs = Q.quantize_weight_nvfp4(w)
         return Nvfp4Experts(codes, scales, gs, e, n, k)
+
+    def checkpoint_arrays(self):
+        """(codes [E * N, K / 2] low nibble = even K index, scales [E * N, K / 16])."""
+        if self.blocks is not None:
+            return nvfp4_unpack_blocks(self.blocks, self.e, self.n, self.k)
+        return self.codes, self.scales
+
+    def row_scales(self, i: int) -> torch.Tensor:
+        """Matrix scale of every row of expert i, [N, 1]."""
+        g = self.gscale[i]
+        if g.numel() == 1:
+            return g.reshape(1, 1).expand(self.n, 1)
+        part = (torch.arange(self.n, device=g.device) // 64) % 2
+        return g[part].reshape(self.n, 1)
 
     def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
         from ..nn import quant as Q
-        out = torch.empty((self.e, self.n, self.k), dtype=dtype, device=self.codes.device)
+        codes, scales = self.checkpoint_arrays()
+        out = torch.empty((self.e, self.n, self.k), dtype=dtype, device=codes.device)
+        one = torch.ones((), dtype=torch.float32, device=codes.device)
         for i in range(self.e):
             sl = slice(i * self.n, (i + 1) * self.n)
-            out[i] = Q.dequantize_nvfp4(Q.unpack_e2m1(self.codes[sl]), self.scales[sl], self.gscale[i], dtype)
+            w = Q.dequantize_nvfp4(Q.unpack_e2m1(codes[sl]), scales[sl], one, torch.float32)
+            out[i] = (w * self.row_scales(i)).to(dtype)
         return out
 
     def nbytes(self) -> int:
-        return self.codes.numel() + self.scales.numel() + self.gscale.numel() * 4
+        body = self.blocks.numel() if self.blocks is not None else self.codes.numel() + self.scales.numel()
+        return body + self.gscale.numel() * 4
 
 
 def grouped_gemm_w4(xs: torch.Tensor, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8):
     """`grouped_gemm` with NVFP4 expert weights de-quantised inside the kernel (few tokens per
     expert; libzb_cuda.so: zb_moe_grouped_gemm_w4).  CPU tensors: de-quantise, then the float path."""
-    if not xs.is_cuda:
+    if not xs.is_cuda or not w.kernel_ready:
         return grouped_gemm(xs, w.dequantize(xs.dtype), meta, swiglu, avg_tokens)
     cap = xs.shape[0]
     n_out = w.n // 2 if swiglu else w.n
     assert xs.dtype == torch.bfloat16 and xs.is_contiguous() and xs.shape[1] == w.k
     out = torch.empty((cap, n_out), dtype=xs.dtype, device=xs.device)
-    _lib.check(_lib.lib().zb_moe_grouped_gemm_w4(xs.data_ptr(), w.codes.data_ptr(), w.scales.data_ptr(), w.gscale.data_ptr(),
-                                                 out.data_ptr(), meta.data_ptr(), w.e, w.n, w.k, cap, n_out, int(swiglu),
+    _lib.check(_lib.lib().zb_moe_grouped_gemm_w4(xs.data_ptr(), w.blocks.data_ptr(), w.gscale.data_ptr(),
+                                                 int(w.gscale.shape[1]), out.data_ptr(), meta.data_ptr(), w.e, w.n, w.k, cap, n_out,
+                                                 int(swiglu),
                                                  int(avg_tokens), _lib.stream_ptr()), "zb_moe_grouped_gemm_w4")
     return out
 
@@ -216,16 +305,38 @@ def finalize(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tok
     return y
 
 
+def combine(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tokens: int, k: int, extra=None, residual=None,
+            fused=None):
+    """residual + [sum over the ranks of `fused`] (extra + finalize(o, pair_pos, weights)) in one kernel
+    (libzb_cuda.so: zb_moe_combine); `fused` is a SymmetricContext whose slot area holds the exchange."""
+    if not o.is_cuda:
+        assert fused is None
+        y = finalize(o, pair_pos, weights, tokens, k)
+        if extra is not None:
+            y = y + extra
+        return y + residual if residual is not None else y
+    if fused is not None:
+        return fused.moe_combine(o, pair_pos, weights, tokens, k, extra, residual)
+    d = o.shape[1]
+    y = torch.empty((tokens, d), dtype=o.dtype, device=o.device)
+    _lib.check(_lib.lib().zb_moe_combine(o.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(),
+                                         extra.data_ptr() if extra is not None else None,
+                                         residual.data_ptr() if residual is not None else None, y.data_ptr(), tokens, k, d,
+                                         None, 0, 0, _lib.stream_ptr()), "zb_moe_combine")
+    return y
+
+
 # ---------------------------------------------------------------------- fused experts
 W4_MAX_AVG_TOKENS = 32      # NVFP4 kernel: tiles of at most 64 tokens per expert
 
 
 def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w_gate_up_il: torch.Tensor,
                   w_down: torch.Tensor, e0: int = 0, num_experts_total: Optional[int] = None,
-                  w4: Optional[tuple] = None) -> torch.Tensor:
+                  w4: Optional[tuple] = None, extra=None, residual=None, fused=None) -> torch.Tensor:
     """Mixture output of the LOCAL experts for all tokens: permute -> grouped GEMM (+SwiGLU) ->
     grouped GEMM -> un-permute x routing weight.  x [T, D] bf16; w_gate_up_il [E_local, 2F, D]
-    (interleaved, see `interleave_gate_up`); w_down [E_local, D, F]."""
+    (interleaved, see `interleave_gate_up`); w_down [E_local, D, F].  `extra`, `residual` and `fused`
+    go to `combine`: with `fused` the result is the sum over the expert-parallel group."""
     t, d = x.shape
     k = topk_ids.shape[1]
     e_local = w_gate_up_il.shape[0]
@@ -234,14 +345,16 @@ def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor,
     avg = max(1, (t * k) // max(total_e, 1))
     meta, sorted_pair, pair_pos = moe_align(topk_ids, e0, e_local)
     xs = gather(x, sorted_pair, meta, e_local, k, cap)
-    if w4 is not None and avg <= W4_MAX_AVG_TOKENS:
+    if w4 is not None and avg <= W4_MAX_AVG_TOKENS and w4[0].kernel_ready and w4[1].kernel_ready:
         # few tokens per expert: the step is bound by reading expert weights - read them as NVFP4
         h = grouped_gemm_w4(xs, w4[0], meta, swiglu=True, avg_tokens=avg)
         o = grouped_gemm_w4(h, w4[1], meta, swiglu=False, avg_tokens=avg)
     else:
         h = grouped_gemm(xs, w_gate_up_il, meta, swiglu=True, avg_tokens=avg)
         o = grouped_gemm(h, w_down, meta, swiglu=False, avg_tokens=avg)
-    return finalize(o, pair_pos, topk_w, t, k)
+    if extra is None and residual is None and fused is None:
+        return finalize(o, pair_pos, topk_w, t, k)
+    return combine(o, pair_pos, topk_w, t, k, extra, residual, fused)
 
 
 def reference_fused_experts(x, topk_ids, topk_w, gate, up, down, e0: int = 0):
@@ -307,7 +420,14 @@ def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Ten
         if world > 1:
             y = comm.all_reduce_(y)
         return y + residual if residual is not None else y
-    y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, num_experts_total or e_local * world, w4)
+    total = num_experts_total or e_local * world
+    fused_ctx = getattr(comm, "fused", None) if world > 1 else None
+    if world == 1 and x.is_cuda and x.dtype == torch.bfloat16:
+        return fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, 0, total, w4, extra=extra_partial, residual=residual)
+    if fused_ctx is not None and x.is_cuda and x.dtype == torch.bfloat16 and fused_ctx.can_combine(x.shape[0], x.shape[1]):
+        return fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, total, w4, extra=extra_partial,
+                             residual=residual, fused=fused_ctx)
+    y = fused_experts(x, topk_ids, topk_weights, w_gate_up, w_down, rank * e_local, total, w4)
     if extra_partial is not None:
         y = y + extra_partial
     if world > 1:

@@ -76,7 +76,8 @@ class SymmetricContext:
         self.fused_max_tokens = 32
 
     @staticmethod
-    def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0) -> "SymmetricContext":
+    def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0,
+               combine_tokens: int = 0) -> "SymmetricContext":
         """Collective: every rank of `comm` must call it with the same arguments."""
         l = _lib.lib()
         self = SymmetricContext()
@@ -91,6 +92,9 @@ class SymmetricContext:
         recv_bytes = _align(max(m_pad, 256) * n_pad * 2 + w * 128 * 256 * 2)
         act_bytes = _align(max_tokens * hidden * 2)
         stg_bytes = _align(staging_elems * 2)
+        # slot area of the mixture-of-experts combine: 2 parity halves x world sources x tokens x hidden, 4 bytes per element
+        self.combine_tokens = combine_tokens
+        self.combine_bytes = _align(2 * w * combine_tokens * hidden * 4)
         self.push_off = 0
         self.done_off = push_bytes
         self.bar_off = self.done_off + done_bytes
@@ -98,7 +102,8 @@ class SymmetricContext:
         self.recv_bytes = recv_bytes
         self.act_off = [self.recv_off + recv_bytes, self.recv_off + recv_bytes + act_bytes]
         self.staging_off = self.act_off[1] + act_bytes
-        self.heap_bytes = self.staging_off + stg_bytes
+        self.combine_off = self.staging_off + stg_bytes
+        self.heap_bytes = self.combine_off + self.combine_bytes
         self.hidden, self.max_tokens = hidden, max_tokens
         p = C.c_void_p()
         _lib.check(l.zb_symm_alloc(self.heap_bytes, C.byref(p)), "zb_symm_alloc")
@@ -165,6 +170,22 @@ class SymmetricContext:
                                                    _lib.stream_ptr()), "zb_allreduce_oneshot")
         self.barrier()
         return out
+
+    def can_combine(self, tokens: int, d: int) -> bool:
+        return self.ctx is not None and 2 * self.comm.world * tokens * d * 4 <= self.combine_bytes and d % 8 == 0
+
+    def moe_combine(self, o, pair_pos, weights, tokens: int, k: int, extra=None, residual=None):
+        """All ranks: residual + sum over ranks of (extra + routing-weighted, un-permuted expert outputs), bf16
+        [tokens, d]; un-permute, all-reduce and residual add are one kernel (libzb_cuda.so: zb_moe_combine)."""
+        d = o.shape[1]
+        assert self.can_combine(tokens, d) and o.dtype == torch.bfloat16 and o.is_contiguous()
+        y = torch.empty((tokens, d), dtype=o.dtype, device=o.device)
+        _lib.check(_lib.lib().zb_moe_combine(o.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(),
+                                             extra.data_ptr() if extra is not None else None,
+                                             residual.data_ptr() if residual is not None else None, y.data_ptr(),
+                                             tokens, k, d, self.ctx, self.combine_off, self.combine_bytes,
+                                             _lib.stream_ptr()), "zb_moe_combine")
+        return y
 
     def close(self):
         l = _lib.lib()

@@ -300,7 +300,7 @@ def save_file(tensors: Mapping[str, torch.Tensor], path: str, metadata: Optional
         st = (dtype_names or {}).get(name) or _TORCH_TO_ST.get(t.dtype)
         if st is None:
             raise SafetensorsError(f"cannot store dtype {t.dtype}")
-        raw = t.view(torch.uint8).reshape(-1).numpy() if t.dtype != torch.bool else t.to(torch.uint8).reshape(-1).numpy()
+        raw = t.reshape(-1).view(torch.uint8).numpy() if t.dtype != torch.bool else t.to(torch.uint8).reshape(-1).numpy()
         shp = list((shapes or {}).get(name, t.shape))
         header[name] = {"dtype": st, "shape": [int(x) for x in shp], "data_offsets": [off, off + raw.nbytes]}
         blobs.append(raw)
