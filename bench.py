@@ -106,6 +106,19 @@ class ClockSampler:
         return out
 
 
+def tp_collectives(comm, args, baseline: bool) -> str:
+    if comm.world == 1:
+        return "none"
+    fused = getattr(comm, "fused", None)
+    if fused is None or baseline or not args.fused:
+        return "nccl"
+    tuned = fused.tuned or {}
+    note = f" (measured at start: fused {tuned.get('fused_us')} us vs GEMM+NCCL {tuned.get('nccl_us')} us per decoder layer)" if tuned else ""
+    if fused.fused_max_tokens > 0:
+        return "in-kernel (fused GEMM+all-reduce over peer memory) for decode, NCCL for prefill" + note
+    return "nccl after the GEMM" + note
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -206,9 +219,7 @@ def main() -> None:
                 "new_tokens": wl["new_tokens"], "parallelism": tp, "kv_page": page,
                 "step": "one full serving job (prefill of all prompts + greedy decode)",
                 "l2": "inputs larger than L2 (weights streamed every decode step); no flush",
-                "tp_collectives": ("in-kernel (fused GEMM+all-reduce over peer memory)"
-                                   if (comm.world > 1 and args.fused and not baseline) else
-                                   ("nccl" if comm.world > 1 else "none")),
+                "tp_collectives": tp_collectives(comm, args, baseline),
             },
             "clocks": clocks,
             "e2e": {"value": out_tokens / (wall_ms / 1e3), "unit": "tokens/s",

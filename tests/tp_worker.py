@@ -104,7 +104,7 @@ def main():
         prompts2 = [torch.randint(3, 1000, (n,), generator=torch.Generator().manual_seed(11)).tolist() for n in (21, 70)]
         got = {}
         for label, c, fused in (("tp_nccl", comm, False), ("tp_fused", comm, True), ("single", single, False)):
-            model = registry.build_model(name, c, device=dev, seed=3, fused=fused)
+            model = registry.build_model(name, c, device=dev, seed=3, fused=fused, autotune=False)
             eng = Engine(model, num_pages=32, page_size=64, max_batch=4, max_seq_len=512)
             got[label], _ = eng.generate(prompts2, 10)
             if fused and c.fused is not None:
@@ -116,10 +116,16 @@ def main():
         allo = comm.all_gather_object(got["tp_fused"])
         assert all(o == allo[0] for o in allo), name
         ops.raise_on_status()
+    # the measured choice between the fused kernel and GEMM + NCCL is the same on every rank
+    tuned = ctx.autotune_projections([512, 1024])
+    allt = comm.all_gather_object(tuned)
+    assert all(t == allt[0] for t in allt) and tuned["choice"] in ("fused", "nccl"), allt
+    assert ctx.fused_max_tokens in (0, 32)
+    ops.raise_on_status()
     ctx.close()
     comm.barrier()
     if comm.rank == 0:
-        print("TP_OK", flush=True)
+        print("TP_OK", tuned, flush=True)
     comm.finish(0)
 
 

@@ -291,6 +291,13 @@ class LlamaModel:
     def kv_cache_shape(self, num_pages: int, page_size: int):
         return (self.config.num_hidden_layers, 2, num_pages, page_size, self.hkv, self.config.hd)
 
+    def row_parallel_ks(self):
+        """Input widths (per rank) of the row-parallel projections, for `SymmetricContext.autotune`."""
+        ks = [self.hq * self.config.hd]
+        if getattr(self.config, "num_experts", 0) == 0:
+            ks.append(self.f_local)
+        return ks
+
     def row_parallel(self, a, w, residual):
         """Row-parallel linear + all-reduce + residual add: the o_proj / down_proj pattern."""
         comm = self.comm

@@ -74,6 +74,7 @@ class SymmetricContext:
         # 32-token tiles: 76.8 vs 90.6 us per Llama-8B TP8-shaped decoder layer); with 64-token tiles
         # and for prefill-sized batches the GEMM followed by an NCCL all-reduce measured faster
         self.fused_max_tokens = 32
+        self.tuned = None      # result of `autotune`, if it ran
 
     @staticmethod
     def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0,
@@ -154,6 +155,72 @@ class SymmetricContext:
             force_splits, _lib.stream_ptr())
         _lib.check(rc, "zb_gemm_ar_fused")
         return out
+
+    def autotune(self, run, tokens: int = 32, reps: int = 5, units: int = 1) -> dict:
+        """Collective.  Times `run()` - a decode-sized piece of the model that goes through
+        `LlamaModel.row_parallel`, with weights that do not fit the L2 - once with the fused GEMM + all-reduce
+        and once with the GEMM followed by the NCCL all-reduce, each as a CUDA graph, and keeps the fused path
+        (`fused_max_tokens`) only if it is not slower.  Which one wins depends on the tensor-parallel degree and
+        on the NVLink latency of the box (measured on B200, Llama-3.1-8B: 8 ranks fused 1.31x faster end to end;
+        2 ranks NCCL 10 % faster, although a chain of the projections alone has the fused kernel ahead)."""
+        comm, dev = self.comm, self.comm.device
+
+        def graph_us() -> float:
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                run()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            comm.barrier()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                run()
+            gr.replay()
+            torch.cuda.synchronize()
+            comm.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return comm.max_over_ranks(e0.elapsed_time(e1) * 1e3 / (reps * units))
+
+        self.fused_max_tokens = tokens
+        t_fused = graph_us()
+        self.fused_max_tokens = 0
+        t_nccl = graph_us()
+        self.fused_max_tokens = tokens if t_fused <= t_nccl else 0
+        self.tuned = {"fused_us": round(t_fused, 2), "nccl_us": round(t_nccl, 2), "tokens": tokens,
+                      "choice": "fused" if self.fused_max_tokens else "nccl"}
+        return self.tuned
+
+    def autotune_projections(self, ks, tokens: int = 32, chain: int = 4) -> dict:
+        """`autotune` on a stand-in for models without a plain attention layer: for every row-parallel weight
+        [hidden, k] (k in `ks`) a column-parallel GEMM [k, hidden] produces its input; `chain` such blocks."""
+        from .. import ops
+        comm, dev = self.comm, self.comm.device
+        gen = torch.Generator(device=dev).manual_seed(17)
+        blocks = []
+        for _ in range(chain):
+            for k in ks:
+                wc = torch.empty(k, self.hidden, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+                wr = torch.empty(self.hidden, k, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
+                blocks.append((wc, wr))
+        x0 = torch.empty(tokens, self.hidden, device=dev, dtype=torch.bfloat16).normal_(0, 0.5, generator=gen)
+
+        def run():
+            x = x0
+            for wc, wr in blocks:
+                a = ops.gemm(x, wc, static_w=True)
+                if a.shape[0] <= self.fused_max_tokens:
+                    x = self.gemm_allreduce(a, wr, x)
+                else:
+                    x = comm.all_reduce_(ops.gemm(a, wr, residual=x if comm.rank == 0 else None, static_w=True))
+            return x
+
+        return self.autotune(run, tokens, units=len(blocks))
 
     def barrier(self):
         """Device-side barrier across the group on the current stream."""
