@@ -102,7 +102,15 @@ def bench_gemm(a: Args) -> None:
     out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
     fns = [(lambda w=w: ops.gemm(x, w, out=out, static_w=True)) for w in ws]
     ms = timed(fns, a.iters, a.warmup)
-    report(a, ms, wb + (a.m * a.k + a.m * a.n) * 2, 2.0 * a.m * a.n * a.k, {"m": a.m, "n": a.n, "k": a.k, "copies": c})
+    import ctypes
+    from zml_b200.ops import _lib
+    plan = (ctypes.c_int * 6)()
+    _lib.lib().zb_gemm_describe_plan(a.m, a.n, a.k, plan)
+    bn = plan[1]
+    extra = {"m": a.m, "n": a.n, "k": a.k, "copies": c,
+             "plan": {"swap_ab": plan[0], "tile_tokens": bn, "grid": plan[2], "k_blocks_per_cta": plan[3], "cluster": plan[4]},
+             "cluster_capacity": {s: _lib.lib().zb_gemm_cluster_capacity(bn, s) for s in (2, 3, 4, 6, 8)} if plan[0] else {}}
+    report(a, ms, wb + (a.m * a.k + a.m * a.n) * 2, 2.0 * a.m * a.n * a.k, extra)
 
 
 def _kv(a: Args, copies: int, page: int = 64):

@@ -733,11 +733,11 @@ size_t zb_decode_scratch_bytes(int batch, int num_q_heads, int head_dim, int num
 int zb_decode_plan_chunks(int batch, int num_kv_heads, int max_seq_len, int num_sms, int* max_chunks) {
   // Cost model fitted to measurements on B200 (batch 32 x 8 KV heads x 1 344 keys and 128 x 4 x 1 152, 1 to 7
   // chunks): an SM streams K and V at about 45 GB/s whatever the number of resident CTAs (0.0114 us per key of
-  // 128-dim bf16 K + V), a CTA of a split sequence pays about 2.5 us more (partial write, fence, ticket) and
-  // the merge about 3 us once.  Splitting therefore only pays when there are too few (sequence, KV head)
-  // pairs to occupy the SMs.
+  // 128-dim bf16 K + V), one CTA alone at about 32 GB/s (0.016 us per key; 16 x 8 x 1 344: 21.7 us), a CTA of a
+  // split sequence pays about 2.5 us more (partial write, fence, ticket) and the merge about 3 us once.
+  // Splitting therefore only pays when there are too few (sequence, KV head) pairs to occupy the SMs.
   const long long base = static_cast<long long>(batch) * num_kv_heads;
-  const double us_per_key = 0.0114, cta_fixed_us = 2.5, merge_us = 3.0;
+  const double us_per_key = 0.0114, us_per_key_one_cta = 0.016, cta_fixed_us = 2.5, merge_us = 3.0;
   int best_mc = 1, best_keys = (max_seq_len + 63) / 64 * 64;
   double best_t = 1e30;
   for (int mc = 1; mc <= 64; ++mc) {
@@ -747,7 +747,8 @@ int zb_decode_plan_chunks(int batch, int num_kv_heads, int max_seq_len, int num_
     const int real_mc = (max_seq_len + keys - 1) / keys;
     if (real_mc < mc) continue;                         // same plan as a smaller mc
     const long long per_sm = (base * real_mc + num_sms - 1) / num_sms;
-    const double t = per_sm * (keys * us_per_key + (real_mc > 1 ? cta_fixed_us : 0.0)) + (real_mc > 1 ? merge_us : 0.0);
+    const double stream = per_sm * keys * us_per_key > keys * us_per_key_one_cta ? per_sm * keys * us_per_key : keys * us_per_key_one_cta;
+    const double t = stream + (real_mc > 1 ? per_sm * cta_fixed_us + merge_us : 0.0);
     if (t < best_t - 1e-9) {
       best_t = t;
       best_mc = real_mc;

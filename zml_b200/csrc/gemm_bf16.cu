@@ -1336,6 +1336,26 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   return -12;
 }
 
+// The decomposition zb_gemm_bf16 would use for [m, n, k]: out[0..5] = swap-AB, tile columns, grid, k-blocks per
+// CTA, cluster size (1: none), resident-CTA capacity of that cluster size (0 without a cluster).
+int zb_gemm_describe_plan(int m, int n, int k, int* out6) {
+  ZbDeviceState* st = zb_device_state();
+  if (st == nullptr) return -20;
+  int sw, bn, grid, upc, rr;
+  const int tiles = zb_gemm_plan(m, n, k, st->num_sms, 0, &sw, &bn, &grid, &upc, &rr);
+  int cluster = 1;
+  if (sw && rr == 0) cluster = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &grid, &upc);
+  int cap = 0;
+  if (cluster > 1) cap = bn <= 16 ? max_cluster_ctas<16>(cluster) : (bn <= 32 ? max_cluster_ctas<32>(cluster) : max_cluster_ctas<64>(cluster));
+  out6[0] = sw, out6[1] = bn, out6[2] = grid, out6[3] = upc, out6[4] = cluster, out6[5] = cap;
+  return 0;
+}
+
+// Resident-CTA capacity of the swap-AB kernel (tile of `bn` tokens) launched in clusters of `s`.
+int zb_gemm_cluster_capacity(int bn, int s) {
+  return bn <= 16 ? max_cluster_ctas<16>(s) : (bn <= 32 ? max_cluster_ctas<32>(s) : max_cluster_ctas<64>(s));
+}
+
 // Convenience entry point using the library's per-device scratch (see runtime.cu).
 int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, const void* bias,
                  int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,

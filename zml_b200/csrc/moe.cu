@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "host_api.h"
+#include "moe_tiles.cuh"
 
 int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld, int box_rows);
 
@@ -474,29 +475,20 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 
   // tiles of expert e: weight tiles x token tiles
   const int w_tiles = SWAP ? prm.n / kBlockP : prm.n / BN;
-  auto token_tiles = [&](int e) {
-    const int cnt = prm.offsets[e + 1] - prm.offsets[e];
-    return SWAP ? (cnt + BN - 1) / BN : (cnt + kBlockP - 1) / kBlockP;
-  };
+  __shared__ int32_t tile_prefix[kZbMaxExperts + 1];
+  zb_tile_prefix_build(tile_prefix, prm.offsets, prm.e_local, w_tiles, SWAP ? BN : kBlockP);
   // iterator over this CTA's tiles: global tile index g = blockIdx.x, += gridDim.x
   struct Cursor {
     int e;         // current expert
-    int base;      // global index of the expert's first tile
+    int hint;      // where the bisection for the next tile starts
   };
   auto locate = [&](Cursor& c, int g, int& wt, int& tt) -> bool {
-    while (c.e < prm.e_local) {
-      const int n_e = w_tiles * token_tiles(c.e);
-      if (g < c.base + n_e) {
-        const int local = g - c.base;
-        // token tile varies slowest so that CTAs running together share the expert's tokens
-        tt = local / w_tiles;
-        wt = local - tt * w_tiles;
-        return true;
-      }
-      c.base += n_e;
-      ++c.e;
-    }
-    return false;
+    ZbTilePos pos;
+    if (!zb_tile_locate(tile_prefix, prm.e_local, w_tiles, g, c.hint, pos)) return false;
+    c.e = pos.e;
+    wt = pos.wt;
+    tt = pos.tt;
+    return true;
   };
 
   if (warp == 0) {
@@ -824,6 +816,8 @@ int zb_moe_grouped_gemm(const void* xs, const void* w, void* out, const int32_t*
                         int cap, int ldo, int swiglu, int avg_tokens, void* stream) {
   if (cap <= 0 || e_local <= 0) return 0;
   if (k % 8 != 0 || ldo % 8 != 0) return -63;
+  if (e_local > kZbMaxExperts) return -61;
+
   ZbDeviceState* st = zb_device_state();
   if (!st) return -20;
   const bool swap = avg_tokens <= 48;

@@ -44,6 +44,7 @@
 
 #include "common.cuh"
 #include "host_api.h"
+#include "moe_tiles.cuh"
 
 int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld, int box_rows);
 
@@ -71,7 +72,10 @@ struct W4Params {
   const float* gscale;      // [e_local, gs_per] per-matrix scale (gs_per = 2: gate rows, up rows)
   int gs_per;
   ZbStatus* status;
+  unsigned long long* timeline;   // null, or [kTimelineStages][8] time stamps of CTA 0 (see zb_moe_w4_set_timeline)
 };
+
+constexpr int kTimelineStages = 64;
 
 // Two rings.  The LOAD ring is what hides the latency of HBM: a stage holds everything the copy engine
 // brings for 4 k-blocks of one tile (codes, block scales, the activation tiles), and the ring is as deep
@@ -168,24 +172,20 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   zb_pdl_launch();
   zb_pdl_wait();
 
+  unsigned long long* tl = blockIdx.x == 0 ? prm.timeline : nullptr;
   const int w_tiles = prm.n / kBlockP;
-  auto token_tiles = [&](int e) { return (prm.offsets[e + 1] - prm.offsets[e] + BN - 1) / BN; };
+  __shared__ int32_t tile_prefix[kZbMaxExperts + 1];
+  zb_tile_prefix_build(tile_prefix, prm.offsets, prm.e_local, w_tiles, BN);
   struct Cursor {
-    int e, base;
+    int e, hint;
   };
   auto locate = [&](Cursor& c, int g, int& wt, int& tt) -> bool {
-    while (c.e < prm.e_local) {
-      const int n_e = w_tiles * token_tiles(c.e);
-      if (g < c.base + n_e) {
-        const int local = g - c.base;
-        tt = local / w_tiles;
-        wt = local - tt * w_tiles;
-        return true;
-      }
-      c.base += n_e;
-      ++c.e;
-    }
-    return false;
+    ZbTilePos pos;
+    if (!zb_tile_locate(tile_prefix, prm.e_local, w_tiles, g, c.hint, pos)) return false;
+    c.e = pos.e;
+    wt = pos.wt;
+    tt = pos.tt;
+    return true;
   };
   auto codes_of = [&](uint32_t ls) { return load_base + ls * kLoadBytes; };
   auto scales_of = [&](uint32_t ls) { return load_base + ls * kLoadBytes + kCodeBytes; };
@@ -196,6 +196,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     if (lane == 0) {
       zb_tma_prefetch_desc(&tmap_x);
       uint32_t ls = 0, lphase = 0;
+      int q = 0;
       Cursor c{0, 0};
       bool ok = true;
       for (int g = blockIdx.x; ok; g += gridDim.x) {
@@ -208,6 +209,8 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
             ok = false;
             break;
           }
+          if (tl != nullptr && q < kTimelineStages) tl[q * 8 + 0] = zb_globaltimer();
+          ++q;
           zb_mbar_expect_tx(&load_full[ls], kCodeBytes + kScaleBytes + kSub * kTileBBytes);
           zb_bulk_load(codes_of(ls), wblock + static_cast<size_t>(lb) * (kCodeBytes + kScaleBytes), kCodeBytes + kScaleBytes,
                        &load_full[ls]);
@@ -225,6 +228,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       uint32_t ls = 0, lphase = 0, as = 0, aphase = 0, acc = 0, acc_phase = 0;
+      int q = 0;
       Cursor c{0, 0};
       bool ok = true;
       for (int g = blockIdx.x; ok; g += gridDim.x) {
@@ -243,6 +247,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
             break;
           }
           zb_tc_fence_after();
+          if (tl != nullptr && q < kTimelineStages) tl[q * 8 + 5] = zb_globaltimer();
           {
 #pragma unroll
             for (int sub = 0; sub < kSub; ++sub) {
@@ -260,6 +265,8 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           }
           if (!ok) break;
           zb_umma_commit(&load_empty[ls]);
+          if (tl != nullptr && q < kTimelineStages) tl[q * 8 + 6] = zb_globaltimer();
+          ++q;
           if (++ls == kLoadStages) {
             ls = 0;
             lphase ^= 1u;
@@ -279,16 +286,19 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
     const int r = (warp & 3) * 32 + lane;                  // a warp reaches the 32 tensor-memory lanes of its quarter
     const uint32_t ta_row = tmem_base + kTmemACol + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     uint32_t ls = 0, lphase = 0, as = 0, aphase = 0;
+    int q = 0;
+    unsigned long long* tlw = (lane == 0 && (warp & 3) == 2) ? tl : nullptr;      // one warp of each group stamps
     Cursor c{0, 0};
     bool ok = true;
     for (int g = blockIdx.x; ok; g += gridDim.x) {
       int wt, tt;
       if (!locate(c, g, wt, tt)) break;
-      for (int lb = 0; lb < lb_total && ok; ++lb) {
+      for (int lb = 0; lb < lb_total && ok; ++lb, ++q) {
         if (!zb_mbar_wait(&load_full[ls], lphase, abort_flag)) {
           ok = false;
           break;
         }
+        if (tlw != nullptr && group == 0 && q < kTimelineStages) tlw[q * 8 + 1] = zb_globaltimer();
         const uint4* crow = reinterpret_cast<const uint4*>(codes_of(ls)) + r;      // chunk c of this row at crow[c * 128]
         const uint4 sc = *reinterpret_cast<const uint4*>(scales_of(ls) + r * 16);
         const uint32_t s4s[kSub] = {sc.x, sc.y, sc.z, sc.w};
@@ -297,6 +307,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           break;
         }
         zb_tc_fence_after();
+        if (tlw != nullptr && group == 0 && q < kTimelineStages) tlw[q * 8 + 2] = zb_globaltimer();
         {
 #pragma unroll
           for (int sub = 0; sub < kSub; ++sub) {
@@ -315,6 +326,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           }
         }
         zb_tmem_st_wait();
+        if (tlw != nullptr && q < kTimelineStages) tlw[q * 8 + 3 + (group != 0 ? 1 : 0)] = zb_globaltimer();
         zb_tc_fence_before();
         __syncwarp();
         if (lane == 0) zb_mbar_arrive(&a_full[as]);
@@ -428,9 +440,17 @@ int launch_w4(const CUtensorMap& tx, const W4Params& prm, int grid, cudaStream_t
   return static_cast<int>(cudaGetLastError());
 }
 
+unsigned long long* g_w4_timeline = nullptr;
+
 }  // namespace
 
 extern "C" {
+
+// Phase time stamps of the next launches' CTA 0: `buf` holds 64 x 8 u64 (device memory), or null to switch off.
+// Per load stage q: [0] producer issues the copies, [1] a de-quantising warp sees them, [2] it has an operand
+// stage, [3] / [4] the two groups' tensor-memory stores are done, [5] the MMA thread has both operands, [6] it
+// has issued the MMAs and commits.  %globaltimer nanoseconds.
+void zb_moe_w4_set_timeline(void* buf) { g_w4_timeline = reinterpret_cast<unsigned long long*>(buf); }
 
 // xs [cap, k] bf16 rows grouped by expert (offsets [e_local + 1]); blocks [e_local, n / 128, k / 256, 18432]
 // bytes: the tile-major packed e2m1 codes and f8e4m3fn block scales (see the head of this file); gscale
@@ -442,6 +462,7 @@ int zb_moe_grouped_gemm_w4(const void* xs, const void* blocks, const float* gsca
                            void* out, const int32_t* offsets, int e_local, int n, int k, int cap, int ldo, int swiglu,
                            int avg_tokens, void* stream) {
   if (cap <= 0 || e_local <= 0) return 0;
+  if (e_local > kZbMaxExperts) return -61;
   if (k % (kBlockK * kSub) != 0 || n % kBlockP != 0 || ldo % 8 != 0) return -66;
   if (gs_per != 1 && !(gs_per == 2 && swiglu)) return -67;
   ZbDeviceState* st = zb_device_state();
@@ -459,6 +480,7 @@ int zb_moe_grouped_gemm_w4(const void* xs, const void* blocks, const float* gsca
   prm.gscale = gscale;
   prm.gs_per = gs_per;
   prm.status = st->status;
+  prm.timeline = g_w4_timeline;
   if ((reinterpret_cast<uintptr_t>(blocks) & 15) != 0) return -66;
   prm.blocks = reinterpret_cast<const uint8_t*>(blocks);
   CUtensorMap tx;

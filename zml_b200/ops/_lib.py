@@ -47,6 +47,9 @@ _SIGS = {
     "zb_moe_combine": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_sz, c_sz, c_p]),
     "zb_wait_probe": (c_i, [c_p, C.c_uint, c_ull, C.c_uint, c_p, c_p]),
     "zb_decode_advance": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p]),
+    "zb_moe_w4_set_timeline": (None, [c_p]),
+    "zb_gemm_describe_plan": (c_i, [c_i, c_i, c_i, c_p]),
+    "zb_gemm_cluster_capacity": (c_i, [c_i, c_i]),
     "zb_gemm_plan": (c_i, [c_i, c_i, c_i, c_i, c_i, c_p, c_p, c_p, c_p, c_p]),
     "zb_gemm_workspace_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "zb_gemm_bf16": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
