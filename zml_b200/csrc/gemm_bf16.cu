@@ -347,7 +347,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const int q0 = qt * BN;
       const int out_tile = pt * num_q + qt;
 
-      if constexpr (SWAP && BN <= 64) {
+      if constexpr (SWAP && (BN <= 64 || (!FUSED && BN <= 128))) {
         if (prm.cluster > 1) {
           // Cluster split-K: every CTA of the cluster holds a partial of the same tile.  Partials go
           // to the CTA's own shared memory (the operand ring is idle: this CTA has no other tile),
@@ -1160,14 +1160,15 @@ int g_cluster_splitk = 1;
 // Cluster split-K plan for a weight-streaming GEMM with fewer tiles than SMs: every tile is cut
 // along K over the CTAs of one cluster, which reduce it through distributed shared memory.
 // Returns the cluster size (1: keep the stream-K plan) and updates grid / units per CTA.
+int zb_gemm_cluster_capacity_of(int bn, int s);
 int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* upc) {
-  if (!g_cluster_splitk || bn > 64 || tiles >= num_sms) return 1;
+  if (!g_cluster_splitk || bn > 128 || tiles >= num_sms) return 1;
   int best = 1, best_ctas = 0;
   const int sizes[5] = {8, 6, 4, 3, 2};
   for (int i = 0; i < 5; ++i) {
     const int s = sizes[i];
     if ((kb_total + s - 1) / s < 2) continue;
-    const int cap = bn <= 16 ? max_cluster_ctas<16>(s) : (bn <= 32 ? max_cluster_ctas<32>(s) : max_cluster_ctas<64>(s));
+    const int cap = zb_gemm_cluster_capacity_of(bn, s);
     const int ctas = tiles * s;
     if (ctas > cap || ctas > num_sms) continue;
     if (ctas > best_ctas) {
@@ -1179,6 +1180,10 @@ int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* u
   *grid = best_ctas;
   *upc = (kb_total + best - 1) / best;
   return best;
+}
+
+int zb_gemm_cluster_capacity_of(int bn, int s) {
+  return bn <= 16 ? max_cluster_ctas<16>(s) : (bn <= 32 ? max_cluster_ctas<32>(s) : (bn <= 64 ? max_cluster_ctas<64>(s) : max_cluster_ctas<128>(s)));
 }
 
 // Weight tiles per CTA to pull into L2 ahead of the shared-memory ring while the preceding
@@ -1346,15 +1351,13 @@ int zb_gemm_describe_plan(int m, int n, int k, int* out6) {
   int cluster = 1;
   if (sw && rr == 0) cluster = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &grid, &upc);
   int cap = 0;
-  if (cluster > 1) cap = bn <= 16 ? max_cluster_ctas<16>(cluster) : (bn <= 32 ? max_cluster_ctas<32>(cluster) : max_cluster_ctas<64>(cluster));
+  if (cluster > 1) cap = zb_gemm_cluster_capacity_of(bn, cluster);
   out6[0] = sw, out6[1] = bn, out6[2] = grid, out6[3] = upc, out6[4] = cluster, out6[5] = cap;
   return 0;
 }
 
 // Resident-CTA capacity of the swap-AB kernel (tile of `bn` tokens) launched in clusters of `s`.
-int zb_gemm_cluster_capacity(int bn, int s) {
-  return bn <= 16 ? max_cluster_ctas<16>(s) : (bn <= 32 ? max_cluster_ctas<32>(s) : max_cluster_ctas<64>(s));
-}
+int zb_gemm_cluster_capacity(int bn, int s) { return zb_gemm_cluster_capacity_of(bn, s); }
 
 // Convenience entry point using the library's per-device scratch (see runtime.cu).
 int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, const void* bias,
