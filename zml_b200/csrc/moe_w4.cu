@@ -19,10 +19,13 @@
 // which is exactly the shared-memory image the de-quantising threads read without bank conflicts, so
 // the weights of a load stage are ONE untiled bulk copy of sequential memory.
 //
-// Measured on B200, 128 experts x [1536, 2048], 8 tokens per expert: 110 us against 131 us for the bf16
-// kernel.  With the MMAs or the bit placement switched off the time drops to 82-86 us, with both off to
-// 47 us (4.8 TB/s of packed weights): the three stages do not overlap as the ring depths would allow,
-// and the tensor pipe spends about 55 cycles on each 128 x 16 x 16 MMA however A is supplied.
+// Measured on B200, 128 experts x [1536, 2048], 8 tokens per expert: 84 us against 129 us for the bf16
+// kernel (down projection 48 against 67).  What set the pace at each step of the way: conversion
+// instructions (140 us), the shared-memory traffic of a bf16 staging tile (140), one commit per k-block
+// (135), walking the expert offsets in global memory at every tile change (110 -> 106), and one thread
+// issuing the 16 small-N MMAs of a stage (770 ns per stage; two issuing threads: 106 -> 84).  Now the bit
+// placement (about 600 ns per stage on the ALU pipe) and the tensor pipe (about 30 ns per 128 x 16 x 16
+// MMA) are level; four groups of de-quantising warps instead of two measured slower (94 us).
 //
 // De-quantisation is integer bit placement plus one packed bf16 multiply per two weights (no
 // conversion instructions, which issue at a fraction of the ALU rate):
@@ -55,7 +58,12 @@ constexpr int kBlockP = 128;
 constexpr int kBlockK = 64;
 constexpr int kUmmaK = 16;
 constexpr int kDqGroups = 2;          // groups of 4 de-quantising warps; group g takes k-block g of every stage
-constexpr int kThreads = 192 + kDqGroups * 128;   // producer, MMA, 4 epilogue warps, the de-quantising warps
+constexpr int kIssuerBWarp = 6 + 4 * kDqGroups;          // second MMA-issuing warp, after the de-quantising warps
+constexpr int kThreads = (kIssuerBWarp + 1) * 32;   // producer, MMA, 4 epilogue warps, the de-quantising warps, MMA
+// Two threads issue the MMAs of a stage (two k-blocks each, into accumulators of their own that the epilogue
+// adds) when tensor memory has room for four accumulators: one thread needs about 770 ns for the 16 small-N
+// MMAs of a stage, which was the period of the whole pipeline.
+__host__ __device__ constexpr int w4_issuers(int bn) { return bn <= 32 ? 2 : 1; }
 constexpr int kSub = 4;              // k-blocks per load stage: 128 bytes of codes and 16 bytes of scales per weight row
 constexpr int kCodeBytes = kBlockP * kSub * kBlockK / 2;      // 16 KB of packed codes per load stage
 constexpr int kScaleBytes = kBlockP * kSub * kBlockK / 16;    // 2 KB of block scales per load stage
@@ -124,7 +132,8 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   constexpr int kLoadStages = w4_load_stages(BN);
   constexpr int kLoadBytes = w4_load_stage_bytes(BN);
   constexpr int kTileBBytes = BN * kBlockK * 2;
-  static_assert(2 * BN <= static_cast<int>(kTmemACol), "accumulators below the operand tiles");
+  constexpr int kIssuers = w4_issuers(BN);
+  static_assert(2 * kIssuers * BN <= static_cast<int>(kTmemACol), "accumulators below the operand tiles");
   constexpr uint32_t kIdesc = zb_make_idesc_bf16(kBlockP, BN);
   constexpr int kXchBytes = SWIGLU ? BN * 64 * 4 : 0;
 
@@ -148,14 +157,14 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kLoadStages; ++s) {
       zb_mbar_init(&load_full[s], 1);        // producer, with the bytes of the three copies
-      zb_mbar_init(&load_empty[s], 4 * kDqGroups + 1);   // one lane per de-quantising warp + the MMA commit (activation tiles)
+      zb_mbar_init(&load_empty[s], 4 * kDqGroups + kIssuers);   // one lane per de-quantising warp + the MMA commits (activation tiles)
     }
     for (int s = 0; s < kAStages; ++s) {
       zb_mbar_init(&a_full[s], 4 * kDqGroups);   // one lane per de-quantising warp (each wrote its k-blocks of its 32 rows)
-      zb_mbar_init(&a_empty[s], 1);          // MMA commit
+      zb_mbar_init(&a_empty[s], kIssuers);   // MMA commits
     }
     for (int a = 0; a < 2; ++a) {
-      zb_mbar_init(&tmem_full[a], 1);
+      zb_mbar_init(&tmem_full[a], kIssuers);
       zb_mbar_init(&tmem_empty[a], 128);
     }
     *abort_flag = 0u;
@@ -224,9 +233,12 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == kIssuerBWarp) {
+    // ------------------------------------------------------------------ MMA issuers
+    const int issuer = warp == 1 ? 0 : 1;
+    constexpr int kSubsPer = kSub / kIssuers;
+    if (lane == 0 && issuer < kIssuers) {
+      if (issuer != 0) tl = nullptr;
       uint32_t ls = 0, lphase = 0, as = 0, aphase = 0, acc = 0, acc_phase = 0;
       int q = 0;
       Cursor c{0, 0};
@@ -236,7 +248,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         if (!locate(c, g, wt, tt)) break;
         if (!zb_mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) break;
         zb_tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_base + (acc * kIssuers + issuer) * BN;
         for (int lb = 0; lb < lb_total && ok; ++lb) {
           if (!zb_mbar_wait(&load_full[ls], lphase, abort_flag)) {      // the activation tiles of 4 k-blocks
             ok = false;
@@ -250,12 +262,13 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
           if (tl != nullptr && q < kTimelineStages) tl[q * 8 + 5] = zb_globaltimer();
           {
 #pragma unroll
-            for (int sub = 0; sub < kSub; ++sub) {
+            for (int s2 = 0; s2 < kSubsPer; ++s2) {
+              const int sub = issuer * kSubsPer + s2;
               const uint32_t ta = tmem_base + kTmemACol + as * kAStageCols + sub * kACols;
               const uint64_t db = zb_make_desc_sw128(zb_smem_u32(btile_of(ls, sub)));
 #pragma unroll
               for (int k = 0; k < kBlockK / kUmmaK; ++k)
-                zb_umma_f16_ts(tmem_d, ta + 8 * k, db + 2 * k, kIdesc, (lb > 0 || sub > 0 || k > 0) ? 1u : 0u);
+                zb_umma_f16_ts(tmem_d, ta + 8 * k, db + 2 * k, kIdesc, (lb > 0 || s2 > 0 || k > 0) ? 1u : 0u);
             }
           }
           zb_umma_commit(&a_empty[as]);
@@ -278,10 +291,9 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         if (acc == 0) acc_phase ^= 1u;
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= 6 && warp < kIssuerBWarp) {
     // ------------------------------------------------------------------ de-quantisers: thread = weight row
-    // every group of four warps de-quantises its share of the four k-blocks of a stage (four groups measured
-    // slower than two: 119 vs 110 us on 128 experts x 1536 x 2048)
+    // every group of four warps de-quantises its share of the four k-blocks of a stage
     const int group = (warp - 6) >> 2;
     const int r = (warp & 3) * 32 + lane;                  // a warp reaches the 32 tensor-memory lanes of its quarter
     const uint32_t ta_row = tmem_base + kTmemACol + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -355,7 +367,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
       w4_epi_bar();
       if (*abort_flag != 0u) break;
       zb_tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * kIssuers * BN + (static_cast<uint32_t>(quad * 32) << 16);
       const int off_e = prm.offsets[c.e];
       const int end_e = min(prm.offsets[c.e + 1], prm.cap);
       const int tok0 = off_e + tt * BN;
@@ -368,6 +380,13 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t rr[16];
           zb_tmem_ld16(taddr + c0, rr);
+          if constexpr (kIssuers == 2) {
+            uint32_t r2[16];
+            zb_tmem_ld16(taddr + BN + c0, r2);
+            zb_tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) rr[j] = __float_as_uint(__uint_as_float(rr[j]) + __uint_as_float(r2[j]));
+          }
           zb_tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -383,6 +402,13 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
         for (int c0 = 0; c0 < BN; c0 += 16) {
           uint32_t rr[16];
           zb_tmem_ld16(taddr + c0, rr);
+          if constexpr (kIssuers == 2) {
+            uint32_t r2[16];
+            zb_tmem_ld16(taddr + BN + c0, r2);
+            zb_tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) rr[j] = __float_as_uint(__uint_as_float(rr[j]) + __uint_as_float(r2[j]));
+          }
           zb_tmem_ld_wait();
           if (is_up) {
 #pragma unroll
