@@ -113,10 +113,13 @@ def tp_collectives(comm, args, baseline: bool) -> str:
     if fused is None or baseline or not args.fused:
         return "nccl"
     tuned = fused.tuned or {}
-    note = f" (measured at start: fused {tuned.get('fused_us')} us vs GEMM+NCCL {tuned.get('nccl_us')} us per decoder layer)" if tuned else ""
+    note = (f" (measured at start, us per decoder layer: fused {tuned.get('fused_us')}, GEMM + tagged-slot all-reduce "
+            f"{tuned.get('ll_us')}, GEMM + NCCL {tuned.get('nccl_us')})") if tuned else ""
+    above = "in-kernel two-shot all-reduce over peer memory after the GEMM" if fused.ll_enabled else "NCCL after the GEMM"
     if fused.fused_max_tokens > 0:
-        return "in-kernel (fused GEMM+all-reduce over peer memory) for decode, NCCL for prefill" + note
-    return "nccl after the GEMM" + note
+        return (f"in-kernel (fused GEMM+all-reduce over peer memory) up to {fused.fused_max_tokens} tokens, {above} up to 256, "
+                "NCCL for prefill" + note)
+    return f"{above} for decode, NCCL for prefill" + note
 
 
 def main() -> None:

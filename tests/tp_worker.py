@@ -52,6 +52,22 @@ def main():
         assert all(torch.equal(gathered[0], gathered[r]) for r in range(comm.world)), (m, k)
     ops.raise_on_status()
 
+    # two-shot tagged-slot all-reduce (+ residual) vs NCCL, several sizes and repeated calls (epoch parity)
+    for it, (t, d) in enumerate([(1, 1024), (33, 1024), (64, 1024), (256, 1024), (33, 1024), (7, 512)]):
+        part = (torch.randn(t, d, device=dev) * 0.5).bfloat16()
+        res = torch.randn(t, d, device=dev).bfloat16()
+        dist.broadcast(res, 0)
+        assert ctx.can_all_reduce_ll(t, d), (t, d)
+        want = part.float().clone()
+        dist.all_reduce(want)
+        got = ctx.all_reduce_ll(part, res)
+        expect_close(got.float(), want + res.float(), atol=6e-2, rtol=3e-2, min_close=0.995)
+        gathered = comm.all_gather(got[None].contiguous())
+        assert all(torch.equal(gathered[0], gathered[r]) for r in range(comm.world)), ("all_reduce_ll", t, d)
+        plain = ctx.all_reduce_ll(part)
+        expect_close(plain.float(), want, atol=6e-2, rtol=3e-2, min_close=0.995)
+    ops.raise_on_status()
+
     # mixture-of-experts combine with the expert-parallel all-reduce inside vs finalize + NCCL all-reduce
     from zml_b200 import moe
     cctx = SymmetricContext.create(comm, 512, max_tokens=64, combine_tokens=64)
@@ -119,7 +135,7 @@ def main():
     # the measured choice between the fused kernel and GEMM + NCCL is the same on every rank
     tuned = ctx.autotune_projections([512, 1024])
     allt = comm.all_gather_object(tuned)
-    assert all(t == allt[0] for t in allt) and tuned["choice"] in ("fused", "nccl"), allt
+    assert all(t == allt[0] for t in allt) and tuned["choice"] in ("fused", "ll", "nccl"), allt
     assert ctx.fused_max_tokens in (0, 32)
     ops.raise_on_status()
     ctx.close()

@@ -66,6 +66,120 @@ __global__ void zb_allreduce_oneshot_kernel(ZbArContext ctx, size_t in_off, __nv
   }
 }
 
+// ------------------------------------------------------------------ two-shot all-reduce in tagged slots
+// out = residual + sum over ranks of `in` (bf16 [tokens, d]) for decode-sized tensors (tens of KB to a few MB),
+// where a bandwidth-optimal ring pays its latency many times over.  The tensor is cut into `world` shards of
+// `vs` 16-byte vectors.  Every thread owns vector g of every shard:
+//   1. it stores its partial of every foreign shard into the owner's slot area (8-byte {two bf16, epoch}
+//      words: a word arrives whole, so the tag needs no fence and no flag);
+//   2. for its own shard it waits for the peers' words, sums all ranks in rank order, adds the residual and
+//      rounds to bf16 - one rank computes every element, so all ranks end with the same bits;
+//   3. it stores the result into every peer's second slot area and collects the other shards from its own.
+// Each rank sends 2 x (world - 1) / world of the tensor (twice that in slot bytes) and waits two NVLink
+// latencies.  Slot areas alternate by epoch parity (see fused_ar.h for why one alternation is enough).
+// The reference leaves this reduction to NCCL through XLA (zml/ops.zig:24-173).
+constexpr uint32_t kKernelAllReduceLl = 11;
+
+struct LlAllReduce {
+  uint2* slots[8];          // slot area in every rank's heap ([rank] is local)
+  size_t region_words;      // 8-byte words of one (phase, parity) region: world * vs * 4
+  uint32_t* epoch;
+  uint32_t* ticket;
+  int rank;
+  int world;
+};
+
+__global__ void __launch_bounds__(128)
+zb_allreduce_ll_kernel(const uint4* __restrict__ in, const uint4* __restrict__ residual, uint4* __restrict__ out, long long vs,
+                       const LlAllReduce ar, ZbStatus* status) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(ar.epoch);
+  const size_t par = epoch & 1u;
+  const int W = ar.world, rank = ar.rank;
+  bool timed_out = false;
+  const uint64_t t0 = zb_globaltimer();
+  auto wait4 = [&](const uint2* src, uint32_t (&w)[4]) {
+    uint32_t spins = 0;
+    while (true) {
+      bool ready = true;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint2 x = zb_ld_ll(src + q);
+        w[q] = x.x;
+        ready = ready && (x.y == epoch);
+      }
+      if (ready || timed_out) return;
+      if ((++spins & 0x3f) == 0 && zb_globaltimer() - t0 > ZB_WAIT_LIMIT_NS) timed_out = true;
+    }
+  };
+  for (long long g = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; g < vs;
+       g += static_cast<long long>(gridDim.x) * blockDim.x) {
+    // 1. partials of the foreign shards go to their owners
+    for (int s = 0; s < W; ++s) {
+      if (s == rank) continue;
+      const uint4 v = in[s * vs + g];
+      uint2* dst = ar.slots[s] + ((0 * 2 + par) * W + rank) * static_cast<size_t>(vs) * 4 + g * 4;
+      zb_st_ll(dst + 0, v.x, epoch);
+      zb_st_ll(dst + 1, v.y, epoch);
+      zb_st_ll(dst + 2, v.z, epoch);
+      zb_st_ll(dst + 3, v.w, epoch);
+    }
+    // 2. own shard: sum of all ranks in rank order
+    const uint4 mine = in[rank * vs + g];
+    uint4 rv = make_uint4(0u, 0u, 0u, 0u);
+    if (residual != nullptr) rv = residual[rank * vs + g];
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < W; ++r) {
+      uint32_t w[4] = {mine.x, mine.y, mine.z, mine.w};
+      if (r != rank) wait4(ar.slots[rank] + ((0 * 2 + par) * W + r) * static_cast<size_t>(vs) * 4 + g * 4, w);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = zb_unpack_bf16x2(w[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    {
+      const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = zb_unpack_bf16x2(w[q]);
+        acc[2 * q] += f.x;
+        acc[2 * q + 1] += f.y;
+      }
+    }
+    const uint4 res = make_uint4(zb_pack_bf16x2(acc[0], acc[1]), zb_pack_bf16x2(acc[2], acc[3]), zb_pack_bf16x2(acc[4], acc[5]),
+                                 zb_pack_bf16x2(acc[6], acc[7]));
+    // 3. the finished shard goes to every peer; the other shards come from theirs
+    for (int p = 0; p < W; ++p) {
+      if (p == rank) continue;
+      uint2* dst = ar.slots[p] + ((1 * 2 + par) * W + rank) * static_cast<size_t>(vs) * 4 + g * 4;
+      zb_st_ll(dst + 0, res.x, epoch);
+      zb_st_ll(dst + 1, res.y, epoch);
+      zb_st_ll(dst + 2, res.z, epoch);
+      zb_st_ll(dst + 3, res.w, epoch);
+    }
+    out[rank * vs + g] = res;
+    for (int s = 0; s < W; ++s) {
+      if (s == rank) continue;
+      uint32_t w[4];
+      wait4(ar.slots[rank] + ((1 * 2 + par) * W + s) * static_cast<size_t>(vs) * 4 + g * 4, w);
+      out[s * vs + g] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  if (timed_out) zb_record_error(status, ZB_ERR_FLAG_TIMEOUT, kKernelAllReduceLl, blockIdx.x, rank);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(ar.ticket, 1u);
+    if (ticket == gridDim.x - 1) {
+      *ar.ticket = 0u;
+      *reinterpret_cast<volatile uint32_t*>(ar.epoch) = epoch + 1u;
+    }
+  }
+}
+
 }  // namespace
 
 // A wait with a caller-chosen limit on a flag the caller owns: the building block of every
@@ -143,8 +257,8 @@ ZbArContext* zb_ar_ctx_create(int rank, int world, void* const* heap, size_t rec
     delete c;
     return nullptr;
   }
-  // {gemm epoch, exit ticket, barrier epoch, unused, combine epoch, combine exit ticket, unused, unused}
-  const uint32_t init[8] = {1u, 0u, 1u, 0u, 1u, 0u, 0u, 0u};
+  // {gemm epoch, exit ticket, barrier epoch, unused, combine epoch, combine exit ticket, all-reduce epoch, its exit ticket}
+  const uint32_t init[8] = {1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u};
   cudaMemcpy(ctr, init, sizeof(init), cudaMemcpyHostToDevice);
   c->epoch = ctr;
   c->exit_ticket = ctr + 1;
@@ -177,6 +291,33 @@ int zb_allreduce_oneshot(const ZbArContext* c, size_t in_off, void* out, size_t 
   if (blocks > 296) blocks = 296;
   zb_allreduce_oneshot_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       *c, in_off, reinterpret_cast<__nv_bfloat16*>(out), n_vec);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out = residual + sum over the group of `in`, bf16 [tokens, d], by the two-shot tagged-slot kernel.  `in`,
+// `residual` (may be null) and `out` are local; the exchange goes through the slot area at `slot_off` of every
+// rank's heap (at least 16 bytes per element of the tensor).  tokens * d / 8 must be a multiple of the group size.
+int zb_allreduce_ll(const ZbArContext* c, const void* in, const void* residual, void* out, long long elems, size_t slot_off,
+                    size_t slot_bytes, void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (!st || !c) return -20;
+  if (elems <= 0) return 0;
+  if (elems % (8ll * c->world) != 0 || slot_off % 16 != 0) return -10;
+  const long long vs = elems / 8 / c->world;
+  LlAllReduce ar = {};
+  ar.region_words = static_cast<size_t>(c->world) * vs * 4;
+  if (4 * ar.region_words * sizeof(uint2) > slot_bytes) return -68;
+  for (int r = 0; r < c->world; ++r) ar.slots[r] = reinterpret_cast<uint2*>(reinterpret_cast<char*>(c->heap[r]) + slot_off);
+  ar.epoch = c->epoch + 6;
+  ar.ticket = c->epoch + 7;
+  ar.rank = c->rank;
+  ar.world = c->world;
+  long long blocks = (vs + 127) / 128;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  zb_launch(zb_allreduce_ll_kernel, dim3(static_cast<unsigned>(blocks)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
+            reinterpret_cast<const uint4*>(in), reinterpret_cast<const uint4*>(residual), reinterpret_cast<uint4*>(out), vs, ar,
+            st->status);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -305,6 +305,8 @@ class LlamaModel:
             return ops.gemm(a, w, residual=residual, out=residual if residual.is_cuda else None, static_w=True)
         if comm.fused is not None and a.is_cuda and a.shape[0] <= comm.fused.fused_max_tokens:
             return comm.fused.gemm_allreduce(a, w, residual)
+        if comm.fused is not None and a.is_cuda and comm.fused.can_all_reduce_ll(a.shape[0], w.shape[0]):
+            return comm.fused.all_reduce_ll(ops.gemm(a, w, static_w=True), residual)
         part = ops.gemm(a, w, residual=residual if comm.rank == 0 else None, static_w=True)
         return comm.all_reduce_(part)
 

@@ -75,10 +75,11 @@ class SymmetricContext:
         # and for prefill-sized batches the GEMM followed by an NCCL all-reduce measured faster
         self.fused_max_tokens = 32
         self.tuned = None      # result of `autotune`, if it ran
+        self.ll_enabled = True  # two-shot tagged-slot all-reduce after the GEMM for batches the fused kernel does not take
 
     @staticmethod
     def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0,
-               combine_tokens: int = 0) -> "SymmetricContext":
+               combine_tokens: int = 0, ll_tokens: int = 256) -> "SymmetricContext":
         """Collective: every rank of `comm` must call it with the same arguments."""
         l = _lib.lib()
         self = SymmetricContext()
@@ -104,7 +105,10 @@ class SymmetricContext:
         self.act_off = [self.recv_off + recv_bytes, self.recv_off + recv_bytes + act_bytes]
         self.staging_off = self.act_off[1] + act_bytes
         self.combine_off = self.staging_off + stg_bytes
-        self.heap_bytes = self.combine_off + self.combine_bytes
+        # slot area of the two-shot all-reduce: 2 phases x 2 parity halves, 4 bytes per element each
+        self.ll_bytes = _align(16 * ll_tokens * hidden)
+        self.ll_off = self.combine_off + self.combine_bytes
+        self.heap_bytes = self.ll_off + self.ll_bytes
         self.hidden, self.max_tokens = hidden, max_tokens
         p = C.c_void_p()
         _lib.check(l.zb_symm_alloc(self.heap_bytes, C.byref(p)), "zb_symm_alloc")
@@ -159,8 +163,10 @@ class SymmetricContext:
     def autotune(self, run, tokens: int = 32, reps: int = 5, units: int = 1) -> dict:
         """Collective.  Times `run()` - a decode-sized piece of the model that goes through
         `LlamaModel.row_parallel`, with weights that do not fit the L2 - once with the fused GEMM + all-reduce
-        and once with the GEMM followed by the NCCL all-reduce, each as a CUDA graph, and keeps the fused path
-        (`fused_max_tokens`) only if it is not slower.  Which one wins depends on the tensor-parallel degree and
+        once with the GEMM followed by the two-shot tagged-slot all-reduce (`all_reduce_ll`) and once with the GEMM
+        followed by the NCCL all-reduce, each as a CUDA graph, and keeps the fastest: the fused path up to `tokens`
+        (`fused_max_tokens`) only if it wins, the tagged-slot all-reduce for decode-sized batches (`ll_enabled`) only
+        if it beats NCCL.  Which one wins depends on the tensor-parallel degree and
         on the NVLink latency of the box (measured on B200, Llama-3.1-8B: 8 ranks fused 1.31x faster end to end;
         2 ranks NCCL 10 % faster, although a chain of the projections alone has the fused kernel ahead)."""
         comm, dev = self.comm, self.comm.device
@@ -187,13 +193,17 @@ class SymmetricContext:
             torch.cuda.synchronize()
             return comm.max_over_ranks(e0.elapsed_time(e1) * 1e3 / (reps * units))
 
-        self.fused_max_tokens = tokens
+        self.fused_max_tokens, self.ll_enabled = tokens, False
         t_fused = graph_us()
-        self.fused_max_tokens = 0
+        self.fused_max_tokens, self.ll_enabled = 0, True
+        t_ll = graph_us()
+        self.fused_max_tokens, self.ll_enabled = 0, False
         t_nccl = graph_us()
-        self.fused_max_tokens = tokens if t_fused <= t_nccl else 0
-        self.tuned = {"fused_us": round(t_fused, 2), "nccl_us": round(t_nccl, 2), "tokens": tokens,
-                      "choice": "fused" if self.fused_max_tokens else "nccl"}
+        self.fused_max_tokens = tokens if t_fused <= min(t_ll, t_nccl) else 0
+        self.ll_enabled = t_ll <= t_nccl
+        self.tuned = {"fused_us": round(t_fused, 2), "ll_us": round(t_ll, 2), "nccl_us": round(t_nccl, 2), "tokens": tokens,
+                      "choice": "fused" if self.fused_max_tokens else ("ll" if self.ll_enabled else "nccl"),
+                      "above": "ll" if self.ll_enabled else "nccl"}
         return self.tuned
 
     def autotune_projections(self, ks, tokens: int = 32, chain: int = 4) -> dict:
@@ -216,6 +226,8 @@ class SymmetricContext:
                 a = ops.gemm(x, wc, static_w=True)
                 if a.shape[0] <= self.fused_max_tokens:
                     x = self.gemm_allreduce(a, wr, x)
+                elif self.can_all_reduce_ll(a.shape[0], self.hidden):
+                    x = self.all_reduce_ll(ops.gemm(a, wr, static_w=True), x)
                 else:
                     x = comm.all_reduce_(ops.gemm(a, wr, residual=x if comm.rank == 0 else None, static_w=True))
             return x
@@ -236,6 +248,20 @@ class SymmetricContext:
         _lib.check(_lib.lib().zb_allreduce_oneshot(self.ctx, self.staging_off, out.data_ptr(), n,
                                                    _lib.stream_ptr()), "zb_allreduce_oneshot")
         self.barrier()
+        return out
+
+    def can_all_reduce_ll(self, tokens: int, d: int) -> bool:
+        n = tokens * d
+        return self.ctx is not None and self.ll_enabled and 16 * n <= self.ll_bytes and n % (8 * self.comm.world) == 0
+
+    def all_reduce_ll(self, part: torch.Tensor, residual=None) -> torch.Tensor:
+        """All ranks: residual + sum over ranks of `part` (bf16, decode-sized) by the two-shot tagged-slot kernel
+        (libzb_cuda.so: zb_allreduce_ll); every rank receives the same bits."""
+        assert part.dtype == torch.bfloat16 and part.is_contiguous()
+        out = torch.empty_like(part)
+        _lib.check(_lib.lib().zb_allreduce_ll(self.ctx, part.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                              out.data_ptr(), part.numel(), self.ll_off, self.ll_bytes, _lib.stream_ptr()),
+                   "zb_allreduce_ll")
         return out
 
     def can_combine(self, tokens: int, d: int) -> bool:
