@@ -53,6 +53,8 @@ def main():
     ops.raise_on_status()
 
     # two-shot tagged-slot all-reduce (+ residual) vs NCCL, several sizes and repeated calls (epoch parity)
+    ctx.ll_enabled = True
+    SymmetricContext.LL_ALLREDUCE = True
     for it, (t, d) in enumerate([(1, 1024), (33, 1024), (64, 1024), (256, 1024), (33, 1024), (7, 512)]):
         part = (torch.randn(t, d, device=dev) * 0.5).bfloat16()
         res = torch.randn(t, d, device=dev).bfloat16()

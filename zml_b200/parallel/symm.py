@@ -19,6 +19,7 @@ the GEMM (examples/llm/models/llama/model.zig:421-442,613-617).
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -58,6 +59,7 @@ def _align(n: int, a: int = 256) -> int:
 
 class SymmetricContext:
     MAX_TILES = 8192
+    LL_ALLREDUCE = os.environ.get("ZB_LL_ALLREDUCE", "0") == "1"     # `autotune` considers the two-shot tagged-slot all-reduce
 
     def __init__(self):
         self.comm: Optional[Comm] = None
@@ -75,7 +77,7 @@ class SymmetricContext:
         # and for prefill-sized batches the GEMM followed by an NCCL all-reduce measured faster
         self.fused_max_tokens = 32
         self.tuned = None      # result of `autotune`, if it ran
-        self.ll_enabled = True  # two-shot tagged-slot all-reduce after the GEMM for batches the fused kernel does not take
+        self.ll_enabled = False  # two-shot tagged-slot all-reduce after the GEMM for batches the fused kernel does not take
 
     @staticmethod
     def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0,
@@ -195,15 +197,18 @@ class SymmetricContext:
 
         self.fused_max_tokens, self.ll_enabled = tokens, False
         t_fused = graph_us()
-        self.fused_max_tokens, self.ll_enabled = 0, True
-        t_ll = graph_us()
+        t_ll = float("inf")
+        if self.LL_ALLREDUCE:
+            self.fused_max_tokens, self.ll_enabled = 0, True
+            t_ll = graph_us()
         self.fused_max_tokens, self.ll_enabled = 0, False
         t_nccl = graph_us()
         self.fused_max_tokens = tokens if t_fused <= min(t_ll, t_nccl) else 0
         self.ll_enabled = t_ll <= t_nccl
-        self.tuned = {"fused_us": round(t_fused, 2), "ll_us": round(t_ll, 2), "nccl_us": round(t_nccl, 2), "tokens": tokens,
+        self.tuned = {"fused_us": round(t_fused, 2), "ll_us": round(t_ll, 2) if t_ll != float("inf") else None, "nccl_us": round(t_nccl, 2), "tokens": tokens,
                       "choice": "fused" if self.fused_max_tokens else ("ll" if self.ll_enabled else "nccl"),
                       "above": "ll" if self.ll_enabled else "nccl"}
+
         return self.tuned
 
     def autotune_projections(self, ks, tokens: int = 32, chain: int = 4) -> dict:
