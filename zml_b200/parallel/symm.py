@@ -59,7 +59,7 @@ def _align(n: int, a: int = 256) -> int:
 
 class SymmetricContext:
     MAX_TILES = 8192
-    LL_ALLREDUCE = os.environ.get("ZB_LL_ALLREDUCE", "0") == "1"     # `autotune` considers the two-shot tagged-slot all-reduce
+    LL_ALLREDUCE = os.environ.get("ZB_LL_ALLREDUCE", "1") == "1"     # `autotune` considers the two-shot tagged-slot all-reduce
 
     def __init__(self):
         self.comm: Optional[Comm] = None
