@@ -62,6 +62,48 @@ def test_protocol_slow_rank_within_limit_is_fine_and_stale_epoch_does_not_satisf
     assert isinstance(res[0], sim.Timeout) and res[0].epoch == 2
 
 
+@pytest.mark.parametrize("world,vs", [(2, 16), (4, 5), (8, 3)])
+def test_two_shot_allreduce_protocol_over_several_epochs(world, vs):
+    """Same slot indexing and parity halves as the device kernel: every rank ends with the same, correct sum, launch
+    after launch, although the slots of older launches are never cleared."""
+    heap = sim.SlotHeap(world, vs)
+    rng = np.random.default_rng(world * 100 + vs)
+    for epoch in range(1, 6):
+        xs = [rng.standard_normal(world * vs).astype(np.float32) for _ in range(world)]
+        res = sim.run_two_shot(heap, epoch, xs)
+        assert not res["timeouts"]
+        want = np.zeros(world * vs, dtype=np.float32)
+        for shard in range(world):                      # the owner sums its shard in rank order
+            acc = np.zeros(vs, dtype=np.float32)
+            for r in range(world):
+                acc += xs[r][shard * vs:(shard + 1) * vs]
+            want[shard * vs:(shard + 1) * vs] = acc
+        for r in range(world):
+            assert np.array_equal(res["out"][r], want), (epoch, r)
+
+
+def test_two_shot_allreduce_dead_rank_and_lost_words_are_reported():
+    heap = sim.SlotHeap(4, 8)
+    xs = [np.full(32, float(r + 1), dtype=np.float32) for r in range(4)]
+    res = sim.run_two_shot(heap, 1, xs, limit_s=0.1, faults=sim.Faults(dead_ranks={2}))
+    assert set(res["timeouts"]) == {0, 1, 3}
+    for r, t in res["timeouts"].items():
+        assert t.phase == sim.PHASE_SHARD_WAIT and t.awaited == 2 and t.epoch == 1
+    # rank 1's partial for shard 3 never arrives: the owner (3) names rank 1, everybody else misses shard 3
+    heap = sim.SlotHeap(4, 8)
+    res = sim.run_two_shot(heap, 1, xs, limit_s=0.1, faults=sim.Faults(drop_push={(1, 3)}))
+    assert res["timeouts"][3].phase == sim.PHASE_SHARD_WAIT and res["timeouts"][3].awaited == 1
+    for r in (0, 1, 2):
+        assert res["timeouts"][r].phase == sim.PHASE_GATHER_WAIT and res["timeouts"][r].awaited == 3
+    # a stale half (two launches old, same parity) does not satisfy a wait
+    heap = sim.SlotHeap(2, 4)
+    ys = [np.ones(8, dtype=np.float32), np.ones(8, dtype=np.float32)]
+    assert not sim.run_two_shot(heap, 1, ys)["timeouts"]
+    assert not sim.run_two_shot(heap, 2, ys)["timeouts"]
+    res = sim.run_two_shot(heap, 3, ys, limit_s=0.1, faults=sim.Faults(dead_ranks={1}))
+    assert res["timeouts"][0].phase == sim.PHASE_SHARD_WAIT and res["timeouts"][0].epoch == 3
+
+
 def test_heartbeat_detects_silent_and_departed_ranks():
     store = torch.distributed.HashStore()
     hb = [health.Heartbeat(store, r, 3, timeout_s=5.0) for r in range(3)]

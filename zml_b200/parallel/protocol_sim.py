@@ -110,3 +110,75 @@ def run_step(heap: SharedHeap, epoch: int, partials: list, limit_s: float = 0.3,
     for t in threads:
         t.join()
     return results
+
+
+# ---------------------------------------------------------------------------------------------
+# Two-shot all-reduce in tagged slots (csrc/comm.cu: zb_allreduce_ll), rank per thread.
+#
+# A slot word carries (value, epoch); a reader accepts a word only when its tag equals the launch's
+# epoch, so there are no flags.  Slot areas: [phase 0 / 1][epoch parity][source rank][vector].  Every
+# launch uses the half of its parity; the simulation keeps the words of older launches in place, as
+# the device does, so a protocol that read a stale half would be caught by the tags or by the sums.
+PHASE_SHARD_WAIT = 3     # owner waiting for a peer's partial of its shard
+PHASE_GATHER_WAIT = 4    # rank waiting for a finished shard
+
+
+class SlotHeap:
+    def __init__(self, world: int, vs: int):
+        self.world, self.vs = world, vs
+        self.value = np.zeros((world, 2, 2, world, vs), dtype=np.float32)     # [rank][phase][parity][src][g]
+        self.tag = np.zeros((world, 2, 2, world, vs), dtype=np.int64)
+
+
+def run_two_shot_rank(heap: SlotHeap, rank: int, epoch: int, x: np.ndarray, limit_s: float, faults: Faults,
+                      out: np.ndarray) -> Optional[Timeout]:
+    """x: this rank's input [world * vs]; out: [world * vs] receives the sum over ranks."""
+    w, vs, par = heap.world, heap.vs, epoch & 1
+    if rank in faults.delay_s:
+        time.sleep(faults.delay_s[rank])
+    for s in range(w):                       # 1. partials of foreign shards go to their owners
+        if s == rank or (rank, s) in faults.drop_push:
+            continue
+        heap.value[s, 0, par, rank] = x[s * vs:(s + 1) * vs]
+        heap.tag[s, 0, par, rank] = epoch
+    acc = np.zeros(vs, dtype=np.float32)     # 2. own shard, summed in rank order
+    for r in range(w):
+        if r == rank:
+            acc += x[rank * vs:(rank + 1) * vs]
+            continue
+        if not _wait(lambda: int(heap.tag[rank, 0, par, r].min()), epoch, limit_s):
+            return Timeout(rank, PHASE_SHARD_WAIT, rank, r, epoch)
+        acc += heap.value[rank, 0, par, r]
+    for p in range(w):                       # 3. the finished shard goes to every peer
+        if p == rank or (rank, p, rank) in faults.drop_done:
+            continue
+        heap.value[p, 1, par, rank] = acc
+        heap.tag[p, 1, par, rank] = epoch
+    out[rank * vs:(rank + 1) * vs] = acc
+    for s in range(w):
+        if s == rank:
+            continue
+        if not _wait(lambda: int(heap.tag[rank, 1, par, s].min()), epoch, limit_s):
+            return Timeout(rank, PHASE_GATHER_WAIT, s, s, epoch)
+        out[s * vs:(s + 1) * vs] = heap.value[rank, 1, par, s]
+    return None
+
+
+def run_two_shot(heap: SlotHeap, epoch: int, inputs: list, limit_s: float = 0.3, faults: Optional[Faults] = None) -> dict:
+    """One launch on every live rank; returns {"out": [world][world * vs], "timeouts": {rank: Timeout}}."""
+    faults = faults or Faults()
+    w = heap.world
+    outs = [np.zeros(w * heap.vs, dtype=np.float32) for _ in range(w)]
+    timeouts: dict = {}
+
+    def body(r):
+        t = run_two_shot_rank(heap, r, epoch, inputs[r], limit_s, faults, outs[r])
+        if t is not None:
+            timeouts[r] = t
+
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(w) if r not in faults.dead_ranks]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    return {"out": outs, "timeouts": timeouts}
