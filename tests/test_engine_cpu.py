@@ -196,3 +196,48 @@ def test_moe_loads_nvfp4_expert_checkpoints(tmp_path):
             assert torch.allclose(lw.extra["down"][e], want[f"model.layers.0.mlp.experts.{e}.down_proj.weight"], rtol=1e-6, atol=1e-8)
         outs, _ = Engine(m2, num_pages=32, page_size=16, max_batch=2, max_seq_len=128).generate([[3, 4, 5, 6, 7]], 4)
         assert len(outs[0]) == 4
+
+
+_OVERLAP_WORKER = r"""
+import os, sys, torch
+sys.path.insert(0, os.environ["ZB_ROOT"])
+from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
+from zml_b200.parallel.comm import Comm
+from zml_b200.serving import Engine
+c = Comm.from_env(backend="gloo")
+cfg = LlamaConfig.from_hf(PRESETS["tiny-llama-test"])
+g = torch.Generator().manual_seed(3)
+prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 9, 31, 22)]
+outs, calls = {}, {}
+for name, threshold in (("whole", 10 ** 9), ("halves", 16)):
+    model = LlamaModel(cfg, c, device="cpu", dtype=torch.float32).init_random(seed=5, std=0.05)
+    model.prefill_overlap_min_tokens = threshold
+    n = [0]
+    inner = model._hidden_states_overlapped
+    def counted(*a, _inner=inner, _n=n, **k):
+        _n[0] += 1
+        return _inner(*a, **k)
+    model._hidden_states_overlapped = counted
+    eng = Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128)
+    outs[name], _ = eng.generate(prompts, 6)
+    calls[name] = n[0]
+assert calls["whole"] == 0 and calls["halves"] >= 1, calls
+assert outs["whole"] == outs["halves"], outs
+print("OVERLAP_OK", c.rank, flush=True)
+c.finish(0)
+"""
+
+
+def test_prefill_in_two_halves_with_async_all_reduce_matches_whole_chunk(tmp_path):
+    """Tensor-parallel prefill split at a sequence boundary, all-reduces issued asynchronously: same tokens."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "w.py"
+    script.write_text(_OVERLAP_WORKER)
+    env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29641", str(script)],
+                       capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("OVERLAP_OK") == 2

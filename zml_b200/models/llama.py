@@ -15,6 +15,8 @@ so a layer is 4 GEMMs, and the B200 kernels never materialise a transpose.
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Optional
@@ -131,6 +133,7 @@ class AttnMeta:
     max_seq_len: Optional[int] = None
     logits_rows: Optional[torch.Tensor] = None    # rows of the hidden state that need logits
     state_slots: Optional[torch.Tensor] = None    # {b} slot of every sequence in a model's recurrent-state pool
+    q_start_host: Optional[list] = None           # host copy of q_start (prefill), for splitting a chunk by sequences
 
 
 class LayerWeights:
@@ -338,11 +341,71 @@ class LlamaModel:
         n2 = ops.rmsnorm(x, lw.post_norm, c.rms_norm_eps)
         return self.mlp(lw, x, n2)
 
+    # With ZB_PREFILL_OVERLAP=1 a prefill chunk of at least this many tokens (and two sequences) is processed as
+    # two halves whose tensor-parallel all-reduces overlap the other half's GEMMs and attention.  Off by default:
+    # on 2 B200s (Llama-3.1-8B) it measured slower (job 2 488 vs 2 450 ms, TTFT p50 253 vs 215 ms) - the all-reduce
+    # is a small share there and the collective's CTAs take SMs from the GEMMs; not measured on 8 GPUs, where the
+    # all-reduce is about a fifth of a 70B prefill chunk.
+    prefill_overlap_min_tokens = 2048 if os.environ.get("ZB_PREFILL_OVERLAP", "0") == "1" else 1 << 62
+
     def hidden_states(self, ids, meta: AttnMeta, kv_cache):
         x = ops.embedding(ids, self.embed)
+        halves = self._split_prefill(x, meta)
+        if halves is not None:
+            return self._hidden_states_overlapped(x, halves, kv_cache)
         for l in range(self.config.num_hidden_layers):
             x = self.layer(l, x, meta, kv_cache)
         return x
+
+    def _split_prefill(self, x, meta: AttnMeta):
+        """Two (token range, AttnMeta) halves of a prefill chunk, cut at a sequence boundary near the middle; None
+        when the chunk is not worth splitting (one rank, one sequence, few tokens, a layer type with state)."""
+        qs = meta.q_start_host
+        from ..ops import baseline as _baseline
+        if _baseline.enabled():
+            return None
+        if (type(self).layer is not LlamaModel.layer or type(self).mlp is not LlamaModel.mlp or self.comm.world == 1
+                or not meta.is_prefill or qs is None or len(qs) < 3 or x.shape[0] < self.prefill_overlap_min_tokens):
+            return None
+        total = qs[-1]
+        cut = min(range(1, len(qs) - 1), key=lambda i: abs(qs[i] - total / 2))
+        out = []
+        for s0, s1 in ((0, cut), (cut, len(qs) - 1)):
+            t0, t1 = qs[s0], qs[s1]
+            blocks = sum((qs[i + 1] - qs[i] + 63) // 64 for i in range(s0, s1))
+            out.append((t0, t1, AttnMeta(True, meta.positions[t0:t1], meta.slot_mapping[t0:t1], meta.block_table[s0:s1],
+                                         meta.seq_lens[s0:s1], meta.q_start[s0:s1 + 1] - t0, total_q_blocks=blocks)))
+        return out
+
+    def _row_parallel_async(self, a, w, residual):
+        """Row-parallel GEMM whose all-reduce runs on the collective library's stream: (tensor, work); the tensor
+        holds the sum (+ residual) once `work.wait()` has been called on the consuming stream."""
+        import torch.distributed as dist
+        part = ops.gemm(a, w, residual=residual if self.comm.rank == 0 else None, static_w=True)
+        return part, dist.all_reduce(part, group=self.comm.group, async_op=True)
+
+    def _hidden_states_overlapped(self, x, halves, kv_cache):
+        c = self.config
+        xs = [x[t0:t1] for t0, t1, _ in halves]
+        metas = [m for _, _, m in halves]
+        works = [None, None]
+        for l in range(c.num_hidden_layers):
+            lw = self.layers[l]
+            kc, vc = kv_cache[l, 0], kv_cache[l, 1]
+            for h in (0, 1):
+                if works[h] is not None:
+                    works[h].wait()
+                n1 = ops.rmsnorm(xs[h], lw.input_norm, c.rms_norm_eps)
+                a = self.attention(lw, n1, metas[h], kc, vc)
+                xs[h], works[h] = self._row_parallel_async(a, lw.o, xs[h])
+            for h in (0, 1):
+                works[h].wait()
+                n2 = ops.rmsnorm(xs[h], lw.post_norm, c.rms_norm_eps)
+                act = ops.swiglu(ops.gemm(n2, lw.gate_up, static_w=True))
+                xs[h], works[h] = self._row_parallel_async(act, lw.down, xs[h])
+        for h in (0, 1):
+            works[h].wait()
+        return torch.cat(xs, 0)
 
     def logits(self, x, rows=None):
         """float32 logits of this rank's vocab shard for the selected rows."""

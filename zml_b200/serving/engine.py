@@ -217,7 +217,7 @@ class Engine:
         nb = len(chunk)
         meta = AttnMeta(True, dev[1], dev[2], bt_d, meta_d[nb + 1:2 * nb + 1], meta_d[:nb + 1],
                         total_q_blocks=sum((b - a + 63) // 64 for _, a, b in chunk),
-                        logits_rows=meta_d[3 * nb + 1:] if rows else None,
+                        logits_rows=meta_d[3 * nb + 1:] if rows else None, q_start_host=list(qs),
                         state_slots=meta_d[2 * nb + 1:3 * nb + 1] if self.stateful else None)
         if rows:
             toks = self.model.forward(dev[0], meta, self.kv_cache, strategy, self.seed, 0)
