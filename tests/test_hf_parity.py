@@ -153,3 +153,38 @@ def test_lfm2_parity(tmp_path):
     torch.manual_seed(0)
     d = c.to_dict()
     _check(transformers.Lfm2ForCausalLM(c), d, tmp_path, 0.04)
+
+
+def test_model_tests_runner_checks_layers_against_captured_activations(tmp_path):
+    """`examples/llm/model_tests.py`: activations captured from the HF model with ActivationCollector, then every
+    recorded decoder layer and the final norm re-computed on this framework's weights."""
+    import importlib.util
+    import sys
+    from zml_b200.utils.activations import ActivationCollector, save_activations
+    cfgd = dict(model_type="llama", architectures=["LlamaForCausalLM"], vocab_size=320, hidden_size=128, intermediate_size=256,
+                num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=32, rms_norm_eps=1e-5,
+                rope_theta=10000.0, max_position_embeddings=256, tie_word_embeddings=False, hidden_act="silu",
+                bos_token_id=1, eos_token_id=2)
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(transformers.LlamaConfig(**{k: v for k, v in cfgd.items() if k not in ("architectures",)}))
+    hf = hf.eval().float()
+    repo = tmp_path / "repo"
+    repo.mkdir()
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, str(repo / "model.safetensors"))
+    (repo / "config.json").write_text(json.dumps(cfgd))
+    ids = torch.randint(3, 320, (2, 21), generator=torch.Generator().manual_seed(4))
+    _, acts = ActivationCollector(hf, blacklist_regexes=())(ids)
+    keep = {k: v for k, v in acts.items() if k.startswith("model.layers.") and k.count(".") == 4 or k.startswith("model.norm.")}
+    assert "model.layers.2.in.0" in keep and "model.norm.out.0" in keep
+    save_activations(str(tmp_path / "acts.safetensors"), keep)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("model_tests", os.path.join(root, "examples", "llm", "model_tests.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["model_tests"] = mod
+    spec.loader.exec_module(mod)
+    rc = mod.main([f"--model={repo}", f"--activations={tmp_path / 'acts.safetensors'}", "--device=cpu", "--atol=2e-3", "--rtol=2e-3"])
+    assert rc == 0
+    # a corrupted fixture is reported
+    keep["model.layers.1.out.0"] = keep["model.layers.1.out.0"] + 1.0
+    save_activations(str(tmp_path / "bad.safetensors"), keep)
+    assert mod.main([f"--model={repo}", f"--activations={tmp_path / 'bad.safetensors'}", "--device=cpu"]) == 1
