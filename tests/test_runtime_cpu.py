@@ -159,3 +159,25 @@ def test_tracer_and_profiler_write_trace_events(tmp_path):
         with tracer.span("step"):
             pass
     assert os.path.exists(prof.host_trace)
+
+
+def test_decode_split_planner_splits_only_when_pairs_are_few():
+    """The KV-split plan of the paged decode kernel is host code: no GPU needed.  Many (sequence, KV head) pairs ->
+    one chunk per sequence (a split costs a partial write and a merge); few pairs with a long context -> many."""
+    import ctypes
+    import os
+    so = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "zml_b200", "_C", "libzb_cuda.so")
+    if not os.path.exists(so):
+        pytest.skip("libzb_cuda.so not built")
+    lib = ctypes.CDLL(so)
+    plan = lambda b, h, s: lib.zb_decode_plan_splits(b, h, s, 148)
+    assert plan(32, 8, 1344) == 1 and plan(128, 4, 1152) == 1 and plan(256, 8, 2048) == 1
+    assert plan(1, 8, 32768) >= 16
+    assert 2 <= plan(4, 8, 4096) <= 16
+    assert plan(1, 8, 64) == 1                                  # one page: nothing to split
+    for b, h, s in [(1, 1, 100000), (3, 2, 5000), (64, 1, 2176)]:
+        mc = plan(b, h, s)
+        assert 1 <= mc <= 64
+        assert mc == 1 or (s + mc - 1) // mc >= 64              # chunks are at least a page
+    # more pairs never ask for more chunks at the same context
+    assert plan(2, 8, 8192) >= plan(8, 8, 8192) >= plan(64, 8, 8192)
