@@ -23,7 +23,7 @@ def _status_clean():
 
 
 @pytest.mark.parametrize("m,n,k", [
-    (1, 256, 128), (7, 384, 64), (16, 4096, 4096), (32, 6144, 4096), (33, 1000 * 8, 512),
+    (1, 256, 128), (7, 384, 64), (5, 256, 320), (16, 1024, 256), (32, 128, 2048), (128, 128, 2048), (16, 4096, 4096), (32, 6144, 4096), (33, 1000 * 8, 512),
     (64, 4096, 14336), (128, 2048, 2048), (128, 5120, 2048), (100, 2048, 4096), (97, 4096, 4096 + 64), (200, 512, 1024), (256, 1024, 4096),
     (257, 1024, 1024), (512, 4096, 4096), (1000, 2048 + 64, 512), (4096, 4096, 4096),
     (3000, 14336 * 2, 4096 // 2),

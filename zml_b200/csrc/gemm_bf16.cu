@@ -1161,13 +1161,14 @@ int g_cluster_splitk = 1;
 // along K over the CTAs of one cluster, which reduce it through distributed shared memory.
 // Returns the cluster size (1: keep the stream-K plan) and updates grid / units per CTA.
 int zb_gemm_cluster_capacity_of(int bn, int s);
-int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* upc) {
+int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* upc, bool allow_tiny = true) {
   if (!g_cluster_splitk || bn > 128 || tiles >= num_sms) return 1;
   int best = 1, best_ctas = 0;
   const int sizes[5] = {8, 6, 4, 3, 2};
   for (int i = 0; i < 5; ++i) {
     const int s = sizes[i];
-    if ((kb_total + s - 1) / s < 2) continue;
+    const int per_rank = (kb_total + s - 1) / s;
+    if (per_rank < 2 || (s - 1) * per_rank >= kb_total) continue;      // every CTA of the cluster gets k-blocks
     const int cap = zb_gemm_cluster_capacity_of(bn, s);
     const int ctas = tiles * s;
     if (ctas > cap || ctas > num_sms) continue;
@@ -1176,7 +1177,11 @@ int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* u
       best_ctas = ctas;
     }
   }
-  if (best == 1 || best_ctas * 2 < num_sms) return 1;     // under half of the SMs busy: stream-K does better
+  // Under half of the SMs busy: stream-K (all SMs stream) does better - unless the whole problem is a few
+  // k-blocks (a router or a small head: 1 - 2 tiles), where the few CTAs are the same either way and the
+  // cluster reduction through shared memory replaces the fix-up through global memory.
+  const bool tiny = allow_tiny && static_cast<long long>(tiles) * kb_total <= 64;
+  if (best == 1 || (best_ctas * 2 < num_sms && !tiny)) return 1;
   *grid = best_ctas;
   *upc = (kb_total + best - 1) / best;
   return best;
@@ -1392,7 +1397,7 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
                              2 * static_cast<size_t>(ctx->world) * tiles * kBlockP * bn * 2 <= ctx->recv_bytes;
   if (one_shot_fits && rr == 0 && split_hint <= 0) {
     int cg = grid, cu = upc;
-    const int cs = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &cg, &cu);
+    const int cs = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &cg, &cu, /*allow_tiny=*/false);
     // the tensor-parallel epilogue keeps at most 32 elements per thread (two halves of 16)
     if (cs > 1 && bn * ((kBlockP + cs - 1) / cs) <= 32 * kEpiThreads &&
         2 * static_cast<size_t>(ctx->world) * tiles * cs * 16 * kEpiThreads * sizeof(uint2) <= ctx->recv_bytes) {
