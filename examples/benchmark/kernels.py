@@ -8,6 +8,7 @@
     python examples/benchmark/kernels.py --op=gated_delta_scan --batch=32 --seqlen=1024
     python examples/benchmark/kernels.py --op=decode_layers --model=llama-3.1-8b --batch=32 --seqlen=1344
     python examples/benchmark/kernels.py --op=gemm_chain_timeline --model=llama-3.1-8b --batch=32
+    python examples/benchmark/kernels.py --op=moe_w4_timeline --tokens=128 --experts=128 --topk=8 --n=768 --k=2048
 
 Every op works on inputs larger than the L2 (or rotates through several copies of its operands
 so that each launch reads cold data); `--iters` timed launches follow `--warmup` untimed ones.
@@ -305,7 +306,40 @@ def bench_gemm_chain_timeline(a: Args) -> None:
     print(json.dumps({"op": a.op, "model": a.model, "batch": a.batch, "unit": "us since first entry", "launches": rows}))
 
 
-OPS = {"gemm_chain_timeline": bench_gemm_chain_timeline, "gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
+def bench_moe_w4_timeline(a: Args) -> None:
+    """Phase stamps of CTA 0 of the NVFP4 grouped GEMM (gate|up of the --op=moe shapes): per load stage of 4 k-blocks
+    the nanoseconds, from the first copy request, at which the producer requested the copies, a de-quantising warp
+    saw them, it obtained an operand stage, the two groups finished their tensor-memory stores, the MMA thread had
+    both operands, and it had issued its MMAs."""
+    from zml_b200 import moe
+    from zml_b200.moe import ops as mops
+    from zml_b200.ops import _lib
+    d, f, e, k = a.k, a.n, a.experts, a.topk
+    g = torch.randn(e, f, d, device="cuda").bfloat16() * 0.02
+    u = torch.randn(e, f, d, device="cuda").bfloat16() * 0.02
+    qs = [moe.Nvfp4Experts.quantize(moe.interleave_gate_up(g, u)) for _ in range(2)]
+    x = torch.randn(a.tokens, d, device="cuda").bfloat16()
+    ids, _ = moe.router_topk(torch.randn(a.tokens, e, device="cuda"), k, True)
+    meta, sorted_pair, _ = mops.moe_align(ids, 0, e)
+    xs = mops.gather(x, sorted_pair, meta, e, k, a.tokens * k)
+    avg = max(1, a.tokens * k // e)
+    for i in range(3):
+        mops.grouped_gemm_w4(xs, qs[i % 2], meta, swiglu=True, avg_tokens=avg)
+    torch.cuda.synchronize()
+    buf = torch.zeros(64 * 8, dtype=torch.int64, device="cuda")
+    _lib.lib().zb_moe_w4_set_timeline(buf.data_ptr())
+    mops.grouped_gemm_w4(xs, qs[1], meta, swiglu=True, avg_tokens=avg)
+    torch.cuda.synchronize()
+    _lib.lib().zb_moe_w4_set_timeline(None)
+    t = buf.cpu().view(64, 8)
+    t0 = int(t[0, 0])
+    names = ["copies_requested", "copies_seen", "operand_stage_free", "stores_done_group0", "stores_done_group1", "mma_operands_ready",
+             "mmas_issued"]
+    stages = [{n: (int(v) - t0 if int(v) else None) for n, v in zip(names, t[q, :7])} for q in range(40) if int(t[q, 0])]
+    print(json.dumps({"op": a.op, "tokens": a.tokens, "experts": e, "stages": stages}))
+
+
+OPS = {"moe_w4_timeline": bench_moe_w4_timeline, "gemm_chain_timeline": bench_gemm_chain_timeline, "gemm": bench_gemm, "decode_attention": bench_decode_attention, "prefill_attention": bench_prefill_attention,
        "moe": bench_moe, "gated_delta_scan": bench_gated_delta_scan, "decode_layers": bench_decode_layers}
 
 
