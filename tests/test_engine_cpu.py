@@ -241,3 +241,42 @@ def test_prefill_in_two_halves_with_async_all_reduce_matches_whole_chunk(tmp_pat
                        capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("OVERLAP_OK") == 2
+
+
+_TP_CPU_WORKER = r"""
+import os, sys, torch
+sys.path.insert(0, os.environ["ZB_ROOT"])
+from zml_b200.models import registry
+from zml_b200.parallel.comm import Comm
+from zml_b200.serving import Engine
+c = Comm.from_env(backend="gloo")
+single = Comm.single(torch.device("cpu"))
+for name in ("tiny-llama-test", "tiny-moe-test", "tiny-qwen35-test", "tiny-qwen35-moe-test", "tiny-lfm2-test"):
+    prompts = [torch.randint(3, 200, (n,), generator=torch.Generator().manual_seed(11)).tolist() for n in (13, 30)]
+    got = {}
+    for label, comm in (("tp", c), ("single", single)):
+        model = registry.build_model(name, comm, device="cpu", seed=3, dtype=torch.float32)
+        eng = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=128)
+        got[label], _ = eng.generate(prompts, 6)
+    assert got["tp"] == got["single"], (name, got)
+    allo = c.all_gather_object(got["tp"])
+    assert all(o == allo[0] for o in allo), name
+print("TP_CPU_OK", c.rank, flush=True)
+c.finish(0)
+"""
+
+
+def test_every_model_family_under_two_way_parallelism_on_cpu(tmp_path):
+    """Tensor / expert parallel shards of every model family over two gloo ranks produce the tokens of one rank
+    holding the whole model (float32, CPU restatements of the kernels)."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "w.py"
+    script.write_text(_TP_CPU_WORKER)
+    env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29651", str(script)],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("TP_CPU_OK") == 2
