@@ -2,6 +2,8 @@
 dense-attention recomputation of the same weights."""
 import math
 
+import pytest
+
 import torch
 
 from zml_b200.models.common import SamplingStrategy
@@ -251,7 +253,7 @@ from zml_b200.parallel.comm import Comm
 from zml_b200.serving import Engine
 c = Comm.from_env(backend="gloo")
 single = Comm.single(torch.device("cpu"))
-for name in ("tiny-llama-test", "tiny-moe-test", "tiny-qwen35-test", "tiny-qwen35-moe-test", "tiny-lfm2-test"):
+for name in os.environ["ZB_FAMILIES"].split(","):
     prompts = [torch.randint(3, 200, (n,), generator=torch.Generator().manual_seed(11)).tolist() for n in (13, 30)]
     got = {}
     for label, comm in (("tp", c), ("single", single)):
@@ -266,17 +268,21 @@ c.finish(0)
 """
 
 
-def test_every_model_family_under_two_way_parallelism_on_cpu(tmp_path):
-    """Tensor / expert parallel shards of every model family over two gloo ranks produce the tokens of one rank
+@pytest.mark.parametrize("world,families", [
+    (2, "tiny-llama-test,tiny-moe-test,tiny-qwen35-test,tiny-qwen35-moe-test,tiny-lfm2-test"),
+    (4, "tiny-llama-test,tiny-moe-test"),           # the tiny hybrids have 2 linear-attention heads: not divisible by 4
+])
+def test_every_model_family_under_two_way_parallelism_on_cpu(tmp_path, world, families):
+    """Tensor / expert parallel shards of every model family over gloo ranks produce the tokens of one rank
     holding the whole model (float32, CPU restatements of the kernels)."""
     import os
     import subprocess
     import sys
     script = tmp_path / "w.py"
     script.write_text(_TP_CPU_WORKER)
-    env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29651", str(script)],
+    env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))), ZB_FAMILIES=families)
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+                        "--master-addr", "127.0.0.1", "--master-port", str(29651 + world), str(script)],
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
-    assert r.stdout.count("TP_CPU_OK") == 2
+    assert r.stdout.count("TP_CPU_OK") == world
