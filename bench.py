@@ -112,52 +112,36 @@ def tp_collectives(comm, args, baseline: bool) -> str:
     fused = getattr(comm, "fused", None)
     if fused is None or baseline or not args.fused:
         return "nccl"
-    tuned = fused.tuned or {}
-    note = (f" (measured at start, us per decoder layer: fused {tuned.get('fused_us')}, GEMM + tagged-slot all-reduce "
-            f"{tuned.get('ll_us')}, GEMM + NCCL {tuned.get('nccl_us')})") if tuned else ""
-    above = "in-kernel two-shot all-reduce over peer memory after the GEMM" if fused.ll_enabled else "NCCL after the GEMM"
-    if fused.fused_max_tokens > 0:
-        return (f"in-kernel (fused GEMM+all-reduce over peer memory) up to {fused.fused_max_tokens} tokens, {above} up to 256, "
-                "NCCL for prefill" + note)
-    return f"{above} for decode, NCCL for prefill" + note
+    parts = [f"row-parallel GEMM + all-reduce in one kernel over peer memory up to {fused.fused_max_tokens} tokens"]
+    if fused.ll_enabled:
+        parts.append("GEMM then in-kernel two-shot all-reduce over peer memory up to 256 tokens")
+    parts.append("prefill: " + fused.prefill_collective())
+    return "; ".join(parts)
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=3)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
-    ap.add_argument("--model", default="llama-3.1-8b", choices=sorted(WORKLOADS))
-    ap.add_argument("--batch", type=int, default=0)
-    ap.add_argument("--new-tokens", type=int, default=0)
-    ap.add_argument("--fused", type=int, default=1, help="fused GEMM+collective kernels for TP (0: NCCL)")
-    ap.add_argument("--seed", type=int, default=0)
-    args = ap.parse_args()
+# Headline configurations of the benchmark suite, measured in the same process group after the scaling
+# configuration: which ones run at which number of GPUs.
+HEADLINE = {8: ["llama-3.1-70b", "qwen3-30b-a3b-nvfp4"], 4: ["qwen3-30b-a3b-nvfp4"], 2: ["qwen3-30b-a3b-nvfp4"]}
 
-    if args.impl == "reference":
-        reference_unavailable()
-        return
+
+def run_workload(name: str, comm, args, steps: int, warmup: int, sample_clocks: bool):
+    """Builds the named model, runs `warmup` untimed and `steps` timed serving jobs, tears everything down.
+    Returns the metrics on every rank (times are the max over ranks)."""
+    import gc
 
     import torch
-    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
     from zml_b200.models.common import SamplingStrategy
     from zml_b200.models.registry import build_model
-    from zml_b200.parallel.comm import Comm
+    from zml_b200.ops import _lib
     from zml_b200.serving import Engine
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (B200)")
-    comm = Comm.from_env()
-    if comm.world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={comm.world}: launch with torch.distributed.run")
-    wl = dict(WORKLOADS[args.model])
-    if args.batch:
+    wl = dict(WORKLOADS[name])
+    if args.batch and name == args.model:
         wl["batch"] = args.batch
-    if args.new_tokens:
+    if args.new_tokens and name == args.model:
         wl["new_tokens"] = args.new_tokens
     baseline = args.impl == "baseline"
-    model = build_model(args.model, comm, device=comm.device, seed=args.seed, baseline=baseline,
+    model = build_model(name, comm, device=comm.device, seed=args.seed, baseline=baseline,
                         fused=bool(args.fused) and not baseline)
     lo, hi = wl["prompt"]
     g = torch.Generator().manual_seed(args.seed + 1)
@@ -173,16 +157,15 @@ def main() -> None:
     def job():
         return engine.generate(prompts, wl["new_tokens"], strat)
 
-    for _ in range(max(args.warmup, 0)):
+    for _ in range(max(warmup, 0)):
         job()
     comm.barrier()
     torch.cuda.synchronize()
-    from zml_b200.ops import _lib
-    sampler = ClockSampler(comm.rank == 0)
+    sampler = ClockSampler(sample_clocks and comm.rank == 0)
     launches0 = _lib.launch_count()
     dev_ms, ttfts, out_tokens, h2d, d2h = 0.0, [], 0, 0, 0
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         _, st = job()
         dev_ms += st.total_ms
         ttfts.extend(st.ttft_ms)
@@ -198,13 +181,64 @@ def main() -> None:
     wall_ms = comm.max_over_ranks(wall_ms)
     ttfts.sort()
     ttft_p50 = comm.max_over_ranks(ttfts[len(ttfts) // 2] if ttfts else 0.0)
+    res = dict(wl=wl, lo=lo, hi=hi, page=page, dev_ms=dev_ms, wall_ms=wall_ms, ttft_p50=ttft_p50, out_tokens=out_tokens,
+               h2d=h2d, d2h=d2h, launches=int(launches), clocks=clocks, collectives=tp_collectives(comm, args, baseline))
+    # free the model, its KV cache and the symmetric heap before the next configuration is built
+    del engine, model
+    if getattr(comm, "fused", None) is not None:
+        comm.fused.close()
+        comm.fused = None
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
+    ap.add_argument("--model", default="llama-3.1-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0)
+    ap.add_argument("--new-tokens", type=int, default=0)
+    ap.add_argument("--fused", type=int, default=1, help="fused GEMM+collective kernels for TP (0: NCCL)")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--headline", default="auto", choices=["auto", "none"],
+                    help="auto: after the scaling configuration also measure the headline configurations that fit this "
+                         "number of GPUs (Llama-3.1-70B and the NVFP4 MoE at 8, the MoE at 2 and 4), 3 timed jobs each")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        reference_unavailable()
+        return
+
+    import torch
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from zml_b200.parallel.comm import Comm
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200)")
+    comm = Comm.from_env()
+    if comm.world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={comm.world}: launch with torch.distributed.run")
+    r = run_workload(args.model, comm, args, args.steps, args.warmup, True)
+    headline = {}
+    if args.headline == "auto" and args.impl == "ours" and args.model == "llama-3.1-8b":
+        for name in HEADLINE.get(comm.world, []):
+            h = run_workload(name, comm, args, 3, 3, False)
+            headline[name] = {"tok_s": h["out_tokens"] / (h["dev_ms"] / 1e3), "ttft_p50_ms": h["ttft_p50"],
+                              "ms_per_step": h["dev_ms"] / 3, "steps": 3, "warmup": 3,
+                              "e2e_tok_s": h["out_tokens"] / (h["wall_ms"] / 1e3), "global_batch": h["wl"]["batch"],
+                              "seq_len": [h["lo"], h["hi"]], "new_tokens": h["wl"]["new_tokens"],
+                              "tp_collectives": h["collectives"]}
     if comm.rank == 0:
         steps = max(args.steps, 1)
-        value = out_tokens / (dev_ms / 1e3)
+        wl, dev_ms, wall_ms = r["wl"], r["dev_ms"], r["wall_ms"]
         tp = f"tp{comm.world}" if comm.world > 1 else "single"
-        print(json.dumps({
+        line = {
             "metric": "output tokens/sec/box",
-            "value": value,
+            "value": r["out_tokens"] / (dev_ms / 1e3),
             "unit": "tokens/s",
             "n_gpus": comm.world,
             "steps": args.steps,
@@ -216,20 +250,23 @@ def main() -> None:
             "dtype": "bf16",
             "data": "synthetic token ids, random-init weights N(0,0.02)",
             "impl": args.impl,
-            "ttft_p50_ms": ttft_p50,
+            "ttft_p50_ms": r["ttft_p50"],
             "config": {
-                "model": args.model, "global_batch": wl["batch"], "seq_len": [lo, hi],
-                "new_tokens": wl["new_tokens"], "parallelism": tp, "kv_page": page,
+                "model": args.model, "global_batch": wl["batch"], "seq_len": [r["lo"], r["hi"]],
+                "new_tokens": wl["new_tokens"], "parallelism": tp, "kv_page": r["page"],
                 "step": "one full serving job (prefill of all prompts + greedy decode)",
                 "l2": "inputs larger than L2 (weights streamed every decode step); no flush",
-                "tp_collectives": tp_collectives(comm, args, baseline),
+                "tp_collectives": r["collectives"],
             },
-            "clocks": clocks,
-            "e2e": {"value": out_tokens / (wall_ms / 1e3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": h2d // steps, "d2h_bytes_per_step": d2h // steps,
+            "clocks": r["clocks"],
+            "e2e": {"value": r["out_tokens"] / (wall_ms / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": r["h2d"] // steps, "d2h_bytes_per_step": r["d2h"] // steps,
                     "ms_per_step": wall_ms / steps},
-            "gpu_launches": int(launches),
-        }))
+            "gpu_launches": r["launches"],
+        }
+        if headline:
+            line["headline"] = headline
+        print(json.dumps(line))
     comm.finish(0)
 
 

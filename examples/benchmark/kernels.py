@@ -211,13 +211,31 @@ def bench_decode_layers(a: Args) -> None:
     nl = c.num_hidden_layers
     qd = torch.randn(B, model.hq, c.hd, device="cuda").bfloat16()
 
+    fused = hasattr(model, "wants_fused_layout") and model.wants_fused_layout()
+    if fused:
+        model.prepare_fused()
+
     def full():
-        x = x0
+        x = x0.clone()
+        if fused:      # norms and SwiGLU inside the GEMM epilogues, row statistics handed from GEMM to GEMM
+            st = ops.row_sumsq(x)
+            for l in range(nl):
+                x, st = model._layer_fused(l, x, st, meta, kv)
+            return
         for l in range(nl):
             x = model.layer(l, x, meta, kv)
 
     def gemms():
-        x = x0
+        x = x0.clone()
+        if fused:
+            st = ops.row_sumsq(x)
+            for l in range(nl):
+                lw = model.layers[l]
+                qkv = ops.gemm(x, lw.qkv, static_w=True, row_stats=st, eps=1e-5)
+                x, st = ops.gemm(qkv[:, :model.hq * c.hd], lw.o, residual=x, out=x, static_w=True, emit_stats=True)
+                act = ops.gemm(x, lw.gate_up, static_w=True, row_stats=st, eps=1e-5, swiglu=True)
+                x, st = ops.gemm(act, lw.down, residual=x, out=x, static_w=True, emit_stats=True)
+            return
         for l in range(nl):
             lw = model.layers[l]
             qkv = ops.gemm(x, lw.qkv, static_w=True)

@@ -7,6 +7,7 @@ all-reduce and GEMM + NCCL variants of the same decoder layers, as CUDA graphs, 
 Arguments: model preset, tensor-parallel degree whose SHARD SHAPES are used (may exceed the number of ranks: the
 collectives then run over the real ranks, the GEMMs and attention on the shapes of the larger degree), batch,
 cached tokens per sequence.  Prints, on rank 0, the whole layer, its GEMMs + collectives alone and its attention alone.
+ZB_FOLD_NORMS=0 times the layer with separate RMSNorm and SwiGLU kernels instead of the GEMM epilogues.
 """
 
 import os, sys, torch, ctypes
@@ -35,12 +36,29 @@ splits = ops.decode_plan_splits(B, model.hkv, L + 64)
 meta = AttnMeta(False, pos, slot, bt, pos + 1, num_splits=splits, max_seq_len=L + 64)
 x0 = ctx.act[0][:B * cfg.hidden_size].view(B, cfg.hidden_size); x0.normal_()
 nl = cfg.num_hidden_layers
+fused_layout = os.environ.get("ZB_FOLD_NORMS", "1") != "0"
+if fused_layout:
+    model.prepare_fused()
 def full():
     x = x0
+    if fused_layout:       # norms and SwiGLU in the GEMM epilogues: 6 launches per layer
+        st = ops.row_sumsq(x)
+        for l in range(nl):
+            x, st = model._layer_fused(l, x, st, meta, kv)
+        return
     for l in range(nl):
         x = model.layer(l, x, meta, kv)
 def gemm_ar_only():
     x = x0
+    if fused_layout:
+        st = ops.row_sumsq(x)
+        for l in range(nl):
+            lw = model.layers[l]
+            qkv = ops.gemm(x, lw.qkv, static_w=True, row_stats=st)
+            x, st = model.row_parallel(qkv[:, :model.hq * cfg.hd], lw.o, x, emit_stats=True, next_w=lw.gate_up)
+            act = ops.gemm(x, lw.gate_up, static_w=True, row_stats=st, swiglu=True)
+            x, st = model.row_parallel(act, lw.down, x, emit_stats=True, next_w=model.layers[(l + 1) % nl].qkv)
+        return
     for l in range(nl):
         lw = model.layers[l]
         qkv = ops.gemm(x, lw.qkv, static_w=True)
@@ -70,7 +88,7 @@ def graph_us(fn, reps=10):
     return round(e0.elapsed_time(e1) / reps / nl * 1000, 1)
 for mode in ("fused", "ll", "nccl"):
     comm.fused = ctx if mode != "nccl" else None
-    ctx.fused_max_tokens, ctx.ll_enabled = (32 if mode == "fused" else 0), mode == "ll"
+    ctx.fused_max_tokens, ctx.ll_enabled = (int(os.environ.get("ZB_FUSED_MAX_TOKENS", "32")) if mode == "fused" else 0), mode == "ll"
     row = {"full": graph_us(full), "gemm+ar": graph_us(gemm_ar_only), "attn": graph_us(attn)}
     if comm.rank == 0:
         print(f"{name} shapes_tp={shapes_tp} B={B} L={L} {mode} us/layer: {row} splits={splits} hq={model.hq} hkv={model.hkv}", flush=True)

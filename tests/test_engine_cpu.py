@@ -10,6 +10,7 @@ from zml_b200.models.common import SamplingStrategy
 from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
 from zml_b200.nn import rotary as rope_mod
 from zml_b200.ops import reference as ref
+from zml_b200 import ops, testing
 from zml_b200.serving import Engine
 
 
@@ -200,49 +201,75 @@ def test_moe_loads_nvfp4_expert_checkpoints(tmp_path):
         assert len(outs[0]) == 4
 
 
-_OVERLAP_WORKER = r"""
+def test_fused_kernel_layout_matches_plain_layers():
+    """Norm weights folded into the qkv / gate|up columns, gate and up rows interleaved, row statistics handed
+    from GEMM to GEMM: the same hidden states as RMSNorm -> GEMM -> SwiGLU layer by layer (float32, CPU)."""
+    from zml_b200.models.llama import AttnMeta
+    cfg = LlamaConfig.from_hf(PRESETS["tiny-llama-test"])
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, cfg.vocab_size, (19,), generator=g, dtype=torch.int32)
+    outs = {}
+    for fused in (False, True):
+        model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=2, std=0.05)
+        for lw in model.layers:             # norm weights that are not all ones
+            lw.input_norm.copy_(1.0 + 0.3 * torch.randn(lw.input_norm.shape, generator=torch.Generator().manual_seed(5)))
+            lw.post_norm.copy_(1.0 + 0.3 * torch.randn(lw.post_norm.shape, generator=torch.Generator().manual_seed(6)))
+        if fused:
+            model.prepare_fused()
+            with pytest.raises(RuntimeError):
+                model.state_dict_hf()
+        kv = torch.zeros(model.kv_cache_shape(4, 16), dtype=torch.float32)
+        meta = AttnMeta(True, torch.arange(19, dtype=torch.int32), torch.arange(16, 35, dtype=torch.int32),
+                        torch.tensor([[1, 2, 3]], dtype=torch.int32), torch.tensor([19], dtype=torch.int32),
+                        torch.tensor([0, 19], dtype=torch.int32), total_q_blocks=1)
+        outs[fused] = model.hidden_states(ids, meta, kv)
+        if fused:      # `layer` stays usable on its own in this layout
+            x = ops.embedding(ids, model.embed)
+            y = model.layer(0, x, meta, torch.zeros_like(kv))
+            assert y.shape == x.shape
+    testing.expect_close(outs[True], outs[False], atol=2e-4, rtol=2e-4)
+
+
+_VOCAB_WORKER = r"""
 import os, sys, torch
 sys.path.insert(0, os.environ["ZB_ROOT"])
+from zml_b200.models.common import SamplingStrategy
 from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
 from zml_b200.parallel.comm import Comm
 from zml_b200.serving import Engine
 c = Comm.from_env(backend="gloo")
-cfg = LlamaConfig.from_hf(PRESETS["tiny-llama-test"])
+single = Comm.single(torch.device("cpu"))
+cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=1021, tie_word_embeddings=False))
 g = torch.Generator().manual_seed(3)
-prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 9, 31, 22)]
-outs, calls = {}, {}
-for name, threshold in (("whole", 10 ** 9), ("halves", 16)):
-    model = LlamaModel(cfg, c, device="cpu", dtype=torch.float32).init_random(seed=5, std=0.05)
-    model.prefill_overlap_min_tokens = threshold
-    n = [0]
-    inner = model._hidden_states_overlapped
-    def counted(*a, _inner=inner, _n=n, **k):
-        _n[0] += 1
-        return _inner(*a, **k)
-    model._hidden_states_overlapped = counted
-    eng = Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128)
-    outs[name], _ = eng.generate(prompts, 6)
-    calls[name] = n[0]
-assert calls["whole"] == 0 and calls["halves"] >= 1, calls
-assert outs["whole"] == outs["halves"], outs
-print("OVERLAP_OK", c.rank, flush=True)
+prompts = [torch.randint(3, cfg.vocab_size, (n,), generator=g).tolist() for n in (17, 9)]
+for strat in (SamplingStrategy(topk=1), SamplingStrategy(topk=4, temperature=0.8)):
+    got = {}
+    for label, comm in (("tp", c), ("single", single)):
+        model = LlamaModel(cfg, comm, device="cpu", dtype=torch.float32).init_random(seed=5, std=0.05)
+        assert model.lm_head.shape[0] == model.v_per
+        torch.manual_seed(99)
+        got[label], _ = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=128).generate(prompts, 6, strat)
+    assert got["tp"] == got["single"], (strat, got)
+    assert all(t < cfg.vocab_size for o in got["tp"] for t in o)
+print("VOCAB_OK", c.rank, flush=True)
 c.finish(0)
 """
 
 
-def test_prefill_in_two_halves_with_async_all_reduce_matches_whole_chunk(tmp_path):
-    """Tensor-parallel prefill split at a sequence boundary, all-reduces issued asynchronously: same tokens."""
+def test_vocab_parallel_head_with_a_vocabulary_that_does_not_divide(tmp_path):
+    """1021 tokens over 2 ranks: the last rank's missing rows are zero rows masked to -inf, greedy and top-k
+    sampling give the tokens of one rank holding the whole head."""
     import os
     import subprocess
     import sys
     script = tmp_path / "w.py"
-    script.write_text(_OVERLAP_WORKER)
+    script.write_text(_VOCAB_WORKER)
     env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                         "--master-addr", "127.0.0.1", "--master-port", "29641", str(script)],
                        capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
-    assert r.stdout.count("OVERLAP_OK") == 2
+    assert r.stdout.count("VOCAB_OK") == 2
 
 
 _TP_CPU_WORKER = r"""

@@ -58,6 +58,60 @@ def test_gemm_split_k_and_epilogue(m, n, k, splits):
     expect_close(inplace.float(), a.float() @ w.float().t() + res.float(), atol=3e-2, rtol=2e-2, min_close=0.999)
 
 
+# every epilogue path of the GEMM: cluster split-K with 4, 3 (odd band heights) and 8 CTAs, the stream-K fix-up,
+# the generic swap-AB path with 128- and 256-token tiles, and whole tiles with tokens as rows
+EPI_SHAPES = [(32, 4096, 4096), (32, 6144, 4096), (8, 2048, 8192), (32, 28672, 4096), (64, 512, 1024), (100, 2048, 4096),
+              (200, 1024, 2048), (257, 1024, 1024), (512, 4096, 2048), (1000, 2048 + 64, 512)]
+
+
+@pytest.mark.parametrize("m,n,k", EPI_SHAPES)
+def test_gemm_row_scale_and_swiglu_epilogues(m, n, k):
+    """rmsnorm(a) @ (w * g)^T as one GEMM with a per-row scale from partial sums of squares, and SwiGLU on
+    interleaved gate / up rows, against the unfused float32 chain."""
+    torch.manual_seed(m + n + k)
+    a = _randn(m, k)
+    w = _randn(n, k, scale=1.0 / math.sqrt(k))
+    g = (1.0 + 0.2 * torch.randn(k, device=DEV)).bfloat16()
+    stats = ops.row_sumsq(a)
+    expect_close(stats.total(), a.float().pow(2).sum(-1), atol=1e-2, rtol=1e-3)
+    # the partial sums may come in several parts: split the one part in three unequal ones
+    parts = torch.stack([stats.parts[0] * 0.5, stats.parts[0] * 0.25, stats.parts[0] * 0.25])
+    stats3 = ops.RowStats(parts.contiguous(), 3)
+    wf = (w.float() * g.float()[None, :]).bfloat16()
+    normed = a.float() * torch.rsqrt(a.float().pow(2).mean(-1, keepdim=True) + 1e-5)
+    want = normed @ wf.float().t()
+    bias = _randn(n)
+    res = _randn(m, n)
+    got = ops.gemm(a, wf, row_stats=stats3, eps=1e-5, bias=bias, residual=res)
+    expect_close(got.float(), want + bias.float() + res.float(), atol=3e-2, rtol=2e-2, min_close=0.999)
+    # SwiGLU on top of the row scale
+    want_act = torch.nn.functional.silu(want[:, : n // 2]) * want[:, n // 2:]
+    act = ops.gemm(a, ops.interleave_gate_up(wf), row_stats=stats, eps=1e-5, swiglu=True)
+    assert act.shape == (m, n // 2)
+    expect_close(act.float(), want_act, atol=3e-2, rtol=3e-2, min_close=0.998)
+    # SwiGLU alone equals the separate kernel on the rounded GEMM output, up to that rounding
+    act2 = ops.gemm(a, ops.interleave_gate_up(w), swiglu=True)
+    expect_close(act2.float(), ref.swiglu((a.float() @ w.float().t()).bfloat16()).float(), atol=3e-2, rtol=3e-2, min_close=0.998)
+
+
+@pytest.mark.parametrize("m,n,k", EPI_SHAPES)
+def test_gemm_emits_row_statistics_of_its_output(m, n, k):
+    torch.manual_seed(m * 3 + n)
+    a = _randn(m, k)
+    w = _randn(n, k, scale=1.0 / math.sqrt(k))
+    res = _randn(m, n)
+    out, stats = ops.gemm(a, w, residual=res, emit_stats=True)
+    expect_close(out.float(), a.float() @ w.float().t() + res.float(), atol=3e-2, rtol=2e-2, min_close=0.999)
+    # the statistics describe the stored (rounded) output exactly, up to fp32 summation order
+    expect_close(stats.total(), out.float().pow(2).sum(-1), atol=1e-2, rtol=1e-4, min_close=1.0)
+    # twice: same bits (fixed summation order), also in place on the residual
+    out2, stats2 = ops.gemm(a, w, residual=res, emit_stats=True)
+    assert torch.equal(out, out2) and stats.n == stats2.n and torch.equal(stats.parts[:stats.n], stats2.parts[:stats2.n])
+    inplace = res.clone()
+    out3, stats3 = ops.gemm(a, w, residual=inplace, out=inplace, emit_stats=True, prefetch=w)
+    assert torch.equal(out3, out) and torch.equal(stats3.total(), stats.total())
+
+
 @pytest.mark.parametrize("rows,d", [(1, 2048), (33, 4096), (64, 8192), (5, 1024 + 8), (3, 16384)])
 @pytest.mark.parametrize("with_res", [False, True])
 def test_rmsnorm(rows, d, with_res):

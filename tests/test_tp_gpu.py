@@ -1,4 +1,5 @@
-"""Multi-GPU tests (2 ranks): in-kernel collectives, fused GEMM + all-reduce, TP engine."""
+"""Multi-GPU tests: in-kernel collectives, fused GEMM + all-reduce, tensor-parallel models.  One worker process
+per GPU, on 2, 4 and 8 ranks as far as the machine has GPUs."""
 import os
 import subprocess
 import sys
@@ -10,10 +11,11 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_fused_collectives_and_engine():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
-           "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "tp_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_collectives_and_tensor_parallel_models(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29611 + world), os.path.join(ROOT, "tests", "tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode == 0 and "TP_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

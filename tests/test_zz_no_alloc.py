@@ -49,11 +49,16 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
         bias = torch.randn(n, device=dev).bfloat16()
         want = ops.gemm(a, w, residual=res, bias=bias)
         out = torch.full_like(want, float("nan"))
-        mem_before = torch.cuda.memory_allocated()
-        assert _call(fn, a, w, out, res, bias, status) == 0
-        assert _call(fn, a, w, out, res, bias, status) == 0          # second call, same array
+        assert _call(fn, a, w, out, res, bias, status) == 0          # first call of this tile shape: set-up
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == mem_before
+        # free device memory as the driver sees it: an allocation made inside the library (which torch's own
+        # counters cannot see) would show here
+        free_before = torch.cuda.mem_get_info()[0]
+        out.fill_(float("nan"))
+        assert _call(fn, a, w, out, res, bias, status) == 0
+        assert _call(fn, a, w, out, res, bias, status) == 0          # again right away, same array
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
         assert status.tolist() == [0, 0, 0, 0]
         expect_close(out.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.999)
         ref = a.float() @ w.float().t() + bias.float() + res.float()
@@ -63,6 +68,13 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
     w = torch.randn(256, 512, device=dev).bfloat16()
     out32 = torch.empty(16, 256, device=dev)
     assert _call(fn, a, w, out32, None, None, status) == 0
+    torch.cuda.synchronize()
+    expect_close(out32, ops.gemm(a, w, out_dtype=torch.float32), atol=1e-2, rtol=1e-2, min_close=0.999)
+    # any non-zero out_f32 means fp32 output (and nothing else)
+    out32.fill_(float("nan"))
+    m, k = a.shape
+    assert fn(a.data_ptr(), w.data_ptr(), out32.data_ptr(), None, None, m, 256, k, k, k, 256, 2, status.data_ptr(),
+              torch.cuda.current_stream().cuda_stream) == 0
     torch.cuda.synchronize()
     expect_close(out32, ops.gemm(a, w, out_dtype=torch.float32), atol=1e-2, rtol=1e-2, min_close=0.999)
 

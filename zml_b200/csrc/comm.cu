@@ -180,6 +180,98 @@ zb_allreduce_ll_kernel(const uint4* __restrict__ in, const uint4* __restrict__ r
   }
 }
 
+// ------------------------------------------------------------------ all-reduce through NVSwitch (multimem)
+// out = residual + sum over ranks of `in`, bf16, any size that is a multiple of 16 bytes; `in` and `out` live at
+// the same offsets of every rank's heap, and the heap is bound to a multicast address.  Every rank owns a
+// contiguous shard of the tensor: it loads the shard with multimem.ld_reduce (NVSwitch fetches the W copies
+// and returns their sum, accumulated in fp32 - one rank computes every element, so all ranks end with the
+// same bits), adds the residual, and writes the result into every rank's `out` with one multimem.st.  Per
+// rank about one tensor's worth of bytes crosses NVLink in each direction, against 2 (W - 1) / W through a
+// ring or peer stores.  A cross-rank barrier per block brackets the pass: before it, every rank's partial
+// sums are complete (the kernel that wrote them precedes this one on the stream); after it, every shard has
+// been written everywhere.  `in` == `out` is allowed: an element is read and written by its owner only.
+// The reference gets this sum from NCCL through XLA (zml/ops.zig:24-173).
+constexpr uint32_t kKernelAllReduceMm = 12;
+constexpr int kMmMaxBlocks = 128;
+
+struct MmAllReduce {
+  char* mc;                 // multicast base of the heaps
+  uint32_t* flags[8];       // [2 phases][kMmMaxBlocks][8] u32 in every rank's heap ([rank] is local)
+  uint32_t* epoch;
+  uint32_t* ticket;
+  int rank;
+  int world;
+};
+
+__global__ void __launch_bounds__(512)
+zb_allreduce_mm_kernel(size_t in_off, size_t out_off, const uint4* __restrict__ residual, long long n_vec, const MmAllReduce ar,
+                       ZbStatus* status) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) abort_flag = 0u;
+  __syncthreads();
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(ar.epoch);
+  const int W = ar.world, rank = ar.rank;
+  auto block_barrier = [&](int phase) {
+    // rank r's block b tells block b of every rank that it got here, and waits for all of them
+    if (static_cast<int>(threadIdx.x) < W) {
+      const size_t slot = (static_cast<size_t>(phase) * kMmMaxBlocks + blockIdx.x) * 8;
+      __threadfence_system();
+      zb_st_release_sys(ar.flags[threadIdx.x] + slot + rank, epoch);
+      if (!zb_wait_flag(ar.flags[rank] + slot + threadIdx.x, epoch, &abort_flag))
+        zb_record_error(status, ZB_ERR_FLAG_TIMEOUT, kKernelAllReduceMm, static_cast<uint32_t>(phase * 8 + threadIdx.x), epoch);
+    }
+    __syncthreads();
+  };
+  block_barrier(0);
+  if (abort_flag == 0u) {
+    const long long vs = (n_vec + W - 1) / W;                       // vectors per shard
+    const long long v0 = static_cast<long long>(rank) * vs;
+    const long long mine = max(0ll, min(vs, n_vec - v0));
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    constexpr int kUnroll = 4;                                      // loads in flight per thread
+    for (long long base = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; base < mine; base += stride * kUnroll) {
+      uint4 v[kUnroll], r[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long i = base + u * stride;
+        if (i < mine) {
+          v[u] = zb_multimem_ld_reduce_bf16x8(ar.mc + in_off + static_cast<size_t>(v0 + i) * 16);
+          r[u] = residual != nullptr ? residual[v0 + i] : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const long long i = base + u * stride;
+        if (i < mine) {
+          if (residual != nullptr) {
+            const uint32_t a[4] = {v[u].x, v[u].y, v[u].z, v[u].w}, b[4] = {r[u].x, r[u].y, r[u].z, r[u].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 fa = zb_unpack_bf16x2(a[q]), fb = zb_unpack_bf16x2(b[q]);
+              o[q] = zb_pack_bf16x2(fa.x + fb.x, fa.y + fb.y);
+            }
+            v[u] = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+          zb_multimem_st_16(ar.mc + out_off + static_cast<size_t>(v0 + i) * 16, v[u]);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  block_barrier(1);
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(ar.ticket, 1u);
+    if (ticket == gridDim.x - 1) {
+      *ar.ticket = 0u;
+      *reinterpret_cast<volatile uint32_t*>(ar.epoch) = epoch + 1u;
+    }
+  }
+}
+
 }  // namespace
 
 // A wait with a caller-chosen limit on a flag the caller owns: the building block of every
@@ -253,16 +345,23 @@ ZbArContext* zb_ar_ctx_create(int rank, int world, void* const* heap, size_t rec
   c->done_flag_off = done_flag_off;
   c->max_tiles = max_tiles;
   uint32_t* ctr = nullptr;
-  if (cudaMalloc(&ctr, 8 * sizeof(uint32_t)) != cudaSuccess) {
+  if (cudaMalloc(&ctr, 16 * sizeof(uint32_t)) != cudaSuccess) {
     delete c;
     return nullptr;
   }
-  // {gemm epoch, exit ticket, barrier epoch, unused, combine epoch, combine exit ticket, all-reduce epoch, its exit ticket}
-  const uint32_t init[8] = {1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u};
+  // {gemm epoch, exit ticket, barrier epoch, unused, combine epoch, combine exit ticket, tagged-slot all-reduce epoch,
+  //  its exit ticket, multimem all-reduce epoch, its exit ticket, band-pipeline epoch, unused ...}
+  const uint32_t init[16] = {1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u};
   cudaMemcpy(ctr, init, sizeof(init), cudaMemcpyHostToDevice);
   c->epoch = ctr;
   c->exit_ticket = ctr + 1;
+  c->mc_heap = nullptr;
   return c;
+}
+
+// Tells the context the NVLink multicast address that aliases every rank's heap (null: none).
+void zb_ar_ctx_set_multicast(ZbArContext* c, void* mc_heap) {
+  if (c != nullptr) c->mc_heap = mc_heap;
 }
 
 void zb_ar_ctx_destroy(ZbArContext* c) {
@@ -314,10 +413,47 @@ int zb_allreduce_ll(const ZbArContext* c, const void* in, const void* residual, 
   ar.rank = c->rank;
   ar.world = c->world;
   long long blocks = (vs + 127) / 128;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  // Threads of one rank wait for the same threads of its peers, so every block of the grid must be resident at once
+  // on every rank: the grid never exceeds what the occupancy calculator says fits (the grid-stride loop covers the rest).
+  static int resident_per_sm = 0;
+  if (resident_per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, zb_allreduce_ll_kernel, 128, 0) != cudaSuccess || n < 1) n = 1;
+    resident_per_sm = n > 8 ? 8 : n;
+  }
+  const long long cap = static_cast<long long>(st->num_sms) * resident_per_sm;
+  if (blocks > cap) blocks = cap;
   zb_launch(zb_allreduce_ll_kernel, dim3(static_cast<unsigned>(blocks)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
             reinterpret_cast<const uint4*>(in), reinterpret_cast<const uint4*>(residual), reinterpret_cast<uint4*>(out), vs, ar,
             st->status);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out = residual + sum over the group of `in` by multimem load-reduce and store (see zb_allreduce_mm_kernel).  `in_off` and
+// `out_off` are byte offsets into every rank's heap (16-byte aligned, may be equal); `flag_off` addresses
+// 2 * 128 * 8 u32 of flags; `residual` (may be null) is local.  Needs a context with a multicast address.
+int zb_allreduce_mm(const ZbArContext* c, size_t in_off, size_t out_off, const void* residual, long long elems, size_t flag_off,
+                    void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (!st || !c) return -20;
+  if (c->mc_heap == nullptr) return -69;
+  if (elems <= 0) return 0;
+  if (elems % 8 != 0 || in_off % 16 != 0 || out_off % 16 != 0 || flag_off % 16 != 0) return -10;
+  const long long n_vec = elems / 8;
+  MmAllReduce ar = {};
+  ar.mc = reinterpret_cast<char*>(c->mc_heap);
+  for (int r = 0; r < c->world; ++r) ar.flags[r] = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(c->heap[r]) + flag_off);
+  ar.epoch = c->epoch + 8;
+  ar.ticket = c->epoch + 9;
+  ar.rank = c->rank;
+  ar.world = c->world;
+  const long long vs = (n_vec + c->world - 1) / c->world;
+  long long blocks = (vs + 512 * 4 - 1) / (512 * 4);
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMmMaxBlocks) blocks = kMmMaxBlocks;
+  zb_launch(zb_allreduce_mm_kernel, dim3(static_cast<unsigned>(blocks)), dim3(512), 0, reinterpret_cast<cudaStream_t>(stream), in_off,
+            out_off, reinterpret_cast<const uint4*>(residual), n_vec, ar, st->status);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

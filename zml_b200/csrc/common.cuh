@@ -424,3 +424,22 @@ ZB_DEVICE bool zb_wait_flag_limit(const uint32_t* p, uint32_t epoch, volatile ui
 ZB_DEVICE bool zb_wait_flag(const uint32_t* p, uint32_t epoch, volatile uint32_t* abort_flag) {
   return zb_wait_flag_limit(p, epoch, abort_flag, ZB_WAIT_LIMIT_NS);
 }
+
+// ----------------------------------------------------------------------------
+// multimem: loads and stores on an NVLink multicast address (one virtual address bound to the same buffer of
+// every GPU of the group).  A load-reduce returns the sum over all GPUs' copies, added up inside NVSwitch
+// (fp32 accumulation of the bf16 pairs); a store writes every GPU's copy.  16 bytes per instruction.
+// ----------------------------------------------------------------------------
+ZB_DEVICE uint4 zb_multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+ZB_DEVICE void zb_multimem_st_16(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}

@@ -60,6 +60,7 @@ struct GemmParams {
   float* workspace;  // [grid][2][BN][128] fp32 partial tiles
   uint32_t* counters;  // one per output tile, zero between launches
   ZbStatus* status;
+  ZbGemmEpi epi;       // row scale / SwiGLU / sum-of-squares / next-weight prefetch (host_api.h)
   ZbFusedAr ar;        // used by the fused GEMM + all-reduce variant only
 };
 
@@ -67,24 +68,23 @@ struct GemmParams {
 // weight-streaming configurations for two CTAs per SM, so that the next GEMM of the stream could
 // run under this one's tail, measured slower: 127 vs 121 us per decoder layer on the 8B shapes.)
 __host__ __device__ constexpr int stages_for(int bn, bool swap) {
-#ifdef ZB_GEMM_TWO_CTA
-  if (swap) return bn <= 16 ? 6 : (bn <= 32 ? 5 : (bn <= 64 ? 4 : (bn <= 128 ? 3 : 4)));
-#endif
   (void)swap;
   return bn >= 256 ? 4 : (bn >= 128 ? 6 : 8);
 }
 __host__ __device__ constexpr int stage_bytes(int bn) { return (kBlockP + bn) * kBlockK * 2; }
+// Dynamic shared memory of one CTA: the operand ring, 1 KB of alignment slack, 256 bytes of barriers and
+// flags, and a table of 256 per-token scales (row scale of the epilogue, swap-AB only).
+constexpr int kTailBytes = 256;
+constexpr int kScaleTabBytes = 256 * 4;
+__host__ __device__ constexpr int smem_bytes_for(int bn, bool swap) {
+  return stages_for(bn, swap) * stage_bytes(bn) + 1024 + kTailBytes + kScaleTabBytes;
+}
 
 ZB_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-#ifdef ZB_GEMM_TWO_CTA
-#define ZB_GEMM_MIN_CTAS(SWAP, BN) (((SWAP) && (BN) <= 128) ? 2 : 1)
-#else
-#define ZB_GEMM_MIN_CTAS(SWAP, BN) 1
-#endif
+ZB_DEVICE float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
 template <int BN, bool SWAP, bool FUSED>
-__global__ void __launch_bounds__(kNumThreads, ZB_GEMM_MIN_CTAS(SWAP, BN))
+__global__ void __launch_bounds__(kNumThreads, 1)
 zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                     const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
   constexpr int kStages = stages_for(BN, SWAP);
@@ -105,6 +105,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   volatile uint32_t* abort_flag = tmem_holder + 1;
   volatile uint32_t* is_last_flag = tmem_holder + 2;
   volatile uint32_t* abort_where = tmem_holder + 3;
+  float* scale_tab = reinterpret_cast<float*>(smem + kStages * kStageBytes + kTailBytes);   // [256], swap-AB only
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -206,7 +207,29 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // residual and write the output, wait here.
   zb_pdl_launch();
   if (tl && threadIdx.x == 0) tl[1] = zb_globaltimer();
-  if (warp >= 2) zb_pdl_wait();
+  if (warp >= 2) {
+    zb_pdl_wait();
+    if constexpr (SWAP) {
+      // per-token scale of the accumulators (tokens are the tile's columns; a swap-AB problem has one column
+      // tile): computed here, while the main loop runs, from the partial sums the producing kernel left
+      if (prm.epi.in_sumsq != nullptr) {
+        for (int t = threadIdx.x - 64; t < BN; t += kEpiThreads) {
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};
+          if (t < prm.rows_q) {
+            const float* src = prm.epi.in_sumsq + t;
+            int i = 0;
+            for (; i + 4 <= prm.epi.in_parts; i += 4) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) s4[j] += __ldcg(src + static_cast<size_t>(i + j) * prm.epi.in_ld);
+            }
+            for (; i < prm.epi.in_parts; ++i) s4[0] += __ldcg(src + static_cast<size_t>(i) * prm.epi.in_ld);
+          }
+          scale_tab[t] = rsqrtf(((s4[0] + s4[1]) + (s4[2] + s4[3])) * prm.epi.in_inv_d + prm.epi.in_eps);
+        }
+        epi_bar_sync();
+      }
+    }
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -251,6 +274,19 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           }
         }
         u += kb1 - kb0;
+      }
+      if (prm.epi.pf_bytes != 0ull) {
+        // this CTA's share of the next GEMM's weights goes to L2 while the epilogue (and, in the tensor-parallel
+        // variant, the exchange with the peers) runs: HBM is otherwise idle from here on
+        constexpr unsigned long long kChunk = 16384ull;
+        const unsigned long long nchunks = (prm.epi.pf_bytes + kChunk - 1) / kChunk;
+        for (unsigned long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
+          const unsigned long long off = c * kChunk;
+          const uint32_t sz = static_cast<uint32_t>(min(kChunk, prm.epi.pf_bytes - off)) & ~15u;
+          if (sz != 0u)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(prm.epi.pf_ptr) + off), "r"(sz)
+                         : "memory");
+        }
       }
     }
     if (prm.cluster > 1) {
@@ -337,6 +373,15 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const long long t_begin = static_cast<long long>(t) * kb_total;
       const int first_cta = static_cast<int>(t_begin / prm.units_per_cta);
       const int last_cta = static_cast<int>((t_begin + kb_total - 1) / prm.units_per_cta);
+      float row_scale = 1.f;       // !SWAP: tokens are the tile's rows, this thread owns one
+      if constexpr (!SWAP) {
+        if (prm.epi.in_sumsq != nullptr) {
+          const int pr = min(pt * kBlockP + row_in_tile, prm.rows_p - 1);
+          float ssum = 0.f;
+          for (int i = 0; i < prm.epi.in_parts; ++i) ssum += __ldcg(prm.epi.in_sumsq + static_cast<size_t>(i) * prm.epi.in_ld + pr);
+          row_scale = rsqrtf(ssum * prm.epi.in_inv_d + prm.epi.in_eps);
+        }
+      }
       zb_mbar_wait(&tmem_full[acc], acc_phase, abort_flag);
       if (tl && epi_tid == 0 && tl[5] == 0ull) tl[5] = zb_globaltimer();
       epi_bar_sync();
@@ -369,18 +414,34 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           did_cluster_sync = true;
           const int S = prm.cluster;
           const int rank = static_cast<int>(zb_cluster_ctarank());
-          const int rb0 = rank * kBlockP / S, rb1 = (rank + 1) * kBlockP / S;
+          // bands begin on even rows: with interleaved gate / up rows (SwiGLU epilogue) a pair never straddles two CTAs
+          const int rb0 = (rank * (kBlockP / 2) / S) * 2, rb1 = ((rank + 1) * (kBlockP / 2) / S) * 2;
           const int nrows = rb1 - rb0;
           const int total = BN * nrows;
           const uint32_t part_u32 = zb_smem_u32(part);
           uint32_t peer_base[8];
 #pragma unroll
           for (int c = 0; c < 8; ++c) peer_base[c] = zb_mapa(part_u32, static_cast<uint32_t>(c < S ? c : 0));
+          // squares of this band's finished outputs, [BN][nrows | 1] fp32 in the idle operand ring (behind the
+          // partial tile), summed per token in a fixed order once the band is done
+          float* sq = reinterpret_cast<float*>(smem + 96 * 1024);
+          const int sq_ld = nrows | 1;
+          const bool has_scale = prm.epi.in_sumsq != nullptr;
+          auto emit_sumsq = [&]() {
+            epi_bar_sync();
+            for (int c = epi_tid; c < BN; c += kEpiThreads) {
+              if (q0 + c < prm.rows_q) {
+                float acc = 0.f;
+                for (int j = 0; j < nrows; ++j) acc += sq[c * sq_ld + j];
+                prm.epi.out_sumsq[(static_cast<size_t>(out_tile) * S + rank) * prm.epi.out_ld + q0 + c] = acc;
+              }
+            }
+          };
           // all loads of a batch (peer partials, residual, bias) are issued before its first store:
           // `out` may alias `residual`, so the compiler would otherwise serialise them
           auto reduce_batch = [&](auto kb_tag, auto kc_tag, int e0) {
             constexpr int KB = decltype(kb_tag)::value, KC = decltype(kc_tag)::value;
-            float tv[KB][KC], rsd[KB], bs[KB];
+            float tv[KB][KC], rsd[KB], bs[KB], sc[KB];
             int off[KB];
 #pragma unroll
             for (int i = 0; i < KB; ++i) {
@@ -392,32 +453,52 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
               const int pp = min(pt * kBlockP + row, prm.rows_p - 1), qq = min(q0 + col, prm.rows_q - 1);
               rsd[i] = prm.residual ? __bfloat162float(prm.residual[static_cast<size_t>(qq) * prm.ldo + pp]) : 0.f;
               bs[i] = prm.bias ? __bfloat162float(prm.bias[pp]) : 0.f;
+              sc[i] = has_scale ? scale_tab[col] : 1.f;
             }
 #pragma unroll
             for (int i = 0; i < KB; ++i) {
               const int e = e0 + i * kEpiThreads;
-              if (e >= total) continue;
               float v = 0.f;
 #pragma unroll
               for (int c = 0; c < KC; ++c) v += tv[i][c];            // ascending rank: deterministic
+              v = v * sc[i] + bs[i] + rsd[i];
               const int col = off[i] / kBlockP, row = off[i] - col * kBlockP;
               const int pp = pt * kBlockP + row, qq = q0 + col;
+              if (prm.epi.swiglu) {
+                // even lanes hold gate_i, their neighbours up_i (element and row parity agree: bands and their
+                // heights are even); every lane of the warp takes part in the exchange
+                const float up = __shfl_xor_sync(0xffffffffu, v, 1);
+                if (e < total && (e & 1) == 0 && pp < prm.rows_p && qq < prm.rows_q)
+                  reinterpret_cast<__nv_bfloat16*>(prm.out)[static_cast<size_t>(qq) * prm.ldo + (pp >> 1)] =
+                      __float2bfloat16(silu_f(v) * up);
+                continue;
+              }
+              if (e >= total) continue;
+              float stored = 0.f;
               if (pp < prm.rows_p && qq < prm.rows_q) {
                 const size_t o = static_cast<size_t>(qq) * prm.ldo + pp;
-                v += bs[i] + rsd[i];
-                if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
-                else reinterpret_cast<__nv_bfloat16*>(prm.out)[o] = __float2bfloat16(v);
+                if (prm.out_f32) {
+                  reinterpret_cast<float*>(prm.out)[o] = v;
+                  stored = v;
+                } else {
+                  const __nv_bfloat16 b = __float2bfloat16(v);
+                  reinterpret_cast<__nv_bfloat16*>(prm.out)[o] = b;
+                  stored = __bfloat162float(b);
+                }
               }
+              if (prm.epi.out_sumsq != nullptr) sq[col * sq_ld + (row - rb0)] = stored * stored;
             }
           };
           if constexpr (!FUSED) {
+            // every thread runs every batch (the SwiGLU exchange is warp-wide); elements past the band are masked
             if (S <= 4) {
-              for (int e0 = epi_tid; e0 < total; e0 += 8 * kEpiThreads)
-                reduce_batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{}, e0);
+              for (int base = 0; base < total; base += 8 * kEpiThreads)
+                reduce_batch(std::integral_constant<int, 8>{}, std::integral_constant<int, 4>{}, base + epi_tid);
             } else {
-              for (int e0 = epi_tid; e0 < total; e0 += 4 * kEpiThreads)
-                reduce_batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{}, e0);
+              for (int base = 0; base < total; base += 4 * kEpiThreads)
+                reduce_batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{}, base + epi_tid);
             }
+            if (prm.epi.out_sumsq != nullptr) emit_sumsq();
             // nobody may leave (and release its shared memory) while a peer still reads it
             zb_cluster_arrive();
             zb_cluster_wait();
@@ -554,12 +635,18 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                     const int o_t = elem_off(i0 + i);
                     const int col = o_t / kBlockP, row = o_t - col * kBlockP;
                     const int pp = pt * kBlockP + row, qq = q0 + col;
-                    if (pp < prm.rows_p && qq < prm.rows_q)
-                      ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = __float2bfloat16(sum[i] + add[i]);
+                    float stored = 0.f;
+                    if (pp < prm.rows_p && qq < prm.rows_q) {
+                      const __nv_bfloat16 b = __float2bfloat16(sum[i] + add[i]);
+                      ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = b;
+                      stored = __bfloat162float(b);
+                    }
+                    if (prm.epi.out_sumsq != nullptr) sq[col * sq_ld + (row - rb0)] = stored * stored;
                   }
                 }
               }
             }
+            if (prm.epi.out_sumsq != nullptr) emit_sumsq();
             if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
             if (tl && epi_tid == 0) tl[11] = zb_globaltimer();
             zb_cluster_wait();
@@ -638,10 +725,12 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       // bias / residual (read from this rank's memory) then store into `outp`
       auto finish_chunk = [&](int c0, float (&v)[16]) {
         if constexpr (SWAP) {
-          const float b = prm.bias ? __bfloat162float(prm.bias[p]) : 0.f;
+          const float b = (prm.bias && p < prm.rows_p) ? __bfloat162float(prm.bias[p]) : 0.f;
+          const bool has_scale = prm.epi.in_sumsq != nullptr;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int q = q0 + c0 + j;
+            if (has_scale) v[j] *= scale_tab[c0 + j];
             v[j] += b;
             if (prm.residual && q < prm.rows_q)
               v[j] += __bfloat162float(prm.residual[static_cast<size_t>(q) * prm.ldo + p]);
@@ -649,6 +738,8 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         } else {
           const int q = q0 + c0;
           const size_t o = static_cast<size_t>(p) * prm.ldo + q;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] *= row_scale;
           if (q + 16 <= prm.rows_q) {
             if (prm.bias) {
 #pragma unroll
@@ -717,6 +808,49 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
       };
 
+      // SwiGLU epilogue: rows of the weight interleave gate and up, the output has half as many columns.
+      // Swap-AB: this thread holds one weight row, its neighbour lane the partner (all lanes take part).
+      auto swiglu_store_chunk = [&](int c0, const float (&v)[16]) {
+        __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(prm.out);
+        if constexpr (SWAP) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+            const int q = q0 + c0 + j;
+            if ((row_in_tile & 1) == 0 && p < prm.rows_p && q < prm.rows_q)
+              outp[static_cast<size_t>(q) * prm.ldo + (p >> 1)] = __float2bfloat16(silu_f(v[j]) * up);
+          }
+        } else {
+          const int q = q0 + c0;
+          if (p < prm.rows_p) {
+            const size_t o = static_cast<size_t>(p) * prm.ldo + (q >> 1);
+            if (q + 16 <= prm.rows_q) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                w[j] = zb_pack_bf16x2(silu_f(v[4 * j]) * v[4 * j + 1], silu_f(v[4 * j + 2]) * v[4 * j + 3]);
+              *reinterpret_cast<uint4*>(outp + o) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (q + 2 * j + 1 < prm.rows_q) outp[o + j] = __float2bfloat16(silu_f(v[2 * j]) * v[2 * j + 1]);
+            }
+          }
+        }
+      };
+      // one chunk through the generic epilogue
+      auto epilogue_chunk = [&](int c0) {
+        float v[16];
+        load_chunk(c0, v);
+        if (prm.epi.swiglu) {
+          finish_chunk(c0, v);
+          swiglu_store_chunk(c0, v);
+        } else if (p < prm.rows_p) {
+          finish_chunk(c0, v);
+          store_chunk(c0, v, prm.out);
+        }
+      };
+
       if constexpr (!FUSED && SWAP && BN <= 64) {
         if (partial && do_store) {
           // Fix-up of a split tile, few tokens: the pieces are summed straight from the workspace by
@@ -776,7 +910,18 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           for (int i = 0; i < kCols; ++i) {
             const int q = q0 + cg + 4 * i;
             if (q >= prm.rows_q) continue;
-            float v4[4] = {accv[i].x + bz[0], accv[i].y + bz[1], accv[i].z + bz[2], accv[i].w + bz[3]};
+            const float sc = prm.epi.in_sumsq != nullptr ? scale_tab[cg + 4 * i] : 1.f;
+            float v4[4] = {accv[i].x * sc + bz[0], accv[i].y * sc + bz[1], accv[i].z * sc + bz[2], accv[i].w * sc + bz[3]};
+            if (prm.epi.swiglu) {
+              // rows pb .. pb + 3 are (gate, up, gate, up): two outputs at columns pb / 2, pb / 2 + 1
+              __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(prm.out) + static_cast<size_t>(q) * prm.ldo + (pb >> 1);
+              if (pb + 3 < prm.rows_p) {
+                *reinterpret_cast<uint32_t*>(op) = zb_pack_bf16x2(silu_f(v4[0]) * v4[1], silu_f(v4[2]) * v4[3]);
+              } else if (pb + 1 < prm.rows_p) {
+                op[0] = __float2bfloat16(silu_f(v4[0]) * v4[1]);
+              }
+              continue;
+            }
             const size_t o = static_cast<size_t>(q) * prm.ldo + pb;
             if (vec) {
               if (prm.residual) {
@@ -807,26 +952,12 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           }
         } else if (do_store) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            float v[16];
-            load_chunk(c0, v);
-            if (p < prm.rows_p) {
-              finish_chunk(c0, v);
-              store_chunk(c0, v, prm.out);
-            }
-          }
+          for (int c0 = 0; c0 < BN; c0 += 16) epilogue_chunk(c0);
         }
       } else if constexpr (!FUSED) {
         if (do_store) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 16) {
-            float v[16];
-            load_chunk(c0, v);
-            if (p < prm.rows_p) {
-              finish_chunk(c0, v);
-              store_chunk(c0, v, prm.out);
-            }
-          }
+          for (int c0 = 0; c0 < BN; c0 += 16) epilogue_chunk(c0);
         }
       } else if (SWAP && BN <= 64 && prm.ar.one_shot != 0) {
         if (do_store) {
@@ -1021,6 +1152,35 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   if (tl && threadIdx.x == 64) tl[7] = zb_globaltimer();
 }
 
+// Sum of squares of every row of a bf16 matrix: out[row] = sum_c x[row][c]^2 (fp32, fixed summation order).
+// The one-part form of the partial sums the GEMM epilogue emits, for producers that do not emit them.
+__global__ void __launch_bounds__(256) zb_row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int d,
+                                                           float* __restrict__ out) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(blockIdx.x) * ld);
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < (d >> 3); v += 256) {
+    const uint4 a = xr[v];
+    const uint32_t au[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = zb_unpack_bf16x2(au[j]);
+      ss += f.x * f.x + f.y * f.y;
+    }
+  }
+  __shared__ float red[8];
+  ss = zb_warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    out[blockIdx.x] = tot;
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -1110,12 +1270,15 @@ namespace {
 template <int BN, bool SWAP, bool FUSED = false>
 int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid,
            cudaStream_t stream) {
-  constexpr int smem = stages_for(BN, SWAP) * stage_bytes(BN) + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
+  constexpr int smem = smem_bytes_for(BN, SWAP);
+  // the shared-memory attribute of a kernel is per device: one flag per device for every instantiation
+  static bool configured[16] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return -21;
+  if (!configured[dev]) {
     cudaError_t e = zb_config_smem(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
+    configured[dev] = true;
   }
   const cudaError_t le = zb_launch_cluster(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, dim3(grid), dim3(kNumThreads), smem, stream,
                                            prm.cluster, tp, tq, prm);
@@ -1129,7 +1292,7 @@ int max_cluster_ctas(int s) {
   static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
   if (s < 2 || s > 8) return 0;
   if (cache[s] != 0) return cache[s] < 0 ? 0 : cache[s];
-  constexpr int smem = stages_for(BN, true) * stage_bytes(BN) + 1024 + 256;
+  constexpr int smem = smem_bytes_for(BN, true);
   if (zb_config_smem(zb_gemm_bf16_kernel<BN, true, false>, smem) != cudaSuccess) {
     (void)cudaGetLastError();
     cache[s] = -1;
@@ -1286,26 +1449,52 @@ size_t zb_gemm_workspace_bytes(int m, int n, int k, int num_sms) {
   return static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float);
 }
 
-// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `out_f32` is a bit set: bit 0 selects an
-// fp32 output, bit 1 states that `w` is a parameter (not written by the kernel that precedes
-// this one on the stream), which lets the kernel request weight tiles while that kernel is
-// still finishing.  `scratch` receives the partial
-// tiles of CTAs whose k-range does not cover a whole tile (2 per CTA); `counters`
-// holds one zeroed u32 per output tile (kept zero by the kernel).
-int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residual, const void* bias,
-                    int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
-                    float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
-                    ZbStatus* status, int num_sms, cudaStream_t stream) {
+}  // extern "C"
+
+namespace {
+
+int launch_row_sumsq(const void* x, int rows, int d, long long ld, float* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((d % 8) != 0 || (ld % 8) != 0) return -10;
+  const cudaError_t e = zb_launch(zb_row_sumsq_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, stream,
+                                  reinterpret_cast<const __nv_bfloat16*>(x), ld, d, out);
+  zb_count_launch(1);
+  return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+// Checks the epilogue options against the problem; returns 0 when they can be honoured.
+int check_epi(const ZbGemmEpi* epi, int m, int n, int ldo, int out_f32, const void* residual, const void* bias) {
+  if (epi == nullptr) return 0;
+  if (epi->in_sumsq != nullptr && (epi->in_parts < 1 || epi->in_ld < m)) return -15;
+  if (epi->swiglu) {
+    // gate / up pairs: an even number of weight rows, bf16 output of n / 2 columns, no bias or residual
+    if ((n % 2) != 0 || out_f32 || residual != nullptr || bias != nullptr || (ldo % 8) != 0 || epi->out_sumsq != nullptr) return -16;
+  }
+  if (epi->out_sumsq != nullptr && (out_f32 || epi->out_ld < m)) return -17;
+  if (epi->pf_bytes != 0ull && (epi->pf_ptr == nullptr || (reinterpret_cast<uintptr_t>(epi->pf_ptr) & 15) != 0)) return -18;
+  return 0;
+}
+
+// The GEMM proper.  `epi` may be null.  `out_parts` (may be null) receives the number of sum-of-squares
+// parts written to epi->out_sumsq: tiles x cluster size when the cluster epilogue emits them, else 1 (a
+// follow-up kernel over the finished output).
+int gemm_impl(const void* a, const void* w, void* out, const void* residual, const void* bias,
+              int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
+              float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
+              ZbStatus* status, int num_sms, const ZbGemmEpi* epi, int* out_parts, cudaStream_t stream) {
+  if (out_parts) *out_parts = 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0) return -10;
   const int static_w = (out_f32 >> 1) & 1;
   out_f32 &= 1;
   if (!out_f32 && (ldo % 8) != 0) return -11;
+  int rc = check_epi(epi, m, n, ldo, out_f32, residual, bias);
+  if (rc != 0) return rc;
   int sw, bn, grid, upc, rr;
   const int tiles = zb_gemm_plan(m, n, k, num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
   int cluster = 1;
   if (sw && rr == 0 && split_hint <= 0) cluster = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, num_sms, &grid, &upc);
-  if (static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > scratch_bytes) return -13;
+  if (cluster == 1 && static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > scratch_bytes) return -13;
   if (tiles > counters_len) return -14;
   GemmParams prm;
   prm.cluster = cluster;
@@ -1326,15 +1515,31 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
   prm.workspace = scratch;
   prm.counters = counters;
   prm.status = status;
+  prm.epi = ZbGemmEpi{};
+  bool sumsq_after = false;
+  if (epi != nullptr) {
+    prm.epi = *epi;
+    if (epi->out_sumsq != nullptr) {
+      if (cluster > 1) {
+        if (out_parts) *out_parts = tiles * cluster;
+      } else {
+        prm.epi.out_sumsq = nullptr;      // no emitting epilogue on this plan: one part from a follow-up kernel
+        sumsq_after = true;
+        if (out_parts) *out_parts = 1;
+      }
+    }
+  }
   CUtensorMap tp, tq;
-  int rc = zb_make_tmap_bf16_2d(&tp, sw ? w : a, prm.rows_p, k, sw ? ldw : lda, kBlockP);
+  rc = zb_make_tmap_bf16_2d(&tp, sw ? w : a, prm.rows_p, k, sw ? ldw : lda, kBlockP);
   if (rc != 0) return rc;
   rc = zb_make_tmap_bf16_2d(&tq, sw ? a : w, prm.rows_q, k, sw ? lda : ldw, bn);
   if (rc != 0) return rc;
+  rc = -12;
 #define ZB_GEMM_CASE(BN_)                                                           \
   case BN_:                                                                         \
-    return sw ? launch<BN_, true>(tp, tq, prm, grid, stream)                        \
-              : launch<BN_, false>(tp, tq, prm, grid, stream);
+    rc = sw ? launch<BN_, true>(tp, tq, prm, grid, stream)                          \
+            : launch<BN_, false>(tp, tq, prm, grid, stream);                        \
+    break;
   switch (bn) {
     ZB_GEMM_CASE(16)
     ZB_GEMM_CASE(32)
@@ -1343,7 +1548,67 @@ int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residua
     ZB_GEMM_CASE(256)
   }
 #undef ZB_GEMM_CASE
-  return -12;
+  if (rc == 0 && sumsq_after) rc = launch_row_sumsq(out, m, n, ldo, epi->out_sumsq, stream);
+  return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+// out[M,N] = a[M,K] * w[N,K]^T (+bias) (+residual).  `out_f32` is a bit set: bit 0 selects an
+// fp32 output, bit 1 states that `w` is a parameter (not written by the kernel that precedes
+// this one on the stream), which lets the kernel request weight tiles while that kernel is
+// still finishing.  `scratch` receives the partial
+// tiles of CTAs whose k-range does not cover a whole tile (2 per CTA); `counters`
+// holds one zeroed u32 per output tile (kept zero by the kernel).
+int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residual, const void* bias,
+                    int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
+                    float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
+                    ZbStatus* status, int num_sms, cudaStream_t stream) {
+  return gemm_impl(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, split_hint, scratch, scratch_bytes,
+                   counters, counters_len, status, num_sms, nullptr, nullptr, stream);
+}
+
+// Scratch bytes the launch of [m, n, k] needs (the plan `zb_gemm_bf16_ex` will run, cluster plans included:
+// those reduce through shared memory and need none).
+size_t zb_gemm_scratch_needed(int m, int n, int k, int num_sms) {
+  int sw, bn, grid, upc, rr;
+  const int tiles = zb_gemm_plan(m, n, k, num_sms, 0, &sw, &bn, &grid, &upc, &rr);
+  if (sw && rr == 0 && plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, num_sms, &grid, &upc) > 1) return 0;
+  return static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float);
+}
+
+// Sum of squares of the rows of a bf16 matrix [rows, d] (leading dimension ld) -> out[rows] fp32.
+int zb_row_sumsq(const void* x, int rows, int d, long long ld, float* out, void* stream) {
+  return launch_row_sumsq(x, rows, d, ld, out, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// zb_gemm_bf16 with the epilogue options of ZbGemmEpi (host_api.h) passed as scalars:
+//   in_sumsq [in_parts][in_ld], inv_d, eps  -> accumulators of token t scaled by rsqrt(sum * inv_d + eps)
+//   swiglu                                  -> interleaved gate / up rows, n / 2 output columns
+//   out_sumsq [..][out_ld], *out_parts      -> partial sums of squares of the output rows and how many parts
+//   pf_ptr, pf_bytes                        -> bytes to pull into L2 behind this kernel's own loads
+int zb_gemm_bf16_epi(const void* a, const void* w, void* out, const void* residual, const void* bias, int m, int n, int k,
+                     int lda, int ldw, int ldo, int out_f32, int split_hint, const float* in_sumsq, int in_parts, int in_ld,
+                     float in_inv_d, float in_eps, int swiglu, float* out_sumsq, int out_ld, int* out_parts,
+                     const void* pf_ptr, unsigned long long pf_bytes, void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (st == nullptr) return -20;
+  ZbGemmEpi epi = {};
+  epi.in_sumsq = in_sumsq;
+  epi.in_parts = in_parts;
+  epi.in_ld = in_ld;
+  epi.in_inv_d = in_inv_d;
+  epi.in_eps = in_eps;
+  epi.swiglu = swiglu ? 1 : 0;
+  epi.out_sumsq = out_sumsq;
+  epi.out_ld = out_ld;
+  epi.pf_ptr = pf_bytes ? pf_ptr : nullptr;
+  epi.pf_bytes = pf_ptr ? pf_bytes : 0ull;
+  return gemm_impl(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, split_hint, st->gemm_scratch,
+                   st->gemm_scratch_bytes, st->gemm_counters, st->gemm_counters_len, st->status, st->num_sms, &epi,
+                   out_parts, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // The decomposition zb_gemm_bf16 would use for [m, n, k]: out[0..5] = swap-AB, tile columns, grid, k-blocks per
@@ -1380,11 +1645,17 @@ int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, 
 //   out_r = sum over ranks r' of a_r'[M,K_r'] * w_r'[N,K_r']^T (+ bias) (+ residual), on every rank.
 // `out_off` is the byte offset of the output inside every rank's symmetric heap.  All ranks
 // must call this with the same shapes, in the same order.  See fused_ar.h for the protocol.
-int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_t out_off,
-                     const void* residual, const void* bias, int m, int n, int k, int lda, int ldw,
-                     int ldo, int split_hint, void* stream) {
+// `out_sumsq` (may be null) receives partial sums of squares of the finished output rows, [*out_parts][out_ld];
+// `pf_ptr` / `pf_bytes` name the next GEMM's weights, pulled into L2 while the exchange with the peers runs.
+int zb_gemm_ar_fused_epi(const ZbArContext* ctx, const void* a, const void* w, size_t out_off,
+                         const void* residual, const void* bias, int m, int n, int k, int lda, int ldw,
+                         int ldo, int split_hint, float* out_sumsq, int out_ld, int* out_parts, const void* pf_ptr,
+                         unsigned long long pf_bytes, void* stream) {
+  if (out_parts) *out_parts = 0;
   if (ctx == nullptr || ctx->world < 1 || ctx->world > kZbMaxRanks) return -50;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
+  if (out_sumsq != nullptr && out_ld < m) return -17;
+  if (pf_bytes != 0ull && (pf_ptr == nullptr || (reinterpret_cast<uintptr_t>(pf_ptr) & 15) != 0)) return -18;
   if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (ldo % 8) != 0 || (out_off % 16) != 0) return -10;
   ZbDeviceState* st = zb_device_state();
   if (st == nullptr) return -20;
@@ -1398,8 +1669,8 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   if (one_shot_fits && rr == 0 && split_hint <= 0) {
     int cg = grid, cu = upc;
     const int cs = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, st->num_sms, &cg, &cu, /*allow_tiny=*/false);
-    // the tensor-parallel epilogue keeps at most 32 elements per thread (two halves of 16)
-    if (cs > 1 && bn * ((kBlockP + cs - 1) / cs) <= 32 * kEpiThreads &&
+    // the tensor-parallel epilogue keeps at most 32 elements per thread (two halves of 16); bands have even heights
+    if (cs > 1 && bn * (2 * ((kBlockP / 2 + cs - 1) / cs)) <= 32 * kEpiThreads &&
         2 * static_cast<size_t>(ctx->world) * tiles * cs * 16 * kEpiThreads * sizeof(uint2) <= ctx->recv_bytes) {
       cluster = cs;
       grid = cg;
@@ -1425,6 +1696,20 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   prm.workspace = st->gemm_scratch;
   prm.counters = st->gemm_counters;
   prm.status = st->status;
+  prm.epi = ZbGemmEpi{};
+  prm.epi.pf_ptr = pf_bytes ? pf_ptr : nullptr;
+  prm.epi.pf_bytes = pf_ptr ? pf_bytes : 0ull;
+  bool sumsq_after = false;
+  if (out_sumsq != nullptr) {
+    if (cluster > 1) {
+      prm.epi.out_sumsq = out_sumsq;
+      prm.epi.out_ld = out_ld;
+      if (out_parts) *out_parts = tiles * cluster;
+    } else {
+      sumsq_after = true;
+      if (out_parts) *out_parts = 1;
+    }
+  }
   ZbFusedAr& ar = prm.ar;
   ar.rank = ctx->rank;
   ar.world = ctx->world;
@@ -1453,10 +1738,12 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
   rc = zb_make_tmap_bf16_2d(&tq, sw ? a : w, prm.rows_q, k, sw ? lda : ldw, bn);
   if (rc != 0) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  rc = -12;
 #define ZB_GEMM_CASE(BN_)                                                     \
   case BN_:                                                                   \
-    return sw ? launch<BN_, true, true>(tp, tq, prm, grid, s)                 \
-              : launch<BN_, false, true>(tp, tq, prm, grid, s);
+    rc = sw ? launch<BN_, true, true>(tp, tq, prm, grid, s)                   \
+            : launch<BN_, false, true>(tp, tq, prm, grid, s);                 \
+    break;
   switch (bn) {
     ZB_GEMM_CASE(16)
     ZB_GEMM_CASE(32)
@@ -1465,7 +1752,16 @@ int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_
     ZB_GEMM_CASE(256)
   }
 #undef ZB_GEMM_CASE
-  return -12;
+  if (rc == 0 && sumsq_after)
+    rc = launch_row_sumsq(reinterpret_cast<const char*>(ctx->heap[ctx->rank]) + out_off, m, n, ldo, out_sumsq, s);
+  return rc;
+}
+
+int zb_gemm_ar_fused(const ZbArContext* ctx, const void* a, const void* w, size_t out_off,
+                     const void* residual, const void* bias, int m, int n, int k, int lda, int ldw,
+                     int ldo, int split_hint, void* stream) {
+  return zb_gemm_ar_fused_epi(ctx, a, w, out_off, residual, bias, m, n, k, lda, ldw, ldo, split_hint, nullptr, 0, nullptr,
+                              nullptr, 0ull, stream);
 }
 
 }  // extern "C"

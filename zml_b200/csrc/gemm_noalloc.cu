@@ -10,6 +10,7 @@
 extern "C" {
 int zb_gemm_plan(int m, int n, int k, int num_sms, int split_hint, int* swap, int* bn, int* grid,
                  int* units_per_cta, int* rr_tiles);
+size_t zb_gemm_scratch_needed(int m, int n, int k, int num_sms);
 int zb_gemm_bf16_ex(const void* a, const void* w, void* out, const void* residual, const void* bias,
                     int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
                     float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
@@ -38,7 +39,10 @@ extern "C" int zb_gemm_bf16_noalloc(const void* a, const void* w, void* out, con
                                     int out_f32, void* status_out, void* stream) {
   if (a == nullptr || w == nullptr || out == nullptr || m <= 0 || n <= 0 || k <= 0)
     return ZB_NOALLOC_ERR_BAD_ARG;
-  if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (!out_f32 && (ldo % 8) != 0))
+  // `out_f32` is a yes / no here; the kernel's entry point reads further bits of its flag word (weight prefetch
+  // ahead of the stream dependency), which this entry point never sets
+  const int f32 = out_f32 ? 1 : 0;
+  if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (!f32 && (ldo % 8) != 0))
     return ZB_NOALLOC_ERR_BAD_ARG;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return ZB_NOALLOC_ERR_SETUP;
@@ -61,7 +65,8 @@ extern "C" int zb_gemm_bf16_noalloc(const void* a, const void* w, void* out, con
 
   int sw, bn, grid, upc, rr;
   const int tiles = zb_gemm_plan(m, n, k, g_sms[dev], 0, &sw, &bn, &grid, &upc, &rr);
-  const size_t need = rr > 0 ? 0 : static_cast<size_t>(grid) * 2 * bn * 128 * sizeof(float);
+  // scratch of the plan that will really launch (whole-tile and cluster plans write no partial tile to memory)
+  const size_t need = rr > 0 ? 0 : zb_gemm_scratch_needed(m, n, k, g_sms[dev]);
   if (need > ZB_NOALLOC_SCRATCH_BYTES || (rr == 0 && tiles > kCounters)) {
     fprintf(stderr,
             "zb_gemm_bf16_noalloc: M=%d N=%d K=%d needs %zu bytes of scratch for partial tiles, the "
@@ -75,6 +80,8 @@ extern "C" int zb_gemm_bf16_noalloc(const void* a, const void* w, void* out, con
   if (cudaMemsetAsync(status, 0, sizeof(ZbStatus), s) != cudaSuccess) return ZB_NOALLOC_ERR_SETUP;
   // whole-tile (round-robin) problems write no partial tile, so their size is not bounded by the array
   const size_t bound = rr > 0 ? (static_cast<size_t>(1) << 40) : static_cast<size_t>(ZB_NOALLOC_SCRATCH_BYTES);
-  return zb_gemm_bf16_ex(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, 0, partials, bound,
-                         counters, rr > 0 ? (1 << 30) : kCounters, status, g_sms[dev], s);
+  const int rc = zb_gemm_bf16_ex(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, f32, 0, partials, bound,
+                                 counters, rr > 0 ? (1 << 30) : kCounters, status, g_sms[dev], s);
+  // the kernel's own does-not-fit codes (scratch, counters) are this entry point's "too large"
+  return (rc == -13 || rc == -14) ? ZB_NOALLOC_ERR_TOO_LARGE : rc;
 }

@@ -27,7 +27,7 @@ extern "C" {
 #define ZB_NOALLOC_ERR_BAD_ARG (-103)     // null pointer, non-positive size, or unsupported alignment
 
 // out[M,N] = a[M,K] * w[N,K]^T (+ bias[N]) (+ residual[M,N]); bf16 inputs, fp32 accumulation,
-// bf16 output (out_f32 == 0) or fp32 output (out_f32 != 0).  Same kernel and same numerics as
+// bf16 output (out_f32 == 0) or fp32 output (any non-zero out_f32).  Same kernel and same numerics as
 // zb_gemm_bf16.  All pointers are device pointers owned by the caller; lda / ldw / ldo are in
 // elements and must be multiples of 8; K must be a multiple of 8.  `residual`, `bias` and
 // `status_out` may be null.  `status_out`, when given, points to 16 bytes of device memory
@@ -39,8 +39,10 @@ extern "C" {
 //     Shapes that would need more than ZB_NOALLOC_SCRATCH_BYTES return
 //     ZB_NOALLOC_ERR_TOO_LARGE and print one line to stderr; nothing is launched.
 //   * The first call on a device resolves the address of the built-in array on that device
-//     (cudaGetSymbolAddress with that device current) and sets a function attribute.  Make
-//     that first call before starting any stream capture on that device.
+//     (cudaGetSymbolAddress with that device current).  The first call of each tile shape
+//     (a function of M and N) on each device also sets that kernel's shared-memory attribute.
+//     Make a first call of every shape you will use before starting any stream capture on
+//     that device.
 //   * Every call on a device uses the same array, and the array keeps what the previous call
 //     left in it.  The call zeroes the part that must start at zero (tile counters) on
 //     `stream` before launching.  Two calls whose kernels can overlap on the GPU (different

@@ -37,6 +37,31 @@ struct ZbArContext {
   int max_tiles;
   uint32_t* epoch;        // local device counter, starts at 1
   uint32_t* exit_ticket;  // local device counter
+  void* mc_heap;          // NVLink multicast address of the heaps (one address, every rank's copy), or null
+};
+
+// Optional epilogue work of the bf16 GEMM (gemm_bf16.cu).  All pointers are local device memory.
+//   in_sumsq : partial sums of squares of the activation rows, [in_parts][in_ld] fp32; the accumulator of
+//              token t is multiplied by rsqrt(sum_i in_sumsq[i][t] * in_inv_d + in_eps) before bias and
+//              residual.  With the RMSNorm weight folded into the columns of `w` this makes the GEMM
+//              compute rmsnorm(a) * w^T without a normalisation kernel (zml/nn.zig:486-493).
+//   swiglu   : the rows of `w` interleave gate and up (row 2 i = gate_i, row 2 i + 1 = up_i); the output has
+//              n / 2 columns, out[t][i] = silu(gate_i) * up_i (examples/llm/models/llama/model.zig:491-496).
+//   out_sumsq: the kernel writes partial sums of squares of its (bf16-rounded) output rows, [parts][out_ld];
+//              `parts` is reported by the entry point.
+//   pf_ptr   : contiguous bytes (the next GEMM's weights) that the kernel pulls into L2 once its own operand
+//              loads have been issued.
+struct ZbGemmEpi {
+  const float* in_sumsq;
+  float* out_sumsq;
+  const void* pf_ptr;
+  unsigned long long pf_bytes;
+  int in_parts;
+  int in_ld;
+  int out_ld;
+  float in_inv_d;
+  float in_eps;
+  int swiglu;
 };
 
 ZbDeviceState* zb_device_state();       // state of the current device, or nullptr before zb_init

@@ -163,9 +163,12 @@ class LlamaModel:
         self.hkv = self.kv_rng[1] - self.kv_rng[0]
         self.f_rng = common.shard_range(c.intermediate_size, r, p)
         self.f_local = self.f_rng[1] - self.f_rng[0]
-        # vocab-parallel lm_head; pad so that every rank holds the same number of rows
+        # vocab-parallel lm_head: every rank holds v_per rows; rows past the vocabulary (last ranks, when the
+        # vocabulary does not divide) are zero rows whose logits are masked to -inf
         self.v_per = (c.vocab_size + p - 1) // p
-        self.v_rng = (r * self.v_per, min(c.vocab_size, (r + 1) * self.v_per))
+        self.v_rng = (min(c.vocab_size, r * self.v_per), min(c.vocab_size, (r + 1) * self.v_per))
+        self.v_pad = self.v_per - (self.v_rng[1] - self.v_rng[0])
+        self.fused_layout = False     # see prepare_fused
         opts = c.rope_opts()
         self.rope_layout = opts.layout.value
         self.rot_dim = opts.scaling.partial_rotary_dim(c.hd)
@@ -190,6 +193,7 @@ class LlamaModel:
             self.lm_head = self.embed[self.v_rng[0]:self.v_rng[1]] if self.comm.world > 1 else self.embed
         else:
             self.lm_head = rw((c.vocab_size, d), 2, rows=self.v_rng)
+        self._pad_lm_head()
         q0, q1 = self.q_rng[0] * hd, self.q_rng[1] * hd
         k0, k1 = self.kv_rng[0] * hd, self.kv_rng[1] * hd
         for l in range(c.num_hidden_layers):
@@ -216,6 +220,11 @@ class LlamaModel:
             self.layers.append(lw)
         return self
 
+    def _pad_lm_head(self) -> None:
+        if self.v_pad > 0 and self.comm.world > 1 and self.lm_head.shape[0] < self.v_per:
+            pad = torch.zeros((self.v_pad, self.lm_head.shape[1]), dtype=self.lm_head.dtype, device=self.lm_head.device)
+            self.lm_head = torch.cat([self.lm_head, pad], 0)
+
     def load(self, store, prefix: str = "") -> "LlamaModel":
         """Loads this rank's shards from a TensorStore view (HF names).  Only the byte ranges
         of the shard are read."""
@@ -230,6 +239,7 @@ class LlamaModel:
             self.lm_head = get("lm_head.weight", rows=self.v_rng)
         else:
             self.lm_head = self.embed[self.v_rng[0]:self.v_rng[1]] if self.comm.world > 1 else self.embed
+        self._pad_lm_head()
         for l in range(c.num_hidden_layers):
             p = f"model.layers.{l}."
             lw = LayerWeights()
@@ -255,9 +265,12 @@ class LlamaModel:
     def state_dict_hf(self) -> dict:
         """This rank's weights under HF names (un-fused); with TP=1 this is a full checkpoint."""
         c, hd = self.config, self.config.hd
+        if self.fused_layout:
+            raise RuntimeError("the weights are in the fused-kernel layout (norms folded, gate / up interleaved); "
+                               "export before the first forward pass on a GPU")
         out = {"model.embed_tokens.weight": self.embed, "model.norm.weight": self.final_norm}
         if not c.tie_word_embeddings:
-            out["lm_head.weight"] = self.lm_head
+            out["lm_head.weight"] = self.lm_head[:self.v_rng[1] - self.v_rng[0]]
         nq, nk = self.hq * hd, self.hkv * hd
         for l, lw in enumerate(self.layers):
             p = f"model.layers.{l}."
@@ -294,33 +307,36 @@ class LlamaModel:
     def kv_cache_shape(self, num_pages: int, page_size: int):
         return (self.config.num_hidden_layers, 2, num_pages, page_size, self.hkv, self.config.hd)
 
-    def row_parallel_ks(self):
-        """Input widths (per rank) of the row-parallel projections, for `SymmetricContext.autotune`."""
-        ks = [self.hq * self.config.hd]
-        if getattr(self.config, "num_experts", 0) == 0:
-            ks.append(self.f_local)
-        return ks
-
-    def row_parallel(self, a, w, residual):
-        """Row-parallel linear + all-reduce + residual add: the o_proj / down_proj pattern."""
+    def row_parallel(self, a, w, residual, emit_stats: bool = False, next_w=None):
+        """Row-parallel linear + all-reduce + residual add: the o_proj / down_proj pattern.  With `emit_stats`
+        returns (x, RowStats of x): the partial sums of squares the next GEMM normalises its input with.
+        `next_w`: the weights of the GEMM that follows, which the fused kernel pulls into L2 while it
+        exchanges partial sums with the peers."""
         comm = self.comm
         if comm.world == 1:
-            return ops.gemm(a, w, residual=residual, out=residual if residual.is_cuda else None, static_w=True)
+            return ops.gemm(a, w, residual=residual, out=residual if residual.is_cuda else None, static_w=True,
+                            emit_stats=emit_stats)
         if comm.fused is not None and a.is_cuda and a.shape[0] <= comm.fused.fused_max_tokens:
-            return comm.fused.gemm_allreduce(a, w, residual)
+            return comm.fused.gemm_allreduce(a, w, residual, emit_stats=emit_stats,
+                                             prefetch=next_w if self.prefetch_next else None)
         if comm.fused is not None and a.is_cuda and comm.fused.can_all_reduce_ll(a.shape[0], w.shape[0]):
-            return comm.fused.all_reduce_ll(ops.gemm(a, w, static_w=True), residual)
-        part = ops.gemm(a, w, residual=residual if comm.rank == 0 else None, static_w=True)
-        return comm.all_reduce_(part)
+            x = comm.fused.all_reduce_ll(ops.gemm(a, w, static_w=True), residual)
+        elif comm.fused is not None and a.is_cuda and comm.fused.can_all_reduce_mm(a.shape[0], w.shape[0]):
+            # prefill-sized: partial sums go straight into the symmetric heap, NVSwitch adds them up
+            part = ops.gemm(a, w, static_w=True, out=comm.fused.partial_buffer(a.shape[0], w.shape[0]))
+            x = comm.fused.all_reduce_mm(part, residual)
+        else:
+            part = ops.gemm(a, w, residual=residual if comm.rank == 0 else None, static_w=True)
+            x = comm.all_reduce_(part)
+        return (x, ops.row_sumsq(x)) if emit_stats else x
 
     def mlp(self, lw: LayerWeights, x, n2):
         gu = ops.gemm(n2, lw.gate_up, static_w=True)
         act = ops.swiglu(gu)
         return self.row_parallel(act, lw.down, x)
 
-    def attention(self, lw: LayerWeights, n1, meta: AttnMeta, kc, vc):
+    def attention_from_qkv(self, lw: LayerWeights, qkv, meta: AttnMeta, kc, vc):
         c = self.config
-        qkv = ops.gemm(n1, lw.qkv, bias=lw.qkv_bias, static_w=True)
         q = ops.rope_kvwrite(qkv, meta.positions, meta.slot_mapping, self.inv_freq, kc, vc, self.hq,
                              self.hkv, c.hd, self.rope_layout, self.rot_dim, self.attn_factor,
                              lw.q_norm, lw.k_norm, c.rms_norm_eps, False)
@@ -332,7 +348,48 @@ class LlamaModel:
                                  num_splits=meta.num_splits, max_seq_len=meta.max_seq_len)
         return a.reshape(a.shape[0], self.hq * c.hd)
 
+    def attention(self, lw: LayerWeights, n1, meta: AttnMeta, kc, vc):
+        qkv = ops.gemm(n1, lw.qkv, bias=lw.qkv_bias, static_w=True)
+        return self.attention_from_qkv(lw, qkv, meta, kc, vc)
+
+    # ---- fused-kernel layout: a decoder layer is 6 launches (qkv GEMM, rope + KV write, attention, o GEMM
+    # (+ all-reduce), gate|up GEMM with SwiGLU, down GEMM (+ all-reduce)) instead of 9: the two RMSNorms
+    # become a per-row scale in the epilogue of the GEMM that consumes the normalised activation (the norm
+    # weight is folded into that GEMM's weight columns, the row statistics come out of the epilogue of the
+    # GEMM that produced the residual stream), and SwiGLU runs in the gate|up GEMM's epilogue on interleaved
+    # gate / up rows.  The reference leaves these fusions to XLA (examples/llm/models/llama/model.zig:414-443).
+    # ZB_PREFETCH_NEXT=0: the fused GEMM + all-reduce does not pull the next GEMM's weights into L2
+    prefetch_next = os.environ.get("ZB_PREFETCH_NEXT", "1") != "0"
+
+    def wants_fused_layout(self) -> bool:
+        from ..ops import baseline as _baseline
+        return (type(self).layer is LlamaModel.layer and type(self).mlp is LlamaModel.mlp and self.device.type == "cuda"
+                and not _baseline.enabled() and os.environ.get("ZB_FOLD_NORMS", "1") != "0")
+
+    def prepare_fused(self) -> None:
+        """In place, once: qkv[:, j] *= input_norm[j], gate_up[:, j] *= post_norm[j], gate / up rows interleaved."""
+        if self.fused_layout:
+            return
+        for lw in self.layers:
+            lw.qkv.mul_(lw.input_norm[None, :].to(lw.qkv.dtype))
+            gu = ops.interleave_gate_up(lw.gate_up)
+            gu.mul_(lw.post_norm[None, :].to(gu.dtype))
+            lw.gate_up.copy_(gu)
+            del gu
+        self.fused_layout = True
+
+    def _layer_fused(self, l: int, x, stats, meta: AttnMeta, kv_cache):
+        lw, c = self.layers[l], self.config
+        qkv = ops.gemm(x, lw.qkv, bias=lw.qkv_bias, static_w=True, row_stats=stats, eps=c.rms_norm_eps)
+        a = self.attention_from_qkv(lw, qkv, meta, kv_cache[l, 0], kv_cache[l, 1])
+        x, stats = self.row_parallel(a, lw.o, x, emit_stats=True, next_w=lw.gate_up)
+        act = ops.gemm(x, lw.gate_up, static_w=True, row_stats=stats, eps=c.rms_norm_eps, swiglu=True)
+        nxt = self.layers[l + 1].qkv if l + 1 < len(self.layers) else None
+        return self.row_parallel(act, lw.down, x, emit_stats=True, next_w=nxt)
+
     def layer(self, l: int, x, meta: AttnMeta, kv_cache):
+        if self.fused_layout:
+            return self._layer_fused(l, x, ops.row_sumsq(x), meta, kv_cache)[0]
         lw, c = self.layers[l], self.config
         kc, vc = kv_cache[l, 0], kv_cache[l, 1]
         n1 = ops.rmsnorm(x, lw.input_norm, c.rms_norm_eps)
@@ -341,78 +398,30 @@ class LlamaModel:
         n2 = ops.rmsnorm(x, lw.post_norm, c.rms_norm_eps)
         return self.mlp(lw, x, n2)
 
-    # With ZB_PREFILL_OVERLAP=1 a prefill chunk of at least this many tokens (and two sequences) is processed as
-    # two halves whose tensor-parallel all-reduces overlap the other half's GEMMs and attention.  Off by default:
-    # on 2 B200s (Llama-3.1-8B) it measured slower (job 2 488 vs 2 450 ms, TTFT p50 253 vs 215 ms) - the all-reduce
-    # is a small share there and the collective's CTAs take SMs from the GEMMs; not measured on 8 GPUs, where the
-    # all-reduce is about a fifth of a 70B prefill chunk.
-    prefill_overlap_min_tokens = 2048 if os.environ.get("ZB_PREFILL_OVERLAP", "0") == "1" else 1 << 62
-
     def hidden_states(self, ids, meta: AttnMeta, kv_cache):
         x = ops.embedding(ids, self.embed)
-        halves = self._split_prefill(x, meta)
-        if halves is not None:
-            return self._hidden_states_overlapped(x, halves, kv_cache)
+        if not self.fused_layout and self.wants_fused_layout():
+            self.prepare_fused()
+        if self.fused_layout:
+            stats = ops.row_sumsq(x)
+            for l in range(self.config.num_hidden_layers):
+                x, stats = self._layer_fused(l, x, stats, meta, kv_cache)
+            return x
         for l in range(self.config.num_hidden_layers):
             x = self.layer(l, x, meta, kv_cache)
         return x
-
-    def _split_prefill(self, x, meta: AttnMeta):
-        """Two (token range, AttnMeta) halves of a prefill chunk, cut at a sequence boundary near the middle; None
-        when the chunk is not worth splitting (one rank, one sequence, few tokens, a layer type with state)."""
-        qs = meta.q_start_host
-        from ..ops import baseline as _baseline
-        if _baseline.enabled():
-            return None
-        if (type(self).layer is not LlamaModel.layer or type(self).mlp is not LlamaModel.mlp or self.comm.world == 1
-                or not meta.is_prefill or qs is None or len(qs) < 3 or x.shape[0] < self.prefill_overlap_min_tokens):
-            return None
-        total = qs[-1]
-        cut = min(range(1, len(qs) - 1), key=lambda i: abs(qs[i] - total / 2))
-        out = []
-        for s0, s1 in ((0, cut), (cut, len(qs) - 1)):
-            t0, t1 = qs[s0], qs[s1]
-            blocks = sum((qs[i + 1] - qs[i] + 63) // 64 for i in range(s0, s1))
-            out.append((t0, t1, AttnMeta(True, meta.positions[t0:t1], meta.slot_mapping[t0:t1], meta.block_table[s0:s1],
-                                         meta.seq_lens[s0:s1], meta.q_start[s0:s1 + 1] - t0, total_q_blocks=blocks)))
-        return out
-
-    def _row_parallel_async(self, a, w, residual):
-        """Row-parallel GEMM whose all-reduce runs on the collective library's stream: (tensor, work); the tensor
-        holds the sum (+ residual) once `work.wait()` has been called on the consuming stream."""
-        import torch.distributed as dist
-        part = ops.gemm(a, w, residual=residual if self.comm.rank == 0 else None, static_w=True)
-        return part, dist.all_reduce(part, group=self.comm.group, async_op=True)
-
-    def _hidden_states_overlapped(self, x, halves, kv_cache):
-        c = self.config
-        xs = [x[t0:t1] for t0, t1, _ in halves]
-        metas = [m for _, _, m in halves]
-        works = [None, None]
-        for l in range(c.num_hidden_layers):
-            lw = self.layers[l]
-            kc, vc = kv_cache[l, 0], kv_cache[l, 1]
-            for h in (0, 1):
-                if works[h] is not None:
-                    works[h].wait()
-                n1 = ops.rmsnorm(xs[h], lw.input_norm, c.rms_norm_eps)
-                a = self.attention(lw, n1, metas[h], kc, vc)
-                xs[h], works[h] = self._row_parallel_async(a, lw.o, xs[h])
-            for h in (0, 1):
-                works[h].wait()
-                n2 = ops.rmsnorm(xs[h], lw.post_norm, c.rms_norm_eps)
-                act = ops.swiglu(ops.gemm(n2, lw.gate_up, static_w=True))
-                xs[h], works[h] = self._row_parallel_async(act, lw.down, xs[h])
-        for h in (0, 1):
-            works[h].wait()
-        return torch.cat(xs, 0)
 
     def logits(self, x, rows=None):
         """float32 logits of this rank's vocab shard for the selected rows."""
         if rows is not None:
             x = x.index_select(0, rows.long() if rows.dtype != torch.int64 else rows)
         n = ops.rmsnorm(x, self.final_norm, self.config.rms_norm_eps)
-        return ops.gemm(n, self.lm_head, out_dtype=torch.float32, static_w=True)
+        if self.v_pad > 0 and self.comm.world > 1 and self.lm_head.shape[0] < self.v_per:
+            self._pad_lm_head()         # model families that fill `lm_head` themselves
+        lg = ops.gemm(n, self.lm_head, out_dtype=torch.float32, static_w=True)
+        if self.v_pad > 0 and self.comm.world > 1:
+            lg[:, self.v_per - self.v_pad:] = float("-inf")
+        return lg
 
     def sample(self, logits, strategy: common.SamplingStrategy, seed: int = 0, step: int = 0):
         """Token ids int32 [B] from vocab-parallel logits."""
@@ -425,12 +434,11 @@ class LlamaModel:
             idx = ops.argmax(logits)
             val = logits.gather(1, idx.long()[:, None])[:, 0]
             vals = comm.all_gather(val[None])                   # [P, B]
-            idxs = comm.all_gather((idx + self.v_rng[0])[None])
+            idxs = comm.all_gather((idx + self.comm.rank * self.v_per)[None])
             best = vals.argmax(0)
             return idxs.gather(0, best[None])[0].to(torch.int32)
-        full = comm.all_gather(logits, dim=1)[:, :self.config.vocab_size] if self.v_per * comm.world == self.config.vocab_size \
-            else torch.cat([t[:, :min(self.v_per, self.config.vocab_size - i * self.v_per)]
-                            for i, t in enumerate(comm.all_gather(logits[None]).unbind(0))], 1)
+        # every rank holds v_per columns (padding columns are -inf), so column r * v_per + j is token r * v_per + j
+        full = comm.all_gather(logits, dim=1)
         return ops.topk_sample(full.contiguous(), strategy.topk, strategy.temperature, seed, step)
 
     def forward(self, ids, meta: AttnMeta, kv_cache, strategy: Optional[common.SamplingStrategy] = None,

@@ -29,10 +29,9 @@ def preset_names() -> list[str]:
 
 
 def build_model(name: str, comm: Optional[Comm] = None, device="cuda", seed: int = 0,
-                baseline: bool = False, fused: bool = True, dtype=torch.bfloat16, autotune: bool = True):
+                baseline: bool = False, fused: bool = True, dtype=torch.bfloat16):
     """Random-init model of a named architecture on `device` (this rank's shard).  With `fused` and more than
-    one rank the in-kernel collectives are set up; `autotune` then measures them against NCCL on this machine
-    and keeps the faster path for the row-parallel projections."""
+    one rank the symmetric heap of the in-kernel collectives is set up and the row-parallel projections use them."""
     comm = comm or Comm.single(torch.device(device))
     for presets, cfg_cls, model_cls in _families():
         if name in presets:
@@ -48,44 +47,7 @@ def build_model(name: str, comm: Optional[Comm] = None, device="cuda", seed: int
         is_moe = getattr(model.config, "num_experts", 0) > 0
         comm.fused = symm.SymmetricContext.create(comm, model.config.hidden_size, staging_elems=512 * model.config.hidden_size,
                                                   combine_tokens=256 if is_moe else 0)
-        if autotune:
-            _autotune_collectives(model, comm)
     return model
-
-
-def _autotune_collectives(model, comm, batch: int = 32, context: int = 1024, layers: int = 4) -> None:
-    """Lets `SymmetricContext.autotune` choose between the fused and the NCCL row-parallel path on the first
-    decoder layers of the model itself (a decode step of `batch` sequences with `context` cached tokens);
-    models whose layers need more than a KV cache are tuned on their projection shapes."""
-    from .. import ops
-    from .llama import AttnMeta, LlamaModel
-    from .qwen3_moe import Qwen3MoeModel
-    fused, dev = comm.fused, comm.device
-    if type(model) not in (LlamaModel, Qwen3MoeModel):
-        ks = sorted({int(k) for k in model.row_parallel_ks() if k})
-        if ks:
-            fused.autotune_projections(ks)
-        return
-    page = 64
-    pages_per = (context + 64) // page + 1
-    nl = min(layers, model.config.num_hidden_layers)
-    shape = list(model.kv_cache_shape(batch * pages_per + 1, page))
-    shape[0] = nl
-    kv = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
-    bt = (torch.arange(batch * pages_per, dtype=torch.int32, device=dev) + 1).view(batch, pages_per)
-    pos = torch.full((batch,), context, dtype=torch.int32, device=dev)
-    slot = (bt[:, context // page] * page + context % page).int()
-    meta = AttnMeta(False, pos, slot, bt, pos + 1, num_splits=ops.decode_plan_splits(batch, model.hkv, context + 64),
-                    max_seq_len=context + 64)
-    x0 = torch.randn(batch, model.config.hidden_size, device=dev).to(model.dtype)
-
-    def run():
-        x = x0
-        for l in range(nl):
-            x = model.layer(l, x, meta, kv)
-        return x
-
-    fused.autotune(run, units=nl)
 
 
 def model_class_for(config: dict):

@@ -15,7 +15,7 @@ from . import _lib, reference
 from ._lib import CollectiveTimeout, KernelError, launch_count, raise_on_status  # noqa: F401
 
 __all__ = [
-    "gemm", "linear", "rmsnorm", "rope_kvwrite", "swiglu", "embedding", "argmax", "topk_sample",
+    "gemm", "linear", "row_sumsq", "RowStats", "interleave_gate_up", "rmsnorm", "rope_kvwrite", "swiglu", "embedding", "argmax", "topk_sample",
     "paged_prefill", "paged_decode", "decode_plan_splits", "KernelError", "launch_count",
     "raise_on_status",
 ]
@@ -36,7 +36,47 @@ def _need_bf16(*ts):
 
 
 # ------------------------------------------------------------------ GEMM
-def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits: int = 0, static_w: bool = False):
+class RowStats:
+    """Partial sums of squares of the rows of an activation: `parts[:n]` is float32 [n, rows] and the
+    sum of squares of row t is parts[:n, t].sum().  A GEMM that produces the residual stream leaves
+    them behind (`emit_stats`), the next GEMM turns them into the RMSNorm scale of its input rows
+    (`row_stats`), so no normalisation kernel runs between the two (zml/nn.zig:486-493 is the
+    reference's stand-alone rmsNorm)."""
+    __slots__ = ("parts", "n")
+    MAX_PARTS = 160          # tiles x cluster size of a cluster plan is at most the SM count
+
+    def __init__(self, parts: torch.Tensor, n: int):
+        self.parts, self.n = parts, n
+
+    def total(self) -> torch.Tensor:
+        return self.parts[:self.n].sum(0)
+
+    def scale(self, d: int, eps: float) -> torch.Tensor:
+        return torch.rsqrt(self.total() / d + eps)
+
+
+def row_sumsq(x) -> RowStats:
+    """RowStats of a [rows, d] activation computed by a kernel of its own (one part)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if not _cuda(x2):
+        return RowStats(reference.row_sumsq(x2)[None], 1)
+    _need_bf16(x2)
+    assert x2.stride(1) == 1
+    out = torch.empty((1, x2.shape[0]), dtype=torch.float32, device=x2.device)
+    _lib.check(_lib.lib().zb_row_sumsq(_ptr(x2), x2.shape[0], x2.shape[1], x2.stride(0), _ptr(out), _lib.stream_ptr()),
+               "zb_row_sumsq")
+    return RowStats(out, 1)
+
+
+def interleave_gate_up(gate_up: torch.Tensor) -> torch.Tensor:
+    """[gate rows | up rows] -> rows (gate_0, up_0, gate_1, up_1, ...): the layout `gemm(..., swiglu=True)` takes."""
+    f = gate_up.shape[0] // 2
+    return torch.stack([gate_up[:f], gate_up[f:]], 1).reshape(gate_up.shape)
+
+
+def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits: int = 0, static_w: bool = False,
+         row_stats: RowStats | None = None, eps: float = 1e-5, swiglu: bool = False, emit_stats: bool = False,
+         prefetch=None):
     """out[M,N] = a[M,K] @ w[N,K]^T (+ bias[N]) (+ residual[M,N]).
 
     `w` is stored [N, K] (the safetensors layout of every HF linear weight), so both
@@ -44,13 +84,22 @@ def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits:
     `residual` (in-place residual stream update).  `static_w=True` declares `w` a parameter that
     no kernel still in flight on the stream writes; the kernel then fetches its first weight
     tiles while the preceding kernel drains.
+
+    Epilogue options (all inside the one kernel):
+    `row_stats` - the accumulators of row t are multiplied by rsqrt(sumsq_t / K + eps) before bias and
+    residual: with the RMSNorm weight folded into the columns of `w` the GEMM computes rmsnorm(a) @ w^T;
+    `swiglu` - the rows of `w` interleave gate and up (`interleave_gate_up`), the result is
+    silu(gate) * up, [M, N / 2];
+    `emit_stats` - also returns the RowStats of the (rounded) output: the call returns (out, stats);
+    `prefetch` - a tensor (the next GEMM's weights) pulled into L2 behind this kernel's own loads.
     """
     if not _cuda(a):
-        r = reference.gemm(a, w, residual, bias, out_dtype)
+        scale = row_stats.scale(a.shape[1], eps) if row_stats is not None else None
+        r = reference.gemm(a, w, residual, bias, out_dtype, scale, swiglu)
         if out is not None:
             out.copy_(r)
-            return out
-        return r
+            r = out
+        return (r, RowStats(reference.row_sumsq(r)[None], 1)) if emit_stats else r
     _need_bf16(a, w, residual, bias)
     m, k = a.shape
     n, k2 = w.shape
@@ -58,16 +107,38 @@ def gemm(a, w, residual=None, bias=None, out=None, out_dtype=None, force_splits:
     assert a.stride(1) == 1 and w.stride(1) == 1
     odt = out_dtype or torch.bfloat16
     if out is None:
-        out = torch.empty((m, n), dtype=odt, device=a.device)
+        out = torch.empty((m, n // 2 if swiglu else n), dtype=odt, device=a.device)
     assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     if residual is not None:
         assert residual.stride(0) == out.stride(0) and residual.stride(1) == 1
-    rc = _lib.lib().zb_gemm_bf16(
-        _ptr(a), _ptr(w), _ptr(out), _ptr(residual), _ptr(bias), m, n, k, a.stride(0), w.stride(0),
-        out.stride(0), (1 if out.dtype == torch.float32 else 0) | (2 if static_w else 0), force_splits,
-        _lib.stream_ptr())
-    _lib.check(rc, "zb_gemm_bf16")
+    flags = (1 if out.dtype == torch.float32 else 0) | (2 if static_w else 0)
+    if row_stats is None and not swiglu and not emit_stats and prefetch is None:
+        rc = _lib.lib().zb_gemm_bf16(
+            _ptr(a), _ptr(w), _ptr(out), _ptr(residual), _ptr(bias), m, n, k, a.stride(0), w.stride(0),
+            out.stride(0), flags, force_splits, _lib.stream_ptr())
+        _lib.check(rc, "zb_gemm_bf16")
+        return out
+    import ctypes as C
+    stats_out, parts = None, C.c_int(0)
+    if emit_stats:
+        stats_out = torch.empty((RowStats.MAX_PARTS, m), dtype=torch.float32, device=a.device)
+    if row_stats is not None:
+        assert row_stats.parts.dtype == torch.float32 and row_stats.parts.stride(1) == 1 and row_stats.parts.shape[1] >= m
+    pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES) if prefetch is not None else 0
+    rc = _lib.lib().zb_gemm_bf16_epi(
+        _ptr(a), _ptr(w), _ptr(out), _ptr(residual), _ptr(bias), m, n, k, a.stride(0), w.stride(0), out.stride(0), flags,
+        force_splits, _ptr(row_stats.parts) if row_stats is not None else 0, row_stats.n if row_stats is not None else 0,
+        row_stats.parts.stride(0) if row_stats is not None else 0, 1.0 / k, float(eps), int(swiglu),
+        _ptr(stats_out), m, C.byref(parts), _ptr(prefetch), pf_bytes, _lib.stream_ptr())
+    _lib.check(rc, "zb_gemm_bf16_epi")
+    if emit_stats:
+        assert 0 < parts.value <= RowStats.MAX_PARTS, parts.value
+        return out, RowStats(stats_out, parts.value)
     return out
+
+
+# Upper bound of the bytes one kernel pulls into L2 for its successor (a quarter of the 126 MB L2).
+PREFETCH_MAX_BYTES = 32 << 20
 
 
 def linear(x, w, bias=None, residual=None, out=None, out_dtype=None, static_w: bool = True):

@@ -56,6 +56,10 @@ _SIGS = {
     "zb_gemm_bf16": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
     "zb_gemm_bf16_ex": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i,
                               c_p, c_sz, c_p, c_i, c_p, c_i, c_p]),
+    "zb_gemm_bf16_epi": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p, c_i, c_i, c_f, c_f,
+                               c_i, c_p, c_i, c_p, c_p, c_ull, c_p]),
+    "zb_gemm_scratch_needed": (c_sz, [c_i, c_i, c_i, c_i]),
+    "zb_row_sumsq": (c_i, [c_p, c_i, c_i, c_ll, c_p, c_p]),
     "zb_rmsnorm": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_ll, c_f, c_i, c_p]),
     "zb_rope_kvwrite": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_ll, c_i, c_i, c_i, c_i,
                               c_i, c_i, c_i, c_ll, c_f, c_f, c_i, c_p]),

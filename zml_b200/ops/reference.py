@@ -11,14 +11,24 @@ import math
 import torch
 
 
-def gemm(a, w, residual=None, bias=None, out_dtype=None):
-    """out[M,N] = a[M,K] @ w[N,K]^T (+ bias[N]) (+ residual[M,N]), fp32 accumulate."""
+def gemm(a, w, residual=None, bias=None, out_dtype=None, row_scale=None, swiglu=False):
+    """out[M,N] = a[M,K] @ w[N,K]^T (* row_scale[M]) (+ bias[N]) (+ residual[M,N]), fp32 accumulate.
+    With `swiglu` the rows of `w` interleave gate and up and the result is silu(gate) * up, [M, N / 2]."""
     out = a.float() @ w.float().t()
+    if row_scale is not None:
+        out = out * row_scale.float()[:, None]
     if bias is not None:
         out = out + bias.float()
     if residual is not None:
         out = out + residual.float()
+    if swiglu:
+        out = torch.nn.functional.silu(out[:, 0::2]) * out[:, 1::2]
     return out.to(out_dtype or a.dtype)
+
+
+def row_sumsq(x):
+    """Sum of squares of every row, float32 [rows]."""
+    return x.float().pow(2).sum(-1)
 
 
 def rmsnorm(x, weight, eps=1e-5, residual=None, unit_offset=False):

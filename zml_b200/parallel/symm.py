@@ -39,6 +39,13 @@ _lib.register_signature("zb_ar_ctx_destroy", None, [C.c_void_p], optional=False)
 _lib.register_signature("zb_comm_barrier", C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p], optional=False)
 _lib.register_signature("zb_allreduce_oneshot", C.c_int,
                         [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p], optional=False)
+_lib.register_signature("zb_ar_ctx_set_multicast", None, [C.c_void_p, C.c_void_p], optional=False)
+_lib.register_signature("zb_allreduce_mm", C.c_int,
+                        [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_longlong, C.c_size_t, C.c_void_p], optional=False)
+_lib.register_signature("zb_gemm_ar_fused_epi", C.c_int,
+                        [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
+                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                         C.c_ulonglong, C.c_void_p], optional=False)
 _lib.register_signature("zb_gemm_ar_fused", C.c_int,
                         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p], optional=False)
@@ -59,7 +66,7 @@ def _align(n: int, a: int = 256) -> int:
 
 class SymmetricContext:
     MAX_TILES = 8192
-    LL_ALLREDUCE = os.environ.get("ZB_LL_ALLREDUCE", "1") == "1"     # `autotune` considers the two-shot tagged-slot all-reduce
+    LL_ALLREDUCE = os.environ.get("ZB_LL_ALLREDUCE", "1") == "1"     # two-shot tagged-slot all-reduce for 33 - 256 tokens
 
     def __init__(self):
         self.comm: Optional[Comm] = None
@@ -72,12 +79,11 @@ class SymmetricContext:
         self._next = 0
         self.staging = None
         self.staging_off = 0
-        # the fused GEMM + all-reduce is used up to this many tokens (the single-hop exchange with
-        # 32-token tiles: 76.8 vs 90.6 us per Llama-8B TP8-shaped decoder layer); with 64-token tiles
-        # and for prefill-sized batches the GEMM followed by an NCCL all-reduce measured faster
-        self.fused_max_tokens = 32
-        self.tuned = None      # result of `autotune`, if it ran
-        self.ll_enabled = False  # two-shot tagged-slot all-reduce after the GEMM for batches the fused kernel does not take
+        # The fused GEMM + all-reduce (single-hop exchange of a tile's partial sums with every peer) serves up to
+        # this many tokens: it sends (world - 1) copies of the tensor, which stops paying beyond one 32-token tile.
+        self.fused_max_tokens = int(os.environ.get("ZB_FUSED_MAX_TOKENS", "32"))
+        # batches the fused kernel does not take, up to `ll_tokens`: GEMM, then the two-shot tagged-slot all-reduce
+        self.ll_enabled = self.LL_ALLREDUCE
 
     @staticmethod
     def create(comm: Comm, hidden: int, max_tokens: int = 8192, staging_elems: int = 0,
@@ -110,30 +116,44 @@ class SymmetricContext:
         # slot area of the two-shot all-reduce: 2 phases x 2 parity halves, 4 bytes per element each
         self.ll_bytes = _align(16 * ll_tokens * hidden)
         self.ll_off = self.combine_off + self.combine_bytes
-        self.heap_bytes = self.ll_off + self.ll_bytes
+        # flags of the multimem all-reduce (2 phases x 128 blocks x 8 ranks) and of the band pipeline of the prefill
+        # collectives (3 counters per 128-token band), then the buffer the row-parallel GEMMs leave partial sums in
+        self.mm_flag_off = self.ll_off + self.ll_bytes
+        self.band_flag_off = self.mm_flag_off + 2 * 128 * 8 * 4
+        self.band_flag_bytes = _align(4 * 4 * ((max_tokens + 127) // 128 + 1) * 8)
+        self.part_off = _align(self.band_flag_off + self.band_flag_bytes, 4096)
+        self.heap_bytes = self.part_off + act_bytes
         self.hidden, self.max_tokens = hidden, max_tokens
-        p = C.c_void_p()
-        _lib.check(l.zb_symm_alloc(self.heap_bytes, C.byref(p)), "zb_symm_alloc")
-        self.local_ptr = p.value
-        h = C.create_string_buffer(64)
-        _lib.check(l.zb_symm_ipc_handle(self.local_ptr, h), "zb_symm_ipc_handle")
-        handles = comm.all_gather_object(bytes(h.raw))
-        self.peer_ptrs = []
-        for r, hb in enumerate(handles):
-            if r == comm.rank:
-                self.peer_ptrs.append(self.local_ptr)
-            else:
-                q = C.c_void_p()
-                _lib.check(l.zb_symm_ipc_open(hb, C.byref(q)), f"zb_symm_ipc_open(rank {r})")
-                self.peer_ptrs.append(q.value)
+        self.mc_ptr = 0
+        self._tsm = None
+        if not self._map_multicast_heap():
+            p = C.c_void_p()
+            _lib.check(l.zb_symm_alloc(self.heap_bytes, C.byref(p)), "zb_symm_alloc")
+            self.local_ptr = p.value
+            h = C.create_string_buffer(64)
+            _lib.check(l.zb_symm_ipc_handle(self.local_ptr, h), "zb_symm_ipc_handle")
+            handles = comm.all_gather_object(bytes(h.raw))
+            self.peer_ptrs = []
+            for r, hb in enumerate(handles):
+                if r == comm.rank:
+                    self.peer_ptrs.append(self.local_ptr)
+                else:
+                    q = C.c_void_p()
+                    _lib.check(l.zb_symm_ipc_open(hb, C.byref(q)), f"zb_symm_ipc_open(rank {r})")
+                    self.peer_ptrs.append(q.value)
         arr = (C.c_void_p * 8)(*(self.peer_ptrs + [None] * (8 - w)))
         self.ctx = l.zb_ar_ctx_create(comm.rank, w, arr, self.recv_off, recv_bytes, self.push_off,
                                       self.done_off, self.MAX_TILES)
         if not self.ctx:
             raise _lib.KernelError("zb_ar_ctx_create failed")
+        if self.mc_ptr:
+            l.zb_ar_ctx_set_multicast(self.ctx, self.mc_ptr)
         dev = comm.device
-        self._holder = _DevMem(self.local_ptr, self.heap_bytes, self)
-        heap = torch.as_tensor(self._holder, device=dev)
+        if self._tsm is not None:
+            heap = self._tsm[0]
+        else:
+            self._holder = _DevMem(self.local_ptr, self.heap_bytes, self)
+            heap = torch.as_tensor(self._holder, device=dev)
         self.heap = heap
         self.act = [heap[o:o + act_bytes].view(torch.bfloat16) for o in self.act_off]
         if stg_bytes:
@@ -141,9 +161,82 @@ class SymmetricContext:
         comm.barrier()
         return self
 
+    # Where the heap comes from.  "auto": memory from the driver's virtual-memory API through
+    # torch.distributed._symmetric_memory, which also binds the heaps of all ranks to one NVLink multicast address
+    # (needed by multimem loads / stores); if that is not available, or with ZB_SYMM_BACKEND=ipc / ZB_NVLS=0 /
+    # NCCL_NVLS_ENABLE=0, plain cudaMalloc memory shared through CUDA IPC handles (peer loads and stores only).
+    BACKEND = os.environ.get("ZB_SYMM_BACKEND", "auto")
+    MM_PREFILL = os.environ.get("ZB_MM_PREFILL", "1") == "1"    # multimem all-reduce for prefill-sized tensors
+
+    def _map_multicast_heap(self) -> bool:
+        if (self.BACKEND == "ipc" or os.environ.get("ZB_NVLS", "1") == "0" or os.environ.get("NCCL_NVLS_ENABLE", "1") == "0"
+                or self.comm.world == 1):
+            return False
+        try:
+            import torch.distributed._symmetric_memory as tsm
+            t = tsm.empty(self.heap_bytes, dtype=torch.uint8, device=self.comm.device)
+            hdl = tsm.rendezvous(t, self.comm.group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        except Exception as e:          # no fabric / old driver / unsupported build: peer loads and stores still work over IPC
+            if self.BACKEND == "torch":
+                raise
+            import logging
+            logging.getLogger("zml_b200.symm").warning("multicast heap unavailable (%s); using CUDA IPC", e)
+            return False
+        if len(ptrs) != self.comm.world:
+            return False
+        t.zero_()
+        torch.cuda.synchronize()
+        self._tsm = (t, hdl)
+        self.local_ptr = ptrs[self.comm.rank]
+        self.peer_ptrs = ptrs
+        self.mc_ptr = mc
+        return True
+
+    @property
+    def has_multicast(self) -> bool:
+        return bool(self.mc_ptr)
+
+    def prefill_collective(self) -> str:
+        """One line for logs and benchmark records: how prefill-sized row-parallel outputs are summed."""
+        if self.has_multicast and self.MM_PREFILL:
+            return "GEMM into the symmetric heap, then in-kernel all-reduce inside NVSwitch (multimem load-reduce + store)"
+        return "NCCL all-reduce after the GEMM"
+
     # ------------------------------------------------------------------ ops
-    def gemm_allreduce(self, a, w, residual=None, bias=None, force_splits: int = 0):
-        """All ranks: returns sum_r(a_r @ w_r^T) + bias + residual, bf16 [M, N], N == hidden."""
+    def partial_buffer(self, m: int, n: int) -> torch.Tensor:
+        """bf16 [m, n] view of the heap region row-parallel GEMMs write partial sums to (input of `all_reduce_mm`)."""
+        assert m * n * 2 <= self.heap_bytes - self.part_off
+        return self.heap[self.part_off:self.part_off + m * n * 2].view(torch.bfloat16).view(m, n)
+
+    def can_all_reduce_mm(self, tokens: int, d: int) -> bool:
+        return (self.ctx is not None and self.has_multicast and self.MM_PREFILL and d == self.hidden and tokens <= self.max_tokens
+                and (tokens * d) % 8 == 0)
+
+    def all_reduce_mm(self, part: torch.Tensor, residual=None) -> torch.Tensor:
+        """All ranks: residual + sum over ranks of `part` (a tensor inside the heap, e.g. `partial_buffer`), reduced
+        inside NVSwitch by multimem loads and written to every rank by multimem stores (libzb_cuda.so:
+        zb_allreduce_mm).  Returns one of the two activation buffers of the heap."""
+        assert self.mc_ptr and part.dtype == torch.bfloat16 and part.is_contiguous()
+        in_off = part.data_ptr() - self.local_ptr
+        assert 0 <= in_off < self.heap_bytes, "all_reduce_mm input must live in the symmetric heap"
+        n = part.numel()
+        idx = self._next
+        if residual is not None and residual.data_ptr() == self.act[idx].data_ptr():
+            idx ^= 1
+        self._next = idx ^ 1
+        out = self.act[idx][:n].view(part.shape)
+        _lib.check(_lib.lib().zb_allreduce_mm(self.ctx, in_off, self.act_off[idx], residual.data_ptr() if residual is not None else None,
+                                              n, self.mm_flag_off, _lib.stream_ptr()), "zb_allreduce_mm")
+        return out
+
+    def gemm_allreduce(self, a, w, residual=None, bias=None, force_splits: int = 0, emit_stats: bool = False,
+                       prefetch=None):
+        """All ranks: returns sum_r(a_r @ w_r^T) + bias + residual, bf16 [M, N], N == hidden.  With
+        `emit_stats` returns (out, RowStats of the output rows); `prefetch` names the next GEMM's weights,
+        pulled into L2 while the exchange with the peers is in flight."""
+        from ..ops import PREFETCH_MAX_BYTES, RowStats
         m, k = a.shape
         n = w.shape[0]
         if n != self.hidden or m > self.max_tokens:
@@ -154,90 +247,21 @@ class SymmetricContext:
             idx ^= 1
         self._next = idx ^ 1
         out = self.act[idx][: m * n].view(m, n)
-        rc = _lib.lib().zb_gemm_ar_fused(
+        stats_out, parts = None, C.c_int(0)
+        if emit_stats:
+            stats_out = torch.empty((RowStats.MAX_PARTS, m), dtype=torch.float32, device=a.device)
+        pf_bytes = min(prefetch.numel() * prefetch.element_size(), PREFETCH_MAX_BYTES) if prefetch is not None else 0
+        rc = _lib.lib().zb_gemm_ar_fused_epi(
             self.ctx, a.data_ptr(), w.data_ptr(), self.act_off[idx],
             residual.data_ptr() if residual is not None else None,
             bias.data_ptr() if bias is not None else None, m, n, k, a.stride(0), w.stride(0), n,
-            force_splits, _lib.stream_ptr())
+            force_splits, stats_out.data_ptr() if emit_stats else None, m, C.byref(parts),
+            prefetch.data_ptr() if prefetch is not None else None, pf_bytes, _lib.stream_ptr())
         _lib.check(rc, "zb_gemm_ar_fused")
+        if emit_stats:
+            assert 0 < parts.value <= RowStats.MAX_PARTS, parts.value
+            return out, RowStats(stats_out, parts.value)
         return out
-
-    def autotune(self, run, tokens: int = 32, reps: int = 5, units: int = 1) -> dict:
-        """Collective.  Times `run()` - a decode-sized piece of the model that goes through
-        `LlamaModel.row_parallel`, with weights that do not fit the L2 - once with the fused GEMM + all-reduce
-        once with the GEMM followed by the two-shot tagged-slot all-reduce (`all_reduce_ll`) and once with the GEMM
-        followed by the NCCL all-reduce, each as a CUDA graph, and keeps the fastest: the fused path up to `tokens`
-        (`fused_max_tokens`) only if it wins, the tagged-slot all-reduce for decode-sized batches (`ll_enabled`) only
-        if it beats NCCL.  Which one wins depends on the tensor-parallel degree and
-        on the NVLink latency of the box (measured on B200, Llama-3.1-8B: 8 ranks fused 1.31x faster end to end;
-        2 ranks NCCL 10 % faster, although a chain of the projections alone has the fused kernel ahead)."""
-        comm, dev = self.comm, self.comm.device
-
-        def graph_us() -> float:
-            side = torch.cuda.Stream(device=dev)
-            side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(side):
-                run()
-            torch.cuda.current_stream().wait_stream(side)
-            torch.cuda.synchronize()
-            comm.barrier()
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                run()
-            gr.replay()
-            torch.cuda.synchronize()
-            comm.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                gr.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            return comm.max_over_ranks(e0.elapsed_time(e1) * 1e3 / (reps * units))
-
-        self.fused_max_tokens, self.ll_enabled = tokens, False
-        t_fused = graph_us()
-        t_ll = float("inf")
-        if self.LL_ALLREDUCE:
-            self.fused_max_tokens, self.ll_enabled = 0, True
-            t_ll = graph_us()
-        self.fused_max_tokens, self.ll_enabled = 0, False
-        t_nccl = graph_us()
-        self.fused_max_tokens = tokens if t_fused <= min(t_ll, t_nccl) else 0
-        self.ll_enabled = t_ll <= t_nccl
-        self.tuned = {"fused_us": round(t_fused, 2), "ll_us": round(t_ll, 2) if t_ll != float("inf") else None, "nccl_us": round(t_nccl, 2), "tokens": tokens,
-                      "choice": "fused" if self.fused_max_tokens else ("ll" if self.ll_enabled else "nccl"),
-                      "above": "ll" if self.ll_enabled else "nccl"}
-
-        return self.tuned
-
-    def autotune_projections(self, ks, tokens: int = 32, chain: int = 4) -> dict:
-        """`autotune` on a stand-in for models without a plain attention layer: for every row-parallel weight
-        [hidden, k] (k in `ks`) a column-parallel GEMM [k, hidden] produces its input; `chain` such blocks."""
-        from .. import ops
-        comm, dev = self.comm, self.comm.device
-        gen = torch.Generator(device=dev).manual_seed(17)
-        blocks = []
-        for _ in range(chain):
-            for k in ks:
-                wc = torch.empty(k, self.hidden, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
-                wr = torch.empty(self.hidden, k, device=dev, dtype=torch.bfloat16).normal_(0, 0.02, generator=gen)
-                blocks.append((wc, wr))
-        x0 = torch.empty(tokens, self.hidden, device=dev, dtype=torch.bfloat16).normal_(0, 0.5, generator=gen)
-
-        def run():
-            x = x0
-            for wc, wr in blocks:
-                a = ops.gemm(x, wc, static_w=True)
-                if a.shape[0] <= self.fused_max_tokens:
-                    x = self.gemm_allreduce(a, wr, x)
-                elif self.can_all_reduce_ll(a.shape[0], self.hidden):
-                    x = self.all_reduce_ll(ops.gemm(a, wr, static_w=True), x)
-                else:
-                    x = comm.all_reduce_(ops.gemm(a, wr, residual=x if comm.rank == 0 else None, static_w=True))
-            return x
-
-        return self.autotune(run, tokens, units=len(blocks))
 
     def barrier(self):
         """Device-side barrier across the group on the current stream."""
@@ -290,13 +314,17 @@ class SymmetricContext:
         torch.cuda.synchronize()
         if self.comm is not None:
             self.comm.barrier()
-        for r, p in enumerate(self.peer_ptrs):
-            if self.comm is not None and r != self.comm.rank:
-                l.zb_symm_ipc_close(p)
+        if self._tsm is None:
+            for r, p in enumerate(self.peer_ptrs):
+                if self.comm is not None and r != self.comm.rank:
+                    l.zb_symm_ipc_close(p)
         if self.ctx:
             l.zb_ar_ctx_destroy(self.ctx)
             self.ctx = None
         self.act, self.heap, self.staging = [], None, None
-        if self.local_ptr:
+        if self._tsm is not None:
+            self._tsm = None            # the allocation and its mappings go with the tensor
+            self.local_ptr = 0
+        elif self.local_ptr:
             l.zb_symm_free(self.local_ptr)
             self.local_ptr = 0
