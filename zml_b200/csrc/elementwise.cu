@@ -359,9 +359,15 @@ constexpr int kMaxTopK = 128;
 __global__ void __launch_bounds__(1024) zb_topk_sample_kernel(
     const float* __restrict__ logits, int32_t* __restrict__ out_token, float* __restrict__ topk_vals,
     int32_t* __restrict__ topk_idx, int vocab, long long stride, int k, float temperature,
-    uint64_t seed, uint64_t step) {
+    uint64_t seed, uint64_t step, const unsigned long long* __restrict__ dev_rng) {
   zb_pdl_launch();
   zb_pdl_wait();
+  if (dev_rng != nullptr) {
+    // seed and draw counter live on the device: a captured CUDA graph then samples with fresh noise at every
+    // replay (the counter is advanced by zb_decode_advance) and with whatever seed was copied in before it
+    seed = dev_rng[0];
+    step += dev_rng[1];
+  }
   const float* row = logits + static_cast<size_t>(blockIdx.x) * stride;
   __shared__ uint32_t hist[256];
   __shared__ uint32_t s_prefix, s_remaining;
@@ -516,10 +522,17 @@ __global__ void zb_decode_advance_kernel(const int32_t* __restrict__ sampled, in
 }
 
 // Runs after the kernel above on the same stream, so every block has read the old value.
-__global__ void zb_counter_inc_kernel(int32_t* c) {
+__global__ void zb_counter_inc_kernel(int32_t* c, unsigned long long* rng) {
   zb_pdl_launch();
   zb_pdl_wait();
   *c += 1;
+  if (rng != nullptr) rng[1] += 1ull;      // one more draw of the sampler (see zb_topk_sample_rng)
+}
+
+__global__ void zb_u64_add_kernel(unsigned long long* p, unsigned long long n) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  *p += n;
 }
 
 }  // namespace
@@ -621,29 +634,59 @@ int zb_argmax_f32(const float* logits, int32_t* out, int rows, int vocab, long l
   return static_cast<int>(cudaGetLastError());
 }
 
+// `dev_rng` (may be null): two u64 in device memory, {seed, draws so far}; when given, the seed comes from there
+// and the draw counter is added to `step`.
+int zb_topk_sample_rng(const float* logits, int32_t* out_token, float* topk_vals, int32_t* topk_idx,
+                       int rows, int vocab, long long stride, int k, float temperature,
+                       unsigned long long seed, unsigned long long step, const unsigned long long* dev_rng, void* stream) {
+  if (rows <= 0) return 0;
+  if (k < 1 || k > kMaxTopK) return -45;
+  zb_launch(zb_topk_sample_kernel, dim3(rows), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream),
+      logits, out_token, topk_vals, topk_idx, vocab, stride, k, temperature, seed, step, dev_rng);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int zb_topk_sample(const float* logits, int32_t* out_token, float* topk_vals, int32_t* topk_idx,
                    int rows, int vocab, long long stride, int k, float temperature,
                    unsigned long long seed, unsigned long long step, void* stream) {
-  if (rows <= 0) return 0;
-  if (k < 1 || k > kMaxTopK) return -45;
-  zb_launch(zb_topk_sample_kernel, dim3(rows), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), 
-      logits, out_token, topk_vals, topk_idx, vocab, stride, k, temperature, seed, step);
+  return zb_topk_sample_rng(logits, out_token, topk_vals, topk_idx, rows, vocab, stride, k, temperature, seed, step, nullptr,
+                            stream);
+}
+
+// Adds `n` to a u64 in device memory, in stream order (the draw counter of the sampler).
+int zb_u64_add(unsigned long long* p, unsigned long long n, void* stream) {
+  zb_launch(zb_u64_add_kernel, dim3(1), dim3(1), 0, reinterpret_cast<cudaStream_t>(stream), p, n);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
 
 // Feeds sampled tokens back for the next decode step (see the kernel's comment).
+int zb_decode_advance_rng(const int32_t* sampled, int32_t* ids, int32_t* positions, int32_t* seq_lens,
+                          int32_t* slot_mapping, const int32_t* block_table, int32_t* history,
+                          int32_t* step_counter, int batch, int max_pages, int page_size,
+                          int history_stride, int history_rows, unsigned long long* rng, void* stream);
+
 int zb_decode_advance(const int32_t* sampled, int32_t* ids, int32_t* positions, int32_t* seq_lens,
                       int32_t* slot_mapping, const int32_t* block_table, int32_t* history,
                       int32_t* step_counter, int batch, int max_pages, int page_size,
                       int history_stride, int history_rows, void* stream) {
+  return zb_decode_advance_rng(sampled, ids, positions, seq_lens, slot_mapping, block_table, history, step_counter, batch,
+                               max_pages, page_size, history_stride, history_rows, nullptr, stream);
+}
+
+// The same, and the sampler's draw counter rng[1] (see zb_topk_sample_rng) goes up by one.
+int zb_decode_advance_rng(const int32_t* sampled, int32_t* ids, int32_t* positions, int32_t* seq_lens,
+                          int32_t* slot_mapping, const int32_t* block_table, int32_t* history,
+                          int32_t* step_counter, int batch, int max_pages, int page_size,
+                          int history_stride, int history_rows, unsigned long long* rng, void* stream) {
   if (batch <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   zb_launch(zb_decode_advance_kernel, dim3((batch + 127) / 128), dim3(128), 0, s, sampled, ids, positions, seq_lens,
                                                              slot_mapping, block_table, history,
                                                              step_counter, batch, max_pages, page_size,
                                                              history_stride, history_rows);
-  zb_launch(zb_counter_inc_kernel, dim3(1), dim3(1), 0, s, step_counter);
+  zb_launch(zb_counter_inc_kernel, dim3(1), dim3(1), 0, s, step_counter, rng);
   zb_count_launch(2);
   return static_cast<int>(cudaGetLastError());
 }

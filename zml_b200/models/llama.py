@@ -423,13 +423,15 @@ class LlamaModel:
             lg[:, self.v_per - self.v_pad:] = float("-inf")
         return lg
 
-    def sample(self, logits, strategy: common.SamplingStrategy, seed: int = 0, step: int = 0):
-        """Token ids int32 [B] from vocab-parallel logits."""
+    def sample(self, logits, strategy: common.SamplingStrategy, seed: int = 0, step: int = 0, rng=None):
+        """Token ids int32 [B] from vocab-parallel logits.  `rng`: device-side {seed, draw counter} of
+        `ops.topk_sample` (the serving engine's, so that graph replays draw fresh noise)."""
         comm = self.comm
+        rng = rng if (rng is not None and logits.is_cuda) else None
         if comm.world == 1:
             if strategy.topk <= 1:
                 return ops.argmax(logits)
-            return ops.topk_sample(logits, strategy.topk, strategy.temperature, seed, step)
+            return ops.topk_sample(logits, strategy.topk, strategy.temperature, seed, step, rng=rng)
         if strategy.topk <= 1:
             idx = ops.argmax(logits)
             val = logits.gather(1, idx.long()[:, None])[:, 0]
@@ -439,11 +441,11 @@ class LlamaModel:
             return idxs.gather(0, best[None])[0].to(torch.int32)
         # every rank holds v_per columns (padding columns are -inf), so column r * v_per + j is token r * v_per + j
         full = comm.all_gather(logits, dim=1)
-        return ops.topk_sample(full.contiguous(), strategy.topk, strategy.temperature, seed, step)
+        return ops.topk_sample(full.contiguous(), strategy.topk, strategy.temperature, seed, step, rng=rng)
 
     def forward(self, ids, meta: AttnMeta, kv_cache, strategy: Optional[common.SamplingStrategy] = None,
-                seed: int = 0, step: int = 0):
+                seed: int = 0, step: int = 0, rng=None):
         """ids int32 [T] -> sampled tokens int32 [rows] (one per sequence)."""
         x = self.hidden_states(ids, meta, kv_cache)
         lg = self.logits(x, meta.logits_rows)
-        return self.sample(lg, strategy or common.SamplingStrategy(), seed, step)
+        return self.sample(lg, strategy or common.SamplingStrategy(), seed, step, rng)

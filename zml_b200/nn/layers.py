@@ -127,6 +127,11 @@ def normalize_variance(x: Tensor, eps: float, ax="d") -> Tensor:
 def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float = 1e-5, ax="d", unit_offset: bool = False) -> Tensor:
     """RMSNorm with f32 upcast (zml/nn.zig:486-493); `unit_offset` is the (1 + w) variant."""
     a = x.axis(ax)
+    if (x.data.is_cuda and x.data.dtype == torch.bfloat16 and a == x.rank() - 1 and x.data.shape[-1] % 8 == 0
+            and (weight is None or weight.data.dtype == torch.bfloat16)):
+        from .. import ops             # the library's RMSNorm kernel (bf16, last axis)
+        xd = x.data if x.data.is_contiguous() else x.data.contiguous()
+        return x._like(ops.rmsnorm(xd, weight.data if weight is not None else None, eps, unit_offset=unit_offset))
     xf = x.data.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(a, keepdim=True) + eps)
     if weight is not None:

@@ -16,10 +16,22 @@ def sample_tokens(activations: Tensor, opts: SamplingStrategy, rng: Rng) -> tupl
     """`activations` carries a `voc` axis; returns integer ids without it.  With topk > 1 the
     k best logits are scaled by 1/temperature, Gumbel noise is added and the argmax is taken
     (equivalent to sampling from the softmax over the k)."""
+    d = activations.data
+    on_kernels = (d.is_cuda and d.dtype == torch.float32 and d.dim() == 2 and activations.axis("voc") == 1 and d.stride(1) == 1
+                  and opts.topk <= 128)
     if opts.topk <= 1:
+        if on_kernels:      # the library's arg-max kernel (first index of the maximum)
+            from .. import ops
+            return Tensor(ops.argmax(d), None, (activations.shape().tags[0],)), rng
         _, idx = activations.arg_max("voc")
         return idx.squeeze("voc"), rng
-    vals, idx = activations.top_k({"topk": "voc"}, opts.topk)
+    if on_kernels:          # radix-select top-k kernel; the Gumbel draw below stays on the tagged API's Rng
+        from .. import ops
+        _, v, i = ops.topk_sample(d, opts.topk, 1.0, return_topk=True)
+        tags = (activations.shape().tags[0], "topk")
+        vals, idx = Tensor(v, None, tags), Tensor(i, None, tags)
+    else:
+        vals, idx = activations.top_k({"topk": "voc"}, opts.topk)
     x = vals.convert("f32")
     if opts.temperature != 1.0:
         x = x.scale(1.0 / opts.temperature)

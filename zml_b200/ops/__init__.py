@@ -255,9 +255,12 @@ def argmax(logits, out=None):
 
 
 def topk_sample(logits, k: int, temperature: float = 1.0, seed: int = 0, step: int = 0,
-                return_topk: bool = False, generator=None):
+                return_topk: bool = False, generator=None, rng=None):
     """Top-k then Gumbel-max sampling (zml/nn.zig:2007-2033).  k == 1 is greedy.
 
+    The noise of row r is a function of (seed, step, r).  `rng` (CUDA only): an int64 tensor {seed, draws so
+    far} on the device that replaces `seed` and is added to `step`, so a captured CUDA graph draws fresh noise
+    at every replay once the counter is advanced on the device (`advance_rng`, or the decode bookkeeping).
     Returns tokens int32 [B] (and the sorted top-k values / indices when asked).
     """
     if not _cuda(logits):
@@ -276,11 +279,21 @@ def topk_sample(logits, k: int, temperature: float = 1.0, seed: int = 0, step: i
     if return_topk:
         vals = torch.empty((b, k), dtype=torch.float32, device=logits.device)
         idx = torch.empty((b, k), dtype=torch.int32, device=logits.device)
-    rc = _lib.lib().zb_topk_sample(_ptr(logits), _ptr(tok), _ptr(vals), _ptr(idx), b,
-                                   logits.shape[1], logits.stride(0), k, float(temperature),
-                                   int(seed), int(step), _lib.stream_ptr())
+    if rng is not None:
+        assert rng.dtype == torch.int64 and rng.is_cuda and rng.numel() >= 2
+    rc = _lib.lib().zb_topk_sample_rng(_ptr(logits), _ptr(tok), _ptr(vals), _ptr(idx), b,
+                                       logits.shape[1], logits.stride(0), k, float(temperature),
+                                       int(seed), int(step), _ptr(rng), _lib.stream_ptr())
     _lib.check(rc, "zb_topk_sample")
     return (tok, vals, idx) if return_topk else tok
+
+
+def advance_rng(rng, n: int = 1) -> None:
+    """rng[1] += n in stream order (see `topk_sample`)."""
+    if rng.is_cuda:
+        _lib.check(_lib.lib().zb_u64_add(rng.data_ptr() + 8, int(n), _lib.stream_ptr()), "zb_u64_add")
+    else:
+        rng[1] += n
 
 
 # ------------------------------------------------------------------ attention

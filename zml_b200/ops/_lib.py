@@ -67,6 +67,9 @@ _SIGS = {
     "zb_embedding": (c_i, [c_p, c_p, c_p, c_i, c_i, c_i, c_p]),
     "zb_argmax_f32": (c_i, [c_p, c_p, c_i, c_i, c_ll, c_p]),
     "zb_topk_sample": (c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_f, c_ull, c_ull, c_p]),
+    "zb_topk_sample_rng": (c_i, [c_p, c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_f, c_ull, c_ull, c_p, c_p]),
+    "zb_u64_add": (c_i, [c_p, c_ull, c_p]),
+    "zb_decode_advance_rng": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p, c_p]),
     "zb_decode_plan_splits": (c_i, [c_i, c_i, c_i, c_i]),
     "zb_decode_scratch_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "zb_paged_decode": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_ll, c_f,

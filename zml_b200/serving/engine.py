@@ -130,6 +130,9 @@ class Engine:
         self.d_bt = torch.zeros((mb, self.max_pages), **i32)
         self.d_hist = torch.zeros((history_steps, mb), **i32)
         self.d_step = torch.zeros(1, **i32)
+        # {seed, draws so far} of the top-k sampler: on the device, so that a replayed decode graph draws fresh
+        # noise at every step and follows the seed of the current request
+        self.d_rng = torch.zeros(2, dtype=torch.int64, device=self.device)
         # recurrent-state slots (models with per-sequence state besides KV pages); the last slot is a
         # scratch row for padding rows of a batch bucket and for graph warm-up passes
         self.num_slots = 2 * mb
@@ -142,6 +145,11 @@ class Engine:
             model.alloc_state(self.num_slots + 1)
 
     # ------------------------------------------------------------------ helpers
+    def set_seed(self, seed: int) -> None:
+        """Seed of the sampler for what follows; restarts its draw counter."""
+        self.seed = int(seed)
+        self.d_rng.copy_(torch.tensor([self.seed, 0], dtype=torch.int64))
+
     def _pin(self, t: torch.Tensor) -> torch.Tensor:
         return t.pin_memory() if self.on_gpu else t
 
@@ -220,7 +228,9 @@ class Engine:
                         logits_rows=meta_d[3 * nb + 1:] if rows else None, q_start_host=list(qs),
                         state_slots=meta_d[2 * nb + 1:3 * nb + 1] if self.stateful else None)
         if rows:
-            toks = self.model.forward(dev[0], meta, self.kv_cache, strategy, self.seed, 0)
+            toks = self.model.forward(dev[0], meta, self.kv_cache, strategy, self.seed, 0, rng=self.d_rng)
+            if strategy is not None and strategy.topk > 1:
+                ops.advance_rng(self.d_rng)
         else:
             self.model.hidden_states(dev[0], meta, self.kv_cache)
             toks = None
@@ -234,16 +244,17 @@ class Engine:
                         num_splits=num_splits, max_seq_len=max_seq_len,
                         q_start=self.d_qs[:b + 1] if self.stateful else None,
                         state_slots=self.d_sslot[:b] if self.stateful else None)
-        toks = self.model.forward(self.d_ids[:b], meta, self.kv_cache, strategy, self.seed, 0)
+        toks = self.model.forward(self.d_ids[:b], meta, self.kv_cache, strategy, self.seed, 0, rng=self.d_rng)
         from ..ops import baseline as _baseline
         if self.on_gpu and not _baseline.enabled():
-            rc = _lib.lib().zb_decode_advance(
+            rc = _lib.lib().zb_decode_advance_rng(
                 toks.data_ptr(), self.d_ids.data_ptr(), self.d_pos.data_ptr(), self.d_seq.data_ptr(),
                 self.d_slot.data_ptr(), self.d_bt.data_ptr(), self.d_hist.data_ptr(),
                 self.d_step.data_ptr(), b, self.max_pages, self.page_size, self.d_hist.shape[1],
-                self.d_hist.shape[0], _lib.stream_ptr())
+                self.d_hist.shape[0], self.d_rng.data_ptr(), _lib.stream_ptr())
             _lib.check(rc, "zb_decode_advance")
         else:
+            self.d_rng[1] += 1
             self.d_ids[:b] = toks
             self.d_pos[:b] += 1
             self.d_seq[:b] = self.d_pos[:b] + 1
@@ -264,7 +275,7 @@ class Engine:
         if g is None:
             # warm up on a side stream (lazy kernel attributes, allocator), then capture
             saved = [t.clone() for t in (self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist,
-                                         self.d_sslot)]
+                                         self.d_sslot, self.d_rng)]
             self.d_sslot.fill_(self.scratch_slot)    # the warm-up pass must not advance any real recurrent state
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
@@ -280,7 +291,7 @@ class Engine:
             # the warm-up and capture passes must not count as decode steps: restore the state
             # (the warm-up really ran; the capture pass did not execute anything)
             for dst, src in zip((self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist,
-                                 self.d_sslot), saved):
+                                 self.d_sslot, self.d_rng), saved):
                 dst.copy_(src)
             # the warm-up wrote one KV row per sequence at the slot of the next position; the
             # real step writes the same slot with the real values, so nothing needs undoing
@@ -297,7 +308,7 @@ class Engine:
         memory, generated ids come back device -> host in blocks of `sync_interval` steps.
         Returns (outputs, stats); stats times are device times (CUDA events)."""
         strategy = strategy or SamplingStrategy()
-        self.seed = seed
+        self.set_seed(seed)
         stats = GenerationStats()
         if len(prompts) > self.max_batch:
             raise ValueError(f"{len(prompts)} prompts exceed max_batch={self.max_batch}")
@@ -421,7 +432,7 @@ class Session:
         if engine.stateful:
             self.req.slot = engine.slot_free.pop()
         self._next: Optional[int] = None
-        engine.seed = seed
+        engine.set_seed(seed)
 
     def close(self) -> None:
         self.engine.release(self.req)

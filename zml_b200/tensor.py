@@ -31,6 +31,20 @@ def _torch_dtype(dt) -> torch.dtype:
     return DataType.parse(dt).to_torch()
 
 
+
+def _kernel_gemm_ok(ap: torch.Tensor, bp: torch.Tensor, batch_dims) -> bool:
+    """True when a contraction can run on the library's bf16 GEMM kernel: CUDA, bf16 x bf16, no batch
+    axes, and extents the kernel's 16-byte alignment rules accept."""
+    if batch_dims or not ap.is_cuda or ap.dtype != torch.bfloat16 or bp.dtype != torch.bfloat16:
+        return False
+    m, k = ap.shape[-2], ap.shape[-1]
+    n = bp.shape[-1]
+    if m == 0 or n == 0 or k % 8 != 0 or n % 8 != 0:
+        return False
+    from .ops import _lib
+    return _lib.available()
+
+
 class Rng:
     """Counter-based random state threaded through model code (zml/tensor.zig:667-921).
 
@@ -473,6 +487,12 @@ class Tensor:
         bp = b.permute(bb + cb + fb).reshape(*bs, math.prod([b.shape[i] for i in cb]), math.prod([b.shape[i] for i in fb]))
         if a.dtype in (torch.bfloat16, torch.float16) and not a.is_cuda:
             out = torch.matmul(ap.float(), bp.float()).to(a.dtype)
+        elif _kernel_gemm_ok(ap, bp, bs):
+            # CUDA bf16 without batch axes: the library's tcgen05 GEMM on K-major operands (the common
+            # activation x weight[dout, d] case needs no copy: the weight already is [N, K])
+            from . import ops as _ops
+            bt = b.permute(fb + cb).reshape(bp.shape[-1], bp.shape[-2])
+            out = _ops.gemm(ap if ap.stride(-1) == 1 else ap.contiguous(), bt if bt.stride(-1) == 1 else bt.contiguous())
         else:
             out = torch.matmul(ap, bp.to(ap.dtype))
         out = out.reshape(*bs, *[a.shape[i] for i in fa], *[b.shape[i] for i in fb])
