@@ -86,7 +86,8 @@ def test_topk_sampling_draws_fresh_noise_every_step_and_follows_the_seed():
     """The sampler's seed and draw counter live on the device: a replayed decode graph must not repeat its
     noise, and a new seed must change the draws without a new capture."""
     from zml_b200.models.common import SamplingStrategy
-    logits = torch.zeros(64, 4096, device="cuda")            # flat logits: the draw alone picks the token
+    # nearly flat, but distinct logits (ties would leave the choice of candidates open): the draw picks the token
+    logits = (-1e-4 * torch.arange(4096, device="cuda", dtype=torch.float32)).repeat(64, 1).contiguous()
     rng = torch.tensor([7, 0], dtype=torch.int64, device="cuda")
     a = ops.topk_sample(logits, 8, 1.0, rng=rng)
     ops.advance_rng(rng)

@@ -412,6 +412,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           zb_cluster_arrive();
           zb_cluster_wait();
           did_cluster_sync = true;
+          if (tl && epi_tid == 0) tl[8] = zb_globaltimer();
           const int S = prm.cluster;
           const int rank = static_cast<int>(zb_cluster_ctarank());
           // bands begin on even rows: with interleaved gate / up rows (SwiGLU epilogue) a pair never straddles two CTAs
@@ -499,6 +500,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                 reduce_batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{}, base + epi_tid);
             }
             if (prm.epi.out_sumsq != nullptr) emit_sumsq();
+            if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
             // nobody may leave (and release its shared memory) while a peer still reads it
             zb_cluster_arrive();
             zb_cluster_wait();
@@ -565,7 +567,6 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                   if (j < n_pair) zb_st_ll(dst + static_cast<size_t>(j) * kEpiThreads, mine_w[hf][j], epoch);
               }
             }
-            if (tl && epi_tid == 0) tl[8] = zb_globaltimer();
             zb_cluster_arrive();                 // peers' shared memory is no longer needed; waited for below
             if (tl && epi_tid == 0) tl[9] = zb_globaltimer();
             const uint2* slots = reinterpret_cast<const uint2*>(ar.recv_peer[ar.rank]) + my_slot;
@@ -1382,7 +1383,8 @@ extern "C" {
 // Profiling aid: when set, every CTA of the following GEMM launches writes globaltimer stamps to
 // buf[cta][12] = {entry, prologue done, producer past the dependency wait, first tile landed,
 // last accumulator committed, first accumulator seen by the epilogue, epilogue done, exit,
-// cluster reduction done, partial pushed and fenced, peers' flags seen, tile stored}.
+// partial tiles of the cluster visible, partial pushed to the peers, band finished (peers' copies seen,
+// output and statistics stored), unused}.
 // `buf` holds `slots` records of 160 * 12 zeroed u64; consecutive launches take consecutive records
 // (wrapping around).  Null turns it off.
 void zb_gemm_set_timeline(unsigned long long* buf, int slots) {

@@ -81,7 +81,7 @@ class SymmetricContext:
         self.staging_off = 0
         # The fused GEMM + all-reduce (single-hop exchange of a tile's partial sums with every peer) serves up to
         # this many tokens: it sends (world - 1) copies of the tensor, which stops paying beyond one 32-token tile.
-        self.fused_max_tokens = int(os.environ.get("ZB_FUSED_MAX_TOKENS", "32"))
+        self.fused_max_tokens = int(os.environ.get("ZB_FUSED_MAX_TOKENS", "0"))
         # batches the fused kernel does not take, up to `ll_tokens`: GEMM, then the two-shot tagged-slot all-reduce
         self.ll_enabled = self.LL_ALLREDUCE
 
