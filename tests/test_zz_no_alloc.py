@@ -40,9 +40,9 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
     torch.manual_seed(0)
     dev = "cuda"
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-    # a decode-shaped problem (K split across CTAs -> partial tiles go through the scratch),
+    # a decode-shaped problem whose tiles are cut along K across CTAs (partial tiles go through the scratch),
     # then a different shape right after it: the array still holds the first call's pieces
-    for (m, n, k) in [(32, 4096, 4096), (48, 1024, 14336)]:
+    for (m, n, k) in [(32, 28672, 4096), (48, 1024, 14336)]:
         a = (torch.randn(m, k, device=dev) * 0.5).bfloat16()
         w = (torch.randn(n, k, device=dev) / k ** 0.5).bfloat16()
         res = torch.randn(m, n, device=dev).bfloat16()

@@ -120,6 +120,34 @@ def main():
     elif comm.rank == 0:
         print("no multicast address: multimem all-reduce not exercised", flush=True)
 
+    # prefill collectives overlapped band by band: row-parallel GEMM announcing bands of partial sums, then the
+    # column-parallel GEMM that reduces them inside NVSwitch on a few CTAs and multiplies the rest, vs the same
+    # chain with an NCCL all-reduce; repeated (the flags carry a launch counter) and with the SwiGLU epilogue
+    if ctx.has_multicast:
+        for it, (t, kp, n2, swi) in enumerate([(700, 512, 768, False), (1024, 256, 1024, True), (300, 1024, 512, False),
+                                               (700, 512, 768, False)]):
+            assert ctx.can_band(t, hidden)
+            a = (torch.randn(t, kp, device=dev) * 0.5).bfloat16()
+            wo = (torch.randn(hidden, kp, device=dev) / math.sqrt(kp)).bfloat16()
+            w2 = (torch.randn(n2, hidden, device=dev) / math.sqrt(hidden)).bfloat16()
+            dist.broadcast(w2, 0)
+            res = torch.randn(t, hidden, device=dev).bfloat16()
+            dist.broadcast(res, 0)
+            part = (a.float() @ wo.float().t()).bfloat16().float()
+            dist.all_reduce(part)
+            x_ref = (part + res.float()).bfloat16()
+            normed = x_ref.float() * torch.rsqrt(x_ref.float().pow(2).mean(-1, keepdim=True) + 1e-5)
+            want = normed @ w2.float().t()
+            if swi:
+                want = torch.nn.functional.silu(want[:, : n2 // 2]) * want[:, n2 // 2:]
+            ctx.band_producer(a, wo)
+            got, x = ctx.band_consumer(t, ops.interleave_gate_up(w2) if swi else w2, res, swiglu=swi, eps=1e-5)
+            expect_close(x.float(), x_ref.float(), atol=6e-2, rtol=3e-2, min_close=0.995)
+            expect_close(got.float(), want, atol=6e-2, rtol=4e-2, min_close=0.99)
+            gathered = comm.all_gather(x[None].contiguous())
+            assert all(torch.equal(gathered[0], gathered[r]) for r in range(comm.world)), ("band pipeline", t)
+        ops.raise_on_status()
+
     # mixture-of-experts combine with the expert-parallel all-reduce inside vs finalize + NCCL all-reduce
     from zml_b200 import moe
     cctx = SymmetricContext.create(comm, 512, max_tokens=64, combine_tokens=64)
@@ -148,14 +176,14 @@ def main():
     cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], hidden_size=512, num_attention_heads=8,
                                    num_key_value_heads=8 if comm.world > 2 else 2, intermediate_size=1024))
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(7)).tolist()
-               for n in (33, 70, 129)]
+               for n in (33, 300, 129)]
     hid, toks = {}, {}
     for mode, c in (("nccl", comm), ("fused", comm), ("single", single)):
         model = LlamaModel(cfg, c, device=dev).init_random(seed=5, std=0.05)
         if mode == "fused":
             comm.fused = SymmetricContext.create(comm, cfg.hidden_size, max_tokens=512)
         hid[mode] = hidden_after_prefill_and_decode(model, prompts)
-        toks[mode], _ = Engine(model, num_pages=32, page_size=64, max_batch=4, max_seq_len=512).generate(prompts, 12)
+        toks[mode], _ = Engine(model, num_pages=48, page_size=64, max_batch=4, max_seq_len=512).generate(prompts, 12)
         if mode == "fused":
             comm.fused.close()
             comm.fused = None

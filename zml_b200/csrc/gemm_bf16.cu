@@ -61,6 +61,7 @@ struct GemmParams {
   uint32_t* counters;  // one per output tile, zero between launches
   ZbStatus* status;
   ZbGemmEpi epi;       // row scale / SwiGLU / sum-of-squares / next-weight prefetch (host_api.h)
+  ZbBandPipe band;     // prefill collectives overlapped band by band (host_api.h)
   ZbFusedAr ar;        // used by the fused GEMM + all-reduce variant only
 };
 
@@ -117,9 +118,14 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // Large problems: whole tiles are dealt round-robin (CTAs running at the same time work on
   // neighbouring tiles and share operands in L2); a CTA's "virtual" tiles are then contiguous
   // and map to actual tile (v % rr_tiles) * grid + cta.  Small problems: stream-K ranges.
+  // band pipeline, consumer side: the first comm_ctas CTAs reduce and broadcast, the rest share the tiles
+  const int cta_off = prm.band.mode == 2 ? prm.band.comm_ctas : 0;
+  const int cta_id = static_cast<int>(blockIdx.x) - cta_off;
+  const int n_ctas = static_cast<int>(gridDim.x) - cta_off;
+  const bool comm_cta = cta_id < 0;
   const long long total_units =
-      static_cast<long long>(prm.rr_tiles > 0 ? static_cast<int>(gridDim.x) * prm.rr_tiles : num_out_tiles) * kb_total;
-  long long u_begin = min(total_units, static_cast<long long>(blockIdx.x) * prm.units_per_cta);
+      comm_cta ? 0 : static_cast<long long>(prm.rr_tiles > 0 ? n_ctas * prm.rr_tiles : num_out_tiles) * kb_total;
+  long long u_begin = min(total_units, static_cast<long long>(comm_cta ? 0 : cta_id) * prm.units_per_cta);
   long long u_end = min(total_units, u_begin + prm.units_per_cta);
   if (prm.cluster > 1) {
     // cluster split-K: CTA (tile, rank) takes k-blocks [rank * upc, (rank + 1) * upc) of its tile
@@ -171,7 +177,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         const int v = static_cast<int>(u / kb_total);
         const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
         const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
-        const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles : v;
+        const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * n_ctas + v / prm.rr_tiles : v;
         u += kb1 - kb0;
         if (t >= num_out_tiles) continue;
         int pt, qt;
@@ -213,31 +219,121 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       // per-token scale of the accumulators (tokens are the tile's columns; a swap-AB problem has one column
       // tile): computed here, while the main loop runs, from the partial sums the producing kernel left
       if (prm.epi.in_sumsq != nullptr) {
-        for (int t = threadIdx.x - 64; t < BN; t += kEpiThreads) {
-          float s4[4] = {0.f, 0.f, 0.f, 0.f};
+        // kEpiThreads / BN threads share a token (one thread takes 128 / ... tokens when BN > 128); a thread sums
+        // every TPT-th part with 8 loads in flight, the TPT sums of a token are added in a fixed order
+        constexpr int TPT = BN >= kEpiThreads ? 1 : kEpiThreads / BN;      // threads per token
+        float* part_sums = scale_tab + 128;                                 // [TPT][BN] = 128 floats, used when BN < 128
+        const int et = threadIdx.x - 64;
+        for (int t0 = 0; t0 < BN; t0 += kEpiThreads) {
+          const int t = t0 + (et % (BN < kEpiThreads ? BN : kEpiThreads));
+          const int sub = BN < kEpiThreads ? et / BN : 0;
+          float acc = 0.f;
           if (t < prm.rows_q) {
             const float* src = prm.epi.in_sumsq + t;
-            int i = 0;
-            for (; i + 4 <= prm.epi.in_parts; i += 4) {
+            int i = sub;
+            for (; i + 7 * TPT < prm.epi.in_parts; i += 8 * TPT) {
+              float v[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) s4[j] += __ldcg(src + static_cast<size_t>(i + j) * prm.epi.in_ld);
+              for (int j = 0; j < 8; ++j) v[j] = __ldcg(src + static_cast<size_t>(i + j * TPT) * prm.epi.in_ld);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc += v[j];
             }
-            for (; i < prm.epi.in_parts; ++i) s4[0] += __ldcg(src + static_cast<size_t>(i) * prm.epi.in_ld);
+            for (; i < prm.epi.in_parts; i += TPT) acc += __ldcg(src + static_cast<size_t>(i) * prm.epi.in_ld);
           }
-          scale_tab[t] = rsqrtf(((s4[0] + s4[1]) + (s4[2] + s4[3])) * prm.epi.in_inv_d + prm.epi.in_eps);
+          if constexpr (TPT == 1) {
+            scale_tab[t] = rsqrtf(acc * prm.epi.in_inv_d + prm.epi.in_eps);
+          } else {
+            part_sums[sub * BN + t] = acc;
+            epi_bar_sync();
+            if (et < BN) {
+              float tot = 0.f;
+#pragma unroll
+              for (int j = 0; j < TPT; ++j) tot += part_sums[j * BN + et];
+              scale_tab[et] = rsqrtf(tot * prm.epi.in_inv_d + prm.epi.in_eps);
+            }
+          }
         }
         epi_bar_sync();
       }
     }
   }
 
-  if (warp == 0) {
+  if (comm_cta) {
+    // ------------------------------------------ band pipeline: reduce + broadcast CTA (no tensor-core work)
+    // Every band this rank owns: wait for the partial sums of all ranks, pull their sum through the multicast
+    // address (NVSwitch adds the copies up), add the residual, push the new residual stream and its row
+    // statistics to every rank, then tell every rank that the band is done.  A row is one warp's work.
+    zb_pdl_wait();
+    const ZbBandPipe& bp = prm.band;
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(bp.epoch);
+    const int W = bp.world;
+    const int vec_per_row = bp.d >> 3;
+    constexpr int kWarps = kNumThreads / 32;
+    constexpr int kU = 16;                      // 16-byte loads in flight per lane
+    for (int b = bp.rank; b < bp.num_bands; b += W) {
+      if (static_cast<int>(threadIdx.x) < W) {
+        if (!zb_wait_flag(bp.ready_peer[bp.rank] + static_cast<size_t>(b) * 8 + threadIdx.x, epoch, abort_flag))
+          *abort_where = 300u + threadIdx.x;
+      }
+      __syncthreads();
+      if (*abort_flag != 0u) break;
+      const int row0 = b * kBlockP;
+      const int rows = min(kBlockP, bp.tokens - row0);
+      for (int r = static_cast<int>(blockIdx.x) * kWarps + warp; r < rows; r += bp.comm_ctas * kWarps) {
+        const size_t row = static_cast<size_t>(row0 + r);
+        const size_t row_bytes = row * static_cast<size_t>(bp.d) * 2;
+        const uint4* res_row = bp.residual != nullptr ? reinterpret_cast<const uint4*>(bp.residual + row * bp.d) : nullptr;
+        float ss = 0.f;
+        for (int v0 = lane; v0 < vec_per_row; v0 += 32 * kU) {
+          uint4 x[kU], rs[kU];
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            const int v = v0 + u * 32;
+            if (v < vec_per_row) {
+              x[u] = zb_multimem_ld_reduce_bf16x8(bp.mc + bp.part_off + row_bytes + static_cast<size_t>(v) * 16);
+              rs[u] = res_row != nullptr ? res_row[v] : make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            const int v = v0 + u * 32;
+            if (v < vec_per_row) {
+              const uint32_t a[4] = {x[u].x, x[u].y, x[u].z, x[u].w}, c[4] = {rs[u].x, rs[u].y, rs[u].z, rs[u].w};
+              uint32_t o[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float2 fa = zb_unpack_bf16x2(a[q]), fc = zb_unpack_bf16x2(c[q]);
+                o[q] = zb_pack_bf16x2(fa.x + fc.x, fa.y + fc.y);
+                const float2 fo = zb_unpack_bf16x2(o[q]);       // statistics of what is stored
+                ss += fo.x * fo.x + fo.y * fo.y;
+              }
+              zb_multimem_st_16(bp.mc + bp.x_off + row_bytes + static_cast<size_t>(v) * 16, make_uint4(o[0], o[1], o[2], o[3]));
+            }
+          }
+        }
+        ss = zb_warp_sum(ss);
+        if (lane < W) bp.sumsq_peer[lane][row] = ss;
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t prev = atomicAdd(&bp.count_c[b], 1u);
+        if (prev == static_cast<uint32_t>(bp.comm_ctas - 1)) {
+          bp.count_c[b] = 0u;
+          __threadfence_system();
+          for (int r = 0; r < W; ++r) zb_st_release_sys(bp.done_peer[r] + b, epoch);
+        }
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       zb_tma_prefetch_desc(&tmap_p);
       zb_tma_prefetch_desc(&tmap_q);
       zb_pdl_wait();
       if (tl) tl[2] = zb_globaltimer();
+      const uint32_t band_epoch = prm.band.mode == 2 ? *reinterpret_cast<volatile uint32_t*>(prm.band.epoch) : 0u;
+      int band_seen = -1;                     // band pipeline: last band whose done flag this producer has seen
       uint32_t stage = 0, phase = 0;
       int issued = 0;
       bool ok = true;
@@ -245,13 +341,25 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         const int v = static_cast<int>(u / kb_total);
         const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
         const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
-        const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles : v;
+        const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * n_ctas + v / prm.rr_tiles : v;
         if (t >= num_out_tiles) {
           u += kb1 - kb0;
           continue;
         }
         int pt, qt;
         decode(t, pt, qt);
+        if constexpr (!SWAP) {
+          if (prm.band.mode == 2 && pt != band_seen) {
+            // the rows of this tile are band `pt` of the reduced activation: wait until its owner has written it here
+            if (!zb_wait_flag(prm.band.done_peer[prm.band.rank] + pt, band_epoch, abort_flag)) {
+              *abort_where = 400u;
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");      // the copies below go through the async proxy
+            band_seen = pt;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb, ++issued) {
           uint8_t* sa = smem + stage * kStageBytes;
           uint8_t* sb = sa + kTileABytes;
@@ -308,7 +416,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         const int kb0 = static_cast<int>(u - static_cast<long long>(v) * kb_total);
         const int kb1 = static_cast<int>(min(static_cast<long long>(kb_total), kb0 + (u_end - u)));
         u += kb1 - kb0;
-        if (prm.rr_tiles > 0 && (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles >= num_out_tiles) continue;
+        if (prm.rr_tiles > 0 && (v % prm.rr_tiles) * n_ctas + v / prm.rr_tiles >= num_out_tiles) continue;
         if (!zb_mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) break;
         zb_tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -365,7 +473,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const bool partial = !(kb0 == 0 && kb1 == kb_total);
       const int my_slot = (u == u_begin) ? 0 : 1;
       u += kb1 - kb0;
-      const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * static_cast<int>(gridDim.x) + v / prm.rr_tiles : v;
+      const int t = prm.rr_tiles > 0 ? (v % prm.rr_tiles) * n_ctas + v / prm.rr_tiles : v;
       if (t >= num_out_tiles) continue;
       int pt, qt;
       decode(t, pt, qt);
@@ -374,15 +482,24 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const int first_cta = static_cast<int>(t_begin / prm.units_per_cta);
       const int last_cta = static_cast<int>((t_begin + kb_total - 1) / prm.units_per_cta);
       float row_scale = 1.f;       // !SWAP: tokens are the tile's rows, this thread owns one
+      auto load_row_scale = [&]() {
+        const int pr = min(pt * kBlockP + row_in_tile, prm.rows_p - 1);
+        float ssum = 0.f;
+        for (int i = 0; i < prm.epi.in_parts; ++i) ssum += __ldcg(prm.epi.in_sumsq + static_cast<size_t>(i) * prm.epi.in_ld + pr);
+        row_scale = rsqrtf(ssum * prm.epi.in_inv_d + prm.epi.in_eps);
+      };
       if constexpr (!SWAP) {
-        if (prm.epi.in_sumsq != nullptr) {
-          const int pr = min(pt * kBlockP + row_in_tile, prm.rows_p - 1);
-          float ssum = 0.f;
-          for (int i = 0; i < prm.epi.in_parts; ++i) ssum += __ldcg(prm.epi.in_sumsq + static_cast<size_t>(i) * prm.epi.in_ld + pr);
-          row_scale = rsqrtf(ssum * prm.epi.in_inv_d + prm.epi.in_eps);
-        }
+        // ahead of the wait for the accumulator, unless the statistics arrive with the band (band pipeline)
+        if (prm.epi.in_sumsq != nullptr && prm.band.mode != 2) load_row_scale();
       }
       zb_mbar_wait(&tmem_full[acc], acc_phase, abort_flag);
+      if constexpr (!SWAP) {
+        if (prm.epi.in_sumsq != nullptr && prm.band.mode == 2) {
+          // the band's rows were loaded, so its done flag is set: acquire it, then read the statistics its owner wrote
+          (void)zb_ld_acquire_sys(prm.band.done_peer[prm.band.rank] + pt);
+          load_row_scale();
+        }
+      }
       if (tl && epi_tid == 0 && tl[5] == 0ull) tl[5] = zb_globaltimer();
       epi_bar_sync();
       if (*abort_flag != 0u) break;
@@ -960,6 +1077,23 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) epilogue_chunk(c0);
         }
+        if constexpr (!SWAP) {
+          if (prm.band.mode == 1) {
+            // band pipeline, producer side: count the stored tiles of the band; the CTA that stores the last
+            // one tells the band's owner that this rank's partial sums of the band are complete
+            __threadfence_system();
+            epi_bar_sync();
+            if (epi_tid == 0) {
+              const uint32_t prev = atomicAdd(&prm.band.count_p[pt], 1u);
+              if (prev == static_cast<uint32_t>(prm.band.tiles_per_band - 1)) {
+                prm.band.count_p[pt] = 0u;
+                __threadfence_system();
+                const uint32_t ep = *reinterpret_cast<volatile uint32_t*>(prm.band.epoch);
+                zb_st_release_sys(prm.band.ready_peer[pt % prm.band.world] + static_cast<size_t>(pt) * 8 + prm.band.rank, ep);
+              }
+            }
+          }
+        }
       } else if (SWAP && BN <= 64 && prm.ar.one_shot != 0) {
         if (do_store) {
           // single-hop all-reduce of a tile (few tokens)
@@ -1135,6 +1269,16 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // ------------------------------------------------------------ common exit
   zb_tc_fence_before();
   __syncthreads();
+  if (prm.band.mode == 2 && threadIdx.x == 0) {
+    // band pipeline: every wait of this launch is over once all CTAs are here; the last one opens the next epoch
+    __threadfence();
+    const uint32_t ticket = atomicAdd(prm.band.epoch + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      prm.band.epoch[1] = 0u;
+      const uint32_t e = *reinterpret_cast<volatile uint32_t*>(prm.band.epoch);
+      *reinterpret_cast<volatile uint32_t*>(prm.band.epoch) = e + 1u;
+    }
+  }
   if (*abort_flag != 0u) {
     if (threadIdx.x == 0)
       zb_record_error(prm.status, *abort_where >= 100u ? ZB_ERR_FLAG_TIMEOUT : ZB_ERR_MBAR_TIMEOUT,
@@ -1341,13 +1485,25 @@ int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* u
       best_ctas = ctas;
     }
   }
-  // Under half of the SMs busy: stream-K (all SMs stream) does better - unless the whole problem is a few
-  // k-blocks (a router or a small head: 1 - 2 tiles), where the few CTAs are the same either way and the
-  // cluster reduction through shared memory replaces the fix-up through global memory.
-  const bool tiny = allow_tiny && static_cast<long long>(tiles) * kb_total <= 64;
-  if (best == 1 || (best_ctas * 2 < num_sms && !tiny)) return 1;
+  if (best == 1) return 1;
+  (void)allow_tiny;
+  // Few CTAs stream less than the whole machine, but the stream-K plan pays for using every SM with a fix-up
+  // that grows with the pieces per tile (measured inside a decoder layer: 12 us for 16 pieces of a 32-token
+  // tile, against 2.5 us for the cluster reduction through shared memory).  Estimated time of either plan:
+  // k-blocks per CTA x stage bytes / min(what one SM can pull, its share of the HBM bandwidth) + the tail.
+  const double stage_b = static_cast<double>((kBlockP + bn) * kBlockK * 2);
+  auto stream_us = [&](int ctas, int kbs) {
+    const double per_sm_gbs = 50.0, hbm_gbs = 6500.0;
+    const double rate = per_sm_gbs < hbm_gbs / ctas ? per_sm_gbs : hbm_gbs / ctas;       // GB/s = 1000 bytes per us
+    return kbs * stage_b / (rate * 1000.0);
+  };
+  const int c_upc = (kb_total + best - 1) / best;
+  const double t_cluster = stream_us(best_ctas, c_upc) + 2.5;
+  const int pieces = (kb_total + *upc - 1) / *upc + 1;
+  const double t_streamk = stream_us(*grid, *upc) + (kb_total > *upc ? 2.0 + 0.6 * pieces : 0.0);
+  if (t_cluster >= t_streamk) return 1;
   *grid = best_ctas;
-  *upc = (kb_total + best - 1) / best;
+  *upc = c_upc;
   return best;
 }
 
@@ -1483,7 +1639,8 @@ int check_epi(const ZbGemmEpi* epi, int m, int n, int ldo, int out_f32, const vo
 int gemm_impl(const void* a, const void* w, void* out, const void* residual, const void* bias,
               int m, int n, int k, int lda, int ldw, int ldo, int out_f32, int split_hint,
               float* scratch, size_t scratch_bytes, uint32_t* counters, int counters_len,
-              ZbStatus* status, int num_sms, const ZbGemmEpi* epi, int* out_parts, cudaStream_t stream) {
+              ZbStatus* status, int num_sms, const ZbGemmEpi* epi, int* out_parts, cudaStream_t stream,
+              const ZbBandPipe* band = nullptr) {
   if (out_parts) *out_parts = 0;
   if (m <= 0 || n <= 0 || k <= 0) return 0;
   if ((k % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0) return -10;
@@ -1496,9 +1653,24 @@ int gemm_impl(const void* a, const void* w, void* out, const void* residual, con
   const int tiles = zb_gemm_plan(m, n, k, num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
   int cluster = 1;
   if (sw && rr == 0 && split_hint <= 0) cluster = plan_cluster(bn, tiles, (k + kBlockK - 1) / kBlockK, num_sms, &grid, &upc);
-  if (cluster == 1 && static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > scratch_bytes) return -13;
+  if (band != nullptr && band->mode != 0) {
+    // band pipeline: whole tiles only (a band is complete when its column tiles are), tokens as rows, and on the
+    // consumer side the first comm_ctas CTAs of the grid do the reduction instead of tiles
+    if (sw || cluster > 1) return -70;
+    const int workers = num_sms - (band->mode == 2 ? band->comm_ctas : 0);
+    if (workers < 1) return -70;
+    rr = (tiles + workers - 1) / workers;
+    grid = num_sms;
+    upc = rr * ((k + kBlockK - 1) / kBlockK);
+  }
+  if (cluster == 1 && rr == 0 && static_cast<size_t>(grid) * 2 * bn * kBlockP * sizeof(float) > scratch_bytes) return -13;
   if (tiles > counters_len) return -14;
   GemmParams prm;
+  prm.band = ZbBandPipe{};
+  if (band != nullptr) {
+    prm.band = *band;
+    prm.band.tiles_per_band = (n + bn - 1) / bn;
+  }
   prm.cluster = cluster;
   prm.rows_p = sw ? n : m;
   prm.rows_q = sw ? m : n;
@@ -1511,7 +1683,7 @@ int gemm_impl(const void* a, const void* w, void* out, const void* residual, con
   prm.flags = static_w;
   prm.l2_prefetch = l2_prefetch_tiles(sw, bn, grid, rr);
   prm.timeline = next_timeline(grid);
-  prm.group_p = 16;
+  prm.group_p = (band != nullptr && band->mode != 0) ? 8 : 16;     // band pipeline: bands finish (and start) in groups of 8
   prm.units_per_cta = upc;
   prm.rr_tiles = rr;
   prm.workspace = scratch;
@@ -1643,6 +1815,74 @@ int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, 
                          reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Prefill collectives overlapped band by band (ZbBandPipe in host_api.h).  All ranks call both modes with the same
+// shapes, in the same order, producer first.
+//   mode 1: part[tokens, d] (at part_off of this rank's heap) = a[tokens, k] * w[d, k]^T; bands of 128 tokens are
+//           announced to their owners as their last column tile is stored.
+//   mode 2: out[tokens, n] = f(x[tokens, d]) * w[n, d]^T (+ bias) where x (at x_off of every heap) = residual +
+//           sum over ranks of part, reduced inside NVSwitch and written to every rank by the first `comm_ctas` CTAs
+//           of this launch while the other CTAs multiply the bands that are already there; f is the RMSNorm
+//           scale of the row (statistics travel with the band; eps < 0: none); `swiglu` as in zb_gemm_bf16_epi.
+// `flag_off` addresses the pipeline's flag region in every heap, laid out for `nb_cap` bands:
+// ready [nb_cap][8] u32 | done [nb_cap] | producer counts [nb_cap] | consumer counts [nb_cap] | row statistics
+// [nb_cap * 128] fp32 (256-byte aligned).  Needs a context with a multicast address and tokens > 256.
+size_t zb_band_flag_bytes(int nb_cap) {
+  return ((static_cast<size_t>(nb_cap) * 44 + 255) / 256) * 256 + static_cast<size_t>(nb_cap) * 128 * 4;
+}
+
+int zb_gemm_band(const ZbArContext* ctx, int mode, const void* a, const void* w, void* out, const void* bias,
+                 const void* residual, int tokens, int n, int k, int lda, int ldw, int ldo, size_t part_off, size_t x_off,
+                 size_t flag_off, int nb_cap, int comm_ctas, int swiglu, float eps, void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (st == nullptr || ctx == nullptr) return -20;
+  if (ctx->mc_heap == nullptr) return -69;
+  if (mode != 1 && mode != 2) return -10;
+  const int nb = (tokens + kBlockP - 1) / kBlockP;
+  if (tokens <= 256 || nb > nb_cap || (part_off % 16) != 0 || (x_off % 16) != 0 || (flag_off % 256) != 0) return -70;
+  if (mode == 2 && (comm_ctas < 1 || comm_ctas >= st->num_sms)) return -70;
+  ZbBandPipe bp = {};
+  bp.mode = mode;
+  bp.num_bands = nb;
+  bp.comm_ctas = comm_ctas;
+  bp.world = ctx->world;
+  bp.rank = ctx->rank;
+  bp.tokens = tokens;
+  bp.d = mode == 1 ? n : k;
+  bp.epoch = ctx->epoch + 10;
+  const size_t stats_off = ((static_cast<size_t>(nb_cap) * 44 + 255) / 256) * 256;
+  for (int r = 0; r < ctx->world; ++r) {
+    char* base = reinterpret_cast<char*>(ctx->heap[r]) + flag_off;
+    bp.ready_peer[r] = reinterpret_cast<uint32_t*>(base);
+    bp.done_peer[r] = reinterpret_cast<uint32_t*>(base + static_cast<size_t>(nb_cap) * 32);
+    bp.sumsq_peer[r] = reinterpret_cast<float*>(base + stats_off);
+  }
+  char* mine = reinterpret_cast<char*>(ctx->heap[ctx->rank]);
+  bp.count_p = reinterpret_cast<uint32_t*>(mine + flag_off + static_cast<size_t>(nb_cap) * 36);
+  bp.count_c = reinterpret_cast<uint32_t*>(mine + flag_off + static_cast<size_t>(nb_cap) * 40);
+  bp.mc = reinterpret_cast<char*>(ctx->mc_heap);
+  bp.part_off = part_off;
+  bp.x_off = x_off;
+  bp.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (mode == 1) {
+    // `w` is a parameter (flag bit 1): its tiles may be requested before the preceding kernel has finished
+    return gemm_impl(a, w, mine + part_off, nullptr, nullptr, tokens, n, k, lda, ldw, n, 2, 0, st->gemm_scratch,
+                     st->gemm_scratch_bytes, st->gemm_counters, st->gemm_counters_len, st->status, st->num_sms, nullptr, nullptr,
+                     s, &bp);
+  }
+  ZbGemmEpi epi = {};
+  if (eps >= 0.f) {
+    epi.in_sumsq = bp.sumsq_peer[ctx->rank];
+    epi.in_parts = 1;
+    epi.in_ld = tokens;
+    epi.in_inv_d = 1.0f / static_cast<float>(k);
+    epi.in_eps = eps;
+  }
+  epi.swiglu = swiglu ? 1 : 0;
+  return gemm_impl(mine + x_off, w, out, nullptr, bias, tokens, n, k, k, ldw, ldo, 2, 0, st->gemm_scratch, st->gemm_scratch_bytes,
+                   st->gemm_counters, st->gemm_counters_len, st->status, st->num_sms, &epi, nullptr, s, &bp);
+}
+
 // Row-parallel GEMM fused with the tensor-parallel all-reduce (and bias / residual):
 //   out_r = sum over ranks r' of a_r'[M,K_r'] * w_r'[N,K_r']^T (+ bias) (+ residual), on every rank.
 // `out_off` is the byte offset of the output inside every rank's symmetric heap.  All ranks
@@ -1680,6 +1920,7 @@ int zb_gemm_ar_fused_epi(const ZbArContext* ctx, const void* a, const void* w, s
     }
   }
   GemmParams prm;
+  prm.band = ZbBandPipe{};
   prm.cluster = cluster;
   prm.rows_p = sw ? n : m;
   prm.rows_q = sw ? m : n;

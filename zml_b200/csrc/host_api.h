@@ -64,6 +64,38 @@ struct ZbGemmEpi {
   int swiglu;
 };
 
+// Band pipeline of the prefill collectives (gemm_bf16.cu): the tensor-parallel all-reduce of a row-parallel
+// GEMM's output, cut into bands of 128 tokens and overlapped with the GEMM that consumes the sum.
+//   mode 1 (producer, the row-parallel GEMM): partial sums go to `part` in this rank's heap; when the last
+//     column tile of a band is stored the band's owner (band % world) is told: ready[owner][band][rank] = epoch.
+//   mode 2 (consumer, the column-parallel GEMM that follows): the first `comm_ctas` CTAs of the grid do not
+//     multiply.  For every band this rank owns they wait for the `world` ready flags, load the band through
+//     the multicast address with multimem.ld_reduce (NVSwitch returns the sum of all ranks' partial sums),
+//     add the residual, write the new residual stream and its row statistics into every rank's heap
+//     (multimem.st / peer stores) and publish done[rank'][band] = epoch on every rank.  The other CTAs run
+//     the GEMM; their TMA producer waits for done[band] before it loads the band's rows.
+// Flags carry a device-side launch counter, so nothing is reset and CUDA-graph replays need no host change.
+struct ZbBandPipe {
+  int mode;                    // 0: off
+  int num_bands;
+  int tiles_per_band;          // producer: column tiles per band
+  int comm_ctas;               // consumer
+  int world;
+  int rank;
+  int d;                       // row length of the reduced tensor (hidden size)
+  int tokens;
+  uint32_t* epoch;             // local device counter {epoch, exit ticket}
+  uint32_t* count_p;           // local [num_bands]: tiles of the band stored (producer), zero between launches
+  uint32_t* count_c;           // local [num_bands]: comm CTAs done with the band (consumer), zero between launches
+  uint32_t* ready_peer[8];     // [num_bands][8] in every rank's heap
+  uint32_t* done_peer[8];      // [num_bands] in every rank's heap
+  float* sumsq_peer[8];        // [tokens] in every rank's heap: sum of squares of the rows of the new residual stream
+  char* mc;                    // multicast base of the heaps
+  size_t part_off;             // heap offset of the partial sums [tokens, d] bf16
+  size_t x_off;                // heap offset of the reduced tensor [tokens, d] bf16
+  const __nv_bfloat16* residual;   // local [tokens, d] or null
+};
+
 ZbDeviceState* zb_device_state();       // state of the current device, or nullptr before zb_init
 void zb_count_launch(int n);            // adds to the process-wide kernel-launch counter
 

@@ -398,10 +398,38 @@ class LlamaModel:
         n2 = ops.rmsnorm(x, lw.post_norm, c.rms_norm_eps)
         return self.mlp(lw, x, n2)
 
+    def _layers_banded(self, x, meta: AttnMeta, kv_cache):
+        """Prefill-sized step under tensor parallelism: the all-reduce after o_proj / down_proj never runs on its
+        own.  The row-parallel GEMM leaves partial sums in the symmetric heap and announces them band by band
+        (128 tokens); the column-parallel GEMM that follows (gate|up, next layer's qkv) sums them inside NVSwitch
+        on a few of its CTAs, adds the residual, hands the bands with their RMSNorm statistics to every rank and
+        multiplies them as they arrive.  Only the last down_proj of the stack is followed by a stand-alone sum."""
+        c, fused = self.config, self.comm.fused
+        t, n_layers = x.shape[0], len(self.layers)
+        stats, owed = ops.row_sumsq(x), False
+        for l, lw in enumerate(self.layers):
+            if owed:
+                qkv, x = fused.band_consumer(t, lw.qkv, x, bias=lw.qkv_bias, eps=c.rms_norm_eps)
+            else:
+                qkv = ops.gemm(x, lw.qkv, bias=lw.qkv_bias, static_w=True, row_stats=stats, eps=c.rms_norm_eps)
+            a = self.attention_from_qkv(lw, qkv, meta, kv_cache[l, 0], kv_cache[l, 1])
+            fused.band_producer(a, lw.o)
+            act, x = fused.band_consumer(t, lw.gate_up, x, swiglu=True, eps=c.rms_norm_eps)
+            if l + 1 < n_layers:
+                fused.band_producer(act, lw.down)
+                owed = True
+            else:
+                x, stats = self.row_parallel(act, lw.down, x, emit_stats=True)
+                owed = False
+        return x
+
     def hidden_states(self, ids, meta: AttnMeta, kv_cache):
         x = ops.embedding(ids, self.embed)
         if not self.fused_layout and self.wants_fused_layout():
             self.prepare_fused()
+        if self.fused_layout and self.comm.world > 1 and self.comm.fused is not None and \
+                self.comm.fused.can_band(x.shape[0], self.config.hidden_size):
+            return self._layers_banded(x, meta, kv_cache)
         if self.fused_layout:
             stats = ops.row_sumsq(x)
             for l in range(self.config.num_hidden_layers):

@@ -431,9 +431,15 @@ def forward_moe(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Ten
     if extra_partial is not None:
         y = y + extra_partial
     if world > 1:
-        if (getattr(comm, "fused", None) is not None and y.is_cuda and comm.fused.staging is not None
-                and y.numel() <= comm.fused.staging.numel()):
-            y = comm.fused.all_reduce(y)
+        fz = getattr(comm, "fused", None)
+        if fz is not None and y.is_cuda and y.dim() == 2 and fz.can_all_reduce_mm(y.shape[0], y.shape[1]):
+            # prefill-sized: the partial outputs go through the symmetric heap and are added up inside NVSwitch
+            # (multimem load-reduce), the residual rides along
+            part = fz.partial_buffer(y.shape[0], y.shape[1])
+            part.copy_(y)
+            return fz.all_reduce_mm(part, residual)
+        if fz is not None and y.is_cuda and fz.staging is not None and y.numel() <= fz.staging.numel():
+            y = fz.all_reduce(y)
         else:
             y = comm.all_reduce_(y)
     if residual is not None:

@@ -42,6 +42,11 @@ _lib.register_signature("zb_allreduce_oneshot", C.c_int,
 _lib.register_signature("zb_ar_ctx_set_multicast", None, [C.c_void_p, C.c_void_p], optional=False)
 _lib.register_signature("zb_allreduce_mm", C.c_int,
                         [C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_longlong, C.c_size_t, C.c_void_p], optional=False)
+_lib.register_signature("zb_band_flag_bytes", C.c_size_t, [C.c_int], optional=False)
+_lib.register_signature("zb_gemm_band", C.c_int,
+                        [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                         C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_float,
+                         C.c_void_p], optional=False)
 _lib.register_signature("zb_gemm_ar_fused_epi", C.c_int,
                         [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int,
                          C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
@@ -120,7 +125,8 @@ class SymmetricContext:
         # collectives (3 counters per 128-token band), then the buffer the row-parallel GEMMs leave partial sums in
         self.mm_flag_off = self.ll_off + self.ll_bytes
         self.band_flag_off = self.mm_flag_off + 2 * 128 * 8 * 4
-        self.band_flag_bytes = _align(4 * 4 * ((max_tokens + 127) // 128 + 1) * 8)
+        self.nb_cap = (max_tokens + 127) // 128
+        self.band_flag_bytes = _align(int(l.zb_band_flag_bytes(self.nb_cap)))
         self.part_off = _align(self.band_flag_off + self.band_flag_bytes, 4096)
         self.heap_bytes = self.part_off + act_bytes
         self.hidden, self.max_tokens = hidden, max_tokens
@@ -200,6 +206,10 @@ class SymmetricContext:
 
     def prefill_collective(self) -> str:
         """One line for logs and benchmark records: how prefill-sized row-parallel outputs are summed."""
+        if self.has_multicast and self.BAND_PIPE:
+            return ("row-parallel GEMM announces 128-token bands of partial sums; the column-parallel GEMM that follows "
+                    "reduces them inside NVSwitch (multimem) on a few of its CTAs while the others multiply the bands "
+                    "that have arrived")
         if self.has_multicast and self.MM_PREFILL:
             return "GEMM into the symmetric heap, then in-kernel all-reduce inside NVSwitch (multimem load-reduce + store)"
         return "NCCL all-reduce after the GEMM"
@@ -209,6 +219,43 @@ class SymmetricContext:
         """bf16 [m, n] view of the heap region row-parallel GEMMs write partial sums to (input of `all_reduce_mm`)."""
         assert m * n * 2 <= self.heap_bytes - self.part_off
         return self.heap[self.part_off:self.part_off + m * n * 2].view(torch.bfloat16).view(m, n)
+
+    # ---- prefill collectives overlapped band by band (libzb_cuda.so: zb_gemm_band) ----
+    BAND_PIPE = os.environ.get("ZB_BAND_PIPE", "1") == "1"
+    COMM_CTAS = int(os.environ.get("ZB_COMM_CTAS", "16"))     # CTAs of the consuming GEMM that reduce and broadcast
+
+    def can_band(self, tokens: int, d: int) -> bool:
+        return (self.ctx is not None and self.has_multicast and self.BAND_PIPE and d == self.hidden
+                and 256 < tokens <= self.max_tokens and d % 8 == 0)
+
+    def band_producer(self, a, w) -> None:
+        """Row-parallel GEMM whose partial sums stay in this rank's heap; every band of 128 tokens is announced to
+        the rank that will reduce it as soon as it is complete.  Must be followed by `band_consumer`."""
+        m, k = a.shape
+        assert w.shape[0] == self.hidden and a.stride(1) == 1 and w.stride(1) == 1
+        _lib.check(_lib.lib().zb_gemm_band(self.ctx, 1, a.data_ptr(), w.data_ptr(), None, None, None, m, self.hidden, k,
+                                           a.stride(0), w.stride(0), self.hidden, self.part_off, 0, self.band_flag_off,
+                                           self.nb_cap, self.COMM_CTAS, 0, -1.0, _lib.stream_ptr()), "zb_gemm_band(producer)")
+
+    def band_consumer(self, tokens: int, w, residual, bias=None, swiglu: bool = False, eps: float = 1e-5):
+        """The column-parallel GEMM that consumes the all-reduced, normalised activation: returns (out, x) with
+        x = residual + sum over ranks of the producer's partial sums (bf16 [tokens, hidden], in the heap) and
+        out = rmsnorm_scale(x) @ w^T (+ bias), or its SwiGLU.  The sum is formed inside NVSwitch and written to all
+        ranks by a few CTAs of this launch while the others already multiply the bands that have arrived."""
+        n, k = w.shape
+        assert k == self.hidden and w.stride(1) == 1
+        idx = self._next
+        if residual is not None and residual.data_ptr() == self.act[idx].data_ptr():
+            idx ^= 1
+        self._next = idx ^ 1
+        x = self.act[idx][: tokens * k].view(tokens, k)
+        out = torch.empty((tokens, n // 2 if swiglu else n), dtype=torch.bfloat16, device=w.device)
+        _lib.check(_lib.lib().zb_gemm_band(self.ctx, 2, None, w.data_ptr(), out.data_ptr(),
+                                           bias.data_ptr() if bias is not None else None,
+                                           residual.data_ptr() if residual is not None else None, tokens, n, k, k, w.stride(0),
+                                           out.stride(0), self.part_off, self.act_off[idx], self.band_flag_off, self.nb_cap,
+                                           self.COMM_CTAS, int(swiglu), float(eps), _lib.stream_ptr()), "zb_gemm_band(consumer)")
+        return out, x
 
     def can_all_reduce_mm(self, tokens: int, d: int) -> bool:
         return (self.ctx is not None and self.has_multicast and self.MM_PREFILL and d == self.hidden and tokens <= self.max_tokens
