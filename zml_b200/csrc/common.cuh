@@ -140,6 +140,25 @@ ZB_DEVICE void zb_bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes
       : "memory");
 }
 
+// Untiled bulk copy shared -> global (both addresses 16-byte aligned, size a multiple of 16), tracked by the issuing
+// thread's bulk async-group: commit the group, then wait until its copies have read their source (the shared
+// memory may be overwritten) or are complete (the data is in global memory).
+ZB_DEVICE void zb_bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(zb_smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+ZB_DEVICE void zb_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+ZB_DEVICE void zb_bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+ZB_DEVICE void zb_bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// Orders this thread's earlier generic-proxy writes to shared memory before later async-proxy (bulk copy) reads of it.
+ZB_DEVICE void zb_fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 ZB_DEVICE void zb_tma_load_2d(void* smem_dst, const void* tmap, uint64_t* bar, int32_t x,
                               int32_t y) {
   asm volatile(

@@ -84,10 +84,26 @@ __host__ __device__ constexpr int smem_bytes_for(int bn, bool swap) {
 ZB_DEVICE void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 ZB_DEVICE float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
-template <int BN, bool SWAP, bool FUSED>
+// MODE 0: the GEMM and its epilogue options; 1: fused with the tensor-parallel all-reduce (fused_ar.h);
+// 2: one side of the band pipeline of the prefill collectives (ZbBandPipe; tokens as rows only).  The modes are
+// separate instantiations so that the weight-streaming decode kernels do not carry the other modes' code.
+// EPI 0 would compile the epilogue options of ZbGemmEpi out, PLAN 0 / 1 only the code of the plans without / with
+// cluster split-K.  The library instantiates EPI 1, PLAN 2 (everything) only: with one instantiation per option
+// set the four GEMMs of a decoder layer alternate between kernels and a layer measured 9 us slower (157.7 vs
+// 148.6 us on Llama-3.1-8B, one GPU) than with one kernel that stays in the instruction cache.
+template <int BN, bool SWAP, int MODE, int EPI, int PLAN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                     const __grid_constant__ CUtensorMap tmap_q, const GemmParams prm) {
+  constexpr bool FUSED = MODE == 1;
+  constexpr bool BAND = MODE == 2 && !SWAP;
+  constexpr bool kEpi = EPI != 0;
+  constexpr bool kCluster = PLAN != 0;      // cluster split-K code present
+  constexpr bool kGeneric = PLAN != 1;      // whole-tile / stream-K code present
+  const float* const epi_in_sumsq = kEpi ? prm.epi.in_sumsq : nullptr;
+  float* const epi_out_sumsq = kEpi ? prm.epi.out_sumsq : nullptr;
+  const int epi_swiglu = kEpi ? prm.epi.swiglu : 0;
+  const unsigned long long epi_pf_bytes = kEpi ? prm.epi.pf_bytes : 0ull;
   constexpr int kStages = stages_for(BN, SWAP);
   constexpr int kStageBytes = stage_bytes(BN);
   constexpr int kTileABytes = kBlockP * kBlockK * 2;
@@ -119,10 +135,10 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // neighbouring tiles and share operands in L2); a CTA's "virtual" tiles are then contiguous
   // and map to actual tile (v % rr_tiles) * grid + cta.  Small problems: stream-K ranges.
   // band pipeline, consumer side: the first comm_ctas CTAs reduce and broadcast, the rest share the tiles
-  const int cta_off = prm.band.mode == 2 ? prm.band.comm_ctas : 0;
+  const int cta_off = (BAND && prm.band.mode == 2) ? prm.band.comm_ctas : 0;
   const int cta_id = static_cast<int>(blockIdx.x) - cta_off;
   const int n_ctas = static_cast<int>(gridDim.x) - cta_off;
-  const bool comm_cta = cta_id < 0;
+  const bool comm_cta = BAND && cta_id < 0;
   const long long total_units =
       comm_cta ? 0 : static_cast<long long>(prm.rr_tiles > 0 ? n_ctas * prm.rr_tiles : num_out_tiles) * kb_total;
   long long u_begin = min(total_units, static_cast<long long>(comm_cta ? 0 : cta_id) * prm.units_per_cta);
@@ -218,7 +234,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     if constexpr (SWAP) {
       // per-token scale of the accumulators (tokens are the tile's columns; a swap-AB problem has one column
       // tile): computed here, while the main loop runs, from the partial sums the producing kernel left
-      if (prm.epi.in_sumsq != nullptr) {
+      if (epi_in_sumsq != nullptr) {
         // kEpiThreads / BN threads share a token (one thread takes 128 / ... tokens when BN > 128); a thread sums
         // every TPT-th part with 8 loads in flight, the TPT sums of a token are added in a fixed order
         constexpr int TPT = BN >= kEpiThreads ? 1 : kEpiThreads / BN;      // threads per token
@@ -229,7 +245,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           const int sub = BN < kEpiThreads ? et / BN : 0;
           float acc = 0.f;
           if (t < prm.rows_q) {
-            const float* src = prm.epi.in_sumsq + t;
+            const float* src = epi_in_sumsq + t;
             int i = sub;
             for (; i + 7 * TPT < prm.epi.in_parts; i += 8 * TPT) {
               float v[8];
@@ -260,17 +276,32 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
 
   if (comm_cta) {
     // ------------------------------------------ band pipeline: reduce + broadcast CTA (no tensor-core work)
-    // Every band this rank owns: wait for the partial sums of all ranks, pull their sum through the multicast
-    // address (NVSwitch adds the copies up), add the residual, push the new residual stream and its row
-    // statistics to every rank, then tell every rank that the band is done.  A row is one warp's work.
+    // Every band this rank owns: wait for the partial sums of all ranks, pull them chunk by chunk from every
+    // rank's heap into this CTA's (otherwise idle) operand ring with bulk copies, add them up in rank order with
+    // the residual, push the result to every rank with bulk copies and the row statistics with plain stores,
+    // then tell every rank that the band is done.  A row of the band belongs to one comm CTA.
     zb_pdl_wait();
     const ZbBandPipe& bp = prm.band;
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(bp.epoch);
     const int W = bp.world;
-    const int vec_per_row = bp.d >> 3;
-    constexpr int kWarps = kNumThreads / 32;
-    constexpr int kU = 16;                      // 16-byte loads in flight per lane
-    for (int b = bp.rank; b < bp.num_bands; b += W) {
+    const int row_bytes = bp.d * 2;
+    const int chunk = (row_bytes >= 4096 && row_bytes % 4096 == 0) ? 4096 : row_bytes;      // bytes per copy
+    const int chunks_per_row = row_bytes / chunk;
+    const int n_src = W + (bp.residual != nullptr ? 1 : 0);
+    // stage = n_src source chunks + one output chunk; as many stages as the ring holds (at most 4)
+    const int stage_sz = (n_src + 1) * chunk;
+    int n_stage = (kStages * kStageBytes) / stage_sz;
+    n_stage = n_stage > 4 ? 4 : n_stage;
+    uint64_t* cbar = full_bar;                       // the ring's "full" barriers, one per stage (count 1)
+    float* red = scale_tab;                          // per-warp partial sums of a row
+    const int vec_per_chunk = chunk >> 4;
+    bool ok = n_stage >= 2;
+    if (!ok && threadIdx.x == 0) {
+      *abort_flag = 1u;
+      *abort_where = 350u;
+    }
+    uint32_t use = 0;                                // chunks this CTA has pushed through the ring (all bands)
+    for (int b = bp.rank; ok && b < bp.num_bands; b += W) {
       if (static_cast<int>(threadIdx.x) < W) {
         if (!zb_wait_flag(bp.ready_peer[bp.rank] + static_cast<size_t>(b) * 8 + threadIdx.x, epoch, abort_flag))
           *abort_where = 300u + threadIdx.x;
@@ -279,41 +310,91 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       if (*abort_flag != 0u) break;
       const int row0 = b * kBlockP;
       const int rows = min(kBlockP, bp.tokens - row0);
-      for (int r = static_cast<int>(blockIdx.x) * kWarps + warp; r < rows; r += bp.comm_ctas * kWarps) {
-        const size_t row = static_cast<size_t>(row0 + r);
-        const size_t row_bytes = row * static_cast<size_t>(bp.d) * 2;
-        const uint4* res_row = bp.residual != nullptr ? reinterpret_cast<const uint4*>(bp.residual + row * bp.d) : nullptr;
-        float ss = 0.f;
-        for (int v0 = lane; v0 < vec_per_row; v0 += 32 * kU) {
-          uint4 x[kU], rs[kU];
-#pragma unroll
-          for (int u = 0; u < kU; ++u) {
-            const int v = v0 + u * 32;
-            if (v < vec_per_row) {
-              x[u] = zb_multimem_ld_reduce_bf16x8(bp.mc + bp.part_off + row_bytes + static_cast<size_t>(v) * 16);
-              rs[u] = res_row != nullptr ? res_row[v] : make_uint4(0u, 0u, 0u, 0u);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < kU; ++u) {
-            const int v = v0 + u * 32;
-            if (v < vec_per_row) {
-              const uint32_t a[4] = {x[u].x, x[u].y, x[u].z, x[u].w}, c[4] = {rs[u].x, rs[u].y, rs[u].z, rs[u].w};
-              uint32_t o[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float2 fa = zb_unpack_bf16x2(a[q]), fc = zb_unpack_bf16x2(c[q]);
-                o[q] = zb_pack_bf16x2(fa.x + fc.x, fa.y + fc.y);
-                const float2 fo = zb_unpack_bf16x2(o[q]);       // statistics of what is stored
-                ss += fo.x * fo.x + fo.y * fo.y;
-              }
-              zb_multimem_st_16(bp.mc + bp.x_off + row_bytes + static_cast<size_t>(v) * 16, make_uint4(o[0], o[1], o[2], o[3]));
-            }
-          }
-        }
-        ss = zb_warp_sum(ss);
-        if (lane < W) bp.sumsq_peer[lane][row] = ss;
+      const int my_rows = rows > static_cast<int>(blockIdx.x) ? (rows - 1 - static_cast<int>(blockIdx.x)) / bp.comm_ctas + 1 : 0;
+      const int n_units = my_rows * chunks_per_row;
+      auto unit_off = [&](int u) {                   // byte offset of unit u inside the [tokens, d] tensors
+        const int r = row0 + static_cast<int>(blockIdx.x) + (u / chunks_per_row) * bp.comm_ctas;
+        return static_cast<size_t>(r) * row_bytes + static_cast<size_t>(u % chunks_per_row) * chunk;
+      };
+      auto issue = [&](int u) {                      // thread 0: the copies of unit u into its stage
+        const uint32_t st = (use + u) % n_stage;
+        uint8_t* base = smem + st * stage_sz;
+        const size_t off = unit_off(u);
+        zb_mbar_expect_tx(&cbar[st], static_cast<uint32_t>(n_src * chunk));
+        for (int r = 0; r < W; ++r) zb_bulk_load(base + r * chunk, bp.heap[r] + bp.part_off + off, chunk, &cbar[st]);
+        if (bp.residual != nullptr)
+          zb_bulk_load(base + W * chunk, reinterpret_cast<const char*>(bp.residual) + off, chunk, &cbar[st]);
+      };
+      if (threadIdx.x == 0) {
+        for (int u = 0; u < n_stage - 1 && u < n_units; ++u) issue(u);
       }
+      float ss = 0.f;
+      for (int u = 0; u < n_units && ok; ++u) {
+        const uint32_t g = use + u;
+        const uint32_t st = g % n_stage;
+        uint8_t* base = smem + st * stage_sz;
+        if (threadIdx.x == 0) {
+          // the stage refilled now was computed on one iteration ago (everybody passed that iteration's barrier); the
+          // output chunk written below was last pushed n_stage iterations ago: that push must have read it
+          if (u + n_stage - 1 < n_units) issue(u + n_stage - 1);
+          if (n_stage >= 4) zb_bulk_wait_read<3>();          // at most n_stage - 1 pushes may still be reading
+          else if (n_stage == 3) zb_bulk_wait_read<2>();
+          else zb_bulk_wait_read<1>();
+        }
+        if (!zb_mbar_wait(&cbar[st], (g / n_stage) & 1u, abort_flag)) {
+          *abort_where = 360u;
+          ok = false;
+        }
+        __syncthreads();                             // stage complete for everybody; thread 0's wait_read done
+        if (*abort_flag != 0u) {
+          ok = false;
+          break;
+        }
+        uint4* outc = reinterpret_cast<uint4*>(base + n_src * chunk);
+        for (int v = threadIdx.x; v < vec_per_chunk; v += kNumThreads) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int r = 0; r < n_src; ++r) {          // ranks in ascending order, then the residual
+            const uint4 x = reinterpret_cast<const uint4*>(base + r * chunk)[v];
+            const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = zb_unpack_bf16x2(w4[q]);
+              acc[2 * q] += f.x;
+              acc[2 * q + 1] += f.y;
+            }
+          }
+          uint32_t o[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            o[q] = zb_pack_bf16x2(acc[2 * q], acc[2 * q + 1]);
+            const float2 fo = zb_unpack_bf16x2(o[q]);           // statistics of what is stored
+            ss += fo.x * fo.x + fo.y * fo.y;
+          }
+          outc[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        zb_fence_proxy_async_smem();
+        const bool row_end = (u % chunks_per_row) == chunks_per_row - 1;
+        if (row_end) {
+          const float ws = zb_warp_sum(ss);
+          if (lane == 0) red[warp] = ws;
+          ss = 0.f;
+        }
+        __syncthreads();                             // output chunk (and the row's partial sums) written
+        if (threadIdx.x == 0) {
+          const size_t off = unit_off(u);
+          for (int r = 0; r < W; ++r) zb_bulk_store(bp.heap[r] + bp.x_off + off, outc, chunk);
+          zb_bulk_commit();
+        }
+        if (row_end && static_cast<int>(threadIdx.x) < W) {
+          float tot = 0.f;
+#pragma unroll
+          for (int i = 0; i < kNumThreads / 32; ++i) tot += red[i];
+          const int r = row0 + static_cast<int>(blockIdx.x) + (u / chunks_per_row) * bp.comm_ctas;
+          bp.sumsq_peer[threadIdx.x][r] = tot;
+        }
+      }
+      use += static_cast<uint32_t>(n_units);
+      if (threadIdx.x == 0) zb_bulk_wait<0>();       // every push of this band is in the peers' memory
       __syncthreads();
       if (threadIdx.x == 0) {
         __threadfence_system();
@@ -325,6 +406,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
       }
     }
+    if (threadIdx.x == 0) zb_bulk_wait<0>();
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -332,7 +414,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       zb_tma_prefetch_desc(&tmap_q);
       zb_pdl_wait();
       if (tl) tl[2] = zb_globaltimer();
-      const uint32_t band_epoch = prm.band.mode == 2 ? *reinterpret_cast<volatile uint32_t*>(prm.band.epoch) : 0u;
+      const uint32_t band_epoch = (BAND && prm.band.mode == 2) ? *reinterpret_cast<volatile uint32_t*>(prm.band.epoch) : 0u;
       int band_seen = -1;                     // band pipeline: last band whose done flag this producer has seen
       uint32_t stage = 0, phase = 0;
       int issued = 0;
@@ -348,7 +430,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
         int pt, qt;
         decode(t, pt, qt);
-        if constexpr (!SWAP) {
+        if constexpr (BAND) {
           if (prm.band.mode == 2 && pt != band_seen) {
             // the rows of this tile are band `pt` of the reduced activation: wait until its owner has written it here
             if (!zb_wait_flag(prm.band.done_peer[prm.band.rank] + pt, band_epoch, abort_flag)) {
@@ -383,14 +465,14 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         }
         u += kb1 - kb0;
       }
-      if (prm.epi.pf_bytes != 0ull) {
+      if (epi_pf_bytes != 0ull) {
         // this CTA's share of the next GEMM's weights goes to L2 while the epilogue (and, in the tensor-parallel
         // variant, the exchange with the peers) runs: HBM is otherwise idle from here on
         constexpr unsigned long long kChunk = 16384ull;
-        const unsigned long long nchunks = (prm.epi.pf_bytes + kChunk - 1) / kChunk;
+        const unsigned long long nchunks = (epi_pf_bytes + kChunk - 1) / kChunk;
         for (unsigned long long c = blockIdx.x; c < nchunks; c += gridDim.x) {
           const unsigned long long off = c * kChunk;
-          const uint32_t sz = static_cast<uint32_t>(min(kChunk, prm.epi.pf_bytes - off)) & ~15u;
+          const uint32_t sz = static_cast<uint32_t>(min(kChunk, epi_pf_bytes - off)) & ~15u;
           if (sz != 0u)
             asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(static_cast<const char*>(prm.epi.pf_ptr) + off), "r"(sz)
                          : "memory");
@@ -485,16 +567,16 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       auto load_row_scale = [&]() {
         const int pr = min(pt * kBlockP + row_in_tile, prm.rows_p - 1);
         float ssum = 0.f;
-        for (int i = 0; i < prm.epi.in_parts; ++i) ssum += __ldcg(prm.epi.in_sumsq + static_cast<size_t>(i) * prm.epi.in_ld + pr);
+        for (int i = 0; i < prm.epi.in_parts; ++i) ssum += __ldcg(epi_in_sumsq + static_cast<size_t>(i) * prm.epi.in_ld + pr);
         row_scale = rsqrtf(ssum * prm.epi.in_inv_d + prm.epi.in_eps);
       };
       if constexpr (!SWAP) {
         // ahead of the wait for the accumulator, unless the statistics arrive with the band (band pipeline)
-        if (prm.epi.in_sumsq != nullptr && prm.band.mode != 2) load_row_scale();
+        if (epi_in_sumsq != nullptr && !(BAND && prm.band.mode == 2)) load_row_scale();
       }
       zb_mbar_wait(&tmem_full[acc], acc_phase, abort_flag);
-      if constexpr (!SWAP) {
-        if (prm.epi.in_sumsq != nullptr && prm.band.mode == 2) {
+      if constexpr (BAND) {
+        if (epi_in_sumsq != nullptr && prm.band.mode == 2) {
           // the band's rows were loaded, so its done flag is set: acquire it, then read the statistics its owner wrote
           (void)zb_ld_acquire_sys(prm.band.done_peer[prm.band.rank] + pt);
           load_row_scale();
@@ -509,7 +591,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       const int q0 = qt * BN;
       const int out_tile = pt * num_q + qt;
 
-      if constexpr (SWAP && (BN <= 64 || (!FUSED && BN <= 128))) {
+      if constexpr (kCluster && SWAP && (BN <= 64 || (!FUSED && BN <= 128))) {
         if (prm.cluster > 1) {
           // Cluster split-K: every CTA of the cluster holds a partial of the same tile.  Partials go
           // to the CTA's own shared memory (the operand ring is idle: this CTA has no other tile),
@@ -544,14 +626,14 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           // partial tile), summed per token in a fixed order once the band is done
           float* sq = reinterpret_cast<float*>(smem + 96 * 1024);
           const int sq_ld = nrows | 1;
-          const bool has_scale = prm.epi.in_sumsq != nullptr;
+          const bool has_scale = epi_in_sumsq != nullptr;
           auto emit_sumsq = [&]() {
             epi_bar_sync();
             for (int c = epi_tid; c < BN; c += kEpiThreads) {
               if (q0 + c < prm.rows_q) {
                 float acc = 0.f;
                 for (int j = 0; j < nrows; ++j) acc += sq[c * sq_ld + j];
-                prm.epi.out_sumsq[(static_cast<size_t>(out_tile) * S + rank) * prm.epi.out_ld + q0 + c] = acc;
+                epi_out_sumsq[(static_cast<size_t>(out_tile) * S + rank) * prm.epi.out_ld + q0 + c] = acc;
               }
             }
           };
@@ -582,7 +664,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
               v = v * sc[i] + bs[i] + rsd[i];
               const int col = off[i] / kBlockP, row = off[i] - col * kBlockP;
               const int pp = pt * kBlockP + row, qq = q0 + col;
-              if (prm.epi.swiglu) {
+              if (epi_swiglu) {
                 // even lanes hold gate_i, their neighbours up_i (element and row parity agree: bands and their
                 // heights are even); every lane of the warp takes part in the exchange
                 const float up = __shfl_xor_sync(0xffffffffu, v, 1);
@@ -604,7 +686,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                   stored = __bfloat162float(b);
                 }
               }
-              if (prm.epi.out_sumsq != nullptr) sq[col * sq_ld + (row - rb0)] = stored * stored;
+              if (epi_out_sumsq != nullptr) sq[col * sq_ld + (row - rb0)] = stored * stored;
             }
           };
           if constexpr (!FUSED) {
@@ -616,7 +698,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
               for (int base = 0; base < total; base += 4 * kEpiThreads)
                 reduce_batch(std::integral_constant<int, 4>{}, std::integral_constant<int, 8>{}, base + epi_tid);
             }
-            if (prm.epi.out_sumsq != nullptr) emit_sumsq();
+            if (epi_out_sumsq != nullptr) emit_sumsq();
             if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
             // nobody may leave (and release its shared memory) while a peer still reads it
             zb_cluster_arrive();
@@ -759,12 +841,12 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
                       ar.out_peer[ar.rank][static_cast<size_t>(qq) * prm.ldo + pp] = b;
                       stored = __bfloat162float(b);
                     }
-                    if (prm.epi.out_sumsq != nullptr) sq[col * sq_ld + (row - rb0)] = stored * stored;
+                    if (epi_out_sumsq != nullptr) sq[col * sq_ld + (row - rb0)] = stored * stored;
                   }
                 }
               }
             }
-            if (prm.epi.out_sumsq != nullptr) emit_sumsq();
+            if (epi_out_sumsq != nullptr) emit_sumsq();
             if (tl && epi_tid == 0) tl[10] = zb_globaltimer();
             if (tl && epi_tid == 0) tl[11] = zb_globaltimer();
             zb_cluster_wait();
@@ -775,7 +857,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           continue;
         }
       }
-
+      if constexpr (kGeneric) {
       bool do_store = true;
       if (partial) {
         // write this CTA's piece: ws[((cta*2 + slot)*BN + c)*128 + row]
@@ -844,7 +926,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       auto finish_chunk = [&](int c0, float (&v)[16]) {
         if constexpr (SWAP) {
           const float b = (prm.bias && p < prm.rows_p) ? __bfloat162float(prm.bias[p]) : 0.f;
-          const bool has_scale = prm.epi.in_sumsq != nullptr;
+          const bool has_scale = epi_in_sumsq != nullptr;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int q = q0 + c0 + j;
@@ -960,7 +1042,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
       auto epilogue_chunk = [&](int c0) {
         float v[16];
         load_chunk(c0, v);
-        if (prm.epi.swiglu) {
+        if (epi_swiglu) {
           finish_chunk(c0, v);
           swiglu_store_chunk(c0, v);
         } else if (p < prm.rows_p) {
@@ -1028,9 +1110,9 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           for (int i = 0; i < kCols; ++i) {
             const int q = q0 + cg + 4 * i;
             if (q >= prm.rows_q) continue;
-            const float sc = prm.epi.in_sumsq != nullptr ? scale_tab[cg + 4 * i] : 1.f;
+            const float sc = epi_in_sumsq != nullptr ? scale_tab[cg + 4 * i] : 1.f;
             float v4[4] = {accv[i].x * sc + bz[0], accv[i].y * sc + bz[1], accv[i].z * sc + bz[2], accv[i].w * sc + bz[3]};
-            if (prm.epi.swiglu) {
+            if (epi_swiglu) {
               // rows pb .. pb + 3 are (gate, up, gate, up): two outputs at columns pb / 2, pb / 2 + 1
               __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(prm.out) + static_cast<size_t>(q) * prm.ldo + (pb >> 1);
               if (pb + 3 < prm.rows_p) {
@@ -1077,7 +1159,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 16) epilogue_chunk(c0);
         }
-        if constexpr (!SWAP) {
+        if constexpr (BAND) {
           if (prm.band.mode == 1) {
             // band pipeline, producer side: count the stored tiles of the band; the CTA that stores the last
             // one tells the band's owner that this rank's partial sums of the band are complete
@@ -1232,6 +1314,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
         zb_tc_fence_before();
         zb_mbar_arrive(&tmem_empty[acc]);
       }
+      }  // kGeneric
       acc ^= 1u;
       if (acc == 0) acc_phase ^= 1u;
     }
@@ -1269,7 +1352,7 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
   // ------------------------------------------------------------ common exit
   zb_tc_fence_before();
   __syncthreads();
-  if (prm.band.mode == 2 && threadIdx.x == 0) {
+  if (BAND && prm.band.mode == 2 && threadIdx.x == 0) {
     // band pipeline: every wait of this launch is over once all CTAs are here; the last one opens the next epoch
     __threadfence();
     const uint32_t ticket = atomicAdd(prm.band.epoch + 1, 1u);
@@ -1412,23 +1495,29 @@ int zb_make_tmap_kv_cache(CUtensorMap* out, const void* base, long long slots, i
 
 namespace {
 
-template <int BN, bool SWAP, bool FUSED = false>
-int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid,
-           cudaStream_t stream) {
+template <int BN, bool SWAP, int MODE, int EPI, int PLAN>
+int launch_k(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid, cudaStream_t stream) {
   constexpr int smem = smem_bytes_for(BN, SWAP);
   // the shared-memory attribute of a kernel is per device: one flag per device for every instantiation
   static bool configured[16] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return -21;
   if (!configured[dev]) {
-    cudaError_t e = zb_config_smem(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, smem);
+    cudaError_t e = zb_config_smem(zb_gemm_bf16_kernel<BN, SWAP, MODE, EPI, PLAN>, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured[dev] = true;
   }
-  const cudaError_t le = zb_launch_cluster(zb_gemm_bf16_kernel<BN, SWAP, FUSED>, dim3(grid), dim3(kNumThreads), smem, stream,
-                                           prm.cluster, tp, tq, prm);
+  const cudaError_t le = zb_launch_cluster(zb_gemm_bf16_kernel<BN, SWAP, MODE, EPI, PLAN>, dim3(grid), dim3(kNumThreads), smem,
+                                           stream, prm.cluster, tp, tq, prm);
   zb_count_launch(1);
   return static_cast<int>(le != cudaSuccess ? le : cudaGetLastError());
+}
+
+template <int BN, bool SWAP, int MODE = 0>
+int launch(const CUtensorMap& tp, const CUtensorMap& tq, const GemmParams& prm, int grid, cudaStream_t stream) {
+  constexpr bool can_cluster = SWAP && (BN <= 64 || (MODE != 1 && BN <= 128));
+  if (prm.cluster > 1 && !can_cluster) return -12;
+  return launch_k<BN, SWAP, MODE, 1, 2>(tp, tq, prm, grid, stream);
 }
 
 // CTAs of the swap-AB kernel that can be resident at once when launched in clusters of `s`.
@@ -1438,7 +1527,7 @@ int max_cluster_ctas(int s) {
   if (s < 2 || s > 8) return 0;
   if (cache[s] != 0) return cache[s] < 0 ? 0 : cache[s];
   constexpr int smem = smem_bytes_for(BN, true);
-  if (zb_config_smem(zb_gemm_bf16_kernel<BN, true, false>, smem) != cudaSuccess) {
+  if (zb_config_smem(zb_gemm_bf16_kernel<BN, true, 0, 1, 2>, smem) != cudaSuccess) {
     (void)cudaGetLastError();
     cache[s] = -1;
     return 0;
@@ -1455,7 +1544,7 @@ int max_cluster_ctas(int s) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, zb_gemm_bf16_kernel<BN, true, false>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, zb_gemm_bf16_kernel<BN, true, 0, 1, 2>, &cfg) != cudaSuccess) {
     (void)cudaGetLastError();
     n = 0;
   }
@@ -1485,25 +1574,16 @@ int plan_cluster(int bn, int tiles, int kb_total, int num_sms, int* grid, int* u
       best_ctas = ctas;
     }
   }
-  if (best == 1) return 1;
-  (void)allow_tiny;
-  // Few CTAs stream less than the whole machine, but the stream-K plan pays for using every SM with a fix-up
-  // that grows with the pieces per tile (measured inside a decoder layer: 12 us for 16 pieces of a 32-token
-  // tile, against 2.5 us for the cluster reduction through shared memory).  Estimated time of either plan:
-  // k-blocks per CTA x stage bytes / min(what one SM can pull, its share of the HBM bandwidth) + the tail.
-  const double stage_b = static_cast<double>((kBlockP + bn) * kBlockK * 2);
-  auto stream_us = [&](int ctas, int kbs) {
-    const double per_sm_gbs = 50.0, hbm_gbs = 6500.0;
-    const double rate = per_sm_gbs < hbm_gbs / ctas ? per_sm_gbs : hbm_gbs / ctas;       // GB/s = 1000 bytes per us
-    return kbs * stage_b / (rate * 1000.0);
-  };
-  const int c_upc = (kb_total + best - 1) / best;
-  const double t_cluster = stream_us(best_ctas, c_upc) + 2.5;
-  const int pieces = (kb_total + *upc - 1) / *upc + 1;
-  const double t_streamk = stream_us(*grid, *upc) + (kb_total > *upc ? 2.0 + 0.6 * pieces : 0.0);
-  if (t_cluster >= t_streamk) return 1;
+  // Under half of the SMs busy: stream-K (all SMs stream) does better - unless the whole problem is a few
+  // k-blocks (a router or a small head: 1 - 2 tiles), or a handful of tiles would each be cut into many pieces:
+  // the stream-K fix-up then costs more than the whole GEMM (measured inside a decoder layer: 12 us for 16
+  // pieces of a 32-token tile, against 2.5 us for the cluster reduction through shared memory).
+  const bool tiny = allow_tiny && static_cast<long long>(tiles) * kb_total <= 64;
+  const int pieces = (kb_total + *upc - 1) / *upc;
+  const bool shredded = allow_tiny && tiles <= 8 && pieces >= 8;
+  if (best == 1 || (best_ctas * 2 < num_sms && !tiny && !shredded)) return 1;
   *grid = best_ctas;
-  *upc = c_upc;
+  *upc = (kb_total + best - 1) / best;
   return best;
 }
 
@@ -1711,15 +1791,22 @@ int gemm_impl(const void* a, const void* w, void* out, const void* residual, con
   rc = -12;
 #define ZB_GEMM_CASE(BN_)                                                           \
   case BN_:                                                                         \
-    rc = sw ? launch<BN_, true>(tp, tq, prm, grid, stream)                          \
-            : launch<BN_, false>(tp, tq, prm, grid, stream);                        \
+    rc = launch<BN_, true>(tp, tq, prm, grid, stream);                              \
     break;
-  switch (bn) {
-    ZB_GEMM_CASE(16)
-    ZB_GEMM_CASE(32)
-    ZB_GEMM_CASE(64)
-    ZB_GEMM_CASE(128)
-    ZB_GEMM_CASE(256)
+  if (band != nullptr && band->mode != 0) {
+    if (bn == 256) rc = launch<256, false, 2>(tp, tq, prm, grid, stream);
+    else if (bn == 128) rc = launch<128, false, 2>(tp, tq, prm, grid, stream);
+  } else if (!sw) {
+    if (bn == 256) rc = launch<256, false>(tp, tq, prm, grid, stream);
+    else if (bn == 128) rc = launch<128, false>(tp, tq, prm, grid, stream);
+  } else {
+    switch (bn) {
+      ZB_GEMM_CASE(16)
+      ZB_GEMM_CASE(32)
+      ZB_GEMM_CASE(64)
+      ZB_GEMM_CASE(128)
+      ZB_GEMM_CASE(256)
+    }
   }
 #undef ZB_GEMM_CASE
   if (rc == 0 && sumsq_after) rc = launch_row_sumsq(out, m, n, ldo, epi->out_sumsq, stream);
@@ -1820,12 +1907,12 @@ int zb_gemm_bf16(const void* a, const void* w, void* out, const void* residual, 
 //   mode 1: part[tokens, d] (at part_off of this rank's heap) = a[tokens, k] * w[d, k]^T; bands of 128 tokens are
 //           announced to their owners as their last column tile is stored.
 //   mode 2: out[tokens, n] = f(x[tokens, d]) * w[n, d]^T (+ bias) where x (at x_off of every heap) = residual +
-//           sum over ranks of part, reduced inside NVSwitch and written to every rank by the first `comm_ctas` CTAs
-//           of this launch while the other CTAs multiply the bands that are already there; f is the RMSNorm
+//           sum over ranks of part, pulled from and pushed to the peers' heaps with bulk copies by the first `comm_ctas`
+//           CTAs of this launch while the other CTAs multiply the bands that are already there; f is the RMSNorm
 //           scale of the row (statistics travel with the band; eps < 0: none); `swiglu` as in zb_gemm_bf16_epi.
 // `flag_off` addresses the pipeline's flag region in every heap, laid out for `nb_cap` bands:
 // ready [nb_cap][8] u32 | done [nb_cap] | producer counts [nb_cap] | consumer counts [nb_cap] | row statistics
-// [nb_cap * 128] fp32 (256-byte aligned).  Needs a context with a multicast address and tokens > 256.
+// [nb_cap * 128] fp32 (256-byte aligned).  Needs tokens > 256 and a hidden size whose rows are a multiple of 16 bytes.
 size_t zb_band_flag_bytes(int nb_cap) {
   return ((static_cast<size_t>(nb_cap) * 44 + 255) / 256) * 256 + static_cast<size_t>(nb_cap) * 128 * 4;
 }
@@ -1835,7 +1922,6 @@ int zb_gemm_band(const ZbArContext* ctx, int mode, const void* a, const void* w,
                  size_t flag_off, int nb_cap, int comm_ctas, int swiglu, float eps, void* stream) {
   ZbDeviceState* st = zb_device_state();
   if (st == nullptr || ctx == nullptr) return -20;
-  if (ctx->mc_heap == nullptr) return -69;
   if (mode != 1 && mode != 2) return -10;
   const int nb = (tokens + kBlockP - 1) / kBlockP;
   if (tokens <= 256 || nb > nb_cap || (part_off % 16) != 0 || (x_off % 16) != 0 || (flag_off % 256) != 0) return -70;
@@ -1859,7 +1945,7 @@ int zb_gemm_band(const ZbArContext* ctx, int mode, const void* a, const void* w,
   char* mine = reinterpret_cast<char*>(ctx->heap[ctx->rank]);
   bp.count_p = reinterpret_cast<uint32_t*>(mine + flag_off + static_cast<size_t>(nb_cap) * 36);
   bp.count_c = reinterpret_cast<uint32_t*>(mine + flag_off + static_cast<size_t>(nb_cap) * 40);
-  bp.mc = reinterpret_cast<char*>(ctx->mc_heap);
+  for (int r = 0; r < ctx->world; ++r) bp.heap[r] = reinterpret_cast<char*>(ctx->heap[r]);
   bp.part_off = part_off;
   bp.x_off = x_off;
   bp.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
@@ -1984,15 +2070,19 @@ int zb_gemm_ar_fused_epi(const ZbArContext* ctx, const void* a, const void* w, s
   rc = -12;
 #define ZB_GEMM_CASE(BN_)                                                     \
   case BN_:                                                                   \
-    rc = sw ? launch<BN_, true, true>(tp, tq, prm, grid, s)                   \
-            : launch<BN_, false, true>(tp, tq, prm, grid, s);                 \
+    rc = launch<BN_, true, 1>(tp, tq, prm, grid, s);                          \
     break;
-  switch (bn) {
-    ZB_GEMM_CASE(16)
-    ZB_GEMM_CASE(32)
-    ZB_GEMM_CASE(64)
-    ZB_GEMM_CASE(128)
-    ZB_GEMM_CASE(256)
+  if (!sw) {
+    if (bn == 256) rc = launch<256, false, 1>(tp, tq, prm, grid, s);
+    else if (bn == 128) rc = launch<128, false, 1>(tp, tq, prm, grid, s);
+  } else {
+    switch (bn) {
+      ZB_GEMM_CASE(16)
+      ZB_GEMM_CASE(32)
+      ZB_GEMM_CASE(64)
+      ZB_GEMM_CASE(128)
+      ZB_GEMM_CASE(256)
+    }
   }
 #undef ZB_GEMM_CASE
   if (rc == 0 && sumsq_after)

@@ -69,11 +69,12 @@ struct ZbGemmEpi {
 //   mode 1 (producer, the row-parallel GEMM): partial sums go to `part` in this rank's heap; when the last
 //     column tile of a band is stored the band's owner (band % world) is told: ready[owner][band][rank] = epoch.
 //   mode 2 (consumer, the column-parallel GEMM that follows): the first `comm_ctas` CTAs of the grid do not
-//     multiply.  For every band this rank owns they wait for the `world` ready flags, load the band through
-//     the multicast address with multimem.ld_reduce (NVSwitch returns the sum of all ranks' partial sums),
-//     add the residual, write the new residual stream and its row statistics into every rank's heap
-//     (multimem.st / peer stores) and publish done[rank'][band] = epoch on every rank.  The other CTAs run
-//     the GEMM; their TMA producer waits for done[band] before it loads the band's rows.
+//     multiply.  For every band this rank owns they wait for the `world` ready flags, pull the band's partial
+//     sums from every rank's heap with bulk copies (cp.async.bulk, peer memory over NVLink, no multicast) into
+//     shared memory, add them up in rank order in fp32 together with the residual, and push the new residual
+//     stream with bulk copies - and its row statistics with plain stores - into every rank's heap, then publish
+//     done[rank'][band] = epoch on every rank.  The other CTAs run the GEMM; their TMA producer waits for
+//     done[band] before it loads the band's rows.
 // Flags carry a device-side launch counter, so nothing is reset and CUDA-graph replays need no host change.
 struct ZbBandPipe {
   int mode;                    // 0: off
@@ -90,7 +91,7 @@ struct ZbBandPipe {
   uint32_t* ready_peer[8];     // [num_bands][8] in every rank's heap
   uint32_t* done_peer[8];      // [num_bands] in every rank's heap
   float* sumsq_peer[8];        // [tokens] in every rank's heap: sum of squares of the rows of the new residual stream
-  char* mc;                    // multicast base of the heaps
+  char* heap[8];               // base of every rank's heap ([rank] is local)
   size_t part_off;             // heap offset of the partial sums [tokens, d] bf16
   size_t x_off;                // heap offset of the reduced tensor [tokens, d] bf16
   const __nv_bfloat16* residual;   // local [tokens, d] or null

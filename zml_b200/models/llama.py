@@ -401,9 +401,10 @@ class LlamaModel:
     def _layers_banded(self, x, meta: AttnMeta, kv_cache):
         """Prefill-sized step under tensor parallelism: the all-reduce after o_proj / down_proj never runs on its
         own.  The row-parallel GEMM leaves partial sums in the symmetric heap and announces them band by band
-        (128 tokens); the column-parallel GEMM that follows (gate|up, next layer's qkv) sums them inside NVSwitch
-        on a few of its CTAs, adds the residual, hands the bands with their RMSNorm statistics to every rank and
-        multiplies them as they arrive.  Only the last down_proj of the stack is followed by a stand-alone sum."""
+        (128 tokens); a few CTAs of the column-parallel GEMM that follows (gate|up, next layer's qkv) pull them from
+        the peers' heaps, add them up with the residual and hand the bands with their RMSNorm statistics to every
+        rank, the other CTAs multiply the bands as they arrive.  Only the last down_proj of the stack is followed by
+        a stand-alone sum."""
         c, fused = self.config, self.comm.fused
         t, n_layers = x.shape[0], len(self.layers)
         stats, owed = ops.row_sumsq(x), False

@@ -11,7 +11,9 @@ import os
 from pathlib import Path
 
 _LIB = None
-_PATH = Path(__file__).resolve().parent.parent / "_C" / "libzb_cuda.so"
+# ZB_CUDA_LIB: path of another build of the library (kernel experiments: same ABI, different code)
+_PATH = Path(os.environ["ZB_CUDA_LIB"]) if os.environ.get("ZB_CUDA_LIB") else \
+    Path(__file__).resolve().parent.parent / "_C" / "libzb_cuda.so"
 
 c_p = C.c_void_p
 c_i = C.c_int

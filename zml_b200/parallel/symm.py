@@ -206,10 +206,10 @@ class SymmetricContext:
 
     def prefill_collective(self) -> str:
         """One line for logs and benchmark records: how prefill-sized row-parallel outputs are summed."""
-        if self.has_multicast and self.BAND_PIPE:
-            return ("row-parallel GEMM announces 128-token bands of partial sums; the column-parallel GEMM that follows "
-                    "reduces them inside NVSwitch (multimem) on a few of its CTAs while the others multiply the bands "
-                    "that have arrived")
+        if self.BAND_PIPE:
+            return ("row-parallel GEMM announces 128-token bands of partial sums; a few CTAs of the column-parallel GEMM "
+                    "that follows pull them from the peers with bulk copies over NVLink, add them up and push the sum to "
+                    "every rank while its other CTAs multiply the bands that have arrived")
         if self.has_multicast and self.MM_PREFILL:
             return "GEMM into the symmetric heap, then in-kernel all-reduce inside NVSwitch (multimem load-reduce + store)"
         return "NCCL all-reduce after the GEMM"
@@ -225,8 +225,7 @@ class SymmetricContext:
     COMM_CTAS = int(os.environ.get("ZB_COMM_CTAS", "16"))     # CTAs of the consuming GEMM that reduce and broadcast
 
     def can_band(self, tokens: int, d: int) -> bool:
-        return (self.ctx is not None and self.has_multicast and self.BAND_PIPE and d == self.hidden
-                and 256 < tokens <= self.max_tokens and d % 8 == 0)
+        return (self.ctx is not None and self.BAND_PIPE and d == self.hidden and 256 < tokens <= self.max_tokens and d % 8 == 0)
 
     def band_producer(self, a, w) -> None:
         """Row-parallel GEMM whose partial sums stay in this rank's heap; every band of 128 tokens is announced to
@@ -240,8 +239,9 @@ class SymmetricContext:
     def band_consumer(self, tokens: int, w, residual, bias=None, swiglu: bool = False, eps: float = 1e-5):
         """The column-parallel GEMM that consumes the all-reduced, normalised activation: returns (out, x) with
         x = residual + sum over ranks of the producer's partial sums (bf16 [tokens, hidden], in the heap) and
-        out = rmsnorm_scale(x) @ w^T (+ bias), or its SwiGLU.  The sum is formed inside NVSwitch and written to all
-        ranks by a few CTAs of this launch while the others already multiply the bands that have arrived."""
+        out = rmsnorm_scale(x) @ w^T (+ bias), or its SwiGLU.  A few CTAs of this launch pull the partial sums from
+        the peers' heaps with bulk copies, add them up and push the result to every rank, while the others already
+        multiply the bands that have arrived."""
         n, k = w.shape
         assert k == self.hidden and w.stride(1) == 1
         idx = self._next
