@@ -123,6 +123,7 @@ def main():
     # prefill collectives overlapped band by band: row-parallel GEMM announcing bands of partial sums, then the
     # column-parallel GEMM that sums them over peer memory on a few CTAs and multiplies on the rest, vs the same
     # chain with an NCCL all-reduce; repeated (the flags carry a launch counter) and with the SwiGLU epilogue
+    SymmetricContext.BAND_PIPE = True
     if True:
         for it, (t, kp, n2, swi) in enumerate([(700, 512, 768, False), (1024, 256, 1024, True), (300, 1024, 512, False),
                                                (700, 512, 768, False)]):
@@ -147,6 +148,7 @@ def main():
             gathered = comm.all_gather(x[None].contiguous())
             assert all(torch.equal(gathered[0], gathered[r]) for r in range(comm.world)), ("band pipeline", t)
         ops.raise_on_status()
+    SymmetricContext.BAND_PIPE = False
 
     # mixture-of-experts combine with the expert-parallel all-reduce inside vs finalize + NCCL all-reduce
     from zml_b200 import moe
@@ -178,17 +180,21 @@ def main():
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=torch.Generator().manual_seed(7)).tolist()
                for n in (33, 300, 129)]
     hid, toks = {}, {}
-    for mode, c in (("nccl", comm), ("fused", comm), ("single", single)):
+    for mode, c in (("nccl", comm), ("fused", comm), ("band", comm), ("single", single)):
         model = LlamaModel(cfg, c, device=dev).init_random(seed=5, std=0.05)
-        if mode == "fused":
+        SymmetricContext.BAND_PIPE = mode == "band"        # prefill collectives overlapped band by band
+        if mode in ("fused", "band"):
             comm.fused = SymmetricContext.create(comm, cfg.hidden_size, max_tokens=512)
         hid[mode] = hidden_after_prefill_and_decode(model, prompts)
         toks[mode], _ = Engine(model, num_pages=48, page_size=64, max_batch=4, max_seq_len=512).generate(prompts, 12)
-        if mode == "fused":
+        if mode in ("fused", "band"):
             comm.fused.close()
             comm.fused = None
-    for mode in ("nccl", "fused"):
+    SymmetricContext.BAND_PIPE = False
+    for mode in ("nccl", "fused", "band"):
         expect_close(hid[mode], hid["single"], atol=6e-2, rtol=6e-2, min_close=0.99)
+    allb = comm.all_gather(hid["band"][None].contiguous())
+    assert all(torch.equal(allb[0], allb[r]) for r in range(comm.world)), "band-pipeline hidden states differ between ranks"
     allh = comm.all_gather(hid["fused"][None].contiguous())
     assert all(torch.equal(allh[0], allh[r]) for r in range(comm.world)), "fused hidden states differ between ranks"
     allo = comm.all_gather_object(toks["fused"])

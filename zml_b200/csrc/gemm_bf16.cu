@@ -285,14 +285,29 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
     const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(bp.epoch);
     const int W = bp.world;
     const int row_bytes = bp.d * 2;
-    const int chunk = (row_bytes >= 4096 && row_bytes % 4096 == 0) ? 4096 : row_bytes;      // bytes per copy
-    const int chunks_per_row = row_bytes / chunk;
     const int n_src = W + (bp.residual != nullptr ? 1 : 0);
-    // stage = n_src source chunks + one output chunk; as many stages as the ring holds (at most 4)
+    // A stage holds n_src source chunks and one output chunk; a chunk is a row or a power-of-two fraction of it.
+    // The copies of n_stage - 1 stages are in flight while one is summed: pick the split of the idle operand ring
+    // (up to 2 * kStages stages: the ring's full and empty barriers are one array) that keeps most bytes in flight -
+    // a peer copy takes microseconds to come back, so bytes in flight are throughput.
+    int chunk = row_bytes, n_stage = 0;
+    {
+      long long best = -1;
+      for (int c = row_bytes; c >= 1024 && (c % 16) == 0; c >>= 1) {
+        int ns = (kStages * kStageBytes) / ((n_src + 1) * c);
+        ns = ns > 2 * kStages ? 2 * kStages : ns;
+        const long long inflight = static_cast<long long>(ns - 1) * n_src * c;
+        if (ns >= 2 && inflight > best) {
+          best = inflight;
+          chunk = c;
+          n_stage = ns;
+        }
+        if ((c & 1) != 0) break;
+      }
+    }
+    const int chunks_per_row = row_bytes / chunk;
     const int stage_sz = (n_src + 1) * chunk;
-    int n_stage = (kStages * kStageBytes) / stage_sz;
-    n_stage = n_stage > 4 ? 4 : n_stage;
-    uint64_t* cbar = full_bar;                       // the ring's "full" barriers, one per stage (count 1)
+    uint64_t* cbar = full_bar;                       // full_bar[kStages] and empty_bar[kStages] are contiguous (count 1 each)
     float* red = scale_tab;                          // per-warp partial sums of a row
     const int vec_per_chunk = chunk >> 4;
     bool ok = n_stage >= 2;
@@ -337,9 +352,16 @@ zb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_p,
           // the stage refilled now was computed on one iteration ago (everybody passed that iteration's barrier); the
           // output chunk written below was last pushed n_stage iterations ago: that push must have read it
           if (u + n_stage - 1 < n_units) issue(u + n_stage - 1);
-          if (n_stage >= 4) zb_bulk_wait_read<3>();          // at most n_stage - 1 pushes may still be reading
-          else if (n_stage == 3) zb_bulk_wait_read<2>();
-          else zb_bulk_wait_read<1>();
+          // at most n_stage - 1 pushes may still be reading their output chunk
+          switch (n_stage) {
+            case 2: zb_bulk_wait_read<1>(); break;
+            case 3: zb_bulk_wait_read<2>(); break;
+            case 4: zb_bulk_wait_read<3>(); break;
+            case 5: zb_bulk_wait_read<4>(); break;
+            case 6: zb_bulk_wait_read<5>(); break;
+            case 7: zb_bulk_wait_read<6>(); break;
+            default: zb_bulk_wait_read<7>(); break;
+          }
         }
         if (!zb_mbar_wait(&cbar[st], (g / n_stage) & 1u, abort_flag)) {
           *abort_where = 360u;

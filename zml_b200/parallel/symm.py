@@ -221,7 +221,10 @@ class SymmetricContext:
         return self.heap[self.part_off:self.part_off + m * n * 2].view(torch.bfloat16).view(m, n)
 
     # ---- prefill collectives overlapped band by band (libzb_cuda.so: zb_gemm_band) ----
-    BAND_PIPE = os.environ.get("ZB_BAND_PIPE", "1") == "1"
+    # Off unless ZB_BAND_PIPE=1: on two B200s the pipeline measured slower than the GEMM followed by the all-reduce
+    # inside NVSwitch (a peer copy takes ~4 us to come back, so the few reducing CTAs move ~25 GB/s each and the
+    # short qkv GEMM cannot hide its share); it needs no multicast, so it is also the path for heaps without one.
+    BAND_PIPE = os.environ.get("ZB_BAND_PIPE", "0") == "1"
     COMM_CTAS = int(os.environ.get("ZB_COMM_CTAS", "16"))     # CTAs of the consuming GEMM that reduce and broadcast
 
     def can_band(self, tokens: int, d: int) -> bool:
