@@ -225,6 +225,29 @@ def test_paged_prefill_mixed_batch(hq, hkv, hd):
     expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
 
 
+@pytest.mark.parametrize("hq,hkv,lens", [(8, 2, [(2048, 0), (300, 1700)]), (4, 1, [(129, 0), (64, 64), (7, 500)]), (16, 8, [(1000, 24)])])
+def test_paged_prefill_tensor_core_kernel(hq, hkv, lens):
+    """The tcgen05 prefill kernel (head_dim 128, 64-token pages, two query heads of a KV group per CTA) against the
+    float32 reference and against the mma.sync kernel: long prompts, chunked continuations, ragged tails."""
+    torch.manual_seed(6)
+    hd, page = 128, 64
+    q_lens = [a for a, _ in lens]
+    seq_lens = [a + c for a, c in lens]
+    kc, vc, bt = _make_paged(len(lens), seq_lens, hkv, hd, page)
+    qs = [0]
+    for n in q_lens:
+        qs.append(qs[-1] + n)
+    q = _randn(qs[-1], hq, hd)
+    sl = torch.tensor(seq_lens, dtype=torch.int32, device=DEV)
+    qst = torch.tensor(qs, dtype=torch.int32, device=DEV)
+    for window in (0, 333):
+        got = ops.paged_prefill(q, kc, vc, bt, sl, qst, window=window, impl="tc")
+        old = ops.paged_prefill(q, kc, vc, bt, sl, qst, window=window, impl="mma")
+        want = ref.paged_attention(q, kc, vc, bt, seq_lens, qs, window=window)
+        expect_close(got.float(), want.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+        expect_close(got.float(), old.float(), atol=2e-2, rtol=2e-2, min_close=0.995)
+
+
 @pytest.mark.parametrize("layout,rot", [(0, None), (1, None), (0, 32), (2, 32)])
 @pytest.mark.parametrize("qk_norm", [False, True])
 def test_rope_kvwrite(layout, rot, qk_norm):

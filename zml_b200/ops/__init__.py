@@ -328,11 +328,18 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale: float | None
     return out
 
 
+# ZB_ATTN_TC=0: prefill attention always on the mma.sync kernel (the tensor-core kernel takes head_dim 128,
+# 64-token pages and an even number of query heads per KV head)
+import os as _os
+_ATTN_TC = _os.environ.get("ZB_ATTN_TC", "1") != "0"
+
+
 def paged_prefill(q, k_cache, v_cache, block_table, seq_lens, q_start, scale: float | None = None,
-                  window: int = 0, out=None, total_q_blocks: int | None = None):
+                  window: int = 0, out=None, total_q_blocks: int | None = None, impl: str = "auto"):
     """Varlen causal attention of new tokens against the paged KV (which already holds them).
 
     q [T, hq, hd]; q_start int32 [B+1] (device); seq_lens int32 [B] = keys per sequence.
+    `impl`: "auto" (the tcgen05 kernel where it applies), "tc" (require it) or "mma" (the mma.sync kernel).
     """
     if not _cuda(q):
         return reference.paged_attention(q, k_cache, v_cache, block_table, seq_lens.tolist(),
@@ -347,6 +354,17 @@ def paged_prefill(q, k_cache, v_cache, block_table, seq_lens, q_start, scale: fl
     if out is None:
         out = torch.empty((t, hq, hd), dtype=q.dtype, device=q.device)
     nqb = total_q_blocks if total_q_blocks is not None else t // 64 + b
+    l = _lib.lib()
+    tc_ok = bool(l.zb_paged_prefill_tc_supported(hq, hkv, hd, page)) and q.stride(0) % 8 == 0
+    if impl == "tc" and not tc_ok:
+        raise ValueError(f"the tensor-core prefill kernel does not take hq={hq} hkv={hkv} hd={hd} page={page}")
+    if tc_ok and (impl == "tc" or (impl == "auto" and _ATTN_TC)):
+        rc = l.zb_paged_prefill_tc(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(seq_lens), _ptr(q_start), b, nqb, t,
+            hq, hkv, block_table.shape[1], q.stride(0), float(scale if scale is not None else 1.0 / math.sqrt(hd)), int(window),
+            int(_os.environ.get("ZB_ATTN_V_LBO", "0")), int(_os.environ.get("ZB_ATTN_V_SBO", "0")), _lib.stream_ptr())
+        _lib.check(rc, "zb_paged_prefill_tc")
+        return out
     rc = _lib.lib().zb_paged_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(seq_lens),
         _ptr(q_start), b, nqb, hq, hkv, hd, page, block_table.shape[1], q.stride(0),

@@ -76,6 +76,9 @@ _SIGS = {
     "zb_decode_scratch_bytes": (c_sz, [c_i, c_i, c_i, c_i]),
     "zb_paged_decode": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_ll, c_f,
                               c_i, c_i, c_p]),
+    "zb_paged_prefill_tc_supported": (c_i, [c_i, c_i, c_i, c_i]),
+    "zb_paged_prefill_tc": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_ll, c_f, c_i,
+                                  C.c_uint, C.c_uint, c_p]),
     "zb_paged_prefill": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i,
                                c_ll, c_f, c_i, c_p]),
 }
