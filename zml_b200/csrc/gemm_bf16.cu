@@ -1711,6 +1711,10 @@ size_t zb_gemm_workspace_bytes(int m, int n, int k, int num_sms) {
 
 }  // extern "C"
 
+int zb_gemm_2cta_wants(int m, int n, int k);
+int zb_gemm_2cta_launch(const void* a, const void* w, void* out, const void* residual, const void* bias, int m, int n, int k, int lda,
+                        int ldw, int ldo, int out_f32, const ZbGemmEpi* epi, ZbStatus* status, int num_sms, cudaStream_t stream);
+
 namespace {
 
 int launch_row_sumsq(const void* x, int rows, int d, long long ld, float* out, cudaStream_t stream) {
@@ -1751,6 +1755,16 @@ int gemm_impl(const void* a, const void* w, void* out, const void* residual, con
   if (!out_f32 && (ldo % 8) != 0) return -11;
   int rc = check_epi(epi, m, n, ldo, out_f32, residual, bias);
   if (rc != 0) return rc;
+  if ((band == nullptr || band->mode == 0) && split_hint <= 0 && zb_gemm_2cta_wants(m, n, k)) {
+    // prefill-sized: 256 x 256 tiles on pairs of SMs (gemm_2cta.cu); the row statistics of the output, when asked
+    // for, come from the follow-up kernel as on every plan without an emitting epilogue
+    rc = zb_gemm_2cta_launch(a, w, out, residual, bias, m, n, k, lda, ldw, ldo, out_f32, epi, status, num_sms, stream);
+    if (rc == 0 && epi != nullptr && epi->out_sumsq != nullptr) {
+      if (out_parts) *out_parts = 1;
+      rc = launch_row_sumsq(out, m, n, ldo, epi->out_sumsq, stream);
+    }
+    return rc;
+  }
   int sw, bn, grid, upc, rr;
   const int tiles = zb_gemm_plan(m, n, k, num_sms, split_hint, &sw, &bn, &grid, &upc, &rr);
   int cluster = 1;
