@@ -1,13 +1,15 @@
 #!/usr/bin/env python
-"""Load/execute timing of one sharded matmul (the reference's examples/benchmark).
+"""Compile/execute timing of one sharded matmul (the reference's examples/benchmark/main.zig).
 
-    python examples/benchmark/main.py [--size=4096] [--dtype=f16] [--iters=10]
+    python examples/benchmark/main.py [--size=4096] [--dtype=bf16] [--iters=10]
     python -m torch.distributed.run --nproc-per-node=N --master-addr 127.0.0.1 examples/benchmark/main.py ...
 
-a{m,k} is sharded on m over the `m` logical axis, b{k,n} on n over the `n` axis, and the
-result is constrained to {m sharded, n replicated}: every rank multiplies its row block of
-a by its column block of b and the column blocks are all-gathered.  Prints the compile
-("plan") time, the time of one call and 2*size^3 / elapsed in GFLOP/s, device-timed.
+The program is `a.dot(b, "k").with_partitioning({"m": "m", "n": "replicated"})`, compiled with `Platform.compile`
+and run through `Exe.call` on sharded `Buffer`s: a{m,k} is sharded on m over the logical axis `m`, b{n,k} (K-major)
+on n over the logical axis `n`.  Both logical axes lie on the one physical NVLink axis, so the two cuts cannot
+coexist in the product: every rank all-gathers b's shards and multiplies its own row block of a by it (bf16 on a
+GPU: this library's tcgen05 GEMM).  Prints the compile time, the time of one call and 2*size^3 / elapsed in
+GFLOP/s, device-timed, max over ranks.
 """
 from __future__ import annotations
 
@@ -20,12 +22,14 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 
 import torch  # noqa: E402
 
-from zml_b200 import flags, ops  # noqa: E402
+from zml_b200 import flags  # noqa: E402
+from zml_b200.buffer import Buffer  # noqa: E402
 from zml_b200.dtype import DataType  # noqa: E402
 from zml_b200.parallel.comm import Comm  # noqa: E402
 from zml_b200.platform import Platform  # noqa: E402
 from zml_b200.shape import Shape  # noqa: E402
 from zml_b200.sharding import LogicalMesh  # noqa: E402
+from zml_b200.tensor import Tensor  # noqa: E402
 
 
 @dataclass
@@ -36,50 +40,55 @@ class Args:
     help = __doc__
 
 
+def benchmark(a: Tensor, b: Tensor) -> Tensor:
+    return a.dot(b, "k").with_partitioning({"m": "m", "n": "replicated"})
+
+
+def random_buffer(platform, shape: Shape, sharding, seed: int) -> Buffer:
+    """A buffer of N(0, 1) values: every process draws its own shard on its device."""
+    local = sharding.sharded_shape(shape)
+    shards = {}
+    for dev in platform.local_devices():
+        g = torch.Generator(device=dev.torch_device).manual_seed(seed * 1009 + dev.id)
+        shards[dev.id] = torch.randn(local.dims, device=dev.torch_device, generator=g).to(shape.dtype.to_torch())
+    return Buffer(shape, sharding, shards, platform)
+
+
 def main(argv=None) -> int:
     args = flags.parse(argv, Args)
     comm = Comm.from_env()
     platform = Platform.auto(comm=comm)
-    sharding = platform.register_sharding("bench", LogicalMesh({"m": "low_bandwidth", "n": "high_bandwidth"}))
+    sharding = platform.register_sharding("benchmark_mesh", LogicalMesh({"m": "low_bandwidth", "n": "high_bandwidth"}))
     dt = DataType.parse(args.dtype)
-    n, p, r = args.size, comm.world, comm.rank
+    n = args.size
     dev = platform.local_devices()[0].torch_device
+    a_shape = Shape({"m": n, "k": n}, dt).with_partitioning({"m": "m", "k": "replicated"})
+    b_shape = Shape({"n": n, "k": n}, dt).with_partitioning({"k": "replicated", "n": "n"})
     t0 = time.perf_counter()
-    a_shape = Shape({"m": n, "k": n}, dt).with_partitioning({"m": "m"})
-    b_shape = Shape({"k": n, "n": n}, dt).with_partitioning({"n": "n"})
-    local_a = sharding.sharded_shape(a_shape) if p > 1 else a_shape
+    exe = platform.compile(benchmark, (Tensor.from_shape(a_shape), Tensor.from_shape(b_shape)), cuda_graph=False,
+                           program_name="benchmark")
     compile_s = time.perf_counter() - t0
-    g = torch.Generator(device=dev).manual_seed(r)
-    rows = n // p
-    a = torch.randn((rows, n), device=dev, generator=g).to(dt.to_torch())
-    bt = torch.randn((n // p, n), device=dev, generator=g).to(dt.to_torch())      # b^T column block, K-major
-    use_kernel = dev.type == "cuda" and dt is DataType.bf16
-
-    def call():
-        # every rank needs the full b: gather the column blocks, then multiply its row block
-        full_bt = comm.all_gather(bt) if p > 1 else bt
-        return ops.gemm(a, full_bt) if use_kernel else a.float() @ full_bt.float().t()
-
-    call()
+    a = random_buffer(platform, a_shape, sharding, 1)
+    b = random_buffer(platform, b_shape, sharding, 2)
+    out = exe.call(a, b, wait=True)
     if dev.type == "cuda":
-        torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         for _ in range(args.iters):
-            call()
+            out = exe.call(a, b)
         e.record()
         torch.cuda.synchronize()
         elapsed = s.elapsed_time(e) / 1e3 / args.iters
     else:
         t0 = time.perf_counter()
         for _ in range(args.iters):
-            call()
+            out = exe.call(a, b)
         elapsed = (time.perf_counter() - t0) / args.iters
     elapsed = comm.max_over_ranks(elapsed)
-    if r == 0:
+    if comm.rank == 0:
         gflops = 2.0 * n ** 3 / elapsed / 1e9
-        print(f"plan {compile_s * 1e3:.2f} ms; local a {local_a}; call {elapsed * 1e3:.3f} ms; {gflops:.1f} GFLOP/s "
-              f"({args.dtype}, size {n}, {p} device(s), {'tcgen05 kernel' if use_kernel else 'torch'})")
+        print(f"compile {compile_s * 1e3:.2f} ms; result {out}; call {elapsed * 1e3:.3f} ms; {gflops:.1f} GFLOP/s "
+              f"({args.dtype}, size {n}, {comm.world} process(es))")
     comm.finish(0)
     return 0
 

@@ -85,6 +85,8 @@ class Buffer:
         out = torch.empty(self._shape.dims, dtype=self._shape.dtype.to_torch())
         devices = self.sharding.devices_in_canonical_order()
         missing = [d for d in devices if d.id not in self.shards]
+        if missing and self.placement.shape.dims == self._shape.dims:
+            return self.local().cpu().clone()           # replicated: every process holds the whole tensor
         if missing and self.platform is not None and self.platform.comm is not None and self.platform.comm.world > 1:
             mine = self.local().contiguous()
             gathered = self.platform.comm.all_gather(mine[None])

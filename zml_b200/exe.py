@@ -11,7 +11,7 @@ from typing import Any, Callable, Optional, Sequence
 
 import torch
 
-from . import meta
+from . import meta, spmd
 from .buffer import Buffer
 from .profiling import tracer
 from .shape import Shape
@@ -100,6 +100,11 @@ class Exe:
     def _to_tensors(self, flat: Sequence[Buffer]) -> list[torch.Tensor]:
         dev = self._device()
         out = []
+        if self.platform.spmd() is not None:
+            # one process per device: the program runs on this rank's shards
+            self._local_shapes = [b.placement.shape for b in flat]
+            return [b.local().to(dev) for b in flat]
+        self._local_shapes = None
         for b in flat:
             if len(b.shards) == 1 and b.sharding.sharded_shape(b.shape()).dims == b.shape().dims:
                 out.append(b.local().to(dev))
@@ -109,11 +114,26 @@ class Exe:
 
     def _run_fn(self, tensors: list[torch.Tensor]):
         it = iter(tensors)
-        wrapped = meta.map_tree(lambda t: Tensor(next(it), t.shape()), self.arg_tree, lambda x: isinstance(x, Tensor))
-        return self.fn(*wrapped)
+        ctx = self.platform.spmd()
+        if ctx is None:
+            wrapped = meta.map_tree(lambda t: Tensor(next(it), t.shape()), self.arg_tree, lambda x: isinstance(x, Tensor))
+            return self.fn(*wrapped)
+        shapes = iter(self._local_shapes)
+        wrapped = meta.map_tree(lambda t: Tensor(next(it), next(shapes)), self.arg_tree, lambda x: isinstance(x, Tensor))
+        with spmd.activate(ctx):
+            out = self.fn(*wrapped)
+            for t in meta.collect(out, lambda x: isinstance(x, Tensor)):
+                t.data                                  # pending partial sums are settled inside the context
+        return out
 
     def _wrap_results(self, out):
+        ctx = self.platform.spmd()
+
         def to_buf(t: Tensor) -> Buffer:
+            if ctx is not None:
+                shape = ctx.global_shape(t.shape())
+                dev = self.platform.local_devices()[0]
+                return Buffer(shape, self.platform.pick_sharding(shape), {dev.id: t.data}, self.platform)
             return Buffer.from_tensor(self.platform, t.data, t.shape(), self.platform.pick_sharding(t.shape()))
         return meta.map_tree(to_buf, out, lambda x: isinstance(x, Tensor))
 

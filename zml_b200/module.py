@@ -11,11 +11,17 @@ compiler here.  "Compiling" a function means:
            that a launch-bound program costs one graph launch (the role XLA's fused
            executable plays).
 
-Execution is per process: inputs that are sharded Buffers are gathered to the process's
-device, the function runs on the global logical tensors, and results are re-sharded
-according to the partition specs they carry.  Resharding points inside the function are
-explicit (`zml_b200.ops_dist`).  The LLM serving path does not go through this generic
-executor; it calls the fused kernels directly (zml_b200.serving).
+Execution on one process (any number of local devices): inputs that are sharded Buffers are
+gathered to the process's device, the function runs on the global logical tensors, and
+results are re-sharded according to the partition specs they carry.
+
+Execution on a multi-process platform (one process per GPU, `Platform(comm=...)`) is SPMD:
+every rank runs the function on its own shards; contractions over a sharded axis, reductions
+and `Tensor.with_partitioning` issue the collectives (`zml_b200.spmd`), and the results come
+back as Buffers whose global shape follows from the partition specs they carry.
+
+The LLM serving path does not go through this generic executor; it calls the fused kernels
+directly (zml_b200.serving).
 """
 from __future__ import annotations
 
@@ -26,7 +32,7 @@ from typing import Any, Callable, Optional
 
 import torch
 
-from . import meta
+from . import meta, spmd
 from .buffer import Buffer
 from .exe import Exe
 from .profiling import tracer
@@ -64,10 +70,20 @@ def compile(fn: Callable, args=(), platform=None, program_name: Optional[str] = 
         result_shapes = None
         if validate:
             dev = platform.local_devices()[0].torch_device
-            zeros = meta.map_tree(lambda t: Tensor(torch.zeros(t.shape().dims, dtype=t.dtype().to_torch(), device=dev), t.shape()),
-                                  arg_tree, _is_tensor)
-            out = fn(*zeros)
-            result_shapes = meta.map_tree(lambda t: t.shape(), out, _is_tensor)
+            ctx = platform.spmd()
+
+            def zero(t: Tensor) -> Tensor:
+                # multi-process platform: every rank validates on zeros of its own shard's extent
+                shape = ctx.local_shape(t.shape()) if ctx is not None else t.shape()
+                return Tensor(torch.zeros(shape.dims, dtype=t.dtype().to_torch(), device=dev), shape)
+            zeros = meta.map_tree(zero, arg_tree, _is_tensor)
+            with spmd.activate(ctx):
+                out = fn(*zeros)
+                if ctx is not None:
+                    for t in meta.collect(out, _is_tensor):
+                        t.data                                  # settles pending sums inside the context
+            result_shapes = meta.map_tree(lambda t: ctx.global_shape(t.shape()) if ctx is not None else t.shape(),
+                                          out, _is_tensor)
         exe = Exe(fn, tuple(arg_tree), arg_shapes, result_shapes, platform, name, cuda_graph)
         log.info("Compiled %s [%.3fs]", name, time.perf_counter() - t0)
     return exe

@@ -79,6 +79,8 @@ class Platform:
                 raise RuntimeError("cuda target requested but no CUDA device is visible")
             world = comm.world if comm is not None and comm.world > 1 else None
             n = world or torch.cuda.device_count()
+        elif comm is not None and comm.world > 1:
+            n = comm.world                       # one process per (virtual) device
         else:
             n = self.options.cpu.device_count
         if n & (n - 1):
@@ -154,6 +156,16 @@ class Platform:
                 if s.covers(shape):
                     return s
         return self._replicated
+
+    def spmd(self):
+        """The SPMD context of a multi-process platform (None on a single process): programs compiled here run once
+        per rank on local shards, see `zml_b200.spmd`."""
+        if self.comm is None or self.comm.world <= 1:
+            return None
+        if getattr(self, "_spmd", None) is None:
+            from .spmd import SpmdContext
+            self._spmd = SpmdContext(self)
+        return self._spmd
 
     # ------------------------------------------------------------------ compile / profile
     def compile(self, fn, args=(), **opts):

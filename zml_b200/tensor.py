@@ -21,6 +21,7 @@ from typing import Iterable, Mapping, Optional, Sequence, Union
 import torch
 
 from .dtype import DataType
+from . import spmd as _spmd
 from .shape import AUTO, Axis, PartitionSpec, Shape, _parse_dims
 
 _ids = itertools.count(1)
@@ -85,19 +86,87 @@ class Rng:
         return Tensor(g.to(shape.dtype.to_torch()), shape)
 
 
+def _spmd_align_dot(lhs: "Tensor", rhs: "Tensor", ca, cb, ba, bb):
+    """Brings the shards of two dot operands into agreement inside an SPMD program.
+
+    Returns (lhs, rhs, pending): possibly re-laid-out operands (then the caller starts over) and the mesh axes the
+    local product still has to be summed over.  Rules, in order: a pair of contracted (or batch) axes must be cut
+    the same way - if only one side is sharded the other keeps its matching slice, if both are sharded over
+    different mesh axes both are gathered; a contracted pair sharded over mesh axis A makes the product a partial
+    sum over A; a free axis whose mesh axis is already taken (by a batch axis, a pending sum or an earlier free
+    axis) is gathered."""
+    ctx = _spmd.current()
+    pending: set = set()
+    used: set = set()
+
+    def keep(t: "Tensor", i: int, spec) -> "Tensor":
+        specs = {j: p for j, p in enumerate(t._shape.partitioning) if p.kind != "unknown"}
+        specs[i] = spec
+        return t.with_partitioning(specs)
+
+    for pairs, is_contract in ((list(zip(ba, bb)), False), (list(zip(ca, cb)), True)):
+        for i, j in pairs:
+            x, y = lhs._sharded_on(i), rhs._sharded_on(j)
+            if x is None and y is None:
+                continue
+            if x is not None and y is not None and x != y:
+                return keep(lhs, i, "replicated"), keep(rhs, j, "replicated"), pending
+            ax = x or y
+            if ctx.clashes(ax, used | pending):
+                return (keep(lhs, i, "replicated") if x else lhs), (keep(rhs, j, "replicated") if y else rhs), pending
+            if x is None:
+                return keep(lhs, i, ax), rhs, pending
+            if y is None:
+                return lhs, keep(rhs, j, ax), pending
+            (pending if is_contract else used).add(ax)
+    for t, skip in ((lhs, set(ca) | set(ba)), (rhs, set(cb) | set(bb))):
+        for i in range(t.rank()):
+            if i in skip:
+                continue
+            ax = t._sharded_on(i)
+            if ax is None:
+                continue
+            if ctx.clashes(ax, used | pending):
+                if t is lhs:
+                    return keep(lhs, i, "replicated"), rhs, pending
+                return lhs, keep(rhs, i, "replicated"), pending
+            used.add(ax)
+    return lhs, rhs, pending
+
+
 class Tensor:
-    __slots__ = ("data", "_shape", "id", "_source", "_donated")
+    """A tagged tensor.  Inside an `Exe` of a multi-process platform the value is this rank's shard and the
+    shape's partition specs say how the shards tile the global tensor; `_partial` then names the logical mesh axes
+    the value still has to be summed over (the result of contracting a sharded axis).  Reading `data` settles
+    that sum with an all-reduce; `with_partitioning` can turn it into a reduce-scatter instead."""
+    __slots__ = ("_data", "_shape", "id", "_source", "_donated", "_partial")
 
     def __init__(self, data: Optional[torch.Tensor], shape: Optional[Shape] = None, tags=None):
         if data is not None and shape is None:
             shape = Shape(tuple(data.shape), DataType.from_torch(data.dtype), tags)
         if data is not None and tuple(data.shape) != tuple(shape.dims):
             raise ValueError(f"data shape {tuple(data.shape)} does not match {shape}")
-        self.data = data
+        self._data = data
         self._shape = shape
         self.id = next(_ids)
         self._source = None
         self._donated = False
+        self._partial = None
+
+    @property
+    def data(self) -> Optional[torch.Tensor]:
+        if self._partial:
+            ctx = _spmd.current()
+            if ctx is None:
+                raise RuntimeError(f"{self} holds partial sums over {sorted(self._partial)} outside of an SPMD program")
+            self._data = ctx.all_reduce(self._data, self._partial)
+            self._partial = None
+        return self._data
+
+    @data.setter
+    def data(self, value) -> None:
+        self._data = value
+        self._partial = None
 
     # ------------------------------------------------------------------ construction
     @staticmethod
@@ -150,6 +219,8 @@ class Tensor:
         tags = self._shape.tags if tags is None else tags
         if len(tags) != data.dim():
             tags = (None,) * data.dim()
+        if part is None and tuple(data.shape) == tuple(self._shape.dims):
+            part = self._shape.partitioning         # same extent: the shards tile the result like the operand
         part = part if part is not None and len(part) == data.dim() else None
         return Tensor(data, Shape(tuple(data.shape), DataType.from_torch(data.dtype), tags, part))
 
@@ -187,10 +258,10 @@ class Tensor:
         return self._shape.axes(axes_)
 
     def is_symbolic(self) -> bool:
-        return self.data is None
+        return self._data is None
 
     def __repr__(self) -> str:
-        return f"Tensor({self._shape}{', symbolic' if self.data is None else ''})"
+        return f"Tensor({self._shape}{', symbolic' if self._data is None else ''})"
 
     def value(self):
         return self._need()
@@ -203,8 +274,9 @@ class Tensor:
 
     # ------------------------------------------------------------------ tags / partitioning / memory
     def _reshape_meta(self, shape: Shape) -> "Tensor":
-        t = Tensor(self.data, shape)
+        t = Tensor(self._data, shape)
         t._source = self._source
+        t._partial = self._partial
         return t
 
     def with_tags(self, *tags) -> "Tensor":
@@ -220,11 +292,57 @@ class Tensor:
         return self._reshape_meta(self._shape.set_tag(ax, new))
 
     def with_partitioning(self, specs: Mapping) -> "Tensor":
-        """Attaches partition specs.  On an already-computed tensor this is a sharding
-        constraint (the resharding point of the reference, zml/tensor.zig:150-199); the
-        eager runtime records the constraint, and `zml_b200.module` turns a change of layout
-        into the matching collective."""
-        return self._reshape_meta(self._shape.with_partitioning(specs))
+        """Attaches partition specs.  On a symbolic tensor, or outside an SPMD program, this only records them.
+        On a computed tensor inside an SPMD program it is the resharding point of the reference
+        (zml/tensor.zig:150-199): per axis, sharded -> replicated (or another mesh axis) all-gathers the shards,
+        replicated -> sharded keeps this rank's slice, and partial sums over the mesh axis an axis becomes
+        sharded on are reduce-scattered; partial sums that remain are all-reduced."""
+        new_shape = self._shape.with_partitioning(specs)
+        ctx = _spmd.current()
+        if ctx is None or self._data is None:
+            return self._reshape_meta(new_shape)
+        d = self._data
+        partial = set(self._partial or ())
+        cut = [n.axis for n in new_shape.partitioning if n.kind == "axis" and ctx.parts(n.axis) > 1]
+        for k, ax in enumerate(cut):
+            if ctx.clashes(ax, cut[:k]):
+                raise ValueError(f"{new_shape}: logical axes {cut} share a physical mesh axis and cannot cut one tensor twice")
+        for i, (o, n) in enumerate(zip(self._shape.partitioning, new_shape.partitioning)):
+            if o == n or (o.kind != "axis" and n.kind != "axis"):
+                continue
+            if o.kind == "axis":
+                if partial:                                   # settle the sum before moving shards around
+                    d = ctx.all_reduce(d, partial)
+                    partial = set()
+                d = ctx.all_gather(d, i, o.axis)
+            if n.kind == "axis":
+                if n.axis in partial:
+                    d = ctx.reduce_scatter(d, i, n.axis)
+                    partial.discard(n.axis)
+                else:
+                    d = ctx.slice_local(d, i, n.axis)
+        if partial:
+            d = ctx.all_reduce(d, partial)
+        t = Tensor(d, Shape(tuple(d.shape), new_shape.dtype, new_shape.tags, new_shape.partitioning))
+        t._source = self._source
+        return t
+
+    def _sharded_on(self, i: int) -> Optional[str]:
+        """Logical mesh axis that axis `i` is split over in the running SPMD program (None: every rank holds it whole)."""
+        ctx = _spmd.current()
+        spec = self._shape.partitioning[i]
+        if ctx is None or spec.kind != "axis" or ctx.parts(spec.axis) == 1:
+            return None
+        return spec.axis
+
+    def _gathered(self, i: int) -> "Tensor":
+        """This tensor with axis `i` whole on every rank."""
+        ax = self._sharded_on(i)
+        if ax is None:
+            return self
+        specs = {j: p for j, p in enumerate(self._shape.partitioning) if p.kind != "unknown"}
+        specs[i] = "replicated"
+        return self.with_partitioning(specs)
 
     def to_memory(self, kind: str) -> "Tensor":
         """Moves to a memory kind: device | host_pinned | host_unpinned | default (zml/platform.zig:63-115)."""
@@ -277,7 +395,14 @@ class Tensor:
                     b = other.broad(self._shape).data if other.rank() < self.rank() else b
                     if other.rank() > self.rank():
                         return other._like(fn(self.broad(other._shape).data, b))
-            return self._like(fn(a, b))
+            out = fn(a, b)
+            if other.rank() == self.rank() and tuple(out.shape) == tuple(other._shape.dims):
+                part = [q if (p.kind != "axis" and q.kind == "axis") else p
+                        for p, q in zip(self._shape.partitioning, other._shape.partitioning)]
+                if tuple(out.shape) == tuple(self._shape.dims):
+                    return self._like(out, part=part)
+                return other._like(out)
+            return self._like(out)
         return self._like(fn(a, other))
 
     def add(self, o): return self._bin(o, torch.add)
@@ -410,10 +535,30 @@ class Tensor:
     # ------------------------------------------------------------------ reductions (keep the axis, size 1)
     def _reduce(self, ax: Axis, fn) -> "Tensor":
         a = self.axis(ax)
+        if self._sharded_on(a) is not None:                 # SPMD: bring the axis together, then reduce it whole
+            return self._gathered(a)._reduce(a, fn)
         return self._like(fn(self._need(), a), part=self._shape.partitioning)
 
-    def sum(self, ax: Axis): return self._reduce(ax, lambda x, a: x.sum(a, keepdim=True))
-    def mean(self, ax: Axis): return self._reduce(ax, lambda x, a: x.float().mean(a, keepdim=True).to(x.dtype))
+    def sum(self, ax: Axis):
+        a = self.axis(ax)
+        mesh_axis = self._sharded_on(a)
+        if mesh_axis is None:
+            return self._reduce(ax, lambda x, a: x.sum(a, keepdim=True))
+        # SPMD: every rank sums its shard; the sum over the mesh axis stays pending like a contraction's
+        pending = set(self._partial or ())
+        out = self._data.sum(a, keepdim=True)
+        part = list(self._shape.partitioning)
+        part[a] = PartitionSpec("replicated")
+        t = self._like(out, part=part)
+        t._partial = frozenset(pending | {mesh_axis})
+        return t
+
+    def mean(self, ax: Axis):
+        a = self.axis(ax)
+        if self._sharded_on(a) is not None:
+            n = self._shape.dims[a] * _spmd.current().parts(self._sharded_on(a))
+            return self.convert(DataType.f32).sum(ax).scale(1.0 / n).convert(self.dtype())
+        return self._reduce(ax, lambda x, a: x.float().mean(a, keepdim=True).to(x.dtype))
     def max(self, ax: Axis): return self._reduce(ax, lambda x, a: x.max(a, keepdim=True).values)
     def min(self, ax: Axis): return self._reduce(ax, lambda x, a: x.min(a, keepdim=True).values)
     def any(self, ax: Axis): return self._reduce(ax, lambda x, a: x.bool().any(a, keepdim=True))
@@ -422,6 +567,8 @@ class Tensor:
     def arg_max(self, ax: Axis):
         """(values, indices), both keeping the reduced axis with size 1."""
         a = self.axis(ax)
+        if self._sharded_on(a) is not None:
+            return self._gathered(a).arg_max(a)
         v, i = self._need().max(a, keepdim=True)
         return self._like(v), self._like(i.to(torch.int32))
 
@@ -430,6 +577,8 @@ class Tensor:
     def softmax(self, ax: Axis) -> "Tensor":
         """Softmax in float32; a row that is entirely -inf gives zeros (zml/tensor.zig:1606-1617)."""
         a = self.axis(ax)
+        if self._sharded_on(a) is not None:
+            return self._gathered(a).softmax(a)
         x = self._need().float()
         m = x.max(a, keepdim=True).values
         m = torch.where(torch.isinf(m) & (m < 0), torch.zeros_like(m), m)
@@ -464,7 +613,6 @@ class Tensor:
 
     def dot_general(self, other: "Tensor", contracting: Sequence[tuple[Axis, Axis]],
                     batching: Optional[Sequence[tuple[Axis, Axis]]] = None) -> "Tensor":
-        a, b = self._need(), other._need()
         ca = [self.axis(x) for x, _ in contracting]
         cb = [other.axis(y) for _, y in contracting]
         if batching is None:
@@ -477,6 +625,21 @@ class Tensor:
                     batching.append((i, j))
         ba = [self.axis(x) for x, _ in batching]
         bb = [other.axis(y) for _, y in batching]
+        pending: set = set()
+        if _spmd.current() is not None:
+            lhs, rhs, pending = _spmd_align_dot(self, other, ca, cb, ba, bb)
+            if lhs is not self or rhs is not other:
+                out = lhs.dot_general(rhs, list(zip(ca, cb)), list(zip(ba, bb)))
+                return out
+            pending |= set(self._partial or ()) | set(other._partial or ())
+            if self._partial and other._partial:              # a product of two sums: settle one of them first
+                pending -= set(other._partial)
+                other._need()
+            if self._data is None or other._data is None:
+                self._need(), other._need()
+            a, b = self._data, other._data
+        else:
+            a, b = self._need(), other._need()
         fa = [i for i in range(a.dim()) if i not in ca and i not in ba]
         fb = [i for i in range(b.dim()) if i not in cb and i not in bb]
         for x, y in zip(ca, cb):
@@ -507,7 +670,11 @@ class Tensor:
         used = [p.axis for p in part if p.kind == "axis"]
         if len(used) != len(set(used)):
             part = None
-        return Tensor(out, Shape(tuple(out.shape), DataType.from_torch(out.dtype), tags if ok else None, part if ok else None))
+        res = Tensor(out, Shape(tuple(out.shape), DataType.from_torch(out.dtype), tags if ok else None,
+                                part if (ok or _spmd.current() is not None) else None))
+        if pending:
+            res._partial = frozenset(pending)
+        return res
 
     def outer(self, other: "Tensor") -> "Tensor":
         a, b = self._need(), other._need()
@@ -581,17 +748,58 @@ class Tensor:
         p[i], p[j] = p[j], p[i]
         return self.transpose(p)
 
+    def _all_gathered(self) -> "Tensor":
+        """Inside an SPMD program: this tensor with every axis whole (for ops that mix axes freely)."""
+        t = self
+        for i in range(self.rank()):
+            t = t._gathered(i)
+        return t
+
     def reshape(self, new_shape) -> "Tensor":
+        if _spmd.current() is not None:
+            t = self._all_gathered()
+            if t is not self:
+                return t.reshape(new_shape)
         s = self._shape.reshape(new_shape)
         return Tensor(self._need().reshape(s.dims), s)
 
     def split_axis(self, ax: Axis, split_shape) -> "Tensor":
+        """Inside an SPMD program the sizes are those of the shard: splitting a sharded axis leaves its outermost part
+        sharded (give that part as `auto`, or as the per-shard count)."""
+        a = self.axis(ax)
         s = self._shape.split_axis(ax, split_shape)
+        mesh_axis = self._sharded_on(a)
+        if mesh_axis is not None:
+            part = list(s.partitioning)
+            part[a] = PartitionSpec("axis", mesh_axis)
+            s = Shape(s.dims, s.dtype, s.tags, part)
         return Tensor(self._need().reshape(s.dims), s)
 
     unflatten = split_axis
 
     def merge(self, axes_: Mapping[str, Iterable[Axis]]) -> "Tensor":
+        """Inside an SPMD program a group whose outermost axis is sharded stays sharded the same way; a sharded
+        inner axis is gathered first (its shards would interleave in the merged axis)."""
+        if _spmd.current() is not None:
+            t, outer = self, {}
+            for tag, group in axes_.items():
+                idx = self.axes(group)
+                for k, i in enumerate(idx):
+                    if self._sharded_on(i) is None:
+                        continue
+                    if k == 0:
+                        outer[tag] = self._sharded_on(i)
+                    else:
+                        t = t._gathered(i)
+            if t is not self:
+                return t.merge(axes_)
+            s = self._shape.merge_axes(axes_)
+            if outer:
+                part = list(s.partitioning)
+                for tag, mesh_axis in outer.items():
+                    part[s.axis(tag)] = PartitionSpec("axis", mesh_axis)
+                s = Shape(s.dims, s.dtype, s.tags, part)
+            return Tensor(self._need().reshape(s.dims), s)
         s = self._shape.merge_axes(axes_)
         return Tensor(self._need().reshape(s.dims), s)
 
@@ -606,6 +814,11 @@ class Tensor:
 
     def flatten(self, start: Axis = 0, end: Axis = -1) -> "Tensor":
         a, b = self.axis(start), self.axis(end)
+        if _spmd.current() is not None and any(self._sharded_on(i) for i in range(a, b + 1)):
+            t = self
+            for i in range(a, b + 1):
+                t = t._gathered(i)
+            return t.flatten(a, b)
         d = self._need()
         out = d.reshape(*d.shape[:a], -1, *d.shape[b + 1:])
         tags = self._shape.tags[:a] + (None,) + self._shape.tags[b + 1:]
