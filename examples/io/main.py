@@ -3,7 +3,10 @@
 
     io cat <uri> | tree <dir> | ls <uri> | cp <src> <dst> | stat <uri> | realpath <uri>
     io safetensors <file|index|dir>      list tensors (name, dtype, shape, bytes) and metadata
-    io load <file|index|dir> [--device=cpu|cuda]   stream every tensor to the device, report GiB/s
+    io load <file|index|dir> [--device=cpu|cuda] [--chunk-mib=128] [--chunks=16] [--parallelism=16]
+                                         every tensor through the Loader (pinned staging ring, asynchronous
+                                         host-to-device copies) to the device, report GiB/s
+    io synth <dir> [--gib=16] [--tensor-mib=512]   write a synthetic bf16 checkpoint of that size (sharded files)
 URIs: plain paths, file://, http(s)://, hf://org/repo[@rev]/file, s3://bucket/key, gs://bucket/key.
 """
 from __future__ import annotations
@@ -45,6 +48,16 @@ class TwoArgs:
 class LoadArgs:
     positional: One
     device: str = "cpu"
+    chunk_mib: int = 128
+    chunks: int = 16
+    parallelism: int = 16
+
+
+@dataclass
+class SynthArgs:
+    positional: One
+    gib: float = 16.0
+    tensor_mib: int = 512
 
 
 def tree(vfs, path, prefix=""):
@@ -57,7 +70,7 @@ def tree(vfs, path, prefix=""):
 
 def main(argv=None) -> int:
     cmds = {"cat": OneArg, "tree": OneArg, "ls": OneArg, "stat": OneArg, "realpath": OneArg, "cp": TwoArgs,
-            "safetensors": OneArg, "load": LoadArgs}
+            "safetensors": OneArg, "load": LoadArgs, "synth": SynthArgs}
     name, a = flags.parse(argv, cmds, __doc__)
     vfs = Vfs.default()
     if name == "cat":
@@ -83,20 +96,43 @@ def main(argv=None) -> int:
             print(f"metadata {k} = {v}")
         print(f"{len(reg)} tensors, {reg.total_bytes() / 2 ** 20:.2f} MiB")
     elif name == "load":
-        from zml_b200.io import TensorStore
+        import torch
+        from zml_b200.io import Loader, TensorStore
+        from zml_b200.platform import CpuOptions, CreateOptions, Platform, Target
         store = TensorStore.from_path(a.positional.path)
+        on_gpu = a.device.startswith("cuda")
+        platform = Platform.init(Target.cuda) if on_gpu else Platform.init(Target.cpu, CreateOptions(cpu=CpuOptions(1)))
+        view = store.view()
+        model = {k: view.create_tensor(k) for k in store.registry.keys()}
+        loader = Loader(platform, parallelism=a.parallelism, dma_chunk_size=a.chunk_mib << 20, dma_chunks=a.chunks)
         t0 = time.perf_counter()
-        total = 0
-        for k in store.registry.keys():
-            if store.registry.get(k).shape.dtype.bit_size_of() < 8:
-                continue
-            t = store.load_tensor(k, device=a.device)
-            total += t.numel() * t.element_size()
-        if a.device.startswith("cuda"):
-            import torch
-            torch.cuda.synchronize()
+        bufs = loader.load(model, store, [])
         dt = time.perf_counter() - t0
-        print(f"loaded {total / 2 ** 30:.3f} GiB in {dt:.2f}s: {total / 2 ** 30 / max(dt, 1e-9):.2f} GiB/s")
+        st = loader.stats()
+        print(f"loaded {st['bytes_loaded'] / 2 ** 30:.3f} GiB ({len(bufs)} tensors) in {dt:.2f}s: "
+              f"{st['bytes_loaded'] / 2 ** 30 / max(dt, 1e-9):.2f} GiB/s  [staging {st['staging_bytes'] >> 20} MiB pinned, "
+              f"{st['chunk_waits']} waits for a free chunk, {st['read_seconds']:.2f} reader-seconds]")
+        loader.close()
+        del torch
+    elif name == "synth":
+        import torch
+        os.makedirs(a.positional.path, exist_ok=True)
+        per = a.tensor_mib << 20
+        n = max(1, int(a.gib * 2 ** 30) // per)
+        g = torch.Generator().manual_seed(0)
+        base = torch.randn(per // 2, generator=g).bfloat16()
+        t0 = time.perf_counter()
+        # one file per 8 tensors; the same values rotated so that files differ and no page is shared
+        names = {}
+        for f0 in range(0, n, 8):
+            part = {f"w.{i}": torch.roll(base, i).reshape(-1, 4096) for i in range(f0, min(n, f0 + 8))}
+            fname = f"model-{f0 // 8 + 1:05d}.safetensors"
+            safetensors.save_file(part, os.path.join(a.positional.path, fname))
+            names.update({k: fname for k in part})
+        import json
+        with open(os.path.join(a.positional.path, safetensors.INDEX_NAME), "w") as f:
+            json.dump({"metadata": {"total_size": n * per}, "weight_map": names}, f)
+        print(f"wrote {n} tensors of {a.tensor_mib} MiB ({n * per / 2 ** 30:.2f} GiB) in {time.perf_counter() - t0:.1f}s")
     return 0
 
 

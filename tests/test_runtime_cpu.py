@@ -139,6 +139,49 @@ def test_tensorstore_views_and_sharded_loader(tmp_path):
     loader.close()
 
 
+def test_loader_staging_ring_bound_tensors_and_load_execute(tmp_path):
+    """Shards larger than a staging chunk go through the ring piece by piece (spans cut at chunk boundaries, chunks
+    reused); a tensor bound to several entries is cut across their virtual concatenation; `load_execute` builds
+    a weight from its entries with an Exe."""
+    from zml_b200.io import PinnedRing, _cut_spans
+    from zml_b200.shape import Shape
+    from zml_b200.tensor import Tensor
+    assert list(_cut_spans([(0, 10), (100, 7)], 8)) == [([(0, 8)], 8), ([(8, 2), (100, 6)], 8), ([(106, 1)], 1)]
+    ring = PinnedRing(64, 2, pin=False)
+    a, b = ring.acquire(), ring.acquire()
+    ring.release(a)
+    assert ring.acquire() is a and ring.allocated_bytes() == 128
+    torch.manual_seed(2)
+    q, k, v = torch.randn(16, 24), torch.randn(8, 24), torch.randn(8, 24)
+    safetensors.save_file({"q": q, "k": k, "v": v}, str(tmp_path / "model.safetensors"))
+    store = TensorStore.from_path(str(tmp_path))
+    p = cpu_platform(PhysicalMesh.grid((2, 2), TORUS))
+    sh = p.register_sharding_with_strategy("model", LogicalMesh({"model": "high_bandwidth"}),
+                                           Strategy.parse_bindings({"model": ("link_x", "link_y")}))
+
+    class M:
+        def __init__(self, view):
+            self.q = view.create_tensor("q", ("dout", "d"), {"d": "model"})           # column shards: many short spans
+            self.qkv = view.maybe_create_binding(["q", "k", "v"], Shape({"dout": 32, "d": 24}, "f32").with_partitioning({"dout": "model"}))
+
+    m = M(store.view())
+    loader = Loader(p, parallelism=3, dma_chunk_size=200, dma_chunks=2)              # 200-byte chunks: every shard needs several
+    bufs = loader.load(m, store, [sh])
+    assert torch.equal(bufs.q.to_tensor(), q) and tuple(bufs.q.local(3).shape) == (16, 6)
+    assert torch.equal(bufs.qkv.to_tensor(), torch.cat([q, k, v], 0))
+    assert torch.equal(bufs.qkv.local(2), torch.cat([q, k, v], 0)[16:24])             # rows 16..23 are all of k
+    st = loader.stats()
+    assert st["bytes_loaded"] == (16 * 24 + 32 * 24) * 4 and st["staging_bytes"] == 400 and st["gib_per_s"] > 0
+
+    def fuse(q_, k_, v_):                                                            # entries arrive with their stored shapes
+        return q_.with_tags("dout", "d").scale(2.0)
+
+    exe = p.compile(fuse, tuple(Tensor.from_shape(Shape(t.shape, "f32")) for t in (q, k, v)), cuda_graph=False)
+    out = loader.load_execute(m.qkv, store, [sh], exe)
+    assert torch.equal(out.to_tensor(), q * 2.0)
+    loader.close()
+
+
 def test_tracer_and_profiler_write_trace_events(tmp_path):
     tracer.start()
     with tracer.span("zml.exe.call", wait=True, arg_count=2):

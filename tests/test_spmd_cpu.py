@@ -79,6 +79,16 @@ ref_logits = serving.logits(serving.hidden_states(tokens, meta, eng.kv_cache)).f
 err2 = (logits - ref_logits).abs().max().item()
 assert err2 < 5e-4 * max(1.0, ref_logits.abs().max().item()), err2
 
+# 3b. the serving model of this rank, filled from Loader buffers cut by `Sharding.placement`, holds exactly the
+#     weights its own range-based loader reads
+by_ranges = LlamaModel(cfg, c, device="cpu", dtype=torch.float32).load(store)
+by_placement = LlamaModel(cfg, c, device="cpu", dtype=torch.float32).load(store, platform=platform)
+assert by_placement.layers and len(by_placement.layers) == len(by_ranges.layers)
+for a_, b_ in zip(by_ranges.layers, by_placement.layers):
+    for name in ("input_norm", "post_norm", "qkv", "o", "gate_up", "down"):
+        assert torch.equal(getattr(a_, name), getattr(b_, name)), name
+assert torch.equal(by_ranges.lm_head, by_placement.lm_head) and torch.equal(by_ranges.embed, by_placement.embed)
+
 # 4. a resharding chain on its own: rows sharded -> columns sharded -> replicated
 mesh = platform.sharding("tp")
 x_shape = Shape({"m": 16, "k": 32}, "f32").with_partitioning({"m": "model"})

@@ -169,20 +169,95 @@ class View:
         return t
 
 
-class Loader:
-    """Loads symbolic model structs into device buffers, a bounded number of tensors at a time."""
+class _Chunk:
+    __slots__ = ("host", "event")
 
-    def __init__(self, platform, parallelism: int = 16, dma_chunk_size: int = 256 << 20, dma_chunks: int = 32,
+    def __init__(self, host: torch.Tensor):
+        self.host = host
+        self.event = None                 # CUDA event of the device copy that last read this chunk
+
+
+class PinnedRing:
+    """At most `chunks` staging buffers of `chunk_bytes` pinned host memory each, allocated on first use and handed
+    round: a reader thread fills one from disk while the copies out of the others are still in flight, and a
+    buffer is handed out again only once the copy that read it has completed (its event).  This is the
+    reference's DMA pool (`dma_chunks` x `dma_chunk_size`, zml/io.zig:289-325)."""
+
+    def __init__(self, chunk_bytes: int, chunks: int, pin: bool):
+        self.chunk_bytes = max(16, int(chunk_bytes))
+        self.max_chunks = max(2, int(chunks))            # two is what double buffering needs
+        self.pin = pin
+        self._free: list[_Chunk] = []
+        self._made = 0
+        self._cv = threading.Condition()
+        self.waits = 0                                   # times a reader had to wait for a free chunk
+
+    def acquire(self) -> _Chunk:
+        with self._cv:
+            while not self._free and self._made >= self.max_chunks:
+                self.waits += 1
+                self._cv.wait()
+            if self._free:
+                ch = self._free.pop(0)
+            else:
+                self._made += 1
+                ch = None
+        if ch is None:
+            ch = _Chunk(torch.empty(self.chunk_bytes, dtype=torch.uint8, pin_memory=self.pin))
+        if ch.event is not None:
+            ch.event.synchronize()
+            ch.event = None
+        return ch
+
+    def release(self, ch: _Chunk, event=None) -> None:
+        ch.event = event
+        with self._cv:
+            self._free.append(ch)
+            self._cv.notify()
+
+    def allocated_bytes(self) -> int:
+        return self._made * self.chunk_bytes
+
+
+def _cut_spans(spans: Sequence[tuple[int, int]], limit: int):
+    """Groups (offset, length) spans into pieces of at most `limit` bytes, cutting spans that are longer."""
+    piece, size = [], 0
+    for off, ln in spans:
+        while ln > 0:
+            take = min(ln, limit - size)
+            piece.append((off, take))
+            size += take
+            off += take
+            ln -= take
+            if size == limit:
+                yield piece, size
+                piece, size = [], 0
+    if piece:
+        yield piece, size
+
+
+class Loader:
+    """Loads symbolic model structs into device buffers, a bounded number of tensors at a time.
+
+    Data path per shard: `Placement.byte_spans` lists the byte ranges of the checkpoint entry that belong to this
+    process's device; the ranges are cut into pieces of at most `dma_chunk_size`; each piece is read (threaded
+    pread) into a chunk of the pinned ring and copied to its place in the device buffer with one asynchronous
+    host-to-device copy on a copy stream, while the next piece is already being read into another chunk."""
+
+    def __init__(self, platform, parallelism: int = 16, dma_chunk_size: int = 128 << 20, dma_chunks: int = 16,
                  read_threads: int = 8):
         self.platform = platform
         self.parallelism = max(1, parallelism)
-        self.dma_chunk_size = dma_chunk_size
-        self.dma_chunks = dma_chunks
         self.read_threads = read_threads
         self.bytes_loaded = 0
+        self.read_seconds = 0.0             # summed over reader threads
         self._lock = threading.Lock()
         self._pool = cf.ThreadPoolExecutor(max_workers=self.parallelism)
-        self._pending: list[cf.Future] = []
+        devs = platform.local_devices()
+        self._cuda = any(d.torch_device.type == "cuda" for d in devs)
+        self.ring = PinnedRing(dma_chunk_size, dma_chunks, pin=self._cuda)
+        self._streams = {d.id: torch.cuda.Stream(d.torch_device) for d in devs if d.torch_device.type == "cuda"}
+        self.last_seconds = 0.0
 
     def _pick_sharding(self, shape: Shape, shardings: Sequence[Sharding]) -> Sharding:
         """The first sharding that binds every logical axis the shape names, else replicated
@@ -197,28 +272,48 @@ class Loader:
         keys = store.sources_of(tensor)
         if not keys:
             raise KeyError(f"{tensor} was not created from this store")
-        shape = tensor.shape()
+        return self._load_keys(keys, tensor.shape(), store, shardings)
+
+    def _load_keys(self, keys: Sequence[str], shape: Shape, store: TensorStore, shardings: Sequence[Sharding]) -> Buffer:
         sharding = self._pick_sharding(shape, shardings)
         placement = sharding.placement(shape)
+        infos = [store.registry.get(k) for k in keys]
         shards = {}
         for dev in self.platform.local_devices():
             spans = placement.byte_spans(dev.mesh_device)
             nbytes = sum(l for _, l in spans)
-            pin = dev.torch_device.type == "cuda"
-            host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=pin)
-            if len(keys) == 1:
-                TensorReader(store.registry.get(keys[0])).read_into(host.numpy(), spans, self.read_threads)
+            raw = torch.empty(nbytes, dtype=torch.uint8, device=dev.torch_device)
+            stream = self._streams.get(dev.id)
+            pos = 0
+            for piece, size in _cut_spans(spans, self.ring.chunk_bytes):
+                ch = self.ring.acquire()
+                t0 = time.perf_counter()
+                self._read(infos, piece, ch.host.numpy()[:size])
+                dt = time.perf_counter() - t0
+                if stream is not None:
+                    with torch.cuda.stream(stream):
+                        raw[pos:pos + size].copy_(ch.host[:size], non_blocking=True)
+                        ev = torch.cuda.Event()
+                        ev.record(stream)
+                else:
+                    raw[pos:pos + size].copy_(ch.host[:size])
+                    ev = None
+                self.ring.release(ch, ev)
+                pos += size
+                with self._lock:
+                    self.bytes_loaded += size
+                    self.read_seconds += dt
+            if shape.dtype is DataType.f4e2m1 or shape.dtype.bit_size_of() < 8:
+                shards[dev.id] = raw                       # packed sub-byte data stays as bytes
             else:
-                self._read_bound(keys, store, spans, host.numpy())
-            t = bytes_to_torch(host.numpy(), placement.shape.dims, shape.dtype)
-            shards[dev.id] = t.to(dev.torch_device, non_blocking=pin)
-            with self._lock:
-                self.bytes_loaded += nbytes
+                shards[dev.id] = raw.view(shape.dtype.to_torch()).reshape(placement.shape.dims)
         return Buffer(shape, sharding, shards, self.platform)
 
-    def _read_bound(self, keys, store, spans, dst: np.ndarray) -> None:
-        """Spans address the virtual concatenation (along axis 0) of several entries."""
-        infos = [store.registry.get(k) for k in keys]
+    def _read(self, infos, spans, dst: np.ndarray) -> None:
+        """Spans address the virtual concatenation (along axis 0) of the entries `infos` (one entry: the entry)."""
+        if len(infos) == 1:
+            TensorReader(infos[0]).read_into(dst, spans, self.read_threads)
+            return
         starts, off = [], 0
         for i in infos:
             starts.append(off)
@@ -239,6 +334,7 @@ class Loader:
              progress: Optional[Callable[[str, int], None]] = None):
         """Returns the bufferized twin of `model` (Tensor -> Buffer, other fields dropped)."""
         t0 = time.perf_counter()
+        before = self.bytes_loaded
         futures = {}
 
         def submit(t: Tensor):
@@ -251,16 +347,40 @@ class Loader:
         def resolve(x):
             return x.result() if isinstance(x, cf.Future) else x
         out = meta.map_tree(resolve, out, lambda x: isinstance(x, cf.Future))
+        self.await_()
         if progress:
             progress("done", len(futures))
         dt = time.perf_counter() - t0
-        rate = self.bytes_loaded / dt if dt > 0 else 0.0
-        log.info("Loaded weights [%.2f GiB, %.2fs, %.2f GiB/s]", self.bytes_loaded / 2 ** 30, dt, rate / 2 ** 30)
+        self.last_seconds = dt
+        n = self.bytes_loaded - before
+        log.info("Loaded weights [%.2f GiB, %.2fs, %.2f GiB/s; %d x %d MiB staging, %d waits for a free chunk]",
+                 n / 2 ** 30, dt, n / 2 ** 30 / dt if dt > 0 else 0.0, self.ring._made, self.ring.chunk_bytes >> 20,
+                 self.ring.waits)
         return out
 
+    def load_execute(self, tensor: Tensor, store: TensorStore, shardings: Sequence[Sharding], exe, wait: bool = True):
+        """Loads every checkpoint entry `tensor` is bound to as a buffer of its own (the entry's stored shape) and
+        runs `exe` on them; the result is the tensor's buffer.  For weights that are computed from several
+        entries at load time - fused, transposed, de-quantised (zml/io.zig:444-488)."""
+        keys = store.sources_of(tensor)
+        if not keys:
+            raise KeyError(f"{tensor} was not created from this store")
+        futs = [self._pool.submit(self._load_keys, [k], store.registry.get(k).shape, store, shardings) for k in keys]
+        bufs = [f.result() for f in futs]
+        self.await_()
+        return exe.call(*bufs, wait=wait)
+
     def await_(self) -> None:
-        if torch.cuda.is_available():
-            torch.cuda.synchronize()
+        """Waits for every host-to-device copy issued so far."""
+        for s in self._streams.values():
+            s.synchronize()
+
+    def stats(self) -> dict:
+        return {"bytes_loaded": self.bytes_loaded, "seconds": self.last_seconds,
+                "gib_per_s": self.bytes_loaded / 2 ** 30 / self.last_seconds if self.last_seconds > 0 else 0.0,
+                "read_seconds": self.read_seconds, "staging_bytes": self.ring.allocated_bytes(),
+                "chunk_waits": self.ring.waits}
 
     def close(self) -> None:
         self._pool.shutdown(wait=True)
+        self.await_()

@@ -34,7 +34,18 @@ def load_model(path: str, comm: Optional[Comm] = None, device="cpu", dtype=torch
     config = config_cls.from_hf(cfg.get("text_config", cfg) if "hidden_size" not in cfg else cfg)
     comm = comm or Comm.single(torch.device(device))
     t0 = time.perf_counter()
-    model = model_cls(config, comm, device=device, dtype=dtype).load(store)
+    model = model_cls(config, comm, device=device, dtype=dtype)
+    if model_cls.__name__ == "LlamaModel":
+        # dense decoder: the generic Loader cuts the checkpoint by `Sharding.placement`
+        from ..platform import CpuOptions, CreateOptions, Platform, Target
+        on_gpu = torch.device(device).type == "cuda"
+        if on_gpu and comm.world == 1 and torch.device(device).index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        platform = (Platform.init(Target.cuda, comm=comm) if on_gpu and comm.world > 1 else
+                    Platform.init(Target.cpu, CreateOptions(cpu=CpuOptions(device_count=1)), comm=comm) if not on_gpu else None)
+        model = model.load(store, platform=platform)
+    else:
+        model = model.load(store)
     dt = time.perf_counter() - t0
     nbytes = model.weight_bytes()
     log.info("Loaded weights [%.2f GiB, %.2fs, %.2f GiB/s]", nbytes / 2 ** 30, dt, nbytes / 2 ** 30 / max(dt, 1e-9))

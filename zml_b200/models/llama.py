@@ -225,9 +225,17 @@ class LlamaModel:
             pad = torch.zeros((self.v_pad, self.lm_head.shape[1]), dtype=self.lm_head.dtype, device=self.lm_head.device)
             self.lm_head = torch.cat([self.lm_head, pad], 0)
 
-    def load(self, store, prefix: str = "") -> "LlamaModel":
+    def load(self, store, prefix: str = "", platform=None) -> "LlamaModel":
         """Loads this rank's shards from a TensorStore view (HF names).  Only the byte ranges
-        of the shard are read."""
+        of the shard are read.  With a `platform`, the weights are described as tagged tensors with partition
+        specs and cut by the generic `Loader` (`Sharding.placement` decides each rank's rows and columns) when the
+        layout allows it; otherwise the ranges come from this model's own head / vocabulary split."""
+        if platform is not None:
+            from . import tagged_llama
+            try:
+                return tagged_llama.load_serving_weights(self, platform, store, prefix)
+            except ValueError:
+                pass
         c, hd = self.config, self.config.hd
         dev, dt = self.device, self.dtype
         q0, q1 = self.q_rng[0] * hd, self.q_rng[1] * hd

@@ -44,6 +44,12 @@ class TaggedLlamaLayer:
         self.gate = m.create_tensor("gate_proj.weight", ("dout", "d"), col)
         self.up = m.create_tensor("up_proj.weight", ("dout", "d"), col)
         self.down = m.create_tensor("down_proj.weight", ("d", "din"), row)
+        # Qwen2-style projection biases and Qwen3-style per-head q / k norms, where the checkpoint has them
+        self.q_bias = a.maybe_create_tensor("q_proj.bias", ("dout",), col)
+        self.k_bias = a.maybe_create_tensor("k_proj.bias", ("dout",), col)
+        self.v_bias = a.maybe_create_tensor("v_proj.bias", ("dout",), col)
+        self.q_norm = a.maybe_create_tensor("q_norm.weight", ("hd",))
+        self.k_norm = a.maybe_create_tensor("k_norm.weight", ("hd",))
 
 
 class TaggedLlama:
@@ -89,9 +95,13 @@ class TaggedLlama:
         c = self.cfg
         h = layers.rms_norm(x, w.input_norm, c.rms_norm_eps)
         heads = {"h": "auto", "hd": c.hd}
-        q = self._rope(h.dot(w.q, "d").split_axis("dout", heads), positions)
-        k = self._rope(h.dot(w.k, "d").split_axis("dout", heads), positions)
-        v = h.dot(w.v, "d").split_axis("dout", heads)
+        bias = lambda y, b: y if b is None else y.add(b.broad(y.shape()))
+        hnorm = lambda y, g: y if g is None else layers.rms_norm(y, g, c.rms_norm_eps, ax="hd")
+        q = bias(h.dot(w.q, "d"), getattr(w, "q_bias", None)).split_axis("dout", heads)
+        k = bias(h.dot(w.k, "d"), getattr(w, "k_bias", None)).split_axis("dout", heads)
+        v = bias(h.dot(w.v, "d"), getattr(w, "v_bias", None)).split_axis("dout", heads)
+        q = self._rope(hnorm(q, getattr(w, "q_norm", None)), positions)
+        k = self._rope(hnorm(k, getattr(w, "k_norm", None)), positions)
         att = attention_ref.sdpa(q.rename({"s": "q"}).transpose(("h", "q", "hd")),
                                  k.rename({"s": "k"}).transpose(("h", "k", "hd")),
                                  v.rename({"s": "k"}).transpose(("h", "k", "hd")), mask)
@@ -121,3 +131,44 @@ def compile_prefill(model: TaggedLlama, platform, seq_len: int, cuda_graph: bool
     from ..shape import Shape
     tokens = Tensor.from_shape(Shape({"s": seq_len}, "i32"))
     return platform.compile(model.forward, (model, tokens), cuda_graph=cuda_graph, program_name="tagged_llama.prefill")
+
+
+def load_serving_weights(model, platform, store: TensorStore, prefix: str = ""):
+    """Fills a `LlamaModel` (the serving path's weights: fused qkv and gate|up matrices of this rank) from the
+    buffers the generic `Loader` produced for the `TaggedLlama` description of the same checkpoint: each rank's
+    rows and columns are the ones `Sharding.placement` assigns to its device, read as byte ranges.
+
+    Needs layouts a placement can express: key/value heads and the vocabulary divisible by the number of ranks
+    (the range-based `LlamaModel.load` also covers replicated KV heads and a padded vocabulary)."""
+    from ..sharding import LogicalMesh
+    c, world = model.config, model.comm.world
+    if c.num_key_value_heads % world or c.vocab_size % world or c.intermediate_size % world:
+        raise ValueError("this checkpoint's head / vocabulary counts do not divide over the ranks")
+    if len(platform.local_devices()) != 1 or platform.num_devices() != world:
+        raise ValueError("the serving model holds one shard per process: the platform must have one device per rank")
+    try:
+        tp = platform.sharding("model")
+    except KeyError:
+        tp = platform.register_sharding("model", LogicalMesh({MODEL_AXIS: "high_bandwidth"}))
+    view = store.view().with_prefix(prefix.rstrip(".")) if prefix else store.view()
+    desc = TaggedLlama(view, c)
+    bufs = desc.load(platform, store, [tp])
+    dev, dt = model.device, model.dtype
+    loc = lambda b: None if b is None else b.local().to(device=dev, dtype=dt)
+    model.embed = loc(bufs.embed)
+    model.final_norm = loc(bufs.norm)
+    model.lm_head = loc(bufs.lm_head) if (world > 1 or not c.tie_word_embeddings) else model.embed
+    from .llama import LayerWeights
+    for lb in bufs.layers:
+        lw = LayerWeights()
+        lw.input_norm, lw.post_norm = loc(lb.input_norm), loc(lb.post_norm)
+        lw.qkv = torch.cat([loc(lb.q), loc(lb.k), loc(lb.v)], 0)
+        if getattr(lb, "q_bias", None) is not None:
+            lw.qkv_bias = torch.cat([loc(lb.q_bias), loc(lb.k_bias), loc(lb.v_bias)], 0)
+        if getattr(lb, "q_norm", None) is not None:
+            lw.q_norm, lw.k_norm = loc(lb.q_norm), loc(lb.k_norm)
+        lw.o = loc(lb.o)
+        lw.gate_up = torch.cat([loc(lb.gate), loc(lb.up)], 0)
+        lw.down = loc(lb.down)
+        model.layers.append(lw)
+    return model
