@@ -313,3 +313,26 @@ def test_every_model_family_under_two_way_parallelism_on_cpu(tmp_path, world, fa
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("TP_CPU_OK") == world
+
+
+@pytest.mark.parametrize("name", ["tiny-llama-test", "tiny-qwen35-test"])
+def test_continuous_admission_matches_one_at_a_time_generation(name):
+    """Seven prompts through three batch rows: sequences leave and join between decode blocks (also with staggered
+    arrivals); every prompt gets the tokens it gets alone, and all pages and state slots come back."""
+    import torch
+    from zml_b200.models import registry
+    from zml_b200.parallel.comm import Comm
+    from zml_b200.serving import Engine
+    m = registry.build_model(name, Comm.single(torch.device("cpu")), device="cpu", seed=3, dtype=torch.float32)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(3, 200, (n,), generator=g).tolist() for n in (5, 17, 9, 30, 12, 7, 21)]
+    budgets = [6, 3, 9, 4, 1, 8, 5]
+    eng = Engine(m, num_pages=16, page_size=16, max_batch=3, max_seq_len=64)
+    want = [eng.generate([p], b)[0][0] for p, b in zip(prompts, budgets)]
+    got, st = eng.serve(prompts, budgets, sync_interval=4)
+    assert got == want and len(st.ttft_ms) == 7 and st.output_tokens == sum(budgets)
+    got, _ = eng.serve(prompts, budgets, sync_interval=3, arrivals=[0, 0, 2, 2, 5, 5, 9])
+    assert got == want and eng.pool.num_free == 15
+    eos = want[2][3]
+    got, _ = eng.serve(prompts[2:3], 9, eos_ids=[eos])
+    assert got[0] == want[2][:want[2].index(eos) + 1]

@@ -166,6 +166,46 @@ def test_rank_leaving_between_steps_is_seen_before_the_next_collective(tmp_path)
     assert "[2]" in r.stdout
 
 
+_ENGINE_WORKER = r"""
+import os, sys, time, torch
+sys.path.insert(0, os.environ["ZB_ROOT"])
+from zml_b200.models import registry
+from zml_b200.parallel import health
+from zml_b200.parallel.comm import Comm
+from zml_b200.serving import Engine
+c = Comm.from_env(backend="gloo", timeout_s=20)
+c.enable_heartbeat(timeout_s=3.0)
+model = registry.build_model("tiny-llama-test", c, device="cpu", seed=3, dtype=torch.float32)
+eng = Engine(model, num_pages=16, page_size=16, max_batch=2, max_seq_len=64)
+prompts = [[5, 6, 7, 8], [9, 10, 11]]
+out, _ = eng.serve(prompts, 4, sync_interval=2)              # every rank is here
+assert all(len(o) == 4 for o in out)
+if c.rank == c.world - 1:
+    c.leave()                                                # between requests, nothing in flight
+    print("LEFT", c.rank, flush=True)
+    os._exit(0)
+time.sleep(0.3)
+try:
+    eng.serve(prompts, 4, sync_interval=2)                   # must not reach a collective the departed rank never joins
+    print("NOT DETECTED", c.rank, flush=True)
+except health.RankFailure as e:
+    print("DETECTED", c.rank, e.ranks, flush=True)
+assert eng.pool.num_free == 15                               # nothing was admitted
+os._exit(0)
+"""
+
+
+def test_serving_loop_notices_a_departed_rank_before_launching(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text(_ENGINE_WORKER)
+    env = dict(os.environ, ZB_ROOT=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29645", str(script)],
+                       capture_output=True, text=True, env=env, timeout=240)
+    assert "DETECTED 0 [1]" in r.stdout and "LEFT 1" in r.stdout and "NOT DETECTED" not in r.stdout, \
+        r.stdout[-1500:] + r.stderr[-1500:]
+
+
 @pytest.mark.gpu
 def test_bounded_wait_times_out_cleanly_on_the_gpu():
     from zml_b200 import ops

@@ -56,6 +56,32 @@ class Comm:
                                     timeout=datetime.timedelta(seconds=timeout_s), **kw)
         return Comm(rank, world, dist.group.WORLD, device)
 
+    # ----------------------------------------------------------------- liveness
+    def enable_heartbeat(self, timeout_s: float = 30.0, store=None) -> None:
+        """Starts host-side failure detection (`zml_b200.parallel.health`): every `check_peers()` bumps this rank's
+        counter in the job's rendezvous store and raises `RankFailure` if a peer announced its exit or has not
+        bumped its own for `timeout_s`."""
+        if self.world == 1:
+            return
+        from .health import Heartbeat
+        if store is None:
+            store = dist.distributed_c10d._get_default_store()
+        self.heartbeat = Heartbeat(store, self.rank, self.world, timeout_s)
+
+    def check_peers(self) -> None:
+        """Call between steps, with none of this rank's kernels or collectives waiting on a peer: the serving loop
+        does before every decode block.  A no-op until `enable_heartbeat`."""
+        hb = getattr(self, "heartbeat", None)
+        if hb is not None:
+            hb.beat()
+            hb.check()
+
+    def leave(self) -> None:
+        """Announces an orderly exit to the other ranks (they see it at their next `check_peers`)."""
+        hb = getattr(self, "heartbeat", None)
+        if hb is not None:
+            hb.leave()
+
     # ----------------------------------------------------------------- collectives
     def all_reduce_(self, t: torch.Tensor, op: str = "sum") -> torch.Tensor:
         if self.world > 1:

@@ -371,7 +371,10 @@ class Engine:
         alive = [not (eos and outputs[i] and outputs[i][-1] in eos) for i in range(b)]
         steps_total = max_new_tokens - 1
         done_steps = 0
+        comm = getattr(self.model, "comm", None)
         while done_steps < steps_total and any(alive):
+            if comm is not None:
+                comm.check_peers()       # a rank that stopped is noticed here, before kernels that wait on it launch
             n = min(sync_interval, steps_total - done_steps, self.history_steps)
             self.d_step.zero_()
             for _ in range(n):
@@ -412,6 +415,147 @@ class Engine:
             self.release(r)
         if self.on_gpu:
             ops.raise_on_status()
+        return outputs, stats
+
+
+    # ------------------------------------------------------------------ continuous batching
+    def serve(self, prompts: Seq[Seq[int]], max_new_tokens, strategy: Optional[SamplingStrategy] = None,
+              eos_ids: Seq[int] = (), sync_interval: int = 16, seed: int = 0,
+              arrivals: Optional[Seq[int]] = None) -> tuple[list[list[int]], GenerationStats]:
+        """Continuous batching over any number of prompts: at most `max_batch` sequences decode together; between two
+        decode blocks (`sync_interval` steps, one device -> host read) finished sequences leave - their batch row,
+        KV pages and recurrent-state slot are free again - and waiting prompts are admitted as soon as a row and
+        enough pages are free: they are prefilled and join the next block.  `max_new_tokens` is one number or one per
+        prompt; `arrivals[i]` (optional) is the first block at which prompt i may be admitted.
+
+        On a multi-rank job every rank calls this with the same arguments; a rank that stopped or left is noticed
+        on the host before the next block is launched (`Comm.check_peers`)."""
+        strategy = strategy or SamplingStrategy()
+        self.set_seed(seed)
+        stats = GenerationStats()
+        n_req = len(prompts)
+        budget = [int(max_new_tokens)] * n_req if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
+        eos = set(int(e) for e in eos_ids)
+        cap = min(self.max_batch, max(1, n_req))
+        bb = min(_bucket(cap) if self.use_graphs else cap, self.max_batch)
+        cap = min(cap, bb)
+        ps = self.page_size
+        max_total = max((len(p) + m for p, m in zip(prompts, budget)), default=1)
+        num_splits = ops.decode_plan_splits(bb, self.model.hkv, max_total) if self.on_gpu else 1
+        launches0 = _lib.launch_count() if self.on_gpu else 0
+        outputs: list[list[int]] = [[] for _ in range(n_req)]
+        waiting = list(range(n_req))
+        running: dict[int, tuple[int, Request]] = {}          # batch row -> (prompt index, request)
+        free_rows = list(range(cap - 1, -1, -1))
+        # host mirror of the decode state; rows without a sequence point at the reserved page 0 and write no KV
+        ids_h = torch.zeros(bb, dtype=torch.int32)
+        pos_h = torch.zeros(bb, dtype=torch.int32)
+        bt_h = torch.zeros((bb, self.max_pages), dtype=torch.int32)
+        ss_h = torch.full((bb,), self.scratch_slot if self.stateful else 0, dtype=torch.int32)
+        t0 = time.perf_counter()
+        admitted_at: dict[int, float] = {}
+        ttft: dict[int, float] = {}
+        block = 0
+        dirty = False                                         # a row's owner changed since the last upload
+        comm = getattr(self.model, "comm", None)
+
+        def finish(row: int) -> None:
+            nonlocal dirty
+            dirty = True
+            idx, r = running.pop(row)
+            r.output, r.finished = outputs[idx], True
+            self.release(r)
+            free_rows.append(row)
+            ids_h[row], pos_h[row] = 0, 0
+            bt_h[row].zero_()
+            ss_h[row] = self.scratch_slot if self.stateful else 0
+
+        while waiting or running:
+            if comm is not None:
+                comm.check_peers()
+            # ---------------- admission
+            fresh: list[tuple[int, int, Request]] = []
+            while waiting and free_rows and (arrivals is None or arrivals[waiting[0]] <= block):
+                idx = waiting[0]
+                try:
+                    r = self.new_request(prompts[idx], budget[idx])
+                except OutOfPages:
+                    if not running and not fresh:
+                        raise
+                    break
+                waiting.pop(0)
+                fresh.append((free_rows.pop(), idx, r))
+                admitted_at[idx] = time.perf_counter()
+            if fresh:
+                dirty = True
+                stats.prompt_tokens += sum(len(r.prompt) for _, _, r in fresh)
+                first: dict[int, int] = {}
+                for chunk in self._prefill_chunks([r for _, _, r in fresh]):
+                    done, toks, _ = self._run_prefill_chunk(chunk, strategy, stats)
+                    if done:
+                        host = toks.cpu()
+                        stats.d2h_bytes += len(done) * 4
+                        for i, r in enumerate(done):
+                            first[r.rid] = int(host[i])
+                now = time.perf_counter()
+                for row, idx, r in fresh:
+                    tok = first[r.rid]
+                    ttft[idx] = (now - admitted_at[idx]) * 1e3
+                    running[row] = (idx, r)
+                    if budget[idx] > 0:
+                        outputs[idx].append(tok)
+                    n0 = len(r.prompt)
+                    ids_h[row], pos_h[row] = tok, n0
+                    bt_h[row].zero_()
+                    bt_h[row, :len(r.pages)] = torch.tensor(r.pages, dtype=torch.int32)
+                    ss_h[row] = r.slot if self.stateful else 0
+                    if len(outputs[idx]) >= budget[idx] or tok in eos:
+                        finish(row)
+            if not running:
+                block += 1
+                continue
+            # ---------------- device state (only when the set of sequences changed: a row that lost its sequence
+            # must stop writing KV before its pages go to another request)
+            if dirty:
+                dirty = False
+                pg = torch.div(pos_h, ps, rounding_mode="floor").long().clamp_max(self.max_pages - 1)
+                slot_h = bt_h.gather(1, pg[:, None])[:, 0] * ps + pos_h % ps
+                live = torch.zeros(bb, dtype=torch.bool)
+                live[list(running)] = True
+                slot_h = torch.where(live, slot_h, torch.full_like(slot_h, -1))
+                st = self._to_dev(self._pin(torch.stack([ids_h, pos_h, pos_h + 1, slot_h.to(torch.int32), ss_h])), stats)
+                self.d_ids[:bb].copy_(st[0]); self.d_pos[:bb].copy_(st[1]); self.d_seq[:bb].copy_(st[2])
+                self.d_slot[:bb].copy_(st[3])
+                if self.stateful:
+                    self.d_sslot[:bb].copy_(st[4])
+                self.d_bt[:bb].copy_(self._to_dev(self._pin(bt_h), stats))
+            # ---------------- one decode block
+            left = max(budget[idx] - len(outputs[idx]) for idx, _ in running.values())
+            n = max(1, min(sync_interval, self.history_steps, left))
+            self.d_step.zero_()
+            for _ in range(n):
+                self._decode_step(bb, strategy, num_splits, max_total, stats)
+            hist = self.d_hist[:n, :bb].cpu()                  # device -> host read (synchronises)
+            stats.d2h_bytes += n * bb * 4
+            stats.decode_steps += n
+            pos_h += n                                         # every row advanced n positions on the device
+            ids_h.copy_(hist[n - 1])
+            for row in list(running):
+                idx, _ = running[row]
+                for s_ in range(n):
+                    tok = int(hist[s_, row])
+                    outputs[idx].append(tok)
+                    if tok in eos or len(outputs[idx]) >= budget[idx]:
+                        finish(row)
+                        break
+            block += 1
+        if self.on_gpu:
+            torch.cuda.synchronize()
+            stats.launches = _lib.launch_count() - launches0
+            ops.raise_on_status()
+        stats.total_ms = (time.perf_counter() - t0) * 1e3
+        stats.ttft_ms = [ttft[i] for i in range(n_req)]
+        stats.output_tokens = sum(len(o) for o in outputs)
         return outputs, stats
 
 
