@@ -3,6 +3,11 @@
 
     python examples/llm/main.py --model=<repo dir | .safetensors | index.json> [--prompt=...]
         [--seqlen=2048] [--topk=1] [--temperature=1.0] [--seed=0] [--no-chat-template] [--profile]
+        [--backend=b200|vanilla|attnd] [--attnd-ip=IP:PORT]
+
+--backend picks the attention implementation (default: this library's paged kernels; `vanilla` is PyTorch SDPA on K/V
+gathered from the pages); --attnd-ip registers a remote attention daemon at IP:PORT and prefers it (dense decoder
+models, one conversation).
 
 Without --prompt an interactive chat loop starts (history in ~/.llm_chat_history).  For
 tensor / expert parallelism launch one process per GPU:
@@ -44,12 +49,15 @@ class Args:
     no_chat_template: bool = False
     profile: bool = False
     cpu: bool = False
+    backend: Optional[str] = None
+    attnd_ip: Optional[str] = None
     help = __doc__
 
 
 class Chat:
-    def __init__(self, session: Session, tok, template: Optional[str], bos, rank: int):
+    def __init__(self, session: Session, tok, template: Optional[str], bos, rank: int, comm=None):
         self.session, self.tok, self.template, self.bos, self.rank = session, tok, template, bos, rank
+        self.comm = comm
         self.first = True
 
     def run_once(self, prompt: str, max_new: Optional[int]) -> str:
@@ -98,9 +106,16 @@ class Chat:
         except Exception:
             readline, hist = None, None
         while self.session.remaining() > 8:
-            try:
-                line = input("> ")
-            except (EOFError, KeyboardInterrupt):
+            # rank 0 owns the terminal; the others get the line (or the end of the chat) from it
+            line = None
+            if self.rank == 0:
+                try:
+                    line = input("> ")
+                except (EOFError, KeyboardInterrupt):
+                    line = None
+            if self.comm is not None and self.comm.world > 1:
+                line = self.comm.broadcast_object(line)
+            if line is None:
                 break
             if not line.strip():
                 continue
@@ -121,13 +136,26 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     model, tok = hub.load_model(args.model, comm, device, dtype)
     cfg = model.config
+    backend = "attnd" if args.attnd_ip and args.backend in (None, "attnd") else (args.backend or "b200")
+    if backend != "b200":
+        if not hasattr(model, "set_attention_backend"):
+            raise SystemExit(f"--backend={backend} is implemented for the dense decoder models, not for {type(model).__name__}")
+        addr = None
+        if backend == "attnd":
+            if not args.attnd_ip:
+                raise SystemExit("--backend=attnd needs --attnd-ip=IP:PORT")
+            host, _, port = args.attnd_ip.rpartition(":")
+            addr = (host or "127.0.0.1", int(port))
+        model.set_attention_backend(backend, addr)
+        log.info("attention backend: %s%s", backend, f" at {addr[0]}:{addr[1]}" if addr else "")
     page = 64
     engine = Engine(model, num_pages=(args.seqlen + page - 1) // page + 2, page_size=page, max_batch=1,
-                    max_seq_len=args.seqlen, max_prefill_tokens=min(8192, args.seqlen))
+                    max_seq_len=args.seqlen, max_prefill_tokens=min(8192, args.seqlen),
+                    use_graphs=False if backend == "attnd" else None)     # the daemon is reached from the host: no graph
     strategy = SamplingStrategy(topk=args.topk, temperature=args.temperature)
     session = Session(engine, args.seqlen, strategy, cfg.eos_ids(), args.seed)
     template = None if args.no_chat_template or tok is None else hub.chat_template(getattr(cfg, "model_type", "llama"))
-    chat = Chat(session, tok, template, getattr(cfg, "bos_token_id", None), comm.rank)
+    chat = Chat(session, tok, template, getattr(cfg, "bos_token_id", None), comm.rank, comm)
     max_new = args.max_new_tokens or None
     prof = Profiler().start() if args.profile else None
     if args.prompt is not None:

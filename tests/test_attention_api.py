@@ -149,3 +149,40 @@ def test_attnd_reports_a_dead_daemon_instead_of_hanging():
         attnd.deinit()
     with pytest.raises(attnd.AttndError):
         attnd.Parameters.init(0, 32, 8, 2, True)
+
+
+def test_serving_model_attention_backends_agree():
+    """The dense decoder with `vanilla` (SDPA on gathered pages) and `attnd` (loopback daemon that owns the KV) gives
+    the hidden states of the default backend, for a prefill and for the decode step after it."""
+    from zml_b200.models import registry
+    from zml_b200.parallel.comm import Comm
+    from zml_b200.serving import Engine
+    from zml_b200.serving.engine import AttnMeta
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    tokens = torch.randint(3, 200, (11,), generator=torch.Generator().manual_seed(2)).to(torch.int32)
+    n = len(tokens)
+
+    def run(backend, addr=None):
+        m = registry.build_model("tiny-llama-test", Comm.single(torch.device("cpu")), device="cpu", seed=3, dtype=torch.float32)
+        if backend != "b200":
+            m.set_attention_backend(backend, addr)
+        eng = Engine(m, num_pages=4, page_size=16, max_batch=1, max_seq_len=32)
+        bt = i32([[1, 2]])
+        pre = m.hidden_states(tokens, AttnMeta(True, i32(list(range(n))), i32([16 + p for p in range(n)]), bt, i32([n]), i32([0, n])),
+                              eng.kv_cache)
+        dec = m.hidden_states(i32([7]), AttnMeta(False, i32([n]), i32([16 + n]), bt, i32([n + 1]), i32([0, 1])), eng.kv_cache)
+        return pre.float(), dec.float()
+
+    want = run("b200")
+    got = run("vanilla")
+    assert torch.allclose(got[0], want[0], atol=1e-4) and torch.allclose(got[1], want[1], atol=1e-4)
+    d = attnd.Daemon().start()
+    try:
+        got = run("attnd", d.address)
+        scale = want[0].abs().max().item()
+        assert (got[0] - want[0]).abs().max().item() < 0.03 * scale        # q, k, v cross the wire in bf16
+        assert (got[1] - want[1]).abs().max().item() < 0.03 * scale
+        assert d.requests > 0
+    finally:
+        attnd.deinit()
+        d.stop()

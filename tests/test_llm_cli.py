@@ -51,3 +51,28 @@ def test_cli_prompt_mode(tmp_path):
                        capture_output=True, text=True, timeout=180)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "tok/s" in r.stdout and "Loaded weights" in r.stderr
+
+
+_CHAT_WORKER = r"""
+import os, sys
+sys.path.insert(0, os.path.join(os.environ["ZB_ROOT"], "examples", "llm"))
+sys.path.insert(0, os.environ["ZB_ROOT"])
+import main as llm
+sys.exit(llm.main([f"--model={os.environ['ZB_REPO']}", "--seqlen=128", "--max-new-tokens=3", "--cpu", "--backend=vanilla"]))
+"""
+
+
+def test_cli_chat_loop_on_two_ranks_reads_stdin_on_rank_0_only(tmp_path):
+    """Two gloo ranks, interactive mode: only rank 0 sees the terminal; the line and the end of input reach rank 1 by
+    broadcast, so both run the same turns and leave together.  The attention backend flag is honoured."""
+    repo = tmp_path / "repo"
+    repo.mkdir()
+    make_repo(str(repo))
+    script = tmp_path / "w.py"
+    script.write_text(_CHAT_WORKER)
+    env = dict(os.environ, ZB_ROOT=ROOT, ZB_REPO=str(repo))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29661", "--local-ranks-filter", "0", str(script)],
+                       input="hello\nworld\n", capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
+    assert r.stdout.count("tok/s") == 2 and "attention backend: vanilla" in r.stderr

@@ -189,8 +189,9 @@ class Metadata:
 
 
 def causal_attention(q: Tensor, k: Tensor, v: Tensor, token_offset, metadata: Metadata, parameters: Parameters,
-                     device_ordinal: int = 0, num_partitions: int = 1) -> Tensor:
-    """q {q, h, hd}; k, v {k, h, hd}.  In decode only the K/V row at `token_offset` is sent."""
+                     device_ordinal: int = 0, num_partitions: int = 1, new_rows_only: bool = False) -> Tensor:
+    """q {q, h, hd}; k, v {k, h, hd}.  In decode only the K/V row at `token_offset` is sent: `k` / `v` are the
+    whole cache and the row is read at that index, or - with `new_rows_only` - they hold just the new row."""
     if _context is None:
         raise AttndError("attnd wasn't registered yet, use register() first")
     client = _context.clients[device_ordinal]
@@ -202,7 +203,7 @@ def causal_attention(q: Tensor, k: Tensor, v: Tensor, token_offset, metadata: Me
     n = metadata.num_tokens or qt.shape[0]
     if p.is_prefill:
         kt, vt = kt[:n], vt[:n]
-    else:
+    elif not new_rows_only:
         kt, vt = kt[t0:t0 + 1], vt[t0:t0 + 1]
     heads_local = p.num_kv_heads // num_partitions
     head0 = heads_local * device_ordinal

@@ -343,17 +343,71 @@ class LlamaModel:
         act = ops.swiglu(gu)
         return self.row_parallel(act, lw.down, x)
 
+    # Attention backend (the reference's `zml.attention.Backend`, zml/attention/attention.zig:9-27):
+    #   "b200"     the paged tcgen05 / flash-decoding kernels of this library (on CPU: their float32 restatements)
+    #   "vanilla"  PyTorch SDPA on K/V gathered from the pages (what the reference's `vanilla` tensor formulation is)
+    #   "attnd"    a remote attention daemon that owns the KV cache (one UDP datagram per token and KV head)
+    attn_backend = "b200"
+    _attnd = None
+
+    def set_attention_backend(self, name: str, attnd_address=None, model_id: int = 0, conversation_id: int = 749,
+                              mtu: int = 1500) -> None:
+        if name not in ("b200", "vanilla", "attnd"):
+            raise ValueError(f"unknown attention backend {name!r}; known: b200, vanilla, attnd")
+        if name == "attnd":
+            from ..attention import attnd
+            if attnd_address is None:
+                raise ValueError("the attnd backend needs the daemon's address (IP:PORT)")
+            attnd.register(attnd.Config(tuple(attnd_address), mtu), num_devices=1)
+            c = self.config
+            mk = lambda prefill: attnd.Parameters.init(model_id, c.hd, c.num_attention_heads, c.num_key_value_heads, prefill)
+            self._attnd = (attnd, mk(True), mk(False), conversation_id)
+        self.attn_backend = name
+
+    def _attention_attnd(self, lw: LayerWeights, qkv, meta: AttnMeta):
+        """One sequence at a time (a chat session): q, k, v of the new tokens go to the daemon, which keeps the KV."""
+        from ..ops import reference as R
+        from ..tensor import Tensor
+        attnd, p_prefill, p_decode, conv = self._attnd
+        c, hd = self.config, self.config.hd
+        t = qkv.shape[0]
+        q, k, v = qkv.split([self.hq * hd, self.hkv * hd, self.hkv * hd], dim=-1)
+        q, k, v = q.reshape(t, self.hq, hd), k.reshape(t, self.hkv, hd), v.reshape(t, self.hkv, hd)
+        if lw.q_norm is not None:
+            q = R.rmsnorm(q, lw.q_norm, c.rms_norm_eps)
+            k = R.rmsnorm(k, lw.k_norm, c.rms_norm_eps)
+        q = R.rope_rotate(q, meta.positions, self.inv_freq, self.rope_layout, self.rot_dim, self.attn_factor)
+        k = R.rope_rotate(k, meta.positions, self.inv_freq, self.rope_layout, self.rot_dim, self.attn_factor)
+        b16 = lambda x: x.to(torch.bfloat16)
+        md = attnd.Metadata(conv, self.layers.index(lw), t)
+        start = int(meta.positions[0])
+        if meta.is_prefill:
+            # the client sends rows 0..t-1 of k / v as positions start..start+t-1
+            out = attnd.causal_attention(Tensor(b16(q), None, ("q", "h", "hd")), Tensor(b16(k), None, ("k", "h", "hd")),
+                                         Tensor(b16(v), None, ("k", "h", "hd")), start, md, p_prefill,
+                                         self.comm.rank, self.comm.world)
+        else:
+            out = attnd.causal_attention(Tensor(b16(q), None, ("q", "h", "hd")), Tensor(b16(k), None, ("k", "h", "hd")),
+                                         Tensor(b16(v), None, ("k", "h", "hd")), start, md, p_decode,
+                                         self.comm.rank, self.comm.world, new_rows_only=True)
+        return out.to_torch().to(qkv.dtype).reshape(t, self.hq * hd)
+
     def attention_from_qkv(self, lw: LayerWeights, qkv, meta: AttnMeta, kc, vc):
         c = self.config
+        if self.attn_backend == "attnd":
+            return self._attention_attnd(lw, qkv, meta)
         q = ops.rope_kvwrite(qkv, meta.positions, meta.slot_mapping, self.inv_freq, kc, vc, self.hq,
                              self.hkv, c.hd, self.rope_layout, self.rot_dim, self.attn_factor,
                              lw.q_norm, lw.k_norm, c.rms_norm_eps, False)
+        impl = ops
+        if self.attn_backend == "vanilla":
+            from ..ops import baseline as impl
         if meta.is_prefill:
-            a = ops.paged_prefill(q, kc, vc, meta.block_table, meta.seq_lens, meta.q_start,
-                                  window=c.sliding_window, total_q_blocks=meta.total_q_blocks)
+            a = impl.paged_prefill(q, kc, vc, meta.block_table, meta.seq_lens, meta.q_start,
+                                   window=c.sliding_window, total_q_blocks=meta.total_q_blocks)
         else:
-            a = ops.paged_decode(q, kc, vc, meta.block_table, meta.seq_lens, window=c.sliding_window,
-                                 num_splits=meta.num_splits, max_seq_len=meta.max_seq_len)
+            a = impl.paged_decode(q, kc, vc, meta.block_table, meta.seq_lens, window=c.sliding_window,
+                                  num_splits=meta.num_splits, max_seq_len=meta.max_seq_len)
         return a.reshape(a.shape[0], self.hq * c.hd)
 
     def attention(self, lw: LayerWeights, n1, meta: AttnMeta, kc, vc):

@@ -130,6 +130,14 @@ class Comm:
             dist.broadcast(t, src=src, group=self.group)
         return t
 
+    def broadcast_object(self, obj, src: int = 0):
+        """Any picklable host value from `src` to every rank (the chat loop's input line)."""
+        if self.world == 1:
+            return obj
+        box = [obj]
+        dist.broadcast_object_list(box, src=src, group=self.group)
+        return box[0]
+
     def all_gather_object(self, obj):
         if self.world == 1:
             return [obj]
