@@ -345,3 +345,76 @@ def test_moe_align_is_a_permutation(tokens):
     assert torch.equal(m[1:25] - m[:24], counts.to(torch.int32))
     pp = pair_pos.cpu()
     assert (pp[~local] == -1).all() and torch.equal(pp[sp], torch.arange(n, dtype=torch.int32))
+
+
+_BOUNDS_WORKER = r"""
+import os, sys, torch
+sys.path.insert(0, os.environ["ZB_ROOT"])
+from zml_b200 import ops
+from zml_b200.ops import _lib
+assert _lib.bounds_check_build(), "the bounds-checking library is not the one that was loaded"   # nothing below runs otherwise
+dev = "cuda"
+g = torch.Generator(device=dev).manual_seed(0)
+bf = lambda *s: (torch.randn(*s, device=dev, generator=g) * 0.5).to(torch.bfloat16)
+i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+
+# the small-shape kernel cases run clean under the checks
+a, w = bf(8, 256), bf(384, 256)
+assert torch.allclose(ops.gemm(a, w).float(), a.float() @ w.float().t(), atol=0.5, rtol=0.05)
+x = bf(4, 256)
+ops.rmsnorm(x, torch.ones(256, device=dev, dtype=torch.bfloat16))
+table = bf(100, 64)
+assert torch.equal(ops.embedding(i32([3, 99, 0]), table), table[[3, 99, 0]])
+hq, hkv, hd, page, pages = 4, 2, 64, 16, 8
+_lib.set_bounds_extents(pages, 0)
+kc = torch.zeros(pages, page, hkv, hd, device=dev, dtype=torch.bfloat16)
+vc = torch.zeros_like(kc)
+inv = torch.rand(hd // 2, device=dev)
+qkv = bf(3, (hq + 2 * hkv) * hd)
+ops.rope_kvwrite(qkv, i32([0, 1, 2]), i32([16, 17, -1]), inv, kc, vc, hq, hkv, hd)
+q = bf(2, hq, hd)
+ops.paged_decode(q, kc, vc, i32([[1, 2, 0, 0], [3, 0, 0, 0]]), i32([20, 5]))
+ops.raise_on_status()
+print("CLEAN", flush=True)
+
+def expect(kernel, index, fn):
+    fn()
+    try:
+        ops.raise_on_status()
+    except _lib.BoundsError as e:
+        assert e.kernel == kernel and e.index == index, (e.kernel, e.site, e.index)
+        print("CAUGHT", kernel, index, flush=True)
+        return
+    raise AssertionError(f"{kernel}: index {index} was not reported")
+
+# a token id past the vocabulary, a KV slot past the cache, a page number past the pool: reported, not accessed
+expect("embedding", 100, lambda: ops.embedding(i32([3, 100]), table))
+expect("rope_kvwrite", pages * page + 5, lambda: ops.rope_kvwrite(qkv, i32([0, 1, 2]), i32([16, pages * page + 5, -1]), inv, kc, vc, hq, hkv, hd))
+expect("paged_decode", 4000, lambda: ops.paged_decode(q, kc, vc, i32([[1, 4000, 0, 0], [3, 0, 0, 0]]), i32([20, 5])))
+# and the context is intact
+assert torch.equal(ops.embedding(i32([5]), table), table[[5]])
+ops.raise_on_status()
+print("BOUNDS_OK", flush=True)
+"""
+
+
+@pytest.mark.gpu
+def test_bounds_checking_build_reports_bad_indices(tmp_path):
+    """The same sources built with -DZB_BOUNDS_CHECK (libzb_cuda_bc.so): small-shape cases run clean, and an index
+    read from memory that lies outside its extent is recorded in the status word (kernel, site, index) and the
+    access skipped, where the normal build masks it silently.  Runs in a process of its own, which loads the
+    checking library through ZB_CUDA_LIB and verifies that before it feeds any bad index."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    so = os.path.join(root, "zml_b200", "_C", "libzb_cuda_bc.so")
+    if not os.path.exists(so):
+        from zml_b200 import _build
+        _build.build_cuda(extra_flags=["-DZB_BOUNDS_CHECK", "-rdc=true"], variant="bc")
+    script = tmp_path / "w.py"
+    script.write_text(_BOUNDS_WORKER)
+    r = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, ZB_ROOT=root, ZB_CUDA_LIB=so))
+    assert r.returncode == 0 and "BOUNDS_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-2500:]
+    assert r.stdout.count("CAUGHT") == 3

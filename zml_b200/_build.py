@@ -8,8 +8,9 @@ Two shared objects are produced next to the sources, never installed elsewhere:
 * ``zml_b200/_C/libzb_host.so``  - ``csrc/host/*.cpp`` compiled by ``g++``: the
   safetensors reader, tracer, tokenizer and monitor back-ends.  CPU only.
 
-The role of this file is what Bazel + the downloaded binaries play in the
-reference (platforms/cuda/cuda.bzl, third_party/*/repo.bzl).
+The reference gets its native parts from Bazel rules and from binaries downloaded at build time
+(platforms/cuda/cuda.bzl, third_party/*/repo.bzl); here everything native is compiled from the sources in this
+tree by the two functions below.
 """
 from __future__ import annotations
 
@@ -56,31 +57,39 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError("build step failed: %s\n%s\n%s" % (" ".join(cmd), r.stdout, r.stderr))
 
 
-def build_cuda(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None) -> Path:
+def build_cuda(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None,
+               variant: str = "") -> Path:
+    """Builds `_C/libzb_cuda.so`.  With `variant` (and usually `extra_flags`) the same sources are built into
+    `_C/libzb_cuda_<variant>.so` with objects of their own - e.g. `variant="bc", extra_flags=["-DZB_BOUNDS_CHECK"]`,
+    the checking build that `ZB_CUDA_LIB` then selects."""
     nvcc = _nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found; cannot build libzb_cuda.so")
     srcs = sorted(CSRC.glob("*.cu"))
     hdrs = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    target = OUT / "libzb_cuda.so"
+    target = OUT / (f"libzb_cuda_{variant}.so" if variant else "libzb_cuda.so")
     if not force and _newer(target, srcs + hdrs):
         return target
+    obj_dir = OBJ.parent / (f"obj_{variant}" if variant else "obj")
     OUT.mkdir(parents=True, exist_ok=True)
-    OBJ.mkdir(parents=True, exist_ok=True)
+    obj_dir.mkdir(parents=True, exist_ok=True)
     flags = NVCC_FLAGS + (extra_flags or []) + (["-Xptxas", "-v"] if verbose else [])
 
     def compile_one(src: Path) -> Path:
-        obj = OBJ / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         if force or not _newer(obj, [src] + hdrs):
             _run([nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)])
         return obj
 
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
         objs = list(ex.map(compile_one, srcs))
-    _run([nvcc, "-shared", "-o", str(target), *map(str, objs), "-lpthread", "-ldl"])
+    # link beside the target and rename: a reader never sees a half-written library
+    tmp = target.with_suffix(".so.tmp")
+    _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-lpthread", "-ldl"])
     # every symbol must resolve at load time (works without a GPU or a driver)
     import ctypes
-    ctypes.CDLL(str(target), mode=getattr(os, "RTLD_NOW", 2))
+    ctypes.CDLL(str(tmp), mode=getattr(os, "RTLD_NOW", 2))
+    os.replace(tmp, target)
     return target
 
 

@@ -352,7 +352,8 @@ __global__ void __launch_bounds__(128) zb_paged_decode_kernel(const AttnParams p
   auto issue = [&](int blk, int stage) {
     if (blk < blk1) {
       const int tok0 = blk << 4;
-      const int page = bt[tok0 / p.page_size];
+      int page = bt[tok0 / p.page_size];
+      if (!ZB_BC_OK(page, ZB_BC_PAGES, kKernelDecode, 10)) page = 0;      // checking build: reported, page 0 read instead
       const int off0 = tok0 % p.page_size;
       const size_t base = (static_cast<size_t>(page) * p.page_size + off0) * row_elems +
                           static_cast<size_t>(kvh) * HD;
@@ -462,7 +463,8 @@ __global__ void __launch_bounds__(160) zb_paged_decode_tma_kernel(const __grid_c
       uint32_t stage = 0, phase = 0;
       for (int t = tile0; t < tile1; ++t) {
         if (!zb_mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) break;
-        const int page = bt[t];
+        int page = bt[t];
+        if (!ZB_BC_OK(page, ZB_BC_PAGES, kKernelDecode, 11)) page = 0;
         uint8_t* ks = smem + stage * 2 * kTileBytes;
         zb_mbar_expect_tx(&full_bar[stage], 2 * kTileBytes);
         zb_tma_load_4d(ks, &tmap_k, &full_bar[stage], 0, page * 64, 0, kvh);
@@ -594,7 +596,8 @@ __global__ void __launch_bounds__(128) zb_paged_prefill_kernel(const AttnParams 
       const int tok = tile * 64 + row;
       const bool valid = tok < len;
       const int tk = valid ? tok : 0;
-      const int page = bt[tk / p.page_size];
+      int page = bt[tk / p.page_size];
+      if (!ZB_BC_OK(page, ZB_BC_PAGES, kKernelPrefill, 10)) page = 0;
       const size_t goff = (static_cast<size_t>(page) * p.page_size + tk % p.page_size) * row_elems +
                           static_cast<size_t>(kvh) * HD + chunk * 8;
       cp_async16(ks + tile_off<HD>(row, chunk), p.k_cache + goff, valid ? 16u : 0u);

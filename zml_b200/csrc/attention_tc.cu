@@ -178,7 +178,8 @@ zb_paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __g
             break;
           }
         }
-        const int page = bt[j];
+        int page = bt[j];
+        if (!ZB_BC_OK(page, ZB_BC_PAGES, kKernelId, 10)) page = 0;
         zb_mbar_expect_tx(&k_full[stage], kKvBytes);
         zb_tma_load_4d(k_s + stage * kKvBytes, &tmap_k, &k_full[stage], 0, page * kKeys, 0, kvh);
         zb_mbar_expect_tx(&v_full[stage], kKvBytes);

@@ -48,6 +48,36 @@ ZB_DEVICE void zb_record_error(ZbStatus* st, uint32_t code, uint32_t kernel,
   }
 }
 
+// ----------------------------------------------------------------------------
+// Bounds-checking build (-DZB_BOUNDS_CHECK -rdc=true, built beside the normal library as libzb_cuda_bc.so): every
+// index that a kernel reads from memory (token ids, KV slots, page numbers, expert ids, state slots) is checked
+// against its extent before it is used; a bad one is RECORDED in the status word as ZB_ERR_BOUNDS with the kernel
+// id, the site and the index, and the access is skipped.  The normal build masks the same indices silently (or
+// trusts them where it has no extent).  Extents a kernel's arguments do not carry (the number of KV pages) are
+// declared once by the host with zb_bc_set_extents.  Stands in for compute-sanitizer's memcheck.
+// ----------------------------------------------------------------------------
+#ifdef ZB_BOUNDS_CHECK
+struct ZbBcExtents {
+  long long num_pages;        // pages of the paged KV cache (0 = not declared: page numbers are not checked)
+  long long num_state_slots;  // rows of the recurrent-state pools (0 = not declared)
+};
+extern __device__ ZbStatus* zb_bc_status;
+extern __device__ ZbBcExtents zb_bc_ext;
+// true when idx is inside [0, extent); records the first offender otherwise.  extent <= 0: unchecked.
+ZB_DEVICE bool zb_bc_ok(long long idx, long long extent, uint32_t kernel, uint32_t site) {
+  if (extent <= 0 || (idx >= 0 && idx < extent)) return true;
+  zb_record_error(zb_bc_status, ZB_ERR_BOUNDS, kernel, site, static_cast<uint32_t>(idx));
+  return false;
+}
+#define ZB_BC_OK(idx, extent, kernel, site) zb_bc_ok((idx), (extent), (kernel), (site))
+#define ZB_BC_PAGES (zb_bc_ext.num_pages)
+#define ZB_BC_STATE_SLOTS (zb_bc_ext.num_state_slots)
+#else
+#define ZB_BC_OK(idx, extent, kernel, site) true
+#define ZB_BC_PAGES 0
+#define ZB_BC_STATE_SLOTS 0
+#endif
+
 ZB_DEVICE uint64_t zb_globaltimer() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

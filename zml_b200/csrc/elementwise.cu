@@ -11,6 +11,9 @@
 #include "host_api.h"
 
 namespace {
+constexpr uint32_t kKernelRopeKvWrite = 20;
+constexpr uint32_t kKernelEmbedding = 21;
+constexpr uint32_t kKernelDecodeAdvance = 22;
 
 // ---------------------------------------------------------------- RMSNorm
 // y = x_total * rsqrt(mean(x_total^2) + eps) * (w or 1 + w), x_total = x (+ residual).
@@ -157,7 +160,8 @@ __global__ void __launch_bounds__(128) zb_rope_kvwrite_kernel(const RopeParams p
     }
   }
   const long long slot = p.slot_mapping[tok];
-  const bool slot_ok = slot >= 0 && slot < p.num_slots;
+  // negative = padding row (no KV write); the checking build reports a slot past the cache instead of dropping it
+  const bool slot_ok = slot >= 0 && slot < p.num_slots && ZB_BC_OK(slot, p.num_slots, kKernelRopeKvWrite, 1);
   for (int h = h_begin; h < h_end; ++h) {
     const __nv_bfloat16* __restrict__ src = p.qkv + static_cast<size_t>(tok) * p.qkv_stride + static_cast<size_t>(h) * p.hd;
     const bool is_q = h < p.hq;
@@ -279,7 +283,10 @@ __global__ void __launch_bounds__(128) zb_embedding_kernel(const int32_t* __rest
   const int t = blockIdx.x;
   if (t >= tokens) return;
   int id = ids[t];
-  if (id < 0 || id >= vocab) id = 0;
+  if (id < 0 || id >= vocab) {
+    (void)ZB_BC_OK(id, vocab, kKernelEmbedding, 1);      // the checking build reports the id; both builds read row 0
+    id = 0;
+  }
   const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * d);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * d);
   for (int i = threadIdx.x; i < d / 8; i += 128) dst[i] = src[i];
@@ -516,7 +523,9 @@ __global__ void zb_decode_advance_kernel(const int32_t* __restrict__ sampled, in
     positions[b] = pos;
     seq_lens[b] = pos + 1;
     const int pg = pos / page_size;
-    slot_mapping[b] = pg < max_pages ? block_table[static_cast<size_t>(b) * max_pages + pg] * page_size + pos % page_size : -1;
+    int page = pg < max_pages ? block_table[static_cast<size_t>(b) * max_pages + pg] : -1;
+    if (page >= 0 && !ZB_BC_OK(page, ZB_BC_PAGES, kKernelDecodeAdvance, 1)) page = -1;
+    slot_mapping[b] = page >= 0 ? page * page_size + pos % page_size : -1;
     if (step < history_rows) history[static_cast<size_t>(step) * history_stride + b] = tok;
   }
 }

@@ -20,6 +20,8 @@
 #include "host_api.h"
 
 namespace {
+constexpr uint32_t kKernelCausalConv = 24;
+constexpr uint32_t kKernelGdnScan = 25;
 
 // ------------------------------------------------------------------------------------------
 struct ConvParams {
@@ -50,6 +52,7 @@ __global__ void __launch_bounds__(128) zb_causal_conv1d_kernel(const ConvParams 
   const int t0 = p.q_start[s], t1 = p.q_start[s + 1];
   if (t1 <= t0) return;
   const bool fresh = p.seq_lens[s] - (t1 - t0) <= 0;
+  if (!ZB_BC_OK(p.slots[s], ZB_BC_STATE_SLOTS, kKernelCausalConv, 1)) return;
   __nv_bfloat16* st = p.state + static_cast<size_t>(p.slots[s]) * (K - 1) * p.channels + c;
   float w[K], win[K - 1];
 #pragma unroll
@@ -110,6 +113,7 @@ __global__ void __launch_bounds__(256) zb_gated_delta_scan_kernel(const GdnParam
   const int t0 = p.q_start[s], t1 = p.q_start[s + 1];
   const int n = t1 - t0;
   if (n <= 0) return;
+  if (!ZB_BC_OK(p.slots[s], ZB_BC_STATE_SLOTS, kKernelGdnScan, 1)) return;      // uniform over the block: no barrier is skipped by a part of it
   float* sq = gdn_smem;                       // [CH][DK]
   float* sk = sq + kGdnChunk * DK;            // [CH][DK]
   float* sv = sk + kGdnChunk * DK;            // [CH][dv]

@@ -3,7 +3,14 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "common.cuh"
 #include "host_api.h"
+
+#ifdef ZB_BOUNDS_CHECK
+// one copy per device for the whole library (relocatable device code): see common.cuh
+__device__ ZbStatus* zb_bc_status = nullptr;
+__device__ ZbBcExtents zb_bc_ext = {0, 0};
+#endif
 
 namespace {
 constexpr int kMaxDevices = 16;
@@ -66,6 +73,9 @@ int zb_init(int device) {
   s.attn_counters_len = 1 << 16;
   if (cudaMalloc(&s.attn_counters, sizeof(uint32_t) * s.attn_counters_len) != cudaSuccess) return -8;
   cudaMemset(s.attn_counters, 0, sizeof(uint32_t) * s.attn_counters_len);
+#ifdef ZB_BOUNDS_CHECK
+  if (cudaMemcpyToSymbol(zb_bc_status, &s.status, sizeof(s.status)) != cudaSuccess) return -9;
+#endif
   cudaDeviceSynchronize();
   g_ready[device] = true;
   if (prev >= 0 && prev != device) cudaSetDevice(prev);
@@ -93,6 +103,28 @@ int zb_status_reset() {
   ZbDeviceState* s = zb_device_state();
   if (!s) return -1;
   return static_cast<int>(cudaMemset(s->status, 0, sizeof(ZbStatus)));
+}
+
+// 1 in the bounds-checking build of the library, 0 in the normal one.
+int zb_bc_enabled() {
+#ifdef ZB_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Declares the extents that kernel arguments do not carry (bounds-checking build; a no-op otherwise).
+int zb_bc_set_extents(long long num_pages, long long num_state_slots) {
+#ifdef ZB_BOUNDS_CHECK
+  if (!zb_device_state()) return -1;
+  ZbBcExtents e = {num_pages, num_state_slots};
+  return static_cast<int>(cudaMemcpyToSymbol(zb_bc_ext, &e, sizeof(e)));
+#else
+  (void)num_pages;
+  (void)num_state_slots;
+  return 0;
+#endif
 }
 
 unsigned long long zb_launch_count() { return g_launches.load(); }

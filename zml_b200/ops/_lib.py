@@ -42,6 +42,8 @@ _SIGS = {
     "zb_status_read": (c_i, [c_p]),
     "zb_status_reset": (c_i, []),
     "zb_status_ptr": (c_p, []),
+    "zb_bc_enabled": (c_i, []),
+    "zb_bc_set_extents": (c_i, [c_ll, c_ll]),
     "zb_launch_count": (c_ull, []),
     "zb_launch_count_reset": (None, []),
     "zb_launch_count_add": (None, [c_ull]),
@@ -136,7 +138,28 @@ def check(rc: int, what: str) -> None:
 STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out",
                 3: "index out of bounds", 4: "bad argument"}
 KERNEL_NAMES = {1: "gemm_bf16", 2: "paged_decode", 3: "paged_prefill", 4: "gemm_ar_fused",
-                5: "comm_barrier", 6: "moe_grouped_gemm", 7: "moe_a2a", 8: "wait_probe"}
+                5: "comm_barrier", 6: "moe_grouped_gemm", 7: "moe_a2a", 8: "wait_probe", 9: "moe_grouped_gemm_w4",
+                10: "moe_combine", 11: "allreduce_ll", 12: "allreduce_mm", 13: "paged_prefill_tc", 14: "gemm_2cta",
+                20: "rope_kvwrite", 21: "embedding", 22: "decode_advance", 24: "causal_conv1d", 25: "gated_delta_scan"}
+
+
+class BoundsError(KernelError):
+    """The bounds-checking build of the library saw an index outside its extent (`kernel`, `site`, `index`); the
+    access was skipped."""
+
+    def __init__(self, msg: str, kernel: str, site: int, index: int):
+        super().__init__(msg)
+        self.kernel, self.site, self.index = kernel, site, index
+
+
+def bounds_check_build() -> bool:
+    """True when the loaded library is the bounds-checking build (`ZB_CUDA_LIB=.../libzb_cuda_bc.so`)."""
+    return bool(lib().zb_bc_enabled())
+
+
+def set_bounds_extents(num_pages: int = 0, num_state_slots: int = 0) -> None:
+    """Declares the extents that kernel arguments do not carry (checked by the bounds-checking build only)."""
+    check(lib().zb_bc_set_extents(int(num_pages), int(num_state_slots)), "zb_bc_set_extents")
 
 
 def read_status() -> tuple[int, int, int, int]:
@@ -157,6 +180,8 @@ def raise_on_status() -> None:
             import os
             raise CollectiveTimeout(msg, str(KERNEL_NAMES.get(kernel, kernel)), where, detail,
                                     int(os.environ.get("RANK", "0")))
+        if code == 3:
+            raise BoundsError(msg, str(KERNEL_NAMES.get(kernel, kernel)), where, detail if detail < 2 ** 31 else detail - 2 ** 32)
         raise KernelError(msg)
 
 

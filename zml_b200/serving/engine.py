@@ -143,6 +143,9 @@ class Engine:
         self.stateful = hasattr(model, "alloc_state")
         if self.stateful:
             model.alloc_state(self.num_slots + 1)
+        if self.on_gpu:
+            # read by the bounds-checking build of the library only: the extents kernel arguments do not carry
+            _lib.set_bounds_extents(num_pages, self.num_slots + 1 if self.stateful else 0)
 
     # ------------------------------------------------------------------ helpers
     def set_seed(self, seed: int) -> None:
