@@ -191,10 +191,12 @@ def test_nvfp4_linear_runs_on_the_bf16_gemm():
 
 @pytest.mark.parametrize("tokens,e_local,k_top,d,f", [(24, 8, 2, 256, 256), (128, 16, 4, 512, 768), (7, 4, 1, 256, 512), (300, 8, 2, 512, 256),
                                                      (9, 4, 2, 128, 128)])
-def test_moe_grouped_gemm_nvfp4_weights(tokens, e_local, k_top, d, f):
-    """NVFP4 expert weights de-quantised inside the grouped GEMM == the bf16 kernels on the de-quantised weights
-    (the last case has K = 128, which the NVFP4 kernel does not take: the bf16 kernels run)."""
+def test_moe_grouped_gemm_nvfp4_weights(tokens, e_local, k_top, d, f, monkeypatch):
+    """NVFP4 expert weights de-quantised inside the grouped GEMM (bf16 activations, `ZB_MOE_FP4=a16`) == the bf16
+    kernels on the de-quantised weights (the last case has K = 128, which the NVFP4 kernel does not take: the bf16
+    kernels run)."""
     from zml_b200 import moe
+    monkeypatch.setenv("ZB_MOE_FP4", "a16")
     torch.manual_seed(tokens)
     gate = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
     up = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
@@ -217,3 +219,76 @@ def test_moe_grouped_gemm_nvfp4_weights(tokens, e_local, k_top, d, f):
     g, u = moe.deinterleave_gate_up(gu_bf)
     ref = moe.reference_fused_experts(x.cpu(), ids.cpu(), w.cpu(), g.cpu(), u.cpu(), dn_bf.cpu(), 0)
     expect_close(got.float().cpu(), ref.float(), atol=3e-2, rtol=3e-2, min_close=0.99)
+
+
+def _offsets(counts):
+    off = [0]
+    for c in counts:
+        off.append(off[-1] + c)
+    return torch.tensor(off, dtype=torch.int32, device=DEV), off[-1]
+
+
+@pytest.mark.parametrize("e,n,k,counts,swiglu,avg", [
+    (2, 128, 256, [5, 3], False, 8),
+    (4, 256, 512, [16, 0, 7, 33], True, 8),
+    (8, 512, 1024, [40, 1, 0, 64, 17, 3, 90, 8], False, 32),
+    (8, 512, 1024, [40, 1, 0, 64, 17, 3, 90, 8], True, 64),
+    (3, 256, 768, [200, 130, 5], False, 100),
+])
+def test_block_scaled_nvfp4_grouped_gemm(e, n, k, counts, swiglu, avg):
+    """`tcgen05.mma.kind::mxf4nvf4.block_scale` on NVFP4 weights and NVFP4 activations == a float32 matmul of the
+    de-quantised operands (`nn/quant.py`), for token tiles of 16 to 128, with and without the SwiGLU epilogue."""
+    from zml_b200 import moe
+    from zml_b200.nn import quant as Q
+    torch.manual_seed(e * 7 + n)
+    wq = moe.Nvfp4Experts.quantize((torch.randn(e, n, k, device=DEV) * 0.05).bfloat16())
+    meta, cap = _offsets(counts)
+    xs = torch.randn(cap, k, device=DEV).bfloat16()
+    got = moe.grouped_gemm_fp4(xs, wq, meta, swiglu=swiglu, avg_tokens=avg)
+    codes, scales = Q.quantize_nvfp4(xs.cpu(), None)
+    xq = Q.dequantize_nvfp4(codes, scales, None, torch.float32)
+    wd = wq.dequantize(torch.float32).cpu()
+    off = meta.cpu().tolist()
+    want = torch.zeros(cap, n // 2 if swiglu else n)
+    for i in range(e):
+        a, b = off[i], off[i + 1]
+        y = xq[a:b] @ wd[i].t()
+        if swiglu:
+            y = y.reshape(b - a, n // 128, 2, 64)
+            y = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(b - a, n // 2)
+        want[a:b] = y
+    expect_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2, min_close=0.995)
+
+
+def test_block_scaled_nvfp4_expert_block():
+    """The whole expert block on the block-scaled path: the gather quantises the activations, the gate|up GEMM
+    quantises its SwiGLU output in the epilogue (bit-equal to the stand-alone quantiser), and the result equals the
+    CPU restatement of the same recipe; against bf16 activations the difference is the 4-bit activation noise."""
+    from zml_b200 import moe
+    torch.manual_seed(3)
+    wq = moe.Nvfp4Experts.quantize((torch.randn(4, 512, 512, device=DEV) * 0.05).bfloat16())
+    meta, cap = _offsets([16, 0, 7, 33])
+    xq = moe.Fp4Activations.quantize(torch.randn(cap, 512, device=DEV).bfloat16())
+    h = moe.grouped_gemm_fp4(xq, wq, meta, swiglu=True, avg_tokens=8)
+    hq = moe.grouped_gemm_fp4(xq, wq, meta, swiglu=True, avg_tokens=8, quantize_out=True)
+    want = moe.Fp4Activations.quantize(h)
+    assert (hq.codes == want.codes).float().mean().item() > 0.999
+    assert (hq.scales.view(torch.uint8) == want.scales.view(torch.uint8)).float().mean().item() > 0.999
+    for tokens in (32, 300):
+        e_local, k_top, d, f = 16, 4, 512, 768
+        gate = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
+        up = (torch.randn(e_local, f, d, device=DEV) * 0.05).bfloat16()
+        down = (torch.randn(e_local, d, f, device=DEV) * 0.05).bfloat16()
+        gu_q = moe.Nvfp4Experts.quantize(moe.interleave_gate_up(gate, up))
+        dn_q = moe.Nvfp4Experts.quantize(down)
+        gu_bf, dn_bf = gu_q.dequantize(), dn_q.dequantize()
+        x = torch.randn(tokens, d, device=DEV).bfloat16()
+        ids, wts = moe.router_topk(torch.randn(tokens, e_local, device=DEV), k_top, True)
+        assert moe.fp4_activations()
+        y = moe.fused_experts(x, ids, wts, gu_bf, dn_bf, 0, e_local, w4=(gu_q, dn_q))
+        cpu_q = (moe.Nvfp4Experts.quantize(moe.interleave_gate_up(gate, up).cpu()), moe.Nvfp4Experts.quantize(down.cpu()))
+        yc = moe.fused_experts(x.cpu(), ids.cpu(), wts.cpu(), gu_bf.cpu(), dn_bf.cpu(), 0, e_local, w4=cpu_q)
+        assert ((y.float().cpu() - yc.float()).norm() / yc.float().norm()).item() < 0.05
+        ybf = moe.fused_experts(x, ids, wts, gu_bf, dn_bf, 0, e_local)
+        assert ((y.float() - ybf.float()).norm() / ybf.float().norm()).item() < 0.3
+    ops.raise_on_status()

@@ -135,3 +135,34 @@ def test_rope_layouts_and_scalings():
     assert nn.Scaling.from_hf({"rope_type": "unknown-kind"}).kind == "default"
     with pytest.raises(ValueError):
         nn.Scaling.from_hf({"factor": 2})
+
+
+def test_nvfp4_block_scaled_weight_layout_and_cpu_recipe():
+    """`nvfp4_pack_blocks_mma` writes, per (128 rows x 256 K) tile, the shared-memory image the block-scaled MMA reads:
+    codes with the 128-byte swizzle and four [32 rows][4 row groups][4 scales] images; and the CPU restatement of the
+    NVFP4-activation path quantises the activations (so it differs from bf16 activations by 4-bit noise only)."""
+    import random
+    from zml_b200 import moe
+    from zml_b200.moe import ops as m
+    e, n, k = 2, 256, 512
+    g = torch.Generator().manual_seed(0)
+    codes = torch.randint(0, 256, (e * n, k // 2), dtype=torch.uint8, generator=g)
+    scales = torch.randint(0, 120, (e * n, k // 16), dtype=torch.uint8, generator=g)
+    b = m.nvfp4_pack_blocks_mma(codes, scales.view(torch.float8_e4m3fn), e, n, k)
+    assert b.shape == (e, n // 128, k // 256, 18432)
+    rnd = random.Random(1)
+    for _ in range(500):
+        ee, t, kc, r = rnd.randrange(e), rnd.randrange(n // 128), rnd.randrange(k // 256), rnd.randrange(128)
+        j, bb, jj, s_ = rnd.randrange(8), rnd.randrange(16), rnd.randrange(4), rnd.randrange(4)
+        assert codes[ee * n + t * 128 + r, kc * 128 + j * 16 + bb] == b[ee, t, kc, r * 128 + ((j ^ (r % 8)) * 16) + bb]
+        assert scales[ee * n + t * 128 + r, kc * 16 + jj * 4 + s_] == b[ee, t, kc, 16384 + jj * 512 + (r % 32) * 16 + (r // 32) * 4 + s_]
+    w = (torch.randn(2, 256, 256, generator=g) * 0.05).bfloat16()
+    wq = moe.Nvfp4Experts.quantize(w)
+    meta = torch.tensor([0, 5, 12], dtype=torch.int32)
+    xs = torch.randn(12, 256, generator=g).bfloat16()
+    y4 = moe.grouped_gemm_fp4(xs, wq, meta)
+    y16 = moe.grouped_gemm(xs, wq.dequantize(), meta)
+    rel = ((y4.float() - y16.float()).norm() / y16.float().norm()).item()
+    assert 0.01 < rel < 0.25
+    hq = moe.grouped_gemm_fp4(xs, wq, meta, swiglu=True, quantize_out=True)
+    assert hq.codes.shape == (12, 64) and hq.scales.shape == (12, 8)

@@ -161,7 +161,8 @@ __global__ void __launch_bounds__(128) zb_rope_kvwrite_kernel(const RopeParams p
   }
   const long long slot = p.slot_mapping[tok];
   // negative = padding row (no KV write); the checking build reports a slot past the cache instead of dropping it
-  const bool slot_ok = slot >= 0 && slot < p.num_slots && ZB_BC_OK(slot, p.num_slots, kKernelRopeKvWrite, 1);
+  if (slot >= p.num_slots) (void)ZB_BC_OK(slot, p.num_slots, kKernelRopeKvWrite, 1);
+  const bool slot_ok = slot >= 0 && slot < p.num_slots;
   for (int h = h_begin; h < h_end; ++h) {
     const __nv_bfloat16* __restrict__ src = p.qkv + static_cast<size_t>(tok) * p.qkv_stride + static_cast<size_t>(h) * p.hd;
     const bool is_q = h < p.hq;

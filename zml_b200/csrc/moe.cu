@@ -13,6 +13,7 @@
 #include "common.cuh"
 #include "host_api.h"
 #include "moe_tiles.cuh"
+#include "quant.cuh"
 
 int zb_make_tmap_bf16_2d(CUtensorMap* out, const void* base, int rows, int k, int ld, int box_rows);
 
@@ -227,6 +228,34 @@ __global__ void __launch_bounds__(128) zb_moe_gather_kernel(const __nv_bfloat16*
     const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * d);
     uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(pos) * d);
     for (int i = threadIdx.x; i < d / 8; i += 128) dst[i] = src[i];
+  }
+}
+
+// The gather with the NVFP4 activation quantiser behind it: xq[pos, :] = e2m1 codes of x[sorted_pair[pos] / k, :],
+// xsf[pos, :] = one f8e4m3 scale per 16 values (same numerics as zb_nvfp4_quantize without a per-tensor scale).
+// One thread per 16-value block.
+__global__ void __launch_bounds__(128) zb_moe_gather_fp4_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const int32_t* __restrict__ sorted_pair,
+                                                                const int32_t* __restrict__ meta, uint8_t* __restrict__ xq,
+                                                                uint8_t* __restrict__ xsf, int e_local, int k, int d, int cap) {
+  zb_pdl_launch();
+  zb_pdl_wait();
+  const int total = min(meta[e_local], cap);
+  const int kblocks = d / 16;
+  for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
+    const int t = sorted_pair[pos] / k;
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * d);
+    for (int b = threadIdx.x; b < kblocks; b += 128) {
+      const uint4 raw[2] = {src[2 * b], src[2 * b + 1]};
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(raw);
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(e[i]);
+      uint8_t s8;
+      const uint2 c = zb_nvfp4_quantize_block(v, s8);
+      *reinterpret_cast<uint2*>(xq + (static_cast<size_t>(pos) * kblocks + b) * 8) = c;
+      xsf[static_cast<size_t>(pos) * kblocks + b] = s8;
+    }
   }
 }
 
@@ -760,6 +789,19 @@ int zb_moe_gather(const void* x, const int32_t* sorted_pair, const int32_t* meta
   int blocks = cap < 2368 ? cap : 2368;
   zb_launch(zb_moe_gather_kernel, dim3(blocks), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), 
       reinterpret_cast<const __nv_bfloat16*>(x), sorted_pair, meta, reinterpret_cast<__nv_bfloat16*>(xs), e_local, k, d, cap);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// xq [cap, d / 2] bytes, xsf [cap, d / 16] bytes; d a multiple of 16.
+int zb_moe_gather_fp4(const void* x, const int32_t* sorted_pair, const int32_t* meta, void* xq, void* xsf, int e_local, int k,
+                      int d, int cap, void* stream) {
+  if (cap <= 0) return 0;
+  if (d % 16 != 0) return -62;
+  int blocks = cap < 2368 ? cap : 2368;
+  zb_launch(zb_moe_gather_fp4_kernel, dim3(blocks), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
+            reinterpret_cast<const __nv_bfloat16*>(x), sorted_pair, meta, reinterpret_cast<uint8_t*>(xq),
+            reinterpret_cast<uint8_t*>(xsf), e_local, k, d, cap);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

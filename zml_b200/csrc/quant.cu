@@ -13,37 +13,9 @@
 
 #include "common.cuh"
 #include "host_api.h"
+#include "quant.cuh"
 
 namespace {
-
-ZB_DEVICE float bf16_round(float x) { return __bfloat162float(__float2bfloat16(x)); }
-
-// round-to-nearest-even onto {0, .5, 1, 1.5, 2, 3, 4, 6}, saturating; returns the 4-bit code
-ZB_DEVICE uint32_t e2m1_code(float x) {
-  const float a = fabsf(x);
-  uint32_t idx = 0;
-  idx += a > 0.25f;     // tie 0.25 -> 0   (even mantissa)
-  idx += a >= 0.75f;    // tie 0.75 -> 1.0
-  idx += a > 1.25f;     // tie 1.25 -> 1.0
-  idx += a >= 1.75f;    // tie 1.75 -> 2.0
-  idx += a > 2.5f;      // tie 2.5  -> 2.0
-  idx += a >= 3.5f;     // tie 3.5  -> 4.0
-  idx += a > 5.0f;      // tie 5.0  -> 4.0
-  return idx | (signbit(x) ? 8u : 0u);
-}
-
-ZB_DEVICE float e2m1_value(uint32_t code) {
-  const uint32_t m = code & 7u;
-  // 0, .5, 1, 1.5, 2, 3, 4, 6
-  const float v = m < 2 ? 0.5f * static_cast<float>(m)
-                        : static_cast<float>((2u | (m & 1u)) << ((m >> 1) - 1u)) * 0.5f;
-  return (code & 8u) ? -v : v;
-}
-
-ZB_DEVICE float fp8_e4m3_to_float(uint8_t b) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(b), __NV_E4M3);
-  return __half2float(*reinterpret_cast<const __half*>(&h));
-}
 
 // one thread per 16-value block
 __global__ void __launch_bounds__(256) zb_nvfp4_quantize_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
@@ -66,14 +38,9 @@ __global__ void __launch_bounds__(256) zb_nvfp4_quantize_kernel(const __nv_bfloa
     if (global_scale != nullptr) v[i] = bf16_round(v[i] / gs);
     amax = fmaxf(amax, fabsf(v[i]));
   }
-  float s = bf16_round(amax * (1.0f / 6.0f));
-  s = fminf(fmaxf(s, 0.015625f), 448.f);
-  const uint8_t s8 = static_cast<uint8_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
-  const float div = fmaxf(fp8_e4m3_to_float(s8), 0.015625f);
-  uint32_t packed[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 16; ++i) packed[i >> 3] |= e2m1_code(bf16_round(v[i] / div)) << (4 * (i & 7));
-  *reinterpret_cast<uint2*>(codes + (static_cast<size_t>(r) * kblocks + b) * 8) = make_uint2(packed[0], packed[1]);
+  (void)amax;
+  uint8_t s8;
+  *reinterpret_cast<uint2*>(codes + (static_cast<size_t>(r) * kblocks + b) * 8) = zb_nvfp4_quantize_block(v, s8);
   scales[static_cast<size_t>(r) * kblocks + b] = s8;
 }
 

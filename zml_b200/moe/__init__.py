@@ -10,6 +10,6 @@ runs every token through the local experts with masked weights), the gate/up pro
 and SwiGLU are one grouped tcgen05 GEMM, and the cross-rank sum is done from inside a
 kernel over NVLink peer memory when symmetric memory is set up.
 """
-from .ops import (Backend, Nvfp4Experts, combine, grouped_gemm_w4, deinterleave_gate_up, finalize, forward_moe, fused_experts, gather, grouped_gemm, interleave_gate_up,  # noqa: F401
+from .ops import (Backend, Fp4Activations, Nvfp4Experts, combine, fp4_activations, gather_fp4, grouped_gemm_fp4, grouped_gemm_w4, deinterleave_gate_up, finalize, forward_moe, fused_experts, gather, grouped_gemm, interleave_gate_up,  # noqa: F401
                   nvfp4_roundtrip,
                   moe_align, reference_fused_experts, router_topk)

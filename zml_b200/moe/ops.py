@@ -197,6 +197,25 @@ def nvfp4_pack_blocks(codes: torch.Tensor, scales: torch.Tensor, e: int, n: int,
     return torch.cat([c, sc], -1).contiguous()
 
 
+def nvfp4_pack_blocks_mma(codes: torch.Tensor, scales: torch.Tensor, e: int, n: int, k: int) -> torch.Tensor:
+    """Checkpoint-order codes [E * N, K / 2] and f8e4m3fn scales [E * N, K / 16] -> the tile-major layout of the
+    block-scaled tensor-core kernel (csrc/moe_fp4.cu): uint8 [E, N / 128, K / 256, 18432].  Each block is the
+    shared-memory image of its (128 rows x 256 K) tile: 16 KB of codes with the 128-byte swizzle (16-byte chunk j
+    of row r at chunk j ^ (r % 8) of the row's 128 bytes), then four 512-byte scale images (one per K = 64):
+    [32 rows r % 32][4 row groups r / 32][4 scales]."""
+    assert n % 128 == 0 and k % 256 == 0
+    dev = codes.device
+    c = codes.reshape(e, n // 128, 128, k // 256, 8, 16)                       # [e, tile, r, kchunk, j, b]
+    r = torch.arange(128, device=dev)
+    j = torch.arange(8, device=dev)
+    src = (j[None, :] ^ (r[:, None] % 8))                                      # position p holds chunk p ^ (r % 8)
+    c = torch.gather(c, 4, src[None, None, :, None, :, None].expand(e, n // 128, 128, k // 256, 8, 16))
+    c = c.permute(0, 1, 3, 2, 4, 5).reshape(e, n // 128, k // 256, 128 * 128)
+    sc = scales.reshape(e * n, k // 16).view(torch.uint8).reshape(e, n // 128, 4, 32, k // 256, 4, 4)   # [e, tile, r/32, r%32, kchunk, j, s]
+    sc = sc.permute(0, 1, 4, 5, 3, 2, 6).reshape(e, n // 128, k // 256, 128 * 16)                       # [.., kchunk, j, r%32, r/32, s]
+    return torch.cat([c, sc], -1).contiguous()
+
+
 def nvfp4_unpack_blocks(blocks: torch.Tensor, e: int, n: int, k: int):
     """Inverse of `nvfp4_pack_blocks`: (codes [E * N, K / 2] in checkpoint order, scales [E * N, K / 16])."""
     c = blocks[..., :128 * 128].reshape(e, n // 128, k // 256, 8, 128, 16).permute(0, 1, 4, 2, 3, 5).reshape(e * n, k // 2)
@@ -270,6 +289,13 @@ class Nvfp4Experts:
             out[i] = (w * self.row_scales(i)).to(dtype)
         return out
 
+    def mma_blocks(self) -> torch.Tensor:
+        """The weights in the layout of the block-scaled tensor-core kernel (made once, on first use)."""
+        if getattr(self, "_mma_blocks", None) is None:
+            codes, scales = self.checkpoint_arrays()
+            self._mma_blocks = nvfp4_pack_blocks_mma(codes, scales, self.e, self.n, self.k)
+        return self._mma_blocks
+
     def nbytes(self) -> int:
         body = self.blocks.numel() if self.blocks is not None else self.codes.numel() + self.scales.numel()
         return body + self.gscale.numel() * 4
@@ -289,6 +315,66 @@ def grouped_gemm_w4(xs: torch.Tensor, w: Nvfp4Experts, meta: torch.Tensor, swigl
                                                  int(swiglu),
                                                  int(avg_tokens), _lib.stream_ptr()), "zb_moe_grouped_gemm_w4")
     return out
+
+
+class Fp4Activations:
+    """Activation rows in NVFP4: packed e2m1 codes [rows, K / 2] and f8e4m3fn block scales [rows, K / 16]."""
+    __slots__ = ("codes", "scales", "k")
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor):
+        self.codes, self.scales, self.k = codes, scales, codes.shape[1] * 2
+
+    @staticmethod
+    def quantize(xs: torch.Tensor) -> "Fp4Activations":
+        from ..ops import quant as opsq
+        return Fp4Activations(*opsq.nvfp4_quantize(xs.to(torch.bfloat16)))
+
+    def dequantize(self, dtype=torch.bfloat16) -> torch.Tensor:
+        from ..nn import quant as Q
+        return Q.dequantize_nvfp4(Q.unpack_e2m1(self.codes), self.scales, None, dtype)
+
+
+def gather_fp4(x: torch.Tensor, sorted_pair: torch.Tensor, meta: torch.Tensor, e_local: int, k: int, cap: int) -> Fp4Activations:
+    """`gather` with the NVFP4 activation quantiser behind it (one kernel): the rows leave as codes + block scales."""
+    d = x.shape[1]
+    if not x.is_cuda:
+        return Fp4Activations.quantize(gather(x, sorted_pair, meta, e_local, k, cap))
+    # rows past the last pair stay unwritten: the GEMM computes their columns too but never stores them
+    xq = torch.empty((cap, d // 2), dtype=torch.uint8, device=x.device)
+    xsf = torch.empty((cap, d // 16), dtype=torch.uint8, device=x.device)
+    _lib.check(_lib.lib().zb_moe_gather_fp4(x.data_ptr(), sorted_pair.data_ptr(), meta.data_ptr(), xq.data_ptr(), xsf.data_ptr(),
+                                            e_local, k, d, cap, _lib.stream_ptr()), "zb_moe_gather_fp4")
+    return Fp4Activations(xq, xsf.view(torch.float8_e4m3fn))
+
+
+def grouped_gemm_fp4(xs, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8,
+                     quantize_out: bool = False):
+    """`grouped_gemm` with NVFP4 weights AND NVFP4 activations (one f8e4m3 scale per 16 values on both sides),
+    multiplied by the block-scaled tensor-core instruction (libzb_cuda.so: zb_moe_grouped_gemm_fp4).  `xs` is an
+    `Fp4Activations` or a bf16 tensor (quantised first).  `quantize_out` (with `swiglu`): the result is returned as
+    `Fp4Activations`, quantised in the kernel's epilogue.  CPU tensors: de-quantise both sides, then the float path."""
+    if not isinstance(xs, Fp4Activations):
+        xs = Fp4Activations.quantize(xs)
+    if not xs.codes.is_cuda or not w.kernel_ready:
+        out = grouped_gemm(xs.dequantize(torch.float32), w.dequantize(torch.float32), meta, swiglu, avg_tokens).to(torch.bfloat16)
+        return Fp4Activations.quantize(out) if quantize_out else out
+    cap = xs.codes.shape[0]
+    n_out = w.n // 2 if swiglu else w.n
+    assert xs.k == w.k and xs.codes.is_contiguous() and xs.scales.is_contiguous()
+    dev = xs.codes.device
+    out = oq = osf = None
+    if quantize_out:
+        assert swiglu and n_out % 64 == 0
+        oq = torch.empty((cap, n_out // 2), dtype=torch.uint8, device=dev)
+        osf = torch.empty((cap, n_out // 16), dtype=torch.uint8, device=dev)
+    else:
+        out = torch.empty((cap, n_out), dtype=torch.bfloat16, device=dev)
+    ptr = lambda t: t.data_ptr() if t is not None else None
+    _lib.check(_lib.lib().zb_moe_grouped_gemm_fp4(xs.codes.data_ptr(), xs.scales.data_ptr(), None, w.mma_blocks().data_ptr(),
+                                                  w.gscale.data_ptr(), int(w.gscale.shape[1]), ptr(out), ptr(oq), ptr(osf),
+                                                  meta.data_ptr(), w.e, w.n, w.k, cap, n_out, int(swiglu), int(avg_tokens),
+                                                  _lib.stream_ptr()), "zb_moe_grouped_gemm_fp4")
+    return Fp4Activations(oq, osf.view(torch.float8_e4m3fn)) if quantize_out else out
 
 
 def finalize(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, tokens: int, k: int):
@@ -330,6 +416,16 @@ def combine(o: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor, toke
 W4_MAX_AVG_TOKENS = 32      # NVFP4 kernel: tiles of at most 64 tokens per expert
 
 
+FP4_MAX_AVG_TOKENS = 128
+
+
+def fp4_activations() -> bool:
+    """NVFP4 expert weights are multiplied with NVFP4 activations on the block-scaled tensor-core path (`ZB_MOE_FP4=a4`,
+    the default) or with bf16 activations after de-quantising the weights inside the kernel (`ZB_MOE_FP4=a16`)."""
+    import os
+    return os.environ.get("ZB_MOE_FP4", "a4") != "a16"
+
+
 def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w_gate_up_il: torch.Tensor,
                   w_down: torch.Tensor, e0: int = 0, num_experts_total: Optional[int] = None,
                   w4: Optional[tuple] = None, extra=None, residual=None, fused=None) -> torch.Tensor:
@@ -344,6 +440,17 @@ def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor,
     cap = t * k
     avg = max(1, (t * k) // max(total_e, 1))
     meta, sorted_pair, pair_pos = moe_align(topk_ids, e0, e_local)
+    if w4 is not None and fp4_activations() and avg <= FP4_MAX_AVG_TOKENS and w4[0].kernel_ready and w4[1].kernel_ready:
+        # NVFP4 on both sides: the gather quantises the activations, the gate|up GEMM applies SwiGLU and quantises its
+        # output, and both GEMMs run on the block-scaled tensor-core instruction.  Up to FP4_MAX_AVG_TOKENS per expert:
+        # with 128 x 128 tiles the kernel is bound by operand traffic into shared memory, and at prefill sizes the
+        # bf16 grouped GEMM on de-quantised weights is faster (787 against 559 TFLOP/s at 512 tokens per expert)
+        xq = gather_fp4(x, sorted_pair, meta, e_local, k, cap)
+        hq = grouped_gemm_fp4(xq, w4[0], meta, swiglu=True, avg_tokens=avg, quantize_out=True)
+        o = grouped_gemm_fp4(hq, w4[1], meta, swiglu=False, avg_tokens=avg)
+        if extra is None and residual is None and fused is None:
+            return finalize(o, pair_pos, topk_w, t, k)
+        return combine(o, pair_pos, topk_w, t, k, extra, residual, fused)
     xs = gather(x, sorted_pair, meta, e_local, k, cap)
     if w4 is not None and avg <= W4_MAX_AVG_TOKENS and w4[0].kernel_ready and w4[1].kernel_ready:
         # few tokens per expert: the step is bound by reading expert weights - read them as NVFP4

@@ -48,6 +48,8 @@ _SIGS = {
     "zb_launch_count_reset": (None, []),
     "zb_launch_count_add": (None, [c_ull]),
     "zb_moe_grouped_gemm_w4": (c_i, [c_p, c_p, c_p, c_i, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
+    "zb_moe_grouped_gemm_fp4": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
+    "zb_moe_gather_fp4": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p]),
     "zb_allreduce_ll": (c_i, [c_p, c_p, c_p, c_p, C.c_longlong, c_sz, c_sz, c_p]),
     "zb_moe_combine": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_sz, c_sz, c_p]),
     "zb_wait_probe": (c_i, [c_p, C.c_uint, c_ull, C.c_uint, c_p, c_p]),
