@@ -1,5 +1,7 @@
 """Linear-attention / short-conv kernels and the hybrid models on a B200, against the float32
 PyTorch restatement of the same ops on the CPU."""
+import os
+
 import pytest
 import torch
 
@@ -291,4 +293,34 @@ def test_block_scaled_nvfp4_expert_block():
         assert ((y.float().cpu() - yc.float()).norm() / yc.float().norm()).item() < 0.05
         ybf = moe.fused_experts(x, ids, wts, gu_bf, dn_bf, 0, e_local)
         assert ((y.float() - ybf.float()).norm() / ybf.float().norm()).item() < 0.3
+    ops.raise_on_status()
+
+
+@pytest.mark.parametrize("activation", ["geglu", "geglu_tanh", "relu2"])
+@pytest.mark.parametrize("tokens", [24, 600])
+def test_expert_mlp_activations(activation, tokens):
+    """geglu / geglu_tanh / relu2 in the epilogues of the grouped GEMMs (few and many tokens per expert: both tile
+    orientations; bf16 weights, NVFP4 weights with bf16 and with NVFP4 activations) == the CPU restatement."""
+    from zml_b200 import moe
+    torch.manual_seed(tokens)
+    e, f, d, k = 8, 256, 256, 2
+    gate, up, down = ((torch.randn(e, f, d, device=DEV) * 0.05).bfloat16(), (torch.randn(e, f, d, device=DEV) * 0.05).bfloat16(),
+                      (torch.randn(e, d, f, device=DEV) * 0.05).bfloat16())
+    x = torch.randn(tokens, d, device=DEV).bfloat16()
+    ids, w = moe.router_topk(torch.randn(tokens, e, device=DEV), k, True)
+    w1 = up if activation == "relu2" else moe.interleave_gate_up(gate, up)
+    got = moe.fused_experts(x, ids, w, w1, down, 0, e, activation=activation)
+    want = moe.fused_experts(x.cpu().float(), ids.cpu(), w.cpu(), w1.cpu().float(), down.cpu().float(), 0, e, activation=activation)
+    expect_close(got.float().cpu(), want, atol=2e-2, rtol=3e-2, min_close=0.99)
+    if tokens <= 64:
+        w4 = (moe.Nvfp4Experts.quantize(w1), moe.Nvfp4Experts.quantize(down))
+        w4c = (moe.Nvfp4Experts.quantize(w1.cpu()), moe.Nvfp4Experts.quantize(down.cpu()))
+        for mode in ("a16", "a4"):
+            os.environ["ZB_MOE_FP4"] = mode
+            try:
+                y = moe.fused_experts(x, ids, w, w4[0].dequantize(), w4[1].dequantize(), 0, e, w4=w4, activation=activation)
+                yc = moe.fused_experts(x.cpu(), ids.cpu(), w.cpu(), w4c[0].dequantize(), w4c[1].dequantize(), 0, e, w4=w4c, activation=activation)
+            finally:
+                os.environ.pop("ZB_MOE_FP4", None)
+            assert ((y.float().cpu() - yc.float()).norm() / yc.float().norm()).item() < 0.06, mode
     ops.raise_on_status()

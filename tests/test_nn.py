@@ -166,3 +166,30 @@ def test_nvfp4_block_scaled_weight_layout_and_cpu_recipe():
     assert 0.01 < rel < 0.25
     hq = moe.grouped_gemm_fp4(xs, wq, meta, swiglu=True, quantize_out=True)
     assert hq.codes.shape == (12, 64) and hq.scales.shape == (12, 8)
+
+
+@pytest.mark.parametrize("activation", ["swiglu", "geglu", "geglu_tanh", "relu2"])
+def test_expert_mlp_activations_cpu(activation):
+    """The expert MLP with each activation of the reference's MoE runner: gated ones on an interleaved gate|up weight,
+    relu2 on a plain up projection."""
+    from zml_b200 import moe
+    g = torch.Generator().manual_seed(4)
+    e, f, d, t, k = 4, 128, 64, 9, 2
+    gate, up, down = (torch.randn(e, f, d, generator=g) * 0.1, torch.randn(e, f, d, generator=g) * 0.1, torch.randn(e, d, f, generator=g) * 0.1)
+    x = torch.randn(t, d, generator=g)
+    ids, w = moe.router_topk(torch.randn(t, e, generator=g), k, True)
+    w1 = up if activation == "relu2" else moe.interleave_gate_up(gate, up)
+    got = moe.fused_experts(x, ids, w, w1, down, 0, e, activation=activation)
+    want = torch.zeros(t, d)
+    for ti in range(t):
+        for j in range(k):
+            ex = int(ids[ti, j])
+            if activation == "relu2":
+                h = torch.relu(up[ex] @ x[ti]).square()
+            else:
+                gt = gate[ex] @ x[ti]
+                act = {"swiglu": torch.nn.functional.silu(gt), "geglu": torch.nn.functional.gelu(gt),
+                       "geglu_tanh": torch.nn.functional.gelu(gt, approximate="tanh")}[activation]
+                h = act * (up[ex] @ x[ti])
+            want[ti] += w[ti, j] * (down[ex] @ h)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)

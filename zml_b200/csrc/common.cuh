@@ -420,6 +420,26 @@ __host__ __device__ constexpr uint32_t zb_make_idesc_bf16(uint32_t m, uint32_t n
 // ----------------------------------------------------------------------------
 // small numeric helpers
 // ----------------------------------------------------------------------------
+// Activations of the expert MLPs (the reference's zml/moe/cutlass_flashinfer.zig:24-28).  The grouped GEMMs take
+// the code in their `swiglu` argument: 0 none, 1 swiglu (silu(gate) * up), 2 geglu (erf GELU), 3 geglu_tanh,
+// 4 relu2 (not gated: relu(x)^2 on a plain projection).
+enum ZbMoeAct : int { ZB_ACT_NONE = 0, ZB_ACT_SWIGLU = 1, ZB_ACT_GEGLU = 2, ZB_ACT_GEGLU_TANH = 3, ZB_ACT_RELU2 = 4 };
+ZB_DEVICE bool zb_act_is_gated(int act) { return act >= ZB_ACT_SWIGLU && act <= ZB_ACT_GEGLU_TANH; }
+ZB_DEVICE float zb_gate_act(float g, int act) {
+  if (act == ZB_ACT_GEGLU) return 0.5f * g * (1.f + erff(g * 0.70710678118654752f));
+  if (act == ZB_ACT_GEGLU_TANH) {
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(u));
+  }
+  return g / (1.f + __expf(-g));
+}
+ZB_DEVICE float zb_plain_act(float x, int act) {
+  if (act == ZB_ACT_RELU2) {
+    const float r = fmaxf(x, 0.f);
+    return r * r;
+  }
+  return x;
+}
 ZB_DEVICE uint32_t zb_pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -444,6 +444,7 @@ struct GroupedParams {
   int ldo;                  // leading dimension of out
   __nv_bfloat16* out;
   int cap;                  // rows allocated in xs / out
+  int act;                  // ZbMoeAct: which gate activation the gated epilogue applies, or relu2 on a plain projection
   ZbStatus* status;
 };
 
@@ -618,7 +619,7 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             for (int j = 0; j < 16; ++j) {
               const int tok = tok0 + c0 + j;
               if (tok < end_e)
-                prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(__uint_as_float(r[j]));
+                prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(zb_plain_act(__uint_as_float(r[j]), prm.act));
             }
           }
           zb_tc_fence_before();
@@ -644,7 +645,7 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
                 if (tok < end_e) {
                   const float gt = __uint_as_float(r[j]);
                   const float up = xch[(c0 + j) * 64 + row_in_tile];
-                  prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(gt / (1.f + __expf(-gt)) * up);
+                  prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(zb_gate_act(gt, prm.act) * up);
                 }
               }
             }
@@ -662,6 +663,10 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
             uint32_t r[16];
             zb_tmem_ld16(taddr + c0, r);
             zb_tmem_ld_wait();
+            if (prm.act == ZB_ACT_RELU2) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(zb_plain_act(__uint_as_float(r[j]), ZB_ACT_RELU2));
+            }
             if (tok < end_e) {
               uint4* op = reinterpret_cast<uint4*>(prm.out + static_cast<size_t>(tok) * prm.ldo + wt * BN + c0);
               op[0] = make_uint4(zb_pack_bf16x2(__uint_as_float(r[0]), __uint_as_float(r[1])),
@@ -689,7 +694,7 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                   const float gt = __uint_as_float(gr[j]);
-                  h[j] = gt / (1.f + __expf(-gt)) * __uint_as_float(ur[j]);
+                  h[j] = zb_gate_act(gt, prm.act) * __uint_as_float(ur[j]);
                 }
                 uint4* op = reinterpret_cast<uint4*>(prm.out + static_cast<size_t>(tok) * prm.ldo + wt * (BN / 2) +
                                                      blk * 64 + c0);
@@ -852,7 +857,8 @@ int zb_moe_combine(const void* o, const int32_t* pair_pos, const float* weights,
 }
 
 // out[rows of expert e, :] = xs[rows of expert e, :K] * w[e][N, K]^T for all local experts.
-// swiglu != 0: w holds the interleaved gate/up weight (N = 2F, see above) and out is [cap, F].
+// swiglu = 1 / 2 / 3 (swiglu / geglu / geglu_tanh, see ZbMoeAct): w holds the interleaved gate/up weight (N = 2F, see
+// above) and out is [cap, F]; swiglu = 4 (relu2): a plain projection followed by relu(x)^2; 0: a plain projection.
 // avg_tokens (expected tokens per expert) picks the tile orientation.
 int zb_moe_grouped_gemm(const void* xs, const void* w, void* out, const int32_t* offsets, int e_local, int n, int k,
                         int cap, int ldo, int swiglu, int avg_tokens, void* stream) {
@@ -880,7 +886,10 @@ int zb_moe_grouped_gemm(const void* xs, const void* w, void* out, const int32_t*
   prm.ldo = ldo;
   prm.out = reinterpret_cast<__nv_bfloat16*>(out);
   prm.cap = cap;
+  prm.act = swiglu;
   prm.status = st->status;
+  if (swiglu < 0 || swiglu > ZB_ACT_RELU2) return -67;
+  const bool gated = swiglu >= ZB_ACT_SWIGLU && swiglu <= ZB_ACT_GEGLU_TANH;
   CUtensorMap tx, tw;
   int rc = zb_make_tmap_bf16_2d(&tx, xs, cap, k, k, swap ? bn : kBlockP);
   if (rc != 0) return rc;
@@ -889,8 +898,8 @@ int zb_moe_grouped_gemm(const void* xs, const void* w, void* out, const int32_t*
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = st->num_sms;
 #define ZB_G(BN_, SW_)                                                                          \
-  return swiglu ? launch_grouped<BN_, SW_, true>(tx, tw, prm, grid, s)                         \
-                : launch_grouped<BN_, SW_, false>(tx, tw, prm, grid, s);
+  return gated ? launch_grouped<BN_, SW_, true>(tx, tw, prm, grid, s)                          \
+               : launch_grouped<BN_, SW_, false>(tx, tw, prm, grid, s);
   if (swap) {
     switch (bn) {
       case 16: ZB_G(16, true)

@@ -79,6 +79,7 @@ struct Fp4Params {
   const float* x_gscale;    // one fp32: the activations' per-tensor scale, or null (1)
   uint8_t* out_q;           // QOUT: [cap, ldo / 2] e2m1 codes of the (SwiGLU) output instead of `out`
   uint8_t* out_sf;          // QOUT: [cap, ldo / 16] f8e4m3 block scales
+  int act;                  // ZbMoeAct
   ZbStatus* status;
 };
 
@@ -389,7 +390,8 @@ zb_moe_grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_x, const
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
-            if (tok < end_e) prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(__uint_as_float(rr[j]) * oscale);
+            if (tok < end_e)
+              prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(zb_plain_act(__uint_as_float(rr[j]) * oscale, prm.act));
           }
         }
       } else {
@@ -414,7 +416,7 @@ zb_moe_grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_x, const
                 if (tok < end_e) {
                   const float gt = __uint_as_float(rr[j]) * oscale;
                   const float up = xch[(c0 + j) * 64 + row_in_tile];
-                  prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(gt / (1.f + __expf(-gt)) * up);
+                  prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(zb_gate_act(gt, prm.act) * up);
                 }
               }
             }
@@ -427,7 +429,7 @@ zb_moe_grouped_gemm_fp4_kernel(const __grid_constant__ CUtensorMap tmap_x, const
               for (int j = 0; j < 16; ++j) {
                 const float gt = __uint_as_float(rr[j]) * oscale;
                 const float up = xch[(c0 + j) * 64 + row_in_tile];
-                xch[(c0 + j) * 64 + row_in_tile] = bf16_round(gt / (1.f + __expf(-gt)) * up);
+                xch[(c0 + j) * 64 + row_in_tile] = bf16_round(zb_gate_act(gt, prm.act) * up);
               }
             }
             fp4_epi_bar();
@@ -509,9 +511,11 @@ int zb_moe_grouped_gemm_fp4(const void* xq, const void* x_sf, const float* x_gsc
   if (cap <= 0 || e_local <= 0) return 0;
   if (e_local > kZbMaxExperts) return -61;
   if (k % kStageK != 0 || n % kBlockP != 0 || ldo % 8 != 0) return -66;
-  if (gs_per != 1 && !(gs_per == 2 && swiglu)) return -67;
+  if (swiglu < 0 || swiglu > ZB_ACT_RELU2) return -67;
+  const bool gated = swiglu >= ZB_ACT_SWIGLU && swiglu <= ZB_ACT_GEGLU_TANH;
+  if (gs_per != 1 && !(gs_per == 2 && gated)) return -67;
   const bool qout = out_q != nullptr;
-  if (qout && (!swiglu || out_sf == nullptr || ldo % 64 != 0 || (reinterpret_cast<uintptr_t>(out_q) & 7) != 0)) return -68;
+  if (qout && (!gated || out_sf == nullptr || ldo % 64 != 0 || (reinterpret_cast<uintptr_t>(out_q) & 7) != 0)) return -68;
   if ((reinterpret_cast<uintptr_t>(blocks) & 15) != 0 || (reinterpret_cast<uintptr_t>(x_sf) & 15) != 0) return -66;
   ZbDeviceState* st = zb_device_state();
   if (!st) return -20;
@@ -532,6 +536,7 @@ int zb_moe_grouped_gemm_fp4(const void* xq, const void* x_sf, const float* x_gsc
   prm.x_gscale = x_gscale;
   prm.out_q = reinterpret_cast<uint8_t*>(out_q);
   prm.out_sf = reinterpret_cast<uint8_t*>(out_sf);
+  prm.act = swiglu;
   prm.status = st->status;
   CUtensorMap tx;
   int rc = zb_make_tmap_u8_2d_ex(&tx, xq, cap, k / 2, kStageK / 2, bn, 1);
@@ -540,7 +545,7 @@ int zb_moe_grouped_gemm_fp4(const void* xq, const void* x_sf, const float* x_gsc
   const int grid = st->num_sms;
 #define ZB_FP4(BN_)                                                                  \
   return qout ? launch_fp4<BN_, true, true>(tx, prm, grid, s)                         \
-              : (swiglu ? launch_fp4<BN_, true, false>(tx, prm, grid, s) : launch_fp4<BN_, false, false>(tx, prm, grid, s));
+              : (gated ? launch_fp4<BN_, true, false>(tx, prm, grid, s) : launch_fp4<BN_, false, false>(tx, prm, grid, s));
   switch (bn) {
     case 16: ZB_FP4(16)
     case 32: ZB_FP4(32)

@@ -79,6 +79,7 @@ struct W4Params {
   const uint8_t* blocks;    // [e_local, n / 128, k / 256] blocks of 18 KB (codes, then scales)
   const float* gscale;      // [e_local, gs_per] per-matrix scale (gs_per = 2: gate rows, up rows)
   int gs_per;
+  int act;                  // ZbMoeAct
   ZbStatus* status;
   unsigned long long* timeline;   // null, or [kTimelineStages][8] time stamps of CTA 0 (see zb_moe_w4_set_timeline)
 };
@@ -391,7 +392,8 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int tok = tok0 + c0 + j;
-            if (tok < end_e) prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(__uint_as_float(rr[j]) * oscale);
+            if (tok < end_e)
+              prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(zb_plain_act(__uint_as_float(rr[j]) * oscale, prm.act));
           }
         }
       } else {
@@ -422,7 +424,7 @@ zb_moe_grouped_gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const 
               if (tok < end_e) {
                 const float gt = __uint_as_float(rr[j]) * oscale;
                 const float up = xch[(c0 + j) * 64 + row_in_tile];
-                prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(gt / (1.f + __expf(-gt)) * up);
+                prm.out[static_cast<size_t>(tok) * prm.ldo + feat] = __float2bfloat16(zb_gate_act(gt, prm.act) * up);
               }
             }
           }
@@ -490,7 +492,9 @@ int zb_moe_grouped_gemm_w4(const void* xs, const void* blocks, const float* gsca
   if (cap <= 0 || e_local <= 0) return 0;
   if (e_local > kZbMaxExperts) return -61;
   if (k % (kBlockK * kSub) != 0 || n % kBlockP != 0 || ldo % 8 != 0) return -66;
-  if (gs_per != 1 && !(gs_per == 2 && swiglu)) return -67;
+  if (swiglu < 0 || swiglu > ZB_ACT_RELU2) return -67;
+  const bool gated = swiglu >= ZB_ACT_SWIGLU && swiglu <= ZB_ACT_GEGLU_TANH;
+  if (gs_per != 1 && !(gs_per == 2 && gated)) return -67;
   ZbDeviceState* st = zb_device_state();
   if (!st) return -20;
   int bn = 16;
@@ -505,6 +509,7 @@ int zb_moe_grouped_gemm_w4(const void* xs, const void* blocks, const float* gsca
   prm.cap = cap;
   prm.gscale = gscale;
   prm.gs_per = gs_per;
+  prm.act = swiglu;
   prm.status = st->status;
   prm.timeline = g_w4_timeline;
   if ((reinterpret_cast<uintptr_t>(blocks) & 15) != 0) return -66;
@@ -514,7 +519,7 @@ int zb_moe_grouped_gemm_w4(const void* xs, const void* blocks, const float* gsca
   if (rc != 0) return rc;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = st->num_sms;
-#define ZB_W4(BN_) return swiglu ? launch_w4<BN_, true>(tx, prm, grid, s) : launch_w4<BN_, false>(tx, prm, grid, s);
+#define ZB_W4(BN_) return gated ? launch_w4<BN_, true>(tx, prm, grid, s) : launch_w4<BN_, false>(tx, prm, grid, s);
   switch (bn) {
     case 16: ZB_W4(16)
     case 32: ZB_W4(32)

@@ -127,30 +127,54 @@ def deinterleave_gate_up(w: torch.Tensor):
     return b[:, :, 0].reshape(e, f2 // 2, d), b[:, :, 1].reshape(e, f2 // 2, d)
 
 
-def grouped_gemm(xs: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8):
-    """Per local expert e: out[rows_e] = xs[rows_e] @ w[e]^T; `swiglu`: w is the interleaved
-    gate/up weight [E, 2F, K] and out is silu(gate) * up, [cap, F]."""
+# Activations of the expert MLP (zml/moe/cutlass_flashinfer.zig:24-28 of the reference): the gated ones take an
+# interleaved gate|up weight, `relu2` a plain up projection.  The code is what the kernels' `swiglu` argument carries.
+ACTIVATIONS = {"none": 0, "swiglu": 1, "geglu": 2, "geglu_tanh": 3, "relu2": 4}
+
+
+def activation_code(swiglu) -> int:
+    """False / True (SwiGLU) / an activation name -> kernel code."""
+    if isinstance(swiglu, str):
+        return ACTIVATIONS[swiglu]
+    return 1 if swiglu else 0
+
+
+def _gate_act(g: torch.Tensor, code: int) -> torch.Tensor:
+    if code == 2:
+        return torch.nn.functional.gelu(g)
+    if code == 3:
+        return torch.nn.functional.gelu(g, approximate="tanh")
+    return torch.nn.functional.silu(g)
+
+
+def grouped_gemm(xs: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, swiglu=False, avg_tokens: int = 8):
+    """Per local expert e: out[rows_e] = xs[rows_e] @ w[e]^T.  `swiglu` True or "swiglu" / "geglu" / "geglu_tanh": w is
+    the interleaved gate/up weight [E, 2F, K] and out is act(gate) * up, [cap, F]; "relu2": relu(x w^T)^2."""
     e_local, n, k = w.shape
     cap = xs.shape[0]
-    n_out = n // 2 if swiglu else n
+    code = activation_code(swiglu)
+    gated = 1 <= code <= 3
+    n_out = n // 2 if gated else n
     if not xs.is_cuda:
         out = torch.zeros((cap, n_out), dtype=xs.dtype)
-        gate_up = deinterleave_gate_up(w) if swiglu else None
+        gate_up = deinterleave_gate_up(w) if gated else None
         for e in range(e_local):
             a, b = int(meta[e]), int(meta[e + 1])
             if b <= a:
                 continue
             x = xs[a:b].float()
-            if swiglu:
+            if gated:
                 g, u = gate_up
-                out[a:b] = (torch.nn.functional.silu(x @ g[e].float().t()) * (x @ u[e].float().t())).to(xs.dtype)
+                out[a:b] = (_gate_act(x @ g[e].float().t(), code) * (x @ u[e].float().t())).to(xs.dtype)
+            elif code == 4:
+                out[a:b] = torch.relu(x @ w[e].float().t()).square().to(xs.dtype)
             else:
                 out[a:b] = (x @ w[e].float().t()).to(xs.dtype)
         return out
     assert xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and xs.is_contiguous() and w.is_contiguous()
     out = torch.empty((cap, n_out), dtype=xs.dtype, device=xs.device)
     _lib.check(_lib.lib().zb_moe_grouped_gemm(xs.data_ptr(), w.data_ptr(), out.data_ptr(), meta.data_ptr(), e_local, n, k,
-                                              cap, n_out, int(swiglu), int(avg_tokens), _lib.stream_ptr()),
+                                              cap, n_out, code, int(avg_tokens), _lib.stream_ptr()),
                "zb_moe_grouped_gemm")
     return out
 
@@ -301,18 +325,19 @@ class Nvfp4Experts:
         return body + self.gscale.numel() * 4
 
 
-def grouped_gemm_w4(xs: torch.Tensor, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8):
+def grouped_gemm_w4(xs: torch.Tensor, w: Nvfp4Experts, meta: torch.Tensor, swiglu=False, avg_tokens: int = 8):
     """`grouped_gemm` with NVFP4 expert weights de-quantised inside the kernel (few tokens per
     expert; libzb_cuda.so: zb_moe_grouped_gemm_w4).  CPU tensors: de-quantise, then the float path."""
     if not xs.is_cuda or not w.kernel_ready:
         return grouped_gemm(xs, w.dequantize(xs.dtype), meta, swiglu, avg_tokens)
     cap = xs.shape[0]
-    n_out = w.n // 2 if swiglu else w.n
+    code = activation_code(swiglu)
+    n_out = w.n // 2 if 1 <= code <= 3 else w.n
     assert xs.dtype == torch.bfloat16 and xs.is_contiguous() and xs.shape[1] == w.k
     out = torch.empty((cap, n_out), dtype=xs.dtype, device=xs.device)
     _lib.check(_lib.lib().zb_moe_grouped_gemm_w4(xs.data_ptr(), w.blocks.data_ptr(), w.gscale.data_ptr(),
                                                  int(w.gscale.shape[1]), out.data_ptr(), meta.data_ptr(), w.e, w.n, w.k, cap, n_out,
-                                                 int(swiglu),
+                                                 code,
                                                  int(avg_tokens), _lib.stream_ptr()), "zb_moe_grouped_gemm_w4")
     return out
 
@@ -347,7 +372,7 @@ def gather_fp4(x: torch.Tensor, sorted_pair: torch.Tensor, meta: torch.Tensor, e
     return Fp4Activations(xq, xsf.view(torch.float8_e4m3fn))
 
 
-def grouped_gemm_fp4(xs, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = False, avg_tokens: int = 8,
+def grouped_gemm_fp4(xs, w: Nvfp4Experts, meta: torch.Tensor, swiglu=False, avg_tokens: int = 8,
                      quantize_out: bool = False):
     """`grouped_gemm` with NVFP4 weights AND NVFP4 activations (one f8e4m3 scale per 16 values on both sides),
     multiplied by the block-scaled tensor-core instruction (libzb_cuda.so: zb_moe_grouped_gemm_fp4).  `xs` is an
@@ -359,12 +384,14 @@ def grouped_gemm_fp4(xs, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = Fal
         out = grouped_gemm(xs.dequantize(torch.float32), w.dequantize(torch.float32), meta, swiglu, avg_tokens).to(torch.bfloat16)
         return Fp4Activations.quantize(out) if quantize_out else out
     cap = xs.codes.shape[0]
-    n_out = w.n // 2 if swiglu else w.n
+    code = activation_code(swiglu)
+    gated = 1 <= code <= 3
+    n_out = w.n // 2 if gated else w.n
     assert xs.k == w.k and xs.codes.is_contiguous() and xs.scales.is_contiguous()
     dev = xs.codes.device
     out = oq = osf = None
     if quantize_out:
-        assert swiglu and n_out % 64 == 0
+        assert gated and n_out % 64 == 0
         oq = torch.empty((cap, n_out // 2), dtype=torch.uint8, device=dev)
         osf = torch.empty((cap, n_out // 16), dtype=torch.uint8, device=dev)
     else:
@@ -372,7 +399,7 @@ def grouped_gemm_fp4(xs, w: Nvfp4Experts, meta: torch.Tensor, swiglu: bool = Fal
     ptr = lambda t: t.data_ptr() if t is not None else None
     _lib.check(_lib.lib().zb_moe_grouped_gemm_fp4(xs.codes.data_ptr(), xs.scales.data_ptr(), None, w.mma_blocks().data_ptr(),
                                                   w.gscale.data_ptr(), int(w.gscale.shape[1]), ptr(out), ptr(oq), ptr(osf),
-                                                  meta.data_ptr(), w.e, w.n, w.k, cap, n_out, int(swiglu), int(avg_tokens),
+                                                  meta.data_ptr(), w.e, w.n, w.k, cap, n_out, code, int(avg_tokens),
                                                   _lib.stream_ptr()), "zb_moe_grouped_gemm_fp4")
     return Fp4Activations(oq, osf.view(torch.float8_e4m3fn)) if quantize_out else out
 
@@ -428,8 +455,9 @@ def fp4_activations() -> bool:
 
 def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor, w_gate_up_il: torch.Tensor,
                   w_down: torch.Tensor, e0: int = 0, num_experts_total: Optional[int] = None,
-                  w4: Optional[tuple] = None, extra=None, residual=None, fused=None) -> torch.Tensor:
-    """Mixture output of the LOCAL experts for all tokens: permute -> grouped GEMM (+SwiGLU) ->
+                  w4: Optional[tuple] = None, extra=None, residual=None, fused=None, activation: str = "swiglu") -> torch.Tensor:
+    """Mixture output of the LOCAL experts for all tokens: permute -> grouped GEMM (+ `activation`: swiglu | geglu |
+    geglu_tanh on an interleaved gate|up weight, relu2 on a plain up projection [E_local, F, D]) ->
     grouped GEMM -> un-permute x routing weight.  x [T, D] bf16; w_gate_up_il [E_local, 2F, D]
     (interleaved, see `interleave_gate_up`); w_down [E_local, D, F].  `extra`, `residual` and `fused`
     go to `combine`: with `fused` the result is the sum over the expert-parallel group."""
@@ -446,7 +474,7 @@ def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor,
         # with 128 x 128 tiles the kernel is bound by operand traffic into shared memory, and at prefill sizes the
         # bf16 grouped GEMM on de-quantised weights is faster (787 against 559 TFLOP/s at 512 tokens per expert)
         xq = gather_fp4(x, sorted_pair, meta, e_local, k, cap)
-        hq = grouped_gemm_fp4(xq, w4[0], meta, swiglu=True, avg_tokens=avg, quantize_out=True)
+        hq = grouped_gemm_fp4(xq, w4[0], meta, swiglu=activation, avg_tokens=avg, quantize_out=activation != "relu2")
         o = grouped_gemm_fp4(hq, w4[1], meta, swiglu=False, avg_tokens=avg)
         if extra is None and residual is None and fused is None:
             return finalize(o, pair_pos, topk_w, t, k)
@@ -454,10 +482,10 @@ def fused_experts(x: torch.Tensor, topk_ids: torch.Tensor, topk_w: torch.Tensor,
     xs = gather(x, sorted_pair, meta, e_local, k, cap)
     if w4 is not None and avg <= W4_MAX_AVG_TOKENS and w4[0].kernel_ready and w4[1].kernel_ready:
         # few tokens per expert: the step is bound by reading expert weights - read them as NVFP4
-        h = grouped_gemm_w4(xs, w4[0], meta, swiglu=True, avg_tokens=avg)
+        h = grouped_gemm_w4(xs, w4[0], meta, swiglu=activation, avg_tokens=avg)
         o = grouped_gemm_w4(h, w4[1], meta, swiglu=False, avg_tokens=avg)
     else:
-        h = grouped_gemm(xs, w_gate_up_il, meta, swiglu=True, avg_tokens=avg)
+        h = grouped_gemm(xs, w_gate_up_il, meta, swiglu=activation, avg_tokens=avg)
         o = grouped_gemm(h, w_down, meta, swiglu=False, avg_tokens=avg)
     if extra is None and residual is None and fused is None:
         return finalize(o, pair_pos, topk_w, t, k)
