@@ -2,7 +2,9 @@
 """zb-smi: device monitor in the spirit of the reference's zml-smi (NVIDIA only).
 
     zb-smi                      one-shot table
-    zb-smi --top [--interval=1] refreshing terminal view (q / Ctrl-C to quit)
+    zb-smi --top [--interval=1] [--page=overview|processes|charts]
+                                terminal pages: bars per GPU, the process table, history charts
+                                (keys 1 / 2 / 3 switch pages, s changes the process sort, q quits)
     zb-smi --csv | --json       one line per sample (streams with --interval)
     zb-smi --prometheus-listen=127.0.0.1:9400   serve /metrics, /json
     zb-smi --fake               use the built-in fake NVML (no GPU needed)
@@ -35,6 +37,7 @@ class Args:
     interval: float = 0.0
     count: int = 0
     prometheus_listen: Optional[str] = None
+    page: str = "overview"
     help = __doc__
 
 
@@ -93,6 +96,12 @@ def main(argv=None) -> int:
         srv.shutdown()
         coll.stop()
         return 0
+    if args.top and not (args.csv or args.json):
+        import tui
+        tui.run(lambda: metrics.snapshot(backend, host), args.interval or 1.0, args.count, args.page)
+        if backend:
+            backend.close()
+        return 0
     n = 0
     if args.csv:
         print(outputs.csv_header())
@@ -103,8 +112,6 @@ def main(argv=None) -> int:
         elif args.json:
             print(outputs.to_json(snap), flush=True)
         else:
-            if args.top:
-                sys.stdout.write("\x1b[2J\x1b[H")
             print(outputs.to_table(snap), flush=True)
         n += 1
         if not (args.top or args.interval > 0) or (args.count and n >= args.count):

@@ -44,3 +44,28 @@ def test_cli_fake_one_shot():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "zb_smi", "main.py"), "--fake", "--csv", "--interval=0.1", "--count=2"],
                        capture_output=True, text=True, timeout=60)
     assert r.returncode == 0 and len(r.stdout.strip().splitlines()) == 5
+
+
+def test_tui_pages_render_bars_process_table_and_charts():
+    import tui
+    fake = metrics.FakeNvml(devices=2)
+    be = metrics.NvmlBackend(fake)
+    host = metrics.HostPoller()
+    hist = tui.History(depth=8)
+    for _ in range(3):
+        snap = metrics.snapshot(be, host)
+        hist.add(snap)
+    over = tui.render(snap, hist, "overview", 120)
+    assert "[1:overview]" in over and "█" in over and "950/1000" in over and "sw_power_cap" in over
+    procs = tui.render(snap, hist, "processes", 120)
+    assert str(os.getpid()) in procs and "MiB" in procs and "sorted by gpu_memory_bytes" in procs
+    assert [p["gpu"] for p in tui.processes(snap, "gpu")] == [0, 1]
+    charts = tui.render(snap, hist, "charts", 120)
+    assert charts.count("util %") == 2 and any(c in charts for c in "▁▂▃▄▅▆▇█")
+    assert tui.sparkline([0, 50, 100, None], 6, 100.0) == "   ▄█ "
+    assert tui.bar(0.5, 10) == "█████░░░░░" and tui.bar(None, 4) == "----"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "zb_smi", "main.py"), "--fake", "--top", "--count=2", "--interval=0.1",
+                        "--page=processes"], capture_output=True, text=True, timeout=60, stdin=subprocess.DEVNULL)
+    assert r.returncode == 0 and "[2:processes]" in r.stdout
+    be.close()
+    assert fake.calls == ["init", "shutdown"]
