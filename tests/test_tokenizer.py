@@ -69,3 +69,28 @@ def test_sentencepiece_style_bpe_with_byte_fallback():
     ids = tok.encode("hi €")
     assert ids == [5, 1, 6, 7, 8]
     assert tok.decode(ids) == "hi €"
+
+
+def test_unigram_tokenizer_matches_hf():
+    """The in-house Unigram tokenizer (Viterbi over piece log-probabilities, Metaspace, unknown fusion) against the
+    `tokenizers` library on a model trained here."""
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer as HfTok, decoders, models, normalizers, pre_tokenizers, trainers
+    from zml_b200.tokenizer import Tokenizer
+    corpus = ["the quick brown fox jumps over the lazy dog", "a stitch in time saves nine", "hello world, hello tokens",
+              "unigram language models segment text into pieces", "tokenization is fun and pieces are nice"] * 8
+    t = HfTok(models.Unigram())
+    t.normalizer = normalizers.NFKC()
+    t.pre_tokenizer = pre_tokenizers.Metaspace()
+    t.decoder = decoders.Metaspace()
+    t.train_from_iterator(corpus, trainers.UnigramTrainer(vocab_size=120, special_tokens=["<unk>", "<s>"], unk_token="<unk>"))
+    data = t.to_str().encode()
+    ours = Tokenizer.from_bytes(data, backend="homemade")
+    assert ours.backend == "homemade" and type(ours.impl).__name__ == "UnigramTokenizer"
+    for text in ["the quick brown fox", "hello world", "time saves the lazy tokens", "pieces of text", "a dog in time",
+                 "<s>hello world", "zebra quartz ωμέγα"]:
+        want = t.encode(text, add_special_tokens=False).ids
+        got = ours.encode(text)
+        assert got == want, (text, got, want)
+        assert ours.decode(got) == t.decode(want, skip_special_tokens=False)
+    assert ours.vocab_size() == t.get_vocab_size() and ours.token_id("<s>") == t.token_to_id("<s>")

@@ -4,7 +4,8 @@
                     (the reference uses the IREE tokenizer, patched to match HF);
 * `sentencepiece` - `.model` / `.pb` files through the `sentencepiece` package (the
                     reference wraps the C++ library with SWIG);
-* `homemade`      - the in-house BPE of `zml_b200.tokenizer.bpe` (no dependency).
+* `homemade`      - the in-house tokenizers (no dependency): BPE (`zml_b200.tokenizer.bpe`) and Unigram
+                    (`zml_b200.tokenizer.unigram`), chosen by the `model.type` of the tokenizer.json.
 
 `Tokenizer.encoder()` / `.decoder()` give the reference's stateful objects: the decoder is
 a streaming one (`next(id)` returns the text that became printable with that id, holding
@@ -106,6 +107,11 @@ class Tokenizer:
             except ImportError:
                 if backend == "hf":
                     raise
+        import json
+        kind = json.loads(data.decode("utf-8")).get("model", {}).get("type", "BPE")
+        if kind == "Unigram":
+            from .unigram import UnigramTokenizer
+            return Tokenizer("homemade", UnigramTokenizer.from_bytes(data))
         return Tokenizer("homemade", BpeTokenizer.from_bytes(data))
 
     # ------------------------------------------------------------------ API
