@@ -418,3 +418,27 @@ def test_bounds_checking_build_reports_bad_indices(tmp_path):
                        env=dict(os.environ, ZB_ROOT=root, ZB_CUDA_LIB=so))
     assert r.returncode == 0 and "BOUNDS_OK" in r.stdout, r.stdout[-1500:] + r.stderr[-2500:]
     assert r.stdout.count("CAUGHT") == 3
+
+
+@pytest.mark.gpu
+def test_platform_cuda_options_cap_and_preallocate():
+    """`CudaOptions.memory_fraction` caps the process's share of the device, `preallocate` reserves it at start-up."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = r"""
+import sys, torch
+sys.path.insert(0, %r)
+from zml_b200.platform import CreateOptions, CudaOptions, Platform, Target
+p = Platform.init(Target.cuda, CreateOptions(cuda=CudaOptions(memory_fraction=0.02, preallocate=True)))
+total = torch.cuda.mem_get_info()[1]
+assert torch.cuda.memory_reserved() >= 0.015 * total
+try:
+    torch.empty(int(0.05 * total), dtype=torch.uint8, device="cuda")
+    print("NOT CAPPED")
+except torch.OutOfMemoryError:
+    print("CAPPED")
+""" % root
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "CAPPED" in r.stdout and "NOT CAPPED" not in r.stdout, r.stdout + r.stderr[-1500:]

@@ -97,7 +97,6 @@ struct AttnParams {
   uint32_t* counters;           // decode: one per (sequence, kv head), zero between launches
   int window;                   // sliding window (keys), <= 0: none
   float scale_log2;             // softmax scale * log2(e)
-  float softcap;                // reserved (0 = off)
   ZbStatus* status;
 };
 

@@ -40,11 +40,12 @@ class CpuOptions:
 
 @dataclass
 class CudaOptions:
-    allocator: str = "async"            # bfc | async | platform: torch's caching allocator is always used
-    memory_fraction: float = 0.90
+    """What of the reference's CUDA client options (zml/platform.zig:117-166: allocator kind, memory fraction,
+    preallocation) has a meaning on torch's caching allocator: the share of the device's memory this process may
+    take, and whether to reserve it at start-up (one large block, returned to the allocator's cache at once, so
+    that later allocations do not go to the driver)."""
+    memory_fraction: float = 1.0        # < 1: cap of this process's share (torch.cuda.set_per_process_memory_fraction)
     preallocate: bool = False
-    collective_memory_size_mb: int = 0  # size of the symmetric heap for in-kernel collectives (0: on demand)
-    gpu_async_dispatch: bool = True
 
 
 @dataclass
@@ -97,9 +98,23 @@ class Platform:
             else:
                 td, desc = torch.device("cpu"), "virtual cpu device"
             self.devices.append(DeviceInfo(md.id, md, td, desc))
+        if target is Target.cuda:
+            self._apply_cuda_options()
         self._shardings: dict[str, Sharding] = {}
         self._replicated = Sharding.replicated(self.physical_mesh)
         self._shardings["replicated"] = self._replicated
+
+    def _apply_cuda_options(self) -> None:
+        o = self.options.cuda
+        for dev in {d.torch_device for d in self.local_devices()}:
+            if 0.0 < o.memory_fraction < 1.0:
+                torch.cuda.set_per_process_memory_fraction(o.memory_fraction, dev)
+            if o.preallocate:
+                free, total = torch.cuda.mem_get_info(dev)
+                want = min(int(total * min(o.memory_fraction, 1.0)), int(free * 0.95))
+                if want > 0:
+                    block = torch.empty(want, dtype=torch.uint8, device=dev)
+                    del block            # stays in the caching allocator
 
     # ------------------------------------------------------------------ construction
     @staticmethod
