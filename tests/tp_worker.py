@@ -219,6 +219,44 @@ def main():
         allh = comm.all_gather(got["tp_fused"][None].contiguous())
         assert all(torch.equal(allh[0], allh[r]) for r in range(comm.world)), name
         ops.raise_on_status()
+    # the generic stack, SPMD over NCCL: the tagged-tensor Llama through Loader (shards cut by Sharding.placement),
+    # Platform.compile and Exe on every rank, against the serving model's prefill logits from the same checkpoint
+    import tempfile
+    from zml_b200 import safetensors as st
+    from zml_b200.buffer import Buffer
+    from zml_b200.io import TensorStore
+    from zml_b200.models.tagged_llama import TaggedLlama, compile_prefill
+    from zml_b200.platform import Platform, Target
+    from zml_b200.serving.engine import AttnMeta
+    from zml_b200.shape import Shape
+    from zml_b200.sharding import LogicalMesh
+    cfg2 = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], hidden_size=512, num_attention_heads=8, num_key_value_heads=8,
+                                    intermediate_size=1024, vocab_size=1024))
+    repo = tempfile.mkdtemp() if comm.rank == 0 else None
+    repo = comm.broadcast_object(repo)
+    ref = LlamaModel(cfg2, single, device=dev).init_random(seed=9, std=0.05)
+    if comm.rank == 0:
+        st.save_file({k: v.contiguous().cpu() for k, v in ref.state_dict_hf().items()}, os.path.join(repo, "model.safetensors"))
+    comm.barrier()
+    store = TensorStore.from_path(repo)
+    platform = Platform.init(Target.cuda, comm=comm)
+    tp = platform.register_sharding("tp", LogicalMesh({"model": "high_bandwidth"}))
+    tagged = TaggedLlama.from_store(store, cfg2)
+    weights = tagged.load(platform, store, [tp])
+    assert tuple(weights.layers[0].q.local().shape) == (cfg2.num_attention_heads * cfg2.hd // comm.world, cfg2.hidden_size)
+    toks2 = torch.randint(3, 1000, (40,), generator=torch.Generator().manual_seed(2)).to(torch.int32)
+    exe = compile_prefill(tagged, platform, len(toks2))
+    logits = exe.call(weights, Buffer.from_tensor(platform, toks2, Shape({"s": len(toks2)}, "i32"))).to_tensor().float()
+    n2 = len(toks2)
+    kv2 = torch.zeros(ref.kv_cache_shape(3, 64), dtype=ref.dtype, device=dev)
+    i32d = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    meta2 = AttnMeta(True, i32d(list(range(n2))), i32d([64 + p for p in range(n2)]), i32d([[1, 2]]), i32d([n2]), i32d([0, n2]),
+                     total_q_blocks=1, q_start_host=[0, n2])
+    want_logits = ref.logits(ref.hidden_states(toks2.to(dev), meta2, kv2)).float().cpu()[:, :cfg2.vocab_size]
+    expect_close(logits, want_logits, atol=8e-2, rtol=8e-2, min_close=0.98)
+    alll = comm.all_gather(logits.to(dev)[None].contiguous())
+    assert all(torch.equal(alll[0], alll[r]) for r in range(comm.world)), "SPMD logits differ between ranks"
+    ops.raise_on_status()
     ctx.close()
     comm.barrier()
     if comm.rank == 0:
