@@ -336,3 +336,28 @@ def test_continuous_admission_matches_one_at_a_time_generation(name):
     eos = want[2][3]
     got, _ = eng.serve(prompts[2:3], 9, eos_ids=[eos])
     assert got[0] == want[2][:want[2].index(eos) + 1]
+
+
+def test_session_decode_in_blocks_matches_token_by_token():
+    """`Session.run_decode(stream_interval=n)` reads the generated ids every n steps; the conversation (two turns)
+    is the one the token-by-token loop produces, and an EOS inside a block ends the turn at that token."""
+    import torch
+    from zml_b200.models import registry
+    from zml_b200.parallel.comm import Comm
+    from zml_b200.serving import Engine
+    from zml_b200.serving.engine import Session
+    m = registry.build_model("tiny-llama-test", Comm.single(torch.device("cpu")), device="cpu", seed=11, dtype=torch.float32)
+    outs = []
+    for si in (1, 4, 7):
+        s = Session(Engine(m, num_pages=16, page_size=16, max_batch=1, max_seq_len=128), 100)
+        s.run_prefill([5, 6, 7, 8, 9])
+        a = s.run_decode(max_new_tokens=10, stream_interval=si)
+        s.run_prefill([11, 12])
+        b = s.run_decode(max_new_tokens=6, stream_interval=si)
+        outs.append((a, b, list(s.tokens)))
+        s.close()
+    assert outs[0] == outs[1] == outs[2] and len(outs[0][0]) == 10 and len(outs[0][1]) == 6
+    eos = outs[0][0][4]
+    s = Session(Engine(m, num_pages=16, page_size=16, max_batch=1, max_seq_len=128), 100, eos_ids=[eos])
+    s.run_prefill([5, 6, 7, 8, 9])
+    assert s.run_decode(stream_interval=4) == outs[0][0][:outs[0][0].index(eos) + 1]

@@ -602,19 +602,20 @@ class Session:
         self._next = tok
         return tok
 
-    def run_decode(self, on_token=None, max_new_tokens: Optional[int] = None) -> list[int]:
-        """Generates until EOS or the token budget; `on_token(id)` is called per token.
-        One device -> host read per token, like the reference's decode loop."""
+    def run_decode(self, on_token=None, max_new_tokens: Optional[int] = None, stream_interval: int = 1) -> list[int]:
+        """Generates until EOS or the token budget; `on_token(id)` is called per token.  The host reads the generated
+        ids every `stream_interval` decode steps: 1 is the reference's loop (one device -> host read per token, lowest
+        latency to the first character), larger values let the GPU run ahead (steps past an EOS inside a block are
+        discarded)."""
         eng = self.engine
         out: list[int] = []
         if self._next is None:
             return out
         budget = self.remaining() - 1 if max_new_tokens is None else min(max_new_tokens, self.remaining() - 1)
-        tok = self._next
         ps = eng.page_size
         pos = len(self.tokens)
         i32 = dict(dtype=torch.int32, device=eng.device)
-        eng.d_ids[:1] = torch.tensor([tok], **i32)
+        eng.d_ids[:1] = torch.tensor([self._next], **i32)
         eng.d_pos[:1] = torch.tensor([pos], **i32)
         eng.d_seq[:1] = torch.tensor([pos + 1], **i32)
         eng.d_slot[:1] = torch.tensor([self.req.pages[pos // ps] * ps + pos % ps], **i32)
@@ -623,16 +624,24 @@ class Session:
         if eng.stateful:
             eng.d_sslot[:1] = torch.tensor([self.req.slot], **i32)
         splits = ops.decode_plan_splits(1, eng.model.hkv, self.max_tokens) if eng.on_gpu else 1
-        while True:
-            out.append(tok)
-            self.tokens.append(tok)
-            if on_token is not None:
-                on_token(tok)
-            if tok in self.eos or len(out) >= budget:
+        pending = [self._next]
+        done = False
+        while not done:
+            for tok in pending:
+                out.append(tok)
+                self.tokens.append(tok)
+                if on_token is not None:
+                    on_token(tok)
+                if tok in self.eos or len(out) >= budget:
+                    done = True
+                    break
+            if done:
                 break
+            n = max(1, min(stream_interval, budget - len(out), eng.history_steps))
             eng.d_step.zero_()
-            eng._decode_step(1, self.strategy, splits, self.max_tokens, None)
-            tok = int(eng.d_ids[0])
+            for _ in range(n):
+                eng._decode_step(1, self.strategy, splits, self.max_tokens, None)
+            pending = eng.d_hist[:n, 0].cpu().tolist() if n > 1 else [int(eng.d_ids[0])]
         self._next = None
         self.req.computed = len(self.tokens) - 1
         return out
