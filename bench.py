@@ -124,6 +124,16 @@ def tp_collectives(comm, args, baseline: bool) -> str:
 HEADLINE = {8: ["llama-3.1-70b", "qwen3-30b-a3b-nvfp4"], 4: ["qwen3-30b-a3b-nvfp4"], 2: ["qwen3-30b-a3b-nvfp4"]}
 
 
+_T0 = time.perf_counter()
+
+
+def progress(comm, msg: str) -> None:
+    """One line on stderr (rank 0): where the run is, in seconds since start - what a log of a run that was cut
+    short has to show."""
+    if comm.rank == 0:
+        print(f"[bench +{time.perf_counter() - _T0:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+
 def run_workload(name: str, comm, args, steps: int, warmup: int, sample_clocks: bool):
     """Builds the named model, runs `warmup` untimed and `steps` timed serving jobs, tears everything down.
     Returns the metrics on every rank (times are the max over ranks)."""
@@ -141,8 +151,10 @@ def run_workload(name: str, comm, args, steps: int, warmup: int, sample_clocks: 
     if args.new_tokens and name == args.model:
         wl["new_tokens"] = args.new_tokens
     baseline = args.impl == "baseline"
+    progress(comm, f"{name}: building the model on {comm.world} rank(s)")
     model = build_model(name, comm, device=comm.device, seed=args.seed, baseline=baseline,
                         fused=bool(args.fused) and not baseline)
+    progress(comm, f"{name}: model built, collectives: {tp_collectives(comm, args, baseline)}")
     lo, hi = wl["prompt"]
     g = torch.Generator().manual_seed(args.seed + 1)
     lens = torch.randint(lo, hi + 1, (wl["batch"],), generator=g).tolist()
@@ -157,16 +169,18 @@ def run_workload(name: str, comm, args, steps: int, warmup: int, sample_clocks: 
     def job():
         return engine.generate(prompts, wl["new_tokens"], strat)
 
-    for _ in range(max(warmup, 0)):
+    for i in range(max(warmup, 0)):
         job()
+        progress(comm, f"{name}: warm-up job {i + 1} of {warmup} done")
     comm.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(sample_clocks and comm.rank == 0)
     launches0 = _lib.launch_count()
     dev_ms, ttfts, out_tokens, h2d, d2h = 0.0, [], 0, 0, 0
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for i in range(steps):
         _, st = job()
+        progress(comm, f"{name}: timed job {i + 1} of {steps}: {st.total_ms:.0f} ms")
         dev_ms += st.total_ms
         ttfts.extend(st.ttft_ms)
         out_tokens += st.output_tokens
@@ -219,13 +233,25 @@ def main() -> None:
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (B200)")
+    import faulthandler
+    # a run that takes this long prints the Python stack of every thread of every rank (and again later): a cut-off
+    # log then shows where each rank was
+    faulthandler.dump_traceback_later(float(os.environ.get("ZB_BENCH_STACKS_AFTER_S", "420")), repeat=True, file=sys.stderr)
     comm = Comm.from_env()
     if comm.world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={comm.world}: launch with torch.distributed.run")
+    progress(comm, f"process group of {comm.world} rank(s) is up")
     r = run_workload(args.model, comm, args, args.steps, args.warmup, True)
     headline = {}
     if args.headline == "auto" and args.impl == "ours" and args.model == "llama-3.1-8b":
+        budget_s = float(os.environ.get("ZB_BENCH_HEADLINE_BUDGET_S", "420"))
         for name in HEADLINE.get(comm.world, []):
+            # every rank takes the same decision: rank 0's clock decides
+            go = comm.broadcast_object(time.perf_counter() - _T0 < budget_s)
+            if not go:
+                headline[name] = {"skipped": f"the run had used its {budget_s:.0f} s when this configuration came up"}
+                progress(comm, f"{name}: skipped (time budget)")
+                continue
             h = run_workload(name, comm, args, 3, 3, False)
             headline[name] = {"tok_s": h["out_tokens"] / (h["dev_ms"] / 1e3), "ttft_p50_ms": h["ttft_p50"],
                               "ms_per_step": h["dev_ms"] / 3, "steps": 3, "warmup": 3,
@@ -267,6 +293,7 @@ def main() -> None:
         if headline:
             line["headline"] = headline
         print(json.dumps(line))
+    faulthandler.cancel_dump_traceback_later()
     comm.finish(0)
 
 

@@ -284,6 +284,9 @@ class Loader:
             nbytes = sum(l for _, l in spans)
             raw = torch.empty(nbytes, dtype=torch.uint8, device=dev.torch_device)
             stream = self._streams.get(dev.id)
+            if stream is not None:
+                # the block may be recycled memory whose last use is still queued on the allocating stream
+                stream.wait_stream(torch.cuda.current_stream(dev.torch_device))
             pos = 0
             for piece, size in _cut_spans(spans, self.ring.chunk_bytes):
                 ch = self.ring.acquire()
