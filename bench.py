@@ -27,6 +27,7 @@ import os
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 WORKLOADS = {
@@ -243,22 +244,13 @@ def main() -> None:
     progress(comm, f"process group of {comm.world} rank(s) is up")
     r = run_workload(args.model, comm, args, args.steps, args.warmup, True)
     headline = {}
-    if args.headline == "auto" and args.impl == "ours" and args.model == "llama-3.1-8b":
-        budget_s = float(os.environ.get("ZB_BENCH_HEADLINE_BUDGET_S", "420"))
-        for name in HEADLINE.get(comm.world, []):
-            # every rank takes the same decision: rank 0's clock decides
-            go = comm.broadcast_object(time.perf_counter() - _T0 < budget_s)
-            if not go:
-                headline[name] = {"skipped": f"the run had used its {budget_s:.0f} s when this configuration came up"}
-                progress(comm, f"{name}: skipped (time budget)")
-                continue
-            h = run_workload(name, comm, args, 3, 3, False)
-            headline[name] = {"tok_s": h["out_tokens"] / (h["dev_ms"] / 1e3), "ttft_p50_ms": h["ttft_p50"],
-                              "ms_per_step": h["dev_ms"] / 3, "steps": 3, "warmup": 3,
-                              "e2e_tok_s": h["out_tokens"] / (h["wall_ms"] / 1e3), "global_batch": h["wl"]["batch"],
-                              "seq_len": [h["lo"], h["hi"]], "new_tokens": h["wl"]["new_tokens"],
-                              "tp_collectives": h["collectives"]}
-    if comm.rank == 0:
+    printed = threading.Event()
+
+    def emit() -> None:
+        """Rank 0 prints the one JSON line (once)."""
+        if comm.rank != 0 or printed.is_set():
+            return
+        printed.set()
         steps = max(args.steps, 1)
         wl, dev_ms, wall_ms = r["wl"], r["dev_ms"], r["wall_ms"]
         tp = f"tp{comm.world}" if comm.world > 1 else "single"
@@ -291,8 +283,45 @@ def main() -> None:
             "gpu_launches": r["launches"],
         }
         if headline:
-            line["headline"] = headline
-        print(json.dumps(line))
+            line["headline"] = dict(headline)
+        print(json.dumps(line), flush=True)
+
+    if args.headline == "auto" and args.impl == "ours" and args.model == "llama-3.1-8b" and HEADLINE.get(comm.world):
+        budget_s = float(os.environ.get("ZB_BENCH_HEADLINE_BUDGET_S", "420"))
+        deadline_s = float(os.environ.get("ZB_BENCH_DEADLINE_S", "760"))
+        current = {"name": None}
+
+        def give_up() -> None:
+            # the scaling configuration has been measured; a headline configuration that does not finish must not
+            # cost the whole run its result: report what there is and leave (every rank has the same timer)
+            if current["name"] is not None:
+                headline[current["name"]] = {"aborted": f"not finished {deadline_s:.0f} s into the run"}
+            progress(comm, f"deadline: leaving with {current['name']} unfinished")
+            emit()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+        timer = threading.Timer(max(1.0, deadline_s - (time.perf_counter() - _T0)), give_up)
+        timer.daemon = True
+        timer.start()
+        for name in HEADLINE.get(comm.world, []):
+            # every rank takes the same decision: rank 0's clock decides
+            go = comm.broadcast_object(time.perf_counter() - _T0 < budget_s)
+            if not go:
+                headline[name] = {"skipped": f"the run had used its {budget_s:.0f} s when this configuration came up"}
+                progress(comm, f"{name}: skipped (time budget)")
+                continue
+            current["name"] = name
+            h = run_workload(name, comm, args, 3, 3, False)
+            headline[name] = {"tok_s": h["out_tokens"] / (h["dev_ms"] / 1e3), "ttft_p50_ms": h["ttft_p50"],
+                              "ms_per_step": h["dev_ms"] / 3, "steps": 3, "warmup": 3,
+                              "e2e_tok_s": h["out_tokens"] / (h["wall_ms"] / 1e3), "global_batch": h["wl"]["batch"],
+                              "seq_len": [h["lo"], h["hi"]], "new_tokens": h["wl"]["new_tokens"],
+                              "tp_collectives": h["collectives"]}
+            current["name"] = None
+        timer.cancel()
+    emit()
     faulthandler.cancel_dump_traceback_later()
     comm.finish(0)
 

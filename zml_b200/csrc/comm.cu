@@ -206,8 +206,11 @@ struct MmAllReduce {
 __global__ void __launch_bounds__(512)
 zb_allreduce_mm_kernel(size_t in_off, size_t out_off, const uint4* __restrict__ residual, long long n_vec, const MmAllReduce ar,
                        ZbStatus* status) {
-  zb_pdl_launch();
-  zb_pdl_wait();
+  // No programmatic dependent launch around this kernel (it is launched without the attribute and never triggers
+  // its dependents early): its blocks wait for another GPU, and with the two-SM GEMMs of a large model's prefill
+  // started early on every SM behind it, one rank's GPU stopped making progress (Llama-3.1-70B shapes, 64 x 2048
+  // tokens, 2 and 4 ranks; any one of: no early launch, the one-SM GEMM, NCCL instead of this kernel - and the
+  // run completes).  The kernel before it has finished when it starts, the kernel after it starts when it is done.
   __shared__ uint32_t abort_flag;
   if (threadIdx.x == 0) abort_flag = 0u;
   __syncthreads();
@@ -452,8 +455,8 @@ int zb_allreduce_mm(const ZbArContext* c, size_t in_off, size_t out_off, const v
   long long blocks = (vs + 512 * 4 - 1) / (512 * 4);
   if (blocks < 1) blocks = 1;
   if (blocks > kMmMaxBlocks) blocks = kMmMaxBlocks;
-  zb_launch(zb_allreduce_mm_kernel, dim3(static_cast<unsigned>(blocks)), dim3(512), 0, reinterpret_cast<cudaStream_t>(stream), in_off,
-            out_off, reinterpret_cast<const uint4*>(residual), n_vec, ar, st->status);
+  zb_allreduce_mm_kernel<<<dim3(static_cast<unsigned>(blocks)), dim3(512), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      in_off, out_off, reinterpret_cast<const uint4*>(residual), n_vec, ar, st->status);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }
