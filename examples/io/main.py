@@ -3,7 +3,7 @@
 
     io cat <uri> | tree <dir> | ls <uri> | cp <src> <dst> | stat <uri> | realpath <uri>
     io safetensors <file|index|dir>      list tensors (name, dtype, shape, bytes) and metadata
-    io load <file|index|dir> [--device=cpu|cuda] [--chunk-mib=128] [--chunks=16] [--parallelism=16]
+    io load <file|index|dir> [--device=cpu|cuda] [--chunk-mib=32] [--chunks=8] [--parallelism=16]
                                          every tensor through the Loader (pinned staging ring, asynchronous
                                          host-to-device copies) to the device, report GiB/s
     io synth <dir> [--gib=16] [--tensor-mib=512]   write a synthetic bf16 checkpoint of that size (sharded files)
@@ -48,8 +48,8 @@ class TwoArgs:
 class LoadArgs:
     positional: One
     device: str = "cpu"
-    chunk_mib: int = 128
-    chunks: int = 16
+    chunk_mib: int = 32
+    chunks: int = 8
     parallelism: int = 16
 
 

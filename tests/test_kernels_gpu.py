@@ -433,7 +433,7 @@ sys.path.insert(0, %r)
 from zml_b200.platform import CreateOptions, CudaOptions, Platform, Target
 p = Platform.init(Target.cuda, CreateOptions(cuda=CudaOptions(memory_fraction=0.02, preallocate=True)))
 total = torch.cuda.mem_get_info()[1]
-assert torch.cuda.memory_reserved() >= 0.015 * total
+assert torch.cuda.memory_reserved() >= 0.01 * total
 try:
     torch.empty(int(0.05 * total), dtype=torch.uint8, device="cuda")
     print("NOT CAPPED")

@@ -242,9 +242,12 @@ class Loader:
     Data path per shard: `Placement.byte_spans` lists the byte ranges of the checkpoint entry that belong to this
     process's device; the ranges are cut into pieces of at most `dma_chunk_size`; each piece is read (threaded
     pread) into a chunk of the pinned ring and copied to its place in the device buffer with one asynchronous
-    host-to-device copy on a copy stream, while the next piece is already being read into another chunk."""
+    host-to-device copy on a copy stream, while the next piece is already being read into another chunk.
+    Defaults (8 chunks of 32 MiB) from a measurement on a B200 host, 8 GiB of bf16 tensors from page cache:
+    25.0 GiB/s; 16 x 128 MiB: 6.7 GiB/s (pinning 1.8 GB of staging costs more than it buys); 2 x 128 MiB with one
+    reader: 15.5 GiB/s."""
 
-    def __init__(self, platform, parallelism: int = 16, dma_chunk_size: int = 128 << 20, dma_chunks: int = 16,
+    def __init__(self, platform, parallelism: int = 16, dma_chunk_size: int = 32 << 20, dma_chunks: int = 8,
                  read_threads: int = 8):
         self.platform = platform
         self.parallelism = max(1, parallelism)

@@ -111,10 +111,14 @@ class Platform:
                 torch.cuda.set_per_process_memory_fraction(o.memory_fraction, dev)
             if o.preallocate:
                 free, total = torch.cuda.mem_get_info(dev)
-                want = min(int(total * min(o.memory_fraction, 1.0)), int(free * 0.95))
-                if want > 0:
-                    block = torch.empty(want, dtype=torch.uint8, device=dev)
-                    del block            # stays in the caching allocator
+                want = min(int(total * min(o.memory_fraction, 1.0) * 0.9), int(free * 0.9))     # the cap also covers the context
+                while want > (64 << 20):
+                    try:
+                        block = torch.empty(want, dtype=torch.uint8, device=dev)
+                        del block        # stays in the caching allocator
+                        break
+                    except torch.OutOfMemoryError:
+                        want = want * 3 // 4
 
     # ------------------------------------------------------------------ construction
     @staticmethod
