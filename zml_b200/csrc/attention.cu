@@ -669,12 +669,8 @@ int launch_decode(const AttnParams& p, cudaStream_t stream) {
   constexpr int pipe = 4 * kDecStages * 2 * 16 * HD * 2;
   constexpr int merge = 4 * 16 * HD * 4 + 4 * 16 * 2 * 4;
   constexpr int smem = pipe > merge ? pipe : merge;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_paged_decode_kernel<HD>, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_paged_decode_kernel<HD>, smem, configured)) return rc;
   dim3 grid(p.batch * p.num_kv_heads, p.num_splits);
   zb_launch(zb_paged_decode_kernel<HD>, dim3(grid), dim3(128), smem, stream, p);
   zb_count_launch(1);
@@ -686,12 +682,8 @@ int g_decode_tma = 1;
 template <int HD>
 int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
   constexpr int smem = dec_tma_stages<HD>() * 2 * 64 * HD * 2 + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_paged_decode_tma_kernel<HD>, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_paged_decode_tma_kernel<HD>, smem, configured)) return rc;
   CUtensorMap tk, tv;
   const long long slots = 1ll << 30;      // bound only: pages are addressed through the block table
   int rc = zb_make_tmap_kv_cache(&tk, p.k_cache, slots, p.num_kv_heads, HD, 64);
@@ -707,12 +699,8 @@ int launch_decode_tma(const AttnParams& p, cudaStream_t stream) {
 template <int HD>
 int launch_prefill(const AttnParams& p, int num_q_blocks, cudaStream_t stream) {
   constexpr int smem = 5 * 64 * HD * 2;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_paged_prefill_kernel<HD>, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_paged_prefill_kernel<HD>, smem, configured)) return rc;
   dim3 grid(num_q_blocks, p.num_q_heads);
   zb_launch(zb_paged_prefill_kernel<HD>, dim3(grid), dim3(128), smem, stream, p);
   zb_count_launch(1);

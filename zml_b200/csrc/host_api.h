@@ -148,6 +148,20 @@ inline cudaError_t zb_config_smem(K kernel, int smem) {
   return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
+// The same, once per device and kernel: `done` is the caller's static flag array (a function attribute belongs to
+// the device that was current when it was set, and one process may drive several GPUs).  Returns 0 or a CUDA error.
+template <typename K>
+inline int zb_config_smem_once(K kernel, int smem, bool (&done)[16]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return -21;
+  if (!done[dev]) {
+    cudaError_t e = zb_config_smem(kernel, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    done[dev] = true;
+  }
+  return 0;
+}
+
 extern "C" {
 void zb_set_pdl(int on);
 int zb_init(int device);

@@ -238,12 +238,8 @@ template <int DK>
 int launch_gdn(const GdnParams& p, int num_seqs, cudaStream_t s) {
   const int threads = (p.dv + 31) / 32 * 32;
   const size_t smem = (2 * kGdnChunk * DK + 2 * kGdnChunk * p.dv + 2 * kGdnChunk) * sizeof(float);
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_gated_delta_scan_kernel<DK>, (2 * kGdnChunk * DK + 2 * kGdnChunk * 256 + 2 * kGdnChunk) * 4);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_gated_delta_scan_kernel<DK>, (2 * kGdnChunk * DK + 2 * kGdnChunk * 256 + 2 * kGdnChunk) * 4, configured)) return rc;
   zb_launch(zb_gated_delta_scan_kernel<DK>, dim3(p.hv, num_seqs), dim3(threads), smem, s, p);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());

@@ -732,12 +732,8 @@ zb_moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __g
 template <int BN, bool SWAP, bool SWIGLU>
 int launch_grouped(const CUtensorMap& tx, const CUtensorMap& tw, const GroupedParams& prm, int grid, cudaStream_t s) {
   constexpr int smem = g_stages(BN) * g_stage_bytes(BN) + ((SWAP && SWIGLU) ? BN * 64 * 4 : 0) + 1024 + 256;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU>, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU>, smem, configured)) return rc;
   zb_launch(zb_moe_grouped_gemm_kernel<BN, SWAP, SWIGLU>, dim3(grid), dim3(kThreads), smem, s, tx, tw, prm);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());

@@ -483,12 +483,8 @@ template <int BN, bool SWIGLU, bool QOUT>
 int launch_fp4(const CUtensorMap& tx, const Fp4Params& prm, int grid, cudaStream_t s) {
   constexpr int smem = fp4_smem_bytes(BN, SWIGLU);
   static_assert(smem <= 232448, "shared memory of one CTA");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_moe_grouped_gemm_fp4_kernel<BN, SWIGLU, QOUT>, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_moe_grouped_gemm_fp4_kernel<BN, SWIGLU, QOUT>, smem, configured)) return rc;
   zb_launch(zb_moe_grouped_gemm_fp4_kernel<BN, SWIGLU, QOUT>, dim3(grid), dim3(kThreads), smem, s, tx, prm);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());

@@ -457,12 +457,8 @@ template <int BN, bool SWIGLU>
 int launch_w4(const CUtensorMap& tx, const W4Params& prm, int grid, cudaStream_t s) {
   constexpr int smem = w4_smem_bytes(BN, SWIGLU);
   static_assert(smem <= 232448, "shared memory of one CTA");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = zb_config_smem(zb_moe_grouped_gemm_w4_kernel<BN, SWIGLU>, smem);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[16] = {};
+  if (const int rc = zb_config_smem_once(zb_moe_grouped_gemm_w4_kernel<BN, SWIGLU>, smem, configured)) return rc;
   zb_launch(zb_moe_grouped_gemm_w4_kernel<BN, SWIGLU>, dim3(grid), dim3(kThreads), smem, s, tx, prm);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
