@@ -93,3 +93,56 @@ def test_vfs_http_ranges_and_schemes(tmp_path):
     assert vfs.resolve("s3://bucket/key/a.bin")[0].url("s3://bucket/key/a.bin") == "https://bucket.s3.amazonaws.com/key/a.bin"
     with pytest.raises(ValueError):
         vfs.resolve("ftp://x/y")
+
+
+def test_remote_checkpoint_loads_through_range_requests(tmp_path):
+    """A checkpoint behind http: the registry reads only the headers, the Loader fetches each device's shard as
+    parallel range requests (`Vfs.read_spans`); `Vfs.copy` streams a file in pieces."""
+    import torch
+    from zml_b200 import safetensors
+    from zml_b200.io import Loader, TensorStore
+    from zml_b200.platform import CpuOptions, CreateOptions, Platform, Target
+    from zml_b200.sharding import LogicalMesh
+    torch.manual_seed(0)
+    w = {"a.weight": torch.randn(64, 48), "b.weight": torch.randn(32, 16).bfloat16()}
+    safetensors.save_sharded(w, str(tmp_path), max_shard_bytes=8 << 10)
+    files = {n: (tmp_path / n).read_bytes() for n in os.listdir(tmp_path)}
+    requests = []
+
+    class Repo(RangeHandler):
+        def _data(self):
+            return files[self.path.rsplit("/", 1)[1]]
+
+        def do_HEAD(self):
+            self.data = self._data()
+            super().do_HEAD()
+
+        def do_GET(self):
+            self.data = self._data()
+            requests.append((self.path, self.headers.get("Range")))
+            super().do_GET()
+
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Repo)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        base = f"http://127.0.0.1:{srv.server_address[1]}/repo"
+        store = TensorStore.from_path(f"{base}/{safetensors.INDEX_NAME}")
+        assert sorted(store.registry.keys()) == ["a.weight", "b.weight"]
+        platform = Platform.init(Target.cpu, CreateOptions(cpu=CpuOptions(device_count=4)))
+        tp = platform.register_sharding("tp", LogicalMesh({"model": "high_bandwidth"}))
+        view = store.view()
+        model = {"a": view.create_tensor("a.weight", ("dout", "d"), {"d": "model"}), "b": view.create_tensor("b.weight", ("dout", "d"))}
+        requests.clear()
+        loader = Loader(platform, parallelism=2)
+        bufs = loader.load(model, store, [tp])
+        loader.close()
+        assert torch.equal(bufs["a"].to_tensor(), w["a.weight"]) and torch.equal(bufs["b"].to_tensor(), w["b.weight"])
+        assert tuple(bufs["a"].local(1).shape) == (64, 12)
+        assert all(r[1] is not None for r in requests)                      # nothing was fetched whole
+        vfs = Vfs.default()
+        name = sorted(n for n in files if n.endswith(".safetensors"))[0]
+        assert vfs.read_spans(f"{base}/{name}", [(8, 4), (12, 4), (100, 3)]) == files[name][8:16] + files[name][100:103]
+        n = vfs.copy(f"{base}/{name}", str(tmp_path / "copy.bin"), chunk=1000, parallelism=4)
+        assert n == len(files[name]) and (tmp_path / "copy.bin").read_bytes() == files[name]
+    finally:
+        srv.shutdown()

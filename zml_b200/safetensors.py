@@ -126,8 +126,43 @@ def flatten_metadata(val, prefix: str = "", out: Optional[dict] = None) -> dict:
 
 
 # ---------------------------------------------------------------------- registry
+def is_uri(path: str) -> bool:
+    """True for http(s):// hf:// s3:// gs:// locations (read through `zml_b200.vfs`), False for local paths."""
+    return "://" in path and not path.startswith("file://")
+
+
+_VFS = None
+
+
+def _vfs():
+    global _VFS
+    if _VFS is None:
+        from .vfs import Vfs
+        _VFS = Vfs.default()
+    return _VFS
+
+
+def _read_header_remote(uri: str) -> tuple[dict, int, int]:
+    v = _vfs()
+    size = v.stat(uri).size
+    raw = v.read_range(uri, 0, BYTES_HEADER)
+    if len(raw) != BYTES_HEADER:
+        raise SafetensorsError(f"{uri}: too short for a safetensors header")
+    (n,) = struct.unpack("<Q", raw)
+    if n <= 0 or n > size - BYTES_HEADER:
+        raise SafetensorsError(f"{uri}: header length {n} is inconsistent with file size {size}")
+    try:
+        header = json.loads(v.read_range(uri, BYTES_HEADER, n))
+    except json.JSONDecodeError as e:
+        raise SafetensorsError(f"{uri}: invalid header json: {e}") from None
+    return header, BYTES_HEADER + n, size
+
+
 def read_header(path: str) -> tuple[dict, int]:
-    """(header json, offset of the data section)."""
+    """(header json, offset of the data section).  `path` may be a remote location."""
+    if is_uri(path):
+        h, off, _ = _read_header_remote(path)
+        return h, off
     with open(path, "rb") as f:
         raw = f.read(BYTES_HEADER)
         if len(raw) != BYTES_HEADER:
@@ -173,19 +208,24 @@ class TensorRegistry:
     # ------------------------------------------------------------------ construction
     @staticmethod
     def from_path(path: str) -> "TensorRegistry":
-        """`path` is a .safetensors file, an index json, or a repo directory."""
-        if os.path.isdir(path):
+        """`path` is a .safetensors file, an index json, or a repo directory; files may also be remote
+        (`https://...`, `hf://org/repo/model.safetensors.index.json`, `s3://...`, `gs://...`): then only headers are
+        fetched here and tensors are read later as range requests."""
+        if not is_uri(path) and os.path.isdir(path):
             path = resolve_model_entrypoint(path)
         reg = TensorRegistry()
         if path.endswith(".index.json"):
-            with open(path) as f:
-                idx = json.load(f)
+            if is_uri(path):
+                idx = json.loads(_vfs().read(path))
+            else:
+                with open(path) as f:
+                    idx = json.load(f)
             if "weight_map" not in idx:
                 raise SafetensorsError(f"{path}: no weight_map")
             reg.metadata.update(flatten_metadata(idx.get("metadata", {})))
-            repo = os.path.dirname(path) or "."
+            repo = path.rsplit("/", 1)[0] if is_uri(path) else (os.path.dirname(path) or ".")
             for fname in sorted(set(idx["weight_map"].values())):
-                reg._add_file(os.path.join(repo, fname))
+                reg._add_file(f"{repo}/{fname}" if is_uri(path) else os.path.join(repo, fname))
             missing = [k for k in idx["weight_map"] if k not in reg.tensors]
             if missing:
                 raise SafetensorsError(f"{path}: tensors listed but absent from the shards: {missing[:3]}")
@@ -198,8 +238,11 @@ class TensorRegistry:
     from_repo = from_path
 
     def _add_file(self, path: str) -> None:
-        header, data_off = read_header(path)
-        size = os.path.getsize(path)
+        if is_uri(path):
+            header, data_off, size = _read_header_remote(path)
+        else:
+            header, data_off = read_header(path)
+            size = os.path.getsize(path)
         self.files.append(path)
         for name, ent in header.items():
             if name == "__metadata__":
@@ -245,7 +288,8 @@ class TensorReader:
         self._fd: Optional[int] = None
 
     def __enter__(self):
-        self._fd = os.open(self.info.file, os.O_RDONLY)
+        if not is_uri(self.info.file):
+            self._fd = os.open(self.info.file, os.O_RDONLY)
         return self
 
     def __exit__(self, *exc):
@@ -255,6 +299,14 @@ class TensorReader:
 
     def read_into(self, dst: np.ndarray, spans: Optional[Sequence[tuple[int, int]]] = None, threads: int = 8) -> int:
         """`spans` are (offset, length) relative to the tensor's first byte."""
+        if is_uri(self.info.file):
+            if spans is None:
+                spans = [(0, self.info.byte_size())]
+            for off, ln in spans:
+                if off < 0 or off + ln > self.info.byte_size():
+                    raise SafetensorsError(f"span [{off},{off + ln}) outside tensor {self.info.name}")
+            _vfs().read_spans(self.info.file, [(self.info.start + o, l) for o, l in spans], dst, parallelism=threads)
+            return sum(l for _, l in spans)
         own = self._fd is None
         fd = os.open(self.info.file, os.O_RDONLY) if own else self._fd
         try:

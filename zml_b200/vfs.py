@@ -198,17 +198,70 @@ class Vfs:
             parts = list(ex.map(lambda o: b.read_range(p, o, min(chunk, size - o)), offs))
         return b"".join(parts)
 
+    def read_spans(self, uri: str, spans, dst=None, chunk: int = 8 << 20, parallelism: int = 8):
+        """Byte ranges `spans` = [(offset, length), ...] of one file, back to back, as parallel range requests:
+        neighbouring ranges are fetched as one request, long ones are cut into `chunk`-sized requests.  Writes into
+        `dst` (a writable buffer of at least the total length) or returns the bytes.  This is what loads one rank's
+        shard of a checkpoint tensor from a remote repository."""
+        b, p = self.resolve(uri)
+        total = sum(l for _, l in spans)
+        out = memoryview(dst).cast("B") if dst is not None else memoryview(bytearray(total))
+        if len(out) < total:
+            raise ValueError("destination too small")
+        reqs, pos = [], 0                    # (file offset, length, position in the output)
+        for off, ln in spans:
+            if reqs and reqs[-1][0] + reqs[-1][1] == off and reqs[-1][1] + ln <= chunk:
+                reqs[-1] = (reqs[-1][0], reqs[-1][1] + ln, reqs[-1][2])
+            else:
+                done = 0
+                while done < ln:
+                    take = min(chunk, ln - done)
+                    reqs.append((off + done, take, pos + done))
+                    done += take
+            pos += ln
+
+        def fetch(r):
+            data = b.read_range(p, r[0], r[1])
+            if len(data) != r[1]:
+                raise IOError(f"{uri}: short read at {r[0]}: {len(data)} of {r[1]} bytes")
+            out[r[2]:r[2] + r[1]] = data
+
+        if len(reqs) <= 1 or parallelism <= 1:
+            for r in reqs:
+                fetch(r)
+        else:
+            with cf.ThreadPoolExecutor(max_workers=parallelism) as ex:
+                list(ex.map(fetch, reqs))
+        return None if dst is not None else bytes(out)
+
     def open(self, uri: str) -> "VfsFile":
         return VfsFile(self, uri)
 
-    def copy(self, src: str, dst: str) -> int:
-        data = self.read(src)
+    def copy(self, src: str, dst: str, chunk: int = 8 << 20, parallelism: int = 8) -> int:
+        """Streams `src` into the local file `dst`: `parallelism` range requests of `chunk` bytes in flight, written
+        at their offsets (a large remote file never sits in memory as a whole)."""
         b, p = self.resolve(dst)
         if not isinstance(b, FileBackend):
             raise ValueError("copy destination must be a local path")
+        sb, sp = self.resolve(src)
+        size = sb.stat(sp).size
         with open(p, "wb") as f:
-            f.write(data)
-        return len(data)
+            f.truncate(size)
+        fd = os.open(p, os.O_WRONLY)
+        try:
+            def piece(off):
+                data = sb.read_range(sp, off, min(chunk, size - off))
+                os.pwrite(fd, data, off)
+                return len(data)
+            offs = list(range(0, size, chunk))
+            if len(offs) <= 1:
+                n = sum(piece(o) for o in offs)
+            else:
+                with cf.ThreadPoolExecutor(max_workers=parallelism) as ex:
+                    n = sum(ex.map(piece, offs))
+        finally:
+            os.close(fd)
+        return n
 
 
 class VfsFile(io.RawIOBase):
