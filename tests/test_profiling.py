@@ -1,0 +1,25 @@
+"""Trace post-processing: the native Perfetto (protobuf) writer against its own decoder."""
+import json
+
+
+def test_perfetto_protobuf_writer_round_trip(tmp_path):
+    from zml_b200.profiling import perfetto
+    host = tmp_path / "h.json"
+    host.write_text(json.dumps({"traceEvents": [
+        {"ph": "M", "name": "thread_name", "pid": 1, "tid": 7, "args": {"name": "main"}},
+        {"ph": "X", "name": "outer", "ts": 10.0, "dur": 100.0, "pid": 1, "tid": 7, "args": {"step": 3}},
+        {"ph": "X", "name": "inner", "ts": 20.0, "dur": 30.0, "pid": 1, "tid": 7},
+        {"ph": "i", "name": "mark", "ts": 60.0, "pid": 1, "tid": 7},
+    ]}))
+    out = tmp_path / "t.pftrace"
+    assert perfetto.main([str(host), "-o", str(out)]) == 0
+    recs = perfetto.read_perfetto(str(out))
+    tracks = [r for r in recs if r.get("kind") == "track"]
+    events = [r for r in recs if r.get("kind") == "event"]
+    assert [t["name"] for t in tracks] == ["host spans", "main"] and tracks[1]["parent"] == tracks[0]["uuid"]
+    assert [(e["type"], e.get("name"), e["ts_ns"]) for e in events] == [
+        (1, "outer", 0), (1, "inner", 10_000), (2, None, 40_000), (3, "mark", 50_000), (2, None, 100_000)]
+    assert events[0]["args"] == {"step": "3"} and all(e["track"] == tracks[1]["uuid"] for e in events)
+    # varints longer than one byte survive (a timestamp of hours, in ns)
+    n = perfetto.write_perfetto([{"ph": "X", "name": "late", "ts": 3.6e9, "dur": 1.0, "pid": 0, "tid": 0}], str(out))
+    assert n == 4 and perfetto.read_perfetto(str(out))[2]["ts_ns"] == 3_600_000_000_000
