@@ -7,6 +7,8 @@
                                 (keys 1 / 2 / 3 switch pages, s changes the process sort, q quits)
     zb-smi --csv | --json       one line per sample (streams with --interval)
     zb-smi --prometheus-listen=127.0.0.1:9400   serve /metrics, /json
+    zb-smi --api [--api-port=9090]              the same agent on every interface (what --remotes reads)
+    zb-smi --remotes=http://hostA:9090,http://hostB:9090   add the devices of other hosts' agents to every view
     zb-smi --fake               use the built-in fake NVML (no GPU needed)
 Read-only: it never changes clocks, power limits or any other device setting.
 """
@@ -38,6 +40,9 @@ class Args:
     count: int = 0
     prometheus_listen: Optional[str] = None
     page: str = "overview"
+    api: bool = False
+    api_port: int = 9090
+    remotes: Optional[str] = None
     help = __doc__
 
 
@@ -45,10 +50,10 @@ class Collector:
     """Polls in a background thread and publishes the latest snapshot by swapping a reference
     (the double buffer of bin/zml-smi/collector/collector.zig)."""
 
-    def __init__(self, backend, interval: float):
-        self.backend, self.host = backend, metrics.HostPoller()
+    def __init__(self, backend, interval: float, remotes=None):
+        self.backend, self.host, self.remotes = backend, metrics.HostPoller(), remotes
         self.interval = max(interval, 0.1)
-        self.front = metrics.snapshot(backend, self.host)
+        self.front = metrics.snapshot(backend, self.host, remotes)
         self._stop = threading.Event()
         self._t = threading.Thread(target=self._run, daemon=True)
 
@@ -58,7 +63,7 @@ class Collector:
 
     def _run(self):
         while not self._stop.wait(self.interval):
-            self.front = metrics.snapshot(self.backend, self.host)
+            self.front = metrics.snapshot(self.backend, self.host, self.remotes)
 
     def latest(self) -> dict:
         return self.front
@@ -81,9 +86,13 @@ def main(argv=None) -> int:
     args = flags.parse(argv, Args)
     backend = make_backend(args.fake)
     host = metrics.HostPoller()
-    if args.prometheus_listen:
-        h, _, p = args.prometheus_listen.rpartition(":")
-        coll = Collector(backend, args.interval or 1.0).start()
+    remotes = metrics.RemoteAgents([u for u in args.remotes.split(",") if u]) if args.remotes else None
+    if args.prometheus_listen or args.api:
+        if args.prometheus_listen:
+            h, _, p = args.prometheus_listen.rpartition(":")
+        else:
+            h, p = "0.0.0.0", args.api_port
+        coll = Collector(backend, args.interval or 1.0, remotes).start()
         srv = outputs.serve(coll.latest, h or "127.0.0.1", int(p))
         print(f"serving http://{srv.server_address[0]}:{srv.server_address[1]}/metrics", flush=True)
         try:
@@ -98,7 +107,7 @@ def main(argv=None) -> int:
         return 0
     if args.top and not (args.csv or args.json):
         import tui
-        tui.run(lambda: metrics.snapshot(backend, host), args.interval or 1.0, args.count, args.page)
+        tui.run(lambda: metrics.snapshot(backend, host, remotes), args.interval or 1.0, args.count, args.page)
         if backend:
             backend.close()
         return 0
@@ -106,7 +115,7 @@ def main(argv=None) -> int:
     if args.csv:
         print(outputs.csv_header())
     while True:
-        snap = metrics.snapshot(backend, host)
+        snap = metrics.snapshot(backend, host, remotes)
         if args.csv:
             print(outputs.to_csv(snap), flush=True)
         elif args.json:

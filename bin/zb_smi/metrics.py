@@ -222,6 +222,42 @@ class FakeNvml:
     def nvmlDeviceGetComputeRunningProcesses(self, h): return [self._Obj(pid=os.getpid(), usedGpuMemory=5 << 30)]
 
 
-def snapshot(backend: Optional[NvmlBackend], host: HostPoller) -> dict:
+class RemoteAgents:
+    """Devices of other hosts, read from their agents' `/json` endpoint (`zb-smi --api` there): what
+    bin/zml-smi/api/client.zig does for `--remotes`.  A host that does not answer keeps its last devices, marked stale."""
+
+    def __init__(self, urls: list[str], timeout_s: float = 2.0):
+        for u in urls:
+            if not u.startswith(("http://", "https://")):
+                raise ValueError(f"remote host must start with http:// or https://: {u}")
+        self.urls, self.timeout_s = [u.rstrip("/") for u in urls], timeout_s
+        self.last: dict[str, list[dict]] = {u: [] for u in self.urls}
+        self.errors: dict[str, str] = {}
+
+    def poll(self) -> list[dict]:
+        import json
+        import urllib.request
+        out = []
+        for u in self.urls:
+            try:
+                with urllib.request.urlopen(u + "/json", timeout=self.timeout_s) as r:
+                    snap = json.loads(r.read())
+                host = snap.get("host", {}).get("hostname", u)
+                self.last[u] = [dict(g, remote=host, stale=False) for g in snap.get("gpus", [])]
+                self.errors.pop(u, None)
+            except Exception as e:          # unreachable agent: show what it last reported
+                self.errors[u] = f"{type(e).__name__}: {e}"
+                self.last[u] = [dict(g, stale=True) for g in self.last[u]]
+            out.extend(self.last[u])
+        return out
+
+
+def snapshot(backend: Optional[NvmlBackend], host: HostPoller, remotes: Optional[RemoteAgents] = None) -> dict:
     gpus = [asdict(backend.poll(i)) for i in range(backend.count())] if backend else []
-    return {"timestamp": time.time(), "host": asdict(host.poll(backend.versions() if backend else ("", ""))), "gpus": gpus}
+    if remotes is not None:
+        for g in remotes.poll():            # remote devices follow the local ones; their own index is kept beside
+            gpus.append(dict(g, remote_index=g.get("index"), index=len(gpus)))
+    snap = {"timestamp": time.time(), "host": asdict(host.poll(backend.versions() if backend else ("", ""))), "gpus": gpus}
+    if remotes is not None and remotes.errors:
+        snap["remote_errors"] = dict(remotes.errors)
+    return snap

@@ -47,7 +47,8 @@ def to_prometheus(snap: dict) -> str:
             continue
         out.append(f"# TYPE {metric} gauge")
         for g, v in rows:
-            out.append(f'{metric}{{device="{g["index"]}",name="{g["name"]}"}} {v}')
+            where = f',host="{g["remote"]}"' if g.get("remote") else ""
+            out.append(f'{metric}{{device="{g["index"]}",name="{g["name"]}"{where}}} {v}')
     host = snap["host"]
     for field, metric in HOST_GAUGES:
         if host.get(field) is not None:
@@ -66,9 +67,12 @@ def to_table(snap: dict) -> str:
         mem = f"{(g['mem_used_bytes'] or 0) / 2 ** 30:6.1f}/{(g['mem_total_bytes'] or 0) / 2 ** 30:6.1f}"
         lines.append(f"{g['index']:>3} {g['name'][:14]:<14} {gi('util_percent'):>4}% {gi('power_w'):>5}/{gi('power_limit_w'):<5}W "
                      f"{gi('temperature_c'):>4}C {gi('clock_sm_mhz'):>5}/{gi('clock_sm_max_mhz'):<5} {mem:>15}  "
-                     f"{','.join(g['throttle_reasons'])}")
+                     f"{','.join(g['throttle_reasons'])}"
+                     + (f"  @{g['remote']}#{g.get('remote_index')}{' (stale)' if g.get('stale') else ''}" if g.get("remote") else ""))
         for p in g["processes"]:
             lines.append(f"      pid {p['pid']} {p['name']} {p['user']} {(p['gpu_memory_bytes'] or 0) / 2 ** 20:.0f} MiB")
+    for url, err in snap.get("remote_errors", {}).items():
+        lines.append(f"remote {url}: {err}")
     return "\n".join(lines)
 
 

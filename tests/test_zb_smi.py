@@ -69,3 +69,35 @@ def test_tui_pages_render_bars_process_table_and_charts():
     assert r.returncode == 0 and "[2:processes]" in r.stdout
     be.close()
     assert fake.calls == ["init", "shutdown"]
+
+
+def test_remote_agent_devices_join_the_local_ones():
+    """An agent serves its snapshot over HTTP; a second monitor started with --remotes shows the agent's devices after
+    its own, keeps their host and index, and marks them stale when the agent goes away (bin/zml-smi/api/{server,client}.zig)."""
+    agent_backend = metrics.NvmlBackend(metrics.FakeNvml(devices=2))
+    agent_host = metrics.HostPoller()
+    srv = outputs.serve(lambda: metrics.snapshot(agent_backend, agent_host), "127.0.0.1", 0)
+    url = f"http://127.0.0.1:{srv.server_address[1]}"
+    try:
+        remotes = metrics.RemoteAgents([url])
+        snap = metrics.snapshot(metrics.NvmlBackend(metrics.FakeNvml(devices=1)), metrics.HostPoller(), remotes)
+        assert [g["index"] for g in snap["gpus"]] == [0, 1, 2]
+        assert [g.get("remote_index") for g in snap["gpus"]] == [None, 0, 1]
+        assert snap["gpus"][1]["remote"] == snap["host"]["hostname"] and snap["gpus"][1]["stale"] is False
+        assert "remote_errors" not in snap
+        table = outputs.to_table(snap)
+        assert f"@{snap['host']['hostname']}#1" in table
+        assert f'device="2",name="NVIDIA B200",host="{snap["host"]["hostname"]}"' in outputs.to_prometheus(snap)
+        # the command line: one JSON sample that includes the remote devices
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "zb_smi", "main.py"), "--fake", "--json", f"--remotes={url}"],
+                           capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr
+        assert len(json.loads(r.stdout)["gpus"]) == 4
+    finally:
+        srv.shutdown()
+        srv.server_close()
+    snap = metrics.snapshot(None, metrics.HostPoller(), remotes)
+    assert len(snap["gpus"]) == 2 and all(g["stale"] for g in snap["gpus"]) and url in snap["remote_errors"]
+    import pytest
+    with pytest.raises(ValueError):
+        metrics.RemoteAgents(["hostA:9090"])
