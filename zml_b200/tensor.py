@@ -134,6 +134,9 @@ def _spmd_align_dot(lhs: "Tensor", rhs: "Tensor", ca, cb, ba, bb):
     return lhs, rhs, pending
 
 
+_MEMORY_KINDS: dict = {}      # Tensor id -> memory kind declared with `on_memory` on a symbolic input
+
+
 class Tensor:
     """A tagged tensor.  Inside an `Exe` of a multi-process platform the value is this rank's shard and the
     shape's partition specs say how the shards tile the global tensor; `_partial` then names the logical mesh axes
@@ -186,6 +189,11 @@ class Tensor:
     def constant(shape_or_dims, value: Scalar = 0, dtype=None, device="cpu") -> "Tensor":
         s = shape_or_dims if isinstance(shape_or_dims, Shape) else Shape(shape_or_dims, dtype or DataType.f32)
         return Tensor(torch.full(s.dims, value, dtype=s.dtype.to_torch(), device=device), s)
+
+    @staticmethod
+    def uninitialized(shape: Shape, device="cpu") -> "Tensor":
+        """Storage of the given shape whose contents are unspecified (zml/tensor.zig:2359)."""
+        return Tensor(torch.empty(shape.dims, dtype=shape.dtype.to_torch(), device=device), shape)
 
     @staticmethod
     def zeroes(shape: Shape, device="cpu") -> "Tensor":
@@ -291,6 +299,8 @@ class Tensor:
     def rename_axis(self, ax: Axis, new: str) -> "Tensor":
         return self._reshape_meta(self._shape.set_tag(ax, new))
 
+    rename_tag = rename_axis                    # zml/tensor.zig:297
+
     def with_partitioning(self, specs: Mapping) -> "Tensor":
         """Attaches partition specs.  On a symbolic tensor, or outside an SPMD program, this only records them.
         On a computed tensor inside an SPMD program it is the resharding point of the reference
@@ -356,7 +366,42 @@ class Tensor:
             return self._like(d.cpu())
         raise ValueError(f"unknown memory kind {kind!r}")
 
-    on_memory = to_memory
+    def on_memory(self, kind: str) -> "Tensor":
+        """Declares that an executable's input lives in memory `kind` (zml/tensor.zig:257-273): a symbolic tensor
+        records the kind (`input_memory_kind`), a computed one is moved there."""
+        if kind not in ("device", "default", "host_pinned", "host_unpinned"):
+            raise ValueError(f"unknown memory kind {kind!r}")
+        if self._data is None:
+            _MEMORY_KINDS[self.id] = kind
+            return self
+        return self.to_memory(kind)
+
+    def input_memory_kind(self) -> Optional[str]:
+        """The kind set by `on_memory` on a symbolic input, else None (zml/tensor.zig:4505)."""
+        return _MEMORY_KINDS.get(self.id)
+
+    def output_memory_kind(self) -> str:
+        """Where this tensor's value lives (zml/tensor.zig:4501): device unless moved with `to_memory`."""
+        d = self._data
+        if d is None or d.is_cuda or not torch.cuda.is_available():
+            return "device"
+        return "host_pinned" if d.is_pinned() else "host_unpinned"
+
+    def donation(self) -> bool:
+        """True once another tensor's `reuse_buffer` has taken this tensor's storage (zml/tensor.zig:4496)."""
+        return bool(self._donated)
+
+    @staticmethod
+    def to_memory_all(tensors, kind: str):
+        """`to_memory` on every Tensor of a pytree (zml/tensor.zig:239-253)."""
+        from . import meta
+        return meta.map_tree(lambda t: t.to_memory(kind), tensors, lambda x: isinstance(x, Tensor))
+
+    @staticmethod
+    def on_memory_all(tensors, kind: str) -> None:
+        """`on_memory` on every symbolic Tensor of a pytree (zml/tensor.zig:275-288)."""
+        from . import meta
+        meta.visit(lambda t, _path: t.on_memory(kind) if t._data is None else None, tensors, lambda x: isinstance(x, Tensor))
 
     def reuse_buffer(self, other: "Tensor") -> "Tensor":
         """Writes this value into `other`'s storage (buffer donation, zml/tensor.zig:327-338)."""
@@ -454,6 +499,7 @@ class Tensor:
     def floor(self): return self._un(torch.floor)
     def ceil(self): return self._un(torch.ceil)
     def round_nearest_even(self): return self._un(torch.round)
+    round = round_nearest_even                  # zml/tensor.zig:1270
     def round_nearest_afz(self): return self._un(lambda x: torch.sign(x) * torch.floor(torch.abs(x) + 0.5))
     round = round_nearest_even
     def sign(self): return self._un(torch.sign)
@@ -775,7 +821,19 @@ class Tensor:
             s = Shape(s.dims, s.dtype, s.tags, part)
         return Tensor(self._need().reshape(s.dims), s)
 
-    unflatten = split_axis
+    def unflatten(self, ax, n: Optional[int] = None) -> "Tensor":
+        """(d0, d1, m, d3).unflatten(2, n) -> (d0, d1, n, m / n, d3): the axis keeps its tag on the outer part, the
+        inner part is untagged (zml/tensor.zig:1780-1795).  With a shape-like second argument it is `split_axis`."""
+        if not isinstance(n, int):
+            return self.split_axis(ax, n)
+        a = self.axis(ax)
+        d = self._shape.dims[a]
+        if d % n:
+            raise ValueError(f"unflatten expects the dimension to be divisible by n, but {d} is not divisible by {n}")
+        t = self._gathered(a)
+        dims = list(t._shape.dims[:a]) + [n, d // n] + list(t._shape.dims[a + 1:])
+        tags = list(t._shape.tags[:a]) + [t._shape.tags[a], None] + list(t._shape.tags[a + 1:])
+        return Tensor(t._need().reshape(dims), Shape(dims, t._shape.dtype, tags))
 
     def merge(self, axes_: Mapping[str, Iterable[Axis]]) -> "Tensor":
         """Inside an SPMD program a group whose outermost axis is sharded stays sharded the same way; a sharded
