@@ -227,3 +227,41 @@ def test_bounded_wait_times_out_cleanly_on_the_gpu():
     assert int(reached.item()) == 1
     assert torch.ones(4, device="cuda").sum().item() == 4.0
     assert l.zb_wait_probe(flag.data_ptr(), 9, 6_000_000_000, 0, None, _lib.stream_ptr()) == -21
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_vocab_parallel_argmax_protocol(world):
+    """The exchange of the in-kernel arg-max over a split vocabulary: every rank ends with the arg-max of the gathered
+    row, ties across ranks go to the lowest global index, launch after launch on slots that are never cleared."""
+    rows, v_per = 6, 11
+    heap = sim.ArgmaxHeap(world, max_rows=8)
+    rng = np.random.default_rng(world)
+    for epoch in range(1, 6):
+        lg = [rng.standard_normal((rows, v_per)).astype(np.float32) for _ in range(world)]
+        if epoch % 2 == 0:
+            for r in range(world):
+                lg[r][:, 3] = 7.0                      # the same maximum on every rank
+        if epoch == 3:
+            for r in range(world):
+                lg[r][0, :] = -np.inf                  # nothing to choose in row 0: token 0
+        res = sim.run_argmax(heap, epoch, lg, v_per)
+        assert not res["timeouts"]
+        full = np.concatenate(lg, axis=1)
+        want = full.argmax(1)
+        if epoch == 3:
+            want[0] = 0
+        for r in range(world):
+            assert np.array_equal(res["out"][r], want), (epoch, r)
+        if epoch % 2 == 0:
+            assert (want == 3).all()
+
+
+def test_vocab_parallel_argmax_dead_rank_is_reported_and_local_candidate_kept():
+    heap = sim.ArgmaxHeap(2, max_rows=4)
+    lg = [np.array([[0.0, 1.0, 0.5]], dtype=np.float32), np.array([[2.0, 0.0, 0.0]], dtype=np.float32)]
+    assert not sim.run_argmax(heap, 1, lg, 3)["timeouts"]
+    assert not sim.run_argmax(heap, 2, lg, 3)["timeouts"]
+    res = sim.run_argmax(heap, 3, lg, 3, limit_s=0.1, faults=sim.Faults(dead_ranks={1}))      # stale parity-1 slots hold epoch 1
+    t = res["timeouts"][0]
+    assert (t.phase, t.awaited, t.epoch) == (sim.PHASE_ARGMAX_WAIT, 1, 3)
+    assert res["out"][0][0] == 1                       # rank 0's own candidate

@@ -103,6 +103,28 @@ def main():
         expect_close(plain.float(), want, atol=6e-2, rtol=3e-2, min_close=0.995)
     ops.raise_on_status()
 
+    # arg-max over a vocabulary split across the ranks, candidates exchanged inside the kernel, vs the arg-max of the
+    # gathered rows: ties across ranks (lowest global index wins), padding columns, rows beyond one block per SM,
+    # repeated calls (slot parity)
+    v_per = 1000
+    for it, rows in enumerate([1, 32, 200, 32, 1024, 5]):
+        lg = torch.randn(rows, v_per, device=dev)
+        if it % 2 == 1:                       # the same maximum on every rank, and twice inside a shard
+            lg[:, 17] = 9.0
+            lg[:, 400] = 9.0
+        if it == 2:
+            lg[:, v_per - 8:] = float("-inf")
+        if it == 5:
+            lg[:] = float("-inf")             # nothing to choose: token 0 everywhere
+        assert ctx.can_argmax_tp(rows)
+        got = ctx.argmax_tp(lg, comm.rank * v_per)
+        full = comm.all_gather(lg, dim=1)
+        want = full.argmax(1).to(torch.int32) if it != 5 else torch.zeros(rows, dtype=torch.int32, device=dev)
+        if it in (1, 3):
+            assert int(want[0]) == 17
+        assert torch.equal(got, want), ("argmax_tp", rows, got[:8].tolist(), want[:8].tolist())
+    ops.raise_on_status()
+
     # all-reduce inside NVSwitch (multimem load-reduce + store) vs NCCL, in place and out of place, odd sizes
     if ctx.has_multicast:
         for it, (t, d) in enumerate([(1, 1024), (37, 1024), (512, 1024), (1000, 1016), (37, 1024)]):

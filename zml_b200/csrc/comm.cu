@@ -180,6 +180,86 @@ zb_allreduce_ll_kernel(const uint4* __restrict__ in, const uint4* __restrict__ r
   }
 }
 
+// ------------------------------------------------------------------ arg-max over a vocabulary split across ranks
+// Greedy sampling under a vocab-parallel lm_head: every rank holds the logits of its own columns.  One block per
+// row finds the local maximum and its first index, writes {value, tag} and {global index, tag} into its slot of
+// every peer's heap, then the first `world` lanes of warp 0 collect the peers' pairs and pick the winner (highest
+// value; equal values -> lowest global index, which is what an arg-max over the gathered row would return).  Every
+// rank ends with the same token, and nothing but 16 bytes per row and peer crosses NVLink - the reference (and the
+// fallback here) all-gathers the candidates with two NCCL calls and reduces them with tensor ops
+// (examples/llm/models/llama/model.zig: sampling after the lm_head).  Slots alternate by epoch parity, as in the
+// two-shot all-reduce above; waits are bounded and end in the status word, the row then keeps the local candidate.
+constexpr uint32_t kKernelArgmaxTp = 15;
+constexpr int kArgmaxTpMaxRows = 1024;
+
+struct TpArgmax {
+  uint2* slots[8];          // [2 parities][world sources][kArgmaxTpMaxRows][2] in every rank's heap ([rank] is local)
+  uint32_t* epoch;
+  uint32_t* ticket;
+  int rank;
+  int world;
+};
+
+__global__ void __launch_bounds__(1024)
+zb_argmax_tp_kernel(const float* __restrict__ logits, int32_t* __restrict__ out, int rows, int vocab, long long stride,
+                    int col_offset, const TpArgmax ar, ZbStatus* status) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(ar.epoch);
+  const size_t par = epoch & 1u;
+  const int W = ar.world, rank = ar.rank;
+  bool timed_out = false;
+  const uint64_t t0 = zb_globaltimer();
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float best;
+    int bi;
+    zb_block_argmax_1024(logits + static_cast<size_t>(row) * stride, vocab, best, bi);
+    if (threadIdx.x < 32) {
+      const int gi = bi == 0x7fffffff ? bi : bi + col_offset;
+      const int lane = threadIdx.x;
+      if (lane < W && lane != rank) {          // lane p publishes to peer p ...
+        uint2* dst = ar.slots[lane] + ((par * W + rank) * kArgmaxTpMaxRows + row) * 2;
+        zb_st_ll(dst, __float_as_uint(best), epoch);
+        zb_st_ll(dst + 1, static_cast<uint32_t>(gi), epoch);
+      }
+      float cv = best;
+      int ci = gi;
+      if (lane < W && lane != rank) {          // ... and collects peer p's candidate
+        const uint2* src = ar.slots[rank] + ((par * W + lane) * kArgmaxTpMaxRows + row) * 2;
+        uint32_t spins = 0;
+        while (true) {
+          const uint2 a = zb_ld_ll(src), b = zb_ld_ll(src + 1);
+          if (a.y == epoch && b.y == epoch) {
+            cv = __uint_as_float(a.x);
+            ci = static_cast<int>(b.x);
+            break;
+          }
+          if ((++spins & 0x3f) == 0 && zb_globaltimer() - t0 > ZB_WAIT_LIMIT_NS) {
+            timed_out = true;
+            break;
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {         // lanes >= world hold copies of the local candidate
+        const float ov = __shfl_xor_sync(0xffffffffu, cv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, ci, o);
+        zb_argmax_merge(cv, ci, ov, oi);
+      }
+      if (lane == 0) out[row] = ci == 0x7fffffff ? 0 : ci;
+    }
+    __syncthreads();                            // the reduction's shared memory is reused by the next row
+  }
+  if (timed_out) zb_record_error(status, ZB_ERR_FLAG_TIMEOUT, kKernelArgmaxTp, blockIdx.x, rank);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t ticket = atomicAdd(ar.ticket, 1u);
+    if (ticket == gridDim.x - 1) {
+      *ar.ticket = 0u;
+      *reinterpret_cast<volatile uint32_t*>(ar.epoch) = epoch + 1u;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ all-reduce through NVSwitch (multimem)
 // out = residual + sum over ranks of `in`, bf16, any size that is a multiple of 16 bytes; `in` and `out` live at
 // the same offsets of every rank's heap, and the heap is bound to a multicast address.  Every rank owns a
@@ -353,7 +433,8 @@ ZbArContext* zb_ar_ctx_create(int rank, int world, void* const* heap, size_t rec
     return nullptr;
   }
   // {gemm epoch, exit ticket, barrier epoch, unused, combine epoch, combine exit ticket, tagged-slot all-reduce epoch,
-  //  its exit ticket, multimem all-reduce epoch, its exit ticket, band-pipeline epoch, unused ...}
+  //  its exit ticket, multimem all-reduce epoch, its exit ticket, band-pipeline epoch, its ticket, vocab-parallel arg-max
+  //  epoch, its exit ticket, unused ...}
   const uint32_t init[16] = {1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u, 1u, 0u};
   cudaMemcpy(ctr, init, sizeof(init), cudaMemcpyHostToDevice);
   c->epoch = ctr;
@@ -429,6 +510,34 @@ int zb_allreduce_ll(const ZbArContext* c, const void* in, const void* residual, 
   zb_launch(zb_allreduce_ll_kernel, dim3(static_cast<unsigned>(blocks)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
             reinterpret_cast<const uint4*>(in), reinterpret_cast<const uint4*>(residual), reinterpret_cast<uint4*>(out), vs, ar,
             st->status);
+  zb_count_launch(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// out[r] = arg-max over the whole vocabulary of row r; every rank passes the f32 logits of its own `vocab` columns
+// (global column of local column j: col_offset + j; padding columns hold -inf).  `slot_off` addresses
+// zb_argmax_tp_slot_bytes(world) bytes of every rank's heap.  rows <= 1024.
+size_t zb_argmax_tp_slot_bytes(int world) { return static_cast<size_t>(2) * world * kArgmaxTpMaxRows * 2 * sizeof(uint2); }
+
+int zb_argmax_tp(const ZbArContext* c, const float* logits, int32_t* out, int rows, int vocab, long long stride, int col_offset,
+                 size_t slot_off, void* stream) {
+  ZbDeviceState* st = zb_device_state();
+  if (!st || !c) return -20;
+  if (rows <= 0) return 0;
+  if (rows > kArgmaxTpMaxRows || slot_off % 16 != 0 || vocab < 0) return -10;
+  TpArgmax ar = {};
+  for (int r = 0; r < c->world; ++r) ar.slots[r] = reinterpret_cast<uint2*>(reinterpret_cast<char*>(c->heap[r]) + slot_off);
+  ar.epoch = c->epoch + 12;
+  ar.ticket = c->epoch + 13;
+  ar.rank = c->rank;
+  ar.world = c->world;
+  // A block waits for the same block of every peer, so all blocks must be resident at once on every rank: at most one
+  // per SM, the loop over rows covers the rest (every rank visits the rows in the same order, publishing before it waits).
+  const int blocks = rows < st->num_sms ? rows : st->num_sms;
+  // Launched without programmatic dependent launch, like the all-reduce inside NVSwitch below: a kernel that waits for
+  // its peers starts only after the kernel in front of it (the lm_head GEMM) has left the SMs.
+  zb_argmax_tp_kernel<<<dim3(static_cast<unsigned>(blocks)), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      logits, out, rows, vocab, stride, col_offset, ar, st->status);
   zb_count_launch(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -268,6 +268,38 @@ ZB_DEVICE uint2 zb_ld_ll(const uint2* p) {
   return v;
 }
 
+// Row maximum and its first index over `n` floats by a block of 1024 threads: ties go to the lowest index, NaN
+// never wins, an empty row gives (-inf, 0x7fffffff).  The result is valid in warp 0 (every lane).  Uses 256 bytes
+// of static shared memory; callers that loop over rows must __syncthreads() between calls.
+ZB_DEVICE void zb_argmax_merge(float& best, int& bi, float ov, int oi) {
+  if (ov > best || (ov == best && oi < bi)) {
+    best = ov;
+    bi = oi;
+  }
+}
+ZB_DEVICE void zb_block_argmax_1024(const float* __restrict__ row, int n, float& best, int& bi) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  best = -INFINITY;
+  bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += 1024) zb_argmax_merge(best, bi, row[i], i);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    zb_argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = best;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = sv[threadIdx.x];
+    bi = si[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      zb_argmax_merge(best, bi, __shfl_xor_sync(0xffffffffu, best, o), __shfl_xor_sync(0xffffffffu, bi, o));
+  }
+}
+
 // Programmatic dependent launch.  `zb_pdl_wait` blocks until every grid this one depends on has
 // finished and its writes are visible; nothing produced or still read by a preceding kernel may
 // be touched before it.  `zb_pdl_launch` lets the next kernel in the stream begin its own

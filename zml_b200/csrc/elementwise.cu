@@ -300,46 +300,10 @@ __global__ void __launch_bounds__(1024) zb_argmax_f32_kernel(const float* __rest
                                                              long long stride) {
   zb_pdl_launch();
   zb_pdl_wait();
-  const float* row = logits + static_cast<size_t>(blockIdx.x) * stride;
-  float best = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += 1024) {
-    const float v = row[i];
-    if (v > best || (v == best && i < bi)) {
-      best = v;
-      bi = i;
-    }
-  }
-  __shared__ float sv[32];
-  __shared__ int si[32];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > best || (ov == best && oi < bi)) {
-      best = ov;
-      bi = oi;
-    }
-  }
-  if ((threadIdx.x & 31) == 0) {
-    sv[threadIdx.x >> 5] = best;
-    si[threadIdx.x >> 5] = bi;
-  }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    best = sv[threadIdx.x];
-    bi = si[threadIdx.x];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) {
-        best = ov;
-        bi = oi;
-      }
-    }
-    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
-  }
+  float best;
+  int bi;
+  zb_block_argmax_1024(logits + static_cast<size_t>(blockIdx.x) * stride, vocab, best, bi);
+  if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
 }
 
 // ---------------------------------------------------------------- top-k + Gumbel-max

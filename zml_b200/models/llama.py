@@ -524,6 +524,8 @@ class LlamaModel:
                 return ops.argmax(logits)
             return ops.topk_sample(logits, strategy.topk, strategy.temperature, seed, step, rng=rng)
         if strategy.topk <= 1:
+            if comm.fused is not None and logits.is_cuda and comm.fused.can_argmax_tp(logits.shape[0]):
+                return comm.fused.argmax_tp(logits, comm.rank * self.v_per)     # candidates exchanged inside the kernel
             idx = ops.argmax(logits)
             val = logits.gather(1, idx.long()[:, None])[:, 0]
             vals = comm.all_gather(val[None])                   # [P, B]

@@ -51,6 +51,8 @@ _SIGS = {
     "zb_moe_grouped_gemm_fp4": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_i, c_i, c_p]),
     "zb_moe_gather_fp4": (c_i, [c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_p]),
     "zb_allreduce_ll": (c_i, [c_p, c_p, c_p, c_p, C.c_longlong, c_sz, c_sz, c_p]),
+    "zb_argmax_tp": (c_i, [c_p, c_p, c_p, c_i, c_i, c_ll, c_i, c_sz, c_p]),
+    "zb_argmax_tp_slot_bytes": (c_sz, [c_i]),
     "zb_moe_combine": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_p, c_sz, c_sz, c_p]),
     "zb_wait_probe": (c_i, [c_p, C.c_uint, c_ull, C.c_uint, c_p, c_p]),
     "zb_decode_advance": (c_i, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i, c_i, c_i, c_i, c_i, c_p]),
@@ -141,7 +143,7 @@ STATUS_NAMES = {0: "ok", 1: "mbarrier wait timed out", 2: "flag wait timed out",
                 3: "index out of bounds", 4: "bad argument"}
 KERNEL_NAMES = {1: "gemm_bf16", 2: "paged_decode", 3: "paged_prefill", 4: "gemm_ar_fused",
                 5: "comm_barrier", 6: "moe_grouped_gemm", 7: "moe_a2a", 8: "wait_probe", 9: "moe_grouped_gemm_w4",
-                10: "moe_combine", 11: "allreduce_ll", 12: "allreduce_mm", 13: "paged_prefill_tc", 14: "gemm_2cta",
+                10: "moe_combine", 11: "allreduce_ll", 12: "allreduce_mm", 13: "paged_prefill_tc", 14: "gemm_2cta", 15: "argmax_tp",
                 20: "rope_kvwrite", 21: "embedding", 22: "decode_advance", 24: "causal_conv1d", 25: "gated_delta_scan"}
 
 

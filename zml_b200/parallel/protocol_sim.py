@@ -182,3 +182,73 @@ def run_two_shot(heap: SlotHeap, epoch: int, inputs: list, limit_s: float = 0.3,
     for t in threads:
         t.join()
     return {"out": outs, "timeouts": timeouts}
+
+
+# ---- arg-max over a vocabulary split across the ranks (csrc/comm.cu: zb_argmax_tp_kernel) -----------------
+# Per row every rank writes {value, tag} and {global index, tag} into its slot of every peer
+# ([parity][source][row][2]), then collects the peers' pairs and keeps the highest value, equal
+# values going to the lowest global index.  A wait that runs out leaves the local candidate in
+# place and is reported.
+PHASE_ARGMAX_WAIT = 5    # rank waiting for a peer's candidate
+
+
+class ArgmaxHeap:
+    def __init__(self, world: int, max_rows: int):
+        self.world, self.max_rows = world, max_rows
+        self.word = np.zeros((world, 2, world, max_rows, 2), dtype=np.float64)     # [rank][parity][src][row][value | index]
+        self.tag = np.zeros((world, 2, world, max_rows, 2), dtype=np.int64)
+
+
+def run_argmax_rank(heap: ArgmaxHeap, rank: int, epoch: int, logits: np.ndarray, col_offset: int, limit_s: float,
+                    faults: Faults, out: np.ndarray) -> Optional[Timeout]:
+    """logits: this rank's columns [rows, v_local]; out: int64 [rows] receives the global arg-max."""
+    w, par = heap.world, epoch & 1
+    if rank in faults.delay_s:
+        time.sleep(faults.delay_s[rank])
+    first: Optional[Timeout] = None
+    for row in range(logits.shape[0]):
+        r = logits[row]
+        finite = ~np.isnan(r)
+        if r.size and finite.any() and np.max(r[finite]) > -np.inf:
+            best = float(np.max(r[finite]))
+            gi = int(np.flatnonzero(finite & (r == best))[0]) + col_offset
+        else:
+            best, gi = -np.inf, 0x7FFFFFFF
+        for p in range(w):
+            if p == rank or (rank, p) in faults.drop_push:
+                continue
+            heap.word[p, par, rank, row] = (best, gi)
+            heap.tag[p, par, rank, row] = epoch
+        cv, ci = best, gi
+        for p in range(w):
+            if p == rank:
+                continue
+            if not _wait(lambda: int(heap.tag[rank, par, p, row].min()), epoch, limit_s):
+                first = first or Timeout(rank, PHASE_ARGMAX_WAIT, row, p, epoch)
+                continue
+            ov, oi = float(heap.word[rank, par, p, row, 0]), int(heap.word[rank, par, p, row, 1])
+            if ov > cv or (ov == cv and oi < ci):
+                cv, ci = ov, oi
+        out[row] = 0 if ci == 0x7FFFFFFF else ci
+    return first
+
+
+def run_argmax(heap: ArgmaxHeap, epoch: int, logits: list, v_per: int, limit_s: float = 0.3,
+               faults: Optional[Faults] = None) -> dict:
+    """One launch on every live rank; returns {"out": [world][rows], "timeouts": {rank: Timeout}}."""
+    faults = faults or Faults()
+    w = heap.world
+    outs = [np.full(logits[r].shape[0], -1, dtype=np.int64) for r in range(w)]
+    timeouts: dict = {}
+
+    def body(r):
+        t = run_argmax_rank(heap, r, epoch, logits[r], r * v_per, limit_s, faults, outs[r])
+        if t is not None:
+            timeouts[r] = t
+
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(w) if r not in faults.dead_ranks]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    return {"out": outs, "timeouts": timeouts}

@@ -127,7 +127,9 @@ class SymmetricContext:
         self.band_flag_off = self.mm_flag_off + 2 * 128 * 8 * 4
         self.nb_cap = (max_tokens + 127) // 128
         self.band_flag_bytes = _align(int(l.zb_band_flag_bytes(self.nb_cap)))
-        self.part_off = _align(self.band_flag_off + self.band_flag_bytes, 4096)
+        # slots of the arg-max over a vocabulary split across the ranks (16 bytes per row, source rank and parity)
+        self.argmax_off = _align(self.band_flag_off + self.band_flag_bytes)
+        self.part_off = _align(self.argmax_off + int(l.zb_argmax_tp_slot_bytes(w)), 4096)
         self.heap_bytes = self.part_off + act_bytes
         self.hidden, self.max_tokens = hidden, max_tokens
         self.mc_ptr = 0
@@ -341,6 +343,22 @@ class SymmetricContext:
         _lib.check(_lib.lib().zb_allreduce_ll(self.ctx, part.data_ptr(), residual.data_ptr() if residual is not None else None,
                                               out.data_ptr(), part.numel(), self.ll_off, self.ll_bytes, _lib.stream_ptr()),
                    "zb_allreduce_ll")
+        return out
+
+    ARGMAX_MAX_ROWS = 1024
+    TP_ARGMAX = os.environ.get("ZB_TP_ARGMAX", "1") == "1"
+
+    def can_argmax_tp(self, rows: int) -> bool:
+        return self.ctx is not None and self.TP_ARGMAX and 0 < rows <= self.ARGMAX_MAX_ROWS
+
+    def argmax_tp(self, logits: torch.Tensor, col_offset: int) -> torch.Tensor:
+        """All ranks: int32 [rows], the arg-max over the whole vocabulary of rows whose columns are split across the
+        ranks (this rank holds columns col_offset .. col_offset + logits.shape[1]); candidates are exchanged through
+        tagged slots inside the kernel (libzb_cuda.so: zb_argmax_tp), every rank gets the same ids."""
+        assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+        _lib.check(_lib.lib().zb_argmax_tp(self.ctx, logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1],
+                                           logits.stride(0), int(col_offset), self.argmax_off, _lib.stream_ptr()), "zb_argmax_tp")
         return out
 
     def can_combine(self, tokens: int, d: int) -> bool:
