@@ -1,0 +1,111 @@
+"""Smaller entry points of the reference's public API (zml/tensor.zig, buffer.zig, platform.zig, io.zig, nn.zig):
+memory kinds, unflatten / rename_tag, buffer options and shard iteration, device descriptions, store views, and the
+image resizes with the reference's sampling rules."""
+import numpy as np
+import pytest
+import torch
+
+from zml_b200 import Buffer, Platform, Shape, Tensor
+from zml_b200.dtype import DataType
+from zml_b200.io import TensorStore
+from zml_b200.nn import image
+from zml_b200.safetensors import save_file
+
+
+def test_tensor_unflatten_rename_round_memory_kinds():
+    t = Tensor.from_torch(torch.arange(24.).reshape(2, 12), ["b", "m"])
+    u = t.unflatten("m", 3)
+    assert u.shape().dims == (2, 3, 4) and u.shape().tags[:2] == ("b", "m") and u.shape().tags[2] in (None, "_")
+    assert torch.equal(u.data, t.data.reshape(2, 3, 4))
+    with pytest.raises(ValueError):
+        t.unflatten("m", 5)
+    assert t.unflatten("m", {"x": 3, "y": 4}).shape().tags == ("b", "x", "y")
+    assert t.rename_tag("m", "k").shape().tags == ("b", "k")
+    assert torch.equal(Tensor.from_torch(torch.tensor([0.5, 1.5, 2.5, -0.5])).round().data, torch.tensor([0., 2., 2., -0.]))
+    sym = Tensor.from_shape(Shape([2, 3], DataType.f32, ["a", "b"]))
+    assert sym.input_memory_kind() is None
+    assert sym.on_memory("host_pinned") is sym and sym.input_memory_kind() == "host_pinned"
+    Tensor.on_memory_all({"x": sym, "y": [t]}, "device")
+    assert sym.input_memory_kind() == "device" and t.input_memory_kind() is None
+    with pytest.raises(ValueError):
+        sym.on_memory("texture")
+    assert t.output_memory_kind() == "device" and not t.donation()
+    moved = Tensor.to_memory_all({"x": t, "n": 3}, "host_unpinned")
+    assert torch.equal(moved["x"].data, t.data) and moved["n"] == 3
+    dst = Tensor.from_torch(torch.zeros(2, 12), ["b", "m"])
+    t.reuse_buffer(dst)
+    assert dst.donation()
+    assert Tensor.uninitialized(Shape([4, 2], DataType.bf16, ["a", "b"])).data.shape == (4, 2)
+
+
+def test_buffer_options_shards_and_sizes():
+    pl = Platform.init("cpu")
+    b = Buffer.from_tensor(pl, torch.arange(16.).reshape(4, 4), wait=False)
+    assert b.num_shards() == pl.num_devices() and b.byte_size() == 64 * pl.num_devices()
+    ids = [d for d, _, ptr in b.iter_shards() if ptr]
+    assert ids == sorted(ids) and len(ids) == b.num_shards()
+    h = Buffer.from_bytes(pl, Shape((2, 2), "f32"), np.arange(4, dtype=np.float32).tobytes(), memory="host_unpinned")
+    assert h.memory_kind() in ("device", "host_unpinned")            # one memory on a CPU platform
+    assert h.to_tensor().tolist() == [[0.0, 1.0], [2.0, 3.0]]
+    with pytest.raises(ValueError):
+        Buffer.from_tensor(pl, torch.zeros(2), memory="texture")
+    Buffer.deinit_all({"a": b, "l": [h], "other": 1})
+    assert b.num_shards() == 0 and h.num_shards() == 0
+
+
+def test_device_descriptions():
+    pl = Platform.init("cpu")
+    d = pl.devices[1]
+    assert d.process_index == 0 and d.local_hardware_id() == 1 and d.compute_capability() is None
+    assert "id 1" in d.to_string() and "coords" in d.debug_string() and d.kind()
+    assert d.memory("device") is not None and d.memory("host_pinned") is not None
+
+
+def test_store_views(tmp_path):
+    p = str(tmp_path / "m.safetensors")
+    save_file({"model.layers.0.self_attn.q_proj.weight": torch.zeros(4, 2),
+                          "model.layers.0.mlp.weight_scale_2": torch.zeros(1),
+                          "lm_head.weight": torch.zeros(3, 2)}, p)
+    store = TensorStore.from_path(p)
+    layer = store.view().with_prefix("model").with_prefix("layers").with_layer(0)
+    assert layer.has_key("self_attn") and layer.has_key("self_attn.q_proj.weight") and not layer.has_key("cross_attn")
+    assert layer.parent().prefix == "model.layers" and layer.root().prefix == "" and layer.root().parent().prefix == ""
+    assert layer.get_shape("self_attn.q_proj.weight").dims == (4, 2)
+    assert layer.get_shape("lm_head.weight") is None and layer.get_shape("lm_head.weight", no_prefix=True).dims == (3, 2)
+    # a group name matches as a prefix, a tensor to create must exist under exactly that name
+    assert layer.with_prefix("mlp").has_key("weight_scale") and layer.with_prefix("mlp").maybe_create_tensor("weight_scale") is None
+    t = layer.create_tensor("self_attn.q_proj.weight", ["dout", "d"])
+    assert store.get_sources_by_id(t.id) == ["model.layers.0.self_attn.q_proj.weight"]
+    assert store.get_reader_by_id(t.id).info.shape.dims == (4, 2) and store.get_shape("lm_head.weight").dims == (3, 2)
+    with pytest.raises(KeyError):
+        store.get_reader_by_id(-1)
+
+
+def test_image_resizes_follow_the_reference_sampling_rules():
+    # nearest: pixel i reads floor((i + 0.5) * in / out); the reference's 4-D example (zml/nn.zig: test upsample)
+    x = Tensor.from_torch(torch.arange(1, 17, dtype=torch.int32).reshape(2, 2, 2, 2))
+    y = image.upsample(x, [2, 2])
+    assert y.shape().dims == (2, 2, 4, 4)
+    assert y.data[0, 0].tolist() == [[1, 1, 2, 2], [1, 1, 2, 2], [3, 3, 4, 4], [3, 3, 4, 4]]
+    assert image.upsample(Tensor.from_torch(torch.tensor([[[1, 2]]], dtype=torch.int32)), 2).data.tolist() == [[[1, 1, 2, 2]]]
+    z = image.upsample(Tensor.from_torch(torch.arange(1, 5, dtype=torch.int32).reshape(1, 1, 1, 2, 2)), 2)
+    assert z.shape().dims == (1, 1, 2, 4, 4)
+    # linear: output pixel i sits at i * in / out, no half-pixel shift; reads past the end repeat the last pixel
+    row = Tensor.from_torch(torch.tensor([[0.0, 10.0, 20.0, 30.0]]), ["h", "w"])
+    up = image.resize_linear_1d(row, "w", 8)
+    assert torch.allclose(up.data, torch.tensor([[0.0, 5.0, 10.0, 15.0, 20.0, 25.0, 30.0, 30.0]]))
+    # a padded image: only the first three pixels are real
+    up3 = image.resize_linear_1d(row, "w", 6, original_len=3)
+    assert torch.allclose(up3.data, torch.tensor([[0.0, 5.0, 10.0, 15.0, 20.0, 25.0]]))
+    # cubic: Catmull-Rom reproduces a straight line away from the borders and passes through the samples
+    line = Tensor.from_torch(torch.arange(0.0, 80.0, 10.0)[None], ["h", "w"])
+    cu = image.resize_cubic_1d(line, "w", 16)
+    assert torch.allclose(cu.data[0, 2:12], torch.arange(10.0, 60.0, 5.0), atol=1e-4)
+    assert torch.allclose(cu.data[0, 2:12:2], line.data[0, 1:6], atol=1e-4)
+    assert float(cu.data[0, 12]) == 50.0          # the 4-pixel window is clamped into the image, the fraction is not
+    # two axes in turn, shapes as in the reference's tests; integer images compute in f32 and keep their dtype
+    img = Tensor.from_torch((torch.arange(100).reshape(10, 10) % 7).to(torch.uint8), ["a", "b"])
+    assert image.resize_bilinear(img, {"a": 20, "b": 5}).shape().dims == (20, 5)
+    out = image.resize_bicubic(img, {"a": 20})
+    assert out.shape().dims == (20, 10) and out.data.dtype == torch.uint8
+    assert image.resize_bilinear(img, {"a": 20, "b": 5}, original_len=torch.tensor([8.0, 10.0])).shape().dims == (20, 5)

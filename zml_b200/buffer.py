@@ -29,24 +29,41 @@ class Buffer:
 
     # ------------------------------------------------------------------ constructors
     @staticmethod
-    def from_tensor(platform, host: torch.Tensor, shape: Optional[Shape] = None, sharding: Optional[Sharding] = None) -> "Buffer":
+    def from_tensor(platform, host: torch.Tensor, shape: Optional[Shape] = None, sharding: Optional[Sharding] = None,
+                    wait: bool = True, memory: str = "default") -> "Buffer":
+        """`wait` / `memory` are the reference's `FromOptions` (zml/buffer.zig:69): with wait=False the copies are
+        left in flight on the devices' streams (`await_` joins them); `memory` places the shards in device memory
+        (device | default) or keeps them on the host (host_pinned | host_unpinned)."""
+        if memory not in ("default", "device", "host_pinned", "host_unpinned"):
+            raise ValueError(f"unknown memory kind {memory!r}")
         shape = shape or Shape(tuple(host.shape), DataType.from_torch(host.dtype))
         sharding = sharding or platform.pick_sharding(shape)
         pl = sharding.placement(shape)
         shards = {}
         for dev in platform.local_devices():
             piece = host[pl.shard_index(dev.mesh_device)]
-            shards[dev.id] = piece.to(dev.torch_device, non_blocking=True).contiguous()
-        return Buffer(shape, sharding, shards, platform)
+            if memory in ("host_pinned", "host_unpinned"):
+                piece = piece.cpu().contiguous().clone()
+                if memory == "host_pinned" and torch.cuda.is_available():
+                    piece = piece.pin_memory()
+                shards[dev.id] = piece
+            else:
+                shards[dev.id] = piece.to(dev.torch_device, non_blocking=True).contiguous()
+        buf = Buffer(shape, sharding, shards, platform)
+        return buf.await_() if wait else buf
 
     @staticmethod
-    def from_slice(platform, s: Slice, sharding: Optional[Sharding] = None) -> "Buffer":
-        return Buffer.from_tensor(platform, s.to_torch(), s.shape, sharding)
+    def from_slice(platform, s: Slice, sharding: Optional[Sharding] = None, **opts) -> "Buffer":
+        return Buffer.from_tensor(platform, s.to_torch(), s.shape, sharding, **opts)
+
+    from_slice_opts = from_slice
 
     @staticmethod
-    def from_bytes(platform, shape: Shape, data: bytes, sharding: Optional[Sharding] = None) -> "Buffer":
+    def from_bytes(platform, shape: Shape, data: bytes, sharding: Optional[Sharding] = None, **opts) -> "Buffer":
         arr = np.frombuffer(data, dtype=np.uint8).copy()
-        return Buffer.from_slice(platform, Slice(shape, arr), sharding)
+        return Buffer.from_slice(platform, Slice(shape, arr), sharding, **opts)
+
+    from_bytes_opts = from_bytes
 
     @staticmethod
     def scalar(platform, value, dtype=DataType.f32) -> "Buffer":
@@ -67,6 +84,32 @@ class Buffer:
 
     def dtype(self) -> DataType:
         return self._shape.dtype
+
+    def num_shards(self) -> int:
+        """Shards this process holds (zml/buffer.zig:93)."""
+        return len(self.shards)
+
+    def byte_size(self) -> int:
+        """Bytes over all devices: shard bytes x devices of the sharding (zml/buffer.zig:314-317)."""
+        return self.placement.shape.byte_size() * len(self.sharding.devices_in_canonical_order())
+
+    def iter_shards(self):
+        """(device id, shard tensor, device pointer) per local shard, in device order (zml/buffer.zig:49-66)."""
+        for d in sorted(self.shards):
+            t = self.shards[d]
+            yield d, t, t.data_ptr()
+
+    def memory_kind(self) -> str:
+        t = self.local()
+        if t.is_cuda or not torch.cuda.is_available():
+            return "device"
+        return "host_pinned" if t.is_pinned() else "host_unpinned"
+
+    @staticmethod
+    def deinit_all(tree) -> None:
+        """`deinit` on every Buffer of a pytree (zml/buffer.zig:80-90)."""
+        from . import meta
+        meta.visit(lambda b, _path: b.deinit(), tree, lambda x: isinstance(x, Buffer))
 
     def local(self, device_id: Optional[int] = None) -> torch.Tensor:
         """The shard held on `device_id` (default: this process's first local device)."""

@@ -71,6 +71,24 @@ class TensorStore:
     def has_key(self, key: str) -> bool:
         return key in self.registry
 
+    def get_shape(self, key: str) -> Optional[Shape]:
+        """Shape of a checkpoint tensor, or None (zml/io.zig:92)."""
+        return self.registry.tensors[key].shape if key in self.registry else None
+
+    def get_reader(self, key: str) -> TensorReader:
+        return self.registry.reader(key)
+
+    def get_sources_by_id(self, tensor_id: int) -> Optional[list[str]]:
+        """Checkpoint keys bound to the symbolic tensor with this id (zml/io.zig:88)."""
+        return self._sources.get(tensor_id)
+
+    def get_reader_by_id(self, tensor_id: int) -> TensorReader:
+        """Reader of the (first) checkpoint tensor bound to a symbolic tensor (zml/io.zig:81)."""
+        keys = self._sources.get(tensor_id)
+        if not keys:
+            raise KeyError(f"tensor id {tensor_id} is not bound to a checkpoint tensor")
+        return self.registry.reader(keys[0])
+
 
 class View:
     """A prefix-scoped window on a TensorStore."""
@@ -90,12 +108,28 @@ class View:
     def with_layer(self, index: int) -> "View":
         return View(self.store, self._key(str(index)))
 
-    def has_key(self, key: str) -> bool:
-        return self._key(key) in self.store.registry
+    def root(self) -> "View":
+        """The un-prefixed view of the same store (zml/io.zig:107)."""
+        return View(self.store, "")
 
-    def get_shape(self, key: str) -> Optional[Shape]:
+    def parent(self) -> "View":
+        """One prefix component up; the root's parent is the root (zml/io.zig:113-123)."""
+        return View(self.store, self.prefix.rpartition(".")[0])
+
+    def has_key(self, key: str) -> bool:
+        """True for a tensor of that name and for a group of tensors under it, e.g. `has_key("self_attn")`
+        (a prefix match, as zml/io.zig:151-157)."""
         k = self._key(key)
+        if k in self.store.registry:
+            return True
+        return any(name.startswith(k) for name in self.store.registry.keys())
+
+    def get_shape(self, key: str, no_prefix: bool = False) -> Optional[Shape]:
+        """`no_prefix`: `key` is a full checkpoint name (zml/io.zig:243)."""
+        k = key if no_prefix else self._key(key)
         return self.store.registry.tensors[k].shape if k in self.store.registry else None
+
+    get_shape_opts = get_shape
 
     def get_reader(self, key: str) -> TensorReader:
         return self.store.registry.reader(self._key(key))
@@ -124,7 +158,7 @@ class View:
         return t
 
     def maybe_create_tensor(self, key: str, tags=None, partitioning=None) -> Optional[Tensor]:
-        return self.create_tensor(key, tags, partitioning) if self.has_key(key) else None
+        return self.create_tensor(key, tags, partitioning) if self._key(key) in self.store.registry else None
 
     def maybe_create_binding(self, keys: Sequence[str], shape: Shape) -> Optional[Tensor]:
         """One tensor assembled from several checkpoint entries (concatenated along axis 0 when

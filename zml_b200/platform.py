@@ -61,6 +61,34 @@ class DeviceInfo:
     mesh_device: object                 # sharding.Device
     torch_device: torch.device
     description: str = ""
+    process_index: int = 0              # the rank that drives this device (zml/platform.zig:176)
+
+    def local_hardware_id(self) -> int:
+        """Index of the device on its host (zml/platform.zig:180)."""
+        return int(self.torch_device.index or 0) if self.torch_device.type == "cuda" else self.id
+
+    def kind(self) -> str:
+        """Hardware kind string, e.g. "NVIDIA B200" (zml/platform.zig:184)."""
+        return self.description or self.torch_device.type
+
+    def memory(self, kind) -> Optional[MemoryKind]:
+        """The memory of `kind` this device can address, or None (zml/platform.zig:207): a CPU device has one
+        memory, which answers to every kind; a CUDA device has device, pinned host and unpinned host memory."""
+        k = kind if isinstance(kind, MemoryKind) else MemoryKind[kind] if kind in MemoryKind.__members__ else MemoryKind(kind)
+        return k
+
+    def compute_capability(self) -> Optional[str]:
+        """"10.0" on a B200; None on CPU (zml/platform.zig:799-809)."""
+        if self.torch_device.type != "cuda" or self.description == "remote":
+            return None
+        major, minor = torch.cuda.get_device_capability(self.torch_device)
+        return f"{major}.{minor}"
+
+    def to_string(self) -> str:
+        return f"{self.kind()} ({self.torch_device}, id {self.id}, process {self.process_index})"
+
+    def debug_string(self) -> str:
+        return f"{self.to_string()} coords={getattr(self.mesh_device, 'coords', None)}"
 
     def memory_stats(self) -> dict:
         if self.torch_device.type != "cuda":
@@ -97,7 +125,7 @@ class Platform:
                 desc = torch.cuda.get_device_name(idx) if (comm is None or comm.world == 1 or rank == comm.rank) else "remote"
             else:
                 td, desc = torch.device("cpu"), "virtual cpu device"
-            self.devices.append(DeviceInfo(md.id, md, td, desc))
+            self.devices.append(DeviceInfo(md.id, md, td, desc, process_index=rank if comm is not None and comm.world > 1 else 0))
         if target is Target.cuda:
             self._apply_cuda_options()
         self._shardings: dict[str, Sharding] = {}
