@@ -109,3 +109,70 @@ def test_image_resizes_follow_the_reference_sampling_rules():
     out = image.resize_bicubic(img, {"a": 20})
     assert out.shape().dims == (20, 10) and out.data.dtype == torch.uint8
     assert image.resize_bilinear(img, {"a": 20, "b": 5}, original_len=torch.tensor([8.0, 10.0])).shape().dims == (20, 5)
+
+
+def test_slice_strides_runs_and_pretty_print():
+    from zml_b200 import Slice
+    s = Slice.from_numpy(np.arange(60, dtype=np.float32).reshape(3, 20))
+    assert s.element_strides() == (20, 1)
+    assert [r.shape for r in s.contiguous_runs()] == [(60,)]
+    sub = s.sub_slice(1, 2, 5)
+    runs = [r.tolist() for r in sub.contiguous_runs()]
+    assert sub.element_strides() == (20, 1) and runs[1] == [22.0, 23.0, 24.0, 25.0, 26.0] and len(runs) == 3
+    text = s.pretty_print(num_rows=2)
+    assert text.splitlines()[0] == "{" and text.splitlines()[1] == "  {0,1,...,18,19}," and text.splitlines()[-1] == "}"
+    tall = Slice.from_numpy(np.arange(20, dtype=np.int32).reshape(10, 2)).pretty_print(num_rows=2).splitlines()
+    assert tall == ["{", "  {0,1},", "  {2,3},", "  ...", "  {16,17},", "  {18,19},", "}"]
+    bf = Slice.init(Shape((3,), "bf16"), torch.tensor([1.5, -2.0, 3.0]).bfloat16().view(torch.int16).numpy().view(np.uint8))
+    assert bf.pretty_print() == "{1.5,-2,3}"
+    assert Slice(Shape((2,), "f8e4m3fn"), np.array([0x38, 0x40], dtype=np.uint8)).pretty_print() == "{1,2}"
+    assert Slice.from_numpy(np.array(7, dtype=np.int32)).pretty_print() == "7"
+
+
+def test_testing_helpers_compare_like_the_reference():
+    from zml_b200 import testing
+    assert testing.approx_eq(1.0, 1.009, 1e-2) and not testing.approx_eq(1.0, 1.02, 1e-2)
+    assert testing.approx_eq(0.0, 0.004, 1e-2) and not testing.approx_eq(0.0, 0.006, 1e-2)      # absolute: tolerance / 2
+    l = torch.tensor([1.0, 2.0, 3.0, 100.0])
+    r = torch.tensor([1.0, 2.5, 3.0, 100.5])
+    rep = testing.compare_slices(l, r)
+    assert rep.close_fraction == 0.75 and rep.max_absolute_error == 0.5 and not rep.nan_or_inf
+    assert abs(rep.mean_absolute_error - 0.25) < 1e-9 and abs(rep.rmse - (0.5 / 4) ** 0.5) < 1e-6
+    assert rep.p50_absolute_error == 0.5 and rep.p999_absolute_error == 0.5       # sorted errors [0, 0, .5, .5], index round(3 q)
+    assert not rep.ok(testing.CompareOpts()) and rep.ok(testing.CompareOpts(minimum_close_fraction=0.7))
+    assert testing.compare_slices(l, l, testing.CompareOpts.exact_match()).ok(testing.CompareOpts.exact_match())
+    assert testing.compare_slices(torch.tensor([float("nan")]), torch.tensor([0.0])).nan_or_inf
+    # Buffers, Slices and tagged tensors are accepted directly
+    pl = testing.env()
+    assert pl is testing.env() and pl.sharding("model") is not None
+    buf = Buffer.from_tensor(pl, l)
+    testing.expect_close(buf, Tensor.from_torch(l))
+    testing.expect_close(buf.to_slice(), l)
+    exe = pl.compile(lambda x: x.add(x), [Tensor.from_shape(Shape((4,), "f32"))])
+    out = testing.auto_call(exe, buf)
+    testing.expect_close(out[0] if isinstance(out, (list, tuple)) else out, 2 * l)
+
+
+def test_meta_first_zip_collect():
+    from zml_b200 import meta
+    isnum = lambda x: isinstance(x, (int, float)) and not isinstance(x, bool)
+    a, b = {"a": 1, "b": [2, 3], "name": "x"}, {"a": 4, "b": [5, 6], "name": "y"}
+    assert meta.zip_trees(sum, [a, b], isnum) == {"a": 5, "b": [7, 9], "name": "x"}          # the reference's own example
+    assert meta.first(a, isnum) == 1 and meta.first({"n": "x"}, isnum) is None
+    assert meta.collect_map(lambda v: v * 2, a, isnum) == [2, 4, 6]
+    seen = []
+    meta.for_each_visit(a, isnum, lambda i, v, k: seen.append((i, v * k)), 10)
+    assert seen == [(0, 10), (1, 20), (2, 30)]
+    with pytest.raises(ValueError):
+        meta.zip_trees(sum, [a, {"a": 1}], isnum)
+
+
+def test_float_format_predicates():
+    from zml_b200 import floats
+    f = floats.FORMATS["f8e4m3fn"]
+    assert f.is_nan([0x7F, 0x38]).tolist() == [True, False] and not f.is_inf([0x7F]).any()
+    assert f.to_f32(f.neg([0x38])).tolist() == [-1.0]
+    g = floats.FORMATS["f8e5m2"]
+    assert g.is_inf([0x7C, 0xFC, 0x3C]).tolist() == [True, True, False] and g.is_nan([0x7D]).all()
+    h = floats.FORMATS["f8e4m3fnuz"]
+    assert h.neg([0x00, 0x80, 0x40]).tolist() == [0x00, 0x80, 0xC0] and h.is_nan([0x80]).all()

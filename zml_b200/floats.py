@@ -56,6 +56,21 @@ class FloatFormat:
             val = np.where(c == (1 << (self.bits - 1)), np.nan, val)
         return val.astype(np.float32)
 
+    # ------------------------------------------------------------------ predicates on codes (zml/floats.zig:118-230)
+    def is_nan(self, codes) -> np.ndarray:
+        return np.isnan(self.to_f32(codes))
+
+    def is_inf(self, codes) -> np.ndarray:
+        return np.isinf(self.to_f32(codes))
+
+    def neg(self, codes) -> np.ndarray:
+        """Flips the sign bit (the fnuz formats have no negative zero: their code 0x80 is NaN, and zero stays zero)."""
+        c = np.asarray(codes).astype(self.code_dtype)
+        flipped = c ^ self.code_dtype(1 << (self.bits - 1))
+        if self.flavour == "fnuz":
+            return np.where((c == 0) | (c == (1 << (self.bits - 1))), c, flipped).astype(self.code_dtype)
+        return flipped.astype(self.code_dtype)
+
     # ------------------------------------------------------------------ limits
     @property
     def max_finite(self) -> float:

@@ -129,3 +129,36 @@ def bufferize(model, to_buffer: Callable[[Any], Any]):
     from .tensor import Tensor
     out = map_tree(to_buffer, model, lambda x: isinstance(x, Tensor), drop_others=True)
     return None if out is _DROP else out
+
+
+def first(tree, is_leaf):
+    """The first leaf in visiting order, or None (zml/meta.zig:744-752)."""
+    for leaf in collect(tree, is_leaf):
+        return leaf
+    return None
+
+
+def collect_map(fn: Callable[[Any], Any], tree, is_leaf) -> list:
+    """fn(leaf) for every leaf, in visiting order (`collectAlloc` / `collectBuf`, zml/meta.zig:824-880)."""
+    return [fn(leaf) for leaf in collect(tree, is_leaf)]
+
+
+def zip_trees(fn: Callable[[list], Any], trees, is_leaf):
+    """Combines several trees of one structure into one: every leaf position receives fn([leaf of tree 0, leaf of
+    tree 1, ...]); non-leaf fields come from the first tree (`zip`, zml/meta.zig:759-820 - e.g. summing the
+    per-device copies of a struct of tensors)."""
+    trees = list(trees)
+    if not trees:
+        raise ValueError("zip_trees needs at least one tree")
+    columns = [collect(t, is_leaf) for t in trees]
+    n = len(columns[0])
+    if any(len(c) != n for c in columns):
+        raise ValueError(f"trees differ in their number of leaves: {[len(c) for c in columns]}")
+    it = iter(range(n))
+    return map_tree(lambda _leaf: fn([c[i] for c in columns]) if (i := next(it)) is not None else None, trees[0], is_leaf)
+
+
+def for_each_visit(tree, is_leaf, fn: Callable[..., None], *args) -> None:
+    """fn(index, leaf, *args) for every leaf (zml/meta.zig:946-962)."""
+    for i, leaf in enumerate(collect(tree, is_leaf)):
+        fn(i, leaf, *args)

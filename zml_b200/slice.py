@@ -66,6 +66,81 @@ class Slice:
             else np.frombuffer(self.bytes.tobytes()[self.offset_bytes:], dtype=npdt),
             shape=self.shape.dims, strides=self.byte_strides, writeable=self.mutable)
 
+    const_items = items
+
+    def element_strides(self) -> tuple:
+        """Strides in elements rather than bytes (zml/slice.zig:103-111)."""
+        sz = max(self.shape.dtype.size_of(), 1)
+        if any(b % sz for b in self.byte_strides):
+            raise ValueError(f"byte strides {self.byte_strides} are not multiples of the element size {sz}")
+        return tuple(b // sz for b in self.byte_strides)
+
+    def contiguous_runs(self):
+        """Yields the longest contiguous 1-d runs of items in row-major order (zml/slice.zig:157-245): the inner axes
+        whose strides are those of a dense array form one run, the outer axes are walked."""
+        items = self.items()
+        dense = self.shape.compute_byte_strides()
+        a = len(self.byte_strides)
+        while a > 0 and self.byte_strides[a - 1] == dense[a - 1]:
+            a -= 1
+        outer = self.shape.dims[:a]
+        if not outer:
+            yield items.reshape(-1)
+            return
+        for idx in np.ndindex(*outer):
+            yield items[idx].reshape(-1)
+
+    def _to_f32_items(self) -> np.ndarray:
+        """Items as numbers numpy can print: bf16 and the small floats are decoded to f32."""
+        dt = self.shape.dtype
+        if dt is DataType.bf16:
+            raw = np.ascontiguousarray(self.items()).view(np.uint16).astype(np.uint32) << 16
+            return raw.view(np.float32)
+        if dt.is_float() and dt.size_of() == 1:
+            from . import floats
+            fmt = floats.FORMATS.get(dt.value)
+            if fmt is not None:
+                return fmt.to_f32(np.ascontiguousarray(self.items()).view(np.uint8))
+        return self.items()
+
+    def pretty_print(self, num_rows: int = 4, precision: int = 4) -> str:
+        """The reference's layout (zml/slice.zig:249-334): one line per innermost row, nested braces per outer axis,
+        the first and last `num_rows` entries of every axis with `...` between them."""
+        arr = self._to_f32_items()
+
+        def fmt(v) -> str:
+            if isinstance(v, (bool, np.bool_)):
+                return "true" if v else "false"
+            if isinstance(v, (np.integer, int)):
+                return str(int(v))
+            if isinstance(v, (complex, np.complexfloating)):
+                return f"{v.real:.{precision}g}{v.imag:+.{precision}g}i"
+            return f"{float(v):.{precision}g}"
+
+        def line(row) -> str:
+            n = row.shape[0]
+            if n > 2 * num_rows:
+                parts = [fmt(v) for v in row[:num_rows]] + ["..."] + [fmt(v) for v in row[n - num_rows:]]
+            else:
+                parts = [fmt(v) for v in row]
+            return "{" + ",".join(parts) + "}"
+
+        def rec(a, indent: int) -> str:
+            pad = " " * indent
+            if a.ndim == 0:
+                return fmt(a[()])
+            if a.ndim == 1:
+                return pad + line(a)
+            n = a.shape[0]
+            rows = list(range(n)) if n <= 2 * num_rows else list(range(num_rows)) + [None] + list(range(n - num_rows, n))
+            out = [pad + "{"]
+            for r in rows:
+                out.append(" " * (indent + 2) + "..." if r is None else rec(a[r], indent + 2) + ",")
+            out.append(pad + "}")
+            return "\n".join(out)
+
+        return rec(np.asarray(arr), 0)
+
     def sub_slice(self, axis, start: int, size: int) -> "Slice":
         a = self.shape.axis(axis)
         if start < 0 or start + size > self.shape.dims[a]:
