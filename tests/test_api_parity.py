@@ -176,3 +176,30 @@ def test_float_format_predicates():
     assert g.is_inf([0x7C, 0xFC, 0x3C]).tolist() == [True, True, False] and g.is_nan([0x7D]).all()
     h = floats.FORMATS["f8e4m3fnuz"]
     assert h.neg([0x00, 0x80, 0x40]).tolist() == [0x00, 0x80, 0xC0] and h.is_nan([0x80]).all()
+
+
+def test_composite_typed_custom_call_and_scaled_dot():
+    from zml_b200.ops import structured as st
+    x = Tensor.from_torch(torch.arange(6.).reshape(2, 3), ["b", "d"])
+    decomposed = st.composite("test.double", [x], [x.shape()], lambda ins, ctx: [ins[0].add(ins[0])], None)
+    assert torch.equal(decomposed[0].data, 2 * x.data)
+    st.register_composite("test.double", lambda ins, outs, ctx, attrs: [ins[0].scale(2.0 + attrs["version"])])
+    try:
+        fused = st.composite("test.double", [x], [x.shape()], lambda ins, ctx: [ins[0].add(ins[0])], None, version=1)
+        assert torch.equal(fused[0].data, 3 * x.data)
+        with pytest.raises(ValueError):
+            st.composite("test.double", [x], [Shape((3, 3), "f32")], lambda ins, ctx: [ins[0]], None)
+    finally:
+        st.register_composite("test.double", None)
+    st.register_custom_call("test.split", lambda ins, outs, meta: {"hi": ins["x"].scale(meta["k"]), "lo": ins["x"].scale(-meta["k"])})
+    res = st.typed_custom_call("test.split", None, {"x": x}, {"lo": x.shape(), "hi": x.shape()}, {"k": 2.0})
+    assert list(res) == ["lo", "hi"] and torch.equal(res["hi"].data, 2 * x.data) and torch.equal(res["lo"].data, -2 * x.data)
+    with pytest.raises(ValueError):
+        st.typed_custom_call("test.split", None, {"x": x}, {"lo": x.shape(), "mid": x.shape()}, {"k": 1.0})
+    a = Tensor.from_torch(torch.tensor([[1.0, 2.0], [3.0, 4.0]]), ["m", "k"])
+    b = Tensor.from_torch(torch.tensor([[1.0, 0.0], [0.0, 1.0], [1.0, 1.0]]), ["n", "k"])
+    sa = Tensor.from_torch(torch.tensor([2.0, 0.5]), ["m"])
+    sb = Tensor.from_torch(torch.tensor([1.0, 2.0, 4.0]), ["n"])
+    out = st.scaled_dot(a, b, sa, sb, "k")
+    want = (a.data * sa.data[:, None]) @ (b.data * sb.data[:, None]).t()
+    assert out.shape().tags == ("m", "n") and out.data.dtype == torch.bfloat16 and torch.equal(out.data.float(), want)

@@ -375,5 +375,6 @@ def paged_prefill(q, k_cache, v_cache, block_table, seq_lens, q_start, scale: fl
 
 # structured ops (collectives, reductions, control flow, custom calls) live in ops.structured
 from .structured import (CustomCallOptions, ReduceWindowOpts, all_reduce, custom_call, gather, if2, if_,  # noqa: E402,F401
-                         manual_computation, partition_id, print_, reduce, reduce_window, register_custom_call,
-                         scatter, sort, while_)
+                         composite, manual_computation, partition_id, print_, reduce, reduce_window,
+                         register_composite, register_custom_call, scaled_dot, scatter, sort, typed_custom_call,
+                         while_)

@@ -278,3 +278,64 @@ def print_(t: Tensor, label: str = "") -> Tensor:
     """Debug print of a device tensor (`zml$print` host callback, zml/platform.zig:847-898)."""
     print(f"{label}{t.shape()} {t.to_torch().detach().cpu()}")
     return t
+
+
+def typed_custom_call(target_name: str, opts: Optional[CustomCallOptions], input, output: Mapping[str, Shape],
+                      attributes: Optional[Mapping] = None) -> dict:
+    """Custom call with named operands and results (zml/ops.zig:2452-2560): `input` is a dict / dataclass of
+    Tensors, `output` maps result names to Shapes, `attributes` are passed to the target as keyword-like metadata.
+    Returns {name: Tensor}.  The target may return a dict (matched by name) or a sequence (matched by position)."""
+    names = list(output)
+    res = custom_call(target_name, input, [output[n] for n in names], dict(attributes or {}), opts)
+    if isinstance(res, Mapping):
+        missing = [n for n in names if n not in res]
+        if missing:
+            raise ValueError(f"custom call {target_name!r} did not return {missing}")
+        out = {n: res[n] for n in names}
+    else:
+        res = list(res) if isinstance(res, (list, tuple)) else [res]
+        if len(res) != len(names):
+            raise ValueError(f"custom call {target_name!r} returned {len(res)} results, {len(names)} declared")
+        out = dict(zip(names, res))
+    for n, t in out.items():
+        if tuple(t.dims()) != tuple(output[n].dims):
+            raise ValueError(f"custom call {target_name!r}: result {n!r} is {t.shape()}, declared {output[n]}")
+    return out
+
+
+# ---------------------------------------------------------------------------- composites
+_COMPOSITES: dict[str, Callable] = {}
+
+
+def register_composite(name: str, fn: Optional[Callable]) -> None:
+    """Installs (or, with None, removes) a fused implementation for the composite `name`: it is called instead of
+    the decomposition with (inputs, output shapes, context, attributes)."""
+    if fn is None:
+        _COMPOSITES.pop(name, None)
+    else:
+        _COMPOSITES[name] = fn
+
+
+def composite(name: str, inputs: Sequence[Tensor], outputs: Sequence[Shape], decomposition: Callable, context=None,
+              version: int = 0, attributes: Optional[Mapping] = None) -> list:
+    """A named op given by its decomposition into ordinary tensor ops (zml/ops.zig:1751-1837): a back-end that knows
+    `name` substitutes its own kernel, everyone else runs `decomposition(inputs, context)`.  Here the substitution
+    table is `register_composite`; results are checked against the declared shapes either way."""
+    impl = _COMPOSITES.get(name)
+    res = impl(list(inputs), list(outputs), context, dict(attributes or {}, version=version)) if impl else decomposition(list(inputs), context)
+    res = list(res) if isinstance(res, (list, tuple)) else [res]
+    if len(res) != len(outputs):
+        raise ValueError(f"composite {name!r} returned {len(res)} tensors, {len(outputs)} declared")
+    for t, s in zip(res, outputs):
+        if tuple(t.dims()) != tuple(s.dims):
+            raise ValueError(f"composite {name!r} returned {t.shape()}, declared {s}")
+    return res
+
+
+def scaled_dot(lhs: Tensor, rhs: Tensor, lhs_scale: Tensor, rhs_scale: Tensor, contracting) -> Tensor:
+    """(lhs * lhs_scale) . (rhs * rhs_scale) in bf16 (zml/ops.zig:2673-2678); the scales broadcast against their
+    operands by tag.  `contracting`: the axis tag(s) to contract, as for `Tensor.dot`."""
+    def scaled(x: Tensor, s: Tensor) -> Tensor:
+        s = s.convert("bf16")
+        return x.convert("bf16").mul(s.broad(x.shape()) if s.rank() != x.rank() or tuple(s.dims()) != tuple(x.dims()) else s)
+    return scaled(lhs, lhs_scale).dot(scaled(rhs, rhs_scale), contracting).convert("bf16")
