@@ -48,6 +48,12 @@ def test_streaming_decoder_holds_incomplete_utf8(tok_json):
         out = "".join(dec.next(i) for i in tok.encode(text))
         assert out == text
         assert "�" not in out
+        assert dec.finalize() == ""
+        # generation that stops inside a multi-byte character: the held-back bytes come out of finalize()
+        ids = tok.encode("🙂")
+        if len(ids) > 1:
+            shown = "".join(dec.feed_one(i) for i in ids[:-1])
+            assert shown == "" and dec.finalize() != "" and dec.finalize() == ""
 
 
 def test_cli_checker(tok_json, capsys):
@@ -94,3 +100,49 @@ def test_unigram_tokenizer_matches_hf():
         assert got == want, (text, got, want)
         assert ours.decode(got) == t.decode(want, skip_special_tokens=False)
     assert ours.vocab_size() == t.get_vocab_size() and ours.token_id("<s>") == t.token_to_id("<s>")
+
+
+def test_normalizer_matches_the_reference_vectors():
+    """The five cases of zml/tokenizer/homemade.zig `test Normalizer`."""
+    from zml_b200.tokenizer.scored import Normalizer, SENTENCEPIECE_SPACE
+    n = Normalizer(True, True, False, False, False)
+    text, origin = n.normalize_with_mapping("Hellŏ  world!")
+    assert text == " Hellŏ world!"
+    assert origin == [0, 0, 1, 2, 3, 4, 4, 6, 8, 9, 10, 11, 12, 13, 14]
+    assert Normalizer(True, True, True, False, False).normalize("Hello  world!") == " Hello world! "
+    assert Normalizer(False, True, False, False, False, SENTENCEPIECE_SPACE).normalize("Hello  world!") == "▁Hello▁▁world!"
+    assert Normalizer(True, False, True, True, False).normalize("Hello  world!") == "hello world! "
+    assert Normalizer(True, False, True, False, True).normalize("Hello  world!") == "Hello world ! "
+    assert Normalizer.well_known("sentencepiece").normalize("  a  b ") == "▁a▁b"
+    assert Normalizer.well_known("llama3").normalize("   ") == ""
+
+
+def test_scored_tokenizer_from_a_tinyllama_file(tmp_path):
+    """A llama2.c tokenizer.bin: best-scoring merges first, byte pieces for characters outside the vocabulary."""
+    import struct
+    from zml_b200.tokenizer.scored import ScoredTokenizer
+    pieces = [(b"<unk>", 0.0), (b"<s>", 0.0), (b"</s>", 0.0)] + [(b"<0x%02X>" % b, 0.0) for b in range(256)]
+    base = len(pieces)
+    words = [("▁", -1.0), ("h", -2.0), ("e", -2.0), ("l", -2.0), ("o", -2.0), ("w", -2.0), ("r", -2.0), ("d", -2.0),
+             ("he", -3.0), ("ll", -4.0), ("hell", -5.0), ("hello", -0.5), ("▁hello", -0.2), ("wor", -6.0), ("or", -3.5),
+             ("ld", -3.6), ("world", -0.6), ("▁world", -0.3), ("lo", -9.0)]
+    pieces += [(w.encode(), s) for w, s in words]
+    blob = struct.pack("<I", 8) + b"".join(struct.pack("<fI", s, len(p)) + p for p, s in pieces)
+    path = tmp_path / "tokenizer.bin"
+    path.write_bytes(blob)
+    tok = Tokenizer.from_file(str(path))
+    assert tok.backend == "scored" and tok.vocab_size() == len(pieces)
+    ids = tok.encode("hello  world")
+    assert ids == [base + 12, base + 17] and tok.decode(ids) == "hello world"
+    # "held": of the pairs he (-3) and ld (-3.6) the better one merges first, then the other; "held" is no piece
+    assert [tok.impl.tokens[i] for i in tok.encode("held")] == ["▁".encode(), b"he", b"ld"]
+    # a character outside the vocabulary falls back to its bytes and decodes back
+    ids = tok.encode("hé")
+    assert [tok.impl.tokens[i] for i in ids] == ["▁".encode(), b"h", b"\xc3", b"\xa9"] and tok.decode(ids) == "hé"
+    st = ScoredTokenizer.from_tinyllama_file(str(path), vocab_size=1 << 20)
+    assert st.encode("hello", add_bos=True, add_eos=True, pad_to=5) == [1, base + 12, 2, st.special.pad, st.special.pad]
+    assert st.decode([1, base + 12, base + 17, 2], sep="|") == "| hello| world||"       # only the very first id drops its space
+    assert st.decode([base + 12, base + 17], sep="|") == "hello| world|"
+    assert st.lookup_piece(10 ** 6) == b"<oob>" and st.lookup_piece(0) == b"<unk>"
+    dec = tok.decoder()
+    assert "".join(dec.feed_one(i) for i in tok.encode("hello world")) + dec.finalize() == "hello world"

@@ -75,6 +75,18 @@ class Decoder:
         self._printed = len(text)
         return out
 
+    feed_one = next                     # zml/tokenizer/tokenizer.zig:89
+
+    def finalize(self) -> str:
+        """What is still held back when generation ends (an incomplete UTF-8 sequence shows as U+FFFD), and resets
+        the decoder (zml/tokenizer/tokenizer.zig:97)."""
+        if self.tok.backend == "homemade":
+            out = self._pending.decode("utf-8", errors="replace")
+        else:
+            out = self.tok.decode(self._ids)[self._printed:] if self._ids else ""
+        self.reset()
+        return out
+
 
 class Tokenizer:
     def __init__(self, backend: str, impl):
@@ -95,8 +107,16 @@ class Tokenizer:
         if path.endswith((".model", ".pb")):
             import sentencepiece as spm
             return Tokenizer("sentencepiece", spm.SentencePieceProcessor(model_file=path))
+        if path.endswith(".bin"):
+            return Tokenizer.from_tinyllama_file(path)
         with open(path, "rb") as f:
             return Tokenizer.from_bytes(f.read(), backend)
+
+    @staticmethod
+    def from_tinyllama_file(path: str, vocab_size: int = 1 << 20) -> "Tokenizer":
+        """A llama2.c `tokenizer.bin` (zml/tokenizer/homemade.zig:1206): scored pieces merged best-first."""
+        from .scored import ScoredTokenizer
+        return Tokenizer("scored", ScoredTokenizer.from_tinyllama_file(path, vocab_size))
 
     @staticmethod
     def from_bytes(data: bytes, backend: Optional[str] = None) -> "Tokenizer":
