@@ -132,6 +132,9 @@ def main(argv=None) -> int:
     logging.basicConfig(level=logging.INFO, format="%(levelname)s(%(name)s): %(message)s")
     args = flags.parse(argv, Args)
     comm = Comm.from_env()
+    if comm.rank == 0 and sys.stderr.isatty():
+        from zml_b200 import logo
+        logo.write(sys.stderr)
     device = torch.device("cpu") if args.cpu or not torch.cuda.is_available() else comm.device
     dtype = torch.bfloat16 if device.type == "cuda" else torch.float32
     model, tok = hub.load_model(args.model, comm, device, dtype)

@@ -203,3 +203,25 @@ def test_composite_typed_custom_call_and_scaled_dot():
     out = st.scaled_dot(a, b, sa, sb, "k")
     want = (a.data * sa.data[:, None]) @ (b.data * sb.data[:, None]).t()
     assert out.shape().tags == ("m", "n") and out.data.dtype == torch.bfloat16 and torch.equal(out.data.float(), want)
+
+
+def test_logo_rows_and_colour_detection():
+    import io
+    from zml_b200 import logo
+    plain = io.StringIO()
+    logo.write(plain, logo.NO_COLOR)
+    rows = plain.getvalue().splitlines()
+    assert len(rows) == 6 and "\x1b" not in plain.getvalue() and all(r == r.rstrip() for r in rows)
+    colored = io.StringIO()
+    logo.write(colored, logo.TRUE_COLOR)
+    assert "\x1b[38;2;0;255;255m" in colored.getvalue() and colored.getvalue().count("\n") == 6
+    import re
+    assert re.sub(r"\x1b\[[0-9;]*m", "", colored.getvalue()) == plain.getvalue()
+    assert "\x1b[38;5;51m" in (lambda b: (logo.write(b, logo.ANSI_256), b.getvalue())[1])(io.StringIO())
+    pipe = io.StringIO()
+    assert logo.detect_color_support(pipe, {}) == logo.NO_COLOR
+    assert logo.detect_color_support(pipe, {"CLICOLOR_FORCE": "1", "COLORTERM": "truecolor"}) == logo.TRUE_COLOR
+    assert logo.detect_color_support(pipe, {"CLICOLOR_FORCE": "1", "NO_COLOR": "1"}) == logo.NO_COLOR
+    assert logo.detect_color_support(pipe, {"CLICOLOR_FORCE": "1", "TERM": "xterm-256color"}) == logo.ANSI_256
+    with pytest.raises(ValueError):
+        logo.write(io.StringIO(), logo.NO_COLOR, blocks=[("cyan", ["a"]), ("sky", ["a", "b"])])
