@@ -128,3 +128,27 @@ def test_gpu_box_mesh_and_llm_shardings():
     assert shardable_dim(model, 8, "model", 32) == ("sharded", 8, 1)
     assert shardable_dim(model, 4, "model", 32) == ("sharded", 8, 2)
     assert shardable_dim(model, 3, "model", 32) == ("replicated",)
+
+
+def test_mesh_accessors_shard_slice_and_pick_sharding():
+    """Small entry points of zml/Sharding.zig: axis info, shard views of host slices, sharding selection."""
+    import numpy as np
+    from zml_b200 import Shape, Slice
+    from zml_b200.sharding import LogicalMesh, PhysicalMesh, Sharding, pick_sharding
+    m = PhysicalMesh.gpu(4)
+    info = m.axis_info("link")
+    assert info["size"] == 4 and info["tag"] == "link" and m.axis_info("bus") is None
+    assert m.axis("bus") == 1 and m.axis("link") == 4 and m.axis_order() == ("link",)
+    assert m.is_shardable("link") and not m.is_shardable("bus") and m.count_devices() == 4
+    assert [m.linear_index_from_coords(d.coords) for d in m.devices] == [0, 1, 2, 3]
+    sh = Sharding("model", m, LogicalMesh.mesh({"model": "high_bandwidth"}))
+    shape = Shape((4, 8), "f32", ["a", "b"]).with_partitioning({"b": "model"})
+    host = Slice.from_numpy(np.arange(32, dtype=np.float32).reshape(4, 8), ["a", "b"])
+    pl = sh.placement(shape)
+    for d in m.devices:
+        sub = pl.shard_slice(d, host)
+        assert sub.shape.dims == (4, 2) and not sub.is_contiguous()
+        assert np.array_equal(sub.items(), pl.shard(host.items(), d))
+    assert pick_sharding([sh], shape) is sh
+    assert pick_sharding([sh], Shape((2,), "f32"), "explicit_axis_binding") is None
+    assert pick_sharding([sh], Shape((2,), "f32")) is sh

@@ -172,6 +172,33 @@ class PhysicalMesh:
     def num_devices(self) -> int:
         return len(self.devices)
 
+    count_devices = num_devices
+
+    def axis_info(self, tag: str) -> Optional[dict]:
+        """{tag, size, geometry} of a mesh axis, or None (zml/Sharding.zig:650-673)."""
+        if tag not in self.axis_tags:
+            return None
+        i = self.axis_tags.index(tag)
+        return {"tag": tag, "size": self.axis_sizes[i], "geometry": self.axis_geometry[i]}
+
+    def axis(self, tag: str) -> int:
+        """Size of a mesh axis; 1 for an axis the mesh does not have (zml/Sharding.zig:679-683)."""
+        return self.axis_size(tag) if tag in self.axis_tags else 1
+
+    def axis_order(self) -> tuple:
+        """Axis tags from the outermost tree level inwards (zml/Sharding.zig:685)."""
+        return tuple(self.axis_tags)
+
+    def is_shardable(self, tag: str) -> bool:
+        return tag in self.shardable_axes()
+
+    def linear_index_from_coords(self, coords: Sequence[int]) -> int:
+        """Row-major index of a device over the mesh axes (zml/Sharding.zig:630-648)."""
+        idx = 0
+        for size, c in zip(self.axis_sizes, coords):
+            idx = idx * size + int(c)
+        return idx
+
     def shardable_axes(self) -> tuple[str, ...]:
         """Axes usable for sharding, fastest first (what `Strategy.suggest` matches intents to)."""
         return {"tpu": ("link_x", "link_y", "link_z"), "neuron": ("link", "link_x", "link_y", "link_z"),
@@ -293,6 +320,14 @@ class Placement:
 
     def shard(self, array, device):
         return array[self.shard_index(device)]
+
+    def shard_slice(self, device, host_slice):
+        """The sub-`Slice` of a host slice that this device holds: a strided view, no copy (zml/Sharding.zig:1845)."""
+        out = host_slice
+        for ax, (start, size) in enumerate(self.slices(device)):
+            if size != out.shape.dims[ax]:
+                out = out.sub_slice(ax, start, size)
+        return out
 
     def byte_spans(self, device) -> list[tuple[int, int]]:
         """Contiguous (offset, length) byte ranges of the row-major global array that make up
@@ -495,6 +530,19 @@ class Partitioning:
     def local_shape(self, shape: Shape) -> Shape:
         s = self.select_sharding(shape)
         return s.sharded_shape(shape) if s else shape
+
+    local_shape_for_shape = local_shape         # zml/Sharding.zig:110
+
+
+def pick_sharding(shardings: Sequence[Sharding], shape: Shape, mode: str = "any_covering") -> Optional[Sharding]:
+    """The first sharding that covers every partitioned axis of `shape`; with mode `explicit_axis_binding` a shape
+    without a partitioned axis picks none (zml/Sharding.zig:206-225)."""
+    if mode == "explicit_axis_binding" and not shape.has_at_least_one_partitioned_axis():
+        return None
+    for s in shardings:
+        if s.covers(shape):
+            return s
+    return None
 
 
 def shardable_dim(sharding: Sharding, dim: int, logical_axis: str, must_divide: int):
