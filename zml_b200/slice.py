@@ -103,9 +103,10 @@ class Slice:
                 return fmt.to_f32(np.ascontiguousarray(self.items()).view(np.uint8))
         return self.items()
 
-    def pretty_print(self, num_rows: int = 4, precision: int = 4) -> str:
-        """The reference's layout (zml/slice.zig:249-334): one line per innermost row, nested braces per outer axis,
-        the first and last `num_rows` entries of every axis with `...` between them."""
+    def pretty_print(self, num_rows: int = 4, precision: int = 4, num_cols: int = 12) -> str:
+        """The reference's layout (zml/slice.zig:249-334): one line per innermost row - all of it up to `num_cols`
+        items, else the first and last num_cols / 2 around ` ..., ` - nested braces per outer axis, and of an outer
+        axis longer than 2 x num_rows only the first and last `num_rows` entries with `...` between them."""
         arr = self._to_f32_items()
 
         def fmt(v) -> str:
@@ -118,12 +119,8 @@ class Slice:
             return f"{float(v):.{precision}g}"
 
         def line(row) -> str:
-            n = row.shape[0]
-            if n > 2 * num_rows:
-                parts = [fmt(v) for v in row[:num_rows]] + ["..."] + [fmt(v) for v in row[n - num_rows:]]
-            else:
-                parts = [fmt(v) for v in row]
-            return "{" + ",".join(parts) + "}"
+            from .stdx import format_slice
+            return format_slice(row, fmt, num_cols)
 
         def rec(a, indent: int) -> str:
             pad = " " * indent
