@@ -132,8 +132,273 @@ class HfBackend(HttpBackend):
         repo, rev, file = self.split(path)
         return f"{self.endpoint}/{repo}/resolve/{rev}/{file}"
 
+    def tree(self, path: str) -> list[dict]:
+        """Entries {type: file | directory, path, size} of a directory of the repository (the hub's tree API, which
+        vfs/hf.zig uses to enumerate the shards of a checkpoint)."""
+        import json
+        repo, rev, sub = self.split(path)
+        out, url = [], f"{self.endpoint}/api/models/{repo}/tree/{rev}/{sub}".rstrip("/")
+        while url:
+            with urllib.request.urlopen(urllib.request.Request(url, headers=self.headers), timeout=self.timeout) as r:
+                out.extend(json.loads(r.read()))
+                link = r.headers.get("Link", "")
+            url = None
+            for part in link.split(","):                         # pagination: Link: <url>; rel="next"
+                if 'rel="next"' in part and "<" in part:
+                    url = part[part.index("<") + 1:part.index(">")]
+        return out
+
+    def list(self, path):
+        _, _, sub = self.split(path)
+        base = sub.rstrip("/") + "/" if sub.strip("/") else ""
+        return sorted(e["path"][len(base):] + ("/" if e.get("type") == "directory" else "") for e in self.tree(path))
+
+    def stat(self, path):
+        _, _, sub = self.split(path)
+        if sub and not sub.endswith("/"):
+            try:
+                return super().stat(path)
+            except urllib.error.HTTPError as e:
+                if e.code != 404:
+                    raise
+        entries = self.tree(path)
+        return Stat(sum(int(e.get("size", 0)) for e in entries), "directory")
+
+
+class AwsSigV4:
+    """AWS Signature Version 4 for one service / region (vfs/s3.zig:10-140): `headers(method, url, extra)` returns
+    the headers to send - host-independent ones plus `Authorization` - or only the extras without credentials."""
+    ALGORITHM = "AWS4-HMAC-SHA256"
+    UNSIGNED_PAYLOAD = "UNSIGNED-PAYLOAD"
+
+    def __init__(self, access_key: Optional[str], secret_key: Optional[str], region: str, service: str = "s3",
+                 session_token: Optional[str] = None):
+        self.access_key, self.secret_key, self.region, self.service = access_key, secret_key, region, service
+        self.session_token = session_token
+
+    @staticmethod
+    def _quote(s: str, safe: str = "-_.~") -> str:
+        return urllib.parse.quote(s, safe=safe)
+
+    def headers(self, method: str, url: str, extra: Optional[dict] = None, timestamp: Optional[str] = None,
+                payload_hash: Optional[str] = None) -> dict:
+        import hashlib
+        import hmac
+        import time as _time
+        extra = dict(extra or {})
+        if not self.access_key or not self.secret_key:
+            return extra
+        u = urllib.parse.urlsplit(url)
+        timestamp = timestamp or _time.strftime("%Y%m%dT%H%M%SZ", _time.gmtime())
+        date = timestamp[:8]
+        payload_hash = payload_hash or self.UNSIGNED_PAYLOAD
+        signed = {"host": u.netloc, "x-amz-content-sha256": payload_hash, "x-amz-date": timestamp}
+        if self.session_token:
+            signed["x-amz-security-token"] = self.session_token
+        for k, v in extra.items():
+            signed[k.lower()] = str(v).strip()
+        names = sorted(signed)
+        query = sorted(urllib.parse.parse_qsl(u.query, keep_blank_values=True))
+        canonical_query = "&".join(f"{self._quote(k)}={self._quote(v)}" for k, v in query)
+        canonical_path = self._quote(urllib.parse.unquote(u.path) or "/", safe="/-_.~")
+        canonical = "\n".join([method, canonical_path, canonical_query,
+                               "".join(f"{n}:{signed[n]}\n" for n in names), ";".join(names), payload_hash])
+        scope = f"{date}/{self.region}/{self.service}/aws4_request"
+        to_sign = "\n".join([self.ALGORITHM, timestamp, scope, hashlib.sha256(canonical.encode()).hexdigest()])
+        key = ("AWS4" + self.secret_key).encode()
+        for part in (date, self.region, self.service, "aws4_request"):
+            key = hmac.new(key, part.encode(), hashlib.sha256).digest()
+        signature = hmac.new(key, to_sign.encode(), hashlib.sha256).hexdigest()
+        out = {k: v for k, v in signed.items() if k != "host"}
+        out.update(extra)
+        out["Authorization"] = (f"{self.ALGORITHM} Credential={self.access_key}/{scope},"
+                                f"SignedHeaders={';'.join(names)},Signature={signature}")
+        return out
+
+
+class S3Backend(HttpBackend):
+    """s3://bucket/key.  Credentials and placement come from the environment, as in vfs/s3.zig:383-420:
+    AWS_ACCESS_KEY_ID / AWS_SECRET_ACCESS_KEY (/ AWS_SESSION_TOKEN) - without them requests go unsigned -,
+    AWS_REGION or AWS_DEFAULT_REGION (us-east-1), AWS_ENDPOINT_URL or AWS_ENDPOINT_URL_S3 (path-style addressing,
+    for MinIO and friends; default: https://<bucket>.s3.<region>.amazonaws.com).  `list` is ListObjectsV2."""
+
+    def __init__(self, env: Optional[dict] = None, timeout: float = 60.0):
+        super().__init__(timeout=timeout)
+        env = os.environ if env is None else env
+        self.region = env.get("AWS_REGION") or env.get("AWS_DEFAULT_REGION") or "us-east-1"
+        self.endpoint = (env.get("AWS_ENDPOINT_URL") or env.get("AWS_ENDPOINT_URL_S3") or "").rstrip("/")
+        self.signer = AwsSigV4(env.get("AWS_ACCESS_KEY_ID"), env.get("AWS_SECRET_ACCESS_KEY"), self.region, "s3",
+                               env.get("AWS_SESSION_TOKEN"))
+
+    @staticmethod
+    def split(path: str) -> tuple[str, str]:
+        u = urllib.parse.urlparse(path)
+        return u.netloc, u.path.lstrip("/")
+
+    def _bucket_url(self, bucket: str) -> str:
+        return f"{self.endpoint}/{bucket}" if self.endpoint else f"https://{bucket}.s3.{self.region}.amazonaws.com"
+
+    def url(self, path):
+        bucket, key = self.split(path)
+        return f"{self._bucket_url(bucket)}/{urllib.parse.quote(key, safe='/-_.~')}"
+
+    def _open_url(self, url: str, method: str = "GET", extra: Optional[dict] = None):
+        headers = self.signer.headers(method, url, extra)
+        return urllib.request.urlopen(urllib.request.Request(url, method=method, headers=headers), timeout=self.timeout)
+
+    def _req(self, path: str, method: str = "GET", extra: Optional[dict] = None):
+        return self._open_url(self.url(path), method, extra)
+
+    def list_objects(self, bucket: str, prefix: str, delimiter: str = "/") -> tuple[list[tuple[str, int]], list[str]]:
+        """([(key, size)], [common prefixes]) under `prefix`, following continuation tokens."""
+        import xml.etree.ElementTree as ET
+        objects, prefixes, token = [], [], None
+        while True:
+            q = {"list-type": "2", "prefix": prefix}
+            if delimiter:
+                q["delimiter"] = delimiter
+            if token:
+                q["continuation-token"] = token
+            with self._open_url(f"{self._bucket_url(bucket)}/?{urllib.parse.urlencode(sorted(q.items()))}") as r:
+                root = ET.fromstring(r.read())
+            strip = lambda tag: tag.rsplit("}", 1)[-1]
+            token = None
+            for el in root:
+                name = strip(el.tag)
+                if name == "Contents":
+                    f = {strip(c.tag): (c.text or "") for c in el}
+                    objects.append((f.get("Key", ""), int(f.get("Size", "0") or 0)))
+                elif name == "CommonPrefixes":
+                    prefixes.extend((c.text or "") for c in el if strip(c.tag) == "Prefix")
+                elif name == "NextContinuationToken":
+                    token = el.text
+            if not token:
+                return objects, prefixes
+
+    def list(self, path):
+        bucket, key = self.split(path)
+        prefix = key if not key or key.endswith("/") else key + "/"
+        objects, prefixes = self.list_objects(bucket, prefix)
+        names = [k[len(prefix):] for k, _ in objects if k != prefix] + [p[len(prefix):] for p in prefixes]
+        return sorted(n for n in names if n)
+
+    def stat(self, path):
+        bucket, key = self.split(path)
+        if key and not key.endswith("/"):
+            try:
+                return HttpBackend.stat(self, path)
+            except urllib.error.HTTPError as e:
+                if e.code not in (403, 404):
+                    raise
+        prefix = key if not key or key.endswith("/") else key + "/"
+        objects, prefixes = self.list_objects(bucket, prefix)
+        if objects or prefixes or not key:
+            return Stat(sum(n for _, n in objects), "directory")
+        raise FileNotFoundError(path)
+
+
+class GcsBackend(HttpBackend):
+    """gs://bucket/object.  The bearer token comes from, in this order (vfs/gcs.zig:380-520): `GCS_ACCESS_TOKEN` /
+    `GOOGLE_OAUTH_ACCESS_TOKEN`; the authorised-user file named by `GOOGLE_APPLICATION_CREDENTIALS` or gcloud's
+    `application_default_credentials.json` (its refresh token is exchanged at the OAuth token endpoint); the metadata
+    server of a Google Cloud VM; else requests go unauthenticated (public buckets).  `list` uses the JSON API."""
+    TOKEN_URL = "https://oauth2.googleapis.com/token"
+    METADATA_URL = "http://metadata.google.internal/computeMetadata/v1/instance/service-accounts/default/token"
+
+    def __init__(self, env: Optional[dict] = None, endpoint: str = "https://storage.googleapis.com", timeout: float = 60.0):
+        super().__init__(timeout=timeout)
+        self.env = os.environ if env is None else env
+        self.endpoint = endpoint.rstrip("/")
+        self._token: Optional[str] = None
+        self._expires = 0.0
+        self._probed_metadata = False
+
+    def _credentials_file(self) -> Optional[str]:
+        p = self.env.get("GOOGLE_APPLICATION_CREDENTIALS")
+        if p and os.path.exists(p):
+            return p
+        home = self.env.get("HOME")
+        p = os.path.join(home, ".config", "gcloud", "application_default_credentials.json") if home else None
+        return p if p and os.path.exists(p) else None
+
+    def token(self) -> Optional[str]:
+        import json
+        import time as _time
+        static = self.env.get("GCS_ACCESS_TOKEN") or self.env.get("GOOGLE_OAUTH_ACCESS_TOKEN")
+        if static:
+            return static
+        if self._token and _time.time() < self._expires - 60:
+            return self._token
+        cred = self._credentials_file()
+        try:
+            if cred:
+                with open(cred, "r") as f:
+                    c = json.load(f)
+                if c.get("type", "authorized_user") != "authorized_user" or "refresh_token" not in c:
+                    raise ValueError(f"{cred}: only authorised-user credentials (a refresh token) are supported")
+                body = urllib.parse.urlencode({"grant_type": "refresh_token", "client_id": c["client_id"],
+                                               "client_secret": c["client_secret"], "refresh_token": c["refresh_token"]}).encode()
+                req = urllib.request.Request(self.env.get("GCS_TOKEN_URL", self.TOKEN_URL), data=body, method="POST",
+                                             headers={"Content-Type": "application/x-www-form-urlencoded"})
+            elif not self._probed_metadata:
+                self._probed_metadata = True
+                req = urllib.request.Request(self.env.get("GCS_METADATA_URL", self.METADATA_URL), headers={"Metadata-Flavor": "Google"})
+            else:
+                return None
+            with urllib.request.urlopen(req, timeout=min(self.timeout, 5.0)) as r:
+                tok = json.loads(r.read())
+            self._token, self._expires = tok["access_token"], _time.time() + float(tok.get("expires_in", 3600))
+            return self._token
+        except (OSError, KeyError, ValueError) as e:
+            if cred:
+                raise PermissionError(f"could not obtain a Google Cloud access token from {cred}: {e}") from e
+            return None                     # no metadata server: anonymous access
+
+    @staticmethod
+    def split(path: str) -> tuple[str, str]:
+        u = urllib.parse.urlparse(path)
+        return u.netloc, u.path.lstrip("/")
+
+    def url(self, path):
+        bucket, key = self.split(path)
+        return f"{self.endpoint}/{bucket}/{urllib.parse.quote(key, safe='/-_.~')}"
+
+    def _auth(self, extra: Optional[dict]) -> dict:
+        h = dict(extra or {})
+        tok = self.token()
+        if tok:
+            h["Authorization"] = f"Bearer {tok}"
+        return h
+
+    def _req(self, path: str, method: str = "GET", extra: Optional[dict] = None):
+        return urllib.request.urlopen(urllib.request.Request(self.url(path), method=method, headers=self._auth(extra)),
+                                      timeout=self.timeout)
+
+    def list_objects(self, bucket: str, prefix: str, delimiter: str = "/") -> tuple[list[tuple[str, int]], list[str]]:
+        import json
+        objects, prefixes, page = [], [], None
+        while True:
+            q = {"prefix": prefix, "fields": "items(name,size),prefixes,nextPageToken"}
+            if delimiter:
+                q["delimiter"] = delimiter
+            if page:
+                q["pageToken"] = page
+            url = f"{self.endpoint}/storage/v1/b/{bucket}/o?{urllib.parse.urlencode(q)}"
+            with urllib.request.urlopen(urllib.request.Request(url, headers=self._auth(None)), timeout=self.timeout) as r:
+                doc = json.loads(r.read())
+            objects.extend((it["name"], int(it.get("size", 0))) for it in doc.get("items", []))
+            prefixes.extend(doc.get("prefixes", []))
+            page = doc.get("nextPageToken")
+            if not page:
+                return objects, prefixes
+
+    list = S3Backend.list
+    stat = S3Backend.stat
+
 
 class BucketBackend(HttpBackend):
+    """Public objects behind a URL template with `{bucket}` and `{key}` (no signing, no listing)."""
+
     def __init__(self, template: str):
         super().__init__()
         self.template = template
@@ -159,8 +424,8 @@ class Vfs:
         v.register("http", HttpBackend())
         v.register("https", HttpBackend())
         v.register("hf", HfBackend())
-        v.register("s3", BucketBackend("https://{bucket}.s3.amazonaws.com/{key}"))
-        v.register("gs", BucketBackend("https://storage.googleapis.com/{bucket}/{key}"))
+        v.register("s3", S3Backend())
+        v.register("gs", GcsBackend())
         return v
 
     def resolve(self, uri: str) -> tuple[Backend, str]:
