@@ -18,6 +18,7 @@ import itertools
 import math
 from typing import Iterable, Mapping, Optional, Sequence, Union
 
+import numpy as np
 import torch
 
 from .dtype import DataType
@@ -134,6 +135,10 @@ def _spmd_align_dot(lhs: "Tensor", rhs: "Tensor", ca, cb, ba, bb):
     return lhs, rhs, pending
 
 
+def _is_soft_float(dt: DataType) -> bool:
+    return dt.is_float() and not dt.is_native_torch()
+
+
 _MEMORY_KINDS: dict = {}      # Tensor id -> memory kind declared with `on_memory` on a symbolic input
 
 
@@ -209,7 +214,10 @@ class Tensor:
 
     @staticmethod
     def arange(end: int, start: int = 0, step: int = 1, dtype=DataType.i64, device="cpu") -> "Tensor":
-        return Tensor(torch.arange(start, end, step, dtype=_torch_dtype(dtype), device=device))
+        td = _torch_dtype(dtype)
+        if td in (torch.uint16, torch.uint32, torch.uint64):        # torch has no arange kernel for these
+            return Tensor(torch.arange(start, end, step, dtype=torch.int64, device=device).to(td))
+        return Tensor(torch.arange(start, end, step, dtype=td, device=device))
 
     @staticmethod
     def iota(shape: Shape, axis: Axis, device="cpu") -> "Tensor":
@@ -413,8 +421,23 @@ class Tensor:
         return self._like(o)
 
     def convert(self, dtype) -> "Tensor":
+        """Value-preserving cast.  Float formats torch cannot compute with (f4e2m1, f8e3m4, f8e4m3, f8e4m3b11fnuz,
+        f8e8m0) live as their codes in uint8: converting to one encodes (round to nearest even, as
+        zml/floats.zig), converting from one decodes through a 256-entry table."""
         dt = DataType.parse(dtype)
-        return Tensor(self._need().to(dt.to_torch()), self._shape.with_dtype(dt))
+        src = self.dtype()
+        x = self._need()
+        if src is dt:
+            return self
+        if _is_soft_float(src):
+            from . import floats
+            table = torch.from_numpy(np.asarray(floats.FORMATS[src.value].to_f32(np.arange(256, dtype=np.uint8)))).to(x.device)
+            x = table[x.long()]
+        if _is_soft_float(dt):
+            from . import floats
+            codes = floats.FORMATS[dt.value].from_f32(x.detach().float().cpu().numpy())
+            return Tensor(torch.from_numpy(np.ascontiguousarray(codes).astype(np.uint8)).to(x.device), self._shape.with_dtype(dt))
+        return Tensor(x.to(dt.to_torch()), self._shape.with_dtype(dt))
 
     def bit_cast(self, dtype) -> "Tensor":
         dt = DataType.parse(dtype)
@@ -573,10 +596,21 @@ class Tensor:
     def quick_gelu(self): return self._un(lambda x: x * torch.sigmoid(1.702 * x))
     def leaky_relu(self, slope: float = 0.01): return self._un(lambda x: torch.nn.functional.leaky_relu(x, slope))
 
-    def swiglu(self, beta: float, w1: "Tensor", w3: "Tensor", tag: Axis = -1) -> "Tensor":
-        """(x.w1) * sigmoid(beta * x.w1) * (x.w3)  (zml/tensor.zig swiglu)."""
-        g = self.dot(w1, tag)
-        return g.mul(g.scale(beta).sigmoid()).mul(self.dot(w3, tag))
+    def swiglu(self, beta: float, w: "Tensor", v: "Tensor", b=None, c=None, tag: Axis = -1) -> "Tensor":
+        """value = x.w + b, gate = x.v + c, result = value * sigmoid(beta * value) (outer) gate
+        (zml/tensor.zig:1508-1519).  When value and gate carry the same tags the product is element-wise - the usual
+        gated MLP; with different tags it is the outer product the reference's test builds.  `swiglu(beta, w, v, tag)`
+        (no biases) is accepted too."""
+        if c is None and isinstance(b, (str, int)):
+            tag, b = b, None
+        value = self.dot(w, tag)
+        if b is not None:
+            value = value.add(b.broad(value.shape()))
+        gate = self.dot(v, tag)
+        if c is not None:
+            gate = gate.add(c.broad(gate.shape()))
+        act = value.mul(value.scale(beta).sigmoid())
+        return act.mul(gate) if act.shape().tags == gate.shape().tags else act.outer(gate)
 
     # ------------------------------------------------------------------ reductions (keep the axis, size 1)
     def _reduce(self, ax: Axis, fn) -> "Tensor":
@@ -985,8 +1019,14 @@ class Tensor:
             raise ValueError(f"chunk_exact: {self._shape.dims[a]} not divisible by {n_chunks}")
         return [self._like(c, part=None) for c in torch.chunk(self._need(), n_chunks, a)]
 
-    def chunk_allow_trailing(self, ax: Axis, chunk_size: int) -> list["Tensor"]:
-        return [self._like(c) for c in torch.split(self._need(), chunk_size, self.axis(ax))]
+    def chunk_allow_trailing(self, ax: Axis, n_chunks: int) -> list["Tensor"]:
+        """`n_chunks` chunks of floor(dim / n_chunks) entries, plus one shorter chunk with what is left
+        (zml/tensor.zig:3572-3594): 10 entries in 3 chunks -> 3, 3, 3 and a trailing 1."""
+        d = self.dim(ax)
+        size = d // n_chunks
+        if size == 0:
+            raise ValueError(f"chunk_allow_trailing: axis of {d} entries cannot give {n_chunks} chunks")
+        return [self._like(c) for c in torch.split(self._need(), size, self.axis(ax))]
 
     def split(self, ax: Axis, sizes: Sequence[int]) -> list["Tensor"]:
         return [self._like(c) for c in torch.split(self._need(), list(sizes), self.axis(ax))]
@@ -1010,6 +1050,8 @@ class Tensor:
     def dynamic_update_slice(self, offsets: Mapping[Axis, object], update: "Tensor") -> "Tensor":
         """Copy of self with `update` written at the (clamped) offsets; missing axes start at 0.
         If `update` lacks an offset axis it is treated as size 1 there."""
+        if not isinstance(offsets, Mapping):                 # one offset per axis, in order (zml/tensor.zig:3865)
+            offsets = {i: o for i, o in enumerate(offsets)}
         out = self._need().clone()
         u = update._need()
         upd_shape = update._shape
@@ -1231,9 +1273,20 @@ class Tensor:
         return self._like(v.to(self.data.dtype), tags), self._like(i.to(torch.int32), tags)
 
     # ------------------------------------------------------------------ matrices
-    def triangular(self, num_diagonals: int = 0, lower: bool = True) -> "Tensor":
-        fn = torch.tril if lower else torch.triu
-        return self._like(fn(self._need(), num_diagonals))
+    def triangular(self, axes_=(-2, -1), num_diagonals: int = 0, lower: bool = True) -> "Tensor":
+        """Keeps the entries with row + num_diagonals >= column over the two `axes_`, zero elsewhere
+        (zml/tensor.zig:4134-4144); `lower=False` keeps the other triangle.  `triangular(k)` (an int first) means the
+        last two axes."""
+        if isinstance(axes_, int) and not isinstance(axes_, bool):
+            axes_, num_diagonals = (-2, -1), axes_
+        r, c = self.axes(axes_)
+        x = self._need()
+        view_r, view_c = [1] * x.dim(), [1] * x.dim()
+        view_r[r], view_c[c] = x.shape[r], x.shape[c]
+        rows = torch.arange(x.shape[r], device=x.device).view(view_r)
+        cols = torch.arange(x.shape[c], device=x.device).view(view_c)
+        keep = (rows + num_diagonals >= cols) if lower else (rows + num_diagonals <= cols)
+        return self._like(torch.where(keep, x, torch.zeros((), dtype=x.dtype, device=x.device)))
 
     def to_diagonal(self, ax: Axis, new_tags: Sequence[str]) -> "Tensor":
         a = self.axis(ax)
