@@ -1,0 +1,100 @@
+"""Golden values of the reference's nn tests (zml/nn.zig `test` blocks, read as data)."""
+import torch
+
+from zml_b200 import Tensor, nn
+from zml_b200.nn import Layout, RopeOpts, Scaling
+
+X16 = [0.754, -0.146, 0.00443, -0.958, -0.533, 0.834, 0.555, 0.853, -0.309, 0.999, 0.983, -0.693, 0.979, 0.997, -0.359, 0.888]
+
+
+def test_normalize_l2():                                            # zml/nn.zig:518-535
+    x = Tensor.from_torch(torch.tensor([[-0.9686, -1.0058], [-1.7808, 0.6698]]))
+    want = torch.tensor([[-0.6937, -0.7203], [-0.9360, 0.3520]])
+    assert torch.allclose(nn.normalize_l2(x, 1e-12).data, want, atol=1e-4)
+
+
+def test_inv_freq_llama3_and_yarn():                                # zml/nn.zig:882-923
+    llama = Scaling(kind="llama3", factor=32, high_freq_factor=4, low_freq_factor=1, original_max_position_embeddings=8192,
+                    rope_theta=500_000)
+    want = [1.000000000000e+00, 6.636012792587e-01, 4.403666257858e-01, 2.922278344631e-01, 1.939227581024e-01,
+            1.286873817444e-01, 8.539710193872e-02, 5.666961893439e-02, 3.760603070259e-02, 2.495540864766e-02,
+            1.656044088304e-02, 1.098952908069e-02, 7.292665075511e-03, 4.839421249926e-03, 3.211446106434e-03,
+            1.290548010729e-03, 4.295567050576e-04, 9.708286233945e-05, 1.946163865796e-05, 1.291476746701e-05,
+            8.570255886298e-06, 5.687232260243e-06, 3.774054448513e-06, 2.504467147446e-06, 1.661967417022e-06,
+            1.102883629756e-06, 7.318749339902e-07, 4.856731266045e-07, 3.222932889457e-07, 2.138742303259e-07,
+            1.419272024350e-07, 9.418306490261e-08]
+    got = nn.inv_freq(64, RopeOpts(scaling=llama))
+    assert torch.allclose(got, torch.tensor(want), rtol=1e-5, atol=0)
+    yarn = Scaling(kind="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0, original_max_position_embeddings=4096,
+                   truncate=True, rope_theta=150_000)
+    want = [1.000000000000e+00, 6.890442967415e-01, 4.747820496559e-01, 3.271458745003e-01, 2.254180014133e-01,
+            1.553229838610e-01, 1.070244237781e-01, 7.374456524849e-02, 5.081327259541e-02, 3.162075206637e-02,
+            1.945096626878e-02, 1.179219130427e-02, 7.015713956207e-03, 4.069554619491e-03, 2.277272054926e-03,
+            1.206130953506e-03, 5.809474969283e-04, 2.279478358105e-04, 3.830881178146e-05, 2.639646845637e-05,
+            1.818833698053e-05, 1.253256959899e-05, 8.635495760245e-06, 5.950239483354e-06, 4.099978468730e-06,
+            2.825066758305e-06, 1.946596285052e-06, 1.341290953860e-06, 9.242089618056e-07, 6.368209142238e-07,
+            4.387978549403e-07, 3.023511396805e-07]
+    got = nn.inv_freq(64, RopeOpts(scaling=yarn))
+    assert torch.allclose(got, torch.tensor(want), rtol=1e-5, atol=0)
+    assert abs(yarn.attention_scaling() - 1.3465735902799727) < 1e-5
+
+
+def test_rope_scaling_json():                                       # zml/nn.zig:925-984
+    p = Scaling.from_hf({"rope_type": "proportional", "partial_rotary_factor": 0.25, "rope_theta": 1000000})
+    assert p.kind == "proportional" and abs(p.partial_rotary_factor - 0.25) < 1e-9 and p.rope_theta == 1_000_000
+    y = Scaling.from_hf({"rope_type": "yarn", "factor": 32.0, "original_max_position_embeddings": 4096, "partial_rotary_factor": 0.5})
+    assert y.kind == "yarn" and abs(y.partial_rotary_factor - 0.5) < 1e-9
+    d = Scaling.from_hf({"rope_type": "default", "rope_theta": 10000})
+    assert d.kind == "default" and d.rope_theta == 10_000
+
+
+def test_split_and_merge_real_imaginary():                          # zml/nn.zig:986-1090
+    x = torch.arange(20.0).reshape(5, 4)
+    for layout in (Layout.interleaved, Layout.real_im_pass):
+        re, im = nn.split_real_img(x, layout)
+        y = nn.merge_real_img(re, im, layout)
+        assert torch.equal(y, x)
+    re, im = nn.split_real_img(x, Layout.real_im_pass)
+    assert torch.equal(re, torch.stack([torch.arange(0.0, 20, 4), torch.arange(1.0, 20, 4)], 1))
+    assert torch.equal(im, torch.stack([torch.arange(2.0, 20, 4), torch.arange(3.0, 20, 4)], 1))
+    re, im = nn.split_real_img(x, Layout.interleaved)
+    assert torch.equal(re, torch.arange(0.0, 20, 2).reshape(5, 2)) and torch.equal(im, torch.arange(1.0, 20, 2).reshape(5, 2))
+    h = torch.arange(16.0)[None]
+    for layout in Layout:
+        re, im, rest = nn.split_real_img_pass(h, layout, 8)
+        assert re.shape[-1] == 4 and im.shape[-1] == 4
+        assert torch.equal(nn.merge_real_img_pass(re, im, rest, layout), h)
+    re, im, rest = nn.split_real_img_pass(h, Layout.real_pass_im_pass, 4)
+    assert re.tolist() == [[0, 1]] and im.tolist() == [[8, 9]] and rest[0].tolist() == [[2, 3, 4, 5, 6, 7]]
+    assert nn.split_real_img_pass(h, Layout.real_im_pass, 16)[2] is None
+
+
+def test_rope_interleaved_equals_sequential_on_a_symmetric_input():  # zml/nn.zig:1092-1132
+    x = torch.tensor([1.0, 0.1, -1.0, -0.5]).repeat(5, 1)            # [s, hd]
+
+    def run(layout):
+        re, im = nn.split_real_img(x, Layout.real_im_pass)
+        y = nn.rope(nn.merge_real_img(re, im, layout), None, RopeOpts(layout))
+        re, im = nn.split_real_img(y, layout)
+        return nn.merge_real_img(re, im, Layout.real_im_pass)
+    assert torch.allclose(run(Layout.interleaved), run(Layout.real_im_pass), atol=1e-5)
+
+
+def test_rope_proportional_and_yarn_partial():                      # zml/nn.zig:1134-1240
+    x = torch.tensor(X16).repeat(5, 1)
+    same = X16[2:8]
+    want = torch.tensor([[0.754, -0.146, *same, -0.309, 0.999, *X16[10:]],
+                         [0.667, -0.449, *same, 0.468, 0.904, *X16[10:]],
+                         [-0.0328, -0.708, *same, 0.814, 0.719, *X16[10:]],
+                         [-0.703, -0.897, *same, 0.412, 0.464, *X16[10:]],
+                         [-0.727, -0.997, *same, -0.369, 0.162, *X16[10:]]])
+    got = nn.rope(x, None, RopeOpts(Layout.real_pass_im_pass, Scaling(kind="proportional", partial_rotary_factor=0.25)))
+    assert torch.allclose(got, want, atol=2e-3, rtol=1e-2)
+    yarn = Scaling(kind="yarn", factor=32.0, beta_fast=32.0, beta_slow=1.0, original_max_position_embeddings=4096, truncate=True,
+                   rope_theta=150_000, partial_rotary_factor=0.25)
+    rest = X16[4:]
+    want = torch.tensor([[1.02, -0.197, 0.00597, -1.29, *rest], [0.544, -0.195, 0.858, -1.29, *rest],
+                         [-0.428, -0.193, 0.921, -1.29, *rest], [-1.01, -0.191, 0.137, -1.29, *rest],
+                         [-0.659, -0.19, -0.772, -1.29, *rest]])
+    got = nn.rope(x, None, RopeOpts(Layout.real_im_pass, yarn))
+    assert torch.allclose(got, want, atol=5e-3, rtol=1e-2)

@@ -6,5 +6,6 @@ from .layers import (Activation, LayerNorm, Linear, Quant, TensorScale, TokenEmb
                      normalize_variance, rms_norm)
 from .quant import (NVFP4_BLOCK, QuantScheme, dequantize_nvfp4, is_packed_nvfp4, quantize_nvfp4,  # noqa: F401
                     quantize_weight_nvfp4, scaled_dot)
-from .rotary import Layout, RopeOpts, Scaling, inv_freq, rope  # noqa: F401
+from .rotary import (Layout, RopeOpts, Scaling, inv_freq, merge_real_img, merge_real_img_pass, rope,  # noqa: F401
+                     split_real_img, split_real_img_pass)
 from .sampling import DynamicSamplingStrategy, SamplingStrategy, sample_tokens, sample_tokens_dynamic  # noqa: F401

@@ -152,3 +152,43 @@ def rope(x: torch.Tensor, positions: Optional[torch.Tensor] = None, opts: RopeOp
     freqs = inv_freq(hd, opts).to(x.device)
     y = _ref.rope_rotate(x, positions, freqs, opts.layout.value, rot, opts.scaling.attention_scaling())
     return y[:, 0, :] if squeeze else y
+
+
+# ---- how a head vector splits into real / imaginary / pass-through parts (zml/nn.zig:718-790) ----------------
+def split_real_img(x: torch.Tensor, layout: Layout) -> tuple[torch.Tensor, torch.Tensor]:
+    """(real, imaginary) halves of the last axis: first / second half for the sequential layouts, even / odd entries
+    for the interleaved one."""
+    n = x.shape[-1]
+    if layout is Layout.interleaved:
+        return x[..., 0::2], x[..., 1::2]
+    return x[..., : n // 2], x[..., n // 2:]
+
+
+def merge_real_img(real: torch.Tensor, imag: torch.Tensor, layout: Layout) -> torch.Tensor:
+    if layout is Layout.interleaved:
+        return torch.stack([real, imag], dim=-1).flatten(-2)
+    return torch.cat([real, imag], dim=-1)
+
+
+def split_real_img_pass(x: torch.Tensor, layout: Layout, rotary_dim: int):
+    """(real, imaginary, pass-through) when only `rotary_dim` of the head dimension rotates; the pass-through is
+    None, one tensor, or for `real_pass_im_pass` the pair (after the real part, after the imaginary part)."""
+    hd = x.shape[-1]
+    if rotary_dim == hd:
+        return (*split_real_img(x, layout), None)
+    half, hr = hd // 2, rotary_dim // 2
+    if layout is Layout.real_im_pass:
+        return x[..., :hr], x[..., hr:rotary_dim], x[..., rotary_dim:]
+    if layout is Layout.real_pass_im_pass:
+        return x[..., :hr], x[..., half:half + hr], (x[..., hr:half], x[..., half + hr:])
+    return x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2], x[..., rotary_dim:]
+
+
+def merge_real_img_pass(real: torch.Tensor, imag: torch.Tensor, passthrough, layout: Layout) -> torch.Tensor:
+    if passthrough is None:
+        return merge_real_img(real, imag, layout)
+    if layout is Layout.real_im_pass:
+        return torch.cat([real, imag, passthrough], dim=-1)
+    if layout is Layout.real_pass_im_pass:
+        return torch.cat([real, passthrough[0], imag, passthrough[1]], dim=-1)
+    return torch.cat([merge_real_img(real, imag, layout), passthrough], dim=-1)
