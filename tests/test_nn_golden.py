@@ -98,3 +98,45 @@ def test_rope_proportional_and_yarn_partial():                      # zml/nn.zig
                          [-0.659, -0.19, -0.772, -1.29, *rest]])
     got = nn.rope(x, None, RopeOpts(Layout.real_im_pass, yarn))
     assert torch.allclose(got, want, atol=5e-3, rtol=1e-2)
+
+
+def test_gated_delta_net_golden():                                  # zml/nn.zig:1876-1992
+    t = lambda v, tags: Tensor.from_torch(torch.tensor(v), tags)
+    q = t([[[1.0, 0.0], [0.0, 1.0]], [[1.0, 1.0], [1.0, -1.0]]], ["s", "h", "k"])
+    k = t([[[1.0, 2.0], [0.0, 1.0]], [[2.0, 1.0], [1.0, 0.0]]], ["s", "h", "k"])
+    v = t([[[3.0, 1.0], [2.0, 4.0]], [[1.0, 5.0], [3.0, 0.0]]], ["s", "h", "v"])
+    alphas = t([[0.5, 0.25], [0.8, 0.6]], ["s", "h"])
+    betas = t([[1.0, 0.5], [0.75, 1.0]], ["s", "h"])
+    s0 = t([[[1.0, 0.0], [0.0, 1.0]], [[2.0, 1.0], [1.0, 0.0]]], ["h", "v", "k"])
+    res = nn.gated_delta_net(q, k, v, alphas, betas, s0)
+    want_out = torch.tensor([[[3.0, 0.0], [1.125, 2.0]], [[-11.15, 10.75], [2.325, -1.2]]])
+    want_state = torch.tensor([[[-9.3, -1.85], [6.9, 3.85]], [[3.0, 0.675], [0.0, 1.2]]])
+    assert torch.allclose(res.outputs.data, want_out, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(res.state.data, want_state, atol=1e-4, rtol=1e-4)
+
+
+def test_fixup_logits_for_dynamic_sampling():                       # zml/nn.zig:2173-2230
+    import math
+    ninf = -math.inf
+    logits = Tensor.from_torch(torch.tensor([math.log(2.0), math.log(1.0), math.log(4.0), math.log(3.0)]), ["voc"])
+    l4, l3, l2, l1 = math.log(4.0), math.log(3.0), math.log(2.0), math.log(1.0)
+    cases = [(dict(top_k=4), [l4, l3, l2, l1]),
+             (dict(top_k=2), [l4, l3, ninf, ninf]),
+             (dict(top_k=2, temperature=0.1), [l4 / 0.1, l3 / 0.1, ninf, ninf]),
+             (dict(top_k=4, top_p=0.1), [l4, ninf, ninf, ninf]),                    # at least one candidate survives
+             (dict(top_k=4, top_p=0.701), [l4, l3, ninf, ninf]),
+             (dict(top_k=4, top_p=0.901), [l4, l3, l2, ninf]),
+             (dict(top_k=3, top_p=0.701), [l4, ninf, ninf, ninf]),                  # top_p is taken over the top 3 only
+             (dict(top_k=4, top_p=0.901, min_p=0.6), [l4, l3, ninf, ninf])]
+    for kw, want in cases:
+        x, idx = nn.fixup_logits(logits, nn.DynamicSamplingStrategy(**kw))
+        assert idx.data.tolist() == [2, 3, 0, 1] and x.shape().tags == ("topk",)
+        assert torch.allclose(x.data, torch.tensor(want), rtol=1e-5), (kw, x.data)
+    # bf16 with infinite logits: the softmax is NaN, only the first candidate survives
+    boost, nerf = float("inf"), ninf
+    lb = Tensor.from_torch(torch.tensor([boost, boost, 2.0, nerf]).bfloat16(), ["voc"])
+    x, idx = nn.fixup_logits(lb, nn.DynamicSamplingStrategy(top_k=4, top_p=0.9, min_p=0.1))
+    assert idx.data.tolist() == [0, 1, 2, 3] and x.data.float().tolist() == [boost, nerf, nerf, nerf]
+    # a bound on top_k known ahead of time ranks only that many candidates
+    x, idx = nn.fixup_logits(logits, nn.DynamicSamplingStrategy(top_k=2, max_top_k=3))
+    assert idx.data.tolist() == [2, 3, 0] and torch.allclose(x.data, torch.tensor([l4, l3, ninf]))

@@ -8,4 +8,5 @@ from .quant import (NVFP4_BLOCK, QuantScheme, dequantize_nvfp4, is_packed_nvfp4,
                     quantize_weight_nvfp4, scaled_dot)
 from .rotary import (Layout, RopeOpts, Scaling, inv_freq, merge_real_img, merge_real_img_pass, rope,  # noqa: F401
                      split_real_img, split_real_img_pass)
-from .sampling import DynamicSamplingStrategy, SamplingStrategy, sample_tokens, sample_tokens_dynamic  # noqa: F401
+from .sampling import (DynamicSamplingStrategy, SamplingStrategy, fixup_logits, sample_tokens,  # noqa: F401
+                       sample_tokens_dynamic)

@@ -44,34 +44,53 @@ def sample_tokens(activations: Tensor, opts: SamplingStrategy, rng: Rng) -> tupl
 
 @dataclass
 class DynamicSamplingStrategy:
-    """Sampling parameters that arrive at run time (one value per call)."""
+    """Sampling parameters that arrive at run time (one value per call).  `max_top_k` bounds `top_k` ahead of time:
+    only that many candidates are ranked (0: the whole vocabulary is sorted)."""
     top_k: int = 0              # 0: no top-k cut
     temperature: float = 1.0
     top_p: float = 1.0
     min_p: float = 0.0
+    max_top_k: int = 0
+
+
+def fixup_logits(logits: Tensor, opts: DynamicSamplingStrategy) -> tuple[Tensor, Tensor]:
+    """(masked logits over a `topk` axis, their vocabulary indices), candidates sorted best first
+    (zml/nn.zig:2121-2159): entries past `top_k` are masked, the rest is divided by the temperature; then, on the
+    softmax of what is left, an entry stays while the cumulative probability up to and including it is <= top_p and
+    its probability is >= min_p x the best one.  The best candidate always stays (it would be masked when it alone
+    exceeds top_p, or when infinite logits turn the softmax into NaN).  top_p >= 1 switches the top-p test off."""
+    a = logits.axis("voc")
+    x = logits.data.movedim(a, -1)
+    if opts.max_top_k and opts.max_top_k > 0:
+        vals, order = torch.topk(x.float(), min(opts.max_top_k, x.shape[-1]), dim=-1, sorted=True)
+        vals = vals.to(x.dtype)
+    else:
+        vals, order = torch.sort(x, dim=-1, descending=True, stable=True)
+    neg = torch.full((), float("-inf"), dtype=vals.dtype, device=vals.device)
+    pos = torch.arange(vals.shape[-1], device=vals.device)
+    if opts.top_k and opts.top_k > 0:
+        vals = torch.where(pos >= opts.top_k, neg, vals)
+    vals = vals / opts.temperature
+    probs = torch.softmax(vals, -1)
+    keep = probs >= opts.min_p * probs[..., :1]
+    if opts.top_p < 1.0:
+        keep &= torch.cumsum(probs, -1) <= opts.top_p
+    keep |= pos == 0
+    vals = torch.where(keep, vals, neg)
+    tags = tuple(t for i, t in enumerate(logits.shape().tags) if i != a) + ("topk",)
+    return Tensor(vals, None, tags), Tensor(order.to(torch.int32), None, tags)
 
 
 def sample_tokens_dynamic(logits: Tensor, opts: DynamicSamplingStrategy, rng: Rng) -> tuple[Tensor, Rng]:
+    """Gumbel-max over the candidates `fixup_logits` leaves (zml/nn.zig:2108-2119); temperature <= 0 is greedy."""
     a = logits.axis("voc")
-    x = logits.data.float().movedim(a, -1)
     if opts.temperature <= 0:
-        tok = x.argmax(-1)
+        tok = logits.data.float().movedim(a, -1).argmax(-1)
     else:
-        x = x / opts.temperature
-        sorted_x, order = torch.sort(x, dim=-1, descending=True)
-        keep = torch.ones_like(sorted_x, dtype=torch.bool)
-        if opts.top_k and opts.top_k > 0:
-            keep[..., opts.top_k:] = False
-        p = torch.softmax(sorted_x, -1)
-        if opts.top_p < 1.0:
-            cum = torch.cumsum(p, -1)
-            keep &= (cum - p) < opts.top_p
-        if opts.min_p > 0.0:
-            keep &= p >= opts.min_p * p[..., :1]
-        keep[..., 0] = True
-        masked = torch.where(keep, sorted_x, torch.full_like(sorted_x, float("-inf")))
+        x, order = fixup_logits(logits, opts)
+        masked = x.data.float()
         g = rng.gumbel(Shape(tuple(masked.shape), "f32")).data.to(masked.device)
         pick = (masked + g).argmax(-1, keepdim=True)
-        tok = torch.gather(order, -1, pick).squeeze(-1)
+        tok = torch.gather(order.data.long(), -1, pick).squeeze(-1)
     tags = tuple(t for i, t in enumerate(logits.shape().tags) if i != a)
     return Tensor(tok.to(torch.int32), None, tags), rng
