@@ -196,6 +196,25 @@ class Shape:
         bits = self._dtype.bit_size_of()
         return (self.count() * bits + 7) // 8 if bits < 8 else self.count() * (bits // 8)
 
+    def device_byte_size(self) -> int:
+        """Bytes on the device, where sub-byte types are packed: ceil(count x bits / 8), a bool taking a byte
+        (zml/shape.zig:508-520)."""
+        bits = 8 if self._dtype is DataType.bool else self._dtype.bit_size_of()
+        return (self.count() * bits + 7) // 8
+
+    def parse_axes_options(self, options, default):
+        """One value per axis from {axis: value} (axes not named get `default`) or from a sequence that names every
+        axis in order (zml/shape.zig:1568-1594)."""
+        if isinstance(options, Mapping):
+            out = [default] * self.rank()
+            for ax, v in options.items():
+                out[self.axis(ax)] = v
+            return tuple(out)
+        options = tuple(options)
+        if len(options) != self.rank():
+            raise ValueError(f"expects exactly {self.rank()} options for {self}, got {len(options)}")
+        return options
+
     # ------------------------------------------------------------------ comparison / printing
     def eql(self, other: "Shape") -> bool:
         return self._dims == other._dims and self._dtype is other._dtype and self._tags == other._tags
