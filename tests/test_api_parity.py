@@ -225,3 +225,23 @@ def test_logo_rows_and_colour_detection():
     assert logo.detect_color_support(pipe, {"CLICOLOR_FORCE": "1", "TERM": "xterm-256color"}) == logo.ANSI_256
     with pytest.raises(ValueError):
         logo.write(io.StringIO(), logo.NO_COLOR, blocks=[("cyan", ["a"]), ("sky", ["a", "b"])])
+
+
+def test_slice_pretty_print_and_strided_compare_golden():
+    """zml/slice.zig: "slice pretty print rank 0..3 / ellipsis" and "expectClose compares dense and strided slices"."""
+    from zml_b200 import Slice, testing
+    s3 = Slice.from_numpy(np.arange(64, dtype=np.int32).reshape(4, 4, 4))
+    want = "{\n" + "".join("  {\n" + "".join(f"    {{{','.join(str(16 * i + 4 * j + k) for k in range(4))}}},\n" for j in range(4)) + "  },\n"
+                           for i in range(4)) + "}"
+    assert s3.pretty_print() == want
+    assert Slice.from_numpy(np.arange(4, dtype=np.int32).reshape(1, 4)).pretty_print() == "{\n  {0,1,2,3},\n}"
+    assert Slice.from_numpy(np.arange(4, dtype=np.int32)).pretty_print() == "{0,1,2,3}"
+    assert Slice.from_numpy(np.array(0, dtype=np.int32)).pretty_print() == "0"
+    tall = Slice.from_numpy(np.arange(9, dtype=np.int32).reshape(9, 1)).pretty_print()
+    assert tall == "{\n  {0},\n  {1},\n  {2},\n  {3},\n  ...\n  {5},\n  {6},\n  {7},\n  {8},\n}"
+    dense = Slice.from_numpy(np.array([[1, 2], [5, 6]], dtype=np.float32))
+    storage = Slice.from_numpy(np.array([[1, 2, 99, 98], [5, 6, 97, 96]], dtype=np.float32))
+    strided = storage.sub_slice(1, 0, 2)
+    assert not strided.is_contiguous()
+    testing.expect_close(dense, strided, atol=0, rtol=0, min_close=1.0)
+    testing.expect_close(strided, dense, atol=0, rtol=0, min_close=1.0)
