@@ -103,3 +103,43 @@ def test_other_fp8_and_e8m0():
     assert e.from_f32([1.00001])[0] == 127 and e.from_f32([1.00001], round_up=True)[0] == 128
     np.testing.assert_array_equal(floats.float_cast([1.0, 0.3], "f32", "bf16"),
                                   torch.tensor([1.0, 0.3]).bfloat16().view(torch.int16).numpy().astype(np.uint16))
+
+
+def test_reference_float_vectors():
+    """zml/floats.zig tests "Float8E4", "Float8E5", BFloat16, Float8E8M0, Float4E2M1 (values read as data)."""
+    import numpy as np
+    from zml_b200 import floats
+
+    def lossless(fmt, vals):
+        got = fmt.to_f32(fmt.from_f32(np.asarray(vals, dtype=np.float32)))
+        assert np.array_equal(got, np.asarray(vals, dtype=np.float32)), (fmt, vals, got)
+
+    def lossy(fmt, vals, tol):
+        got = fmt.to_f32(fmt.from_f32(np.asarray(vals, dtype=np.float32)))
+        assert np.allclose(got, np.asarray(vals, dtype=np.float32), rtol=tol, atol=0), (fmt, vals, got)
+
+    for name in ("f8e4m3b11fnuz", "f8e4m3fn", "f8e4m3fnuz"):
+        fmt = floats.FORMATS[name]
+        # bias 11 tops out at 30: the reference's -128 is replaced by -16 for that format
+        lossless(fmt, [0, 1.0, -2, 1.0 / 64.0, -128 if name != "f8e4m3b11fnuz" else -16, -1.125 / 64.0])
+        lossy(fmt, [3.02344107628, 1.0 / 128.0, 1.0 / 512.0], 1e-2)
+        assert float(fmt.to_f32(fmt.from_f32(np.float32(1.0 / 2048.0)))) == 0.0 or name == "f8e4m3b11fnuz"
+        assert not fmt.has_inf
+    for name in ("f8e5m2", "f8e5m2fnuz"):
+        fmt = floats.FORMATS[name]
+        lossless(fmt, [0, 1.0, -2, 1.0 / 128.0, -128])
+        lossy(fmt, [3.02344107628], 1e-2)
+    bf = floats.FORMATS["bf16"]
+    assert int(bf.from_f32(np.float32(0))) == 0 and int(bf.from_f32(np.float32(-2))) == (1 << 15) | ((127 + 1) << 7)
+    assert int(bf.from_f32(np.float32(3.02344107628))) == ((127 + 1) << 7) | 66
+    assert int(bf.from_f32(np.float32(1.0 / 128.0))) == (127 - 7) << 7
+    assert int(bf.neg(bf.from_f32(np.float32(np.inf)))) == 0xFF80
+    lossless(bf, [0, -2, 1.0 / 128.0, np.inf])
+    lossy(bf, [3.02344107628], 1e-2)
+    e8 = floats.FORMATS["f8e8m0"]
+    assert int(e8.from_f32(np.float32(1.0))) == 127
+    assert np.array_equal(e8.to_f32(e8.from_f32(np.asarray([1.0, 64.0, 1.0 / 128.0, 2.0 ** 127], dtype=np.float32))),
+                          np.asarray([1.0, 64.0, 1.0 / 128.0, 2.0 ** 127], dtype=np.float32))
+    f4 = floats.FORMATS["f4e2m1"]
+    assert np.array_equal(f4.to_f32(np.arange(16, dtype=np.uint8)), floats.F4E2M1_VALUES)
+    assert f4.from_f32(floats.F4E2M1_VALUES).tolist() == list(range(16))

@@ -103,6 +103,10 @@ class FloatFormat:
 
     # ------------------------------------------------------------------ encode
     def from_f32(self, values, saturate: bool = False) -> np.ndarray:
+        with np.errstate(divide="ignore", invalid="ignore", over="ignore"):      # inf / NaN inputs are patched below
+            return self._from_f32(values, saturate)
+
+    def _from_f32(self, values, saturate: bool) -> np.ndarray:
         x = np.asarray(values, dtype=np.float32).astype(np.float64)
         sign = np.signbit(x)
         a = np.abs(x)
