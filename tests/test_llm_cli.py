@@ -76,3 +76,65 @@ def test_cli_chat_loop_on_two_ranks_reads_stdin_on_rank_0_only(tmp_path):
                        input="hello\nworld\n", capture_output=True, text=True, env=env, timeout=300)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-2500:]
     assert r.stdout.count("tok/s") == 2 and "attention backend: vanilla" in r.stderr
+
+
+def test_load_model_from_a_remote_repository(tmp_path):
+    """The same repository behind an HTTP server: config, tokenizer and the index come through the VFS, tensors as
+    range requests; the loaded model equals the local one."""
+    import http.server
+    import threading
+    ref_model = make_repo(str(tmp_path))
+    files = {n: (tmp_path / n).read_bytes() for n in os.listdir(tmp_path)}
+
+    class Repo(http.server.BaseHTTPRequestHandler):
+        ranged = []
+
+        def log_message(self, *a):
+            pass
+
+        def _serve(self, head):
+            data = files.get(self.path.rsplit("/", 1)[1])
+            if data is None or not self.path.startswith("/models/tiny/"):
+                self.send_response(404)
+                self.send_header("Content-Length", "0")
+                self.end_headers()
+                return
+            rng = self.headers.get("Range")
+            if rng:
+                a, b = (int(v) for v in rng.split("=")[1].split("-"))
+                body = data[a:b + 1]
+                self.send_response(206)
+                self.send_header("Content-Range", f"bytes {a}-{a + len(body) - 1}/{len(data)}")
+                if self.path.endswith(".safetensors"):
+                    Repo.ranged.append(len(body))
+            else:
+                body = data
+                self.send_response(200)
+            self.send_header("Content-Length", str(len(data) if head and not rng else len(body)))
+            self.end_headers()
+            if not head:
+                self.wfile.write(body)
+
+        def do_HEAD(self):
+            self._serve(True)
+
+        def do_GET(self):
+            self._serve(False)
+
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Repo)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        uri = f"http://127.0.0.1:{srv.server_address[1]}/models/tiny"
+        model, tok = hub.load_model(uri, device="cpu", dtype=torch.float32)
+        assert tok is not None and tok.token_id("<|eot_id|>") is not None
+        assert torch.equal(model.layers[1].qkv, ref_model.layers[1].qkv) and torch.equal(model.embed, ref_model.embed)
+        a, _ = Engine(model, 32, 16, 2, 128).generate([[1, 2, 3]], 4)
+        b, _ = Engine(ref_model, 32, 16, 2, 128).generate([[1, 2, 3]], 4)
+        assert a == b
+        assert Repo.ranged and max(Repo.ranged) < max(len(v) for k, v in files.items() if k.endswith(".safetensors"))
+        # the index file itself is accepted too
+        cfg, store, repo = hub.open_repo(f"{uri}/{safetensors.INDEX_NAME}")
+        assert repo == uri and cfg["model_type"] == "llama" and len(store.registry) == len(ref_model.state_dict_hf())
+    finally:
+        srv.shutdown()
+        srv.server_close()

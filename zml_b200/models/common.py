@@ -41,8 +41,9 @@ class GenerationOptions:
 
 
 def read_config_json(repo: str) -> dict:
-    with open(os.path.join(repo, "config.json"), "r") as f:
-        return json.load(f)
+    """config.json of a repository: a local directory or a URI the VFS can read (hf://, s3://, gs://, https://)."""
+    from ..safetensors import read_repo_file
+    return json.loads(read_repo_file(repo, "config.json").decode("utf-8"))
 
 
 def parse_config(cls, source: Union[str, dict]):

@@ -23,7 +23,8 @@ def open_repo(path: str):
     from .. import safetensors
     repo = safetensors.resolve_model_repo(path)
     cfg = common.read_config_json(repo)
-    entry = path if os.path.isfile(path) else safetensors.resolve_model_entrypoint(repo)
+    is_file = path.endswith((".safetensors", ".index.json")) if safetensors.is_uri(path) else os.path.isfile(path)
+    entry = path if is_file else safetensors.resolve_model_entrypoint(repo)
     return cfg, TensorStore.from_path(entry), repo
 
 
@@ -53,11 +54,21 @@ def load_model(path: str, comm: Optional[Comm] = None, device="cpu", dtype=torch
         from ..parallel import symm
         comm.fused = symm.SymmetricContext.create(comm, config.hidden_size, staging_elems=8192 * config.hidden_size)
     tok = None
+    from .. import safetensors
     for name in ("tokenizer.json", "tokenizer.model"):
-        p = os.path.join(repo, name)
-        if os.path.exists(p):
-            tok = Tokenizer.from_file(p)
-            break
+        if not safetensors.repo_file_exists(repo, name):
+            continue
+        if safetensors.is_uri(repo):
+            if name.endswith(".json"):
+                tok = Tokenizer.from_bytes(safetensors.read_repo_file(repo, name))
+            else:                           # SentencePiece wants a file: fetch it next to the other temporaries
+                import tempfile
+                with tempfile.NamedTemporaryFile(suffix=".model", delete=False) as f:
+                    f.write(safetensors.read_repo_file(repo, name))
+                tok = Tokenizer.from_file(f.name)
+        else:
+            tok = Tokenizer.from_file(os.path.join(repo, name))
+        break
     return model, tok
 
 

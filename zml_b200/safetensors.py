@@ -179,22 +179,38 @@ def read_header(path: str) -> tuple[dict, int]:
 
 
 def resolve_model_repo(path: str) -> str:
-    """Directory that holds the checkpoint (a file path resolves to its directory)."""
+    """Directory (or, for a URI, the prefix) that holds the checkpoint: a file path resolves to its directory."""
     if path.endswith(".safetensors.index.json") or path.endswith(".safetensors"):
-        d = os.path.dirname(path) or "."
+        d = path.rsplit("/", 1)[0] if is_uri(path) else (os.path.dirname(path) or ".")
     else:
-        d = path
-    if not os.path.isdir(d):
+        d = path.rstrip("/") if is_uri(path) else path
+    if not is_uri(d) and not os.path.isdir(d):
         raise FileNotFoundError(d)
     return d
 
 
+def repo_file_exists(repo: str, name: str) -> bool:
+    if not is_uri(repo):
+        return os.path.exists(os.path.join(repo, name))
+    try:
+        return _vfs().stat(f"{repo}/{name}").kind == "file"
+    except (OSError, ValueError):            # urllib's HTTPError / URLError are OSErrors
+        return False
+
+
+def read_repo_file(repo: str, name: str) -> bytes:
+    """Bytes of a small file of a repository (config.json, tokenizer.json), local or behind the VFS."""
+    if is_uri(repo):
+        return _vfs().read(f"{repo}/{name}")
+    with open(os.path.join(repo, name), "rb") as f:
+        return f.read()
+
+
 def resolve_model_entrypoint(repo: str) -> str:
     for name in (INDEX_NAME, MODEL_NAME):
-        p = os.path.join(repo, name)
-        if os.path.isfile(p):
-            return p
-    raise FileNotFoundError(f"neither {INDEX_NAME} nor {MODEL_NAME} in {repo}")
+        if repo_file_exists(repo, name):
+            return f"{repo}/{name}" if is_uri(repo) else os.path.join(repo, name)
+    raise FileNotFoundError(f"{repo}: neither {INDEX_NAME} nor {MODEL_NAME}")
 
 
 class TensorRegistry:
@@ -211,8 +227,8 @@ class TensorRegistry:
         """`path` is a .safetensors file, an index json, or a repo directory; files may also be remote
         (`https://...`, `hf://org/repo/model.safetensors.index.json`, `s3://...`, `gs://...`): then only headers are
         fetched here and tensors are read later as range requests."""
-        if not is_uri(path) and os.path.isdir(path):
-            path = resolve_model_entrypoint(path)
+        if (not is_uri(path) and os.path.isdir(path)) or (is_uri(path) and not path.endswith((".safetensors", ".index.json"))):
+            path = resolve_model_entrypoint(path.rstrip("/") if is_uri(path) else path)
         reg = TensorRegistry()
         if path.endswith(".index.json"):
             if is_uri(path):
