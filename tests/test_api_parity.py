@@ -245,3 +245,23 @@ def test_slice_pretty_print_and_strided_compare_golden():
     assert not strided.is_contiguous()
     testing.expect_close(dense, strided, atol=0, rtol=0, min_close=1.0)
     testing.expect_close(strided, dense, atol=0, rtol=0, min_close=1.0)
+
+
+def test_top_level_names_and_fn_exe():
+    import zml_b200 as zml
+    assert zml.GiB == 1 << 30 and zml.Target.cuda.value == "cuda" and zml.Memory.host_pinned.value == "host_pinned"
+    assert zml.Sharding is zml.sharding.Sharding and zml.tracer is zml.profiling.tracer and zml.Bufferized is zml.mem.Bufferized
+    for name in ("logo", "stdx", "vfs", "spmd", "kernel", "flags", "testing"):
+        assert getattr(zml, name).__name__ == f"zml_b200.{name}"
+    pl = Platform.init("cpu")
+    w = Tensor.from_shape(Shape((3, 4), "f32", ("dout", "d")))
+    x = Tensor.from_shape(Shape((2, 4), "f32", ("b", "d")))
+    fx = zml.FnExe(lambda w_, x_: x_.dot(w_, "d")).compile(pl, (w, x))
+    wb = Buffer.from_tensor(pl, torch.arange(12.).reshape(3, 4), w.shape())
+    xb = Buffer.from_tensor(pl, torch.ones(2, 4), x.shape())
+    out = fx.call(wb, xb, wait=True)
+    assert out.to_tensor().tolist() == [[6.0, 22.0, 38.0]] * 2
+    run = fx.runner(wb)                                   # the weights bound once
+    assert run.call(xb).to_tensor().tolist() == [[6.0, 22.0, 38.0]] * 2
+    with pytest.raises(RuntimeError):
+        zml.FnExe(lambda a: a).call(xb)

@@ -206,3 +206,36 @@ class Runner:
     def call(self, *trees, wait: bool = False):
         rest = meta.collect(trees, _is_buffer)
         return self.exe._call_flat(self.baked + rest, wait)
+
+
+class FnExe:
+    """A function and the executable compiled from it (zml/exe.zig:383-470): `FnExe(fn).compile(platform, args)`,
+    then `call(...)` with buffers shaped like the function's arguments, or `runner(weights...)` to bind a prefix of
+    them once.  `raw` is the untyped `Exe`."""
+
+    def __init__(self, fn: Callable, raw: Optional[Exe] = None):
+        self.fn = fn
+        self.raw = raw
+
+    def compile(self, platform, args=(), opts=None) -> "FnExe":
+        from . import module
+        o = opts or module.CompilationOptions(program_name=getattr(self.fn, "__qualname__", "main"))
+        self.raw = module.compile(self.fn, args, platform, program_name=o.program_name, cuda_graph=o.cuda_graph,
+                                  validate=o.validate)
+        return self
+
+    def _exe(self) -> Exe:
+        if self.raw is None:
+            raise RuntimeError("FnExe: compile() has not been called")
+        return self.raw
+
+    def call(self, *trees, wait: bool = False):
+        return self._exe().call(*trees, wait=wait)
+
+    __call__ = call
+
+    def runner(self, *baked_trees) -> Runner:
+        return self._exe().runner(*baked_trees)
+
+    def deinit(self) -> None:
+        self.raw = None
