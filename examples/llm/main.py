@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """LLM CLI (the reference's `examples/llm`): load a HF-format checkpoint and chat with it.
 
-    python examples/llm/main.py --model=<repo dir | .safetensors | index.json> [--prompt=...]
+    python examples/llm/main.py --model=<repo dir | .safetensors | index.json | hf://org/repo | s3://... | gs://... | https://...> [--prompt=...]
         [--seqlen=2048] [--topk=1] [--temperature=1.0] [--seed=0] [--no-chat-template] [--profile]
         [--backend=b200|vanilla|attnd] [--attnd-ip=IP:PORT]
 
