@@ -166,6 +166,26 @@ def test_topk_sample(k):
         assert torch.allclose(counts / n, p, atol=0.04)
 
 
+def test_topk_of_merged_candidates_equals_topk_of_the_whole_row():
+    """What vocab-parallel top-k sampling does: every shard ranks its own columns, the k best of the union of the
+    shards' k best are the k best of the row, and the draw on the merged candidates is the draw on the whole row."""
+    torch.manual_seed(4)
+    k, shards, v_per = 4, 2, 500
+    logits = torch.randn(6, shards * v_per, device=DEV)
+    logits[:, -3:] = float("-inf")                       # padding columns of the last shard
+    cand_v, cand_i = [], []
+    for r in range(shards):
+        v, i = ops.topk(logits[:, r * v_per:(r + 1) * v_per].contiguous(), k)
+        cand_v.append(v)
+        cand_i.append(i + r * v_per)
+    cand_v, cand_i = torch.cat(cand_v, 1).contiguous(), torch.cat(cand_i, 1)
+    assert cand_v.shape == (6, shards * k)
+    pos, mv, mi = ops.topk_sample(cand_v, k, temperature=0.7, seed=3, step=9, return_topk=True)
+    tok, wv, wi = ops.topk_sample(logits, k, temperature=0.7, seed=3, step=9, return_topk=True)
+    assert torch.equal(mv, wv) and torch.equal(cand_i.gather(1, mi.long()), wi)
+    assert torch.equal(cand_i.gather(1, pos.long()[:, None])[:, 0], tok)
+
+
 def _make_paged(batch, seq_lens, hkv, hd, page, extra_pages=3):
     """Random paged cache with a shuffled page assignment."""
     max_pages = max((l + page - 1) // page for l in seq_lens) + 1

@@ -532,9 +532,16 @@ class LlamaModel:
             idxs = comm.all_gather((idx + self.comm.rank * self.v_per)[None])
             best = vals.argmax(0)
             return idxs.gather(0, best[None])[0].to(torch.int32)
-        # every rank holds v_per columns (padding columns are -inf), so column r * v_per + j is token r * v_per + j
-        full = comm.all_gather(logits, dim=1)
-        return ops.topk_sample(full.contiguous(), strategy.topk, strategy.temperature, seed, step, rng=rng)
+        # Every rank ranks its own columns (column j of rank r is token r * v_per + j; padding columns are -inf) and
+        # only the k best (value, token) pairs per row travel: the k best of their union are the k best of the whole
+        # vocabulary, in the same order, so the draw below equals the draw on gathered logits at 1 / (v_per / k) of the bytes.
+        k = min(strategy.topk, logits.shape[1])
+        vals, idx = ops.topk(logits, k)
+        cand_v = comm.all_gather(vals.contiguous(), dim=1).contiguous()
+        cand_i = comm.all_gather((idx + comm.rank * self.v_per).to(torch.int32).contiguous(), dim=1)
+        pos = ops.topk_sample(cand_v, strategy.topk if strategy.topk <= cand_v.shape[1] else cand_v.shape[1],
+                              strategy.temperature, seed, step, rng=rng)
+        return cand_i.gather(1, pos.long()[:, None])[:, 0].to(torch.int32)
 
     def forward(self, ids, meta: AttnMeta, kv_cache, strategy: Optional[common.SamplingStrategy] = None,
                 seed: int = 0, step: int = 0, rng=None):

@@ -288,6 +288,15 @@ def topk_sample(logits, k: int, temperature: float = 1.0, seed: int = 0, step: i
     return (tok, vals, idx) if return_topk else tok
 
 
+def topk(logits, k: int):
+    """(values, indices) of the k largest entries per row, sorted descending: float32 [B, k], int32 [B, k].  On CUDA
+    this is the radix-select kernel behind `topk_sample` (its draw is discarded); no random numbers are consumed."""
+    if not _cuda(logits):
+        return reference.topk(logits, k)
+    _, v, i = topk_sample(logits, k, 1.0, return_topk=True)
+    return v, i
+
+
 def advance_rng(rng, n: int = 1) -> None:
     """rng[1] += n in stream order (see `topk_sample`)."""
     if rng.is_cuda:
