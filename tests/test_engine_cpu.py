@@ -361,3 +361,28 @@ def test_session_decode_in_blocks_matches_token_by_token():
     s = Session(Engine(m, num_pages=16, page_size=16, max_batch=1, max_seq_len=128), 100, eos_ids=[eos])
     s.run_prefill([5, 6, 7, 8, 9])
     assert s.run_decode(stream_interval=4) == outs[0][0][:outs[0][0].index(eos) + 1]
+
+
+def test_engine_rejects_bad_requests_without_stranding_pages():
+    """Empty prompts, prompts that cannot fit and a batch that runs out of pages are refused with a clear error, leave
+    no page allocated, and the engine keeps working; no prompts is an empty result; top-k beyond the vocabulary is capped."""
+    from zml_b200.serving.engine import OutOfPages
+    cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=300))
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=1, std=0.05)
+    eng = Engine(model, num_pages=4, page_size=16, max_batch=2, max_seq_len=64)
+    free0 = len(eng.pool.free)
+    with pytest.raises(ValueError, match="empty prompt"):
+        eng.generate([[1, 2], []], 3)
+    with pytest.raises(ValueError, match="pages"):
+        eng.generate([list(range(1, 80))], 5)
+    with pytest.raises(OutOfPages):
+        eng.generate([list(range(1, 40)), list(range(1, 40))], 4)
+    with pytest.raises(ValueError, match="prompt 1 is empty"):
+        eng.serve([[1], [], [2]], 3)
+    with pytest.raises(ValueError, match="prompt 0 needs"):
+        eng.serve([list(range(1, 80))], 5)
+    assert len(eng.pool.free) == free0
+    assert eng.generate([], 3)[0] == [] and eng.serve([], 3)[0] == []
+    out, _ = eng.generate([[1, 2, 3]], 2, SamplingStrategy(topk=1000, temperature=1.0))
+    assert len(out[0]) == 2 and len(eng.pool.free) == free0
+    assert eng.generate([[1, 2, 3]], 0)[0] == [[]]

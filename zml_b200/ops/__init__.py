@@ -261,8 +261,9 @@ def topk_sample(logits, k: int, temperature: float = 1.0, seed: int = 0, step: i
     The noise of row r is a function of (seed, step, r).  `rng` (CUDA only): an int64 tensor {seed, draws so
     far} on the device that replaces `seed` and is added to `step`, so a captured CUDA graph draws fresh noise
     at every replay once the counter is advanced on the device (`advance_rng`, or the decode bookkeeping).
-    Returns tokens int32 [B] (and the sorted top-k values / indices when asked).
+    Returns tokens int32 [B] (and the sorted top-k values / indices when asked).  k is capped at the row length.
     """
+    k = min(int(k), int(logits.shape[1]))
     if not _cuda(logits):
         v, i = reference.topk(logits, k)
         if k == 1 or temperature <= 0:

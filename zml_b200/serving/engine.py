@@ -163,6 +163,8 @@ class Engine:
 
     def new_request(self, prompt: Seq[int], max_new_tokens: int) -> Request:
         r = Request(list(prompt), max_new_tokens, self._next_rid)
+        if not r.prompt:
+            raise ValueError("empty prompt: a request needs at least one token (e.g. the begin-of-text token)")
         self._next_rid += 1
         need = (len(r.prompt) + max_new_tokens + self.page_size - 1) // self.page_size
         if need > self.max_pages:
@@ -315,8 +317,17 @@ class Engine:
         stats = GenerationStats()
         if len(prompts) > self.max_batch:
             raise ValueError(f"{len(prompts)} prompts exceed max_batch={self.max_batch}")
+        if not prompts:
+            return [], stats
         launches0 = _lib.launch_count() if self.on_gpu else 0
-        reqs = [self.new_request(p, max_new_tokens) for p in prompts]
+        reqs: list[Request] = []
+        try:
+            for p in prompts:
+                reqs.append(self.new_request(p, max_new_tokens))
+        except Exception:
+            for r in reqs:                       # a request that does not fit must not strand the pages of the others
+                self.release(r)
+            raise
         stats.prompt_tokens = sum(len(p) for p in prompts)
         ev = (lambda: torch.cuda.Event(enable_timing=True)) if self.on_gpu else None
         t_host0 = time.perf_counter()
@@ -438,6 +449,12 @@ class Engine:
         stats = GenerationStats()
         n_req = len(prompts)
         budget = [int(max_new_tokens)] * n_req if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
+        for i, (p, m) in enumerate(zip(prompts, budget)):     # reject what can never run before anything is admitted
+            if len(p) == 0:
+                raise ValueError(f"prompt {i} is empty: a request needs at least one token")
+            need = (len(p) + m + self.page_size - 1) // self.page_size
+            if need > self.max_pages:
+                raise ValueError(f"prompt {i} needs {need} pages, engine allows {self.max_pages} per sequence")
         eos = set(int(e) for e in eos_ids)
         cap = min(self.max_batch, max(1, n_req))
         bb = min(_bucket(cap) if self.use_graphs else cap, self.max_batch)
