@@ -265,3 +265,20 @@ def test_top_level_names_and_fn_exe():
     assert run.call(xb).to_tensor().tolist() == [[6.0, 22.0, 38.0]] * 2
     with pytest.raises(RuntimeError):
         zml.FnExe(lambda a: a).call(xb)
+
+
+def test_bad_inputs_are_refused_with_clear_errors():
+    pl = Platform.init("cpu")
+    with pytest.raises(ValueError, match="needs 16"):
+        Buffer.from_bytes(pl, Shape((2, 2), "f32"), bytes(8))
+    exe = pl.compile(lambda x: x.add(x), [Tensor.from_shape(Shape((2,), "f32"))])
+    with pytest.raises(ValueError, match="expected 1 buffers"):
+        exe.call()
+    with pytest.raises(ValueError, match="compiled for"):
+        exe.call(Buffer.from_tensor(pl, torch.ones(3)))
+    with pytest.raises(ValueError, match="compiled for"):
+        exe.call(Buffer.from_tensor(pl, torch.ones(2, dtype=torch.int32)))
+    # gather clamps indices into the axis, like the op the reference lowers to
+    x = Tensor.from_torch(torch.arange(5.0), ["a"])
+    idx = Tensor.from_torch(torch.tensor([7, -3, 2]), ["n"])
+    assert x.gather({"a": idx}).data.tolist() == [4.0, 0.0, 2.0]

@@ -148,6 +148,9 @@ class Exe:
     def _call_flat(self, flat: Sequence[Buffer], wait: bool):
         if len(flat) != len(self.arg_shapes):
             raise ValueError(f"{self.name}: expected {len(self.arg_shapes)} buffers, got {len(flat)}")
+        for i, (b, want) in enumerate(zip(flat, self.arg_shapes)):
+            if b.shape().dims != want.dims or b.shape().dtype is not want.dtype:
+                raise ValueError(f"{self.name}: argument {i} is {b.shape()}, the program was compiled for {want}")
         with tracer.span(f"zml.exe.call#wait={wait},arg_count={len(flat)}#"):
             tensors = self._to_tensors(flat)
             self.calls += 1

@@ -24,6 +24,8 @@ class Slice:
         self.byte_strides = tuple(byte_strides) if byte_strides is not None else shape.compute_byte_strides()
         self.offset_bytes = offset_bytes
         self.mutable = mutable
+        if byte_strides is None and self.bytes.nbytes - offset_bytes < shape.byte_size():
+            raise ValueError(f"{self.bytes.nbytes - offset_bytes} bytes given, {shape} needs {shape.byte_size()}")
 
     # ------------------------------------------------------------------ constructors
     @staticmethod

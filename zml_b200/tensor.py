@@ -1116,7 +1116,8 @@ class Tensor:
         """Gathers VALUES along the given axes.  Axes of the index tensors whose tag also exists
         in self (and is not a gathered axis) are batching axes.  The index axes replace the first
         gathered axis; other gathered axes disappear:
-            gather(f[a,b,c,d], {b: ib[a,n], c: ic[a,n]})[a,n,d] = f[a, ib[a,n], ic[a,n], d]"""
+            gather(f[a,b,c,d], {b: ib[a,n], c: ic[a,n]})[a,n,d] = f[a, ib[a,n], ic[a,n], d]
+        Indices outside an axis are clamped to its ends."""
         d = self._need()
         gaxes = [self.axis(a) for a in indices]
         idxs = list(indices.values())
@@ -1135,7 +1136,8 @@ class Tensor:
             view = [1] * ishape.rank()
             view[k] = ishape.dims[k]
             index.append(torch.arange(ishape.dims[k], device=d.device).reshape(view).expand(ishape.dims))
-        index += [t._need().long() for t in idxs]
+        # out-of-range indices are clamped into the axis, as the gather the reference lowers to does
+        index += [t._need().long().clamp(0, max(self._shape.dims[g] - 1, 0)) for t, g in zip(idxs, gaxes)]
         out = src[tuple(index)]                         # idx dims ++ rest dims
         out_tags = itags + [self._shape.tags[i] for i in rest]
         # target order: self's axes, first gathered axis -> non-batch index axes
