@@ -152,3 +152,29 @@ def test_mesh_accessors_shard_slice_and_pick_sharding():
     assert pick_sharding([sh], shape) is sh
     assert pick_sharding([sh], Shape((2,), "f32"), "explicit_axis_binding") is None
     assert pick_sharding([sh], Shape((2,), "f32")) is sh
+
+
+def test_mesh_and_gspmd_annotations():
+    """Textual mesh / GSPMD forms of the same placements (zml/Sharding.zig:1395-1407, 1511-1577)."""
+    from zml_b200 import Shape
+    from zml_b200.sharding import TORUS, LogicalMesh, Partitioning, PhysicalMesh, Sharding, Strategy
+    phys = PhysicalMesh.grid((2, 2, 2), TORUS, ("link_x", "link_y", "link_z"), target="tpu")
+    logical = LogicalMesh.mesh({"batch": "low_bandwidth", "model": "high_bandwidth"})
+    s = Sharding("m", phys, logical, Strategy.parse_bindings({"batch": "link_x", "model": "link_y"}))
+    assert s.mesh_attr() == '#sdy.mesh<["link_x"=2, "link_y"=2, "link_z"=2]>'
+    shape = Shape({"batch": 4, "model": 4}, "f32").with_partitioning({"batch": "batch", "model": "model"})
+    assert s.gspmd_sharding_attr(shape) == "{devices=[2,2,2]0,1,2,3,4,5,6,7 last_tile_dim_replicate}"
+    assert s.gspmd_sharding_attr(Shape({"batch": 4}, "f32")) == "{replicated}"
+    only_model = Shape({"batch": 4, "model": 4}, "f32").with_partitioning({"model": "model"})
+    assert s.gspmd_sharding_attr(only_model) == "{devices=[1,2,4]0,1,2,3,4,5,6,7 last_tile_dim_replicate}"
+    fold = Strategy.parse_bindings({"model": "link_x"})
+    fold.add_fold("link_x", ["link_x", "link_z"])
+    f = Sharding("f", phys, LogicalMesh.mesh({"model": "high_bandwidth"}), fold)
+    assert f.physical_view() == [("link_x", 4), ("link_y", 2)] and f.mesh_attr() == '#sdy.mesh<["link_x"=4, "link_y"=2]>'
+    m16 = Shape({"model": 16}, "f32").with_partitioning({"model": "model"})
+    assert f.gspmd_sharding_attr(m16) == "{devices=[4,2]0,1,2,3,4,5,6,7 last_tile_dim_replicate}"
+    full = Sharding("all", phys, LogicalMesh.mesh({"model": "high_bandwidth"}),
+                    Strategy.parse_bindings({"model": ["link_x", "link_y", "link_z"]}))
+    assert full.gspmd_sharding_attr(m16) == "{devices=[8]0,1,2,3,4,5,6,7}"
+    assert Partitioning([s], "gspmd").sharding_attr(shape).startswith("{devices=[2,2,2]")
+    assert Partitioning([s], "shardy").sharding_attr(shape).startswith("#sdy.sharding<@m, [")

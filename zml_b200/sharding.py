@@ -491,6 +491,48 @@ class Sharding:
             s += ", replicated={" + ", ".join(f'"{r}"' for r in repl) + "}"
         return s + ">"
 
+    def physical_view(self) -> list[tuple[str, int]]:
+        """(axis, size) of the mesh as this sharding sees it: folded axes appear once, under their target name, with
+        the product of their sources' sizes (zml/Sharding.zig:1309-1393)."""
+        view_of = {src: tgt for tgt, srcs in self.strategy.folding.items() for src in srcs}
+        out: dict[str, int] = {}
+        for t, n in zip(self.physical.axis_tags, self.physical.axis_sizes):
+            v = view_of.get(t, t)
+            out[v] = out.get(v, 1) * n
+        return list(out.items())
+
+    def mesh_attr(self) -> str:
+        """`#sdy.mesh<["link_x"=2, "link_y"=2]>` (zml/Sharding.zig:1395-1407)."""
+        return "#sdy.mesh<[" + ", ".join(f'"{t}"={n}' for t, n in self.physical_view()) + "]>"
+
+    def gspmd_sharding_attr(self, shape: Shape) -> str:
+        """The same placement in GSPMD's textual form (zml/Sharding.zig:1511-1577): `{replicated}`, or
+        `{devices=[t0,t1,...]id0,id1,...}` with one tile count per tensor axis, a trailing count and
+        ` last_tile_dim_replicate` when mesh axes are left over, and the devices in canonical order."""
+        if not any(p.kind == "axis" for p in shape.partitioning):
+            return "{replicated}"
+        view = dict(self.physical_view())
+        view_of = {src: tgt for tgt, srcs in self.strategy.folding.items() for src in srcs}
+        used: list[str] = []
+        tiles = []
+        for spec in shape.partitioning:
+            n = 1
+            if spec.kind == "axis":
+                b = self.binding(spec.axis)
+                if b is None:
+                    raise MissingLogicalBinding(spec.axis)
+                for p in b:
+                    v = view_of.get(p, p)
+                    if v not in used:
+                        used.append(v)
+                        n *= view[v]
+            tiles.append(n)
+        left = math.prod(n for v, n in view.items() if v not in used)
+        if left > 1:
+            tiles.append(left)
+        ids = ",".join(str(i) for i in self.device_assignment())
+        return "{devices=[" + ",".join(str(t) for t in tiles) + "]" + ids + (" last_tile_dim_replicate" if left > 1 else "") + "}"
+
     def __repr__(self) -> str:
         return f"Sharding({self.name!r}, {self.physical}, {self.logical}, bindings={self.strategy.bindings})"
 
@@ -532,6 +574,12 @@ class Partitioning:
         return s.sharded_shape(shape) if s else shape
 
     local_shape_for_shape = local_shape         # zml/Sharding.zig:110
+
+    def sharding_attr(self, shape: Shape) -> str:
+        """The annotation of `shape` in the form of this program's partitioner: Shardy or GSPMD
+        (zml/Sharding.zig:97-108)."""
+        s = self.select_sharding(shape) or self.primary()
+        return s.gspmd_sharding_attr(shape) if self.partitioner == "gspmd" else s.sharding_attr(shape)
 
 
 def pick_sharding(shardings: Sequence[Sharding], shape: Shape, mode: str = "any_covering") -> Optional[Sharding]:
