@@ -38,6 +38,7 @@ def main(argv=None) -> int:
     suggested = Sharding("suggested", physical, logical, Strategy.suggest(logical, physical))
     part = Partitioning([suggested], args.partitioner)
     print("bindings:", suggested.strategy.bindings)
+    print("mesh:", suggested.mesh_attr())
     shapes = [Shape({"batch": 8, "seq": 16, "d": 64}, "bf16").with_partitioning({"batch": "batch"}),
               Shape({"dout": 64, "d": 64}, "bf16").with_partitioning({"dout": "model"}),
               Shape({"batch": 8, "d": 64}, "f32").with_partitioning({"batch": "batch", "d": "model"}),
@@ -45,7 +46,7 @@ def main(argv=None) -> int:
     for s in shapes:
         sh = part.select_sharding(s)
         pl = sh.placement(s)
-        print(f"\n{s}\n  {sh.sharding_attr(s)}\n  local shape {pl.shape.dims}")
+        print(f"\n{s}\n  {part.sharding_attr(s)}\n  local shape {pl.shape.dims}")
         for dev in sh.devices_in_canonical_order():
             print(f"    device {dev.id} coords={dev.coords}: {pl.slices(dev)}")
     return 0
