@@ -166,13 +166,16 @@ def test_mesh_and_gspmd_annotations():
     assert s.gspmd_sharding_attr(shape) == "{devices=[2,2,2]0,1,2,3,4,5,6,7 last_tile_dim_replicate}"
     assert s.gspmd_sharding_attr(Shape({"batch": 4}, "f32")) == "{replicated}"
     only_model = Shape({"batch": 4, "model": 4}, "f32").with_partitioning({"model": "model"})
-    assert s.gspmd_sharding_attr(only_model) == "{devices=[1,2,4]0,1,2,3,4,5,6,7 last_tile_dim_replicate}"
+    assert s.gspmd_sharding_attr(only_model) == "{devices=[1,2,4]0,1,4,5,2,3,6,7 last_tile_dim_replicate}"      # tile = link_y coordinate
     fold = Strategy.parse_bindings({"model": "link_x"})
     fold.add_fold("link_x", ["link_x", "link_z"])
     f = Sharding("f", phys, LogicalMesh.mesh({"model": "high_bandwidth"}), fold)
     assert f.physical_view() == [("link_x", 4), ("link_y", 2)] and f.mesh_attr() == '#sdy.mesh<["link_x"=4, "link_y"=2]>'
     m16 = Shape({"model": 16}, "f32").with_partitioning({"model": "model"})
-    assert f.gspmd_sharding_attr(m16) == "{devices=[4,2]0,1,2,3,4,5,6,7 last_tile_dim_replicate}"
+    # tile = 2 * x + z (the fold), the two devices of a tile differ in y: the list follows the placement
+    assert f.gspmd_sharding_attr(m16) == "{devices=[4,2]0,2,1,3,4,6,5,7 last_tile_dim_replicate}"
+    pl = f.placement(m16)
+    assert [pl.slices(d)[0][0] // 4 for d in phys.devices] == [0, 1, 0, 1, 2, 3, 2, 3]
     full = Sharding("all", phys, LogicalMesh.mesh({"model": "high_bandwidth"}),
                     Strategy.parse_bindings({"model": ["link_x", "link_y", "link_z"]}))
     assert full.gspmd_sharding_attr(m16) == "{devices=[8]0,1,2,3,4,5,6,7}"

@@ -17,6 +17,7 @@ points are explicit collectives (or fused kernels).
 """
 from __future__ import annotations
 
+import itertools
 import math
 from dataclasses import dataclass, field
 from typing import Iterable, Mapping, Optional, Sequence, Union
@@ -528,10 +529,21 @@ class Sharding:
                         n *= view[v]
             tiles.append(n)
         left = math.prod(n for v, n in view.items() if v not in used)
+        # Devices in tile order: the device list of a GSPMD annotation is read row-major over the tile grid, so it
+        # is built from the placement itself (tile index of every device per tensor axis, replicas in canonical
+        # order) - for bindings that follow the mesh order this is the canonical device list the reference prints.
+        pl = self.placement(shape)
+        by_tile: dict[tuple, list[int]] = {}
+        for dev in self.devices_in_canonical_order():
+            key = tuple(start // size if size else 0 for start, size in pl.slices(dev))
+            by_tile.setdefault(key, []).append(dev.id)
+        ids = []
+        for key in itertools.product(*[range(t) for t in tiles]):
+            ids.extend(by_tile.get(key, []))
         if left > 1:
             tiles.append(left)
-        ids = ",".join(str(i) for i in self.device_assignment())
-        return "{devices=[" + ",".join(str(t) for t in tiles) + "]" + ids + (" last_tile_dim_replicate" if left > 1 else "") + "}"
+        return ("{devices=[" + ",".join(str(t) for t in tiles) + "]" + ",".join(str(i) for i in ids)
+                + (" last_tile_dim_replicate" if left > 1 else "") + "}")
 
     def __repr__(self) -> str:
         return f"Sharding({self.name!r}, {self.physical}, {self.logical}, bindings={self.strategy.bindings})"
