@@ -23,3 +23,19 @@ def test_perfetto_protobuf_writer_round_trip(tmp_path):
     # varints longer than one byte survive (a timestamp of hours, in ns)
     n = perfetto.write_perfetto([{"ph": "X", "name": "late", "ts": 3.6e9, "dur": 1.0, "pid": 0, "tid": 0}], str(out))
     assert n == 4 and perfetto.read_perfetto(str(out))[2]["ts_ns"] == 3_600_000_000_000
+
+
+def test_tracer_enabled_and_span_names():
+    from zml_b200.profiling import tracer
+    assert not tracer.enabled()
+    tracer.start()
+    try:
+        assert tracer.enabled()
+        with tracer.span("zml.exe.call", wait=True, arg_count=3):
+            pass
+        assert tracer.count() >= 1
+    finally:
+        tracer.stop()
+    assert not tracer.enabled()
+    assert tracer.format_span_name("zml.exe.call", wait=True, arg_count=3) == "zml.exe.call#wait=True,arg_count=3#"
+    assert tracer.format_span_name("plain") == "plain"

@@ -45,8 +45,20 @@ def encode(name: str, **metadata) -> str:
     return name + "#" + ",".join(f"{k}={v}" for k, v in metadata.items()) + "#"
 
 
+format_span_name = encode           # the reference's name for it (zml/profiling/tracer.zig:63)
+
+_recording = False
+
+
+def enabled() -> bool:
+    """True while a recording session is open (zml/profiling/tracer.zig:35): callers use it to skip building span
+    metadata that nobody would record."""
+    return _recording
+
+
 def start(capacity: int = 1 << 20) -> None:
-    global _fallback_on
+    global _fallback_on, _recording
+    _recording = True
     l = _load()
     if l:
         l.zbh_trace_start(capacity)
@@ -56,7 +68,8 @@ def start(capacity: int = 1 << 20) -> None:
 
 
 def stop() -> None:
-    global _fallback_on
+    global _fallback_on, _recording
+    _recording = False
     l = _load()
     if l:
         l.zbh_trace_stop()
