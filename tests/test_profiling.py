@@ -1,5 +1,6 @@
 """Trace post-processing: the native Perfetto (protobuf) writer against its own decoder."""
 import json
+import os
 
 
 def test_perfetto_protobuf_writer_round_trip(tmp_path):
@@ -39,3 +40,15 @@ def test_tracer_enabled_and_span_names():
     assert not tracer.enabled()
     assert tracer.format_span_name("zml.exe.call", wait=True, arg_count=3) == "zml.exe.call#wait=True,arg_count=3#"
     assert tracer.format_span_name("plain") == "plain"
+
+
+def test_profiler_session_writes_host_trace_and_perfetto_file(tmp_path):
+    from zml_b200.profiling import Profiler, perfetto, tracer
+    with Profiler(logdir=str(tmp_path), device=False, session="s1") as prof:
+        with tracer.span("step", n=1):
+            with tracer.span("inner"):
+                pass
+    assert os.path.isfile(prof.host_trace) and prof.dir.endswith(os.path.join("plugins", "profile", "s1"))
+    recs = perfetto.read_perfetto(prof.perfetto_trace)
+    names = [r.get("name") for r in recs if r.get("kind") == "event" and r.get("type") == 1]
+    assert any(n and n.startswith("step") for n in names) and "inner" in names

@@ -2,8 +2,8 @@
 
 `Profiler` is the session object behind `llm --profile` (examples/llm/chat.zig:74-93):
 it records host spans with the native tracer and, on CUDA, device activity through
-`torch.profiler` (CUPTI), and writes a Chrome / Perfetto trace under
-`<logdir>/plugins/profile/<session>/`.  Setting SKIP_DEVICE_PROFILER=1 keeps only the host
+`torch.profiler` (CUPTI), and writes trace-event JSON files plus one merged native Perfetto trace
+(`profiling.pftrace`) under `<logdir>/plugins/profile/<session>/`.  Setting SKIP_DEVICE_PROFILER=1 keeps only the host
 spans, which is what an external profiler wrapper wants (the reference's SKIP_PJRT_PROFILER).
 """
 from __future__ import annotations
@@ -48,6 +48,16 @@ class Profiler:
             self._tp = None
         tracer.stop()
         tracer.write_json(self.host_trace)
+        try:                                    # one file for ui.perfetto.dev: host spans and device activity merged
+            from . import perfetto
+            merged = os.path.join(self.dir, "profiling.merged.json")
+            perfetto.merge_traces(self.host_trace, out.get("device"), merged)
+            self.perfetto_trace = os.path.join(self.dir, "profiling.pftrace")
+            perfetto.write_perfetto(perfetto._events(merged), self.perfetto_trace)
+            os.remove(merged)
+            out["perfetto"] = self.perfetto_trace
+        except (OSError, ValueError, KeyError):
+            pass
         return out
 
     def __enter__(self):
