@@ -10,10 +10,9 @@ cached tokens per sequence.  Prints, on rank 0, the whole layer, its GEMMs + col
 ZB_FOLD_NORMS=0 times the layer with separate RMSNorm and SwiGLU kernels instead of the GEMM epilogues.
 """
 
-import os, sys, torch, ctypes
+import os, sys, torch
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from zml_b200 import ops
-from zml_b200.ops import _lib
 from zml_b200.models.llama import AttnMeta, LlamaConfig, LlamaModel, PRESETS
 from zml_b200.parallel.comm import Comm
 from zml_b200.parallel.symm import SymmetricContext

@@ -15,7 +15,6 @@ import os
 import sys
 import time
 from dataclasses import dataclass
-from typing import Optional
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from zml_b200 import safetensors
-from zml_b200.vfs import HfBackend, HttpBackend, Vfs
+from zml_b200.vfs import HfBackend, Vfs
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 

@@ -3,7 +3,7 @@ slices must match; the annotation string uses the same Shardy spelling."""
 import pytest
 
 from zml_b200.shape import Shape
-from zml_b200.sharding import (GRID, P2P, TORUS, IncompatibleSharding, LogicalMesh, MissingLogicalBinding,
+from zml_b200.sharding import (P2P, TORUS, IncompatibleSharding, LogicalMesh, MissingLogicalBinding,
                                Partitioning, PhysicalMesh, Sharding, Strategy, shardable_dim)
 
 

@@ -7,7 +7,7 @@ so that later calls pass only the remaining ones.
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Optional, Sequence
+from typing import Callable, Optional, Sequence
 
 import torch
 

@@ -12,7 +12,7 @@ import json
 import os
 from dataclasses import dataclass, field
 from enum import Enum
-from typing import Any, Optional, Union
+from typing import Optional, Union
 
 import torch
 

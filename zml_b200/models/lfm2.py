@@ -14,7 +14,6 @@ across ranks the way attention heads are.
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 from typing import Optional
 

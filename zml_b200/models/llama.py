@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import os
 
-import math
 from dataclasses import dataclass, field
 from typing import Optional
 

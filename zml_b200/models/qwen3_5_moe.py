@@ -20,7 +20,6 @@ import torch
 
 from .. import moe, ops
 from ..parallel.comm import Comm
-from . import common
 from .llama import LayerWeights
 from .qwen3_5 import PRESETS as _DENSE_PRESETS, Qwen35Config, Qwen35Model
 

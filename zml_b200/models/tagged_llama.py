@@ -17,7 +17,6 @@ Prefill only (whole sequences, causal attention, no KV cache): the serving path 
 """
 from __future__ import annotations
 
-from typing import Optional
 
 import torch
 

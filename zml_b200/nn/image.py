@@ -13,7 +13,7 @@ Not on the LLM path; plain tensor ops on whichever device holds the image.
 """
 from __future__ import annotations
 
-from typing import Mapping, Optional, Sequence, Union
+from typing import Mapping, Sequence, Union
 
 import torch
 
@@ -36,10 +36,11 @@ def nearest(x: Tensor, scale_factor: Union[Sequence[float], Mapping]) -> Tensor:
         ratio = torch.tensor(d.shape[ax] / n, dtype=torch.float32)
         idx = ((torch.arange(n, dtype=torch.float32) + 0.5) * ratio).floor().to(torch.int64).clamp_(0, d.shape[ax] - 1)
         d = d.index_select(ax, idx.to(d.device))
-    return Tensor(d, x.shape().set_dims({ax: n for ax, n in targets.items()}) if hasattr(x.shape(), "set_dims") else _with_dims(x, d))
+    return Tensor(d, _with_dims(x, d))
 
 
-def _with_dims(x: Tensor, d: torch.Tensor) -> Tensor:
+def _with_dims(x: Tensor, d: torch.Tensor):
+    """x's shape (dtype, tags) with the dims of `d`."""
     from ..shape import Shape
     s = x.shape()
     return Shape(list(d.shape), s.dtype, s.tags)

@@ -3,7 +3,6 @@ strategy with runtime top_k / temperature / top_p / min_p."""
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
 
 import torch
 

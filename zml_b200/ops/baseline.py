@@ -9,7 +9,6 @@ hand-written kernels inside `zml_b200.ops`; nothing here is used by the product 
 """
 from __future__ import annotations
 
-import math
 
 import torch
 

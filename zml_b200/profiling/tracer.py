@@ -9,7 +9,6 @@ from __future__ import annotations
 import contextlib
 import ctypes as C
 import time
-from typing import Optional
 
 _lib = None
 _fallback_events: list = []

@@ -17,8 +17,7 @@ import json
 import os
 import struct
 from dataclasses import dataclass
-from pathlib import Path
-from typing import Iterable, Mapping, Optional, Sequence
+from typing import Mapping, Optional, Sequence
 
 import numpy as np
 import torch

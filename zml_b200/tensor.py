@@ -23,7 +23,7 @@ import torch
 
 from .dtype import DataType
 from . import spmd as _spmd
-from .shape import AUTO, Axis, PartitionSpec, Shape, _parse_dims
+from .shape import Axis, PartitionSpec, Shape
 
 _ids = itertools.count(1)
 Scalar = Union[int, float, bool]
