@@ -44,6 +44,21 @@ def test_reduce_window_is_max_pool():
     torch.testing.assert_close(y.to_torch(), torch.nn.functional.max_pool2d(x, 2))
 
 
+def test_reduce_window_padding_and_dilations():
+    """A windowed sum with padding, a dilated window and a dilated base against a convolution with ones."""
+    x = torch.arange(1.0, 8.0)[None]                                            # [1, 7]
+    add = lambda a, b: (a[0].add(b[0]),)
+    zero = T(torch.tensor(0.0))
+    (y,) = ops.reduce_window([T(x)], [zero], ops.ReduceWindowOpts([1, 3], [1, 2], None, [1, 2], [(0, 0), (1, 1)]), add)
+    ref = torch.nn.functional.conv1d(x[None], torch.ones(1, 1, 3), stride=2, padding=1, dilation=2)[0]
+    torch.testing.assert_close(y.to_torch(), ref)
+    # base dilation 2: 1 _ 2 _ 3 ... (holes hold the init value), then windows of 3
+    (z,) = ops.reduce_window([T(x)], [zero], ops.ReduceWindowOpts([1, 3], [1, 1], [1, 2], None, None), add)
+    holes = torch.zeros(1, 13)
+    holes[:, ::2] = x
+    torch.testing.assert_close(z.to_torch(), torch.nn.functional.conv1d(holes[None], torch.ones(1, 1, 3))[0])
+
+
 def test_sort_by_key_and_by_comparator():
     torch.manual_seed(1)
     k = torch.randn(3, 9)

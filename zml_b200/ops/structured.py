@@ -121,12 +121,16 @@ def reduce_window(inputs: Sequence[Tensor], inits: Sequence[Tensor], opts: Reduc
     strides = list(opts.window_strides or [1] * r)
     wdil = list(opts.window_dilations or [1] * r)
     pad = list(opts.padding or [(0, 0)] * r)
-    if opts.base_dilations and any(d != 1 for d in opts.base_dilations):
-        raise NotImplementedError("base dilation")
+    bdil = list(opts.base_dilations or [1] * r)
     views = []
     for t, init in zip(inputs, inits):
         x = t.to_torch()
         fill = init.to_torch().item()
+        if any(b != 1 for b in bdil):
+            # base dilation: b - 1 holes holding the init value between neighbouring elements of an axis
+            holes = torch.full([(n - 1) * b + 1 if n > 0 else 0 for n, b in zip(x.shape, bdil)], fill, dtype=x.dtype, device=x.device)
+            holes[tuple(slice(None, None, b) for b in bdil)] = x
+            x = holes
         flat_pad = []
         for lo, hi in reversed(pad):
             flat_pad += [lo, hi]
