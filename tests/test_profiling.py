@@ -52,3 +52,30 @@ def test_profiler_session_writes_host_trace_and_perfetto_file(tmp_path):
     recs = perfetto.read_perfetto(prof.perfetto_trace)
     names = [r.get("name") for r in recs if r.get("kind") == "event" and r.get("type") == 1]
     assert any(n and n.startswith("step") for n in names) and "inner" in names
+
+
+def test_trace_viewer_finds_the_session_and_serves_it_with_cors(tmp_path, capsys):
+    import threading
+    import urllib.request
+    from zml_b200.profiling import Profiler, tracer, view
+    for name in ("old", "new"):
+        with Profiler(logdir=str(tmp_path), device=False, session=name):
+            with tracer.span(f"work_{name}"):
+                pass
+        os.utime(os.path.join(str(tmp_path), "plugins", "profile", name), (1000 if name == "old" else 2000,) * 2)
+    found = view.sessions(str(tmp_path))
+    assert [os.path.basename(s) for s in found] == ["old", "new"]
+    assert view.pick_trace(found[-1]).endswith("profiling.pftrace")
+    assert view.main([str(tmp_path), "--no-serve"]) == 0
+    out = capsys.readouterr().out
+    assert "session new" in out and "work_new" in out and "work_old" not in out
+    assert view.main([str(tmp_path), "--no-serve", "--session=old"]) == 0 and "work_old" in capsys.readouterr().out
+    assert view.main([str(tmp_path / "nothing"), "--no-serve"]) == 1
+    srv = view.make_server(found[-1], 0)
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    try:
+        with urllib.request.urlopen(f"http://127.0.0.1:{srv.server_address[1]}/profiling.pftrace") as r:
+            assert r.headers["Access-Control-Allow-Origin"] == "https://ui.perfetto.dev" and len(r.read()) > 0
+    finally:
+        srv.shutdown()
+        srv.server_close()
