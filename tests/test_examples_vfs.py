@@ -304,9 +304,36 @@ def test_s3_gcs_and_hub_backends_against_a_local_server(tmp_path):
         assert GcsBackend({"GCS_METADATA_URL": base + "/nope"}, endpoint=base).token() is None     # no metadata server: anonymous
 
         vfs.register("hf", HfBackend(endpoint=base))
+        # mirror the repository: every file once, nothing fetched twice, a suffix filter
+        from zml_b200.vfs import download
+        dest = tmp_path / "mirror"
+        files, total = download(vfs, "hf://org/repo", str(dest), log=lambda *_: None)
+        assert files == 4 and total == sum(len(v) for v in FakeCloud.objects.values())
+        assert (dest / "ckpt" / "sub" / "config.json").read_bytes() == b"{}"
+        assert (dest / "ckpt" / "model-00001.safetensors").read_bytes() == bytes(range(200))
+        assert download(vfs, "hf://org/repo", str(dest), log=lambda *_: None) == (0, 0)
+        assert download(vfs, "s3://bkt/ckpt", str(tmp_path / "m2"), only=(".json",), log=lambda *_: None)[0] == 1
+        assert download(vfs, "gs://bkt/other.bin", str(tmp_path / "m3"), log=lambda *_: None) == (1, 1)
         assert vfs.list("hf://org/repo/ckpt") == ["model-00001.safetensors", "model-00002.safetensors", "sub/"]
         assert vfs.list("hf://org/repo") == ["ckpt/", "other.bin"]
         assert vfs.stat("hf://org/repo/ckpt").kind == "directory" and vfs.stat("hf://org/repo/other.bin").size == 1
     finally:
         srv.shutdown()
         srv.server_close()
+
+
+def test_token_commands_never_print_the_token(tmp_path, monkeypatch, capsys):
+    from zml_b200 import vfs
+    monkeypatch.setenv("HF_HOME", str(tmp_path))
+    monkeypatch.delenv("HF_TOKEN", raising=False)
+    assert vfs._auth_main(["auth", "whoami"]) == 0 and "none" in capsys.readouterr().out
+    assert vfs._auth_main(["auth", "login", "--token=hf_secret_value"]) == 0
+    capsys.readouterr()
+    assert vfs.hf_token() == "hf_secret_value" and oct(os.stat(vfs.hf_token_path()).st_mode & 0o777) == "0o600"
+    assert vfs._auth_main(["auth", "whoami"]) == 0
+    out = capsys.readouterr().out
+    assert "hf_sec" not in out and str(tmp_path) in out
+    monkeypatch.setenv("HF_TOKEN", "hf_other")
+    assert vfs._auth_main(["auth", "whoami"]) == 0 and "HF_TOKEN" in capsys.readouterr().out
+    assert vfs._auth_main(["auth", "logout"]) == 0 and not os.path.exists(vfs.hf_token_path())
+    assert vfs._auth_main(["bogus"]) == 1

@@ -557,9 +557,57 @@ class VfsFile(io.RawIOBase):
         return data
 
 
+def download(vfs: "Vfs", uri: str, dest: str, only: Optional[tuple] = None, log=print) -> tuple[int, int]:
+    """Mirrors a remote directory (a hub repository, a bucket prefix) or one file into `dest`: walks the listing,
+    skips files already present with the right size, streams the others with parallel range requests.  `only`:
+    file-name suffixes to keep (e.g. (".json", ".safetensors")).  Returns (files copied, bytes copied).  The reference
+    fetches repositories with a Bazel rule (bazel/huggingface.bzl); this is its command-line counterpart."""
+    uri = uri.rstrip("/")
+    try:
+        kind = vfs.stat(uri).kind
+    except OSError:
+        kind = "directory"
+    todo: list[tuple[str, str]] = []
+    if kind == "file":
+        todo.append((uri, os.path.join(dest, uri.rsplit("/", 1)[1])))
+    else:
+        stack = [""]
+        while stack:
+            sub = stack.pop()
+            for name in vfs.list(f"{uri}/{sub}".rstrip("/")):
+                rel = f"{sub}{name}"
+                if name.endswith("/"):
+                    stack.append(rel)
+                elif only is None or rel.endswith(tuple(only)):
+                    todo.append((f"{uri}/{rel}", os.path.join(dest, rel)))
+    files = total = 0
+    for src, dst in sorted(todo):
+        size = vfs.stat(src).size
+        if os.path.isfile(dst) and os.path.getsize(dst) == size:
+            log(f"have  {dst}")
+            continue
+        os.makedirs(os.path.dirname(dst) or ".", exist_ok=True)
+        tmp = dst + ".part"
+        n = vfs.copy(src, tmp)
+        os.replace(tmp, dst)
+        files, total = files + 1, total + n
+        log(f"fetch {dst} ({n} bytes)")
+    return files, total
+
+
 def _auth_main(argv) -> int:
-    """`python -m zml_b200.vfs auth login [--token=...]` / `auth logout` / `auth whoami`."""
+    """`python -m zml_b200.vfs auth login [--token=...]` / `auth logout` / `auth whoami`
+    `python -m zml_b200.vfs download <uri> <dir> [--only=.json,.safetensors]`     mirror a repository or a prefix
+    `python -m zml_b200.vfs ls <uri>`"""
     import getpass
+    if len(argv) >= 3 and argv[0] == "download":
+        only = next((tuple(a.split("=", 1)[1].split(",")) for a in argv[3:] if a.startswith("--only=")), None)
+        files, total = download(Vfs.default(), argv[1], argv[2], only)
+        print(f"{files} file(s), {total / 2 ** 20:.1f} MiB copied to {argv[2]}")
+        return 0
+    if len(argv) == 2 and argv[0] == "ls":
+        print("\n".join(Vfs.default().list(argv[1])))
+        return 0
     if len(argv) < 2 or argv[0] != "auth" or argv[1] not in ("login", "logout", "whoami"):
         print(_auth_main.__doc__, file=sys.stderr)
         return 1
@@ -570,8 +618,12 @@ def _auth_main(argv) -> int:
         print("logged out")
         return 0
     if argv[1] == "whoami":
-        tok = hf_token()
-        print("token: " + (tok[:6] + "..." if tok else "none"))
+        if os.environ.get("HF_TOKEN"):
+            print("token: from the HF_TOKEN environment variable")
+        elif hf_token():
+            print(f"token: from {path}")
+        else:
+            print("token: none")
         return 0
     tok = next((a.split("=", 1)[1] for a in argv[2:] if a.startswith("--token=")), None) or getpass.getpass("HF token: ")
     os.makedirs(os.path.dirname(path), exist_ok=True)
@@ -583,5 +635,4 @@ def _auth_main(argv) -> int:
 
 
 if __name__ == "__main__":
-    import sys
     sys.exit(_auth_main(sys.argv[1:]))
