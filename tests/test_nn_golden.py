@@ -140,3 +140,34 @@ def test_fixup_logits_for_dynamic_sampling():                       # zml/nn.zig
     # a bound on top_k known ahead of time ranks only that many candidates
     x, idx = nn.fixup_logits(logits, nn.DynamicSamplingStrategy(top_k=2, max_top_k=3))
     assert idx.data.tolist() == [2, 3, 0] and torch.allclose(x.data, torch.tensor([l4, l3, ninf]))
+
+
+def test_collect_dims():                                            # zml/nn.zig:2297-2340
+    from zml_b200 import Shape
+    import pytest
+    mk = lambda xb, yb, bias: {"x": Shape((xb, 5), "f32", ("b", "d")), "y": Shape((yb, 5), "f32", ("b", "d")),
+                               "bias": Shape((bias,), "f32", ("d",))}
+    assert nn.collect_dims(("b", "d"), mk(2, 2, 5), "strict") == {"b": 2, "d": 5}
+    with pytest.raises(ValueError):
+        nn.collect_dims(("b", "d"), mk(2, 3, 5), "strict")
+    assert nn.collect_dims(("b", "d"), mk(2, 3, 5), "ignore_errors") == {"b": nn.DIM_MISMATCH, "d": 5}
+    with pytest.raises(KeyError):
+        nn.collect_dims(("b", "d", "c"), mk(2, 2, 5), "strict")
+    assert nn.collect_dims(("b", "d", "c"), mk(2, 2, 5), "ignore_errors") == {"b": 2, "d": 5, "c": nn.NOT_SET}
+    with pytest.raises(ValueError):
+        nn.collect_dims(("b", "d"), mk(2, 2, 7), "strict")
+    assert nn.collect_dims(("b", "d"), mk(2, 2, 7), "ignore_errors") == {"b": 2, "d": nn.DIM_MISMATCH}
+    # tensors count as their shapes
+    t = Tensor.from_torch(torch.zeros(4, 6), ["s", "d"])
+    assert nn.collect_dims(("s", "d"), [t, {"w": t}]) == {"s": 4, "d": 6}
+
+
+def test_elu_and_tagged_nvfp4_unpack():
+    x = Tensor.from_torch(torch.tensor([-1.0, 0.0, 2.0]))
+    want = torch.tensor([0.5 * (torch.exp(torch.tensor(-1.0)) - 1), 0.0, 2.0])
+    assert torch.allclose(nn.elu(x, 0.5).data, want) and torch.allclose(nn.Activation.elu.forward(x, alpha=0.5).data, want)
+    packed = Tensor.from_torch(torch.tensor([[0x21, 0xF7], [0x80, 0x3C]], dtype=torch.uint8), ["dout", "kw"])
+    codes = nn.unpack_nvfp4(packed, "d")
+    assert codes.shape().tags == ("dout", "d") and codes.shape().dims == (2, 4) and codes.dtype().value == "f4e2m1"
+    assert codes.data.tolist() == [[1, 2, 7, 15], [0, 8, 12, 3]]                 # low nibble first
+    assert codes.convert("f32").data.tolist() == [[0.5, 1.0, 6.0, -6.0], [0.0, -0.0, -2.0, 1.5]]

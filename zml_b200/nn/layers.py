@@ -109,12 +109,53 @@ class Activation(enum.Enum):
     gelu = "gelu"
     quick_gelu = "quick_gelu"
 
-    def forward(self, x: Tensor, slope: float = 0.01) -> Tensor:
+    def forward(self, x: Tensor, slope: float = 0.01, alpha: float = 1.0) -> Tensor:
+        """`slope` is the parameter of leaky_relu, `alpha` of elu (the payloads of the reference's union,
+        zml/nn.zig:439-461)."""
         if self is Activation.leaky_relu:
             return x.leaky_relu(slope)
         if self is Activation.elu:
-            return x._like(torch.nn.functional.elu(x.data))
+            return elu(x, alpha)
         return getattr(x, self.value)()
+
+
+def elu(x: Tensor, alpha: float = 1.0) -> Tensor:
+    """x where x >= 0, alpha * (exp(x) - 1) elsewhere (zml/nn.zig:463-468)."""
+    return x._like(torch.nn.functional.elu(x.data, alpha))
+
+
+NOT_SET, DIM_MISMATCH = -2, -1
+
+
+def collect_dims(dims, tree, mode: str = "strict") -> dict:
+    """The size of each named axis across every Shape / Tensor of a model tree (zml/nn.zig:2243-2295): {tag: size}.
+    `strict`: an axis that is absent raises KeyError, one that differs between tensors ValueError; `ignore_errors`
+    returns NOT_SET (-2) / DIM_MISMATCH (-1) in their place instead."""
+    from .. import meta
+    from ..shape import Shape
+    if mode not in ("strict", "allow_extra_dims", "ignore_errors"):
+        raise ValueError(f"unknown mode {mode!r}")
+    res = {d: NOT_SET for d in dims}
+
+    def see(leaf, _path):
+        shape = leaf.shape() if isinstance(leaf, Tensor) else leaf
+        for d in dims:
+            ax = shape.has_tag(d)
+            if ax is None:
+                continue
+            n = shape.dims[ax]
+            if res[d] == NOT_SET:
+                res[d] = n
+            elif res[d] != DIM_MISMATCH and res[d] != n:
+                res[d] = DIM_MISMATCH
+    meta.visit(see, tree, lambda v: isinstance(v, (Shape, Tensor)))
+    if mode != "ignore_errors":
+        for d, n in res.items():
+            if n == NOT_SET:
+                raise KeyError(f"axis not found: {d}")
+            if n == DIM_MISMATCH:
+                raise ValueError(f"axis {d} has different sizes across the tensors")
+    return res
 
 
 def normalize_variance(x: Tensor, eps: float, ax="d") -> Tensor:

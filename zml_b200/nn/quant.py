@@ -150,3 +150,17 @@ def per_token_group_quant_fp8(x: torch.Tensor, group: int = 128):
     scale = (g.abs().amax(-1) / 448.0).clamp_min(1e-10)
     q = (g / scale[..., None]).clamp(-448, 448).to(torch.float8_e4m3fn)
     return q.reshape(x.shape), scale
+
+
+def unpack_nvfp4(w, k_tag: str):
+    """Tagged form of `unpack_e2m1` (zml/nn.zig:232-239): `w` is a u8 Tensor whose packed axis is tagged `kw`; the
+    result holds one e2m1 code per entry (dtype f4e2m1, low nibble first) with that axis twice as long and renamed
+    to `k_tag`."""
+    from ..shape import Shape
+    from ..tensor import Tensor
+    if w.dtype() is not DataType.u8:
+        raise ValueError(f"unpack_nvfp4 expects packed u8 weights, got {w.dtype()}")
+    a = w.axis("kw")
+    codes = unpack_e2m1(w.data.movedim(a, -1)).movedim(-1, a)
+    tags = tuple(k_tag if i == a else t for i, t in enumerate(w.shape().tags))
+    return Tensor(codes, Shape(tuple(codes.shape), DataType.f4e2m1, tags))
