@@ -186,3 +186,37 @@ def test_serving_model_attention_backends_agree():
     finally:
         attnd.deinit()
         d.stop()
+
+
+def _reference_cases():
+    """(q dims, k dims, token indices) of the reference's dispatcher tests (zml/attention.zig:193-240)."""
+    return [({"q": 1, "h": 64, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [63]),
+            ({"q": 1, "h": 64, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [36]),
+            ({"b": 4, "q": 1, "h": 64, "hd": 64}, {"b": 4, "k": 64, "h": 8, "hd": 64}, [63, 63, 63, 63]),
+            ({"b": 4, "q": 1, "h": 64, "hd": 64}, {"b": 4, "k": 64, "h": 8, "hd": 64}, [61, 57, 23, 63]),
+            ({"q": 1, "h": 8, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [62]),
+            ({"q": 1, "h": 8, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [63]),
+            ({"q": 8, "h": 64, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [56])]
+
+
+@pytest.mark.parametrize("case", range(7))
+def test_vanilla_backend_on_the_reference_cases(case):
+    """The dispatcher's vanilla path against a plain causal attention, with and without a batch axis."""
+    qd, kd, tok = _reference_cases()[case]
+    torch.manual_seed(case)
+    q, k, v = torch.randn(*qd.values()), torch.randn(*kd.values()), torch.randn(*kd.values())
+    be = att.Backend.vanilla
+    out = att.attention(Tensor(q, Shape(qd)), Tensor(k, Shape(kd)), Tensor(v, Shape(kd)),
+                        torch.tensor(tok) if "b" in qd else tok[0], att.Metadata.from_backend(be, 64, qd["h"]),
+                        att.Parameters.from_backend(be))
+    assert out.shape().tags == tuple(qd) and out.shape().dims == tuple(qd.values())
+    if "b" in qd:
+        want = torch.stack([_dense_causal(q[i], k[i], v[i], tok[i]) for i in range(qd["b"])])
+    else:
+        want = _dense_causal(q, k, v, tok[0])
+    torch.testing.assert_close(out.to_torch(), want, atol=1e-5, rtol=1e-5)
+    with pytest.raises(ValueError):
+        att.attention(Tensor(torch.randn(2, 1, 8, 16), Shape({"b": 2, "q": 1, "h": 8, "hd": 16})),
+                      Tensor(torch.randn(2, 4, 8, 16), Shape({"b": 2, "k": 4, "h": 8, "hd": 16})),
+                      Tensor(torch.randn(2, 4, 8, 16), Shape({"b": 2, "k": 4, "h": 8, "hd": 16})),
+                      torch.tensor([1, 2, 3]), att.Metadata.from_backend(be, 4, 8), att.Parameters.from_backend(be))

@@ -48,3 +48,25 @@ def test_paged_api_b200_matches_reference_backend():
         o = paged.paged_attention(p, Tensor(q, Shape({"b": q.shape[0], "h": hq, "hd": hd}, "bf16")), None, None, cache)
         outs.append(o.to_torch().float())
     expect_close(outs[0], outs[1], atol=2e-2, rtol=2e-2, min_close=0.999)
+
+
+@pytest.mark.parametrize("qd,kd,tok", [
+    ({"q": 1, "h": 64, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [36]),
+    ({"b": 4, "q": 1, "h": 64, "hd": 64}, {"b": 4, "k": 64, "h": 8, "hd": 64}, [61, 57, 23, 63]),
+    ({"q": 1, "h": 8, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [62]),
+    ({"q": 8, "h": 64, "hd": 64}, {"k": 64, "h": 8, "hd": 64}, [56]),
+])
+def test_b200_backend_matches_vanilla_on_the_reference_cases(qd, kd, tok):
+    """The shapes of the reference's dispatcher tests (zml/attention.zig:193-240) with its tolerances."""
+    torch.manual_seed(len(tok) + qd["h"])
+    q = torch.randn(*qd.values(), device="cuda").bfloat16()
+    k = torch.randn(*kd.values(), device="cuda").bfloat16()
+    v = torch.randn(*kd.values(), device="cuda").bfloat16()
+    token_index = torch.tensor(tok, device="cuda") if "b" in qd else tok[0]
+    outs = []
+    for be in (att.Backend.b200, att.Backend.vanilla):
+        o = att.attention(Tensor(q, Shape(qd, "bf16")), Tensor(k, Shape(kd, "bf16")), Tensor(v, Shape(kd, "bf16")), token_index,
+                          att.Metadata.from_backend(be, 64, qd["h"]), att.Parameters.from_backend(be))
+        assert o.shape().dims == tuple(qd.values())
+        outs.append(o.to_torch().float())
+    expect_close(outs[0], outs[1], atol=5e-3, rtol=1e-2, min_close=0.99)

@@ -156,8 +156,31 @@ def _flash(q: Tensor, k: Tensor, v: Tensor, token_index, params: FlashParameters
     return Tensor(o, q.transpose(("q", "h", "hd")).shape()).transpose(q.shape().tags)
 
 
+def _token_indices(token_index, batch: int) -> list[int]:
+    if isinstance(token_index, Tensor):
+        token_index = token_index.to_torch()
+    if torch.is_tensor(token_index):
+        vals = [int(x) for x in token_index.reshape(-1).tolist()]
+    elif isinstance(token_index, (list, tuple)):
+        vals = [int(x) for x in token_index]
+    else:
+        vals = [int(token_index)]
+    if len(vals) == 1:
+        vals = vals * batch
+    if len(vals) != batch:
+        raise ValueError(f"token_index has {len(vals)} entries for a batch of {batch}")
+    return vals
+
+
 def attention(q: Tensor, k: Tensor, v: Tensor, token_index, metadata: Metadata, parameters: Parameters) -> Tensor:
-    """Causal attention of q {q, h, hd} at positions token_index.. over k, v {k, h, hd}."""
+    """Causal attention of q {q, h, hd} at positions token_index.. over k, v {k, h, hd}.  With a leading batch axis
+    `b` on q, k and v, `token_index` holds one position per batch entry (or one for all), as in the reference
+    (zml/attention.zig:172-191, its tests use b = 4 with different positions)."""
+    if q.shape().has_tag("b") is not None:
+        nb = q.dim("b")
+        outs = [attention(q.choose1d("b", i), k.choose1d("b", i), v.choose1d("b", i), t, metadata, parameters)
+                for i, t in enumerate(_token_indices(token_index, nb))]
+        return Tensor.stack(outs, q.axis("b"), "b")
     be = parameters.backend
     if be is Backend.vanilla:
         return _vanilla(q, k, v, token_index)
