@@ -52,7 +52,7 @@ class CudaOptions:
 class CreateOptions:
     cpu: CpuOptions = field(default_factory=CpuOptions)
     cuda: CudaOptions = field(default_factory=CudaOptions)
-    physical_mesh: Optional[PhysicalMesh] = None     # custom mesh (tests build 2x2 / 2x2x2 tori)
+    physical_mesh: Optional[object] = None     # a PhysicalMesh, or fn(target name, device count) -> PhysicalMesh
 
 
 @dataclass
@@ -114,7 +114,10 @@ class Platform:
             n = self.options.cpu.device_count
         if n & (n - 1):
             raise ValueError(f"device count must be a power of two, got {n}")
-        self.physical_mesh = self.options.physical_mesh or PhysicalMesh.auto(target.value, n)
+        custom = self.options.physical_mesh
+        if callable(custom) and not isinstance(custom, PhysicalMesh):
+            custom = custom(target.value, n)        # the reference's `.custom = fn(target, devices)` (zml/platform.zig:696-705)
+        self.physical_mesh = custom or PhysicalMesh.auto(target.value, n)
         if self.physical_mesh.num_devices() != n:
             raise ValueError("custom physical mesh does not match the device count")
         self.devices: list[DeviceInfo] = []
