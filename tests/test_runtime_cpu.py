@@ -224,3 +224,32 @@ def test_decode_split_planner_splits_only_when_pairs_are_few():
         assert mc == 1 or (s + mc - 1) // mc >= 64              # chunks are at least a page
     # more pairs never ask for more chunks at the same context
     assert plan(2, 8, 8192) >= plan(8, 8, 8192) >= plan(64, 8, 8192)
+
+
+def test_loader_handles_scalars_empty_tensors_many_tiny_ones_and_a_small_ring(tmp_path):
+    """A checkpoint with a scalar, a zero-size tensor, 200 five-element tensors, several dtypes and one tensor far larger
+    than the staging ring (3 chunks of 64 KiB) loads byte-exactly; the large one arrives sharded."""
+    import os
+    import torch
+    from zml_b200 import safetensors
+    from zml_b200.io import Loader, TensorStore
+    from zml_b200.platform import CpuOptions, CreateOptions, Platform, Target
+    from zml_b200.sharding import LogicalMesh
+    torch.manual_seed(0)
+    w = {"scalar": torch.tensor(3.5), "empty": torch.zeros(0, 4), "tiny": torch.arange(3, dtype=torch.int8),
+         "big": torch.randn(300, 1000), "bf": torch.randn(64, 64).bfloat16(), "bool": torch.tensor([True, False, True])}
+    w.update({f"m{i}": torch.full((5,), float(i)) for i in range(200)})
+    safetensors.save_file(w, os.path.join(str(tmp_path), "model.safetensors"))
+    store = TensorStore.from_path(str(tmp_path))
+    pl = Platform.init(Target.cpu, CreateOptions(cpu=CpuOptions(4)))
+    tp = pl.register_sharding("tp", LogicalMesh({"model": "high_bandwidth"}))
+    view = store.view()
+    model = {k: view.create_tensor(k) for k in w}
+    model["big"] = view.create_tensor("big", ("dout", "d"), {"dout": "model"})
+    loader = Loader(pl, parallelism=4, dma_chunk_size=64 << 10, dma_chunks=3)
+    bufs = loader.load(model, store, [tp])
+    st = loader.stats()
+    loader.close()
+    assert all(torch.equal(bufs[k].to_tensor(), w[k]) for k in w)
+    assert bufs["big"].local().shape == (75, 1000) and bufs["scalar"].get_value() == 3.5
+    assert st["staging_bytes"] == 3 * (64 << 10) and st["bytes_loaded"] >= sum(t.numel() * t.element_size() for t in w.values())
