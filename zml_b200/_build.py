@@ -6,7 +6,8 @@ Two shared objects are produced next to the sources, never installed elsewhere:
   ``sm_100a`` only (``-gencode arch=compute_100a,code=sm_100a``).  nvcc
   cross-compiles, so this builds on a machine without a GPU.
 * ``zml_b200/_C/libzb_host.so``  - ``csrc/host/*.cpp`` compiled by ``g++``: the
-  safetensors reader, tracer, tokenizer and monitor back-ends.  CPU only.
+  threaded file reader behind the weight loader (``file_stream.cpp``) and the span
+  recorder (``tracer.cpp``).  CPU only.
 
 The reference gets its native parts from Bazel rules and from binaries downloaded at build time
 (platforms/cuda/cuda.bzl, third_party/*/repo.bzl); here everything native is compiled from the sources in this
