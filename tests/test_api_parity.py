@@ -282,3 +282,20 @@ def test_bad_inputs_are_refused_with_clear_errors():
     x = Tensor.from_torch(torch.arange(5.0), ["a"])
     idx = Tensor.from_torch(torch.tensor([7, -3, 2]), ["n"])
     assert x.gather({"a": idx}).data.tolist() == [4.0, 0.0, 2.0]
+
+
+def test_exe_keeps_inputs_declared_on_the_host_where_they_are():
+    pl = Platform.init("cpu")
+    table = Tensor.from_shape(Shape((4, 2), "f32", ("v", "d")))
+    table.on_memory("host_pinned")
+    idx = Tensor.from_shape(Shape((3,), "i64", ("n",)))
+    seen = {}
+
+    def fwd(t, i):
+        seen["device"] = t.data.device.type
+        return t.gather({"v": i})
+    exe = pl.compile(fwd, (table, idx))
+    assert exe.arg_memory_kinds == ["host_pinned", None] and not exe.use_graph
+    out = exe.call(Buffer.from_tensor(pl, torch.arange(8.0).reshape(4, 2), table.shape()),
+                   Buffer.from_tensor(pl, torch.tensor([3, 0, 3]), idx.shape()))
+    assert seen["device"] == "cpu" and out.to_tensor().tolist() == [[6.0, 7.0], [0.0, 1.0], [6.0, 7.0]]

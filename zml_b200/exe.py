@@ -81,7 +81,11 @@ class Exe:
         self.result_shapes = result_shapes
         self.platform = platform
         self.name = name
-        self.use_graph = cuda_graph and platform.target.value == "cuda"
+        # memory kind declared per input with `Tensor.on_memory` (zml/tensor.zig:257-273): inputs declared on the host
+        # stay there (the program reads them from pinned or pageable memory), and such a program is not graph-captured
+        self.arg_memory_kinds = [t.input_memory_kind() for t in meta.collect(arg_tree, lambda x: isinstance(x, Tensor))]
+        self._host_args = [k in ("host_pinned", "host_unpinned") for k in self.arg_memory_kinds]
+        self.use_graph = cuda_graph and platform.target.value == "cuda" and not any(self._host_args)
         self._graph = None
         self._static_in: Optional[list[torch.Tensor]] = None
         self._static_out = None
@@ -100,16 +104,18 @@ class Exe:
     def _to_tensors(self, flat: Sequence[Buffer]) -> list[torch.Tensor]:
         dev = self._device()
         out = []
+        host = self._host_args if len(self._host_args) == len(flat) else [False] * len(flat)
         if self.platform.spmd() is not None:
             # one process per device: the program runs on this rank's shards
             self._local_shapes = [b.placement.shape for b in flat]
-            return [b.local().to(dev) for b in flat]
+            return [b.local().to("cpu" if h else dev) for b, h in zip(flat, host)]
         self._local_shapes = None
-        for b in flat:
+        for b, h in zip(flat, host):
+            to = "cpu" if h else dev
             if len(b.shards) == 1 and b.sharding.sharded_shape(b.shape()).dims == b.shape().dims:
-                out.append(b.local().to(dev))
+                out.append(b.local().to(to))
             else:
-                out.append(b.to_tensor().to(dev))
+                out.append(b.to_tensor().to(to))
         return out
 
     def _run_fn(self, tensors: list[torch.Tensor]):
