@@ -179,3 +179,22 @@ def test_convert_round_trips_every_soft_float_format():             # zml/tensor
         back = enc.convert("f32").data
         assert torch.allclose(back, torch.from_numpy(floats.FORMATS[name].to_f32(want)), rtol=0, atol=0, equal_nan=True), name
     assert Tensor.arange(5, dtype="u16").data.tolist() == [0, 1, 2, 3, 4]
+
+
+def test_scatter_slices_with_a_batching_axis_and_with_explicit_coordinates():   # zml/ops.zig:1338-1375 (scatterConfig)
+    """The two forms the reference's scatter configuration distinguishes: the index tensor shares axis `a` with the
+    operand (a batching axis), or coordinates are given for `a` as well; both write windows of 2 along `b`."""
+    torch.manual_seed(0)
+    op = torch.zeros(10, 20)
+    idx_b = torch.randint(0, 19, (10, 8))
+    upd = torch.randn(10, 8, 2)
+    want = op.clone()
+    for a in range(10):
+        for n in range(8):
+            want[a, idx_b[a, n]:idx_b[a, n] + 2] += upd[a, n]
+    o, u = Tensor.from_torch(op, ["a", "b"]), Tensor.from_torch(upd, ["a", "n", "b"])
+    got = o.scatter_slices({"b": Tensor.from_torch(idx_b, ["a", "n"])}, u)
+    assert torch.allclose(got.data, want, atol=1e-6)
+    idx_a = torch.arange(10)[:, None].expand(10, 8).contiguous()
+    got = o.scatter_slices({"a": Tensor.from_torch(idx_a, ["a", "n"]), "b": Tensor.from_torch(idx_b, ["a", "n"])}, u)
+    assert torch.allclose(got.data, want, atol=1e-6)
