@@ -1,0 +1,148 @@
+"""The HTTP front end over Engine.serve: completions, chat, batching of concurrent requests, errors, metrics."""
+import json
+import threading
+import urllib.error
+import urllib.request
+
+import pytest
+import torch
+
+from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
+from zml_b200.serving import Engine
+from zml_b200.serving.server import Server
+
+tokenizers = pytest.importorskip("tokenizers")
+
+
+def _tokenizer():
+    from tokenizers import Tokenizer as HfTok, decoders, models, pre_tokenizers, trainers
+    from zml_b200.tokenizer import Tokenizer
+    t = HfTok(models.BPE())
+    t.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    t.decoder = decoders.ByteLevel()
+    t.train_from_iterator(["hello world the quick brown fox jumps over the lazy dog"] * 10,
+                          trainers.BpeTrainer(vocab_size=300, initial_alphabet=pre_tokenizers.ByteLevel.alphabet(),
+                                              special_tokens=["<|begin_of_text|>", "<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"]))
+    return Tokenizer.from_bytes(t.to_str().encode())
+
+
+def _post(base, route, body):
+    req = urllib.request.Request(base + route, data=json.dumps(body).encode(), headers={"Content-Type": "application/json"})
+    try:
+        with urllib.request.urlopen(req, timeout=60) as r:
+            return r.status, json.loads(r.read())
+    except urllib.error.HTTPError as e:
+        return e.code, json.loads(e.read())
+
+
+def test_server_completions_chat_batching_errors_and_metrics():
+    cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=512))
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=2, std=0.08)
+    tok = _tokenizer()
+    engine = Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128)
+    server = Server(engine, tok, model_name="tiny", template="llama3", bos=0, eos_ids=(3,), batch_window_s=0.3,
+                    default_max_tokens=5, idle_tick_s=0.05)
+    host, port = server.start_http("127.0.0.1", 0)
+    base = f"http://{host}:{port}"
+    loop = threading.Thread(target=server.run, daemon=True)
+    loop.start()
+    try:
+        prompts = ["hello world", "the quick brown fox", "lazy dog", "hello", "fox jumps over", "dog"]
+        results = {}
+
+        def ask(i):
+            results[i] = _post(base, "/v1/completions", {"prompt": prompts[i], "max_tokens": 6})
+        threads = [threading.Thread(target=ask, args=(i,)) for i in range(len(prompts))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        # six concurrent requests fall into one or two batches and equal one-at-a-time generation
+        ref = Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128)
+        for i, p in enumerate(prompts):
+            code, body = results[i]
+            assert code == 200 and body["object"] == "text_completion" and body["model"] == "tiny"
+            ids = [0] + tok.encode(p)
+            want, _ = ref.generate([ids], 6, eos_ids=(3,))
+            want_ids = want[0][:-1] if want[0] and want[0][-1] == 3 else want[0]
+            assert body["choices"][0]["text"] == tok.decode(want_ids)
+            assert body["usage"] == {"prompt_tokens": len(ids), "completion_tokens": len(want[0]), "total_tokens": len(ids) + len(want[0])}
+            assert body["choices"][0]["finish_reason"] in ("length", "stop")
+        assert 1 <= server.stats.batches <= 3 and server.stats.requests == 6
+
+        code, body = _post(base, "/v1/completions", {"prompt": [0, 5, 6, 7]})                     # token ids, default budget
+        assert code == 200 and body["usage"]["prompt_tokens"] == 4 and body["usage"]["completion_tokens"] <= 5
+        code, body = _post(base, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hello world"}], "max_tokens": 4})
+        assert code == 200 and body["object"] == "chat.completion" and body["choices"][0]["message"]["role"] == "assistant"
+        assert body["usage"]["prompt_tokens"] == len(__import__("zml_b200.models.hub", fromlist=["x"]).tokenize_prompt(tok, "hello world", "llama3", 0))
+
+        for bad in ({}, {"prompt": []}, {"prompt": "hi", "max_tokens": 0}, {"prompt": "hi", "max_tokens": 10_000},
+                    {"prompt": "hi", "stream": True}, {"prompt": 3}):
+            assert _post(base, "/v1/completions", bad)[0] == 400, bad
+        assert _post(base, "/v1/chat/completions", {"messages": []})[0] == 400
+        assert _post(base, "/v1/nothing", {})[0] == 404
+        with urllib.request.urlopen(base + "/health") as r:
+            assert json.loads(r.read())["status"] == "ok"
+        with urllib.request.urlopen(base + "/v1/models") as r:
+            assert json.loads(r.read())["data"][0]["id"] == "tiny"
+        with urllib.request.urlopen(base + "/metrics") as r:
+            text = r.read().decode()
+        assert "zml_server_requests_total 8" in text and "zml_server_output_tokens_total" in text and "zml_server_requests_failed_total 0" in text
+    finally:
+        server.shutdown()
+        loop.join(timeout=10)
+    assert not loop.is_alive()
+
+
+_TP_SERVER_WORKER = r"""
+import json, os, sys, threading, time, urllib.request, torch
+sys.path.insert(0, os.environ["ZB_ROOT"])
+sys.path.insert(0, os.path.join(os.environ["ZB_ROOT"], "tests"))
+from test_server import _tokenizer
+from zml_b200.models.llama import PRESETS, LlamaConfig, LlamaModel
+from zml_b200.parallel.comm import Comm
+from zml_b200.serving import Engine
+from zml_b200.serving.server import Server
+c = Comm.from_env(backend="gloo")
+cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=512))
+model = LlamaModel(cfg, c, device="cpu", dtype=torch.float32).init_random(seed=2, std=0.08)
+tok = _tokenizer()
+server = Server(Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128), tok, c, model_name="tiny", bos=0,
+                batch_window_s=0.2, idle_tick_s=0.05)
+if c.rank == 0:
+    host, port = server.start_http("127.0.0.1", 0)
+    def client():
+        outs = {}
+        def ask(i, p):
+            req = urllib.request.Request(f"http://{host}:{port}/v1/completions", data=json.dumps({"prompt": p, "max_tokens": 5}).encode())
+            with urllib.request.urlopen(req, timeout=120) as r:
+                outs[i] = json.loads(r.read())
+        ts = [threading.Thread(target=ask, args=(i, p)) for i, p in enumerate(["hello world", "the lazy dog", "fox"])]
+        [t.start() for t in ts]; [t.join() for t in ts]
+        single = LlamaModel(cfg, Comm.single(torch.device("cpu")), device="cpu", dtype=torch.float32).init_random(seed=2, std=0.08)
+        ref = Engine(single, num_pages=64, page_size=16, max_batch=4, max_seq_len=128)
+        for i, p in enumerate(["hello world", "the lazy dog", "fox"]):
+            want, _ = ref.generate([[0] + tok.encode(p)], 5)
+            assert outs[i]["choices"][0]["text"] == tok.decode(want[0]), (p, outs[i])
+        print("SERVER_TP_CLIENT_OK", flush=True)
+        server.shutdown()
+    threading.Thread(target=client, daemon=True).start()
+server.run()
+print("SERVER_TP_OK", c.rank, flush=True)
+c.finish(0)
+"""
+
+
+def test_server_on_two_tensor_parallel_ranks(tmp_path):
+    """Rank 0 owns the socket, both gloo ranks run every batch; answers equal one rank holding the whole model."""
+    import os
+    import subprocess
+    import sys
+    script = tmp_path / "w.py"
+    script.write_text(_TP_SERVER_WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29671", str(script)],
+                       capture_output=True, text=True, env=dict(os.environ, ZB_ROOT=root), timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert r.stdout.count("SERVER_TP_OK") == 2 and "SERVER_TP_CLIENT_OK" in r.stdout

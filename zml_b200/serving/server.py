@@ -1,0 +1,253 @@
+"""HTTP front end for an `Engine`: OpenAI-style `/v1/completions` and `/v1/chat/completions`, `/health`, and
+Prometheus gauges under `/metrics`.
+
+The reference stops at the chat CLI (examples/llm); this is the small piece a deployment needs on top of
+`Engine.serve`.  Requests are collected for a short window (`batch_window_s`) or until `max_queue` of them wait, then
+run as one `Engine.serve` call, which batches them continuously on the device; requests that arrive while a batch runs
+wait for the next one.  On a multi-rank job every rank calls `Server.run()`: rank 0 owns the socket and the queue and
+broadcasts each batch (token ids and budgets) so that all ranks enter `Engine.serve` with the same arguments; an idle
+tick is broadcast too, so that the heartbeat of `Comm.check_peers` keeps running while no request is in flight.
+
+    python examples/llm/serve.py --model=/models/Llama-3.1-8B-Instruct --port=8000
+    curl -s localhost:8000/v1/completions -d '{"prompt": "The capital of France is", "max_tokens": 16}'
+"""
+from __future__ import annotations
+
+import http.server
+import json
+import queue
+import threading
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Optional
+
+from ..models import hub
+from ..models.common import SamplingStrategy
+
+
+@dataclass
+class _Request:
+    ids: list
+    max_tokens: int
+    chat: bool
+    model: str
+    done: threading.Event = field(default_factory=threading.Event)
+    tokens: list = field(default_factory=list)
+    error: Optional[str] = None
+    arrived: float = field(default_factory=time.perf_counter)
+    finished: float = 0.0
+
+
+@dataclass
+class ServerStats:
+    requests: int = 0
+    failed: int = 0
+    batches: int = 0
+    prompt_tokens: int = 0
+    output_tokens: int = 0
+    busy_s: float = 0.0
+    last_batch: int = 0
+    last_tok_s: float = 0.0
+
+
+class Server:
+    def __init__(self, engine, tokenizer, comm=None, model_name: str = "model", template: Optional[str] = None,
+                 bos: Optional[int] = None, eos_ids=(), strategy: Optional[SamplingStrategy] = None,
+                 batch_window_s: float = 0.02, max_queue: int = 256, default_max_tokens: int = 128,
+                 idle_tick_s: float = 0.5):
+        self.engine, self.tok, self.comm = engine, tokenizer, comm
+        self.model_name, self.template, self.bos = model_name, template, bos
+        self.eos_ids = tuple(int(e) for e in eos_ids)
+        self.strategy = strategy or SamplingStrategy()
+        self.batch_window_s, self.max_queue = batch_window_s, max_queue
+        self.default_max_tokens, self.idle_tick_s = default_max_tokens, idle_tick_s
+        self.queue: "queue.Queue[_Request]" = queue.Queue()
+        self.stats = ServerStats()
+        self._stop = threading.Event()
+        self._httpd: Optional[http.server.ThreadingHTTPServer] = None
+        self.rank = comm.rank if comm is not None else 0
+
+    # ------------------------------------------------------------------ request handling (rank 0)
+    def _limit(self) -> int:
+        return self.engine.max_pages * self.engine.page_size
+
+    def submit(self, body: dict, chat: bool) -> _Request:
+        """Validates a request body and queues it; raises ValueError with the message for a 400 answer."""
+        if chat:
+            msgs = body.get("messages")
+            if not isinstance(msgs, list) or not msgs:
+                raise ValueError("'messages' must be a non-empty list")
+            ids: list = []
+            for i, m in enumerate(msgs):
+                if not isinstance(m, dict) or "content" not in m:
+                    raise ValueError("every message needs a 'content'")
+                if m.get("role", "user") == "assistant":
+                    ids += self.tok.encode(str(m["content"]))
+                else:
+                    ids += hub.tokenize_prompt(self.tok, str(m["content"]), self.template or "llama3", self.bos, first_turn=not ids)
+        else:
+            prompt = body.get("prompt")
+            if isinstance(prompt, list) and prompt and all(isinstance(t, int) for t in prompt):
+                ids = [int(t) for t in prompt]
+            elif isinstance(prompt, str):
+                ids = ([self.bos] if self.bos is not None else []) + self.tok.encode(prompt)
+            else:
+                raise ValueError("'prompt' must be a string or a list of token ids")
+        if not ids:
+            raise ValueError("the prompt is empty")
+        max_tokens = int(body.get("max_tokens", body.get("max_completion_tokens", self.default_max_tokens)))
+        if max_tokens < 1:
+            raise ValueError("'max_tokens' must be at least 1")
+        if len(ids) + max_tokens > self._limit():
+            raise ValueError(f"prompt ({len(ids)} tokens) + max_tokens ({max_tokens}) exceeds the engine's limit of {self._limit()} tokens")
+        if self.queue.qsize() >= self.max_queue:
+            raise OverflowError("the request queue is full")
+        r = _Request(ids, max_tokens, chat, str(body.get("model", self.model_name)))
+        self.queue.put(r)
+        return r
+
+    def _answer(self, r: _Request) -> dict:
+        toks = list(r.tokens)
+        finish = "length"
+        if toks and toks[-1] in self.eos_ids:
+            toks, finish = toks[:-1], "stop"
+        text = self.tok.decode(toks)
+        usage = {"prompt_tokens": len(r.ids), "completion_tokens": len(r.tokens), "total_tokens": len(r.ids) + len(r.tokens)}
+        rid, created = uuid.uuid4().hex[:24], int(time.time())
+        if r.chat:
+            return {"id": f"chatcmpl-{rid}", "object": "chat.completion", "created": created, "model": r.model,
+                    "choices": [{"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": finish}],
+                    "usage": usage}
+        return {"id": f"cmpl-{rid}", "object": "text_completion", "created": created, "model": r.model,
+                "choices": [{"index": 0, "text": text, "finish_reason": finish}], "usage": usage}
+
+    def metrics(self) -> str:
+        s = self.stats
+        rows = [("zml_server_requests_total", "counter", s.requests), ("zml_server_requests_failed_total", "counter", s.failed),
+                ("zml_server_batches_total", "counter", s.batches), ("zml_server_prompt_tokens_total", "counter", s.prompt_tokens),
+                ("zml_server_output_tokens_total", "counter", s.output_tokens), ("zml_server_busy_seconds_total", "counter", round(s.busy_s, 6)),
+                ("zml_server_queue_length", "gauge", self.queue.qsize()), ("zml_server_last_batch_size", "gauge", s.last_batch),
+                ("zml_server_last_batch_tokens_per_second", "gauge", round(s.last_tok_s, 3))]
+        return "".join(f"# TYPE {n} {k}\n{n} {v}\n" for n, k, v in rows)
+
+    def _handler(self):
+        server = self
+
+        class Handler(http.server.BaseHTTPRequestHandler):
+            protocol_version = "HTTP/1.1"
+
+            def log_message(self, *a):
+                pass
+
+            def _send(self, code: int, body, ctype: str = "application/json"):
+                data = body.encode() if isinstance(body, str) else json.dumps(body).encode()
+                self.send_response(code)
+                self.send_header("Content-Type", ctype)
+                self.send_header("Content-Length", str(len(data)))
+                self.end_headers()
+                self.wfile.write(data)
+
+            def do_GET(self):
+                if self.path.startswith("/health"):
+                    return self._send(200, {"status": "ok", "queue": server.queue.qsize()})
+                if self.path.startswith("/metrics"):
+                    return self._send(200, server.metrics(), "text/plain; version=0.0.4")
+                if self.path.startswith("/v1/models"):
+                    return self._send(200, {"object": "list", "data": [{"id": server.model_name, "object": "model"}]})
+                self._send(404, {"error": {"message": f"no route {self.path}"}})
+
+            def do_POST(self):
+                chat = self.path.startswith("/v1/chat/completions")
+                if not chat and not self.path.startswith("/v1/completions"):
+                    return self._send(404, {"error": {"message": f"no route {self.path}"}})
+                try:
+                    body = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
+                    if not isinstance(body, dict):
+                        raise ValueError("the body must be a JSON object")
+                    if body.get("stream"):
+                        raise ValueError("'stream' is not supported")
+                    r = server.submit(body, chat)
+                except OverflowError as e:
+                    return self._send(429, {"error": {"message": str(e)}})
+                except (ValueError, json.JSONDecodeError) as e:
+                    return self._send(400, {"error": {"message": str(e)}})
+                r.done.wait()
+                if r.error:
+                    return self._send(500, {"error": {"message": r.error}})
+                self._send(200, server._answer(r))
+        return Handler
+
+    # ------------------------------------------------------------------ scheduling (every rank)
+    def _next_batch(self) -> Optional[list]:
+        """Rank 0: requests to run now - the first one that arrives, plus what follows within the batching window."""
+        try:
+            first = self.queue.get(timeout=self.idle_tick_s)
+        except queue.Empty:
+            return None
+        batch = [first]
+        deadline = time.perf_counter() + self.batch_window_s
+        while len(batch) < self.max_queue:
+            left = deadline - time.perf_counter()
+            try:
+                batch.append(self.queue.get(timeout=max(left, 0.0)) if left > 0 else self.queue.get_nowait())
+            except queue.Empty:
+                break
+        return batch
+
+    def step(self) -> bool:
+        """One scheduling round on every rank: wait for a batch (rank 0), share it, run it.  Returns False once
+        `shutdown` was called (on every rank)."""
+        batch = self._next_batch() if self.rank == 0 else None
+        msg = ("stop", None, None) if self._stop.is_set() and batch is None else \
+              ("run", [r.ids for r in batch], [r.max_tokens for r in batch]) if batch else ("idle", None, None)
+        if self.comm is not None and self.comm.world > 1:
+            msg = self.comm.broadcast_object(msg if self.rank == 0 else None)
+            self.comm.check_peers()
+        kind, prompts, budgets = msg
+        if kind == "stop":
+            return False
+        if kind == "idle":
+            return True
+        t0 = time.perf_counter()
+        try:
+            outs, _ = self.engine.serve(prompts, budgets, self.strategy, self.eos_ids)
+            err = None
+        except Exception as e:                  # noqa: BLE001 - reported to the callers, the server keeps running
+            outs, err = [[] for _ in prompts], f"{type(e).__name__}: {e}"
+        dt = time.perf_counter() - t0
+        if self.rank == 0 and batch:
+            s = self.stats
+            s.batches += 1
+            s.requests += len(batch)
+            s.failed += len(batch) if err else 0
+            s.prompt_tokens += sum(len(p) for p in prompts)
+            n_out = sum(len(o) for o in outs)
+            s.output_tokens += n_out
+            s.busy_s += dt
+            s.last_batch, s.last_tok_s = len(batch), n_out / max(dt, 1e-9)
+            for r, o in zip(batch, outs):
+                r.tokens, r.error, r.finished = list(o), err, time.perf_counter()
+                r.done.set()
+        return True
+
+    def start_http(self, host: str = "127.0.0.1", port: int = 8000) -> tuple:
+        """Rank 0: opens the socket (port 0 = any free port) and serves it on a thread; returns (host, port)."""
+        self._httpd = http.server.ThreadingHTTPServer((host, port), self._handler())
+        self._httpd.daemon_threads = True
+        threading.Thread(target=self._httpd.serve_forever, daemon=True).start()
+        return self._httpd.server_address[:2]
+
+    def run(self, host: str = "127.0.0.1", port: int = 8000) -> None:
+        """Serves until `shutdown()`; call on every rank."""
+        if self.rank == 0 and self._httpd is None:
+            self.start_http(host, port)
+        while self.step():
+            pass
+        if self._httpd is not None:
+            self._httpd.shutdown()
+            self._httpd.server_close()
+            self._httpd = None
+
+    def shutdown(self) -> None:
+        self._stop.set()
