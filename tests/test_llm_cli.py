@@ -138,3 +138,37 @@ def test_load_model_from_a_remote_repository(tmp_path):
     finally:
         srv.shutdown()
         srv.server_close()
+
+
+def test_serve_cli_answers_and_stops_on_sigterm(tmp_path):
+    """examples/llm/serve.py on CPU: starts on a free port, answers a completion and the health route, leaves cleanly
+    on SIGTERM."""
+    import re
+    import signal
+    import time
+    import urllib.request
+    make_repo(str(tmp_path))
+    p = subprocess.Popen([sys.executable, os.path.join(ROOT, "examples", "llm", "serve.py"), f"--model={tmp_path}", "--cpu",
+                          "--port=0", "--max-batch=2", "--seqlen=64"], stderr=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    try:
+        port, t0 = None, time.time()
+        while port is None and time.time() - t0 < 120:
+            line = p.stderr.readline()
+            if not line and p.poll() is not None:
+                break
+            m = re.search(r"http://127\.0\.0\.1:(\d+)", line)
+            if m:
+                port = int(m.group(1))
+        assert port, "the server did not come up"
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions",
+                                     data=json.dumps({"prompt": "hello world", "max_tokens": 4}).encode())
+        with urllib.request.urlopen(req, timeout=60) as r:
+            body = json.loads(r.read())
+        assert body["usage"]["completion_tokens"] == 4 and isinstance(body["choices"][0]["text"], str)
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=10) as r:
+            assert json.loads(r.read())["status"] == "ok"
+        p.send_signal(signal.SIGTERM)
+        assert p.wait(timeout=60) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()
