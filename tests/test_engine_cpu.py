@@ -386,3 +386,22 @@ def test_engine_rejects_bad_requests_without_stranding_pages():
     out, _ = eng.generate([[1, 2, 3]], 2, SamplingStrategy(topk=1000, temperature=1.0))
     assert len(out[0]) == 2 and len(eng.pool.free) == free0
     assert eng.generate([[1, 2, 3]], 0)[0] == [[]]
+
+
+def test_serve_reports_tokens_block_by_block():
+    """`on_tokens` sees every token exactly once, in order, per prompt, and one final call per prompt."""
+    cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=300))
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=1, std=0.05)
+    eng = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=64)
+    calls = []
+    outs, _ = eng.serve([[1, 2, 3], [4, 5], [6]], [5, 9, 1], sync_interval=3,
+                        on_tokens=lambda i, toks, fin: calls.append((i, list(toks), fin)))
+    acc, final = {0: [], 1: [], 2: []}, set()
+    for i, toks, fin in calls:
+        assert i not in final
+        acc[i] += toks
+        if fin:
+            final.add(i)
+    assert [acc[i] for i in range(3)] == outs and final == {0, 1, 2}
+    assert [len(o) for o in outs] == [5, 9, 1]
+    assert eng.serve([[1, 2, 3], [4, 5], [6]], [5, 9, 1], sync_interval=3)[0] == outs        # the callback changes nothing

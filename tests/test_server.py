@@ -77,7 +77,7 @@ def test_server_completions_chat_batching_errors_and_metrics():
         assert body["usage"]["prompt_tokens"] == len(__import__("zml_b200.models.hub", fromlist=["x"]).tokenize_prompt(tok, "hello world", "llama3", 0))
 
         for bad in ({}, {"prompt": []}, {"prompt": "hi", "max_tokens": 0}, {"prompt": "hi", "max_tokens": 10_000},
-                    {"prompt": "hi", "stream": True}, {"prompt": 3}):
+                    {"prompt": 3}):
             assert _post(base, "/v1/completions", bad)[0] == 400, bad
         assert _post(base, "/v1/chat/completions", {"messages": []})[0] == 400
         assert _post(base, "/v1/nothing", {})[0] == 404
@@ -146,3 +146,34 @@ def test_server_on_two_tensor_parallel_ranks(tmp_path):
                        capture_output=True, text=True, env=dict(os.environ, ZB_ROOT=root), timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert r.stdout.count("SERVER_TP_OK") == 2 and "SERVER_TP_CLIENT_OK" in r.stdout
+
+
+def test_server_streams_server_sent_events():
+    cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=512))
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=2, std=0.08)
+    tok = _tokenizer()
+    server = Server(Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128), tok, model_name="tiny", bos=0,
+                    batch_window_s=0.05, idle_tick_s=0.05)
+    host, port = server.start_http("127.0.0.1", 0)
+    loop = threading.Thread(target=server.run, daemon=True)
+    loop.start()
+    try:
+        whole = _post(f"http://{host}:{port}", "/v1/completions", {"prompt": "the quick brown fox", "max_tokens": 40})[1]
+        for route, body in (("/v1/completions", {"prompt": "the quick brown fox", "max_tokens": 40, "stream": True}),
+                            ("/v1/chat/completions", {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 20, "stream": True})):
+            req = urllib.request.Request(f"http://{host}:{port}{route}", data=json.dumps(body).encode())
+            with urllib.request.urlopen(req, timeout=60) as r:
+                assert r.headers["Content-Type"] == "text/event-stream"
+                lines = [l for l in r.read().decode().split("\n\n") if l]
+            assert lines[-1] == "data: [DONE]" and len(lines) >= 3                  # several decode blocks, then the end
+            events = [json.loads(l[len("data: "):]) for l in lines[:-1]]
+            assert events[-1]["choices"][0]["finish_reason"] in ("length", "stop")
+            assert all(e["choices"][0]["finish_reason"] is None for e in events[:-1])
+            if route == "/v1/completions":
+                assert "".join(e["choices"][0]["text"] for e in events) == whole["choices"][0]["text"]
+            else:
+                assert events[0]["object"] == "chat.completion.chunk"
+                assert isinstance("".join(e["choices"][0]["delta"].get("content", "") for e in events), str)
+    finally:
+        server.shutdown()
+        loop.join(timeout=10)

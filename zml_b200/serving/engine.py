@@ -435,12 +435,13 @@ class Engine:
     # ------------------------------------------------------------------ continuous batching
     def serve(self, prompts: Seq[Seq[int]], max_new_tokens, strategy: Optional[SamplingStrategy] = None,
               eos_ids: Seq[int] = (), sync_interval: int = 16, seed: int = 0,
-              arrivals: Optional[Seq[int]] = None) -> tuple[list[list[int]], GenerationStats]:
+              arrivals: Optional[Seq[int]] = None, on_tokens=None) -> tuple[list[list[int]], GenerationStats]:
         """Continuous batching over any number of prompts: at most `max_batch` sequences decode together; between two
         decode blocks (`sync_interval` steps, one device -> host read) finished sequences leave - their batch row,
         KV pages and recurrent-state slot are free again - and waiting prompts are admitted as soon as a row and
         enough pages are free: they are prefilled and join the next block.  `max_new_tokens` is one number or one per
-        prompt; `arrivals[i]` (optional) is the first block at which prompt i may be admitted.
+        prompt; `arrivals[i]` (optional) is the first block at which prompt i may be admitted.  `on_tokens(i, new_tokens,
+        finished)` (optional) is called on the host after every block with what prompt i produced since the last call.
 
         On a multi-rank job every rank calls this with the same arguments; a rank that stopped or left is noticed
         on the host before the next block is launched (`Comm.check_peers`)."""
@@ -479,10 +480,26 @@ class Engine:
         dirty = False                                         # a row's owner changed since the last upload
         comm = getattr(self.model, "comm", None)
 
+        reported = [0] * n_req
+        finished_idx: set = set()
+
+        def report() -> None:
+            if on_tokens is None:
+                return
+            for i in range(n_req):
+                if reported[i] < 0:                                       # the final call has been made
+                    continue
+                new = outputs[i][reported[i]:]
+                fin = i in finished_idx
+                if new or fin:
+                    reported[i] = -1 if fin else len(outputs[i])
+                    on_tokens(i, new, fin)
+
         def finish(row: int) -> None:
             nonlocal dirty
             dirty = True
             idx, r = running.pop(row)
+            finished_idx.add(idx)
             r.output, r.finished = outputs[idx], True
             self.release(r)
             free_rows.append(row)
@@ -533,6 +550,7 @@ class Engine:
                         finish(row)
             if not running:
                 block += 1
+                report()
                 continue
             # ---------------- device state (only when the set of sequences changed: a row that lost its sequence
             # must stop writing KV before its pages go to another request)
@@ -569,6 +587,7 @@ class Engine:
                         finish(row)
                         break
             block += 1
+            report()
         if self.on_gpu:
             torch.cuda.synchronize()
             stats.launches = _lib.launch_count() - launches0

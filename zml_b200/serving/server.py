@@ -4,7 +4,7 @@ Prometheus gauges under `/metrics`.
 The reference stops at the chat CLI (examples/llm); this is the small piece a deployment needs on top of
 `Engine.serve`.  Requests are collected for a short window (`batch_window_s`) or until `max_queue` of them wait, then
 run as one `Engine.serve` call, which batches them continuously on the device; requests that arrive while a batch runs
-wait for the next one.  On a multi-rank job every rank calls `Server.run()`: rank 0 owns the socket and the queue and
+wait for the next one.  `"stream": true` answers with server-sent events, one per decode block.  On a multi-rank job every rank calls `Server.run()`: rank 0 owns the socket and the queue and
 broadcasts each batch (token ids and budgets) so that all ranks enter `Engine.serve` with the same arguments; an idle
 tick is broadcast too, so that the heartbeat of `Comm.check_peers` keeps running while no request is in flight.
 
@@ -37,6 +37,8 @@ class _Request:
     error: Optional[str] = None
     arrived: float = field(default_factory=time.perf_counter)
     finished: float = 0.0
+    stream: bool = False
+    chunks: "queue.Queue" = field(default_factory=queue.Queue)       # (new tokens, finished) per decode block
 
 
 @dataclass
@@ -103,7 +105,7 @@ class Server:
             raise ValueError(f"prompt ({len(ids)} tokens) + max_tokens ({max_tokens}) exceeds the engine's limit of {self._limit()} tokens")
         if self.queue.qsize() >= self.max_queue:
             raise OverflowError("the request queue is full")
-        r = _Request(ids, max_tokens, chat, str(body.get("model", self.model_name)))
+        r = _Request(ids, max_tokens, chat, str(body.get("model", self.model_name)), stream=bool(body.get("stream", False)))
         self.queue.put(r)
         return r
 
@@ -165,17 +167,56 @@ class Server:
                     body = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
                     if not isinstance(body, dict):
                         raise ValueError("the body must be a JSON object")
-                    if body.get("stream"):
-                        raise ValueError("'stream' is not supported")
                     r = server.submit(body, chat)
                 except OverflowError as e:
                     return self._send(429, {"error": {"message": str(e)}})
                 except (ValueError, json.JSONDecodeError) as e:
                     return self._send(400, {"error": {"message": str(e)}})
+                if r.stream:
+                    return self._stream(r)
                 r.done.wait()
                 if r.error:
                     return self._send(500, {"error": {"message": r.error}})
                 self._send(200, server._answer(r))
+
+            def _stream(self, r):
+                """Server-sent events: one `data:` line per decode block with the text produced since the last one,
+                then a final chunk with the finish reason and `data: [DONE]`."""
+                self.send_response(200)
+                self.send_header("Content-Type", "text/event-stream")
+                self.send_header("Cache-Control", "no-cache")
+                self.send_header("Connection", "close")
+                self.end_headers()
+                rid, created = uuid.uuid4().hex[:24], int(time.time())
+                kind = "chat.completion.chunk" if r.chat else "text_completion"
+                dec = server.tok.decoder()
+
+                def event(text, finish):
+                    choice = ({"index": 0, "delta": {"content": text} if text else {}, "finish_reason": finish} if r.chat
+                              else {"index": 0, "text": text, "finish_reason": finish})
+                    body = {"id": ("chatcmpl-" if r.chat else "cmpl-") + rid, "object": kind, "created": created,
+                            "model": r.model, "choices": [choice]}
+                    self.wfile.write(b"data: " + json.dumps(body).encode() + b"\n\n")
+                    self.wfile.flush()
+                try:
+                    finish = "length"
+                    while True:
+                        toks, fin = r.chunks.get()
+                        if toks is None:                    # the batch failed
+                            event("", "error")
+                            break
+                        if fin and toks and toks[-1] in server.eos_ids:
+                            toks, finish = toks[:-1], "stop"
+                        text = "".join(dec.feed_one(t) for t in toks) + (dec.finalize() if fin else "")
+                        if text or fin:
+                            event(text, finish if fin else None)
+                        if fin:
+                            break
+                    self.wfile.write(b"data: [DONE]\n\n")
+                    self.wfile.flush()
+                except (BrokenPipeError, ConnectionResetError):
+                    pass                                    # the client went away; the batch runs to its end
+                self.close_connection = True
         return Handler
 
     # ------------------------------------------------------------------ scheduling (every rank)
@@ -210,8 +251,13 @@ class Server:
         if kind == "idle":
             return True
         t0 = time.perf_counter()
+        on_tokens = None
+        if self.rank == 0 and batch and any(r.stream for r in batch):
+            def on_tokens(i, toks, fin):
+                if batch[i].stream:
+                    batch[i].chunks.put((list(toks), fin))
         try:
-            outs, _ = self.engine.serve(prompts, budgets, self.strategy, self.eos_ids)
+            outs, _ = self.engine.serve(prompts, budgets, self.strategy, self.eos_ids, on_tokens=on_tokens)
             err = None
         except Exception as e:                  # noqa: BLE001 - reported to the callers, the server keeps running
             outs, err = [[] for _ in prompts], f"{type(e).__name__}: {e}"
@@ -228,6 +274,8 @@ class Server:
             s.last_batch, s.last_tok_s = len(batch), n_out / max(dt, 1e-9)
             for r, o in zip(batch, outs):
                 r.tokens, r.error, r.finished = list(o), err, time.perf_counter()
+                if err and r.stream:
+                    r.chunks.put((None, True))
                 r.done.set()
         return True
 
