@@ -177,3 +177,43 @@ def test_server_streams_server_sent_events():
     finally:
         server.shutdown()
         loop.join(timeout=10)
+
+
+def test_server_reports_a_failed_batch_and_keeps_serving():
+    """A batch whose `serve` raises (a collective that timed out, pages that ran out) answers 500 to its requests - an
+    error event to streaming ones - and the next batch runs normally; a full queue answers 429."""
+    tok = _tokenizer()
+
+    class FlakyEngine:
+        max_pages, page_size = 8, 16
+        calls = 0
+
+        def serve(self, prompts, budgets, strategy, eos_ids, on_tokens=None):
+            FlakyEngine.calls += 1
+            if FlakyEngine.calls == 1:
+                raise RuntimeError("collective timed out")
+            outs = [[7] * b for b in budgets]
+            if on_tokens:
+                for i, o in enumerate(outs):
+                    on_tokens(i, o, True)
+            return outs, None
+
+    server = Server(FlakyEngine(), tok, model_name="fake", bos=0, batch_window_s=0.01, idle_tick_s=0.02, max_queue=2)
+    host, port = server.start_http("127.0.0.1", 0)
+    base = f"http://{host}:{port}"
+    loop = threading.Thread(target=server.run, daemon=True)
+    loop.start()
+    try:
+        code, body = _post(base, "/v1/completions", {"prompt": "hello", "max_tokens": 3})
+        assert code == 500 and "collective timed out" in body["error"]["message"]
+        code, body = _post(base, "/v1/completions", {"prompt": "hello", "max_tokens": 3})
+        assert code == 200 and body["usage"]["completion_tokens"] == 3
+        assert server.stats.failed == 1 and server.stats.requests == 2 and server.stats.batches == 2
+    finally:
+        server.shutdown()
+        loop.join(timeout=10)
+    # with the scheduler stopped, requests pile up: the third one is refused
+    for _ in range(2):
+        server.submit({"prompt": "x", "max_tokens": 1}, chat=False)
+    with pytest.raises(OverflowError):
+        server.submit({"prompt": "x", "max_tokens": 1}, chat=False)
