@@ -77,6 +77,14 @@ def test_sdpa_gqa_mask_and_sinks():
     assert win.data[4, 2] == float("-inf") and win.data[4, 3] == 0 and win.data[4, 4] == 0
     sink = nn.sdpa(q, k, v, softmax_bias=Tensor(torch.full((8,), 50.0), None, ("h",)))
     assert sink.data.abs().max() < 1e-6 * 1e9 and sink.data.abs().mean() < out.data.abs().mean()
+    # the scale as a number and as a scalar tensor give the same result; a non-scalar tensor is refused
+    a = nn.sdpa(q, k, v, attn_mask=mask, scale=0.3)
+    b = nn.sdpa(q, k, v, attn_mask=mask, scale=Tensor(torch.tensor(0.3), None, ()))
+    torch.testing.assert_close(a.data, b.data)
+    torch.testing.assert_close(a.data, torch.nn.functional.scaled_dot_product_attention(q.data, kk, vv, attn_mask=mask.data, scale=0.3),
+                               rtol=1e-4, atol=1e-5)
+    with pytest.raises(ValueError, match="scalar"):
+        nn.sdpa(q, k, v, scale=Tensor(torch.ones(2), None, ("x",)))
 
 
 def test_gated_delta_net_matches_closed_form_small_case():

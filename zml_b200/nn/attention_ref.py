@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Union
 
 import torch
 
@@ -28,17 +28,23 @@ def causal_attn_mask(attn_shape, dtype="f32", attn_window_len: Optional[int] = N
     return mask.convert(s.dtype)
 
 
-def sdpa(q: Tensor, k: Tensor, v: Tensor, attn_mask: Optional[Tensor] = None, scale: Optional[float] = None,
-         softmax_bias: Optional[Tensor] = None) -> Tensor:
+def sdpa(q: Tensor, k: Tensor, v: Tensor, attn_mask: Optional[Tensor] = None,
+         scale: Union[None, float, Tensor] = None, softmax_bias: Optional[Tensor] = None) -> Tensor:
     """q {h, q, hd}; k, v {h, k, hd}; fewer kv heads than q heads are repeated (GQA by splitting
-    the q heads); softmax in float32; optional per-head sink logit `softmax_bias` {h}."""
+    the q heads); softmax in float32; optional per-head sink logit `softmax_bias` {h}.  `scale` is a number or a
+    scalar tensor (the reference passes a tensor, zml/nn.zig:1693-1697); default 1 / sqrt(hd)."""
     for t, need in ((q, ("h", "q", "hd")), (k, ("h", "k", "hd")), (v, ("h", "k", "hd"))):
         if not t.shape().has_tags(need):
             raise ValueError(f"sdpa: {t} is missing tags {need}")
     hk = k.dim("h")
     qs = q.split_axis("h", {"h": hk, "hq": "auto"})
-    sc = scale if scale is not None else 1.0 / math.sqrt(q.dim("hd"))
-    w = qs.dot(k.scale(sc), "hd")                         # {h, hq, q, k}
+    if isinstance(scale, Tensor):
+        if scale.count() != 1:
+            raise ValueError(f"sdpa: scale must be a scalar, got {scale}")
+        ks = Tensor(k.data * scale.data.reshape(()).to(k.data.dtype), k.shape())
+    else:
+        ks = k.scale(scale if scale is not None else 1.0 / math.sqrt(q.dim("hd")))
+    w = qs.dot(ks, "hd")                         # {h, hq, q, k}
     if attn_mask is not None:
         w = w.add(attn_mask.broad(w.shape()))
     wf = w.convert("f32")
