@@ -29,7 +29,7 @@ _LAZY = {
 _SUBMODULES = {
     "dtype", "floats", "shape", "tensor", "slice", "meta", "buffer", "mem", "exe", "module",
     "platform", "sharding", "io", "safetensors", "nn", "ops", "attention", "moe", "tokenizer",
-    "testing", "profiling", "models", "parallel", "utils", "serving", "flags", "kernel", "logo", "stdx", "vfs", "spmd",
+    "testing", "profiling", "models", "parallel", "utils", "serving", "flags", "kernel", "logo", "stdx", "vfs", "spmd", "driver_probe",
 }
 
 # sizes, as the reference exports them (zml/zml.zig:59-62)

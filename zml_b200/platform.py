@@ -105,7 +105,9 @@ class Platform:
         self.comm = comm
         if target is Target.cuda:
             if not torch.cuda.is_available():
-                raise RuntimeError("cuda target requested but no CUDA device is visible")
+                from . import driver_probe
+                why = driver_probe.diagnose(driver_probe.probe_in_child(), driver_probe.runtime_version())
+                raise RuntimeError(f"cuda target requested but no CUDA device is visible: {why}")
             world = comm.world if comm is not None and comm.world > 1 else None
             n = world or torch.cuda.device_count()
         elif comm is not None and comm.world > 1:
