@@ -405,3 +405,23 @@ def test_serve_reports_tokens_block_by_block():
     assert [acc[i] for i in range(3)] == outs and final == {0, 1, 2}
     assert [len(o) for o in outs] == [5, 9, 1]
     assert eng.serve([[1, 2, 3], [4, 5], [6]], [5, 9, 1], sync_interval=3)[0] == outs        # the callback changes nothing
+
+
+def test_a_seed_reproduces_a_sampled_generation_on_cpu():
+    """Top-k sampling draws its noise from (seed, draws so far): the same seed gives the same tokens from a fresh
+    engine and from one that has served before; another seed gives others; consecutive steps draw different noise."""
+    from zml_b200.models.common import SamplingStrategy
+    cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=512))
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=4, std=0.08)
+    strat = SamplingStrategy(topk=16, temperature=1.5)
+    prompts = [[1, 5, 9, 13], [2, 6]]
+    eng = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=64)
+    a, _ = eng.generate(prompts, 12, strat, seed=3)
+    other, _ = eng.generate(prompts, 12, strat, seed=4)
+    again, _ = eng.generate(prompts, 12, strat, seed=3)
+    fresh, _ = Engine(model, num_pages=32, page_size=16, max_batch=2, max_seq_len=64).generate(prompts, 12, strat, seed=3)
+    assert a == again == fresh and a != other
+    served, _ = eng.serve(prompts, 12, strat, seed=3)
+    assert served == eng.serve(prompts, 12, strat, seed=3)[0]
+    greedy, _ = eng.generate(prompts, 12)
+    assert a != greedy                                   # at temperature 1.5 over 16 candidates the draw leaves the arg-max

@@ -188,7 +188,7 @@ def test_server_reports_a_failed_batch_and_keeps_serving():
         max_pages, page_size = 8, 16
         calls = 0
 
-        def serve(self, prompts, budgets, strategy, eos_ids, on_tokens=None):
+        def serve(self, prompts, budgets, strategy, eos_ids, seed=0, on_tokens=None):
             FlakyEngine.calls += 1
             if FlakyEngine.calls == 1:
                 raise RuntimeError("collective timed out")
@@ -217,3 +217,64 @@ def test_server_reports_a_failed_batch_and_keeps_serving():
         server.submit({"prompt": "x", "max_tokens": 1}, chat=False)
     with pytest.raises(OverflowError):
         server.submit({"prompt": "x", "max_tokens": 1}, chat=False)
+
+
+class _RecordingEngine:
+    """Stands in for an Engine: records what `serve` was called with and answers token 7 for every budgeted step."""
+    max_pages, page_size = 64, 16
+
+    def __init__(self):
+        self.calls = []
+
+    def serve(self, prompts, budgets, strategy, eos_ids, seed=0, on_tokens=None):
+        self.calls.append((len(prompts), strategy.topk, strategy.temperature, seed))
+        return [[7] * b for b in budgets], None
+
+
+def test_server_batches_by_sampling_settings_and_validates_them():
+    from zml_b200.models.common import SamplingStrategy
+    eng = _RecordingEngine()
+    server = Server(eng, _tokenizer(), bos=0, eos_ids=(3,), batch_window_s=0.0, idle_tick_s=0.01,
+                    strategy=SamplingStrategy(topk=1, temperature=1.0))
+    a = server.submit({"prompt": "hello", "max_tokens": 2}, chat=False)                                     # the server's strategy
+    b = server.submit({"prompt": "hello", "max_tokens": 2, "temperature": 0.7, "top_k": 40, "seed": 5}, chat=False)
+    c = server.submit({"prompt": "dog", "max_tokens": 3, "temperature": 0}, chat=False)                     # greedy = the default here
+    d = server.submit({"prompt": "fox", "max_tokens": 2, "top_k": 40, "temperature": 0.7, "seed": 5}, chat=False)
+    e = server.submit({"prompt": "fox", "max_tokens": 2, "temperature": 1.5}, chat=False)                   # no top_k: the widest
+    f = server.submit({"prompt": "fox", "max_tokens": 2, "top_k": 1000}, chat=False)                        # capped
+    g = server.submit({"prompt": "fox", "max_tokens": 2, "top_k": -1, "temperature": 1.5}, chat=False)
+    assert a.sampling == (1, 1.0, 0) and b.sampling == (40, 0.7, 5) and c.sampling == (1, 1.0, 0)
+    assert e.sampling == (128, 1.5, 0) and f.sampling == (128, 1.0, 0) and g.sampling == e.sampling
+    assert server.waiting() == 7
+    for _ in range(4):
+        assert server.step()
+    # four batches, oldest first: {a, c}, {b, d}, {e, g}, {f}; nobody is left behind
+    assert eng.calls == [(2, 1, 1.0, 0), (2, 40, 0.7, 5), (2, 128, 1.5, 0), (1, 128, 1.0, 0)]
+    assert all(r.done.is_set() for r in (a, b, c, d, e, f, g)) and server.waiting() == 0
+    assert len(c.tokens) == 3 and len(d.tokens) == 2 and server.stats.batches == 4 and server.stats.requests == 7
+    # a server that samples by default keeps its k when a request only sets the temperature
+    warm = Server(eng, _tokenizer(), bos=0, strategy=SamplingStrategy(topk=8, temperature=0.9))
+    assert warm._sampling({}) == (8, 0.9, 0) and warm._sampling({"temperature": 0.5}) == (8, 0.5, 0)
+    assert warm._sampling({"top_k": 3}) == (3, 0.9, 0) and warm._sampling({"temperature": 0, "top_k": 9}) == (1, 1.0, 0)
+    for bad in ({"temperature": -1}, {"temperature": "hot"}, {"temperature": True}, {"temperature": float("nan")},
+                {"top_k": 0}, {"top_k": 2.5}, {"top_k": -2}, {"seed": "x"}, {"seed": 1.5}):
+        with pytest.raises(ValueError):
+            server.submit(dict({"prompt": "hello"}, **bad), chat=False)
+    assert server.waiting() == 0
+
+
+def test_server_sampled_request_matches_the_engine_with_the_same_settings():
+    from zml_b200.models.common import SamplingStrategy
+    cfg = LlamaConfig.from_hf(dict(PRESETS["tiny-llama-test"], vocab_size=512))
+    model = LlamaModel(cfg, device="cpu", dtype=torch.float32).init_random(seed=2, std=0.08)
+    tok = _tokenizer()
+    server = Server(Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128), tok, bos=0, eos_ids=(3,),
+                    batch_window_s=0.0, idle_tick_s=0.01)
+    r = server.submit({"prompt": "hello world", "max_tokens": 6, "temperature": 0.8, "top_k": 5, "seed": 11}, chat=False)
+    greedy = server.submit({"prompt": "hello world", "max_tokens": 6}, chat=False)
+    assert server.step() and server.step() and r.done.is_set() and greedy.done.is_set() and not r.error
+    ref = Engine(model, num_pages=64, page_size=16, max_batch=4, max_seq_len=128)
+    want, _ = ref.serve([[0] + tok.encode("hello world")], 6, SamplingStrategy(topk=5, temperature=0.8), (3,), seed=11)
+    assert r.tokens == want[0]
+    want_greedy, _ = ref.serve([[0] + tok.encode("hello world")], 6, SamplingStrategy(), (3,))
+    assert greedy.tokens == want_greedy[0]

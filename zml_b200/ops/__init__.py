@@ -262,6 +262,8 @@ def topk_sample(logits, k: int, temperature: float = 1.0, seed: int = 0, step: i
     far} on the device that replaces `seed` and is added to `step`, so a captured CUDA graph draws fresh noise
     at every replay once the counter is advanced on the device (`advance_rng`, or the decode bookkeeping).
     Returns tokens int32 [B] (and the sorted top-k values / indices when asked).  k is capped at the row length.
+    On CPU the noise comes from `generator` when one is given, else from a generator seeded by the same (seed, step)
+    or counter, so that a seed reproduces a generation there too (the draws differ from the device's).
     """
     k = min(int(k), int(logits.shape[1]))
     if not _cuda(logits):
@@ -269,6 +271,10 @@ def topk_sample(logits, k: int, temperature: float = 1.0, seed: int = 0, step: i
         if k == 1 or temperature <= 0:
             tok = i[:, 0].contiguous()
         else:
+            if generator is None:
+                # as on the device, the noise is a function of (seed, step) - or of the {seed, draws so far} counter
+                base, n = (int(rng[0]), int(rng[1]) + int(step)) if rng is not None else (int(seed), int(step))
+                generator = torch.Generator().manual_seed(((base * 1000003) ^ (n * 7919 + 1)) % (2 ** 63))
             u = torch.rand(v.shape, generator=generator).clamp_min(1e-20)
             score = v / temperature - torch.log(-torch.log(u))
             tok = torch.gather(i, 1, score.argmax(-1, keepdim=True))[:, 0].contiguous()

@@ -4,9 +4,13 @@ Prometheus gauges under `/metrics`.
 The reference stops at the chat CLI (examples/llm); this is the small piece a deployment needs on top of
 `Engine.serve`.  Requests are collected for a short window (`batch_window_s`) or until `max_queue` of them wait, then
 run as one `Engine.serve` call, which batches them continuously on the device; requests that arrive while a batch runs
-wait for the next one.  `"stream": true` answers with server-sent events, one per decode block.  On a multi-rank job every rank calls `Server.run()`: rank 0 owns the socket and the queue and
-broadcasts each batch (token ids and budgets) so that all ranks enter `Engine.serve` with the same arguments; an idle
-tick is broadcast too, so that the heartbeat of `Comm.check_peers` keeps running while no request is in flight.
+wait for the next one.  `"stream": true` answers with server-sent events, one per decode block.  A request may set
+`temperature`, `top_k` (at most 128, the widest the sampler draws from) and `seed`; requests of one batch share their
+sampling settings, so a batch is the waiting requests whose settings equal those of the oldest one, and the others run
+in a later batch.  On a multi-rank job every rank calls `Server.run()`: rank 0 owns the socket and the queue and
+broadcasts each batch (token ids, budgets, sampling settings) so that all ranks enter `Engine.serve` with the same
+arguments; an idle tick is broadcast too, so that the heartbeat of `Comm.check_peers` keeps running while no request is
+in flight.
 
     python examples/llm/serve.py --model=/models/Llama-3.1-8B-Instruct --port=8000
     curl -s localhost:8000/v1/completions -d '{"prompt": "The capital of France is", "max_tokens": 16}'
@@ -26,6 +30,9 @@ from ..models import hub
 from ..models.common import SamplingStrategy
 
 
+MAX_TOP_K = 128          # the sampling kernel keeps at most this many candidates per row
+
+
 @dataclass
 class _Request:
     ids: list
@@ -39,6 +46,7 @@ class _Request:
     finished: float = 0.0
     stream: bool = False
     chunks: "queue.Queue" = field(default_factory=queue.Queue)       # (new tokens, finished) per decode block
+    sampling: tuple = (1, 1.0, 0)                                    # (top-k, temperature, seed)
 
 
 @dataclass
@@ -69,10 +77,42 @@ class Server:
         self._stop = threading.Event()
         self._httpd: Optional[http.server.ThreadingHTTPServer] = None
         self.rank = comm.rank if comm is not None else 0
+        self._held: list = []                    # requests taken off the queue whose sampling settings differed from their batch's
 
     # ------------------------------------------------------------------ request handling (rank 0)
     def _limit(self) -> int:
         return self.engine.max_pages * self.engine.page_size
+
+    def waiting(self) -> int:
+        return self.queue.qsize() + len(self._held)
+
+    def _sampling(self, body: dict) -> tuple:
+        """(top-k, temperature, seed) of a request.  Without `temperature` and `top_k` the server's strategy applies;
+        `temperature: 0` is greedy; a positive temperature without `top_k` draws from the server's k when that is more
+        than 1, else from the MAX_TOP_K best tokens."""
+        k, t = None, None
+        if body.get("temperature") is not None:
+            t = body["temperature"]
+            if isinstance(t, bool) or not isinstance(t, (int, float)) or t < 0 or t != t:
+                raise ValueError("'temperature' must be a number >= 0")
+            t = float(t)
+        if body.get("top_k") is not None:
+            k = body["top_k"]
+            if isinstance(k, bool) or not isinstance(k, int) or k == 0 or k < -1:
+                raise ValueError("'top_k' must be a positive integer (or -1 for the widest supported)")
+            k = MAX_TOP_K if k == -1 else min(k, MAX_TOP_K)
+        seed = body.get("seed", 0)
+        if seed is None:
+            seed = 0
+        if isinstance(seed, bool) or not isinstance(seed, int):
+            raise ValueError("'seed' must be an integer")
+        if t is None and k is None:
+            return int(self.strategy.topk), float(self.strategy.temperature), int(seed)
+        if t == 0.0:
+            return 1, 1.0, int(seed)
+        if k is None:
+            k = int(self.strategy.topk) if self.strategy.topk > 1 else MAX_TOP_K
+        return int(k), float(self.strategy.temperature if t is None else t), int(seed)
 
     def submit(self, body: dict, chat: bool) -> _Request:
         """Validates a request body and queues it; raises ValueError with the message for a 400 answer."""
@@ -103,9 +143,11 @@ class Server:
             raise ValueError("'max_tokens' must be at least 1")
         if len(ids) + max_tokens > self._limit():
             raise ValueError(f"prompt ({len(ids)} tokens) + max_tokens ({max_tokens}) exceeds the engine's limit of {self._limit()} tokens")
-        if self.queue.qsize() >= self.max_queue:
+        sampling = self._sampling(body)
+        if self.waiting() >= self.max_queue:
             raise OverflowError("the request queue is full")
-        r = _Request(ids, max_tokens, chat, str(body.get("model", self.model_name)), stream=bool(body.get("stream", False)))
+        r = _Request(ids, max_tokens, chat, str(body.get("model", self.model_name)), stream=bool(body.get("stream", False)),
+                     sampling=sampling)
         self.queue.put(r)
         return r
 
@@ -129,7 +171,7 @@ class Server:
         rows = [("zml_server_requests_total", "counter", s.requests), ("zml_server_requests_failed_total", "counter", s.failed),
                 ("zml_server_batches_total", "counter", s.batches), ("zml_server_prompt_tokens_total", "counter", s.prompt_tokens),
                 ("zml_server_output_tokens_total", "counter", s.output_tokens), ("zml_server_busy_seconds_total", "counter", round(s.busy_s, 6)),
-                ("zml_server_queue_length", "gauge", self.queue.qsize()), ("zml_server_last_batch_size", "gauge", s.last_batch),
+                ("zml_server_queue_length", "gauge", self.waiting()), ("zml_server_last_batch_size", "gauge", s.last_batch),
                 ("zml_server_last_batch_tokens_per_second", "gauge", round(s.last_tok_s, 3))]
         return "".join(f"# TYPE {n} {k}\n{n} {v}\n" for n, k, v in rows)
 
@@ -152,7 +194,7 @@ class Server:
 
             def do_GET(self):
                 if self.path.startswith("/health"):
-                    return self._send(200, {"status": "ok", "queue": server.queue.qsize()})
+                    return self._send(200, {"status": "ok", "queue": server.waiting()})
                 if self.path.startswith("/metrics"):
                     return self._send(200, server.metrics(), "text/plain; version=0.0.4")
                 if self.path.startswith("/v1/models"):
@@ -221,31 +263,37 @@ class Server:
 
     # ------------------------------------------------------------------ scheduling (every rank)
     def _next_batch(self) -> Optional[list]:
-        """Rank 0: requests to run now - the first one that arrives, plus what follows within the batching window."""
-        try:
-            first = self.queue.get(timeout=self.idle_tick_s)
-        except queue.Empty:
-            return None
-        batch = [first]
-        deadline = time.perf_counter() + self.batch_window_s
-        while len(batch) < self.max_queue:
+        """Rank 0: requests to run now - the oldest waiting one, plus what follows within the batching window and has
+        the same sampling settings; the others are held for a later batch, ahead of newer arrivals."""
+        found, self._held = self._held, []
+        if not found:
+            try:
+                found = [self.queue.get(timeout=self.idle_tick_s)]
+            except queue.Empty:
+                return None
+            deadline = time.perf_counter() + self.batch_window_s
+        else:
+            deadline = time.perf_counter()                   # held requests have waited a batch already
+        while len(found) < self.max_queue:
             left = deadline - time.perf_counter()
             try:
-                batch.append(self.queue.get(timeout=max(left, 0.0)) if left > 0 else self.queue.get_nowait())
+                found.append(self.queue.get(timeout=max(left, 0.0)) if left > 0 else self.queue.get_nowait())
             except queue.Empty:
                 break
+        batch = [r for r in found if r.sampling == found[0].sampling]
+        self._held = [r for r in found if r.sampling != found[0].sampling]
         return batch
 
     def step(self) -> bool:
         """One scheduling round on every rank: wait for a batch (rank 0), share it, run it.  Returns False once
         `shutdown` was called (on every rank)."""
         batch = self._next_batch() if self.rank == 0 else None
-        msg = ("stop", None, None) if self._stop.is_set() and batch is None else \
-              ("run", [r.ids for r in batch], [r.max_tokens for r in batch]) if batch else ("idle", None, None)
+        msg = ("stop", None, None, None) if self._stop.is_set() and batch is None else \
+              ("run", [r.ids for r in batch], [r.max_tokens for r in batch], batch[0].sampling) if batch else ("idle", None, None, None)
         if self.comm is not None and self.comm.world > 1:
             msg = self.comm.broadcast_object(msg if self.rank == 0 else None)
             self.comm.check_peers()
-        kind, prompts, budgets = msg
+        kind, prompts, budgets, sampling = msg
         if kind == "stop":
             return False
         if kind == "idle":
@@ -257,7 +305,9 @@ class Server:
                 if batch[i].stream:
                     batch[i].chunks.put((list(toks), fin))
         try:
-            outs, _ = self.engine.serve(prompts, budgets, self.strategy, self.eos_ids, on_tokens=on_tokens)
+            topk, temperature, seed = sampling
+            outs, _ = self.engine.serve(prompts, budgets, SamplingStrategy(topk=topk, temperature=temperature), self.eos_ids,
+                                        seed=seed, on_tokens=on_tokens)
             err = None
         except Exception as e:                  # noqa: BLE001 - reported to the callers, the server keeps running
             outs, err = [[] for _ in prompts], f"{type(e).__name__}: {e}"
