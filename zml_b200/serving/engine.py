@@ -118,6 +118,7 @@ class Engine:
         self.use_graphs = self.on_gpu if use_graphs is None else (use_graphs and self.on_gpu)
         self.history_steps = history_steps
         self._graphs: dict = {}
+        self.max_graphs = 64                     # captured decode graphs kept (one per batch bucket x sampling settings)
         self._next_rid = 0
         self.seed = 0
         i32 = dict(dtype=torch.int32, device=self.device)
@@ -278,6 +279,8 @@ class Engine:
         key = (b, strategy.topk, float(strategy.temperature), num_splits)
         g = self._graphs.get(key)
         if g is None:
+            while len(self._graphs) >= self.max_graphs:          # sampling settings come from requests: bound the cache
+                self._graphs.pop(next(iter(self._graphs)))        # oldest capture first; its memory pool goes with it
             # warm up on a side stream (lazy kernel attributes, allocator), then capture
             saved = [t.clone() for t in (self.d_ids, self.d_pos, self.d_seq, self.d_slot, self.d_step, self.d_hist,
                                          self.d_sslot, self.d_rng)]

@@ -95,7 +95,7 @@ class Server:
             t = body["temperature"]
             if isinstance(t, bool) or not isinstance(t, (int, float)) or t < 0 or t != t:
                 raise ValueError("'temperature' must be a number >= 0")
-            t = float(t)
+            t = round(float(t), 2)                  # a decode graph is captured per setting: keep their number small
         if body.get("top_k") is not None:
             k = body["top_k"]
             if isinstance(k, bool) or not isinstance(k, int) or k == 0 or k < -1:
