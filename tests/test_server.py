@@ -278,3 +278,64 @@ def test_server_sampled_request_matches_the_engine_with_the_same_settings():
     assert r.tokens == want[0]
     want_greedy, _ = ref.serve([[0] + tok.encode("hello world")], 6, SamplingStrategy(), (3,))
     assert greedy.tokens == want_greedy[0]
+
+
+def test_server_stop_strings_cut_the_answer_streamed_or_not():
+    tok = _tokenizer()
+    text = "hello world the quick brown fox jumps over the lazy dog"
+    ids = tok.encode(text)
+    assert tok.decode(ids) == text
+
+    class Scripted:
+        """Answers every request with the tokens of `text`, in blocks of two tokens."""
+        max_pages, page_size = 64, 16
+
+        def serve(self, prompts, budgets, strategy, eos_ids, seed=0, on_tokens=None):
+            outs = [ids[:b] for b in budgets]
+            if on_tokens:
+                for i, o in enumerate(outs):
+                    for j in range(0, len(o), 2):
+                        on_tokens(i, o[j:j + 2], j + 2 >= len(o))
+            return outs, None
+
+    server = Server(Scripted(), tok, bos=0, eos_ids=(3,), batch_window_s=0.0, idle_tick_s=0.01, default_max_tokens=len(ids))
+    host, port = server.start_http("127.0.0.1", 0)
+    base = f"http://{host}:{port}"
+    loop = threading.Thread(target=server.run, daemon=True)
+    loop.start()
+    try:
+        code, body = _post(base, "/v1/completions", {"prompt": "x"})
+        assert code == 200 and body["choices"][0]["text"] == text and body["choices"][0]["finish_reason"] == "length"
+        code, body = _post(base, "/v1/completions", {"prompt": "x", "stop": " brown"})
+        assert body["choices"][0]["text"] == "hello world the quick" and body["choices"][0]["finish_reason"] == "stop"
+        assert body["usage"]["completion_tokens"] == len(ids)                    # generation is not cut short, the answer is
+        code, body = _post(base, "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "stop": ["lazy", "fox", "never"]})
+        assert body["choices"][0]["message"]["content"] == "hello world the quick brown " and body["choices"][0]["finish_reason"] == "stop"
+        code, body = _post(base, "/v1/completions", {"prompt": "x", "stop": ["zebra"]})
+        assert body["choices"][0]["text"] == text and body["choices"][0]["finish_reason"] == "length"
+        for bad in ("", [""], [1], ["a"] * 9, 5, {"a": 1}):
+            code, body = _post(base, "/v1/completions", {"prompt": "x", "stop": bad})
+            assert code == 400 and "stop" in body["error"]["message"]
+
+        def stream(payload):
+            req = urllib.request.Request(base + "/v1/completions", data=json.dumps(dict(payload, stream=True)).encode())
+            events = []
+            with urllib.request.urlopen(req, timeout=60) as resp:
+                for line in resp:
+                    line = line.decode().strip()
+                    if line.startswith("data: "):
+                        events.append(line[6:])
+            assert events[-1] == "[DONE]"
+            chunks = [json.loads(e)["choices"][0] for e in events[:-1]]
+            return "".join(c["text"] for c in chunks), [c["finish_reason"] for c in chunks]
+
+        got, reasons = stream({"prompt": "x"})
+        assert got == text and reasons[-1] == "length" and all(r is None for r in reasons[:-1]) and len(reasons) > 2
+        # a stop string that straddles two blocks is still found, and nothing of it is sent
+        got, reasons = stream({"prompt": "x", "stop": ["ck brown f"]})
+        assert got == "hello world the qui" and reasons[-1] == "stop" and all(r is None for r in reasons[:-1])
+        got, reasons = stream({"prompt": "x", "stop": ["zebra crossing"]})
+        assert got == text and reasons[-1] == "length"
+    finally:
+        server.shutdown()
+        loop.join(timeout=10)

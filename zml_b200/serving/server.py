@@ -5,8 +5,8 @@ The reference stops at the chat CLI (examples/llm); this is the small piece a de
 `Engine.serve`.  Requests are collected for a short window (`batch_window_s`) or until `max_queue` of them wait, then
 run as one `Engine.serve` call, which batches them continuously on the device; requests that arrive while a batch runs
 wait for the next one.  `"stream": true` answers with server-sent events, one per decode block.  A request may set
-`temperature`, `top_k` (at most 128, the widest the sampler draws from) and `seed`; requests of one batch share their
-sampling settings, so a batch is the waiting requests whose settings equal those of the oldest one, and the others run
+`stop` (strings that end the answer), `temperature`, `top_k` (at most 128, the widest the sampler draws from) and
+`seed`; requests of one batch share their sampling settings, so a batch is the waiting requests whose settings equal those of the oldest one, and the others run
 in a later batch.  On a multi-rank job every rank calls `Server.run()`: rank 0 owns the socket and the queue and
 broadcasts each batch (token ids, budgets, sampling settings) so that all ranks enter `Engine.serve` with the same
 arguments; an idle tick is broadcast too, so that the heartbeat of `Comm.check_peers` keeps running while no request is
@@ -31,6 +31,14 @@ from ..models.common import SamplingStrategy
 
 
 MAX_TOP_K = 128          # the sampling kernel keeps at most this many candidates per row
+MAX_STOP = 8             # stop strings per request
+
+
+def _first_stop(text: str, stops) -> int:
+    """Offset of the earliest occurrence of any stop string, or -1.  Generation is not cut short (every rank runs the
+    batch to its budgets); the answer is."""
+    hits = [i for i in (text.find(s) for s in stops) if i >= 0]
+    return min(hits) if hits else -1
 
 
 @dataclass
@@ -47,6 +55,7 @@ class _Request:
     stream: bool = False
     chunks: "queue.Queue" = field(default_factory=queue.Queue)       # (new tokens, finished) per decode block
     sampling: tuple = (1, 1.0, 0)                                    # (top-k, temperature, seed)
+    stop: tuple = ()                                                 # strings that end the answer (not included in it)
 
 
 @dataclass
@@ -144,10 +153,14 @@ class Server:
         if len(ids) + max_tokens > self._limit():
             raise ValueError(f"prompt ({len(ids)} tokens) + max_tokens ({max_tokens}) exceeds the engine's limit of {self._limit()} tokens")
         sampling = self._sampling(body)
+        stop = body.get("stop")
+        stop = () if stop is None else (stop,) if isinstance(stop, str) else tuple(stop) if isinstance(stop, list) else None
+        if stop is None or len(stop) > MAX_STOP or not all(isinstance(x, str) and x for x in stop):
+            raise ValueError(f"'stop' must be a non-empty string or a list of at most {MAX_STOP} of them")
         if self.waiting() >= self.max_queue:
             raise OverflowError("the request queue is full")
         r = _Request(ids, max_tokens, chat, str(body.get("model", self.model_name)), stream=bool(body.get("stream", False)),
-                     sampling=sampling)
+                     sampling=sampling, stop=stop)
         self.queue.put(r)
         return r
 
@@ -157,6 +170,9 @@ class Server:
         if toks and toks[-1] in self.eos_ids:
             toks, finish = toks[:-1], "stop"
         text = self.tok.decode(toks)
+        cut = _first_stop(text, r.stop)
+        if cut >= 0:
+            text, finish = text[:cut], "stop"
         usage = {"prompt_tokens": len(r.ids), "completion_tokens": len(r.tokens), "total_tokens": len(r.ids) + len(r.tokens)}
         rid, created = uuid.uuid4().hex[:24], int(time.time())
         if r.chat:
@@ -242,6 +258,8 @@ class Server:
                     self.wfile.flush()
                 try:
                     finish = "length"
+                    held = ""                               # text kept back: it may be the beginning of a stop string
+                    keep = max((len(x) for x in r.stop), default=1) - 1
                     while True:
                         toks, fin = r.chunks.get()
                         if toks is None:                    # the batch failed
@@ -249,7 +267,13 @@ class Server:
                             break
                         if fin and toks and toks[-1] in server.eos_ids:
                             toks, finish = toks[:-1], "stop"
-                        text = "".join(dec.feed_one(t) for t in toks) + (dec.finalize() if fin else "")
+                        held += "".join(dec.feed_one(t) for t in toks) + (dec.finalize() if fin else "")
+                        cut = _first_stop(held, r.stop)
+                        if cut >= 0:                        # the answer ends here; the batch runs on without a reader
+                            event(held[:cut], "stop")
+                            break
+                        text = held if fin or keep == 0 else held[:max(len(held) - keep, 0)]
+                        held = held[len(text):]
                         if text or fin:
                             event(text, finish if fin else None)
                         if fin:
