@@ -339,3 +339,24 @@ def test_server_stop_strings_cut_the_answer_streamed_or_not():
     finally:
         server.shutdown()
         loop.join(timeout=10)
+
+
+def test_tokenize_chat_equals_the_sessions_turn_by_turn_tokens_and_knows_roles():
+    from zml_b200.models import hub
+    tok = _tokenizer()
+    convo = [{"role": "user", "content": "hello world"}, {"role": "assistant", "content": "the fox"},
+             {"role": "user", "content": "lazy dog"}]
+    turn_by_turn = (hub.tokenize_prompt(tok, "hello world", "llama3", 0, True) + tok.encode("the fox")
+                    + hub.tokenize_prompt(tok, "lazy dog", "llama3", 0, False))
+    assert hub.tokenize_chat(tok, convo, "llama3", 0) == turn_by_turn
+    assert hub.tokenize_chat(tok, convo[:1], "llama3", 0) == hub.tokenize_prompt(tok, "hello world", "llama3", 0, True)
+    sh, eh, eot = (tok.token_id(t) for t in ("<|start_header_id|>", "<|end_header_id|>", "<|eot_id|>"))
+    with_system = hub.tokenize_chat(tok, [{"role": "system", "content": "quick"}] + convo[:1], "llama3", 0)
+    nl = tok.encode("\n")
+    assert with_system[:2] == [0, sh] and with_system[2:2 + len(tok.encode("system"))] == tok.encode("system")
+    assert with_system == [0, sh] + tok.encode("system") + [eh] + nl + tok.encode("quick") + [eot] + nl + \
+        hub.tokenize_prompt(tok, "hello world", "llama3", None, True)
+    # a vocabulary without the ChatML markers: the contents, concatenated
+    assert hub.tokenize_chat(tok, convo, "chatml", None) == tok.encode("hello world") + tok.encode("the fox") + tok.encode("lazy dog")
+    with pytest.raises(ValueError, match="unknown role"):
+        hub.tokenize_chat(tok, [{"role": "narrator", "content": "x"}], "llama3", 0)

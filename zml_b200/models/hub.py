@@ -93,3 +93,34 @@ def tokenize_prompt(tok: Tokenizer, prompt: str, template: str, bos: Optional[in
     nl = tok.encode("\n")
     pre = [] if first_turn else [ime] + nl
     return pre + [ims] + tok.encode("user") + nl + tok.encode(prompt) + [ime] + nl + [ims] + tok.encode("assistant") + nl
+
+
+CHAT_ROLES = ("system", "user", "assistant", "tool")
+
+
+def tokenize_chat(tok: Tokenizer, messages, template: str, bos: Optional[int]) -> list[int]:
+    """A whole conversation - [{"role": "system" | "user" | "assistant" | "tool", "content": str}, ...] - in the same
+    token layout as `tokenize_prompt` builds turn by turn, ending with the header of the assistant's next turn.  A
+    conversation of user and assistant turns gives exactly the tokens the chat session accumulates."""
+    msgs = []
+    for m in messages:
+        role = str(m.get("role", "user"))
+        if role not in CHAT_ROLES:
+            raise ValueError(f"unknown role {role!r}; one of {', '.join(CHAT_ROLES)}")
+        msgs.append((role, str(m["content"])))
+    nl = tok.encode("\n")
+    if template == "llama3":
+        sh, eh, eot = tok.token_id("<|start_header_id|>"), tok.token_id("<|end_header_id|>"), tok.token_id("<|eot_id|>")
+        if None in (sh, eh, eot):
+            return ([bos] if bos is not None else []) + [t for _, c in msgs for t in tok.encode(c)]
+        out = [bos] if bos is not None else []
+        for role, content in msgs:
+            out += [sh] + tok.encode(role) + [eh] + nl + tok.encode(content) + [eot] + nl
+        return out + [sh] + tok.encode("assistant") + [eh] + nl
+    ims, ime = tok.token_id("<|im_start|>"), tok.token_id("<|im_end|>")
+    if None in (ims, ime):
+        return [t for _, c in msgs for t in tok.encode(c)]
+    out = []
+    for role, content in msgs:
+        out += [ims] + tok.encode(role) + nl + tok.encode(content) + [ime] + nl
+    return out + [ims] + tok.encode("assistant") + nl

@@ -129,14 +129,10 @@ class Server:
             msgs = body.get("messages")
             if not isinstance(msgs, list) or not msgs:
                 raise ValueError("'messages' must be a non-empty list")
-            ids: list = []
-            for i, m in enumerate(msgs):
-                if not isinstance(m, dict) or "content" not in m:
-                    raise ValueError("every message needs a 'content'")
-                if m.get("role", "user") == "assistant":
-                    ids += self.tok.encode(str(m["content"]))
-                else:
-                    ids += hub.tokenize_prompt(self.tok, str(m["content"]), self.template or "llama3", self.bos, first_turn=not ids)
+            for m in msgs:
+                if not isinstance(m, dict) or not isinstance(m.get("content"), str):
+                    raise ValueError("every message needs a 'content' string")
+            ids = hub.tokenize_chat(self.tok, msgs, self.template or "llama3", self.bos)
         else:
             prompt = body.get("prompt")
             if isinstance(prompt, list) and prompt and all(isinstance(t, int) for t in prompt):
