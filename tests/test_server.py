@@ -260,7 +260,11 @@ def test_server_batches_by_sampling_settings_and_validates_them():
                 {"top_k": 0}, {"top_k": 2.5}, {"top_k": -2}, {"seed": "x"}, {"seed": 1.5}):
         with pytest.raises(ValueError):
             server.submit(dict({"prompt": "hello"}, **bad), chat=False)
-    assert server.waiting() == 0
+    for unsupported in ({"n": 2}, {"best_of": 4}, {"logprobs": 5}, {"logprobs": True}, {"top_logprobs": 3}, {"echo": True}):
+        with pytest.raises(ValueError, match="not supported"):
+            server.submit(dict({"prompt": "hello"}, **unsupported), chat=False)
+    server.submit({"prompt": "hello", "n": 1, "logprobs": None, "echo": False, "best_of": 1, "logprobs": False}, chat=False)
+    assert server.waiting() == 1 and server.step() and server.waiting() == 0
 
 
 def test_server_sampled_request_matches_the_engine_with_the_same_settings():

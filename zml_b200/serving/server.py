@@ -148,6 +148,9 @@ class Server:
             raise ValueError("'max_tokens' must be at least 1")
         if len(ids) + max_tokens > self._limit():
             raise ValueError(f"prompt ({len(ids)} tokens) + max_tokens ({max_tokens}) exceeds the engine's limit of {self._limit()} tokens")
+        for key, neutral in (("n", 1), ("best_of", 1), ("logprobs", None), ("top_logprobs", None), ("echo", False)):
+            if body.get(key) not in (None, neutral, False if neutral is None else neutral):
+                raise ValueError(f"'{key}' is not supported")           # refused rather than silently ignored
         sampling = self._sampling(body)
         stop = body.get("stop")
         stop = () if stop is None else (stop,) if isinstance(stop, str) else tuple(stop) if isinstance(stop, list) else None
