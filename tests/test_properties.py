@@ -132,3 +132,23 @@ def _bpe():
                               trainers.BpeTrainer(vocab_size=400, initial_alphabet=pre_tokenizers.ByteLevel.alphabet()))
         _BPE = Tokenizer.from_bytes(t.to_str().encode(), backend="homemade")
     return _BPE
+
+
+@given(text=st.text(alphabet="ab c", max_size=40), stops=st.lists(st.text(alphabet="ab c", min_size=1, max_size=4), max_size=3),
+       cuts=st.lists(st.integers(0, 40), max_size=8))
+@settings(max_examples=300, deadline=None, derandomize=True)
+def test_streamed_stop_filter_equals_cutting_the_whole_text(text, stops, cuts):
+    """However the text is split into pieces, what the filter lets through adds up to the text cut at the first stop
+    string, nothing is sent after a stop, and a stop is reported exactly when the text holds one."""
+    from zml_b200.serving.server import StopFilter, _first_stop
+    bounds = sorted({min(c, len(text)) for c in cuts} | {0, len(text)})
+    pieces = [text[a:b] for a, b in zip(bounds, bounds[1:])] or [""]
+    f = StopFilter(stops)
+    sent, stopped = "", False
+    for i, piece in enumerate(pieces):
+        out, now = f.feed(piece, i == len(pieces) - 1)
+        assert not (stopped and out)
+        sent += out
+        stopped = stopped or now
+    cut = _first_stop(text, stops)
+    assert sent == (text if cut < 0 else text[:cut]) and stopped == (cut >= 0)

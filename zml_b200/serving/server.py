@@ -41,6 +41,30 @@ def _first_stop(text: str, stops) -> int:
     return min(hits) if hits else -1
 
 
+class StopFilter:
+    """Cuts a text that arrives in pieces at the first stop string: `feed(piece, last)` returns (text that can be
+    sent now, whether a stop string was met).  The last len(longest stop) - 1 characters are kept back until more text
+    shows whether they begin a stop string; the pieces sent add up to the whole text cut at `_first_stop`."""
+
+    def __init__(self, stops):
+        self.stops = tuple(stops)
+        self.keep = max((len(x) for x in self.stops), default=1) - 1
+        self.held = ""
+        self.stopped = False
+
+    def feed(self, piece: str, last: bool = False) -> tuple:
+        if self.stopped:
+            return "", True
+        self.held += piece
+        cut = _first_stop(self.held, self.stops)
+        if cut >= 0:
+            out, self.held, self.stopped = self.held[:cut], "", True
+            return out, True
+        out = self.held if last or self.keep == 0 else self.held[:max(len(self.held) - self.keep, 0)]
+        self.held = self.held[len(out):]
+        return out, False
+
+
 @dataclass
 class _Request:
     ids: list
@@ -257,8 +281,7 @@ class Server:
                     self.wfile.flush()
                 try:
                     finish = "length"
-                    held = ""                               # text kept back: it may be the beginning of a stop string
-                    keep = max((len(x) for x in r.stop), default=1) - 1
+                    stops = StopFilter(r.stop)
                     while True:
                         toks, fin = r.chunks.get()
                         if toks is None:                    # the batch failed
@@ -266,13 +289,10 @@ class Server:
                             break
                         if fin and toks and toks[-1] in server.eos_ids:
                             toks, finish = toks[:-1], "stop"
-                        held += "".join(dec.feed_one(t) for t in toks) + (dec.finalize() if fin else "")
-                        cut = _first_stop(held, r.stop)
-                        if cut >= 0:                        # the answer ends here; the batch runs on without a reader
-                            event(held[:cut], "stop")
+                        text, stopped = stops.feed("".join(dec.feed_one(t) for t in toks) + (dec.finalize() if fin else ""), fin)
+                        if stopped:                         # the answer ends here; the batch runs on without a reader
+                            event(text, "stop")
                             break
-                        text = held if fin or keep == 0 else held[:max(len(held) - keep, 0)]
-                        held = held[len(text):]
                         if text or fin:
                             event(text, finish if fin else None)
                         if fin:
