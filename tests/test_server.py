@@ -317,6 +317,21 @@ def test_server_stop_strings_cut_the_answer_streamed_or_not():
         assert body["choices"][0]["message"]["content"] == "hello world the quick brown " and body["choices"][0]["finish_reason"] == "stop"
         code, body = _post(base, "/v1/completions", {"prompt": "x", "stop": ["zebra"]})
         assert body["choices"][0]["text"] == text and body["choices"][0]["finish_reason"] == "length"
+        # token counting for clients: the ids a completion or a chat request would run with, and back to text
+        code, body = _post(base, "/tokenize", {"prompt": "hello world"})
+        assert code == 200 and body["tokens"] == [0] + tok.encode("hello world") and body["count"] == len(body["tokens"])
+        assert body["max_model_len"] == 64 * 16
+        code, plain = _post(base, "/tokenize", {"prompt": "hello world", "add_special_tokens": False})
+        assert plain["tokens"] == tok.encode("hello world")
+        code, back = _post(base, "/detokenize", {"tokens": plain["tokens"]})
+        assert code == 200 and back["prompt"] == "hello world"
+        from zml_b200.models import hub
+        msgs = [{"role": "system", "content": "quick"}, {"role": "user", "content": "fox"}]
+        code, body = _post(base, "/tokenize", {"messages": msgs})
+        assert code == 200 and body["tokens"] == hub.tokenize_chat(tok, msgs, "llama3", 0)
+        for route, bad in (("/tokenize", {}), ("/tokenize", {"prompt": 5}), ("/tokenize", {"messages": [{"role": "user"}]}),
+                           ("/detokenize", {"tokens": "abc"}), ("/detokenize", {"tokens": [1.5]})):
+            assert _post(base, route, bad)[0] == 400
         for bad in ("", [""], [1], ["a"] * 9, 5, {"a": 1}):
             code, body = _post(base, "/v1/completions", {"prompt": "x", "stop": bad})
             assert code == 400 and "stop" in body["error"]["message"]

@@ -1,5 +1,5 @@
-"""HTTP front end for an `Engine`: OpenAI-style `/v1/completions` and `/v1/chat/completions`, `/health`, and
-Prometheus gauges under `/metrics`.
+"""HTTP front end for an `Engine`: OpenAI-style `/v1/completions` and `/v1/chat/completions`, `/tokenize` and
+`/detokenize`, `/health`, and Prometheus gauges under `/metrics`.
 
 The reference stops at the chat CLI (examples/llm); this is the small piece a deployment needs on top of
 `Engine.serve`.  Requests are collected for a short window (`batch_window_s`) or until `max_queue` of them wait, then
@@ -240,7 +240,35 @@ class Server:
                     return self._send(200, {"object": "list", "data": [{"id": server.model_name, "object": "model"}]})
                 self._send(404, {"error": {"message": f"no route {self.path}"}})
 
+            def _tokens(self):
+                """`/tokenize` {"prompt": str} or {"messages": [...]} -> {"tokens", "count", "max_model_len"};
+                `/detokenize` {"tokens": [ids]} -> {"prompt"}: what a client needs to budget a request."""
+                try:
+                    body = json.loads(self.rfile.read(int(self.headers.get("Content-Length", 0))) or b"{}")
+                    if not isinstance(body, dict):
+                        raise ValueError("the body must be a JSON object")
+                    if self.path.startswith("/detokenize"):
+                        toks = body.get("tokens")
+                        if not isinstance(toks, list) or not all(isinstance(t, int) and not isinstance(t, bool) for t in toks):
+                            raise ValueError("'tokens' must be a list of token ids")
+                        return self._send(200, {"prompt": server.tok.decode(toks)})
+                    if isinstance(body.get("messages"), list) and body["messages"]:
+                        for m in body["messages"]:
+                            if not isinstance(m, dict) or not isinstance(m.get("content"), str):
+                                raise ValueError("every message needs a 'content' string")
+                        ids = hub.tokenize_chat(server.tok, body["messages"], server.template or "llama3", server.bos)
+                    elif isinstance(body.get("prompt"), str):
+                        ids = ([server.bos] if server.bos is not None and body.get("add_special_tokens", True) else []) + \
+                            server.tok.encode(body["prompt"])
+                    else:
+                        raise ValueError("give 'prompt' (a string) or 'messages'")
+                    self._send(200, {"tokens": ids, "count": len(ids), "max_model_len": server._limit()})
+                except (ValueError, json.JSONDecodeError) as e:
+                    self._send(400, {"error": {"message": str(e)}})
+
             def do_POST(self):
+                if self.path.startswith(("/tokenize", "/detokenize")):
+                    return self._tokens()
                 chat = self.path.startswith("/v1/chat/completions")
                 if not chat and not self.path.startswith("/v1/completions"):
                     return self._send(404, {"error": {"message": f"no route {self.path}"}})
