@@ -2,12 +2,12 @@
 """LLM CLI (the reference's `examples/llm`): load a HF-format checkpoint and chat with it.
 
     python examples/llm/main.py --model=<repo dir | .safetensors | index.json | hf://org/repo | s3://... | gs://... | https://...> [--prompt=...]
-        [--seqlen=2048] [--topk=1] [--temperature=1.0] [--seed=0] [--no-chat-template] [--profile]
+        [--system=...] [--seqlen=2048] [--topk=1] [--temperature=1.0] [--seed=0] [--no-chat-template] [--profile]
         [--backend=b200|vanilla|attnd] [--attnd-ip=IP:PORT]
 
 --backend picks the attention implementation (default: this library's paged kernels; `vanilla` is PyTorch SDPA on K/V
 gathered from the pages); --attnd-ip registers a remote attention daemon at IP:PORT and prefers it (dense decoder
-models, one conversation).
+models, one conversation).  --system puts a system message in front of the first turn (chat template only).
 
 Without --prompt an interactive chat loop starts (history in ~/.llm_chat_history).  For
 tensor / expert parallelism launch one process per GPU:
@@ -41,6 +41,7 @@ log = logging.getLogger("llm")
 class Args:
     model: str
     prompt: Optional[str] = None
+    system: Optional[str] = None
     seqlen: int = 2048
     topk: int = 1
     temperature: float = 1.0
@@ -55,9 +56,10 @@ class Args:
 
 
 class Chat:
-    def __init__(self, session: Session, tok, template: Optional[str], bos, rank: int, comm=None):
+    def __init__(self, session: Session, tok, template: Optional[str], bos, rank: int, comm=None, system: Optional[str] = None):
         self.session, self.tok, self.template, self.bos, self.rank = session, tok, template, bos, rank
         self.comm = comm
+        self.system = system
         self.first = True
 
     def run_once(self, prompt: str, max_new: Optional[int]) -> str:
@@ -65,6 +67,9 @@ class Chat:
             ids = [int(x) for x in prompt.split()]
         elif self.template is None:
             ids = self.tok.encode(prompt)
+        elif self.first and self.system:
+            ids = hub.tokenize_chat(self.tok, [{"role": "system", "content": self.system}, {"role": "user", "content": prompt}],
+                                    self.template, self.bos)
         else:
             ids = hub.tokenize_prompt(self.tok, prompt, self.template, self.bos, self.first)
         self.first = False
@@ -158,7 +163,7 @@ def main(argv=None) -> int:
     strategy = SamplingStrategy(topk=args.topk, temperature=args.temperature)
     session = Session(engine, args.seqlen, strategy, cfg.eos_ids(), args.seed)
     template = None if args.no_chat_template or tok is None else hub.chat_template(getattr(cfg, "model_type", "llama"))
-    chat = Chat(session, tok, template, getattr(cfg, "bos_token_id", None), comm.rank, comm)
+    chat = Chat(session, tok, template, getattr(cfg, "bos_token_id", None), comm.rank, comm, args.system)
     max_new = args.max_new_tokens or None
     prof = Profiler().start() if args.profile else None
     if args.prompt is not None:

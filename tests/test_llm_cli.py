@@ -51,6 +51,11 @@ def test_cli_prompt_mode(tmp_path):
                        capture_output=True, text=True, timeout=180)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "tok/s" in r.stdout and "Loaded weights" in r.stderr
+    # a system message changes the prompt the model sees (more prefill tokens; the run still succeeds)
+    s = subprocess.run([sys.executable, os.path.join(ROOT, "examples", "llm", "main.py"), f"--model={tmp_path}",
+                        "--prompt=hello world", "--system=the quick brown fox", "--seqlen=128", "--max-new-tokens=5", "--cpu"],
+                       capture_output=True, text=True, timeout=180)
+    assert s.returncode == 0 and "tok/s" in s.stdout, s.stderr[-2000:]
 
 
 _CHAT_WORKER = r"""
